@@ -1,0 +1,256 @@
+"""TEST INFRASTRUCTURE - eager restatements of the reference's repro graphs (the ground truth).
+
+The reference defines every fused region as a ``Repro(nn.Module)`` whose ``forward`` is the
+decomposed aten graph captured from a model (``repros/canonical/<id>/repro.py``), and accepts an
+oracle kernel when its outputs match that module on the same seeded inputs
+(``oracle_harness.py:926-963``). The classes below restate those graphs, op for op and with the
+same cast boundaries, for the families this backend covers. They run on any device torch supports;
+the tests and the benchmark's CPU-baseline leg run them on the CPU (and the harness runs them on
+the GPU next to the CUDA kernels, exactly as the reference's check does).
+
+Nothing outside ``tests/``, ``__graft_entry__.smoke()`` and ``bench.py``'s baseline legs may
+import this package: the product path never computes through it.
+
+Pinning: ``tests/golden/`` holds inputs and outputs produced by the reference's own repro modules
+and input generator in this repository's build container (``tests/golden/make_golden.py``);
+``tests/test_oracle_golden.py`` checks every class below against them.
+"""
+from __future__ import annotations
+
+import torch
+from torch import nn
+
+aten = torch.ops.aten
+prims = torch.ops.prims
+
+
+def _f32(t):
+    return prims.convert_element_type.default(t, torch.float32)
+
+
+class RowMean(nn.Module):
+    """x.mean over the last dim. Graph shape: reference repros/canonical/mean_c9e1a8113328/repro.py:23-27
+    (aten.mean.dim; accumulation is fp32, the result has the input dtype)."""
+
+    def forward(self, x):
+        return aten.mean.dim(x, [-1])
+
+
+class RowReduce(nn.Module):
+    """sum / amax / amin / mean over the last dim (aten.sum.dim_IntList, aten.amax, aten.amin)."""
+
+    def __init__(self, op: str, keepdim: bool = False):
+        super().__init__()
+        self.op, self.keepdim = op, keepdim
+
+    def forward(self, x):
+        if self.op == "sum":
+            return aten.sum.dim_IntList(x, [-1], self.keepdim)
+        if self.op == "mean":
+            return aten.mean.dim(x, [-1], self.keepdim)
+        if self.op == "amax":
+            return aten.amax.default(x, [-1], self.keepdim)
+        return aten.amin.default(x, [-1], self.keepdim)
+
+
+class LayerNormFwd(nn.Module):
+    """LayerNorm forward returning (y, mean, rstd).
+
+    Graph: reference repros/canonical/var_mean_f8ec553e339e/repro.py:23-37 (var_mean with
+    correction 0, add eps, rsqrt, sub, mul, mul weight, add bias, cast), with a leading cast to
+    fp32 for 16-bit inputs as in var_mean_af505388b035/repro.py:33-40.
+    """
+
+    def __init__(self, eps: float, out_dtype: torch.dtype, squeeze_stats: bool = True):
+        super().__init__()
+        self.eps, self.out_dtype, self.squeeze_stats = eps, out_dtype, squeeze_stats
+
+    def forward(self, x, weight, bias):
+        xf = _f32(x) if x.dtype != torch.float32 else x
+        var_mean = aten.var_mean.correction(xf, [-1], correction=0, keepdim=True)
+        var, mean = var_mean[0], var_mean[1]
+        rstd = aten.rsqrt.default(aten.add.Tensor(var, self.eps))
+        sub = aten.sub.Tensor(xf, mean)
+        mul = aten.mul.Tensor(sub, rstd)
+        mul_1 = aten.mul.Tensor(mul, weight)
+        add_1 = aten.add.Tensor(mul_1, bias)
+        y = prims.convert_element_type.default(add_1, self.out_dtype)
+        if self.squeeze_stats:
+            mean = aten.squeeze.dim(mean, -1)
+            rstd = aten.squeeze.dim(rstd, -1)
+        return (y, mean, rstd)
+
+
+class RMSNormFwd(nn.Module):
+    """RMSNorm forward. Graph: reference repros/canonical/mean_f667cd8901af/repro.py:23-33."""
+
+    def __init__(self, eps: float, out_dtype: torch.dtype):
+        super().__init__()
+        self.eps, self.out_dtype = eps, out_dtype
+
+    def forward(self, x, weight):
+        xf = _f32(x)
+        pow_1 = aten.pow.Tensor_Scalar(xf, 2)
+        mean = aten.mean.dim(pow_1, [-1], True)
+        rsqrt = aten.rsqrt.default(aten.add.Tensor(mean, self.eps))
+        mul = aten.mul.Tensor(xf, rsqrt)
+        mul_1 = aten.mul.Tensor(mul, weight)
+        return prims.convert_element_type.default(mul_1, self.out_dtype)
+
+
+class MaskedScaledSoftmax(nn.Module):
+    """softmax(float(scores * scale + mask), -1) cast back to the input dtype.
+
+    Graph: reference repros/canonical/amax_sum_20ccc18dda60/repro.py:23-36 (16-bit add, cast to
+    fp32, amax, sub, exp, sum, div, cast), with the attention-scale multiply in front; the multiply
+    and the add run in the input dtype, so their results are rounded to it.
+    """
+
+    def __init__(self, scale: float | None = None, log: bool = False,
+                 out_dtype: torch.dtype | None = None):
+        super().__init__()
+        self.scale, self.log, self.out_dtype = scale, log, out_dtype
+
+    def forward(self, scores, mask=None):
+        t = scores
+        if self.scale is not None:
+            t = aten.mul.Tensor(t, self.scale)
+        if mask is not None:
+            t = aten.add.Tensor(t, mask)
+        f = _f32(t) if t.dtype != torch.float32 else t
+        amax = aten.amax.default(f, [-1], True)
+        sub = aten.sub.Tensor(f, amax)
+        if self.log:
+            exp = aten.exp.default(sub)
+            sum_1 = aten.sum.dim_IntList(exp, [-1], True)
+            out = aten.sub.Tensor(sub, aten.log.default(sum_1))
+        else:
+            exp = aten.exp.default(sub)
+            sum_1 = aten.sum.dim_IntList(exp, [-1], True)
+            out = aten.div.Tensor(exp, sum_1)
+        return prims.convert_element_type.default(out, self.out_dtype or scores.dtype)
+
+
+class BatchNormReluFwd(nn.Module):
+    """BatchNorm2d training forward + ReLU with running-stat update.
+
+    Graph: reference repros/canonical/var_mean_42fad1ece813/repro.py:23-58 - fp32 var_mean over
+    (N,H,W), rsqrt(var+eps), (x-mean)*rstd*w+b, cast to the input dtype, ReLU after the cast,
+    running_mean = mean*m + rm*(1-m), running_var = var*unbiased*m + rv*(1-m), both written back
+    with copy_. Returns (y, mean, invstd, running_mean, running_var).
+    """
+
+    def __init__(self, eps: float, momentum: float, relu: bool = True):
+        super().__init__()
+        self.eps, self.momentum, self.relu = eps, momentum, relu
+
+    def forward(self, x, running_mean, running_var, weight, bias):
+        n = x.numel() // x.shape[1]
+        xf = _f32(x) if x.dtype != torch.float32 else x
+        var_mean = aten.var_mean.correction(xf, [0, 2, 3], correction=0, keepdim=True)
+        var, mean = var_mean[0], var_mean[1]
+        rsqrt = aten.rsqrt.default(aten.add.Tensor(var, self.eps))
+        sub = aten.sub.Tensor(x, mean)
+        mul = aten.mul.Tensor(sub, rsqrt)
+        mean_c = aten.squeeze.dims(mean, [0, 2, 3])
+        invstd_c = aten.squeeze.dims(rsqrt, [0, 2, 3])
+        new_rm = aten.add.Tensor(aten.mul.Tensor(mean_c, self.momentum),
+                                 aten.mul.Tensor(running_mean, 1 - self.momentum))
+        var_c = aten.squeeze.dims(var, [0, 2, 3])
+        unbiased = aten.mul.Tensor(var_c, n / (n - 1))
+        new_rv = aten.add.Tensor(aten.mul.Tensor(unbiased, self.momentum),
+                                 aten.mul.Tensor(running_var, 1 - self.momentum))
+        w4 = aten.unsqueeze.default(aten.unsqueeze.default(weight, -1), -1)
+        b4 = aten.unsqueeze.default(aten.unsqueeze.default(bias, -1), -1)
+        y = aten.add.Tensor(aten.mul.Tensor(mul, w4), b4)
+        y = prims.convert_element_type.default(y, x.dtype)
+        if self.relu:
+            y = aten.relu.default(y)
+        rm_out = aten.copy_.default(running_mean, new_rm)
+        rv_out = aten.copy_.default(running_var, new_rv)
+        return (y, mean_c, invstd_c, rm_out, rv_out)
+
+
+class RMSNormBwdHeadTranspose(nn.Module):
+    """RMSNorm backward producing dx in head-major layout and dweight.
+
+    Graph: reference repros/canonical/sum_sum_2cd99e5eb23e/repro.py:23-46 (the genai RMSNorm
+    backward: g = dy*w, dx = g*rstd + (sum(g*x) * -0.5 * rstd^3 / n) * (2x), dw = sum_rows(dy * (x*rstd)))
+    followed by the head split of pointwise_c0d19d490a2f/repro.py (view [B,S,H,D], permute to
+    [B,H,S,D], contiguous clone).
+    """
+
+    def __init__(self, heads: int):
+        super().__init__()
+        self.heads = heads
+
+    def forward(self, x, dy, weight, rstd):
+        b, s, h, d = x.shape
+        n = h * d
+        xf = _f32(aten.view.default(x, [b * s, n]))
+        dyf = _f32(aten.view.default(dy, [b * s, n]))
+        r = aten.view.default(rstd, [b * s, 1])
+        mul = aten.mul.Tensor(dyf, weight)
+        mul_1 = aten.mul.Tensor(mul, r)
+        mul_2 = aten.mul.Tensor(mul, xf)
+        sum_1 = aten.sum.dim_IntList(mul_2, [1], True)
+        mul_3 = aten.mul.Scalar(sum_1, -0.5)
+        pow_1 = aten.pow.Tensor_Scalar(r, 3)
+        mul_4 = aten.mul.Tensor(mul_3, pow_1)
+        expand_1 = aten.expand.default(mul_4, [b * s, n])
+        div = aten.div.Scalar(expand_1, n)
+        pow_2 = aten.pow.Tensor_Scalar(xf, 1.0)
+        mul_5 = aten.mul.Scalar(pow_2, 2.0)
+        mul_6 = aten.mul.Tensor(div, mul_5)
+        add = aten.add.Tensor(mul_1, mul_6)
+        dx = prims.convert_element_type.default(add, x.dtype)
+        dx = aten.view.default(dx, [b, s, h, d])
+        dx = aten.permute.default(dx, [0, 2, 1, 3])
+        dx = aten.clone.default(dx, memory_format=torch.contiguous_format)
+        mul_7 = aten.mul.Tensor(xf, r)
+        mul_8 = aten.mul.Tensor(dyf, mul_7)
+        sum_2 = aten.sum.dim_IntList(mul_8, [0], True)
+        dw = aten.view.default(sum_2, [n])
+        return (dx, dw)
+
+
+class ColumnSum(nn.Module):
+    """[R, H] -> [H] sum over rows. Graph: reference repros/canonical/sum_eb86a17deab9/repro.py
+    (aten.sum.dim_IntList over dim 0)."""
+
+    def __init__(self, op: str = "sum"):
+        super().__init__()
+        self.op = op
+
+    def forward(self, x):
+        if self.op == "mean":
+            return aten.mean.dim(x, [0])
+        if self.op == "amax":
+            return aten.amax.default(x, [0])
+        return aten.sum.dim_IntList(x, [0])
+
+
+class HeadSplitPermute(nn.Module):
+    """[B*S, H*D] -> [B, H, S, D] contiguous copy. Graph: reference
+    repros/canonical/pointwise_c0d19d490a2f/repro.py (view, permute, clone)."""
+
+    def __init__(self, b: int, s: int, h: int, d: int, scale: float | None = None):
+        super().__init__()
+        self.dims, self.scale = (b, s, h, d), scale
+
+    def forward(self, x):
+        b, s, h, d = self.dims
+        v = aten.view.default(x, [b, s, h, d])
+        if self.scale is not None:
+            v = aten.mul.Tensor(v, self.scale)
+        p = aten.permute.default(v, [0, 2, 1, 3])
+        return aten.clone.default(p, memory_format=torch.contiguous_format)
+
+
+class Transpose2D(nn.Module):
+    """[..., P, C] -> [..., C, P] contiguous copy (reference
+    repros/canonical/pointwise_021e90d9c17d/repro.py: permute + clone)."""
+
+    def forward(self, x):
+        p = aten.transpose.int(x, -1, -2)
+        return aten.clone.default(p, memory_format=torch.contiguous_format)
