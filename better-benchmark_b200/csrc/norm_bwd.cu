@@ -1,0 +1,496 @@
+// LayerNorm / RMSNorm backward: dx rows plus the dweight (and dbias) column reductions, in one
+// pass over x and dy, with an optional head-major (B,S,H,D) -> (B,H,S,D) store of dx.
+//
+// Replaces the "mix-order" Triton kernels of the norm-backward repros in the reference
+// (repros/canonical/sum_sum_2cd99e5eb23e/oracle.py:48-117 for RMSNorm,
+// sum_sum_sum_3cac3bbf4e8f/oracle.py:100-193 for LayerNorm) and fuses the head split of
+// pointwise_c0d19d490a2f/oracle.py:10-33 into the dx store.
+//
+// Evaluation order, as the decomposed aten graphs have it (g = dy * w):
+//   RMSNorm  : dx = g*rstd + (((sum_row(g*x) * -0.5) * rstd^3) / n) * (x*2)
+//              dw = sum_rows(dy * (x*rstd))
+//   LayerNorm: xhat = (x-mean)*rstd
+//              dx = (rstd/n) * ((g*n - sum_row(g)) - xhat*sum_row(g*xhat))
+//              dw = sum_rows(dy * xhat),  db = sum_rows(dy)
+//
+// Structure: a persistent grid; each group of threads (a CTA for long rows, a warp for short
+// ones) walks rows group, group+G, ..., keeps the next row's loads in flight while it reduces the
+// current one, and accumulates its columns of dw/db in registers over all its rows. Each group
+// then writes one fp32 partial row to scratch; after a grid-wide barrier (cooperative launch)
+// the partial rows are summed in fp64, in a fixed order, into dw/db. No atomics: results are
+// bit-reproducible. A two-launch variant (main + finalize) does the same without the barrier.
+#include "rowwise.cuh"
+
+namespace b200 {
+
+struct NormBwdParams {
+  const void* x;
+  const void* dy;
+  const void* w;      // may be null (treated as ones)
+  const float* mean;  // LayerNorm only
+  const float* rstd;
+  void* dx;
+  float* dw;  // may be null
+  float* db;  // may be null
+  long long rows;
+  int n;
+  long long x_row_stride, dy_row_stride;
+  int w_dtype;
+  // dx element (r, c) lives at (r / seq) * dx_batch_stride + (r % seq) * dx_seq_stride
+  //                            + (c / head_dim) * dx_head_stride + (c % head_dim)
+  int seq, head_dim;
+  long long dx_batch_stride, dx_seq_stride, dx_head_stride;
+  float n_f;
+  float* partials;    // [groups][n] for dw, followed by [groups][n] for db
+  unsigned int* bar;  // grid barrier words (cooperative variant)
+  int groups;
+  int fused;  // 1: barrier + finalize inside this launch
+};
+
+template <int V>
+__device__ __forceinline__ void zero(float (&a)[V]) {
+#pragma unroll
+  for (int i = 0; i < V; ++i) a[i] = 0.f;
+}
+
+// Sum `groups` partial rows into out[0..n): each CTA takes 64-column chunks, its warps split the
+// partial rows, fp64 accumulation, fixed order.
+__device__ __forceinline__ void finalize_columns(const float* partials, int groups, int n, float* out,
+                                                 double* smem /* [warps][64] */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int chunks = (n + 63) / 64;
+  for (int chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
+    const int c0 = chunk * 64 + lane, c1 = c0 + 32;
+    double a0 = 0.0, a1 = 0.0;
+    for (int g = warp; g < groups; g += nwarps) {
+      const float* row = partials + (long long)g * n;
+      if (c0 < n) a0 += (double)__ldcg(row + c0);
+      if (c1 < n) a1 += (double)__ldcg(row + c1);
+    }
+    smem[warp * 64 + lane] = a0;
+    smem[warp * 64 + 32 + lane] = a1;
+    __syncthreads();
+    if (warp == 0) {
+      double s0 = 0.0, s1 = 0.0;
+      for (int w = 0; w < nwarps; ++w) {
+        s0 += smem[w * 64 + lane];
+        s1 += smem[w * 64 + 32 + lane];
+      }
+      if (c0 < n) out[c0] = (float)s0;
+      if (c1 < n) out[c1] = (float)s1;
+    }
+    __syncthreads();
+  }
+}
+
+template <typename T, int CH, bool BLOCK, bool LN>
+__global__ void __launch_bounds__(BLOCK ? 512 : 256)
+norm_bwd_kernel(const NormBwdParams p) {
+  constexpr int V = Elem<T>::V;
+  __shared__ float2 red[2][16];
+  __shared__ double fin[16 * 64];
+  __shared__ int bar_ok;
+  const int lane = group_lane<BLOCK>();
+  const int G = group_size<BLOCK>();
+  const int nv = p.n / V;
+  const long long group = BLOCK ? (long long)blockIdx.x
+                                : (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const long long group_stride = BLOCK ? (long long)gridDim.x : (long long)gridDim.x * (blockDim.x >> 5);
+
+  float acc_w[CH][V], acc_b[LN ? CH : 1][V];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) zero(acc_w[c]);
+#pragma unroll
+  for (int c = 0; c < (LN ? CH : 1); ++c) zero(acc_b[c]);
+
+  // column offsets of this thread's slots inside a dx row (head-major aware)
+  long long dx_col[CH];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int col = (c * G + lane) * V;
+    dx_col[c] = (long long)(col / p.head_dim) * p.dx_head_stride + (col % p.head_dim);
+  }
+
+  uint4 nx[CH], ny[CH];  // next row, in flight
+  long long row = group;
+  if (row < p.rows) {
+    const T* xr = reinterpret_cast<const T*>(p.x) + row * p.x_row_stride;
+    const T* yr = reinterpret_cast<const T*>(p.dy) + row * p.dy_row_stride;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int j = c * G + lane;
+      if (j < nv) {
+        nx[c] = ld_stream(xr + (long long)j * V);
+        ny[c] = ld_stream(yr + (long long)j * V);
+      }
+    }
+  }
+  int parity = 0;
+  // In block mode every thread of the CTA runs the same number of iterations (row is CTA-uniform),
+  // so the barrier inside the loop is safe.
+  while (row < p.rows) {
+    uint4 cx[CH], cy[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      cx[c] = nx[c];
+      cy[c] = ny[c];
+    }
+    const long long next = row + group_stride;
+    if (next < p.rows) {
+      const T* xr = reinterpret_cast<const T*>(p.x) + next * p.x_row_stride;
+      const T* yr = reinterpret_cast<const T*>(p.dy) + next * p.dy_row_stride;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const int j = c * G + lane;
+        if (j < nv) {
+          nx[c] = ld_stream(xr + (long long)j * V);
+          ny[c] = ld_stream(yr + (long long)j * V);
+        }
+      }
+    }
+    const float rstd = __ldg(p.rstd + row);
+    const float mean = LN ? __ldg(p.mean + row) : 0.f;
+
+    float xf[CH][V], gf[CH][V];
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int j = c * G + lane;
+      if (j < nv) {
+        float dyf[V], wf[V];
+        Elem<T>::unpack(cx[c], xf[c]);
+        Elem<T>::unpack(cy[c], dyf);
+        if (p.w) {
+          load_param<V>(p.w, p.w_dtype, (long long)j * V, wf);
+        } else {
+#pragma unroll
+          for (int i = 0; i < V; ++i) wf[i] = 1.f;
+        }
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          if constexpr (LN) {
+            xf[c][i] = (xf[c][i] - mean) * rstd;  // xhat
+            gf[c][i] = dyf[i] * wf[i];
+            s1 += gf[c][i];
+            s2 += gf[c][i] * xf[c][i];
+            acc_w[c][i] += dyf[i] * xf[c][i];
+            acc_b[c][i] += dyf[i];
+          } else {
+            gf[c][i] = dyf[i] * wf[i];
+            s2 += gf[c][i] * xf[c][i];
+            acc_w[c][i] += dyf[i] * (xf[c][i] * rstd);
+          }
+        }
+      }
+    }
+    // row sums
+    if constexpr (BLOCK) {
+      s1 = warp_reduce<SumOp>(s1);
+      s2 = warp_reduce<SumOp>(s2);
+      const int warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+      if ((threadIdx.x & 31) == 0) red[parity][warp] = make_float2(s1, s2);
+      __syncthreads();
+      s1 = 0.f;
+      s2 = 0.f;
+      for (int w = 0; w < nwarps; ++w) {
+        const float2 t = red[parity][w];
+        s1 += t.x;
+        s2 += t.y;
+      }
+      parity ^= 1;
+    } else {
+      if constexpr (LN) s1 = warp_reduce<SumOp>(s1);
+      s2 = warp_reduce<SumOp>(s2);
+    }
+
+    T* dxr = reinterpret_cast<T*>(p.dx) + (row / p.seq) * p.dx_batch_stride +
+             (row % p.seq) * p.dx_seq_stride;
+    float k;  // per-row coefficient
+    if constexpr (LN) {
+      k = rstd / p.n_f;
+    } else {
+      k = ((s2 * -0.5f) * (rstd * rstd * rstd)) / p.n_f;
+    }
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int j = c * G + lane;
+      if (j < nv) {
+        float o[V];
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          if constexpr (LN) {
+            o[i] = k * ((gf[c][i] * p.n_f - s1) - xf[c][i] * s2);
+          } else {
+            o[i] = gf[c][i] * rstd + k * (xf[c][i] * 2.0f);
+          }
+        }
+        st_stream(dxr + dx_col[c], Elem<T>::pack(o));
+      }
+    }
+    row = next;
+  }
+
+  // one partial row per group
+  if (p.dw || p.db) {
+    float* pw = p.partials + group * p.n;
+    float* pb = p.partials + ((long long)p.groups + group) * p.n;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int j = c * G + lane;
+      if (j < nv) {
+        float4* dst = reinterpret_cast<float4*>(pw + (long long)j * V);
+#pragma unroll
+        for (int q = 0; q < V / 4; ++q)
+          dst[q] = make_float4(acc_w[c][4 * q], acc_w[c][4 * q + 1], acc_w[c][4 * q + 2], acc_w[c][4 * q + 3]);
+        if constexpr (LN) {
+          if (p.db) {
+            float4* dstb = reinterpret_cast<float4*>(pb + (long long)j * V);
+#pragma unroll
+            for (int q = 0; q < V / 4; ++q)
+              dstb[q] = make_float4(acc_b[c][4 * q], acc_b[c][4 * q + 1], acc_b[c][4 * q + 2], acc_b[c][4 * q + 3]);
+          }
+        }
+      }
+    }
+  }
+  if (p.fused) {
+    const bool ok = grid_barrier(p.bar, 1u, &bar_ok);
+    if (ok) {
+      if (p.dw) finalize_columns(p.partials, p.groups, p.n, p.dw, fin);
+      if (LN && p.db) finalize_columns(p.partials + (long long)p.groups * p.n, p.groups, p.n, p.db, fin);
+    }
+    grid_barrier_depart(p.bar);
+  }
+}
+
+__global__ void __launch_bounds__(512) norm_bwd_finalize_kernel(const NormBwdParams p) {
+  __shared__ double fin[16 * 64];
+  if (p.dw) finalize_columns(p.partials, p.groups, p.n, p.dw, fin);
+  if (p.db) finalize_columns(p.partials + (long long)p.groups * p.n, p.groups, p.n, p.db, fin);
+}
+
+// Element-wise kernels for rows the vector path cannot take (ragged n, unaligned pointers, a head
+// size that is not a multiple of the vector length). Correct for every layout, not tuned.
+template <typename T, bool LN>
+__global__ void __launch_bounds__(256) norm_bwd_rows_general_kernel(const NormBwdParams p) {
+  __shared__ float red[32];
+  const long long row = blockIdx.x;
+  const T* x = reinterpret_cast<const T*>(p.x) + row * p.x_row_stride;
+  const T* dy = reinterpret_cast<const T*>(p.dy) + row * p.dy_row_stride;
+  const float rstd = p.rstd[row];
+  const float mean = LN ? p.mean[row] : 0.f;
+  float s1 = 0.f, s2 = 0.f;
+  for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
+    const float w = p.w ? load_param1(p.w, p.w_dtype, i) : 1.f;
+    const float g = Elem<T>::to_f32(dy[i]) * w;
+    const float xv = Elem<T>::to_f32(x[i]);
+    if (LN) {
+      const float xhat = (xv - mean) * rstd;
+      s1 += g;
+      s2 += g * xhat;
+    } else {
+      s2 += g * xv;
+    }
+  }
+  s1 = block_reduce<SumOp>(s1, red);
+  s2 = block_reduce<SumOp>(s2, red);
+  T* dxr = reinterpret_cast<T*>(p.dx) + (row / p.seq) * p.dx_batch_stride + (row % p.seq) * p.dx_seq_stride;
+  const float k = LN ? rstd / p.n_f : ((s2 * -0.5f) * (rstd * rstd * rstd)) / p.n_f;
+  for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
+    const float w = p.w ? load_param1(p.w, p.w_dtype, i) : 1.f;
+    const float g = Elem<T>::to_f32(dy[i]) * w;
+    const float xv = Elem<T>::to_f32(x[i]);
+    float o;
+    if (LN) {
+      const float xhat = (xv - mean) * rstd;
+      o = k * ((g * p.n_f - s1) - xhat * s2);
+    } else {
+      o = g * rstd + k * (xv * 2.0f);
+    }
+    dxr[(long long)(i / p.head_dim) * p.dx_head_stride + (i % p.head_dim)] = Elem<T>::from_f32(o);
+  }
+}
+
+// One thread per column, rows split over blockIdx.y; partial rows go to scratch like the fast path.
+template <typename T, bool LN>
+__global__ void __launch_bounds__(128) norm_bwd_cols_general_kernel(const NormBwdParams p) {
+  const int col = blockIdx.x * blockDim.x + threadIdx.x;
+  if (col >= p.n) return;
+  const long long per = (p.rows + gridDim.y - 1) / gridDim.y;
+  const long long r0 = (long long)blockIdx.y * per;
+  const long long r1 = r0 + per < p.rows ? r0 + per : p.rows;
+  float aw = 0.f, ab = 0.f;
+  for (long long r = r0; r < r1; ++r) {
+    const float xv = Elem<T>::to_f32(reinterpret_cast<const T*>(p.x)[r * p.x_row_stride + col]);
+    const float dyv = Elem<T>::to_f32(reinterpret_cast<const T*>(p.dy)[r * p.dy_row_stride + col]);
+    const float rstd = p.rstd[r];
+    if (LN) {
+      aw += dyv * ((xv - p.mean[r]) * rstd);
+      ab += dyv;
+    } else {
+      aw += dyv * (xv * rstd);
+    }
+  }
+  p.partials[(long long)blockIdx.y * p.n + col] = aw;
+  if (LN) p.partials[((long long)p.groups + blockIdx.y) * p.n + col] = ab;
+}
+
+static int cached_occupancy(const void* fn, int threads) {
+  // The occupancy query is a host-side calculation; cache it per (kernel, block size).
+  struct Entry { const void* fn; int threads; int blocks; };
+  static Entry cache[64];
+  static int used = 0;
+  for (int i = 0; i < used; ++i)
+    if (cache[i].fn == fn && cache[i].threads == threads) return cache[i].blocks;
+  int blocks = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, fn, threads, 0) != cudaSuccess) {
+    cudaGetLastError();
+    blocks = 1;
+  }
+  if (blocks < 1) blocks = 1;
+  if (used < 64) cache[used++] = Entry{fn, threads, blocks};
+  return blocks;
+}
+
+template <typename T, int CH, bool BLOCK, bool LN>
+static int launch_norm_bwd_fast(NormBwdParams p, int threads, size_t scratch_bytes, bool cooperative,
+                                cudaStream_t st) {
+  auto kernel = norm_bwd_kernel<T, CH, BLOCK, LN>;
+  const int sms = device_info().sm_count;
+  const int per_sm = cached_occupancy(reinterpret_cast<const void*>(kernel), threads);
+  long long grid = (long long)per_sm * sms;
+  const int groups_per_cta = BLOCK ? 1 : threads / 32;
+  const long long max_useful = (p.rows + groups_per_cta - 1) / groups_per_cta;
+  if (grid > max_useful) grid = max_useful;
+  // scratch: 256 bytes of barrier words, then two planes of [groups][n] floats
+  if (p.dw || p.db) {
+    const long long plane = (long long)p.n * sizeof(float);
+    const long long max_groups = ((long long)scratch_bytes - 256) / (2 * plane);
+    if (max_groups < groups_per_cta)
+      return fail(B200_ERR_WORKSPACE, "b200_norm_bwd: scratch of %zu bytes is too small (need >= %lld)",
+                  scratch_bytes, 256 + 2 * plane * groups_per_cta);
+    if (grid * groups_per_cta > max_groups) grid = max_groups / groups_per_cta;
+  }
+  p.groups = (int)(grid * groups_per_cta);
+  p.fused = cooperative ? 1 : 0;
+  if (cooperative) {
+    void* args[] = {&p};
+    cudaError_t e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3((unsigned)grid),
+                                                dim3(threads), args, 0, st);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      return fail((int)e, "b200_norm_bwd: cooperative launch failed: %s", cudaGetErrorString(e));
+    }
+    return B200_OK;
+  }
+  kernel<<<(unsigned)grid, threads, 0, st>>>(p);
+  int rc = launch_status("b200_norm_bwd");
+  if (rc != B200_OK) return rc;
+  if (p.dw || p.db) {
+    const int chunks = (p.n + 63) / 64;
+    norm_bwd_finalize_kernel<<<chunks, 512, 0, st>>>(p);
+    rc = launch_status("b200_norm_bwd finalize");
+  }
+  return rc;
+}
+
+template <typename T, bool LN>
+static int launch_norm_bwd(NormBwdParams p, bool vector_ok, size_t scratch_bytes, bool cooperative,
+                           cudaStream_t st) {
+  constexpr int V = Elem<T>::V;
+  if (p.rows > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "norm_bwd: too many rows");
+  const long long nv = p.n / V;
+  if (vector_ok && p.n % V == 0 && p.head_dim % V == 0 && nv <= 2048) {
+    if (nv <= 128) {
+      if (nv <= 32) return launch_norm_bwd_fast<T, 1, false, LN>(p, 256, scratch_bytes, cooperative, st);
+      if (nv <= 64) return launch_norm_bwd_fast<T, 2, false, LN>(p, 256, scratch_bytes, cooperative, st);
+      return launch_norm_bwd_fast<T, 4, false, LN>(p, 256, scratch_bytes, cooperative, st);
+    }
+    if (nv <= 512) {
+      int threads = (int)((nv + 1) / 2);
+      threads = (threads + 31) / 32 * 32;
+      return launch_norm_bwd_fast<T, 2, true, LN>(p, threads, scratch_bytes, cooperative, st);
+    }
+    int threads = (int)((nv + 3) / 4);
+    threads = (threads + 31) / 32 * 32;
+    return launch_norm_bwd_fast<T, 4, true, LN>(p, threads, scratch_bytes, cooperative, st);
+  }
+  // general path: rows kernel + column kernel + finalize
+  norm_bwd_rows_general_kernel<T, LN><<<(unsigned)p.rows, 256, 0, st>>>(p);
+  int rc = launch_status("b200_norm_bwd rows");
+  if (rc != B200_OK || !(p.dw || p.db)) return rc;
+  const long long plane = (long long)p.n * sizeof(float);
+  long long splits = ((long long)scratch_bytes - 256) / (2 * plane);
+  if (splits < 1) return fail(B200_ERR_WORKSPACE, "b200_norm_bwd: scratch too small");
+  if (splits > 64) splits = 64;
+  if (splits > p.rows) splits = p.rows;
+  p.groups = (int)splits;
+  norm_bwd_cols_general_kernel<T, LN><<<dim3((p.n + 127) / 128, (unsigned)splits), 128, 0, st>>>(p);
+  rc = launch_status("b200_norm_bwd cols");
+  if (rc != B200_OK) return rc;
+  norm_bwd_finalize_kernel<<<(p.n + 63) / 64, 512, 0, st>>>(p);
+  return launch_status("b200_norm_bwd finalize");
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+// Bytes of scratch that let the fast path run its largest grid for rows of n elements.
+extern "C" int64_t b200_norm_bwd_scratch_bytes(int64_t n) {
+  const int sms = device_info().sm_count;
+  // up to 8 resident 256-thread CTAs per SM, 8 warps each, two planes of fp32 partial rows
+  return 256 + 2LL * (int64_t)sms * 64 * n * (int64_t)sizeof(float);
+}
+
+extern "C" int b200_norm_bwd(const void* x, const void* dy, const void* weight, const float* mean,
+                             const float* rstd, void* dx, float* dweight, float* dbias, int64_t rows,
+                             int64_t n, int64_t x_row_stride, int64_t dy_row_stride, int32_t x_dtype,
+                             int32_t w_dtype, int32_t rms, int64_t seq, int64_t head_dim,
+                             int64_t dx_batch_stride, int64_t dx_seq_stride, int64_t dx_head_stride,
+                             void* scratch, int64_t scratch_bytes, int32_t flags, void* stream) {
+  if (!x || !dy || !rstd || !dx) return fail(B200_ERR_INVALID, "b200_norm_bwd: null argument");
+  if (!rms && !mean) return fail(B200_ERR_INVALID, "b200_norm_bwd: LayerNorm backward needs mean");
+  if (rows < 0 || n <= 0 || n > 0x7fffffffLL || seq < 1 || head_dim < 1 || n % head_dim != 0)
+    return fail(B200_ERR_INVALID, "b200_norm_bwd: bad sizes rows=%lld n=%lld seq=%lld head_dim=%lld",
+                (long long)rows, (long long)n, (long long)seq, (long long)head_dim);
+  if ((dweight || dbias) && (!scratch || scratch_bytes < 256))
+    return fail(B200_ERR_WORKSPACE, "b200_norm_bwd: dweight/dbias need a scratch buffer");
+  if ((dweight || dbias) && !aligned16(scratch)) return fail(B200_ERR_ALIGNMENT, "b200_norm_bwd: scratch must be 16-byte aligned");
+  if (rms && dbias) return fail(B200_ERR_INVALID, "b200_norm_bwd: RMSNorm has no bias gradient");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (rows == 0) {
+    if (dweight) cudaMemsetAsync(dweight, 0, n * sizeof(float), st);
+    if (dbias) cudaMemsetAsync(dbias, 0, n * sizeof(float), st);
+    return launch_status("b200_norm_bwd (empty)");
+  }
+
+  NormBwdParams p;
+  p.x = x; p.dy = dy; p.w = weight; p.mean = mean; p.rstd = rstd; p.dx = dx; p.dw = dweight; p.db = dbias;
+  p.rows = rows; p.n = (int)n; p.x_row_stride = x_row_stride; p.dy_row_stride = dy_row_stride;
+  p.w_dtype = w_dtype; p.seq = (int)seq; p.head_dim = (int)head_dim;
+  p.dx_batch_stride = dx_batch_stride; p.dx_seq_stride = dx_seq_stride; p.dx_head_stride = dx_head_stride;
+  p.n_f = (float)n;
+  p.bar = reinterpret_cast<unsigned int*>(scratch);
+  p.partials = scratch ? reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + 256) : nullptr;
+  p.groups = 0; p.fused = 0;
+  const bool cooperative = (flags & 1) == 0 && (dweight || dbias);
+
+  const int eb = dtype_size(x_dtype), wb = dtype_size(w_dtype);
+  const int v = 16 / eb;
+  const int w_chunk = v * wb < 16 ? v * wb : 16;
+  bool vec = aligned16(x) && aligned16(dy) && aligned16(dx) && (x_row_stride * eb) % 16 == 0 &&
+             (dy_row_stride * eb) % 16 == 0 && (dx_batch_stride * eb) % 16 == 0 &&
+             (dx_seq_stride * eb) % 16 == 0 && (dx_head_stride * eb) % 16 == 0;
+  if (weight) vec = vec && reinterpret_cast<uintptr_t>(weight) % w_chunk == 0;
+
+#define B200_NBWD_CASE(TT, DT)                                                              \
+  if (x_dtype == DT)                                                                        \
+    return rms ? launch_norm_bwd<TT, false>(p, vec, (size_t)scratch_bytes, cooperative, st) \
+               : launch_norm_bwd<TT, true>(p, vec, (size_t)scratch_bytes, cooperative, st);
+  B200_NBWD_CASE(float, B200_F32)
+  B200_NBWD_CASE(__nv_bfloat16, B200_BF16)
+  B200_NBWD_CASE(__half, B200_F16)
+#undef B200_NBWD_CASE
+  return fail(B200_ERR_INVALID, "b200_norm_bwd: unknown dtype %d", x_dtype);
+}

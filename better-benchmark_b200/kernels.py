@@ -239,3 +239,143 @@ def norm_fwd(x: torch.Tensor, weight: torch.Tensor | None, bias: torch.Tensor | 
                             _stream()),
           "b200_norm_fwd")
     return y, mean, rstd, var
+
+
+# ---------------------------------------------------------------------------------------------
+# Scratch memory. Kernels that combine per-CTA partial results take a caller-provided scratch
+# buffer. One zero-initialised buffer per device is kept here and grown on demand; the first 256
+# bytes hold the grid-barrier words, which every kernel leaves at zero when it finishes. Kernels
+# on one stream run in order, so sharing the buffer is safe there; callers that launch on several
+# streams at once must pass their own ``scratch``.
+# ---------------------------------------------------------------------------------------------
+_scratch_by_device: dict = {}
+
+
+def scratch_buffer(device: torch.device, nbytes: int) -> torch.Tensor:
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    buf = _scratch_by_device.get(key)
+    if buf is None or buf.numel() < nbytes:
+        buf = torch.zeros(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
+        _scratch_by_device[key] = buf
+    return buf
+
+
+def check_scratch_status(device: torch.device | None = None) -> None:
+    """Raise if a cooperative kernel on this device gave up a grid-wide wait (synchronises)."""
+    device = device or torch.device("cuda", torch.cuda.current_device())
+    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
+    buf = _scratch_by_device.get(key)
+    if buf is None:
+        return
+    lib = load()
+    status = lib.b200_check_status(_ptr(buf), _stream())
+    if status != 0:
+        buf[:16].zero_()
+        check(status, "b200_check_status")
+
+
+NORM_BWD_TWO_LAUNCH = 1  # flag: main kernel + finalize kernel instead of one cooperative launch
+
+
+def norm_bwd(x: torch.Tensor, dy: torch.Tensor, weight: torch.Tensor | None, rstd: torch.Tensor, *,
+             mean: torch.Tensor | None = None, rms: bool, heads: int | None = None,
+             want_dweight: bool = True, want_dbias: bool = False, two_launch: bool = False,
+             scratch: torch.Tensor | None = None):
+    """LayerNorm / RMSNorm backward over the last dimension (flattened over trailing dims for 4-D).
+
+    ``x`` and ``dy`` are [..., n] or, with ``heads``, [B, S, H, D] (n = H*D): dx is then returned
+    as a contiguous [B, H, S, D] tensor, the permute fused into the store. ``rstd`` (and ``mean``
+    for LayerNorm) are fp32 with one value per row. Returns (dx, dweight, dbias); the gradients of
+    weight and bias are fp32 [n].
+    """
+    _require_cuda(x, dy, weight, rstd, mean, scratch)
+    if x.shape != dy.shape or x.dtype != dy.dtype:
+        raise UnsupportedLayout("norm_bwd: x and dy must agree in shape and dtype")
+    if heads is not None:
+        if x.dim() != 4 or x.shape[2] != heads or not x.is_contiguous() or not dy.is_contiguous():
+            raise UnsupportedLayout("norm_bwd: heads= needs contiguous [B, S, H, D] inputs")
+        b, s, h, d = x.shape
+        rows, n = b * s, h * d
+        x_stride = dy_stride = n
+        dx = torch.empty((b, h, s, d), dtype=x.dtype, device=x.device)
+        seq, head_dim = s, d
+        dx_batch, dx_seq, dx_head = h * s * d, d, s * d
+    else:
+        rows, n, x_stride = _rows_2d(x, "norm_bwd")
+        _, _, dy_stride = _rows_2d(dy, "norm_bwd")
+        dx = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        seq, head_dim = 1, n
+        dx_batch, dx_seq, dx_head = n, 0, n
+    if rstd.dtype != torch.float32 or rstd.numel() != rows or not rstd.is_contiguous():
+        raise UnsupportedLayout("norm_bwd: rstd must be contiguous fp32 with one value per row")
+    if not rms:
+        if mean is None or mean.dtype != torch.float32 or mean.numel() != rows or not mean.is_contiguous():
+            raise UnsupportedLayout("norm_bwd: LayerNorm needs a contiguous fp32 mean per row")
+    w_code = F32
+    if weight is not None:
+        if weight.dim() != 1 or weight.shape[0] != n or not weight.is_contiguous():
+            raise UnsupportedLayout("norm_bwd: weight must be contiguous [n]")
+        w_code = _code(weight)
+    dw = torch.empty(n, dtype=torch.float32, device=x.device) if want_dweight else None
+    db = torch.empty(n, dtype=torch.float32, device=x.device) if (want_dbias and not rms) else None
+    lib = load()
+    nbytes = 0
+    if dw is not None or db is not None:
+        nbytes = int(lib.b200_norm_bwd_scratch_bytes(n))
+        if scratch is None:
+            scratch = scratch_buffer(x.device, nbytes)
+        nbytes = scratch.numel() * scratch.element_size()
+    check(lib.b200_norm_bwd(_ptr(x), _ptr(dy), _ptr(weight), _ptr(mean), _ptr(rstd), _ptr(dx),
+                            _ptr(dw), _ptr(db), rows, n, x_stride, dy_stride, _code(x), w_code,
+                            1 if rms else 0, seq, head_dim, dx_batch, dx_seq, dx_head,
+                            _ptr(scratch), nbytes, NORM_BWD_TWO_LAUNCH if two_launch else 0,
+                            _stream()),
+          "b200_norm_bwd")
+    return dx, dw, db
+
+
+def batch_norm_fwd(x: torch.Tensor, weight: torch.Tensor | None, bias: torch.Tensor | None,
+                   running_mean: torch.Tensor | None, running_var: torch.Tensor | None, *,
+                   eps: float, momentum: float, relu: bool = False,
+                   scratch: torch.Tensor | None = None):
+    """BatchNorm2d training forward (+ optional ReLU) on a dense NCHW or channels-last tensor.
+
+    Returns (y, mean, invstd): y has x's dtype and strides, mean/invstd are fp32 [C].
+    ``running_mean`` / ``running_var`` (fp32 [C]) are updated in place when given.
+    """
+    _require_cuda(x, weight, bias, running_mean, running_var, scratch)
+    if x.dim() != 4:
+        raise UnsupportedLayout("batch_norm_fwd: expected a 4-D [N, C, H, W] tensor")
+    n, c, h, w = x.shape
+    sn, sc, sh, sw = x.stride()
+    if x.numel() == 0:
+        raise native.KernelArgumentError("batch_norm_fwd: empty input has no statistics")
+    if h > 1 and w > 1 and sh != w * sw:
+        raise UnsupportedLayout("batch_norm_fwd: H and W must collapse into one strided dimension")
+    ss = sw if w > 1 else (sh if h > 1 else 1)
+    if not _is_dense(x):
+        raise UnsupportedLayout("batch_norm_fwd: x must be dense (NCHW or channels-last)")
+    w_code = F32
+    for prm in (weight, bias):
+        if prm is not None:
+            if prm.dim() != 1 or prm.shape[0] != c or not prm.is_contiguous():
+                raise UnsupportedLayout("batch_norm_fwd: weight/bias must be contiguous [C]")
+            w_code = _code(prm)
+    if weight is not None and bias is not None and weight.dtype != bias.dtype:
+        raise UnsupportedLayout("batch_norm_fwd: weight and bias must share a dtype")
+    for stat in (running_mean, running_var):
+        if stat is not None and (stat.dtype != torch.float32 or stat.shape != (c,) or not stat.is_contiguous()):
+            raise UnsupportedLayout("batch_norm_fwd: running statistics must be contiguous fp32 [C]")
+    y = torch.empty_strided(x.shape, x.stride(), dtype=x.dtype, device=x.device)
+    mean = torch.empty(c, dtype=torch.float32, device=x.device)
+    invstd = torch.empty(c, dtype=torch.float32, device=x.device)
+    lib = load()
+    nbytes = int(lib.b200_batch_norm_scratch_bytes(c))
+    if scratch is None:
+        scratch = scratch_buffer(x.device, nbytes)
+    check(lib.b200_batch_norm_fwd(_ptr(x), _ptr(y), _ptr(weight), _ptr(bias), _ptr(running_mean),
+                                  _ptr(running_var), _ptr(mean), _ptr(invstd), n, c, h * w, sn, sc, ss,
+                                  _code(x), w_code, float(eps), float(momentum), 1 if relu else 0,
+                                  _ptr(scratch), scratch.numel() * scratch.element_size(), _stream()),
+          "b200_batch_norm_fwd")
+    return y, mean, invstd

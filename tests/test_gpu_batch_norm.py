@@ -1,0 +1,82 @@
+"""GPU parity: BatchNorm2d training forward (+ReLU, running statistics) against the eager graph."""
+import pytest
+import torch
+
+from conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _kernels():
+    import better_benchmark_b200.kernels as k
+    return k
+
+
+def _inputs(shape, dtype, channels_last, seed, shift=0.5, scale=2.0):
+    g = torch.Generator().manual_seed(seed)
+    x = (shift + scale * torch.randn(shape, generator=g)).to(dtype)
+    if channels_last:
+        x = x.contiguous(memory_format=torch.channels_last)
+    c = shape[1]
+    w = torch.rand(c, generator=g) + 0.5
+    b = 0.1 * torch.randn(c, generator=g)
+    rm = 0.3 * torch.randn(c, generator=g)
+    rv = torch.rand(c, generator=g) + 0.5
+    return x, rm, rv, w, b
+
+
+SHAPES = [
+    (2, 8, 4, 4), (4, 64, 14, 14), (16, 64, 56, 56), (8, 384, 8, 8), (3, 24, 17, 9), (5, 136, 7, 7),
+    (2, 2048, 7, 7), (1, 16, 1, 1), (32, 32, 1, 1), (2, 5, 6, 6), (7, 40, 13, 13),
+]
+
+
+@pytest.mark.parametrize("relu", [True, False])
+@pytest.mark.parametrize("channels_last", [True, False])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("shape", SHAPES)
+def test_batch_norm_fwd_matches_eager(shape, dtype, channels_last, relu):
+    from oracle.eager import BatchNormReluFwd
+    if shape[0] * shape[2] * shape[3] < 2:
+        pytest.skip("a single element per channel has no unbiased variance")
+    x, rm, rv, w, b = _inputs(shape, dtype, channels_last, seed=sum(shape))
+    want = BatchNormReluFwd(1e-5, 0.1, relu=relu)(x, rm.clone(), rv.clone(), w, b)
+    rm_d, rv_d = rm.cuda(), rv.cuda()
+    y, mean, invstd = _kernels().batch_norm_fwd(x.cuda(), w.cuda(), b.cuda(), rm_d, rv_d, eps=1e-5,
+                                               momentum=0.1, relu=relu)
+    assert y.stride() == x.stride()
+    assert_close(y, want[0], f"bn y {shape} {dtype} cl={channels_last}")
+    assert_close(mean, want[1], f"bn mean {shape}")
+    assert_close(invstd, want[2], f"bn invstd {shape}")
+    assert_close(rm_d, want[3], f"bn running_mean {shape}")
+    assert_close(rv_d, want[4], f"bn running_var {shape}")
+    _kernels().check_scratch_status()
+
+
+def test_batch_norm_large_mean_small_variance():
+    """Shifted sums: a channel with mean 1000 and unit variance keeps its variance."""
+    from oracle.eager import BatchNormReluFwd
+    g = torch.Generator().manual_seed(0)
+    x = (1000.0 + torch.randn((8, 16, 32, 32), generator=g)).contiguous(memory_format=torch.channels_last)
+    w, b = torch.ones(16), torch.zeros(16)
+    rm, rv = torch.zeros(16), torch.ones(16)
+    want = BatchNormReluFwd(1e-5, 0.1, relu=False)(x.double(), rm.double(), rv.double(), w.double(), b.double())
+    y, mean, invstd = _kernels().batch_norm_fwd(x.cuda(), w.cuda(), b.cuda(), None, None, eps=1e-5,
+                                               momentum=0.1)
+    assert_close(mean, want[1].float(), "mean")
+    assert torch.allclose(invstd.cpu(), want[2].float(), rtol=2e-5, atol=0)
+
+
+def test_batch_norm_repeated_calls_update_running_stats_and_reproduce():
+    k = _kernels()
+    x, rm, rv, w, b = _inputs((16, 64, 28, 28), torch.bfloat16, True, seed=3)
+    xd, wd, bd = x.cuda(), w.cuda(), b.cuda()
+    rm1, rv1 = rm.cuda(), rv.cuda()
+    y1, m1, s1 = k.batch_norm_fwd(xd, wd, bd, rm1, rv1, eps=1e-5, momentum=0.1, relu=True)
+    rm2, rv2 = rm.cuda(), rv.cuda()
+    y2, m2, s2 = k.batch_norm_fwd(xd, wd, bd, rm2, rv2, eps=1e-5, momentum=0.1, relu=True)
+    assert torch.equal(y1, y2) and torch.equal(m1, m2) and torch.equal(s1, s2)
+    assert torch.equal(rm1, rm2) and torch.equal(rv1, rv2)
+    k.batch_norm_fwd(xd, wd, bd, rm2, rv2, eps=1e-5, momentum=0.1, relu=True)
+    assert not torch.equal(rm1, rm2)       # a second step moves the running statistics again
+    k.check_scratch_status()
