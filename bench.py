@@ -1,0 +1,383 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 oracle backend.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--workload NAME]
+
+A step is one pass of one fused region (by default the LayerNorm-forward configuration, the
+second of the baseline's list) over one batch of seeded synthetic input that is already resident
+in HBM. Inputs rotate over several buffer sets whose total footprint exceeds the L2 cache, so no
+step finds its input there. The metric is achieved HBM bandwidth: the region's minimum bytes
+(every input once plus every output once) divided by the time per step. One JSON line is printed
+by rank 0.
+
+  value      K timed steps between CUDA events on the launching stream, barrier + synchronize on
+             both sides; with N > 1 every rank runs the same configuration on its own GPU
+             (independent replicas, no collective in the data path) and the time is the maximum
+             over ranks, so value is the aggregate over the N GPUs.
+  roofline   the dominant (here: only) kernel of the step against the measured HBM peak.
+  e2e        the same metric through the public entry point with HOST buffers: every step copies
+             the inputs from pinned host memory, runs ``oracle_forward`` and copies every output
+             back to pinned host memory.
+  cpu_baseline  the eager module of the same region on the host cores (rank 0, N = 1).
+  per_config the other four baseline configurations, timed the same way as ``value``.
+
+``--impl reference`` times only the eager module on the host cores (the reference's own CPU
+path for this region) and prints the same metric with ``"impl": "reference"``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+L2_BYTES_ASSUMED = 126 * 1024 * 1024
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+
+
+def recorded_traffic(workload):
+    """DRAM bytes per launch from the committed ncu capture of this workload's kernel, or None."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
+            return json.load(f).get(workload, {}).get("dram_bytes_per_launch")
+    except Exception:
+        return None
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                 "-i", str(self.gpu_index), "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._drain, daemon=True)
+        self.thread.start()
+
+    def _drain(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.lines:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                mx.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def dist_env():
+    return (int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")),
+            int(os.environ.get("WORLD_SIZE", "1")))
+
+
+# ---------------------------------------------------------------------------------------------
+# reference arm / CPU baseline: the eager module on the host cores
+# ---------------------------------------------------------------------------------------------
+def time_eager_cpu(workload, steps, warmup, budget_s=None):
+    """Seconds per call of the eager module (oracle/canonical/<id>/repro.py) on the CPU."""
+    import torch
+    from better_benchmark_b200.harness import load_repro_module
+    cores = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    torch.set_num_threads(cores)
+    module = load_repro_module(os.path.join(ROOT, "oracle", "canonical", workload.canonical_id))
+    instance = module.Repro()
+    inputs = workload.make_inputs("cpu", 1)
+
+    def run():
+        args = [i.clone() if (workload.mutates_inputs and isinstance(i, torch.Tensor)) else i for i in inputs]
+        with torch.no_grad():
+            return instance(*args)
+
+    for _ in range(max(1, warmup)):
+        run()
+    times = []
+    t_start = time.perf_counter()
+    for _ in range(max(1, steps)):
+        t0 = time.perf_counter()
+        run()
+        times.append(time.perf_counter() - t0)
+        if budget_s is not None and time.perf_counter() - t_start > budget_s:
+            break
+    return sum(times) / len(times), min(times), len(times), cores
+
+
+def reference_arm(args, workload):
+    rank, _, world = dist_env()
+    if rank != 0:
+        return 0
+    mean_s, best_s, done, cores = time_eager_cpu(workload, args.steps, max(1, min(args.warmup, 3)), budget_s=150)
+    gbps = workload.algorithmic_bytes / mean_s / 1e9
+    line = {
+        "impl": "reference", "metric": "achieved_hbm_gbps", "value": round(gbps, 3), "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": done, "warmup": args.warmup, "ms_per_step": round(mean_s * 1e3, 3),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": workload.dtype,
+        "data": "synthetic",
+        "config": {"workload": workload.name, "description": workload.description,
+                   "device": "host CPU", "threads": cores},
+        "cpu_baseline": {"value": round(gbps, 3), "unit": "GB/s", "cores": cores, "kind": "port",
+                         "sample": f"full {workload.name} workload per step, eager aten graph of the region, {done} steps"},
+        "e2e": {"value": round(gbps, 3), "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ---------------------------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------------------------
+def build_input_sets(workload, device, min_total_bytes):
+    """Enough seeded input sets that their tensors together exceed ``min_total_bytes``."""
+    import torch
+    first = workload.make_inputs(device, 1)
+    per_set = sum(t.numel() * t.element_size() for t in first if isinstance(t, torch.Tensor))
+    count = max(2, int(min_total_bytes // max(per_set, 1)) + 1)
+    sets = [first]
+    for s in range(1, count):
+        sets.append(workload.make_inputs(device, 1 + s))
+    return sets, per_set
+
+
+def time_steps(workload, input_sets, steps, warmup, barrier):
+    """(milliseconds for `steps` steps, kernels launched inside the timed region)."""
+    import torch
+    from better_benchmark_b200 import native
+    lib = native.load()
+    n = len(input_sets)
+    for i in range(warmup):
+        workload.oracle_forward(input_sets[i % n])
+    torch.cuda.synchronize()
+    barrier()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = lib.b200_launch_count()
+    start.record()
+    for i in range(steps):
+        workload.oracle_forward(input_sets[i % n])
+    end.record()
+    torch.cuda.synchronize()
+    launches = lib.b200_launch_count() - launches0
+    barrier()
+    return start.elapsed_time(end), int(launches)
+
+
+def time_e2e(workload, device, steps, warmup):
+    """Milliseconds per step with host buffers: H2D of every input, the oracle, D2H of every
+    output; returns (ms_per_step, h2d_bytes, d2h_bytes)."""
+    import torch
+    host_inputs = [t.pin_memory() if isinstance(t, torch.Tensor) else t for t in workload.make_inputs("cpu", 1)]
+    dev_inputs = [torch.empty_like(t, device=device) if isinstance(t, torch.Tensor) else t for t in host_inputs]
+    # channels-last and other dense layouts survive empty_like; keep strides identical
+    for h, d in zip(host_inputs, dev_inputs):
+        if isinstance(h, torch.Tensor):
+            assert h.stride() == d.stride()
+    h2d = sum(t.numel() * t.element_size() for t in host_inputs if isinstance(t, torch.Tensor))
+    host_outputs = None
+
+    def step():
+        nonlocal host_outputs
+        for h, d in zip(host_inputs, dev_inputs):
+            if isinstance(h, torch.Tensor):
+                d.copy_(h, non_blocking=True)
+        outs = workload.oracle_forward(dev_inputs)
+        outs = [outs] if isinstance(outs, torch.Tensor) else list(outs)
+        if host_outputs is None:
+            host_outputs = [torch.empty_strided(o.shape, o.stride(), dtype=o.dtype).pin_memory() for o in outs]
+        for o, h in zip(outs, host_outputs):
+            h.copy_(o, non_blocking=True)
+
+    for _ in range(max(1, warmup)):
+        step()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        step()
+    end.record()
+    torch.cuda.synchronize()
+    d2h = sum(t.numel() * t.element_size() for t in host_outputs)
+    return start.elapsed_time(end) / steps, h2d, d2h
+
+
+def gpu_arm(args, workload):
+    import torch
+    from better_benchmark_b200.workloads import WORKLOADS
+    rank, local_rank, world = dist_env()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: this backend has no CPU path "
+                         "(use --impl reference for the host baseline)")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    use_dist = world > 1
+    if use_dist:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=device)
+
+        def barrier():
+            dist.barrier()
+    else:
+        def barrier():
+            return None
+
+    peak, peak_source = measured_peak()
+    sets, per_set = build_input_sets(workload, device, 4 * L2_BYTES_ASSUMED)
+    n_sets = len(sets)
+    sampler = ClockSampler(os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",")[local_rank]
+                           if os.environ.get("CUDA_VISIBLE_DEVICES") else local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    total_ms, launches = time_steps(workload, sets, args.steps, args.warmup, barrier)
+    if use_dist:
+        import torch.distributed as dist
+        t = torch.tensor([total_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    # keep the GPU under the same load a little longer so that the clock sampler sees it
+    t_end = time.time() + 1.0
+    while time.time() < t_end:
+        for i in range(50):
+            workload.oracle_forward(sets[i % len(sets)])
+        torch.cuda.synchronize()
+    clocks = sampler.stop() if rank == 0 else None
+    gbps_one = workload.algorithmic_bytes / (ms_per_step * 1e-3) / 1e9
+    value = gbps_one * world
+
+    e2e_ms, h2d, d2h = time_e2e(workload, device, max(3, min(args.steps, 20)), 2)
+    if use_dist:
+        import torch.distributed as dist
+        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = workload.algorithmic_bytes / (e2e_ms * 1e-3) / 1e9 * world
+
+    per_config = {}
+    cpu_baseline = None
+    if rank == 0 and world == 1 and not args.only_headline:
+        del sets
+        torch.cuda.empty_cache()
+        for name, wl in WORKLOADS.items():
+            if name == workload.name:
+                continue
+            s, _ = build_input_sets(wl, device, 4 * L2_BYTES_ASSUMED)
+            ms, n_launch = time_steps(wl, s, args.steps, args.warmup, lambda: None)
+            per = ms / args.steps
+            g = wl.algorithmic_bytes / (per * 1e-3) / 1e9
+            per_config[name] = {"us_per_step": round(per * 1e3, 2), "gbps": round(g, 1),
+                                "frac_of_peak": round(g / peak, 4), "launches_per_step": n_launch / args.steps,
+                                "algorithmic_bytes": wl.algorithmic_bytes}
+            del s
+            torch.cuda.empty_cache()
+        per_config[workload.name] = {"us_per_step": round(ms_per_step * 1e3, 2), "gbps": round(gbps_one, 1),
+                                     "frac_of_peak": round(gbps_one / peak, 4),
+                                     "launches_per_step": launches / args.steps,
+                                     "algorithmic_bytes": workload.algorithmic_bytes}
+        mean_s, best_s, done, cores = time_eager_cpu(workload, 20, 2, budget_s=20)
+        cpu_gbps = workload.algorithmic_bytes / mean_s / 1e9
+        cpu_baseline = {"value": round(cpu_gbps, 3), "unit": "GB/s", "cores": cores, "kind": "port",
+                        "sample": f"full {workload.name} workload per call, eager aten graph of the region, "
+                                  f"{done} calls, mean {mean_s * 1e3:.1f} ms"}
+    if use_dist:
+        import torch.distributed as dist
+        dist.barrier()
+        dist.destroy_process_group()
+    if rank != 0:
+        return 0
+    line = {
+        "metric": "achieved_hbm_gbps", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 6),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": workload.dtype,
+        "data": "synthetic",
+        "config": {"workload": workload.name, "description": workload.description,
+                   "replicas": world,
+                   "l2": f"inputs rotate over {n_sets} resident buffer sets "
+                         f"({per_set / 1e6:.0f} MB each) totalling more than 4x the 126 MB L2"},
+        "clocks": clocks,
+        "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
+                "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms, 4)},
+        "gpu_launches": launches,
+        "roofline": {"bound": "hbm", "achieved": round(gbps_one, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(gbps_one / peak, 4), "traffic": recorded_traffic(workload.name),
+                     "peak_source": peak_source, "algorithmic_bytes_per_launch": workload.algorithmic_bytes,
+                     "launches_per_step": launches / args.steps},
+    }
+    if cpu_baseline is not None:
+        line["cpu_baseline"] = cpu_baseline
+    if per_config:
+        line["per_config"] = per_config
+    print(json.dumps(line))
+    return 0
+
+
+def main(argv=None):
+    from better_benchmark_b200.workloads import HEADLINE, WORKLOADS
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS))
+    ap.add_argument("--only-headline", action="store_true", help="skip the other configurations and the CPU baseline")
+    args = ap.parse_args(argv)
+    if args.warmup < 3:
+        args.warmup = 3
+    workload = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        return reference_arm(args, workload)
+    return gpu_arm(args, workload)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,6 +1,7 @@
 // Library-wide pieces of the C ABI: error text, version, device properties, status words.
 #include "common.cuh"
 
+#include <atomic>
 #include <mutex>
 
 namespace b200 {
@@ -32,7 +33,13 @@ const DeviceInfo& device_info() {
   return info[dev];
 }
 
+static std::atomic<long long> g_launches{0};
+void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
 }  // namespace b200
+
+// Number of kernels this library has launched in this process (cooperative launches included).
+extern "C" int64_t b200_launch_count(void) { return b200::g_launches.load(std::memory_order_relaxed); }
 
 extern "C" const char* b200_last_error(void) { return b200::last_error_buffer(); }
 

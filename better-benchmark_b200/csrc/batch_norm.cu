@@ -344,6 +344,7 @@ static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, size_t 
       cudaGetLastError();
       return fail((int)e, "b200_batch_norm_fwd: cooperative launch failed: %s", cudaGetErrorString(e));
     }
+    note_launch();
     return B200_OK;
   }
   // general path

@@ -47,12 +47,16 @@ inline int fail(int code, const char* fmt, ...) {
   return code;
 }
 
+void note_launch();  // defined in abi.cu: counts kernel launches for b200_launch_count()
+
+// Call after every kernel launch: counts it and reports a rejected launch.
 inline int launch_status(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) {
     fail((int)e, "%s: launch failed: %s", what, cudaGetErrorString(e));
     return (int)e;
   }
+  note_launch();
   return B200_OK;
 }
 

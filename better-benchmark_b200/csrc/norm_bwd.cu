@@ -381,6 +381,7 @@ static int launch_norm_bwd_fast(NormBwdParams p, int threads, size_t scratch_byt
       cudaGetLastError();
       return fail((int)e, "b200_norm_bwd: cooperative launch failed: %s", cudaGetErrorString(e));
     }
+    note_launch();
     return B200_OK;
   }
   kernel<<<(unsigned)grid, threads, 0, st>>>(p);

@@ -1,0 +1,135 @@
+/*
+ * C ABI of libb200_oracles.so: hand-written sm_100a CUDA kernels for the memory-bound fused
+ * regions of the better-benchmark corpus (row/column reductions, softmax, LayerNorm / RMSNorm /
+ * BatchNorm forward and backward, permutes with pointwise epilogues).
+ *
+ * The reference has no native code: each fused region is a Python function
+ *     oracle_forward(inputs, **launch_kwargs)            (oracle_harness.py:1777-1779)
+ * in repros/canonical/<id>/oracle.py that launches Triton kernels on torch tensors. An entry
+ * point below is what such a function binds instead; the comment on each names the Triton
+ * kernels it replaces (paths inside the reference repository).
+ *
+ * Conventions
+ *   - All pointers are device pointers; sizes and strides are in ELEMENTS unless a name says
+ *     bytes. Nothing is allocated, freed or synchronised; every launch goes to `stream`
+ *     (a cudaStream_t passed as void*), so calls may be captured into a CUDA graph.
+ *   - dtype codes: 0 = float32, 1 = bfloat16, 2 = float16.
+ *   - Return value: 0 on success; < 0 an argument error found before anything was launched
+ *     (B200_ERR_*); > 0 the cudaError_t of a rejected launch. b200_last_error() returns the text
+ *     of the calling thread's last failure.
+ *   - Kernels that combine per-CTA partial results take a caller-provided `scratch` buffer
+ *     (16-byte aligned). Its first 256 bytes hold grid-barrier words that must be zero before
+ *     the first use; every kernel leaves them zero. Concurrent launches on different streams
+ *     need different scratch buffers.
+ *   - Accumulation is fp32 (fp64 where partial results of many CTAs are combined), no fast-math,
+ *     no fused multiply-add contraction; reductions have a fixed order (bit-reproducible).
+ */
+#ifndef B200_ORACLES_H
+#define B200_ORACLES_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_F32 0
+#define B200_BF16 1
+#define B200_F16 2
+
+#define B200_OK 0
+#define B200_ERR_INVALID -1
+#define B200_ERR_UNSUPPORTED -2
+#define B200_ERR_ALIGNMENT -3
+#define B200_ERR_WORKSPACE -4
+#define B200_ERR_DEVICE_WAIT -5
+
+/* Text of the calling thread's last error ("" if none). Python exceptions in the reference
+ * (oracle_harness.py:1116-1125, scripts/bench_parallel.py:3115-3118) map onto this. */
+const char* b200_last_error(void);
+
+/* ABI version of this library. */
+int32_t b200_version(void);
+
+/* Multiprocessor count and L2 size of the current device. The reference reads the same facts
+ * through torch in oracle_harness.get_hardware_info (oracle_harness.py:46-56). */
+int32_t b200_sm_count(void);
+int32_t b200_l2_bytes(void);
+
+/* Kernels launched by this library in this process so far. No counterpart in the reference; the
+ * benchmark reports the count of launches inside its timed region. */
+int64_t b200_launch_count(void);
+
+/* Reads the status words of a scratch buffer; returns B200_ERR_DEVICE_WAIT if a grid-wide wait
+ * inside a cooperative kernel ran out. Synchronises `stream`: diagnostic use only. No
+ * counterpart in the reference (its kernels never wait on one another). */
+int32_t b200_check_status(const void* scratch, void* stream);
+
+/* Row reduction over the last (unit-stride) dimension: op 0 sum, 1 mean, 2 amax, 3 amin.
+ * x is [rows, n] with rows = d0*d1*d2 addressed through x_strides[3] (row = (i0*d1+i1)*d2+i2);
+ * out[row * out_stride] has dtype out_dtype.
+ * Replaces repros/canonical/mean_c9e1a8113328/oracle.py:11-76 (contiguous case) and the row
+ * max/sum loops of amax_sum_7079889cfc04/oracle.py:20-29. */
+int32_t b200_row_reduce(const void* x, void* out, int64_t rows, int64_t n, int64_t d1, int64_t d2,
+                        const int64_t* x_strides, int64_t out_stride, int32_t x_dtype,
+                        int32_t out_dtype, int32_t op, void* stream);
+
+/* softmax / log_softmax over the last dimension of x [* scale] [+ mask]; mask (nullable, x's
+ * dtype) broadcasts over the outer dimensions through mask_strides (0 = broadcast).
+ * flags: 1 log_softmax, 2 apply scale, 4 run the multiply/add in the 16-bit input dtype with
+ * rounding (what a 16-bit aten graph does) instead of in fp32.
+ * Replaces amax_sum_20ccc18dda60/oracle.py:11-58, amax_sum_d16035e7b826/oracle.py:14-33,
+ * amax_sum_7079889cfc04/oracle.py:10-36. */
+int32_t b200_softmax(const void* x, const void* mask, void* y, int64_t rows, int64_t n, int64_t d1,
+                     int64_t d2, const int64_t* x_strides, const int64_t* mask_strides,
+                     const int64_t* y_strides, int32_t in_dtype, int32_t out_dtype, double scale,
+                     int32_t flags, void* stream);
+
+/* LayerNorm (rms = 0) / RMSNorm (rms = 1) forward over the last dimension; also row var_mean
+ * (y = NULL). weight, bias, y, mean_out, rstd_out, var_out may each be NULL; statistics are fp32
+ * [rows]. var uses the divisor n - correction.
+ * Replaces var_mean_f8ec553e339e/oracle.py:50-84, var_mean_af505388b035/oracle.py:11-40,
+ * var_mean_f7906a6c6957/oracle.py:14-50, mean_f667cd8901af/oracle.py:36-72. */
+int32_t b200_norm_fwd(const void* x, const void* weight, const void* bias, void* y, float* mean_out,
+                      float* rstd_out, float* var_out, int64_t rows, int64_t n, int64_t x_row_stride,
+                      int64_t y_row_stride, int32_t x_dtype, int32_t w_dtype, int32_t y_dtype,
+                      double eps, double correction, int32_t rms, void* stream);
+
+/* Scratch bytes that let b200_norm_bwd run its largest grid for rows of n elements. */
+int64_t b200_norm_bwd_scratch_bytes(int64_t n);
+
+/* LayerNorm / RMSNorm backward in one pass over x and dy: dx rows, dweight and dbias (fp32 [n],
+ * nullable) as column reductions over all rows. dx element (r, c) is stored at
+ *   (r / seq) * dx_batch_stride + (r % seq) * dx_seq_stride + (c / head_dim) * dx_head_stride + c % head_dim
+ * which covers both the plain [rows, n] layout (seq = 1, head_dim = n, dx_batch_stride = n) and the
+ * fused head-major (B,S,H,D) -> (B,H,S,D) store. flags: 1 = two launches (main + finalize)
+ * instead of one cooperative launch.
+ * Replaces sum_sum_2cd99e5eb23e/oracle.py:48-117, sum_sum_sum_3cac3bbf4e8f/oracle.py:100-193 and
+ * the head-split copy of pointwise_c0d19d490a2f/oracle.py:10-33. */
+int32_t b200_norm_bwd(const void* x, const void* dy, const void* weight, const float* mean,
+                      const float* rstd, void* dx, float* dweight, float* dbias, int64_t rows,
+                      int64_t n, int64_t x_row_stride, int64_t dy_row_stride, int32_t x_dtype,
+                      int32_t w_dtype, int32_t rms, int64_t seq, int64_t head_dim,
+                      int64_t dx_batch_stride, int64_t dx_seq_stride, int64_t dx_head_stride,
+                      void* scratch, int64_t scratch_bytes, int32_t flags, void* stream);
+
+/* Scratch bytes b200_batch_norm_fwd needs for `channels` channels. */
+int64_t b200_batch_norm_scratch_bytes(int64_t channels);
+
+/* BatchNorm2d training forward (+ ReLU when relu != 0): x and y are [batch, channels, spatial]
+ * with element strides (stride_n, stride_c, stride_s) - NCHW and channels-last both fit; y uses
+ * x's strides. running_mean/var (fp32 [C], nullable together) are updated in place;
+ * save_mean/save_invstd (fp32 [C], nullable) receive the batch statistics.
+ * Replaces var_mean_42fad1ece813/oracle.py:11-46, :49-87, :90-119 and :122-182. */
+int32_t b200_batch_norm_fwd(const void* x, void* y, const void* weight, const void* bias,
+                            float* running_mean, float* running_var, float* save_mean,
+                            float* save_invstd, int64_t batch, int64_t channels, int64_t spatial,
+                            int64_t stride_n, int64_t stride_c, int64_t stride_s, int32_t x_dtype,
+                            int32_t w_dtype, double eps, double momentum, int32_t relu, void* scratch,
+                            int64_t scratch_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* B200_ORACLES_H */

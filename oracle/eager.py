@@ -254,3 +254,48 @@ class Transpose2D(nn.Module):
     def forward(self, x):
         p = aten.transpose.int(x, -1, -2)
         return aten.clone.default(p, memory_format=torch.contiguous_format)
+
+
+class LayerNormBwd(nn.Module):
+    """LayerNorm backward returning (dx, dweight[, dbias]).
+
+    Graph: reference repros/canonical/sum_sum_sum_3cac3bbf4e8f/repro.py:23-45 - g = dy*w,
+    dx = (rstd/n) * ((g*n - sum(g)) - xhat*sum(g*xhat)) with xhat = (x-mean)*rstd,
+    dweight = sum_rows(dy*xhat); dbias = sum_rows(dy) is the usual third output of the family.
+    """
+
+    def __init__(self, with_bias_grad: bool = False):
+        super().__init__()
+        self.with_bias_grad = with_bias_grad
+
+    def forward(self, x, dy, weight, mean, rstd):
+        rows, n = x.shape
+        div = aten.div.Tensor(rstd, n)
+        dyf = _f32(dy) if dy.dtype != torch.float32 else dy
+        mul = aten.mul.Tensor(dyf, weight)
+        mul_1 = aten.mul.Tensor(mul, n)
+        sum_1 = aten.sum.dim_IntList(mul, [1], True)
+        sub = aten.sub.Tensor(mul_1, sum_1)
+        xf = _f32(x) if x.dtype != torch.float32 else x
+        sub_1 = aten.sub.Tensor(xf, mean)
+        mul_2 = aten.mul.Tensor(sub_1, rstd)
+        mul_3 = aten.mul.Tensor(mul, mul_2)
+        sum_2 = aten.sum.dim_IntList(mul_3, [1], True)
+        mul_4 = aten.mul.Tensor(mul_2, sum_2)
+        sub_2 = aten.sub.Tensor(sub, mul_4)
+        mul_5 = aten.mul.Tensor(div, sub_2)
+        dx = prims.convert_element_type.default(mul_5, x.dtype)
+        mul_6 = aten.mul.Tensor(dyf, mul_2)
+        dw = aten.sum.dim_IntList(mul_6, [0])
+        if self.with_bias_grad:
+            return (dx, dw, aten.sum.dim_IntList(dyf, [0]))
+        return (dx, dw)
+
+
+class SpatialMean(nn.Module):
+    """[N, C, H, W] -> [N, C, 1, 1] mean over H and W (reference
+    repros/canonical/mean_c9e1a8113328/repro.py:23-27); with a channels-last input this is a
+    column reduction per image."""
+
+    def forward(self, x):
+        return aten.mean.dim(x, [2, 3], True)

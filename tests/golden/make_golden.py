@@ -1,0 +1,85 @@
+"""Generate the golden fixtures in this directory from the reference itself.
+
+Run in a container that has the reference checkout (default /root/reference, override with the
+REFERENCE_ROOT environment variable):
+
+    python tests/golden/make_golden.py
+
+For every case below the script loads the reference's own ``Repro`` module from
+``repros/canonical/<dir>/repro.py``, builds inputs with the reference's own
+``repro_harness.make_inputs_from_config`` (seed 1, CPU, at a reduced shape written in the
+reference's compact shapes.json encoding), runs the module, and also records the reference's
+``byte_accounting.count_bytes_effective`` for the same call. Inputs, outputs and byte count go to
+``<case>.pt``. Nothing from the reference is copied: only tensors it computed are stored.
+"""
+import os
+import sys
+from pathlib import Path
+
+import torch
+
+REFERENCE_ROOT = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+HERE = Path(__file__).resolve().parent
+
+# case name -> (canonical dir in the reference, compact input entries at a reduced shape)
+CASES = {
+    "ln_fwd_f8ec553e339e": ("var_mean_f8ec553e339e",
+                            [[[4, 24, 320], "f32"], [[320], "f32"], [[320], "f32"], ["S", [96, 320]]]),
+    "rmsnorm_fwd_f667cd8901af": ("mean_f667cd8901af", [[[96, 512], "bf16"], [[512], "f32"]]),
+    "softmax_bias_20ccc18dda60": ("amax_sum_20ccc18dda60",
+                                  [[[32, 16, 64], "bf16"], [[4, 1, 16, 64], "bf16"],
+                                   ["S", [4, 8, 16, 64]], ["S", [32, 16, 64]]]),
+    "bn_relu_42fad1ece813": ("var_mean_42fad1ece813",
+                             # N*H*W stays 8192: the captured graph hard-codes the unbiasing factor 8192/8191
+                             [[[128, 8, 8, 8], "bf16", {"st": [512, 1, 64, 8]}], [[8], "f32"],
+                              [[8], "f32"], [[8], "f32"], [[8], "f32"]]),
+    "rms_bwd_2cd99e5eb23e": ("sum_sum_2cd99e5eb23e",
+                             # the row length stays 512: the captured graph hard-codes it as a divisor
+                             [[[], "bf16"], [[512], "f32"], [[60, 1], "f32"], [[60, 512], "bf16"],
+                              ["S", [60, 512]], ["S", [60, 512]], ["S", [512]]]),
+    "ln_bwd_3cac3bbf4e8f": ("sum_sum_sum_3cac3bbf4e8f",
+                            [[[60, 1], "f32"], [[], "bf16"], [[512], "f32"], [[60, 512], "bf16"],
+                             [[60, 1], "f32"], ["S", [60, 512]]]),
+    "colsum_eb86a17deab9": ("sum_eb86a17deab9", [[[4, 48, 160], "f32"]]),
+    "headsplit_c0d19d490a2f": ("pointwise_c0d19d490a2f",
+                               [[[64, 96], "bf16"], ["S", [4, 16, 96]], ["S", [4, 16, 3, 32]],
+                                ["S", [12, 16, 32]]]),
+    "transpose_021e90d9c17d": ("pointwise_021e90d9c17d", [[[4, 3, 49, 32], "bf16"], ["S", [4, 96, 7, 7]]]),
+    "logsoftmax_d16035e7b826": ("amax_sum_d16035e7b826", [[[24, 520], "bf16"], ["S", [2, 12, 517]]]),
+    "softmax_long_7079889cfc04": ("amax_sum_7079889cfc04", [[[6, 5000], "bf16"]]),
+    "spatial_mean_c9e1a8113328": ("mean_c9e1a8113328", [[[4, 48, 5, 5], "bf16", {"st": [1200, 1, 240, 48]}]]),
+}
+
+
+def main():
+    sys.path.insert(0, str(REFERENCE_ROOT))
+    sys.path.insert(0, str(REFERENCE_ROOT / "scripts"))
+    import byte_accounting
+    import input_codec
+    import oracle_harness
+    import repro_harness
+
+    def build_inputs(compact):
+        specs = [input_codec.spec_from_compact(e) for e in compact]
+        for s in specs:
+            if s.get("kind") == "tensor":
+                s["device"] = "cpu"
+        torch.manual_seed(1)
+        return repro_harness.make_inputs_from_config({"inputs": specs})
+
+    for name, (dirname, compact) in CASES.items():
+        repro_dir = REFERENCE_ROOT / "repros" / "canonical" / dirname
+        module = oracle_harness.load_repro_module(repro_dir)
+        inputs = build_inputs(compact)
+        with torch.no_grad():
+            outputs = module.Repro()(*build_inputs(compact))
+        nbytes = byte_accounting.count_bytes_effective(module.Repro(), build_inputs(compact))
+        flat = oracle_harness._normalize_outputs(outputs)
+        torch.save({"reference_dir": dirname, "compact_inputs": compact, "inputs": inputs,
+                    "outputs": [o.clone() for o in flat], "effective_bytes": int(nbytes),
+                    "torch_version": torch.__version__}, HERE / f"{name}.pt")
+        print(f"{name}: {len(flat)} outputs, {nbytes} bytes")
+
+
+if __name__ == "__main__":
+    main()

@@ -2,7 +2,7 @@
 import pytest
 import torch
 
-from conftest import assert_close
+from conftest import assert_close, assert_sum_close
 
 pytestmark = pytest.mark.gpu
 
@@ -47,13 +47,8 @@ def _stats(x, eps=1e-6):
 
 
 def _close_columns(got, want, anchor, what):
-    """Column sums over many rows: strict tolerance against the eager fp32 result, or - where
-    summation order alone moves an fp32 sum by more than the absolute tolerance - against the
-    same graph evaluated in fp64."""
-    try:
-        assert_close(got, want, what)
-    except AssertionError:
-        assert_close(got, anchor.float(), what + " (fp64 anchor)")
+    """Column sums over many rows (see conftest.assert_sum_close)."""
+    assert_sum_close(got, want, anchor, what)
 
 
 @pytest.mark.parametrize("two_launch", [False, True])

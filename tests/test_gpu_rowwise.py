@@ -6,7 +6,7 @@ restatement of the reference graph (oracle/eager.py) on the CPU, on the same see
 import pytest
 import torch
 
-from conftest import assert_close
+from conftest import assert_close, assert_sum_close
 
 pytestmark = pytest.mark.gpu
 
@@ -36,17 +36,12 @@ ROW_SHAPES = [
 def test_row_reduce_matches_eager(op, dtype, shape):
     from oracle.eager import RowReduce
     x = _randn(shape, dtype, seed=sum(shape) + len(op))
-    if op == "sum" and dtype == torch.float32:
-        # A long fp32 sum of unnormalised values differs between summation orders by more than
-        # the absolute tolerance wherever the result happens to be near zero; the eager fp32
-        # module is itself that far from the exact sum. The kernel is held to the tolerance
-        # against the eager graph evaluated in fp64 (the reference's own anchor for its numerics
-        # gate), which it must match as a correctly rounded sum would.
-        want = RowReduce(op)(x.double()).float()
-    else:
-        want = RowReduce(op)(x)
+    want = RowReduce(op)(x)
     got = _kernels().row_reduce(x.cuda(), op)
-    assert_close(got, want, f"row_reduce {op} {dtype} {shape}")
+    if op == "sum" and dtype == torch.float32:
+        assert_sum_close(got, want, RowReduce(op)(x.double()), f"row_reduce {op} {dtype} {shape}")
+    else:
+        assert_close(got, want, f"row_reduce {op} {dtype} {shape}")
 
 
 def test_row_reduce_strided_rows_and_offset():
