@@ -26,6 +26,8 @@
 // three-launch general path: strided statistics, finalize, strided normalise.
 #include "rowwise.cuh"
 
+#include <mutex>
+
 namespace b200 {
 
 struct BatchNormParams {
@@ -426,4 +428,92 @@ extern "C" int b200_batch_norm_fwd(const void* x, void* y, const void* weight, c
     case B200_F16: return launch_batch_norm<__half>(p, fast, (size_t)scratch_bytes, st);
   }
   return fail(B200_ERR_INVALID, "b200_batch_norm_fwd: unknown dtype %d", x_dtype);
+}
+
+// ----------------------------------------------------------------------------------------------
+// BatchNorm forward for callers that cannot hand over scratch memory.
+//
+// Some hosts of this library are not allowed to allocate device memory at all: a serving process
+// whose framework carves one arena at start-up and forbids plug-ins to call cudaMalloc (the call
+// would also synchronise the whole device in the middle of a request), or an embedding where the
+// only device buffers the caller owns are the tensors it was given. b200_batch_norm_fwd needs a
+// scratch buffer from its caller; this variant brings its own: a fixed array in the library's
+// device image. Every GPU that loads the library holds those bytes until the process exits, which
+// is why the size is capped (B200_BN_STATIC_MAX_CHANNELS channels, about 1.3 MB).
+//
+// The array's name is only meaningful in device code. On the host it is a stand-in symbol, not a
+// device address, so the address is looked up once per device with cudaGetSymbolAddress - on the
+// first call made while that device is current - and kept. That first call therefore does a little
+// set-up work and should be made before any stream capture begins.
+//
+// All calls on a device share the one array and it keeps whatever the previous call left in it.
+// The only part that must start at zero, the grid-barrier words, is cleared on the stream before
+// every launch; partial sums and statistics are fully rewritten before they are read. Two calls
+// that overlap on the GPU (different streams, no ordering between them) would race on the array:
+// callers must order them.
+// ----------------------------------------------------------------------------------------------
+#define B200_BN_STATIC_MAX_CHANNELS 1024
+#define B200_BN_STATIC_MAX_GROUPS 160  // partial rows: one per CTA (<= SM count) or per split (<= 64)
+
+namespace b200 {
+
+constexpr size_t kBnStaticScratchBytes =
+    256 + ((size_t)B200_BN_STATIC_MAX_GROUPS * 2 * B200_BN_STATIC_MAX_CHANNELS + 2 * B200_BN_STATIC_MAX_CHANNELS) *
+              sizeof(float);
+
+static __device__ __align__(256) unsigned char g_bn_static_scratch[kBnStaticScratchBytes];
+
+// Device address of the array on the current device; looked up on first use per device.
+static int bn_static_scratch_address(void** out) {
+  static void* address[64] = {nullptr};
+  static std::mutex mu;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail((int)e, "b200_batch_norm_fwd_static_scratch: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(B200_ERR_UNSUPPORTED, "b200_batch_norm_fwd_static_scratch: device index %d", dev);
+  std::lock_guard<std::mutex> lock(mu);
+  if (address[dev] == nullptr) {
+    void* ptr = nullptr;
+    e = cudaGetSymbolAddress(&ptr, g_bn_static_scratch);  // `dev` is the current device
+    if (e != cudaSuccess || ptr == nullptr) {
+      cudaGetLastError();
+      return fail(e != cudaSuccess ? (int)e : B200_ERR_INVALID,
+                  "b200_batch_norm_fwd_static_scratch: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    }
+    address[dev] = ptr;
+  }
+  *out = address[dev];
+  return B200_OK;
+}
+
+}  // namespace b200
+
+extern "C" int b200_batch_norm_fwd_static_scratch(const void* x, void* y, const void* weight, const void* bias,
+                                                  float* running_mean, float* running_var, float* save_mean,
+                                                  float* save_invstd, int64_t batch, int64_t channels,
+                                                  int64_t spatial, int64_t stride_n, int64_t stride_c,
+                                                  int64_t stride_s, int32_t x_dtype, int32_t w_dtype, double eps,
+                                                  double momentum, int32_t relu, void* stream) {
+  if (channels > B200_BN_STATIC_MAX_CHANNELS)
+    return fail(B200_ERR_UNSUPPORTED,
+                "b200_batch_norm_fwd_static_scratch: %lld channels exceed the built-in scratch (max %d); "
+                "use b200_batch_norm_fwd with a caller-provided scratch buffer",
+                (long long)channels, B200_BN_STATIC_MAX_CHANNELS);
+  if (channels > 0 && b200_batch_norm_scratch_bytes(channels) > (int64_t)kBnStaticScratchBytes)
+    return fail(B200_ERR_UNSUPPORTED,
+                "b200_batch_norm_fwd_static_scratch: this device needs %lld scratch bytes for %lld channels, "
+                "the built-in array holds %zu",
+                (long long)b200_batch_norm_scratch_bytes(channels), (long long)channels, kBnStaticScratchBytes);
+  void* scratch = nullptr;
+  int rc = bn_static_scratch_address(&scratch);
+  if (rc != B200_OK) return rc;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(scratch, 0, 256, st);  // the barrier words must start at zero
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return fail((int)e, "b200_batch_norm_fwd_static_scratch: clearing the barrier words: %s", cudaGetErrorString(e));
+  }
+  return b200_batch_norm_fwd(x, y, weight, bias, running_mean, running_var, save_mean, save_invstd, batch,
+                             channels, spatial, stride_n, stride_c, stride_s, x_dtype, w_dtype, eps, momentum,
+                             relu, scratch, (int64_t)kBnStaticScratchBytes, stream);
 }

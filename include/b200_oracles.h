@@ -128,6 +128,22 @@ int32_t b200_batch_norm_fwd(const void* x, void* y, const void* weight, const vo
                             int32_t w_dtype, double eps, double momentum, int32_t relu, void* scratch,
                             int64_t scratch_bytes, void* stream);
 
+/* b200_batch_norm_fwd for callers that may not allocate device memory (a host framework that owns
+ * the only arena and forbids plug-ins to call cudaMalloc, or a caller that owns nothing but the
+ * tensors it was handed): the scratch lives in a fixed array inside the library's device image
+ * instead of a caller-provided buffer. Same arguments minus scratch. Limits: at most 1024 channels
+ * (larger requests return B200_ERR_UNSUPPORTED); every GPU that loads the library holds the array
+ * (about 1.3 MB) until the process exits. The first call on each device looks up the array's
+ * device address and should be made before any stream capture. All calls on a device share the
+ * array: calls that overlap on the GPU race and must be ordered by the caller. Allocates nothing.
+ * This entry point has no counterpart in the reference. */
+int32_t b200_batch_norm_fwd_static_scratch(const void* x, void* y, const void* weight, const void* bias,
+                                           float* running_mean, float* running_var, float* save_mean,
+                                           float* save_invstd, int64_t batch, int64_t channels,
+                                           int64_t spatial, int64_t stride_n, int64_t stride_c,
+                                           int64_t stride_s, int32_t x_dtype, int32_t w_dtype, double eps,
+                                           double momentum, int32_t relu, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
