@@ -25,8 +25,10 @@
 // Any other layout (NCHW, channel counts that are not a multiple of the vector width) takes the
 // three-launch general path: strided statistics, finalize, strided normalise.
 #include "rowwise.cuh"
+#include "tile_stream.cuh"
 
 #include <mutex>
+#include <type_traits>
 
 namespace b200 {
 
@@ -50,8 +52,9 @@ struct BatchNormParams {
   float* partials;  // [P][2][C]
   float* stats;     // [2][C] mean, invstd (scratch copy every CTA reads)
   unsigned int* bar;
-  long long rows_per_cta;  // contiguous row range of each CTA (a multiple of rows-per-pass)
-  int smem_tiles;          // tiles of each CTA kept in shared memory between the passes
+  long long rows_per_cta;  // contiguous row range of each CTA
+  int smem_tiles;          // stages of the shared-memory ring
+  int local_stats;         // 1: every CTA combines all partials itself (one grid barrier instead of two)
 };
 
 template <typename T, bool VECTOR>
@@ -87,85 +90,204 @@ __device__ __forceinline__ void bn_finalize_channel(const BatchNormParams& p, in
   }
 }
 
+// Turns the fp64 totals of the shifted sums of one channel into mean / invstd and, for the one
+// caller that owns the channel's global outputs, writes the saved and running statistics.
+__device__ __forceinline__ void bn_channel_stats(const BatchNormParams& p, int c, double s1, double s2, float shift,
+                                                 bool write_global, float* mean_out, float* invstd_out) {
+  const double mean_shifted = s1 / p.count;
+  double var = (s2 - s1 * mean_shifted) / p.count;
+  if (var < 0.0) var = 0.0;
+  const float mean = (float)((double)shift + mean_shifted);
+  const float varf = (float)var;
+  const float invstd = rsqrtf(varf + p.eps);
+  *mean_out = mean;
+  *invstd_out = invstd;
+  if (write_global) {
+    if (p.save_mean) p.save_mean[c] = mean;
+    if (p.save_invstd) p.save_invstd[c] = invstd;
+    if (p.running_mean) {
+      p.running_mean[c] = mean * p.momentum + p.running_mean[c] * p.one_minus_momentum;
+      p.running_var[c] = (varf * p.unbias) * p.momentum + p.running_var[c] * p.one_minus_momentum;
+    }
+  }
+}
+
 // ----------------------------------------------------------------------------------------------
-// Channels-last fused kernel. blockDim.x = vpr * rpp (vpr = C / V vectors per row, rpp = rows per
-// pass); a tile is rpp * U rows. Dynamic shared memory: smem_tiles tiles of raw 16-byte vectors,
-// followed by the reduction area.
+// Channels-last fused kernel (one CTA per SM, cooperative launch).
+//
+// x is streamed through a ring of shared-memory stages with bulk asynchronous copies, one
+// contiguous tile of rows per copy. blockDim.x = vpr * rpp (vpr = C / V vector columns, rpp rows
+// per pass over the CTA); a thread owns one vector column and walks the tile's rows rpp apart, so
+// its per-channel accumulators and, later, its mean / invstd / weight / bias stay in registers.
+//   pass 1  tiles 0 .. n-1 of the CTA's row range go through the ring; the last `stages` tiles
+//           are simply never overwritten, so they are still in shared memory afterwards.
+//   stats   per-CTA shifted sums -> grid barrier -> fp64 combine per channel -> grid barrier.
+//   pass 2  tiles n-1 .. 0: first the ones still in shared memory, then the earlier ones, loaded
+//           again in reverse order (most recently read first: the likeliest to sit in L2) into
+//           the stage each one's successor just freed. y goes out with streaming stores.
+// One CTA barrier per tile carries the bounded-wait verdict and frees the previous tile's stage.
 // ----------------------------------------------------------------------------------------------
 template <typename T, int U>
-__global__ void __launch_bounds__(512, 1) batch_norm_cl_fused_kernel(const BatchNormParams p) {
+__global__ void __launch_bounds__(1024, 1)
+batch_norm_cl_stream_kernel(const BatchNormParams p, const int stages, const int red_rows, const int red_bytes) {
   constexpr int V = Elem<T>::V;
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int bar_ok;
+  const int tid = threadIdx.x;
   const int T_ = blockDim.x;
   const int vpr = p.channels / V;
   const int rpp = T_ / vpr;
-  const int vc = threadIdx.x % vpr;  // this thread's vector column
-  const int tr = threadIdx.x / vpr;  // this thread's row inside a pass
-  const long long tile_rows = (long long)rpp * U;
-  const int tile_vecs = T_ * U;
-  uint4* keep = reinterpret_cast<uint4*>(smem_raw);
-  float* red = reinterpret_cast<float*>(smem_raw + (size_t)p.smem_tiles * tile_vecs * sizeof(uint4));
+  const int vc = tid % vpr;
+  const int tr = tid / vpr;
+  const uint32_t row_bytes = (uint32_t)vpr * 16u;
+  // A tile is U passes of the CTA over rpp rows: as a flat array of 16-byte vectors, thread tid
+  // owns vectors tid, tid + T_, ..., which all fall into its vector column vc.
+  const int tile_rows = rpp * U;
+  const uint32_t tile_bytes = (uint32_t)tile_rows * row_bytes;
+  float* red = reinterpret_cast<float*>(smem + (size_t)stages * tile_bytes);  // [2][red_rows][C], reused later
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)stages * tile_bytes + red_bytes);
 
   const T* x = reinterpret_cast<const T*>(p.x);
-  const long long row_begin = (long long)blockIdx.x * p.rows_per_cta;
-  long long row_end = row_begin + p.rows_per_cta;
-  if (row_end > p.rows) row_end = p.rows;
-  const int my_tiles = row_end > row_begin ? (int)((row_end - row_begin + tile_rows - 1) / tile_rows) : 0;
-  const int first_kept = my_tiles - p.smem_tiles;  // tiles with local index >= this stay in smem
+  // Tiles are dealt out round-robin: CTA b owns tiles b, b + gridDim, ... so that at any moment
+  // the CTAs stream neighbouring addresses and finish within one tile of each other.
+  const long long total_tiles = (p.rows + tile_rows - 1) / tile_rows;
+  const int my_tiles =
+      total_tiles > blockIdx.x ? (int)((total_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x) : 0;
+  auto tile_row0 = [&](int k) { return ((long long)blockIdx.x + (long long)k * gridDim.x) * tile_rows; };
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
 
   const uint64_t keep_policy = l2_policy_evict_last();
+  const uint64_t drop_policy = l2_policy_evict_first();
+  auto issue = [&](int k, int slot, uint64_t policy) {  // thread 0 only
+    const long long r0 = tile_row0(k);
+    const long long left = p.rows - r0;
+    const uint32_t bytes = (uint32_t)(left < tile_rows ? left : tile_rows) * row_bytes;
+    mbar_arrive_expect_tx(&full[slot], bytes);
+    bulk_load_hint(smem + (size_t)slot * tile_bytes, x + r0 * p.channels, bytes, &full[slot], policy);
+  };
+
+#ifdef B200_BN_TIMING
+  unsigned long long* tlog = reinterpret_cast<unsigned long long*>(p.stats + 2 * p.channels) + blockIdx.x * 8;
+#define B200_TMARK(i)                                                        \
+  if (tid == 0) {                                                            \
+    unsigned long long t_;                                                   \
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                   \
+    tlog[i] = t_;                                                            \
+  }
+#else
+#define B200_TMARK(i)
+#endif
+  B200_TMARK(0)
+  bool failed = false;
+  uint32_t phase_bits = 0;  // bit s: parity of the next completion of stage s
+  int issued = 0;           // pass 1: tiles whose copy has been started
+  if (tid == 0) {
+    for (; issued < my_tiles && issued < stages; ++issued) issue(issued, issued, keep_policy);
+  }
+  // What thread 0 still has in flight when a wait runs out: wait for it (bounded) before leaving.
+  auto drain = [&](int first_stage_hint) {
+    (void)first_stage_hint;
+    for (int s = 0; s < stages; ++s) mbar_wait(&full[s], (phase_bits >> s) & 1u);
+  };
 
   // ---- pass 1: shifted sums -------------------------------------------------------------------
-  float shift[V];
+  f32x2 shift[V / 2], s1[V / 2], s2[V / 2];
   {
     float f[V];
     Elem<T>::unpack(ld_keep(x + (long long)vc * V), f);  // row 0 of this thread's channels
 #pragma unroll
-    for (int i = 0; i < V; ++i) shift[i] = f[i];
-  }
-  float s1[V], s2[V];
-#pragma unroll
-  for (int i = 0; i < V; ++i) s1[i] = s2[i] = 0.f;
-
-  for (int t = 0; t < my_tiles; ++t) {
-    const long long r0 = row_begin + (long long)t * tile_rows + tr;
-    uint4 raw[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long r = r0 + (long long)u * rpp;
-      if (r < row_end) raw[u] = ld_policy(x + r * p.channels + (long long)vc * V, keep_policy);
+    for (int i = 0; i < V / 2; ++i) {
+      shift[i] = pack2(f[2 * i], f[2 * i + 1]);
+      s1[i] = s2[i] = splat2(0.f);
     }
-    const bool stash = t >= first_kept;
+  }
+  {
+    int st = 0, issue_slot = issued % (stages > 0 ? stages : 1);
+    for (int k = 0; k < my_tiles; ++k) {
+      const bool arrived = mbar_wait(&full[st], (phase_bits >> st) & 1u);
+      phase_bits ^= 1u << st;
+      if (!__syncthreads_and(arrived)) {
+        failed = true;
+        break;
+      }
+      if (tid == 0 && k >= 1 && issued < my_tiles) {  // everyone is done with tile k-1
+        fence_proxy_async_smem();
+        issue(issued, issue_slot, keep_policy);
+        ++issued;
+        if (++issue_slot == stages) issue_slot = 0;
+      }
+      const long long left = p.rows - tile_row0(k);
+      const int vecs = (int)(left < tile_rows ? left : tile_rows) * vpr;  // vectors in this tile
+      const uint4* src = reinterpret_cast<const uint4*>(smem + (size_t)st * tile_bytes);
+      uint4 raw[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long r = r0 + (long long)u * rpp;
-      if (r < row_end) {
-        if (stash) keep[(size_t)(t - first_kept) * tile_vecs + u * T_ + threadIdx.x] = raw[u];
-        float f[V];
-        Elem<T>::unpack(raw[u], f);
+      for (int u = 0; u < U; ++u)
+        if (tid + u * T_ < vecs) raw[u] = src[tid + u * T_];
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-          const float d = f[i] - shift[i];
-          s1[i] += d;
-          s2[i] += d * d;
+      for (int u = 0; u < U; ++u) {
+        if (tid + u * T_ < vecs) {
+          float f[V];
+          Elem<T>::unpack(raw[u], f);
+#pragma unroll
+          for (int i = 0; i < V / 2; ++i) {
+            const f32x2 d = sub2(pack2(f[2 * i], f[2 * i + 1]), shift[i]);
+            s1[i] = add2(s1[i], d);
+            s2[i] = fma2(d, d, s2[i]);
+          }
         }
       }
+      if (++st == stages) st = 0;
     }
   }
-  // combine the rpp threads that share a vector column: red[2][rpp][C]
-  {
-    float* r1 = red;
-    float* r2 = red + (size_t)rpp * p.channels;
+  if (failed && tid == 0) {
+    note_wait_timeout();
+    atomicExch(&p.bar[1], 1u);
+    // undo the flip of the stage whose wait ran out, then wait (bounded) for every stage in flight
+    drain(0);
+  }
+
+  B200_TMARK(1)
+  // ---- per-CTA partial sums ---------------------------------------------------------------------
+  if (!failed) {
+    float a1[V], a2[V];
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-      r1[(size_t)tr * p.channels + vc * V + i] = s1[i];
-      r2[(size_t)tr * p.channels + vc * V + i] = s2[i];
+    for (int i = 0; i < V / 2; ++i) {
+      unpack2(s1[i], a1[2 * i], a1[2 * i + 1]);
+      unpack2(s2[i], a2[2 * i], a2[2 * i + 1]);
+    }
+    float* r1 = red;
+    float* r2 = red + (size_t)red_rows * p.channels;
+    int my_red_row;
+    bool writer = true;
+    if (red_rows != rpp) {
+      // vpr is a power of two <= 32: lanes vpr apart share a vector column; fold them first
+      for (int off = vpr; off < 32; off <<= 1) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          a1[i] += __shfl_xor_sync(0xffffffffu, a1[i], off);
+          a2[i] += __shfl_xor_sync(0xffffffffu, a2[i], off);
+        }
+      }
+      my_red_row = tid >> 5;
+      writer = (tid & 31) < vpr;
+    } else {
+      my_red_row = tr;
+    }
+    if (writer) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        r1[(size_t)my_red_row * p.channels + vc * V + i] = a1[i];
+        r2[(size_t)my_red_row * p.channels + vc * V + i] = a2[i];
+      }
     }
     __syncthreads();
-    for (int c = threadIdx.x; c < p.channels; c += T_) {
+    for (int c = tid; c < p.channels; c += T_) {
       float a = 0.f, b = 0.f;
-      for (int k = 0; k < rpp; ++k) {
+      for (int k = 0; k < red_rows; ++k) {
         a += r1[(size_t)k * p.channels + c];
         b += r2[(size_t)k * p.channels + c];
       }
@@ -173,74 +295,216 @@ __global__ void __launch_bounds__(512, 1) batch_norm_cl_fused_kernel(const Batch
       p.partials[((long long)blockIdx.x * 2 + 1) * p.channels + c] = b;
     }
   }
-  bool ok = grid_barrier(p.bar, 1u, &bar_ok);
+  B200_TMARK(2)
+  bool ok = !failed && grid_barrier(p.bar, 1u, &bar_ok);
+  B200_TMARK(3)
 
-  // ---- channel statistics: warps of all CTAs split the channels -------------------------------
-  if (ok) {
-    const int warps_per_cta = T_ >> 5;  // blockDim.x is a multiple of 32 (checked by the host)
-    const int gwarp = blockIdx.x * warps_per_cta + (threadIdx.x >> 5);
-    const int total_warps = gridDim.x * warps_per_cta;
-    for (int c = gwarp; c < p.channels; c += total_warps) {
-      const float k = Elem<T>::to_f32(__ldg(x + c));
-      bn_finalize_channel<T, true>(p, c, gridDim.x, k);
+  // ---- channel statistics ------------------------------------------------------------------------
+  // Few channels: every CTA sums all partials itself (coalesced reads of a table that sits in L2)
+  // and keeps mean / invstd in shared memory; CTA 0 also writes the global statistics. No second
+  // grid barrier. Many channels: the channels are dealt out to the CTAs, each combines its own
+  // with all threads, and a second grid barrier publishes the table.
+  double* dred = reinterpret_cast<double*>(red);
+  float* stats_s = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(red) + (size_t)T_ * 16);
+  const int P = gridDim.x;
+  if (ok && p.local_stats) {
+    const int C = p.channels;
+    const int PG = T_ / C;  // groups of threads that split the partial rows
+    const int c = tid % C, pg = tid / C;
+    double d1 = 0.0, d2 = 0.0;
+    if (pg < PG) {
+      for (int g0 = pg; g0 < P; g0 += 8 * PG) {  // eight pairs of loads in flight before any is used
+        float a[8], b[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const int g = g0 + u * PG;
+          a[u] = g < P ? __ldcg(p.partials + ((long long)g * 2) * C + c) : 0.f;
+          b[u] = g < P ? __ldcg(p.partials + ((long long)g * 2 + 1) * C + c) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          d1 += (double)a[u];
+          d2 += (double)b[u];
+        }
+      }
+      dred[((size_t)pg * C + c) * 2] = d1;
+      dred[((size_t)pg * C + c) * 2 + 1] = d2;
     }
+    __syncthreads();
+    if (tid < C) {
+      double t1 = 0.0, t2 = 0.0;
+      for (int g = 0; g < PG; ++g) {
+        t1 += dred[((size_t)g * C + tid) * 2];
+        t2 += dred[((size_t)g * C + tid) * 2 + 1];
+      }
+      float mean, invstd;
+      bn_channel_stats(p, tid, t1, t2, Elem<T>::to_f32(__ldg(x + tid)), blockIdx.x == 0, &mean, &invstd);
+      stats_s[tid] = mean;
+      stats_s[C + tid] = invstd;
+    }
+    __syncthreads();
+  } else if (ok) {
+    for (int c = blockIdx.x; c < p.channels; c += P) {
+      double d1 = 0.0, d2 = 0.0;
+      for (int g = tid; g < P; g += T_) {
+        d1 += (double)__ldcg(p.partials + ((long long)g * 2) * p.channels + c);
+        d2 += (double)__ldcg(p.partials + ((long long)g * 2 + 1) * p.channels + c);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+        d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+      }
+      if ((tid & 31) == 0) {
+        dred[(tid >> 5) * 2] = d1;
+        dred[(tid >> 5) * 2 + 1] = d2;
+      }
+      __syncthreads();
+      if (tid == 0) {
+        double t1 = 0.0, t2 = 0.0;
+        for (int w = 0; w < (T_ >> 5); ++w) {
+          t1 += dred[w * 2];
+          t2 += dred[w * 2 + 1];
+        }
+        float mean, invstd;
+        bn_channel_stats(p, c, t1, t2, Elem<T>::to_f32(__ldg(x + c)), true, &mean, &invstd);
+        p.stats[c] = mean;
+        p.stats[p.channels + c] = invstd;
+      }
+      __syncthreads();
+    }
+    B200_TMARK(4)
     ok = grid_barrier(p.bar, 2u, &bar_ok);
   }
+  B200_TMARK(5)
 
-  // ---- pass 2: normalise, reverse tile order -----------------------------------------------------
-  if (ok) {
-    float mean[V], invstd[V], wv[V], bv[V];
+  // ---- pass 2: normalise, tiles in reverse order --------------------------------------------------
+  if (ok && my_tiles > 0) {
+    f32x2 mean2[V / 2], inv2[V / 2], w2[V / 2], b2[V / 2];
 #pragma unroll
-    for (int i = 0; i < V; ++i) {
-      mean[i] = __ldcg(p.stats + vc * V + i);
-      invstd[i] = __ldcg(p.stats + p.channels + vc * V + i);
-      wv[i] = p.weight ? load_param1(p.weight, p.w_dtype, vc * V + i) : 1.f;
-      bv[i] = p.bias ? load_param1(p.bias, p.w_dtype, vc * V + i) : 0.f;
+    for (int i = 0; i < V / 2; ++i) {
+      const int c = vc * V + 2 * i;
+      if (p.local_stats) {
+        mean2[i] = pack2(stats_s[c], stats_s[c + 1]);
+        inv2[i] = pack2(stats_s[p.channels + c], stats_s[p.channels + c + 1]);
+      } else {
+        mean2[i] = pack2(__ldcg(p.stats + c), __ldcg(p.stats + c + 1));
+        inv2[i] = pack2(__ldcg(p.stats + p.channels + c), __ldcg(p.stats + p.channels + c + 1));
+      }
+      w2[i] = p.weight ? pack2(load_param1(p.weight, p.w_dtype, c), load_param1(p.weight, p.w_dtype, c + 1))
+                       : splat2(1.f);
+      b2[i] = p.bias ? pack2(load_param1(p.bias, p.w_dtype, c), load_param1(p.bias, p.w_dtype, c + 1))
+                     : splat2(0.f);
     }
     T* y = reinterpret_cast<T*>(p.y);
-    const uint64_t drop_policy = l2_policy_evict_first();
-    for (int t = my_tiles - 1; t >= 0; --t) {
-      const long long r0 = row_begin + (long long)t * tile_rows + tr;
-      uint4 raw[U];
-      const bool stashed = t >= first_kept;
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const long long r = r0 + (long long)u * rpp;
-        if (r < row_end) {
-          raw[u] = stashed ? keep[(size_t)(t - first_kept) * tile_vecs + u * T_ + threadIdx.x]
-                           : ld_policy(x + r * p.channels + (long long)vc * V, drop_policy);
-        }
+    const int resident_from = my_tiles - (my_tiles < stages ? my_tiles : stages);  // tiles >= this are in smem
+    int st = (my_tiles - 1) % stages;
+    int next_load = resident_from - 1;  // next tile to bring back, descending
+    for (int k = my_tiles - 1; k >= 0; --k) {
+      bool arrived = true;
+      if (k < resident_from) {
+        arrived = mbar_wait(&full[st], (phase_bits >> st) & 1u);
+        phase_bits ^= 1u << st;
       }
+      if (!__syncthreads_and(arrived)) {
+        failed = true;
+        break;
+      }
+      if (tid == 0 && k < my_tiles - 1 && next_load >= 0) {
+        // everyone is done with tile k+1: its stage takes tile k+1-stages (= next_load)
+        int freed = st + 1;
+        if (freed == stages) freed = 0;
+        fence_proxy_async_smem();
+        issue(next_load, freed, drop_policy);
+        --next_load;
+      }
+      const long long r0 = tile_row0(k);
+      const long long left = p.rows - r0;
+      const int vecs = (int)(left < tile_rows ? left : tile_rows) * vpr;
+      const uint4* src = reinterpret_cast<const uint4*>(smem + (size_t)st * tile_bytes);
+      uint4* dst = reinterpret_cast<uint4*>(y + r0 * p.channels);
+      // Vectors are read one by one (the compiler hoists what the register budget allows): the
+      // per-channel constants already take half of the 64 registers a 1024-thread CTA may use.
 #pragma unroll
       for (int u = 0; u < U; ++u) {
-        const long long r = r0 + (long long)u * rpp;
-        if (r < row_end) {
-          float f[V];
-          Elem<T>::unpack(raw[u], f);
+        if (tid + u * T_ >= vecs) continue;
+        float f[V];
+        Elem<T>::unpack(src[tid + u * T_], f);
+        uint4 packed;
+        if constexpr (sizeof(T) == 2) {
+          using P2 = typename std::conditional<std::is_same<T, __half>::value, __half2, __nv_bfloat162>::type;
+          uint32_t wds[4];
 #pragma unroll
-          for (int i = 0; i < V; ++i) {
-            float o = ((f[i] - mean[i]) * invstd[i]) * wv[i] + bv[i];
-            if (p.relu) o = o < 0.f ? 0.f : o;  // relu commutes with the monotone rounding below
-            f[i] = o;
+          for (int i = 0; i < V / 2; ++i) {
+            f32x2 o = add2(mul2(mul2(sub2(pack2(f[2 * i], f[2 * i + 1]), mean2[i]), inv2[i]), w2[i]), b2[i]);
+            float oa, ob;
+            unpack2(o, oa, ob);
+            P2 h;
+            if constexpr (std::is_same<T, __half>::value) {
+              h = __floats2half2_rn(oa, ob);
+              if (p.relu) h = __hmax2_nan(h, __float2half2_rn(0.f));  // ReLU after the cast; NaN stays NaN
+            } else {
+              h = __floats2bfloat162_rn(oa, ob);
+              if (p.relu) h = __hmax2_nan(h, __float2bfloat162_rn(0.f));
+            }
+            wds[i] = *reinterpret_cast<uint32_t*>(&h);
           }
-          st_stream(y + r * p.channels + (long long)vc * V, Elem<T>::pack(f));
+          packed = make_uint4(wds[0], wds[1], wds[2], wds[3]);
+        } else {
+          float o[V];
+#pragma unroll
+          for (int i = 0; i < V / 2; ++i) {
+            f32x2 r = add2(mul2(mul2(sub2(pack2(f[2 * i], f[2 * i + 1]), mean2[i]), inv2[i]), w2[i]), b2[i]);
+            unpack2(r, o[2 * i], o[2 * i + 1]);
+            if (p.relu) {
+              o[2 * i] = o[2 * i] < 0.f ? 0.f : o[2 * i];
+              o[2 * i + 1] = o[2 * i + 1] < 0.f ? 0.f : o[2 * i + 1];
+            }
+          }
+          packed = Elem<T>::pack(o);
         }
+        st_stream(dst + tid + u * T_, packed);
       }
+      if (--st < 0) st = stages - 1;
+    }
+    if (failed && tid == 0) {
+      note_wait_timeout();
+      atomicExch(&p.bar[1], 1u);
+      drain(0);
     }
   }
+  B200_TMARK(6)
   grid_barrier_depart(p.bar);
 }
 
 // ----------------------------------------------------------------------------------------------
 // General path: x addressed as (n, c, s) with arbitrary strides.
 // ----------------------------------------------------------------------------------------------
-// Rows per pass of the fused kernel for C / V = vpr vector columns: the largest count that keeps
-// the CTA at <= 512 threads and a whole number of warps; 0 when there is none.
-static int fused_rows_per_pass(int vpr) {
-  if (vpr < 1 || vpr > 512) return 0;
-  int rpp = 512 / vpr;
+// Geometry of the fused kernel for vpr = C / V vector columns: CTA size (a multiple of both vpr
+// and 32, at most 1024) and the number of rows of the shared-memory reduction area. When vpr is a
+// power of two <= 32 the lanes of a warp that share a column are folded by shuffles first and the
+// area has one row per warp; otherwise it has one row per thread row and the CTA is kept at <= 256
+// threads so that it stays small. Returns 0 threads when there is no fit.
+struct FusedGeometry {
+  int threads;
+  int red_rows;
+};
+static FusedGeometry fused_geometry(int vpr) {
+  FusedGeometry g = {0, 0};
+  if (vpr < 1 || vpr > 1024) return g;
+  const bool pow2 = (vpr & (vpr - 1)) == 0;
+  if (pow2 && vpr <= 32) {
+    g.threads = 1024;
+    g.red_rows = 1024 / 32;
+    return g;
+  }
+  const int cap = vpr > 256 ? 1024 : 256;
+  int rpp = cap / vpr;
   while (rpp > 0 && (vpr * rpp) % 32 != 0) --rpp;
-  return rpp;
+  if (rpp == 0) return g;
+  g.threads = vpr * rpp;
+  g.red_rows = rpp;
+  return g;
 }
 
 template <typename T>
@@ -304,33 +568,41 @@ template <typename T>
 static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, size_t scratch_bytes,
                              cudaStream_t st) {
   constexpr int V = Elem<T>::V;
-  constexpr int U = 8;
   const DeviceInfo& dev = device_info();
   const long long stats_floats = 2LL * p.channels;
   if (channels_last_fast) {
     const int vpr = p.channels / V;
-    const int rpp = fused_rows_per_pass(vpr);
-    const int threads = vpr * rpp;
-    auto kernel = batch_norm_cl_fused_kernel<T, U>;
-    const long long tile_rows = (long long)rpp * U;
-    const long long passes = (p.rows + rpp - 1) / rpp;
+    const FusedGeometry geo = fused_geometry(vpr);
+    const int threads = geo.threads;
+    const int rpp = threads / vpr;
+    // A tile is U = 2 passes of the CTA (U * threads * 16 bytes): 32 KB at 1024 threads, small
+    // enough that the round-robin tile assignment leaves the CTAs within a few percent of each other.
+    constexpr int passes = 2;
+    auto kernel = batch_norm_cl_stream_kernel<T, passes>;
+    const size_t row_bytes = (size_t)vpr * 16;
+    const int tile_rows = rpp * passes;
+    const size_t tile_bytes = (size_t)tile_rows * row_bytes;
     long long grid = dev.sm_count;  // one CTA per SM
-    if (grid > passes) grid = passes;
+    const long long total_tiles = (p.rows + tile_rows - 1) / tile_rows;
+    if (grid > total_tiles) grid = total_tiles;
     const long long need = 256 + (grid * 2 * p.channels + stats_floats) * (long long)sizeof(float);
     if ((long long)scratch_bytes < need)
       return fail(B200_ERR_WORKSPACE, "b200_batch_norm_fwd: scratch of %zu bytes, need %lld", scratch_bytes, need);
-    p.rows_per_cta = (passes + grid - 1) / grid * rpp;
-    grid = (p.rows + p.rows_per_cta - 1) / p.rows_per_cta;
-    const long long tiles_per_cta = (p.rows_per_cta + tile_rows - 1) / tile_rows;
-    const size_t red_bytes = 2ull * rpp * p.channels * sizeof(float);
-    const size_t tile_bytes = (size_t)threads * U * sizeof(uint4);
-    long long room = (long long)dev.max_smem_optin - (long long)red_bytes - 1024;
-    int smem_tiles = room > 0 ? (int)(room / (long long)tile_bytes) : 0;
-    if (smem_tiles > tiles_per_cta) smem_tiles = (int)tiles_per_cta;
-    p.smem_tiles = smem_tiles;
-    const size_t smem = (size_t)smem_tiles * tile_bytes + red_bytes;
-    if (red_bytes + 1024 > (size_t)dev.max_smem_optin)
+    p.rows_per_cta = 0;  // unused: tiles are assigned round-robin
+    // reduction area: the fp32 fold of pass 1, later reused for the fp64 combine (16 bytes per
+    // thread) followed by the CTA's own mean / invstd table
+    size_t red_bytes = 2ull * geo.red_rows * p.channels * sizeof(float);
+    const size_t stats_area = (size_t)threads * 16 + 2ull * p.channels * sizeof(float);
+    if (red_bytes < stats_area) red_bytes = stats_area;
+    red_bytes = (red_bytes + 15) / 16 * 16;
+    p.local_stats = (p.channels <= threads && (long long)p.channels * grid <= 32768) ? 1 : 0;
+    const size_t fixed = red_bytes + 8 * sizeof(uint64_t) + 256;
+    if (fixed + 2 * tile_bytes > (size_t)dev.max_smem_optin)
       return fail(B200_ERR_UNSUPPORTED, "b200_batch_norm_fwd: %d channels need too much shared memory", p.channels);
+    int stages = (int)(((size_t)dev.max_smem_optin - fixed) / tile_bytes);
+    if (stages > 8) stages = 8;
+    const size_t smem = (size_t)stages * tile_bytes + red_bytes + 8 * sizeof(uint64_t);
+    p.smem_tiles = stages;
     cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) {
@@ -339,7 +611,8 @@ static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, size_t 
                   cudaGetErrorString(e));
     }
     p.stats = p.partials + grid * 2 * p.channels;
-    void* args[] = {&p};
+    int stages_arg = stages, red_rows_arg = geo.red_rows, red_bytes_arg = (int)red_bytes;
+    void* args[] = {&p, &stages_arg, &red_rows_arg, &red_bytes_arg};
     e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3((unsigned)grid), dim3(threads),
                                     args, smem, st);
     if (e != cudaSuccess) {
@@ -375,6 +648,10 @@ static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, size_t 
 
 using namespace b200;
 
+// Bounded waits of the fused kernel that ran out since the library was loaded (0 in normal
+// operation). Synchronises the device.
+extern "C" int64_t b200_batch_norm_wait_timeouts(void) { return (int64_t)read_wait_timeouts(); }
+
 extern "C" int64_t b200_batch_norm_scratch_bytes(int64_t channels) {
   const int sms = device_info().sm_count;
   return 256 + ((int64_t)(sms > 64 ? sms : 64) * 2 * channels + 2 * channels) * (int64_t)sizeof(float);
@@ -408,13 +685,13 @@ extern "C" int b200_batch_norm_fwd(const void* x, void* y, const void* weight, c
   p.relu = relu ? 1 : 0;
   p.bar = reinterpret_cast<unsigned int*>(scratch);
   p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + 256);
-  p.stats = nullptr; p.rows_per_cta = 0; p.smem_tiles = 0;
+  p.stats = nullptr; p.rows_per_cta = 0; p.smem_tiles = 0; p.local_stats = 0;
 
   const int eb = dtype_size(x_dtype);
   const int v = 16 / eb;
   // channels-last: c is the unit-stride dimension, rows are (n, s) pairs with a uniform stride of C
   const bool cl = stride_c == 1 && stride_s == channels && stride_n == spatial * channels;
-  const bool fast = cl && channels % v == 0 && fused_rows_per_pass((int)(channels / v)) > 0 &&
+  const bool fast = cl && channels % v == 0 && fused_geometry((int)(channels / v)).threads > 0 &&
                     aligned16(x) && aligned16(y);
   if (fast) {
     p.rows = batch * spatial;

@@ -293,12 +293,12 @@ __device__ __forceinline__ bool grid_barrier(unsigned int* bar, unsigned int pha
       if (seen >= target) break;
       unsigned int err;
       asm volatile("ld.global.relaxed.gpu.u32 %0, [%1];" : "=r"(err) : "l"(bar + 1) : "memory");
-      if (err != 0u || ++spins > (1u << 22)) {  // ~4M polls of >= 64 ns: a fraction of a second
+      if (err != 0u || ++spins > (1u << 22)) {  // ~4M polls: a fraction of a second
         atomicExch(&bar[1], 1u);
         ok = 0;
         break;
       }
-      __nanosleep(64);
+      if (spins > 4096) __nanosleep(64);  // poll tightly at first: the usual wait is a few microseconds
     }
     __threadfence();
     *smem_flag = ok;

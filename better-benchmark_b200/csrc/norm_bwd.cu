@@ -20,6 +20,9 @@
 // the partial rows are summed in fp64, in a fixed order, into dw/db. No atomics: results are
 // bit-reproducible. A two-launch variant (main + finalize) does the same without the barrier.
 #include "rowwise.cuh"
+#include "tile_stream.cuh"
+
+#include <cstdlib>
 
 namespace b200 {
 
@@ -39,6 +42,7 @@ struct NormBwdParams {
   // dx element (r, c) lives at (r / seq) * dx_batch_stride + (r % seq) * dx_seq_stride
   //                            + (c / head_dim) * dx_head_stride + (c % head_dim)
   int seq, head_dim;
+  FastDiv seq_div;  // rows < 2^31, so row / seq is a 32-bit fast division
   long long dx_batch_stride, dx_seq_stride, dx_head_stride;
   float n_f;
   float* partials;    // [groups][n] for dw, followed by [groups][n] for db
@@ -203,8 +207,9 @@ norm_bwd_kernel(const NormBwdParams p) {
       s2 = warp_reduce<SumOp>(s2);
     }
 
-    T* dxr = reinterpret_cast<T*>(p.dx) + (row / p.seq) * p.dx_batch_stride +
-             (row % p.seq) * p.dx_seq_stride;
+    const unsigned int bi = fast_div((unsigned int)row, p.seq_div);
+    const unsigned int si = (unsigned int)row - bi * (unsigned int)p.seq;
+    T* dxr = reinterpret_cast<T*>(p.dx) + (long long)bi * p.dx_batch_stride + (long long)si * p.dx_seq_stride;
     float k;  // per-row coefficient
     if constexpr (LN) {
       k = rstd / p.n_f;
@@ -255,6 +260,243 @@ norm_bwd_kernel(const NormBwdParams p) {
   }
   if (p.fused) {
     const bool ok = grid_barrier(p.bar, 1u, &bar_ok);
+    if (ok) {
+      if (p.dw) finalize_columns(p.partials, p.groups, p.n, p.dw, fin);
+      if (LN && p.db) finalize_columns(p.partials + (long long)p.groups * p.n, p.groups, p.n, p.db, fin);
+    }
+    grid_barrier_depart(p.bar);
+  }
+}
+
+// ----------------------------------------------------------------------------------------------
+// Streaming variant of the CTA-per-row kernel: rows of x and dy arrive in a ring of shared-memory
+// stages through bulk asynchronous copies (stages-1 rows of each in flight per CTA, whatever the
+// register pressure), the weight is converted to fp32 once per CTA and kept in shared memory, and
+// the arithmetic runs on packed fp32 pairs. The CTA barrier that publishes the row sums also
+// proves that every thread has copied its part of the stage to registers, so the stage is
+// refilled right after it.
+// ----------------------------------------------------------------------------------------------
+template <typename T, int CH, bool LN>
+__global__ void __launch_bounds__(512, CH == 1 ? 2 : 1)
+norm_bwd_stream_kernel(const NormBwdParams p, const int stages) {
+  constexpr int V = Elem<T>::V;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(16) float2 red[2][16];
+  __shared__ double fin[16 * 64];
+  __shared__ int bar_ok;
+  const int tid = threadIdx.x;
+  const int T_ = blockDim.x;
+  const int nv = p.n / V;
+  const uint32_t row_bytes = (uint32_t)nv * 16u;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)stages * 2 * row_bytes);
+  const T* xg = reinterpret_cast<const T*>(p.x);
+  const T* dyg = reinterpret_cast<const T*>(p.dy);
+  const long long my_rows = p.rows > blockIdx.x ? (p.rows - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+
+  auto issue = [&](long long k, int slot) {  // thread 0 only; slot = k mod stages, tracked incrementally
+    const long long row = (long long)blockIdx.x + k * gridDim.x;
+    uint64_t* bar = &full[slot];
+    unsigned char* dst = smem + (size_t)slot * 2 * row_bytes;
+    mbar_arrive_expect_tx(bar, 2 * row_bytes);
+    bulk_load(dst, xg + row * p.x_row_stride, row_bytes, bar);
+    bulk_load(dst + row_bytes, dyg + row * p.dy_row_stride, row_bytes, bar);
+  };
+  long long issued = 0;
+  int issue_slot = 0;
+  if (tid == 0) {
+    for (; issued < my_rows && issued < stages; ++issued) issue(issued, (int)issued);
+    issue_slot = (int)(issued % stages);
+  }
+
+  // A thread owns the same columns in every row: its slice of the weight stays in registers.
+  f32x2 wv[CH][V / 2];
+  f32x2 acc_w[CH][V / 2], acc_b[LN ? CH : 1][V / 2];
+  long long dx_col[CH];
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    const int j = c * T_ + tid;
+    float wf[V];
+    if (p.w && j < nv) {
+      load_param<V>(p.w, p.w_dtype, (long long)j * V, wf);
+    } else {
+#pragma unroll
+      for (int i = 0; i < V; ++i) wf[i] = 1.f;
+    }
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      wv[c][i] = pack2(wf[2 * i], wf[2 * i + 1]);
+      acc_w[c][i] = splat2(0.f);
+    }
+    const int col = j * V;
+    dx_col[c] = (long long)(col / p.head_dim) * p.dx_head_stride + (col % p.head_dim);
+  }
+#pragma unroll
+  for (int c = 0; c < (LN ? CH : 1); ++c)
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) acc_b[c][i] = splat2(0.f);
+
+  const int warp = tid >> 5, nwarps = T_ >> 5;
+  const float inv_n = 1.0f / p.n_f;
+  bool failed = false;
+  int parity = 0;
+  int st = 0;
+  uint32_t phase = 0;
+  for (long long k = 0; k < my_rows; ++k) {
+    const long long row = (long long)blockIdx.x + k * gridDim.x;
+    const bool arrived = mbar_wait(&full[st], phase);
+    const unsigned char* sx = smem + (size_t)st * 2 * row_bytes;
+    const unsigned char* sy = sx + row_bytes;
+    const float rstd = __ldg(p.rstd + row);
+    const float mean = LN ? __ldg(p.mean + row) : 0.f;
+    const f32x2 rstd2 = splat2(rstd), mean2 = splat2(mean);
+
+    f32x2 xv[CH][V / 2], gv[CH][V / 2];
+    f32x2 s1 = splat2(0.f), s2 = splat2(0.f);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int j = c * T_ + tid;
+      if (j < nv) {
+        float xf[V], dyf[V];
+        Elem<T>::unpack(*reinterpret_cast<const uint4*>(sx + (size_t)j * 16), xf);
+        Elem<T>::unpack(*reinterpret_cast<const uint4*>(sy + (size_t)j * 16), dyf);
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) {
+          const f32x2 x2 = pack2(xf[2 * i], xf[2 * i + 1]);
+          const f32x2 dy2 = pack2(dyf[2 * i], dyf[2 * i + 1]);
+          const f32x2 g2 = mul2(dy2, wv[c][i]);
+          gv[c][i] = g2;
+          if constexpr (LN) {
+            const f32x2 xhat = mul2(sub2(x2, mean2), rstd2);
+            xv[c][i] = xhat;
+            s1 = add2(s1, g2);
+            s2 = add2(s2, mul2(g2, xhat));
+            acc_w[c][i] = add2(acc_w[c][i], mul2(dy2, xhat));
+            acc_b[c][i] = add2(acc_b[c][i], dy2);
+          } else {
+            xv[c][i] = x2;
+            s2 = add2(s2, mul2(g2, x2));
+            acc_w[c][i] = add2(acc_w[c][i], mul2(dy2, mul2(x2, rstd2)));
+          }
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) xv[c][i] = gv[c][i] = splat2(0.f);
+      }
+    }
+    float a, b, t1 = 0.f, t2;
+    if constexpr (LN) {
+      unpack2(s1, a, b);
+      t1 = warp_reduce<SumOp>(a + b);
+    }
+    unpack2(s2, a, b);
+    t2 = warp_reduce<SumOp>(a + b);
+    if ((tid & 31) == 0) red[parity][warp] = make_float2(t1, t2);
+    if (!__syncthreads_and(arrived)) {
+      failed = true;
+      if (tid == 0) {
+        note_wait_timeout();
+        atomicExch(&p.bar[1], 1u);  // lets the other CTAs leave the grid barrier at once
+        int ds = st;
+        uint32_t dp = phase;
+        for (long long d = k; d < issued; ++d) {
+          mbar_wait(&full[ds], dp);
+          if (++ds == stages) { ds = 0; dp ^= 1u; }
+        }
+      }
+      break;
+    }
+    if (tid == 0 && issued < my_rows) {  // every thread holds its part of this stage in registers
+      fence_proxy_async_smem();
+      issue(issued, issue_slot);
+      ++issued;
+      if (++issue_slot == stages) issue_slot = 0;
+    }
+    t1 = 0.f;
+    t2 = 0.f;
+    const float4* r4 = reinterpret_cast<const float4*>(red[parity]);
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {  // two warps' (s1, s2) pairs per 16-byte read
+      if (2 * w < nwarps) {
+        const float4 t = r4[w];
+        t1 += t.x;
+        t2 += t.y;
+        if (2 * w + 1 < nwarps) {
+          t1 += t.z;
+          t2 += t.w;
+        }
+      }
+    }
+    parity ^= 1;
+
+    const unsigned int bi = fast_div((unsigned int)row, p.seq_div);
+    const unsigned int si = (unsigned int)row - bi * (unsigned int)p.seq;
+    T* dxr = reinterpret_cast<T*>(p.dx) + (long long)bi * p.dx_batch_stride + (long long)si * p.dx_seq_stride;
+    // The division by n of the aten graph is a multiplication by 1/n here (exact for powers of
+    // two, otherwise within one fp32 ulp of a per-row coefficient).
+    float kf;
+    if constexpr (LN) {
+      kf = rstd * inv_n;
+    } else {
+      kf = ((t2 * -0.5f) * (rstd * rstd * rstd)) * inv_n;
+    }
+    const f32x2 k2 = splat2(kf), n2 = splat2(p.n_f), s1b = splat2(t1), s2b = splat2(t2), two2 = splat2(2.0f);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int j = c * T_ + tid;
+      if (j < nv) {
+        float o[V];
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) {
+          f32x2 r;
+          if constexpr (LN) {
+            r = mul2(k2, sub2(sub2(mul2(gv[c][i], n2), s1b), mul2(xv[c][i], s2b)));
+          } else {
+            r = add2(mul2(gv[c][i], rstd2), mul2(k2, mul2(xv[c][i], two2)));
+          }
+          unpack2(r, o[2 * i], o[2 * i + 1]);
+        }
+        st_stream(dxr + dx_col[c], Elem<T>::pack(o));
+      }
+    }
+    if (++st == stages) {
+      st = 0;
+      phase ^= 1u;
+    }
+  }
+
+  if (!failed && (p.dw || p.db)) {
+    float* pw = p.partials + (long long)blockIdx.x * p.n;
+    float* pb = p.partials + ((long long)p.groups + blockIdx.x) * p.n;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int j = c * T_ + tid;
+      if (j < nv) {
+        float f[V];
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) unpack2(acc_w[c][i], f[2 * i], f[2 * i + 1]);
+#pragma unroll
+        for (int q = 0; q < V / 4; ++q)
+          reinterpret_cast<float4*>(pw + (long long)j * V)[q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+        if constexpr (LN) {
+          if (p.db) {
+#pragma unroll
+            for (int i = 0; i < V / 2; ++i) unpack2(acc_b[c][i], f[2 * i], f[2 * i + 1]);
+#pragma unroll
+            for (int q = 0; q < V / 4; ++q)
+              reinterpret_cast<float4*>(pb + (long long)j * V)[q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+          }
+        }
+      }
+    }
+  }
+  if (p.fused) {
+    const bool ok = !failed && grid_barrier(p.bar, 1u, &bar_ok);
     if (ok) {
       if (p.dw) finalize_columns(p.partials, p.groups, p.n, p.dw, fin);
       if (LN && p.db) finalize_columns(p.partials + (long long)p.groups * p.n, p.groups, p.n, p.db, fin);
@@ -335,21 +577,85 @@ __global__ void __launch_bounds__(128) norm_bwd_cols_general_kernel(const NormBw
   if (LN) p.partials[((long long)p.groups + blockIdx.y) * p.n + col] = ab;
 }
 
-static int cached_occupancy(const void* fn, int threads) {
-  // The occupancy query is a host-side calculation; cache it per (kernel, block size).
-  struct Entry { const void* fn; int threads; int blocks; };
-  static Entry cache[64];
+static int cached_occupancy(const void* fn, int threads, size_t smem = 0) {
+  // The occupancy query is a host-side calculation; cache it per (kernel, block size, smem).
+  struct Entry { const void* fn; int threads; size_t smem; int blocks; };
+  static Entry cache[128];
   static int used = 0;
   for (int i = 0; i < used; ++i)
-    if (cache[i].fn == fn && cache[i].threads == threads) return cache[i].blocks;
+    if (cache[i].fn == fn && cache[i].threads == threads && cache[i].smem == smem) return cache[i].blocks;
   int blocks = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, fn, threads, 0) != cudaSuccess) {
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, fn, threads, smem) != cudaSuccess) {
     cudaGetLastError();
     blocks = 1;
   }
   if (blocks < 1) blocks = 1;
-  if (used < 64) cache[used++] = Entry{fn, threads, blocks};
+  if (used < 128) cache[used++] = Entry{fn, threads, smem, blocks};
   return blocks;
+}
+
+static bool streaming_disabled() {
+  static const bool off = [] {
+    const char* e = getenv("B200_DISABLE_STREAMING");
+    return e && e[0] == '1';
+  }();
+  return off;
+}
+
+// CTA-per-row streaming launch; returns false when the shape does not fit (caller falls back).
+template <typename T, int CH, bool LN>
+static bool try_launch_norm_bwd_stream(NormBwdParams p, int threads, size_t scratch_bytes, bool cooperative,
+                                       cudaStream_t st, int* rc) {
+  constexpr int V = Elem<T>::V;
+  if (streaming_disabled() || p.rows < 1024) return false;
+  const DeviceInfo& dev = device_info();
+  const size_t row_bytes = (size_t)(p.n / V) * 16;
+  const size_t static_bytes = 10 * 1024;  // red + fin + flags
+  const size_t per_cta = ((size_t)dev.max_smem_optin - 2048) / 2;  // aim at two CTAs per SM
+  const size_t fixed = 8 * sizeof(uint64_t);
+  if (per_cta < static_bytes + fixed + 2 * 2 * row_bytes) return false;
+  int stages = (int)((per_cta - static_bytes - fixed) / (2 * row_bytes));
+  if (stages > 8) stages = 8;
+  const size_t smem = (size_t)stages * 2 * row_bytes + fixed;
+  auto kernel = norm_bwd_stream_kernel<T, CH, LN>;
+  cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  const int per_sm = cached_occupancy(reinterpret_cast<const void*>(kernel), threads, smem);
+  long long grid = (long long)per_sm * dev.sm_count;
+  if (grid > p.rows) grid = p.rows;
+  if (p.dw || p.db) {
+    const long long plane = (long long)p.n * sizeof(float);
+    const long long max_groups = ((long long)scratch_bytes - 256) / (2 * plane);
+    if (max_groups < 1) return false;
+    if (grid > max_groups) grid = max_groups;
+  }
+  p.groups = (int)grid;
+  p.fused = cooperative ? 1 : 0;
+  if (cooperative) {
+    int stages_arg = stages;
+    void* args[] = {&p, &stages_arg};
+    e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3((unsigned)grid), dim3(threads),
+                                    args, smem, st);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      *rc = fail((int)e, "b200_norm_bwd: cooperative launch failed: %s", cudaGetErrorString(e));
+      return true;
+    }
+    note_launch();
+    *rc = B200_OK;
+    return true;
+  }
+  kernel<<<(unsigned)grid, threads, smem, st>>>(p, stages);
+  *rc = launch_status("b200_norm_bwd (streaming)");
+  if (*rc == B200_OK && (p.dw || p.db)) {
+    norm_bwd_finalize_kernel<<<(p.n + 63) / 64, 512, 0, st>>>(p);
+    *rc = launch_status("b200_norm_bwd finalize");
+  }
+  return true;
 }
 
 template <typename T, int CH, bool BLOCK, bool LN>
@@ -407,13 +713,23 @@ static int launch_norm_bwd(NormBwdParams p, bool vector_ok, size_t scratch_bytes
       if (nv <= 64) return launch_norm_bwd_fast<T, 2, false, LN>(p, 256, scratch_bytes, cooperative, st);
       return launch_norm_bwd_fast<T, 4, false, LN>(p, 256, scratch_bytes, cooperative, st);
     }
+    int rc = B200_OK;
     if (nv <= 512) {
+      // streaming: one vector per thread (many warps, few registers, the weight slice resident)
+      const int wide = (int)((nv + 31) / 32 * 32);
+      if (try_launch_norm_bwd_stream<T, 1, LN>(p, wide, scratch_bytes, cooperative, st, &rc)) return rc;
       int threads = (int)((nv + 1) / 2);
       threads = (threads + 31) / 32 * 32;
       return launch_norm_bwd_fast<T, 2, true, LN>(p, threads, scratch_bytes, cooperative, st);
     }
+    if (nv <= 1024) {
+      int threads = (int)((nv + 1) / 2);
+      threads = (threads + 31) / 32 * 32;
+      if (try_launch_norm_bwd_stream<T, 2, LN>(p, threads, scratch_bytes, cooperative, st, &rc)) return rc;
+    }
     int threads = (int)((nv + 3) / 4);
     threads = (threads + 31) / 32 * 32;
+    if (try_launch_norm_bwd_stream<T, 4, LN>(p, threads, scratch_bytes, cooperative, st, &rc)) return rc;
     return launch_norm_bwd_fast<T, 4, true, LN>(p, threads, scratch_bytes, cooperative, st);
   }
   // general path: rows kernel + column kernel + finalize
@@ -436,6 +752,10 @@ static int launch_norm_bwd(NormBwdParams p, bool vector_ok, size_t scratch_bytes
 }  // namespace b200
 
 using namespace b200;
+
+// Bounded waits of the streaming kernel that ran out since the library was loaded (0 in normal
+// operation). Synchronises the device.
+extern "C" int64_t b200_norm_bwd_wait_timeouts(void) { return (int64_t)read_wait_timeouts(); }
 
 // Bytes of scratch that let the fast path run its largest grid for rows of n elements.
 extern "C" int64_t b200_norm_bwd_scratch_bytes(int64_t n) {
@@ -470,6 +790,7 @@ extern "C" int b200_norm_bwd(const void* x, const void* dy, const void* weight, 
   p.x = x; p.dy = dy; p.w = weight; p.mean = mean; p.rstd = rstd; p.dx = dx; p.dw = dweight; p.db = dbias;
   p.rows = rows; p.n = (int)n; p.x_row_stride = x_row_stride; p.dy_row_stride = dy_row_stride;
   p.w_dtype = w_dtype; p.seq = (int)seq; p.head_dim = (int)head_dim;
+  p.seq_div = make_fast_div(seq);
   p.dx_batch_stride = dx_batch_stride; p.dx_seq_stride = dx_seq_stride; p.dx_head_stride = dx_head_stride;
   p.n_f = (float)n;
   p.bar = reinterpret_cast<unsigned int*>(scratch);

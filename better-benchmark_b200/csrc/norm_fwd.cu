@@ -8,9 +8,13 @@
 //   LayerNorm: mean = sum(x)/n; var = sum((x-mean)^2)/(n-correction); rstd = 1/sqrt(var+eps)
 //              y = ((x - mean) * rstd) * w + b
 //   RMSNorm  : ms = sum(x*x)/n; rstd = 1/sqrt(ms+eps); y = (x * rstd) * w
-// The variance is the centred second pass over the row held in registers. Statistics are fp32.
+// The variance is the centred second pass over the row held in registers (squares accumulated with
+// fused multiply-adds: aten's var_mean has no multiply/add sequence to mirror). Statistics are fp32.
 // Any of y, mean, rstd, var may be null (var_mean alone = no y, no rstd).
 #include "rowwise.cuh"
+#include "tile_stream.cuh"
+
+#include <cstdlib>
 
 namespace b200 {
 
@@ -35,15 +39,16 @@ struct NormFwdParams {
 // rsqrtf is the 2-ulp hardware approximation aten's CUDA rsqrt uses as well.
 __device__ __forceinline__ float precise_rsqrt(float v) { return rsqrtf(v); }
 
-template <typename Tin, typename Tout, int CH, bool BLOCK>
-__global__ void __launch_bounds__(BLOCK ? 512 : 256)
+template <typename Tin, typename Tout, int CH, int G>
+__global__ void __launch_bounds__(G == 0 ? 512 : 256)
 norm_fwd_resident_kernel(const NormFwdParams p) {
   constexpr int V = Elem<Tin>::V;
   __shared__ float red[32];
-  const int lane = group_lane<BLOCK>();
-  const int G = group_size<BLOCK>();
-  const long long row = group_row<BLOCK>();
-  if (row >= p.rows) return;
+  const int lane = glane<G>();
+  const int gs = gsize<G>();
+  long long row = grow<G>();
+  const bool valid = row < p.rows;  // lanes of a partly filled last CTA recompute the last row
+  if (!valid) row = p.rows - 1;
 
   const Tin* x = reinterpret_cast<const Tin*>(p.x) + row * p.x_row_stride;
   const int nv = p.n / V;
@@ -51,31 +56,38 @@ norm_fwd_resident_kernel(const NormFwdParams p) {
   uint4 raw[CH];
 #pragma unroll
   for (int c = 0; c < CH; ++c) {
-    const int j = c * G + lane;
+    const int j = c * gs + lane;
     if (j < nv) raw[c] = ld_stream(x + (long long)j * V);
   }
-  float v[CH][V];
-  float s = 0.f;
+  // The row as packed fp32 pairs; slots past the end of the row hold zeros and add nothing.
+  f32x2 v[CH][V / 2];
+  f32x2 s2 = splat2(0.f);
+#pragma unroll
+  for (int c = 0; c < CH; ++c) {
+    float f[V];
+    if (c * gs + lane < nv) {
+      Elem<Tin>::unpack(raw[c], f);
+    } else {
+#pragma unroll
+      for (int i = 0; i < V; ++i) f[i] = 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) v[c][i] = pack2(f[2 * i], f[2 * i + 1]);
+  }
   if (p.rms) {
 #pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      if (c * G + lane < nv) {
-        Elem<Tin>::unpack(raw[c], v[c]);
+    for (int c = 0; c < CH; ++c)
 #pragma unroll
-        for (int i = 0; i < V; ++i) s += v[c][i] * v[c][i];
-      }
-    }
+      for (int i = 0; i < V / 2; ++i) s2 = fma2(v[c][i], v[c][i], s2);
   } else {
 #pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      if (c * G + lane < nv) {
-        Elem<Tin>::unpack(raw[c], v[c]);
+    for (int c = 0; c < CH; ++c)
 #pragma unroll
-        for (int i = 0; i < V; ++i) s += v[c][i];
-      }
-    }
+      for (int i = 0; i < V / 2; ++i) s2 = add2(s2, v[c][i]);
   }
-  s = group_reduce<SumOp, BLOCK>(s, red);
+  float sa, sb;
+  unpack2(s2, sa, sb);
+  const float s = greduce<SumOp, G>(sa + sb, red);
 
   float mean = 0.f, var, rstd;
   if (p.rms) {
@@ -83,23 +95,25 @@ norm_fwd_resident_kernel(const NormFwdParams p) {
     rstd = precise_rsqrt(var + p.eps);
   } else {
     mean = s * p.inv_n;
-    float q = 0.f;
+    const f32x2 mean2 = splat2(mean);
+    f32x2 q2 = splat2(0.f);
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
-      const int j = c * G + lane;
-      if (j < nv) {
+      if (c * gs + lane < nv) {  // padding slots must not contribute (0 - mean)^2
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-          v[c][i] = v[c][i] - mean;  // keep the centred value: the output needs it again
-          q += v[c][i] * v[c][i];
+        for (int i = 0; i < V / 2; ++i) {
+          v[c][i] = sub2(v[c][i], mean2);  // keep the centred value: the output needs it again
+          q2 = fma2(v[c][i], v[c][i], q2);
         }
       }
     }
-    q = group_reduce<SumOp, BLOCK>(q, red);
+    float qa, qb;
+    unpack2(q2, qa, qb);
+    const float q = greduce<SumOp, G>(qa + qb, red);
     var = q * p.inv_denom;
     rstd = precise_rsqrt(var + p.eps);
   }
-  if (lane == 0) {
+  if (lane == 0 && valid) {
     if (p.mean_out) p.mean_out[row] = mean;
     if (p.rstd_out) p.rstd_out[row] = rstd;
     if (p.var_out) p.var_out[row] = var;
@@ -107,28 +121,313 @@ norm_fwd_resident_kernel(const NormFwdParams p) {
   if (p.y == nullptr) return;
 
   Tout* y = reinterpret_cast<Tout*>(p.y) + row * p.y_row_stride;
+  const f32x2 rstd2 = splat2(rstd);
 #pragma unroll
   for (int c = 0; c < CH; ++c) {
-    const int j = c * G + lane;
-    if (j < nv) {
-      float o[V];
+    const int j = c * gs + lane;
+    if (j < nv && valid) {
+      f32x2 o[V / 2];
 #pragma unroll
-      for (int i = 0; i < V; ++i) o[i] = v[c][i] * rstd;
+      for (int i = 0; i < V / 2; ++i) o[i] = mul2(v[c][i], rstd2);
       if (p.w) {
         float wf[V];
         load_param<V>(p.w, p.w_dtype, (long long)j * V, wf);
 #pragma unroll
-        for (int i = 0; i < V; ++i) o[i] = o[i] * wf[i];
+        for (int i = 0; i < V / 2; ++i) o[i] = mul2(o[i], pack2(wf[2 * i], wf[2 * i + 1]));
       }
       if (p.b) {
         float bf[V];
         load_param<V>(p.b, p.w_dtype, (long long)j * V, bf);
 #pragma unroll
-        for (int i = 0; i < V; ++i) o[i] = o[i] + bf[i];
+        for (int i = 0; i < V / 2; ++i) o[i] = add2(o[i], pack2(bf[2 * i], bf[2 * i + 1]));
       }
-      store_converted<Tout, V>(y + (long long)j * V, o);
+      float of[V];
+#pragma unroll
+      for (int i = 0; i < V / 2; ++i) unpack2(o[i], of[2 * i], of[2 * i + 1]);
+      store_converted<Tout, V>(y + (long long)j * V, of);
     }
   }
+}
+
+// ----------------------------------------------------------------------------------------------
+// Streaming variant for many short rows: a persistent CTA pulls tiles of R = blockDim/G rows into
+// a ring of shared-memory stages with bulk asynchronous copies (S-1 tiles in flight per CTA,
+// independent of register use), groups of G lanes normalise one row each from shared memory, and
+// weight and bias are converted to fp32 once per CTA and kept in shared memory. One CTA barrier
+// per tile: it makes the bounded-wait outcome CTA-uniform and, at the same time, proves that the
+// previous tile's stage is free to be refilled.
+// ----------------------------------------------------------------------------------------------
+template <typename Tin, typename Tout, int CH, int G, bool EXACT>
+__global__ void __launch_bounds__(256, 4)
+norm_fwd_stream_kernel(const NormFwdParams p, const int stages, const int contiguous) {
+  constexpr int V = Elem<Tin>::V;
+  constexpr int PLANES = V / 4;  // fp32 copies of weight/bias are stored as planes of float4
+  extern __shared__ __align__(128) unsigned char smem[];
+  const int nv = p.n / V;
+  const uint32_t row_bytes = (uint32_t)nv * 16u;
+  const int R = blockDim.x / G;
+  const uint32_t tile_bytes = (uint32_t)R * row_bytes;
+  float* wsm = reinterpret_cast<float*>(smem + (size_t)stages * tile_bytes);
+  float* bsm = wsm + (size_t)nv * V;
+  uint64_t* full = reinterpret_cast<uint64_t*>(bsm + (size_t)nv * V);
+
+  const int lane = threadIdx.x & (G - 1);
+  const int grp = threadIdx.x / G;
+  const long long num_tiles = (p.rows + R - 1) / R;
+  const long long my_tiles =
+      num_tiles > blockIdx.x ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
+  const Tin* xg = reinterpret_cast<const Tin*>(p.x);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_init_fence();
+  }
+  for (int j = threadIdx.x; j < nv; j += blockDim.x) {
+    float f[V];
+    if (p.w) {
+      load_param<V>(p.w, p.w_dtype, (long long)j * V, f);
+#pragma unroll
+      for (int q = 0; q < PLANES; ++q)
+        *reinterpret_cast<float4*>(wsm + ((size_t)q * nv + j) * 4) = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+    }
+    if (p.b) {
+      load_param<V>(p.b, p.w_dtype, (long long)j * V, f);
+#pragma unroll
+      for (int q = 0; q < PLANES; ++q)
+        *reinterpret_cast<float4*>(bsm + ((size_t)q * nv + j) * 4) = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+    }
+  }
+  __syncthreads();
+
+  // Thread 0 only: start the copy of this CTA's k-th tile into stage `slot` (= k mod stages,
+  // tracked incrementally: a 64-bit modulo per tile would cost more than the tile's arithmetic).
+  auto issue = [&](long long k, int slot) {
+    const long long r0 = ((long long)blockIdx.x + k * gridDim.x) * R;
+    const long long left = p.rows - r0;
+    const uint32_t rows_here = (uint32_t)(left < R ? left : R);
+    uint64_t* bar = &full[slot];
+    unsigned char* dst = smem + (size_t)slot * tile_bytes;
+    mbar_arrive_expect_tx(bar, rows_here * row_bytes);
+    if (contiguous) {
+      bulk_load(dst, xg + r0 * p.x_row_stride, rows_here * row_bytes, bar);
+    } else {
+      for (uint32_t r = 0; r < rows_here; ++r)
+        bulk_load(dst + (size_t)r * row_bytes, xg + (r0 + r) * p.x_row_stride, row_bytes, bar);
+    }
+  };
+  long long issued = 0;
+  int issue_slot = 0;  // stage the next copy goes to
+  if (threadIdx.x == 0) {
+    for (; issued < my_tiles && issued < stages; ++issued) issue(issued, (int)issued);
+    issue_slot = (int)(issued % stages);
+  }
+
+  int st = 0;           // stage of tile k
+  uint32_t phase = 0;   // parity of that stage's current use
+  for (long long k = 0; k < my_tiles; ++k) {
+    const bool arrived = mbar_wait(&full[st], phase);
+    if (!__syncthreads_and(arrived)) {
+      // A copy did not complete within the bound: stop streaming. Thread 0 waits (bounded) for
+      // whatever it still has in flight so that nothing lands in shared memory after the exit.
+      if (threadIdx.x == 0) {
+        note_wait_timeout();
+        int ds = st;
+        uint32_t dp = phase;
+        for (long long d = k; d < issued; ++d) {
+          mbar_wait(&full[ds], dp);
+          if (++ds == stages) { ds = 0; dp ^= 1u; }
+        }
+      }
+      return;
+    }
+    // Everyone has passed the barrier, so everyone is done with tile k-1: refill its stage.
+    if (threadIdx.x == 0 && k >= 1 && issued < my_tiles) {
+      fence_proxy_async_smem();
+      issue(issued, issue_slot);
+      ++issued;
+      if (++issue_slot == stages) issue_slot = 0;
+    }
+
+    const long long row = ((long long)blockIdx.x + k * gridDim.x) * R + grp;
+    const bool valid = row < p.rows;
+    const unsigned char* rowbase = smem + (size_t)st * tile_bytes + (size_t)grp * row_bytes;
+
+    f32x2 v[CH][V / 2];
+    f32x2 s2 = splat2(0.f);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int j = c * G + lane;
+      float f[V];
+      if (EXACT || j < nv) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(rowbase + (size_t)j * 16);
+        Elem<Tin>::unpack(raw, f);
+      } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) f[i] = 0.f;
+      }
+#pragma unroll
+      for (int i = 0; i < V / 2; ++i) v[c][i] = pack2(f[2 * i], f[2 * i + 1]);
+    }
+    // one short chain per slot, combined afterwards: a single chain over the whole row would
+    // serialise on the add latency
+    f32x2 part[CH];
+    if (p.rms) {
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        part[c] = mul2(v[c][0], v[c][0]);
+#pragma unroll
+        for (int i = 1; i < V / 2; ++i) part[c] = fma2(v[c][i], v[c][i], part[c]);
+      }
+    } else {
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        part[c] = v[c][0];
+#pragma unroll
+        for (int i = 1; i < V / 2; ++i) part[c] = add2(part[c], v[c][i]);
+      }
+    }
+    s2 = part[0];
+#pragma unroll
+    for (int c = 1; c < CH; ++c) s2 = add2(s2, part[c]);
+    float sa, sb;
+    unpack2(s2, sa, sb);
+    const float s = greduce<SumOp, G>(sa + sb, nullptr);
+
+    float mean = 0.f, var, rstd;
+    if (p.rms) {
+      var = s * p.inv_n;
+      rstd = precise_rsqrt(var + p.eps);
+    } else {
+      mean = s * p.inv_n;
+      const f32x2 mean2 = splat2(mean);
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        part[c] = splat2(0.f);
+        if (EXACT || c * G + lane < nv) {
+#pragma unroll
+          for (int i = 0; i < V / 2; ++i) {
+            v[c][i] = sub2(v[c][i], mean2);
+            part[c] = fma2(v[c][i], v[c][i], part[c]);
+          }
+        }
+      }
+      f32x2 q2 = part[0];
+#pragma unroll
+      for (int c = 1; c < CH; ++c) q2 = add2(q2, part[c]);
+      float qa, qb;
+      unpack2(q2, qa, qb);
+      const float q = greduce<SumOp, G>(qa + qb, nullptr);
+      var = q * p.inv_denom;
+      rstd = precise_rsqrt(var + p.eps);
+    }
+    if (lane == 0 && valid) {
+      if (p.mean_out) p.mean_out[row] = mean;
+      if (p.rstd_out) p.rstd_out[row] = rstd;
+      if (p.var_out) p.var_out[row] = var;
+    }
+    if (p.y != nullptr && valid) {
+      Tout* y = reinterpret_cast<Tout*>(p.y) + row * p.y_row_stride;
+      const f32x2 rstd2 = splat2(rstd);
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        const int j = c * G + lane;
+        if (EXACT || j < nv) {
+          f32x2 o[V / 2];
+#pragma unroll
+          for (int i = 0; i < V / 2; ++i) o[i] = mul2(v[c][i], rstd2);
+          if (p.w) {
+#pragma unroll
+            for (int q = 0; q < PLANES; ++q) {
+              const float4 w4 = *reinterpret_cast<const float4*>(wsm + ((size_t)q * nv + j) * 4);
+              o[2 * q] = mul2(o[2 * q], pack2(w4.x, w4.y));
+              o[2 * q + 1] = mul2(o[2 * q + 1], pack2(w4.z, w4.w));
+            }
+          }
+          if (p.b) {
+#pragma unroll
+            for (int q = 0; q < PLANES; ++q) {
+              const float4 b4 = *reinterpret_cast<const float4*>(bsm + ((size_t)q * nv + j) * 4);
+              o[2 * q] = add2(o[2 * q], pack2(b4.x, b4.y));
+              o[2 * q + 1] = add2(o[2 * q + 1], pack2(b4.z, b4.w));
+            }
+          }
+          float of[V];
+#pragma unroll
+          for (int i = 0; i < V / 2; ++i) unpack2(o[i], of[2 * i], of[2 * i + 1]);
+          store_converted<Tout, V>(y + (long long)j * V, of);
+        }
+      }
+    }
+    if (++st == stages) {
+      st = 0;
+      phase ^= 1u;
+    }
+  }
+}
+
+// Geometry of the streaming kernel: lanes per row and register slots per lane for nv vectors.
+// At most 32 elements per thread, so that the kernel fits in 64 registers and four 256-thread CTAs
+// (32 warps) share an SM: with fewer warps the per-row dependency chains (two shuffle reductions)
+// leave the schedulers idle.
+static bool pick_stream_geometry(long long nv, int* g, int* ch) {
+  if (nv <= 8) { *g = 8; *ch = 1; return true; }
+  if (nv <= 16) { *g = 8; *ch = 2; return true; }
+  if (nv <= 24) { *g = 8; *ch = 3; return true; }
+  if (nv <= 32) { *g = 8; *ch = 4; return true; }
+  if (nv <= 48) { *g = 16; *ch = 3; return true; }
+  if (nv <= 64) { *g = 16; *ch = 4; return true; }
+  if (nv <= 96) { *g = 32; *ch = 3; return true; }
+  if (nv <= 128) { *g = 32; *ch = 4; return true; }
+  return false;
+}
+
+static bool streaming_disabled() {
+  static const bool off = [] {
+    const char* e = getenv("B200_DISABLE_STREAMING");
+    return e && e[0] == '1';
+  }();
+  return off;
+}
+
+template <typename Tin, typename Tout>
+static bool try_launch_norm_fwd_stream(const NormFwdParams& p, cudaStream_t st, int* rc) {
+  constexpr int V = Elem<Tin>::V;
+  const long long nv = p.n / V;
+  int g, ch;
+  if (streaming_disabled() || !pick_stream_geometry(nv, &g, &ch)) return false;
+  const long long total_bytes = p.rows * nv * 16;
+  if (total_bytes < (8ll << 20)) return false;  // small problems: the resident kernel is fine
+  const DeviceInfo& dev = device_info();
+  const int threads = 256;
+  const int R = threads / g;
+  const size_t tile_bytes = (size_t)R * nv * 16;
+  const size_t fixed = 2 * (size_t)nv * V * sizeof(float) + 8 * sizeof(uint64_t);
+  const size_t per_cta = ((size_t)dev.max_smem_optin - 4096) / 4;  // four CTAs per SM
+  if (fixed + 2 * tile_bytes > per_cta) return false;
+  int stages = (int)((per_cta - fixed) / tile_bytes);
+  if (stages > 8) stages = 8;
+  const size_t smem = (size_t)stages * tile_bytes + fixed;
+  const long long num_tiles = (p.rows + R - 1) / R;
+  long long grid = 4ll * dev.sm_count;
+  if (grid > num_tiles) grid = num_tiles;
+  const int contiguous = p.x_row_stride == p.n ? 1 : 0;
+  const bool exact = nv == (long long)g * ch;
+
+  auto launch = [&](auto kernel) {
+    cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      *rc = fail((int)e, "b200_norm_fwd: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+      return;
+    }
+    kernel<<<(unsigned)grid, threads, smem, st>>>(p, stages, contiguous);
+    *rc = launch_status("b200_norm_fwd (streaming)");
+  };
+#define B200_NFS(GG, CC)                                                            if (g == GG && ch == CC) {                                                          if (exact) launch(norm_fwd_stream_kernel<Tin, Tout, CC, GG, true>);               else launch(norm_fwd_stream_kernel<Tin, Tout, CC, GG, false>);                    return true;                                                                    }
+  B200_NFS(8, 1) B200_NFS(8, 2) B200_NFS(8, 3) B200_NFS(8, 4) B200_NFS(16, 3) B200_NFS(16, 4) B200_NFS(32, 3) B200_NFS(32, 4)
+#undef B200_NFS
+  return false;
 }
 
 // Element-wise kernel for ragged, unaligned or very long rows: one CTA per row, sweeps over
@@ -179,23 +478,31 @@ static int launch_norm_fwd(const NormFwdParams& p, bool vector_ok, cudaStream_t 
   constexpr int V = Elem<Tin>::V;
   if (p.rows > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "norm_fwd: too many rows");
   RowGeometry g;
+  if (vector_ok && p.n % V == 0) {
+    int rc = B200_OK;
+    if (try_launch_norm_fwd_stream<Tin, Tout>(p, st, &rc)) return rc;
+  }
   if (vector_ok && p.n % V == 0 && pick_row_geometry(p.n / V, &g)) {
+#define B200_NF_LAUNCH(GG, CC) norm_fwd_resident_kernel<Tin, Tout, CC, GG><<<grid, g.threads, 0, st>>>(p)
     if (!g.block) {
-      const int rows_per_cta = g.threads / 32;
+      const int rows_per_cta = g.threads / g.g;
       const unsigned grid = (unsigned)((p.rows + rows_per_cta - 1) / rows_per_cta);
-      switch (g.ch) {
-        case 1: norm_fwd_resident_kernel<Tin, Tout, 1, false><<<grid, g.threads, 0, st>>>(p); break;
-        case 2: norm_fwd_resident_kernel<Tin, Tout, 2, false><<<grid, g.threads, 0, st>>>(p); break;
-        default: norm_fwd_resident_kernel<Tin, Tout, 4, false><<<grid, g.threads, 0, st>>>(p); break;
+      if (g.g == 8) {
+        if (g.ch == 1) B200_NF_LAUNCH(8, 1);
+        else if (g.ch == 2) B200_NF_LAUNCH(8, 2);
+        else B200_NF_LAUNCH(8, 4);
+      } else if (g.g == 16) {
+        B200_NF_LAUNCH(16, 4);
+      } else {
+        B200_NF_LAUNCH(32, 4);
       }
     } else {
       const unsigned grid = (unsigned)p.rows;
-      switch (g.ch) {
-        case 2: norm_fwd_resident_kernel<Tin, Tout, 2, true><<<grid, g.threads, 0, st>>>(p); break;
-        case 4: norm_fwd_resident_kernel<Tin, Tout, 4, true><<<grid, g.threads, 0, st>>>(p); break;
-        default: norm_fwd_resident_kernel<Tin, Tout, 8, true><<<grid, g.threads, 0, st>>>(p); break;
-      }
+      if (g.ch == 2) B200_NF_LAUNCH(0, 2);
+      else if (g.ch == 4) B200_NF_LAUNCH(0, 4);
+      else B200_NF_LAUNCH(0, 8);
     }
+#undef B200_NF_LAUNCH
   } else {
     int threads = 1024;
     while (threads > 64 && threads / 2 >= p.n) threads /= 2;
@@ -207,6 +514,10 @@ static int launch_norm_fwd(const NormFwdParams& p, bool vector_ok, cudaStream_t 
 }  // namespace b200
 
 using namespace b200;
+
+// Bounded waits of the streaming kernel that ran out since the library was loaded (0 in normal
+// operation). Synchronises the device.
+extern "C" int64_t b200_norm_fwd_wait_timeouts(void) { return (int64_t)read_wait_timeouts(); }
 
 extern "C" int b200_norm_fwd(const void* x, const void* weight, const void* bias, void* y,
                              float* mean_out, float* rstd_out, float* var_out, int64_t rows,

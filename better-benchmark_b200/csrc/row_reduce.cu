@@ -169,7 +169,8 @@ extern "C" int b200_row_reduce(const void* x, void* out, int64_t rows, int64_t n
 
   RowReduceParams p;
   p.x = x; p.out = out; p.rows = rows; p.n = n;
-  p.xmap = RowMap{x_strides[0], x_strides[1], x_strides[2], (int)d1, (int)d2};
+  if (rows > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "b200_row_reduce: more than 2^31-1 rows");
+  p.xmap = make_row_map(x_strides, d1, d2);
   p.out_stride = out_stride; p.out_dtype = out_dtype;
   // mean of an empty row is 0 * (1/0) = NaN, as aten.mean returns
   p.post_scale = op == B200_REDUCE_MEAN ? 1.0f / (float)n : 1.0f;

@@ -11,20 +11,132 @@
 
 namespace b200 {
 
-// Maps a flat row index onto up to three outer dimensions with arbitrary element strides, so
-// broadcast operands (stride 0) and non-contiguous views need no copy. row = (i0*d1 + i1)*d2 + i2.
-struct RowMap {
-  long long s0, s1, s2;
-  int d1, d2;
+// Division by a run-time constant without a divide instruction: q = umulhi(n, mul) >> shr for
+// 0 <= n < 2^31 (host side picks mul/shr for the divisor d >= 1).
+struct FastDiv {
+  unsigned int mul, shr, d;
 };
 
+inline FastDiv make_fast_div(long long d) {
+  FastDiv f;
+  f.d = (unsigned int)d;
+  if (d <= 1) {
+    f.mul = 0;
+    f.shr = 0;
+    return f;
+  }
+  unsigned int lg = 0;
+  while ((1ull << lg) < (unsigned long long)d) ++lg;  // ceil(log2 d)
+  const unsigned int p = 31 + lg;
+  f.mul = (unsigned int)(((1ull << p) + (unsigned long long)d - 1) / (unsigned long long)d);
+  f.shr = p - 32;
+  return f;
+}
+
+__device__ __forceinline__ unsigned int fast_div(unsigned int n, const FastDiv& f) {
+  return f.d == 1 ? n : (__umulhi(n, f.mul) >> f.shr);
+}
+
+// Maps a flat row index onto up to three outer dimensions with arbitrary element strides, so
+// broadcast operands (stride 0) and non-contiguous views need no copy. row = (i0*d1 + i1)*d2 + i2.
+// Rows are limited to 2^31 - 1 (checked by the host).
+struct RowMap {
+  long long s0, s1, s2;
+  FastDiv d1, d2;
+};
+
+inline RowMap make_row_map(const int64_t* strides, long long d1, long long d2) {
+  RowMap m;
+  m.s0 = strides[0];
+  m.s1 = strides[1];
+  m.s2 = strides[2];
+  m.d1 = make_fast_div(d1);
+  m.d2 = make_fast_div(d2);
+  return m;
+}
+
+inline RowMap make_row_map_flat(long long row_stride) {
+  RowMap m;
+  m.s0 = row_stride;
+  m.s1 = m.s2 = 0;
+  m.d1 = make_fast_div(1);
+  m.d2 = make_fast_div(1);
+  return m;
+}
+
 __device__ __forceinline__ long long row_offset(const RowMap& m, long long row) {
-  if (m.d1 == 1 && m.d2 == 1) return row * m.s0;
-  const long long i2 = row % m.d2;
-  const long long t = row / m.d2;
-  const long long i1 = t % m.d1;
-  const long long i0 = t / m.d1;
-  return i0 * m.s0 + i1 * m.s1 + i2 * m.s2;
+  if (m.d1.d == 1 && m.d2.d == 1) return row * m.s0;
+  const unsigned int r = (unsigned int)row;
+  const unsigned int t = fast_div(r, m.d2);
+  const unsigned int i2 = r - t * m.d2.d;
+  const unsigned int i0 = fast_div(t, m.d1);
+  const unsigned int i1 = t - i0 * m.d1.d;
+  return (long long)i0 * m.s0 + (long long)i1 * m.s1 + (long long)i2 * m.s2;
+}
+
+// ----------------------------------------------------------------------------------------------
+// Packed fp32 pairs. sm_100 executes add/sub/mul/fma on two fp32 values held in one 64-bit
+// register pair as ONE instruction (same per-lane arithmetic throughput, half the issue slots),
+// with round-to-nearest on each half: numerically identical to the two scalar operations.
+// ----------------------------------------------------------------------------------------------
+typedef unsigned long long f32x2;
+
+__device__ __forceinline__ f32x2 pack2(float a, float b) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1,%2};" : "=l"(r) : "f"(a), "f"(b));
+  return r;
+}
+__device__ __forceinline__ void unpack2(f32x2 v, float& a, float& b) {
+  asm("mov.b64 {%0,%1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ f32x2 splat2(float a) { return pack2(a, a); }
+__device__ __forceinline__ f32x2 add2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 sub2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 mul2(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+// a*b+c with a single rounding per half: only where the evaluated graph has no separate
+// multiply and add to mirror (polynomial/compensation steps, sums of squares for statistics).
+__device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+
+// Natural exponential of a pair, for results that are rounded to a 16-bit type afterwards.
+// y = x*log2(e) is split into its rounded value yh and the exact rounding residual plus the
+// low part of the constant (el); 2^yh comes from the hardware approximation (relative error
+// 2^-22) and is corrected by the factor (1 + el*ln 2). Relative error below 3e-7 over the whole
+// fp32 range, i.e. the accuracy class of expf, and three orders of magnitude below half a
+// bf16/fp16 ulp.
+__device__ __forceinline__ f32x2 exp2_pair_compensated(f32x2 x) {
+  const f32x2 neg_l2e = splat2(-1.4426950216293335f);      // -fl(log2 e)
+  const f32x2 l2e = splat2(1.4426950216293335f);
+  const f32x2 l2e_lo = splat2(1.9259629911266175e-8f);     // log2 e - fl(log2 e)
+  const f32x2 ln2 = splat2(0.6931471824645996f);
+  const f32x2 nyh = mul2(x, neg_l2e);                      // -(x*L2E), rounded
+  f32x2 el = fma2(x, l2e, nyh);                            // exact residual of that product
+  el = fma2(x, l2e_lo, el);
+  float a, b;
+  unpack2(nyh, a, b);
+  float pa, pb;
+  // .ftz: results below 2^-126 become 0 instead of denormals; they are 38 orders of magnitude
+  // below anything a 16-bit output (or the row sum) can see, and the plain form costs two extra
+  // multiplies, a compare and a select per element for the denormal range.
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pa) : "f"(-a));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pb) : "f"(-b));
+  const f32x2 p = pack2(pa, pb);
+  return fma2(p, mul2(el, ln2), p);
 }
 
 template <bool BLOCK>
@@ -124,31 +236,77 @@ __device__ __forceinline__ float round_through(float v) {
   return Elem<T>::to_f32(Elem<T>::from_f32(v));
 }
 
-// Pick the launch geometry for a register-resident row: nv vectors per row.
-//   warp mode  : nv <= 128 -> 256-thread CTAs (8 rows each), CH = 1, 2 or 4 slots
-//   block mode : nv <= 4096 -> one CTA per row, CH = 2, 4 or 8 slots, 32..512 threads
-// Returns false when the row does not fit (the caller then uses the streaming kernel).
+// ----------------------------------------------------------------------------------------------
+// Register-resident rows: launch geometry and group helpers.
+// A row of nv 16-byte vectors is owned by a group of G threads with CH register slots each
+// (G * CH >= nv). Short rows use sub-warp groups of 8, 16 or 32 lanes with up to four slots, so
+// that a thread still handles ~32 elements and the per-row bookkeeping (index arithmetic, two
+// shuffle reductions, a reciprocal) is amortised; long rows use the whole CTA (G = 0).
+//   nv <= 32   : G = 8,  CH = 1, 2 or 4      (256-thread CTA = 32 rows)
+//   nv <= 64   : G = 16, CH = 4              (16 rows per CTA)
+//   nv <= 128  : G = 32, CH = 4              (8 rows per CTA)
+//   nv <= 4096 : G = 0 (CTA per row), CH = 2, 4 or 8, 96..512 threads
+// ----------------------------------------------------------------------------------------------
 struct RowGeometry {
-  bool block;
-  int ch;
-  int threads;
+  int g;        // lanes per row; 0 = the whole CTA
+  int ch;       // register slots per thread
+  int threads;  // CTA size
+  bool block;   // g == 0
 };
 
 inline bool pick_row_geometry(long long nv, RowGeometry* g) {
   if (nv <= 0) return false;
+  g->threads = 256;
+  g->block = false;
+  if (nv <= 32) {
+    g->g = 8;
+    g->ch = nv <= 8 ? 1 : (nv <= 16 ? 2 : 4);
+    return true;
+  }
+  if (nv <= 64) {
+    g->g = 16;
+    g->ch = 4;
+    return true;
+  }
   if (nv <= 128) {
-    g->block = false;
-    g->threads = 256;
-    g->ch = nv <= 32 ? 1 : (nv <= 64 ? 2 : 4);
+    g->g = 32;
+    g->ch = 4;
     return true;
   }
   if (nv > 4096) return false;
+  g->g = 0;
   g->block = true;
   g->ch = nv <= 512 ? 2 : (nv <= 2048 ? 4 : 8);
   long long t = (nv + g->ch - 1) / g->ch;
   t = (t + 31) / 32 * 32;
   g->threads = (int)t;
   return true;
+}
+
+template <int G>
+__device__ __forceinline__ int glane() {
+  return G == 0 ? (int)threadIdx.x : (int)(threadIdx.x & (G - 1));
+}
+template <int G>
+__device__ __forceinline__ int gsize() {
+  return G == 0 ? (int)blockDim.x : G;
+}
+template <int G>
+__device__ __forceinline__ long long grow() {
+  return G == 0 ? (long long)blockIdx.x
+                : (long long)blockIdx.x * (blockDim.x / (G == 0 ? 1 : G)) + threadIdx.x / (G == 0 ? 1 : G);
+}
+// Reduction over the group; every lane of the warp must call it (sub-warp groups reduce side by
+// side inside one shuffle).
+template <typename Op, int G>
+__device__ __forceinline__ float greduce(float v, float* scratch) {
+  if constexpr (G == 0) {
+    return block_reduce<Op>(v, scratch);
+  } else {
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) v = Op::apply(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+  }
 }
 
 }  // namespace b200

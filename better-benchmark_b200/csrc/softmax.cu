@@ -18,10 +18,13 @@
 //            representable takes exactly that longer route. The packed add rounds the exact sum
 //            once, where aten rounds the fp32 sum; the two differ only when the fp32 sum lands
 //            exactly on a 16-bit rounding tie, by one 16-bit ulp of a logit.
-// exp/log are the full-precision expf/logf. For 16-bit outputs e / s is evaluated as
-// e * (1 / s) with a correctly rounded reciprocal; the extra fp32 rounding is far below half a
-// 16-bit ulp. fp32 outputs use the IEEE division.
+// fp32 outputs: expf / logf and the IEEE division. 16-bit outputs: the natural exponential is
+// evaluated pairwise with a compensated base-2 split (same accuracy class as expf, see
+// exp2_pair_compensated) and e / s as e * (1 / s) with a correctly rounded reciprocal; both
+// deviations are three orders of magnitude below half a 16-bit ulp.
 #include "rowwise.cuh"
+
+#include <type_traits>
 
 namespace b200 {
 
@@ -76,73 +79,101 @@ struct Pair<float> {  // never instantiated for arithmetic; keeps the packed bra
   using type = float2;
 };
 
-// Final phases shared by both prologues: v holds the fp32 logits of this thread's slots.
-template <typename Tout, int CH, int V, bool BLOCK>
-__device__ __forceinline__ void softmax_finish(float (&v)[CH][V], float mx, Tout* y, int nv, int lane,
-                                               int G, bool log_mode, float* red) {
-  float s = 0.f;
-  if (log_mode) {
-#pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      if (c * G < nv) {  // group-uniform: skip slots no lane uses
-#pragma unroll
-        for (int i = 0; i < V; ++i) {
-          v[c][i] = v[c][i] - mx;
-          s += expf(v[c][i]);
-        }
-      }
+// Final phases shared by both prologues. v holds this thread's fp32 logits as packed pairs.
+// FASTEXP (16-bit outputs) uses the compensated pair exponential; fp32 outputs use expf.
+template <typename Tout, int CH, int V, int G, bool FASTEXP>
+__device__ __forceinline__ void softmax_finish(f32x2 (&v)[CH][V / 2], float mx, float mx_raw, Tout* y, int nv,
+                                               int lane, int gs, bool log_mode, bool valid, float* red) {
+  const f32x2 mx2 = splat2(mx);
+  f32x2 s2 = splat2(0.f);
+  auto exp_pair = [](f32x2 d) {
+    if constexpr (FASTEXP) {
+      return exp2_pair_compensated(d);
+    } else {
+      float a, b;
+      unpack2(d, a, b);
+      return pack2(expf(a), expf(b));
     }
-    s = group_reduce<SumOp, BLOCK>(s, red);
-    const float ls = logf(s);
+  };
+  if (log_mode) {  // keep x - max (it may be -inf); the exponentials only feed the sum
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
-      const int j = c * G + lane;
-      if (j < nv) {
+      if (c * gs < nv) {  // group-uniform: skip slots no lane uses
 #pragma unroll
-        for (int i = 0; i < V; ++i) v[c][i] = v[c][i] - ls;
-        store_converted<Tout, V>(y + (long long)j * V, v[c]);
+        for (int i = 0; i < V / 2; ++i) {
+          v[c][i] = sub2(v[c][i], mx2);
+          if constexpr (FASTEXP) {
+            float a, b;
+            unpack2(v[c][i], a, b);
+            a = a < -1e38f ? -1e38f : a;  // finite argument for the pair exponential, NaN kept
+            b = b < -1e38f ? -1e38f : b;
+            s2 = add2(s2, exp_pair(pack2(a, b)));
+          } else {
+            s2 = add2(s2, exp_pair(v[c][i]));
+          }
+        }
       }
     }
   } else {
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
-      if (c * G < nv) {
+      if (c * gs < nv) {
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-          v[c][i] = expf(v[c][i] - mx);
-          s += v[c][i];
+        for (int i = 0; i < V / 2; ++i) {
+          v[c][i] = exp_pair(sub2(v[c][i], mx2));
+          s2 = add2(s2, v[c][i]);
         }
       }
     }
-    s = group_reduce<SumOp, BLOCK>(s, red);
-    const float inv = __frcp_rn(s);
+  }
+  float sa, sb;
+  unpack2(s2, sa, sb);
+  float s = greduce<SumOp, G>(sa + sb, red);
+  if (mx_raw == -INFINITY) s = NAN;  // every logit -inf: aten's x - max is NaN for the whole row
+
+  f32x2 k2;  // second operand of the last step
+  if (log_mode) {
+    k2 = splat2(logf(s));
+  } else {
+    k2 = splat2(__frcp_rn(s));
+  }
 #pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      const int j = c * G + lane;
-      if (j < nv) {
+  for (int c = 0; c < CH; ++c) {
+    const int j = c * gs + lane;
+    if (j < nv && valid) {
+      float o[V];
 #pragma unroll
-        for (int i = 0; i < V; ++i) {
-          if constexpr (sizeof(Tout) == 4) {
-            v[c][i] = v[c][i] / s;
-          } else {
-            v[c][i] = v[c][i] * inv;
-          }
+      for (int i = 0; i < V / 2; ++i) {
+        f32x2 r;
+        if (log_mode) {
+          r = sub2(v[c][i], k2);
+          unpack2(r, o[2 * i], o[2 * i + 1]);
+        } else if constexpr (sizeof(Tout) == 4) {
+          float a, b;
+          unpack2(v[c][i], a, b);
+          o[2 * i] = a / s;
+          o[2 * i + 1] = b / s;
+        } else {
+          r = mul2(v[c][i], k2);
+          unpack2(r, o[2 * i], o[2 * i + 1]);
         }
-        store_converted<Tout, V>(y + (long long)j * V, v[c]);
       }
+      store_converted<Tout, V>(y + (long long)j * V, o);
     }
   }
 }
 
-template <typename Tin, typename Tout, int CH, bool BLOCK, bool PACKED>
-__global__ void __launch_bounds__(BLOCK ? 512 : 256)
+template <typename Tin, typename Tout, int CH, int G, bool PACKED>
+__global__ void __launch_bounds__(G == 0 ? 512 : 256)
 softmax_resident_kernel(const SoftmaxParams p) {
   constexpr int V = Elem<Tin>::V;
+  constexpr bool FASTEXP = sizeof(Tout) == 2;
   __shared__ float red[32];
-  const int lane = group_lane<BLOCK>();
-  const int G = group_size<BLOCK>();
-  const long long row = group_row<BLOCK>();
-  if (row >= p.rows) return;
+  const int lane = glane<G>();
+  const int gs = gsize<G>();
+  long long row = grow<G>();
+  const bool valid = row < p.rows;  // lanes of a partly filled last CTA compute on the last row
+  if (!valid) row = p.rows - 1;
 
   const Tin* x = reinterpret_cast<const Tin*>(p.x) + row_offset(p.xmap, row);
   const Tin* m = p.mask ? reinterpret_cast<const Tin*>(p.mask) + row_offset(p.mmap, row) : nullptr;
@@ -152,89 +183,126 @@ softmax_resident_kernel(const SoftmaxParams p) {
   uint4 raw[CH];
 #pragma unroll
   for (int c = 0; c < CH; ++c) {
-    const int j = c * G + lane;
+    const int j = c * gs + lane;
     if (j < nv) raw[c] = ld_stream(x + (long long)j * V);
   }
 
-  float v[CH][V];
+  f32x2 v[CH][V / 2];
   float mx = -INFINITY;
 
+  // The pair exponential needs finite arguments (inf - inf inside its compensation step would
+  // give NaN where exp(-inf) is 0): logits are clamped to a finite floor AFTER the row maximum was
+  // taken from the unclamped values. A row whose maximum is -inf (fully masked with -inf) makes
+  // aten return NaN for the whole row; the same happens here through the sum (see below).
+  constexpr float kFloor = sizeof(Tin) == 2 && !std::is_same<Tin, __nv_bfloat16>::value ? -60000.f : -1e38f;
+  // log_softmax returns x - max - log(sum) itself, which may legitimately be -inf: there only the
+  // exponential's argument is clamped (in softmax_finish), not the stored value.
+  const bool clamp_now = FASTEXP && !p.log_mode;
   if constexpr (PACKED && sizeof(Tin) == 2) {
     using P2 = typename Pair<Tin>::type;
     const P2 neg_inf = Pair<Tin>::splat(-INFINITY);
+    const P2 floor2 = Pair<Tin>::splat(kFloor);
     P2 mx2 = neg_inf;
-    P2 t[CH][4];
+    // One copy of the slot loop per combination of the (warp-uniform) prologue switches, so that
+    // they are tested once per row and not once per 16-byte slot.
+    //   SK: 0 no scale, 1 packed multiply (scale representable in Tin), 2 fp32 multiply + rounding
+    auto prologue = [&](auto sk_tag, auto hm_tag, auto clamp_tag) {
+      constexpr int SK = decltype(sk_tag)::value;
+      constexpr bool HM = decltype(hm_tag)::value;
+      constexpr bool CLAMP = decltype(clamp_tag)::value;
+      const P2 s2 = Pair<Tin>::splat(p.scale);
 #pragma unroll
-    for (int c = 0; c < CH; ++c) {
-      const int j = c * G + lane;
-      if (j < nv) {
-        const uint32_t w[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
+      for (int c = 0; c < CH; ++c) {
+        const int j = c * gs + lane;
+        P2 t[4];
+        if (j < nv) {
+          const uint32_t w[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
 #pragma unroll
-        for (int i = 0; i < 4; ++i) t[c][i] = *reinterpret_cast<const P2*>(&w[i]);
-        if (p.has_scale) {
-          if (p.scale_exact16) {
-            const P2 s2 = Pair<Tin>::splat(p.scale);
+          for (int i = 0; i < 4; ++i) t[i] = *reinterpret_cast<const P2*>(&w[i]);
+          if constexpr (SK == 1) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) t[c][i] = __hmul2(t[c][i], s2);
-          } else {
+            for (int i = 0; i < 4; ++i) t[i] = __hmul2(t[i], s2);
+          } else if constexpr (SK == 2) {
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
-              const float2 f = Pair<Tin>::widen(t[c][i]);
-              t[c][i] = Pair<Tin>::narrow(f.x * p.scale, f.y * p.scale);
+              const float2 f = Pair<Tin>::widen(t[i]);
+              t[i] = Pair<Tin>::narrow(f.x * p.scale, f.y * p.scale);
             }
           }
-        }
-        if (m != nullptr) {
-          const uint4 mr = ld_keep(m + (long long)j * V);
-          const uint32_t mw[4] = {mr.x, mr.y, mr.z, mr.w};
+          if constexpr (HM) {
+            const uint4 mr = ld_keep(m + (long long)j * V);
+            const uint32_t mw[4] = {mr.x, mr.y, mr.z, mr.w};
 #pragma unroll
-          for (int i = 0; i < 4; ++i) t[c][i] = __hadd2(t[c][i], *reinterpret_cast<const P2*>(&mw[i]));
+            for (int i = 0; i < 4; ++i) t[i] = __hadd2(t[i], *reinterpret_cast<const P2*>(&mw[i]));
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i) mx2 = __hmax2(mx2, t[i]);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) t[i] = neg_inf;
         }
 #pragma unroll
-        for (int i = 0; i < 4; ++i) mx2 = __hmax2(mx2, t[c][i]);
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = Pair<Tin>::widen(CLAMP ? __hmax2_nan(t[i], floor2) : t[i]);  // NaN stays NaN
+          v[c][i] = pack2(f.x, f.y);
+        }
+      }
+    };
+    using I0 = std::integral_constant<int, 0>;
+    using I1 = std::integral_constant<int, 1>;
+    using I2 = std::integral_constant<int, 2>;
+    auto with_mask_and_clamp = [&](auto sk_tag) {
+      if (m != nullptr) {
+        if (clamp_now) prologue(sk_tag, std::true_type{}, std::true_type{});
+        else prologue(sk_tag, std::true_type{}, std::false_type{});
       } else {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) t[c][i] = neg_inf;
+        if (clamp_now) prologue(sk_tag, std::false_type{}, std::true_type{});
+        else prologue(sk_tag, std::false_type{}, std::false_type{});
       }
-    }
+    };
+    if (!p.has_scale) with_mask_and_clamp(I0{});
+    else if (p.scale_exact16) with_mask_and_clamp(I1{});
+    else with_mask_and_clamp(I2{});
     const float2 mf = Pair<Tin>::widen(mx2);
-    mx = group_reduce<FastMax, BLOCK>(fmaxf(mf.x, mf.y), red);
-#pragma unroll
-    for (int c = 0; c < CH; ++c) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float2 f = Pair<Tin>::widen(t[c][i]);
-        v[c][2 * i] = f.x;
-        v[c][2 * i + 1] = f.y;
-      }
-    }
+    mx = greduce<FastMax, G>(fmaxf(mf.x, mf.y), red);
   } else {
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
-      const int j = c * G + lane;
+      const int j = c * gs + lane;
+      float f[V];
       if (j < nv) {
-        Elem<Tin>::unpack(raw[c], v[c]);
+        Elem<Tin>::unpack(raw[c], f);
         if (p.has_scale) {
 #pragma unroll
-          for (int i = 0; i < V; ++i) v[c][i] = v[c][i] * p.scale;
+          for (int i = 0; i < V; ++i) f[i] = f[i] * p.scale;
         }
         if (m != nullptr) {
           float mf[V];
           Elem<Tin>::unpack(ld_keep(m + (long long)j * V), mf);
 #pragma unroll
-          for (int i = 0; i < V; ++i) v[c][i] = v[c][i] + mf[i];
+          for (int i = 0; i < V; ++i) f[i] = f[i] + mf[i];
         }
 #pragma unroll
-        for (int i = 0; i < V; ++i) mx = fmaxf(mx, v[c][i]);
+        for (int i = 0; i < V; ++i) mx = fmaxf(mx, f[i]);
       } else {
 #pragma unroll
-        for (int i = 0; i < V; ++i) v[c][i] = -INFINITY;
+        for (int i = 0; i < V; ++i) f[i] = -INFINITY;
       }
+      if (clamp_now) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) f[i] = f[i] < kFloor ? kFloor : f[i];  // a NaN logit stays NaN
+      }
+#pragma unroll
+      for (int i = 0; i < V / 2; ++i) v[c][i] = pack2(f[2 * i], f[2 * i + 1]);
     }
-    mx = group_reduce<FastMax, BLOCK>(mx, red);
+    mx = greduce<FastMax, G>(mx, red);
   }
 
-  softmax_finish<Tout, CH, V, BLOCK>(v, mx, y, nv, lane, G, p.log_mode != 0, red);
+  // Subtract the maximum of the CLAMPED values (so every difference is <= 0 and finite); the
+  // unclamped maximum still decides whether the whole row was -inf.
+  const float mx_raw = mx;
+  if (clamp_now) mx = fmaxf(mx, kFloor);
+  softmax_finish<Tout, CH, V, G, FASTEXP>(v, mx, mx_raw, y, nv, lane, gs, p.log_mode != 0, valid, red);
 }
 
 // Element-wise kernel for rows that do not fit in registers or break the vector-path alignment
@@ -296,20 +364,24 @@ static int launch_softmax(const SoftmaxParams& p, bool vector_ok, cudaStream_t s
   if (p.rows > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "softmax: too many rows");
   if (vector_ok && p.n % V == 0 && pick_row_geometry(p.n / V, &g)) {
     if (!g.block) {
-      const int rows_per_cta = g.threads / 32;
+      const int rows_per_cta = g.threads / g.g;
       const unsigned grid = (unsigned)((p.rows + rows_per_cta - 1) / rows_per_cta);
-      switch (g.ch) {
-        case 1: softmax_resident_kernel<Tin, Tout, 1, false, PACKED><<<grid, g.threads, 0, st>>>(p); break;
-        case 2: softmax_resident_kernel<Tin, Tout, 2, false, PACKED><<<grid, g.threads, 0, st>>>(p); break;
-        default: softmax_resident_kernel<Tin, Tout, 4, false, PACKED><<<grid, g.threads, 0, st>>>(p); break;
+#define B200_SM_LAUNCH(GG, CC) softmax_resident_kernel<Tin, Tout, CC, GG, PACKED><<<grid, g.threads, 0, st>>>(p)
+      if (g.g == 8) {
+        if (g.ch == 1) B200_SM_LAUNCH(8, 1);
+        else if (g.ch == 2) B200_SM_LAUNCH(8, 2);
+        else B200_SM_LAUNCH(8, 4);
+      } else if (g.g == 16) {
+        B200_SM_LAUNCH(16, 4);
+      } else {
+        B200_SM_LAUNCH(32, 4);
       }
     } else {
       const unsigned grid = (unsigned)p.rows;
-      switch (g.ch) {
-        case 2: softmax_resident_kernel<Tin, Tout, 2, true, PACKED><<<grid, g.threads, 0, st>>>(p); break;
-        case 4: softmax_resident_kernel<Tin, Tout, 4, true, PACKED><<<grid, g.threads, 0, st>>>(p); break;
-        default: softmax_resident_kernel<Tin, Tout, 8, true, PACKED><<<grid, g.threads, 0, st>>>(p); break;
-      }
+      if (g.ch == 2) B200_SM_LAUNCH(0, 2);
+      else if (g.ch == 4) B200_SM_LAUNCH(0, 4);
+      else B200_SM_LAUNCH(0, 8);
+#undef B200_SM_LAUNCH
     }
   } else {
     int threads = 1024;
@@ -356,10 +428,10 @@ extern "C" int b200_softmax(const void* x, const void* mask, void* y, int64_t ro
 
   SoftmaxParams p;
   p.x = x; p.mask = mask; p.y = y; p.rows = rows; p.n = (int)n;
-  p.xmap = RowMap{x_strides[0], x_strides[1], x_strides[2], (int)d1, (int)d2};
-  p.ymap = RowMap{y_strides[0], y_strides[1], y_strides[2], (int)d1, (int)d2};
-  p.mmap = mask ? RowMap{mask_strides[0], mask_strides[1], mask_strides[2], (int)d1, (int)d2}
-                : RowMap{0, 0, 0, 1, 1};
+  if (rows > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "b200_softmax: more than 2^31-1 rows");
+  p.xmap = make_row_map(x_strides, d1, d2);
+  p.ymap = make_row_map(y_strides, d1, d2);
+  p.mmap = mask ? make_row_map(mask_strides, d1, d2) : make_row_map_flat(0);
   p.scale = (float)scale;
   p.has_scale = (flags & B200_SOFTMAX_SCALE) ? 1 : 0;
   p.scale_exact16 = survives_round_trip(p.scale, in_dtype) ? 1 : 0;

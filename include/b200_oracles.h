@@ -95,6 +95,14 @@ int32_t b200_norm_fwd(const void* x, const void* weight, const void* bias, void*
                       int64_t y_row_stride, int32_t x_dtype, int32_t w_dtype, int32_t y_dtype,
                       double eps, double correction, int32_t rms, void* stream);
 
+/* Number of bounded device-side waits of b200_norm_fwd's streaming kernel that ran out since the
+ * library was loaded: 0 in normal operation. Synchronises the device (diagnostic). No counterpart
+ * in the reference. */
+int64_t b200_norm_fwd_wait_timeouts(void);
+
+/* Same counter for b200_norm_bwd's streaming kernel. */
+int64_t b200_norm_bwd_wait_timeouts(void);
+
 /* Scratch bytes that let b200_norm_bwd run its largest grid for rows of n elements. */
 int64_t b200_norm_bwd_scratch_bytes(int64_t n);
 
@@ -112,6 +120,9 @@ int32_t b200_norm_bwd(const void* x, const void* dy, const void* weight, const f
                       int32_t w_dtype, int32_t rms, int64_t seq, int64_t head_dim,
                       int64_t dx_batch_stride, int64_t dx_seq_stride, int64_t dx_head_stride,
                       void* scratch, int64_t scratch_bytes, int32_t flags, void* stream);
+
+/* Same counter for b200_batch_norm_fwd's fused kernel. */
+int64_t b200_batch_norm_wait_timeouts(void);
 
 /* Scratch bytes b200_batch_norm_fwd needs for `channels` channels. */
 int64_t b200_batch_norm_scratch_bytes(int64_t channels);
