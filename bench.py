@@ -10,8 +10,8 @@ step finds its input there. The metric is achieved HBM bandwidth: the region's m
 (every input once plus every output once) divided by the time per step. One JSON line is printed
 by rank 0.
 
-  value      K timed steps between CUDA events on the launching stream, barrier + synchronize on
-             both sides; with N > 1 every rank runs the same configuration on its own GPU
+  value      K timed steps (captured into one CUDA graph, replayed once) between CUDA events on the
+             launching stream, barrier + synchronize on both sides; with N > 1 every rank runs the same configuration on its own GPU
              (independent replicas, no collective in the data path) and the time is the maximum
              over ranks, so value is the aggregate over the N GPUs.
   roofline   the dominant (here: only) kernel of the step against the measured HBM peak.
@@ -191,7 +191,13 @@ def build_input_sets(workload, device, min_total_bytes):
 
 
 def time_steps(workload, input_sets, steps, warmup, barrier):
-    """(milliseconds for `steps` steps, kernels launched inside the timed region)."""
+    """(milliseconds for `steps` steps, kernels launched inside the timed region).
+
+    The K steps are captured into one CUDA graph (step i uses input set i mod n) and the timed
+    region is one replay of that graph between two events: the kernels are 20-100 us long, and a
+    Python loop cannot issue them fast enough to keep the GPU busy. The launch count is what the
+    library launched while the graph was being captured, i.e. per replay.
+    """
     import torch
     from better_benchmark_b200 import native
     lib = native.load()
@@ -199,15 +205,21 @@ def time_steps(workload, input_sets, steps, warmup, barrier):
     for i in range(warmup):
         workload.oracle_forward(input_sets[i % n])
     torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    launches0 = lib.b200_launch_count()
+    with torch.cuda.graph(graph):
+        for i in range(steps):
+            workload.oracle_forward(input_sets[i % n])
+    launches = lib.b200_launch_count() - launches0
+    torch.cuda.synchronize()
+    graph.replay()  # untimed: instantiates everything the first replay touches
+    torch.cuda.synchronize()
     barrier()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    launches0 = lib.b200_launch_count()
     start.record()
-    for i in range(steps):
-        workload.oracle_forward(input_sets[i % n])
+    graph.replay()
     end.record()
     torch.cuda.synchronize()
-    launches = lib.b200_launch_count() - launches0
     barrier()
     return start.elapsed_time(end), int(launches)
 
@@ -286,11 +298,16 @@ def gpu_arm(args, workload):
         total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
     # keep the GPU under the same load a little longer so that the clock sampler sees it
+    load_graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(load_graph):
+        for i in range(len(sets)):
+            workload.oracle_forward(sets[i])
     t_end = time.time() + 1.0
     while time.time() < t_end:
-        for i in range(50):
-            workload.oracle_forward(sets[i % len(sets)])
+        for _ in range(20):
+            load_graph.replay()
         torch.cuda.synchronize()
+    del load_graph
     clocks = sampler.stop() if rank == 0 else None
     gbps_one = workload.algorithmic_bytes / (ms_per_step * 1e-3) / 1e9
     value = gbps_one * world
