@@ -1,0 +1,185 @@
+// Column reductions: x viewed as [batch, rows, cols] with cols contiguous, reduced over rows.
+//
+// Replaces the column-form Triton kernels of the sum/mean repros in the reference:
+// repros/canonical/sum_eb86a17deab9/oracle.py:20-70 (atomic partial sums, grid (R/256, H/32)),
+// sum_c2bf513c1ebf/oracle.py:10-29 (whole column in one tile) and the channels-last spatial mean
+// of mean_c9e1a8113328/oracle.py:11-76 ([N, H*W, C] -> [N, C]).
+//
+// A thread owns one 16-byte vector column; the CTA's thread rows and, for tall inputs, several
+// CTAs split the rows. Partial results of different CTAs go to scratch as fp32 and are combined in
+// fp64 in a fixed order by a second launch: no float atomics, bit-reproducible (the reference's
+// atomic variant is not, and its harness would classify such an output as stochastic).
+#include "rowwise.cuh"
+
+namespace b200 {
+
+#define B200_COL_SUM 0
+#define B200_COL_MEAN 1
+#define B200_COL_AMAX 2
+
+struct ColReduceParams {
+  const void* x;
+  void* out;
+  float* partials;  // [splits][batch][cols]
+  long long batch, rows, cols;
+  long long x_batch_stride, x_row_stride;  // elements
+  long long out_batch_stride;
+  int out_dtype;
+  int op;
+  int splits;
+  long long rows_per_split;
+  float post_scale;
+};
+
+__device__ __forceinline__ void store_out(void* out, int dtype, long long idx, float v) {
+  if (dtype == B200_F32) reinterpret_cast<float*>(out)[idx] = v;
+  else if (dtype == B200_BF16) reinterpret_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(v);
+  else reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
+}
+
+// blockDim = (32 vector columns, 8 thread rows); grid = (column chunks, splits, batch)
+template <typename T, bool IS_MAX, bool VEC>
+__global__ void __launch_bounds__(256) col_reduce_kernel(const ColReduceParams p) {
+  constexpr int V = VEC ? Elem<T>::V : 1;
+  constexpr int U = 4;
+  __shared__ float red[8][32 * (VEC ? Elem<T>::V : 1) + 1];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const long long col0 = ((long long)blockIdx.x * 32 + tx) * V;
+  const long long b = blockIdx.z;
+  const long long r_begin = (long long)blockIdx.y * p.rows_per_split;
+  long long r_end = r_begin + p.rows_per_split;
+  if (r_end > p.rows) r_end = p.rows;
+  const bool active = col0 < p.cols;
+  const T* base = reinterpret_cast<const T*>(p.x) + b * p.x_batch_stride + col0;
+
+  float acc[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) acc[i] = IS_MAX ? -INFINITY : 0.f;
+  if (active) {
+    for (long long r0 = r_begin + ty; r0 < r_end; r0 += 8 * U) {
+      if constexpr (VEC) {
+        uint4 raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long r = r0 + 8 * u;
+          if (r < r_end) raw[u] = ld_stream(base + r * p.x_row_stride);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long r = r0 + 8 * u;
+          if (r < r_end) {
+            float f[V];
+            Elem<T>::unpack(raw[u], f);
+#pragma unroll
+            for (int i = 0; i < V; ++i) acc[i] = IS_MAX ? MaxOp::apply(acc[i], f[i]) : acc[i] + f[i];
+          }
+        }
+      } else {
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          const long long r = r0 + 8 * u;
+          if (r < r_end) {
+            const float f = Elem<T>::to_f32(base[r * p.x_row_stride]);
+            acc[0] = IS_MAX ? MaxOp::apply(acc[0], f) : acc[0] + f;
+          }
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < V; ++i) red[ty][tx * V + i] = acc[i];
+  __syncthreads();
+  // thread rows are folded by the first V*32 threads, one column each
+  for (int c = threadIdx.x; c < 32 * V; c += 256) {
+    const long long col = (long long)blockIdx.x * 32 * V + c;
+    if (col >= p.cols) continue;
+    float r = red[0][c];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) r = IS_MAX ? MaxOp::apply(r, red[k][c]) : r + red[k][c];
+    if (p.splits == 1) {
+      store_out(p.out, p.out_dtype, b * p.out_batch_stride + col, r * p.post_scale);
+    } else {
+      p.partials[((long long)blockIdx.y * p.batch + b) * p.cols + col] = r;
+    }
+  }
+}
+
+template <bool IS_MAX>
+__global__ void __launch_bounds__(256) col_reduce_finalize_kernel(const ColReduceParams p) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over batch * cols
+  if (idx >= p.batch * p.cols) return;
+  const long long b = idx / p.cols, col = idx - b * p.cols;
+  if (IS_MAX) {
+    float r = -INFINITY;
+    for (int s = 0; s < p.splits; ++s) r = MaxOp::apply(r, p.partials[(long long)s * p.batch * p.cols + idx]);
+    store_out(p.out, p.out_dtype, b * p.out_batch_stride + col, r);
+  } else {
+    double r = 0.0;
+    for (int s = 0; s < p.splits; ++s) r += (double)p.partials[(long long)s * p.batch * p.cols + idx];
+    store_out(p.out, p.out_dtype, b * p.out_batch_stride + col, (float)r * p.post_scale);
+  }
+}
+
+template <typename T>
+static int launch_col_reduce(ColReduceParams p, bool vec, size_t scratch_bytes, cudaStream_t st) {
+  const int sms = device_info().sm_count;
+  const int v = vec ? Elem<T>::V : 1;
+  const long long chunks = (p.cols + 32 * v - 1) / (32 * v);
+  if (chunks > 0x7fffffffLL || p.batch > 65535) return fail(B200_ERR_UNSUPPORTED, "b200_col_reduce: grid too large");
+  // enough CTAs to fill the machine about four times over, at least 64 rows each
+  long long splits = (4LL * sms + chunks * p.batch - 1) / (chunks * p.batch);
+  if (splits > (p.rows + 63) / 64) splits = (p.rows + 63) / 64;
+  const long long cap = scratch_bytes / ((size_t)p.batch * p.cols * sizeof(float) + 1);
+  if (splits > cap) splits = cap;
+  if (splits > 65535) splits = 65535;
+  if (splits < 1) splits = 1;
+  p.splits = (int)splits;
+  p.rows_per_split = (p.rows + splits - 1) / splits;
+  const bool is_max = p.op == B200_COL_AMAX;
+  dim3 grid((unsigned)chunks, (unsigned)splits, (unsigned)p.batch);
+  if (is_max) {
+    if (vec) col_reduce_kernel<T, true, true><<<grid, 256, 0, st>>>(p);
+    else col_reduce_kernel<T, true, false><<<grid, 256, 0, st>>>(p);
+  } else {
+    if (vec) col_reduce_kernel<T, false, true><<<grid, 256, 0, st>>>(p);
+    else col_reduce_kernel<T, false, false><<<grid, 256, 0, st>>>(p);
+  }
+  int rc = launch_status("b200_col_reduce");
+  if (rc != B200_OK || splits == 1) return rc;
+  const long long total = p.batch * p.cols;
+  if (is_max) col_reduce_finalize_kernel<true><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p);
+  else col_reduce_finalize_kernel<false><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p);
+  return launch_status("b200_col_reduce finalize");
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_col_reduce(const void* x, void* out, int64_t batch, int64_t rows, int64_t cols,
+                               int64_t x_batch_stride, int64_t x_row_stride, int64_t out_batch_stride,
+                               int32_t x_dtype, int32_t out_dtype, int32_t op, void* scratch,
+                               int64_t scratch_bytes, void* stream) {
+  if (!x || !out) return fail(B200_ERR_INVALID, "b200_col_reduce: null argument");
+  if (batch < 0 || rows < 0 || cols < 0) return fail(B200_ERR_INVALID, "b200_col_reduce: negative size");
+  if (op < 0 || op > 2) return fail(B200_ERR_INVALID, "b200_col_reduce: unknown op %d", op);
+  if (batch == 0 || cols == 0) return B200_OK;
+  if (rows == 0 && op == B200_COL_AMAX) return fail(B200_ERR_INVALID, "b200_col_reduce: amax over zero rows");
+  ColReduceParams p;
+  p.x = x; p.out = out; p.partials = reinterpret_cast<float*>(scratch);
+  p.batch = batch; p.rows = rows; p.cols = cols;
+  p.x_batch_stride = x_batch_stride; p.x_row_stride = x_row_stride; p.out_batch_stride = out_batch_stride;
+  p.out_dtype = out_dtype; p.op = op; p.splits = 1; p.rows_per_split = rows;
+  p.post_scale = op == B200_COL_MEAN ? 1.0f / (float)rows : 1.0f;
+  const int eb = dtype_size(x_dtype);
+  const bool vec = aligned16(x) && (x_batch_stride * eb) % 16 == 0 && (x_row_stride * eb) % 16 == 0 &&
+                   cols % (16 / eb) == 0;
+  const size_t sb = scratch ? (size_t)scratch_bytes : 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  switch (x_dtype) {
+    case B200_F32: return launch_col_reduce<float>(p, vec, sb, st);
+    case B200_BF16: return launch_col_reduce<__nv_bfloat16>(p, vec, sb, st);
+    case B200_F16: return launch_col_reduce<__half>(p, vec, sb, st);
+  }
+  return fail(B200_ERR_INVALID, "b200_col_reduce: unknown dtype %d", x_dtype);
+}

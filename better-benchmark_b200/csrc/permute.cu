@@ -1,0 +1,260 @@
+// Layout-changing copies with a pointwise epilogue (optional scale, dtype conversion):
+//   * general: up to four dimensions with arbitrary input strides into a contiguous output
+//     (head split [B,S,H,D] -> [B,H,S,D], any permute + clone);
+//   * transpose of the two innermost dimensions through a padded shared-memory tile, coalesced
+//     row accesses on both sides;
+//   * contiguous cast / scale (no layout change).
+//
+// Replaces the permuting pointwise Triton kernels of the reference:
+// repros/canonical/pointwise_c0d19d490a2f/oracle.py:10-33 (head-split gather copy),
+// pointwise_021e90d9c17d/oracle.py:10-51 (autotuned 2-D tile transpose),
+// pointwise_8bb40810003c/oracle.py:11-15 and pointwise_95ed2ef35da9/oracle.py:10-44 (cast / scale).
+//
+// Pointwise semantics follow aten: the value is converted to fp32, multiplied by the scale (when
+// given) and rounded once to the output dtype.
+#include "rowwise.cuh"
+
+namespace b200 {
+
+struct PermuteParams {
+  const void* x;
+  void* y;
+  long long shape[4];      // OUTPUT shape, outermost first (unused leading dims are 1)
+  long long in_stride[4];  // input stride of each OUTPUT dimension, in elements
+  FastDiv d1, d2, d3;      // fast division by shape[1], shape[2], shape[3] (in units of the inner vector)
+  long long total;         // output elements
+  float scale;
+  int has_scale;
+};
+
+template <typename Tin, typename Tout>
+__device__ __forceinline__ Tout convert_scaled(Tin v, float scale, int has_scale) {
+  float f = Elem<Tin>::to_f32(v);
+  if (has_scale) f = f * scale;
+  return Elem<Tout>::from_f32(f);
+}
+
+// General kernel. VEC: the innermost output dimension is also unit-stride in the input and both
+// sides are 16-byte friendly, so a thread moves VIN = 16 / sizeof(Tin) elements at once.
+template <typename Tin, typename Tout, bool VEC>
+__global__ void __launch_bounds__(256) permute_general_kernel(const PermuteParams p) {
+  constexpr int VIN = VEC ? Elem<Tin>::V : 1;
+  const long long units = p.total / VIN;
+  for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < units;
+       u += (long long)gridDim.x * blockDim.x) {
+    // decompose the unit index over (shape[0], shape[1], shape[2], shape[3] / VIN)
+    long long rest = u;
+    long long i3, i2, i1, i0;
+    if (rest < 0x7fffffffLL) {
+      unsigned int r = (unsigned int)rest;
+      unsigned int q = fast_div(r, p.d3);
+      i3 = r - q * p.d3.d; r = q;
+      q = fast_div(r, p.d2);
+      i2 = r - q * p.d2.d; r = q;
+      q = fast_div(r, p.d1);
+      i1 = r - q * p.d1.d;
+      i0 = q;
+    } else {
+      const long long n3 = p.d3.d, n2 = p.d2.d, n1 = p.d1.d;
+      i3 = rest % n3; rest /= n3;
+      i2 = rest % n2; rest /= n2;
+      i1 = rest % n1;
+      i0 = rest / n1;
+    }
+    const long long in_off = i0 * p.in_stride[0] + i1 * p.in_stride[1] + i2 * p.in_stride[2] +
+                             i3 * VIN * p.in_stride[3];
+    const Tin* src = reinterpret_cast<const Tin*>(p.x) + in_off;
+    Tout* dst = reinterpret_cast<Tout*>(p.y) + u * VIN;
+    if constexpr (VEC) {
+      float f[VIN];
+      Elem<Tin>::unpack(ld_stream(src), f);
+      if (p.has_scale) {
+#pragma unroll
+        for (int i = 0; i < VIN; ++i) f[i] = f[i] * p.scale;
+      }
+      store_converted<Tout, VIN>(dst, f);
+    } else {
+      *dst = convert_scaled<Tin, Tout>(*src, p.scale, p.has_scale);
+    }
+  }
+}
+
+// Transpose of the two innermost dimensions: output [batch, C, P] from input [batch, P, C]
+// (input row stride in_row_stride, batch stride in_batch_stride). 64 x 64 element tiles; a warp
+// reads and writes whole tile rows (64 consecutive elements), the transposition happens in shared
+// memory (row pitch padded by one 4-byte word to spread the column reads over the banks).
+struct TransposeParams {
+  const void* x;
+  void* y;
+  long long batch, P, C;
+  long long in_batch_stride, in_row_stride;
+  float scale;
+  int has_scale;
+};
+
+template <typename Tin, typename Tout>
+__global__ void __launch_bounds__(256) transpose_tile_kernel(const TransposeParams p) {
+  constexpr int TILE = 64;
+  __shared__ float tile[TILE][TILE + 1];
+  const long long b = blockIdx.z;
+  const long long p0 = (long long)blockIdx.y * TILE, c0 = (long long)blockIdx.x * TILE;
+  const Tin* src = reinterpret_cast<const Tin*>(p.x) + b * p.in_batch_stride;
+  Tout* dst = reinterpret_cast<Tout*>(p.y) + b * p.P * p.C;
+  // load: thread (ty, tx) walks rows of the input tile, columns contiguous
+  for (int r = threadIdx.x / TILE; r < TILE; r += 256 / TILE) {
+    const int c = threadIdx.x % TILE;
+    const long long pr = p0 + r, pc = c0 + c;
+    float v = 0.f;
+    if (pr < p.P && pc < p.C) {
+      v = Elem<Tin>::to_f32(src[pr * p.in_row_stride + pc]);
+      if (p.has_scale) v = v * p.scale;
+    }
+    tile[r][c] = v;
+  }
+  __syncthreads();
+  // store: rows of the output tile are columns of the input tile
+  for (int r = threadIdx.x / TILE; r < TILE; r += 256 / TILE) {
+    const int c = threadIdx.x % TILE;
+    const long long oc = c0 + r, op = p0 + c;  // output row index = input column
+    if (oc < p.C && op < p.P) dst[oc * p.P + op] = Elem<Tout>::from_f32(tile[c][r]);
+  }
+}
+
+// Contiguous cast / scale.
+template <typename Tin, typename Tout, bool VEC>
+__global__ void __launch_bounds__(256) cast_scale_kernel(const void* x, void* y, long long n, float scale,
+                                                         int has_scale) {
+  constexpr int VIN = VEC ? Elem<Tin>::V : 1;
+  const long long units = n / VIN;
+  const Tin* src = reinterpret_cast<const Tin*>(x);
+  Tout* dst = reinterpret_cast<Tout*>(y);
+  for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < units;
+       u += (long long)gridDim.x * blockDim.x) {
+    if constexpr (VEC) {
+      float f[VIN];
+      Elem<Tin>::unpack(ld_stream(src + u * VIN), f);
+      if (has_scale) {
+#pragma unroll
+        for (int i = 0; i < VIN; ++i) f[i] = f[i] * scale;
+      }
+      store_converted<Tout, VIN>(dst + u * VIN, f);
+    } else {
+      dst[u] = convert_scaled<Tin, Tout>(src[u], scale, has_scale);
+    }
+  }
+  if constexpr (VEC) {  // ragged tail
+    const long long done = units * VIN;
+    const long long t = done + (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t < n) dst[t] = convert_scaled<Tin, Tout>(src[t], scale, has_scale);
+  }
+}
+
+static unsigned streaming_grid(long long units) {
+  const long long ctas = (units + 255) / 256;
+  const long long cap = (long long)device_info().sm_count * 16;
+  return (unsigned)(ctas < 1 ? 1 : (ctas > cap ? cap : ctas));
+}
+
+template <typename Tin, typename Tout>
+static int launch_permute(const PermuteParams& p, bool vec, cudaStream_t st) {
+  const long long units = vec ? p.total / Elem<Tin>::V : p.total;
+  if (vec) permute_general_kernel<Tin, Tout, true><<<streaming_grid(units), 256, 0, st>>>(p);
+  else permute_general_kernel<Tin, Tout, false><<<streaming_grid(units), 256, 0, st>>>(p);
+  return launch_status("b200_permute_copy");
+}
+
+template <typename Tin, typename Tout>
+static int launch_transpose(const TransposeParams& p, cudaStream_t st) {
+  dim3 grid((unsigned)((p.C + 63) / 64), (unsigned)((p.P + 63) / 64), (unsigned)p.batch);
+  transpose_tile_kernel<Tin, Tout><<<grid, 256, 0, st>>>(p);
+  return launch_status("b200_transpose_copy");
+}
+
+template <typename Tin, typename Tout>
+static int launch_cast(const void* x, void* y, long long n, float scale, int has_scale, bool vec, cudaStream_t st) {
+  const long long units = vec ? n / Elem<Tin>::V : n;
+  if (vec) cast_scale_kernel<Tin, Tout, true><<<streaming_grid(units > 0 ? units : 1), 256, 0, st>>>(x, y, n, scale, has_scale);
+  else cast_scale_kernel<Tin, Tout, false><<<streaming_grid(units > 0 ? units : 1), 256, 0, st>>>(x, y, n, scale, has_scale);
+  return launch_status("b200_cast_scale");
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+#define B200_DTYPE_PAIRS(MACRO)                                  \
+  MACRO(float, float, B200_F32, B200_F32)                        \
+  MACRO(__nv_bfloat16, __nv_bfloat16, B200_BF16, B200_BF16)      \
+  MACRO(__half, __half, B200_F16, B200_F16)                      \
+  MACRO(__nv_bfloat16, float, B200_BF16, B200_F32)               \
+  MACRO(__half, float, B200_F16, B200_F32)                       \
+  MACRO(float, __nv_bfloat16, B200_F32, B200_BF16)               \
+  MACRO(float, __half, B200_F32, B200_F16)
+
+extern "C" int b200_permute_copy(const void* x, void* y, const int64_t* out_shape, const int64_t* in_strides,
+                                 int32_t in_dtype, int32_t out_dtype, double scale, int32_t has_scale,
+                                 void* stream) {
+  if (!x || !y || !out_shape || !in_strides) return fail(B200_ERR_INVALID, "b200_permute_copy: null argument");
+  PermuteParams p;
+  p.x = x; p.y = y; p.total = 1;
+  for (int i = 0; i < 4; ++i) {
+    if (out_shape[i] < 0) return fail(B200_ERR_INVALID, "b200_permute_copy: negative extent");
+    p.shape[i] = out_shape[i];
+    p.in_stride[i] = in_strides[i];
+    p.total *= out_shape[i];
+  }
+  if (p.total == 0) return B200_OK;
+  for (int i = 1; i < 4; ++i)
+    if (out_shape[i] > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "b200_permute_copy: extent beyond 2^31-1");
+  p.scale = (float)scale; p.has_scale = has_scale ? 1 : 0;
+  const int ib = dtype_size(in_dtype), ob = dtype_size(out_dtype);
+  const int vin = 16 / ib;
+  const int out_chunk = vin * ob < 16 ? vin * ob : 16;
+  bool vec = in_strides[3] == 1 && out_shape[3] % vin == 0 && aligned16(x) &&
+             reinterpret_cast<uintptr_t>(y) % out_chunk == 0;
+  for (int i = 0; i < 3; ++i) vec = vec && (in_strides[i] * ib) % 16 == 0;
+  p.d1 = make_fast_div(out_shape[1]);
+  p.d2 = make_fast_div(out_shape[2]);
+  p.d3 = make_fast_div(vec ? out_shape[3] / vin : out_shape[3]);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define B200_CASE(TI, TO, DI, DO) if (in_dtype == DI && out_dtype == DO) return launch_permute<TI, TO>(p, vec, st);
+  B200_DTYPE_PAIRS(B200_CASE)
+#undef B200_CASE
+  return fail(B200_ERR_UNSUPPORTED, "b200_permute_copy: dtype pair (%d -> %d) not built", in_dtype, out_dtype);
+}
+
+extern "C" int b200_transpose_copy(const void* x, void* y, int64_t batch, int64_t rows, int64_t cols,
+                                   int64_t in_batch_stride, int64_t in_row_stride, int32_t in_dtype,
+                                   int32_t out_dtype, double scale, int32_t has_scale, void* stream) {
+  if (!x || !y) return fail(B200_ERR_INVALID, "b200_transpose_copy: null argument");
+  if (batch < 0 || rows < 0 || cols < 0) return fail(B200_ERR_INVALID, "b200_transpose_copy: negative size");
+  if (batch == 0 || rows == 0 || cols == 0) return B200_OK;
+  if (batch > 65535 || (rows + 63) / 64 > 65535)
+    return fail(B200_ERR_UNSUPPORTED, "b200_transpose_copy: grid too large (fold batch dimensions)");
+  TransposeParams p;
+  p.x = x; p.y = y; p.batch = batch; p.P = rows; p.C = cols;
+  p.in_batch_stride = in_batch_stride; p.in_row_stride = in_row_stride;
+  p.scale = (float)scale; p.has_scale = has_scale ? 1 : 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define B200_CASE(TI, TO, DI, DO) if (in_dtype == DI && out_dtype == DO) return launch_transpose<TI, TO>(p, st);
+  B200_DTYPE_PAIRS(B200_CASE)
+#undef B200_CASE
+  return fail(B200_ERR_UNSUPPORTED, "b200_transpose_copy: dtype pair (%d -> %d) not built", in_dtype, out_dtype);
+}
+
+extern "C" int b200_cast_scale(const void* x, void* y, int64_t n, int32_t in_dtype, int32_t out_dtype,
+                               double scale, int32_t has_scale, void* stream) {
+  if (n < 0) return fail(B200_ERR_INVALID, "b200_cast_scale: negative size");
+  if (n == 0) return B200_OK;
+  if (!x || !y) return fail(B200_ERR_INVALID, "b200_cast_scale: null argument");
+  const int ib = dtype_size(in_dtype), ob = dtype_size(out_dtype);
+  const int vin = 16 / ib;
+  const int out_chunk = vin * ob < 16 ? vin * ob : 16;
+  const bool vec = aligned16(x) && reinterpret_cast<uintptr_t>(y) % out_chunk == 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+#define B200_CASE(TI, TO, DI, DO) \
+  if (in_dtype == DI && out_dtype == DO) return launch_cast<TI, TO>(x, y, n, (float)scale, has_scale ? 1 : 0, vec, st);
+  B200_DTYPE_PAIRS(B200_CASE)
+#undef B200_CASE
+  return fail(B200_ERR_UNSUPPORTED, "b200_cast_scale: dtype pair (%d -> %d) not built", in_dtype, out_dtype);
+}

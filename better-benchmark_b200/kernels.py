@@ -379,3 +379,115 @@ def batch_norm_fwd(x: torch.Tensor, weight: torch.Tensor | None, bias: torch.Ten
                                   _ptr(scratch), scratch.numel() * scratch.element_size(), _stream()),
           "b200_batch_norm_fwd")
     return y, mean, invstd
+
+
+COL_SUM, COL_MEAN, COL_AMAX = 0, 1, 2
+_COL_CODES = {"sum": COL_SUM, "mean": COL_MEAN, "amax": COL_AMAX}
+
+
+def col_reduce(x: torch.Tensor, op: str, *, out_dtype: torch.dtype | None = None,
+               scratch: torch.Tensor | None = None) -> torch.Tensor:
+    """Reduce ``x`` [batch, rows, cols] (or [rows, cols]) over rows; cols must be contiguous.
+
+    Returns [batch, cols] (or [cols]). A channels-last spatial mean is
+    ``col_reduce(x.permute(0, 2, 3, 1).reshape(N, H*W, C), "mean")`` on views, without copies.
+    """
+    _require_cuda(x, scratch)
+    squeeze = x.dim() == 2
+    if squeeze:
+        x = x.unsqueeze(0)
+    if x.dim() != 3:
+        raise UnsupportedLayout("col_reduce: expected [batch, rows, cols] or [rows, cols]")
+    b, r, c = x.shape
+    if c > 1 and x.stride(2) != 1:
+        raise UnsupportedLayout("col_reduce: the kept dimension must be contiguous")
+    out_dtype = out_dtype or x.dtype
+    out = torch.empty((b, c), dtype=out_dtype, device=x.device)
+    if out.numel() == 0:
+        return out[0] if squeeze else out
+    if r == 0:
+        if op == "amax":
+            raise native.KernelArgumentError("col_reduce: amax over zero rows is undefined")
+        out.fill_(0.0 if op == "sum" else float("nan"))
+        return out[0] if squeeze else out
+    if scratch is None:
+        scratch = scratch_buffer(x.device, 1 << 20)
+    # the barrier words at the head of the shared scratch buffer stay untouched
+    usable = scratch[256:]
+    lib = load()
+    check(lib.b200_col_reduce(_ptr(x), _ptr(out), b, r, c, x.stride(0) if b > 1 else r * x.stride(1),
+                              x.stride(1) if r > 1 else c, c, _code(x), _DTYPE_CODE[out_dtype],
+                              _COL_CODES[op], _ptr(usable), usable.numel(), _stream()),
+          "b200_col_reduce")
+    return out[0] if squeeze else out
+
+
+def permute_copy(x: torch.Tensor, dims, *, scale: float | None = None,
+                 out_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``x.permute(dims)`` materialised contiguously, with an optional scale and dtype conversion.
+
+    Up to four dimensions after adjacent dimensions that stay adjacent have been merged. A swap of
+    the two innermost dimensions goes through the shared-memory transpose kernel.
+    """
+    _require_cuda(x)
+    out_dtype = out_dtype or x.dtype
+    view = x.permute(*dims)
+    out = torch.empty(view.shape, dtype=out_dtype, device=x.device)
+    if out.numel() == 0:
+        return out
+    shape, (strides,) = _collapse_all(tuple(view.shape), [tuple(view.stride())])
+    lib = load()
+    has_scale = 1 if scale is not None else 0
+    sc = float(scale) if scale is not None else 1.0
+    # [..., P, C] -> [..., C, P]: innermost output dim strided, the one before it unit-stride
+    if len(shape) >= 2 and strides[-2] == 1 and strides[-1] != 1 and len(shape) <= 3:
+        batch = shape[0] if len(shape) == 3 else 1
+        bstride = strides[0] if len(shape) == 3 else 0
+        cols, rows = shape[-2], shape[-1]          # output [batch, cols, rows], input [batch, rows, cols]
+        check(lib.b200_transpose_copy(_ptr(x), _ptr(out), batch, rows, cols, bstride, strides[-1],
+                                      _code(x), _DTYPE_CODE[out_dtype], sc, has_scale, _stream()),
+              "b200_transpose_copy")
+        return out
+    if len(shape) > 4:
+        raise UnsupportedLayout(f"permute_copy: {len(shape)} dimensions remain after merging (max 4)")
+    pad = 4 - len(shape)
+    shape4 = [1] * pad + list(shape)
+    strides4 = [0] * pad + list(strides)
+    check(lib.b200_permute_copy(_ptr(x), _ptr(out), i64_array(shape4), i64_array(strides4), _code(x),
+                                _DTYPE_CODE[out_dtype], sc, has_scale, _stream()),
+          "b200_permute_copy")
+    return out
+
+
+def _collapse_all(shape, strides_list):
+    """collapse_outer over ALL dimensions (no reserved last dimension, no limit of three)."""
+    dims, strs = [], [[] for _ in strides_list]
+    for i, size in enumerate(shape):
+        if size == 1:
+            continue
+        cur = [s[i] for s in strides_list]
+        if dims and all(strs[k][-1] == cur[k] * size for k in range(len(cur))):
+            dims[-1] *= size
+            for k in range(len(cur)):
+                strs[k][-1] = cur[k]
+        else:
+            dims.append(size)
+            for k in range(len(cur)):
+                strs[k].append(cur[k])
+    if not dims:
+        dims, strs = [1], [[1] for _ in strides_list]
+    return dims, strs
+
+
+def cast_scale(x: torch.Tensor, out_dtype: torch.dtype, *, scale: float | None = None) -> torch.Tensor:
+    """Element-wise ``(x * scale).to(out_dtype)`` for a dense tensor; the result keeps x's strides."""
+    _require_cuda(x)
+    if not _is_dense(x):
+        raise UnsupportedLayout("cast_scale: x must be dense")
+    out = torch.empty_strided(x.shape, x.stride(), dtype=out_dtype, device=x.device)
+    lib = load()
+    check(lib.b200_cast_scale(_ptr(x), _ptr(out), x.numel(), _code(x), _DTYPE_CODE[out_dtype],
+                              float(scale) if scale is not None else 1.0, 1 if scale is not None else 0,
+                              _stream()),
+          "b200_cast_scale")
+    return out

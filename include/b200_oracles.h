@@ -139,6 +139,35 @@ int32_t b200_batch_norm_fwd(const void* x, void* y, const void* weight, const vo
                             int32_t w_dtype, double eps, double momentum, int32_t relu, void* scratch,
                             int64_t scratch_bytes, void* stream);
 
+/* Column reduction: x is [batch, rows, cols] with cols unit-stride; out[b, c] = reduce over rows
+ * (op 0 sum, 1 mean, 2 amax). Tall inputs are split over several CTAs whose fp32 partials (in
+ * `scratch`, batch*cols floats per split; may be NULL for a single split) are combined in fp64 by
+ * a second launch. No atomics.
+ * Replaces sum_eb86a17deab9/oracle.py:20-70, sum_c2bf513c1ebf/oracle.py:10-29 and the
+ * channels-last spatial mean of mean_c9e1a8113328/oracle.py:11-76. */
+int32_t b200_col_reduce(const void* x, void* out, int64_t batch, int64_t rows, int64_t cols,
+                        int64_t x_batch_stride, int64_t x_row_stride, int64_t out_batch_stride,
+                        int32_t x_dtype, int32_t out_dtype, int32_t op, void* scratch, int64_t scratch_bytes,
+                        void* stream);
+
+/* Permuting copy into a contiguous output of shape out_shape[4]; in_strides[i] is the input
+ * stride (elements) of output dimension i. Optional scale (fp32 multiply) and dtype conversion.
+ * Replaces pointwise_c0d19d490a2f/oracle.py:10-33 (head split) and other permute + clone regions. */
+int32_t b200_permute_copy(const void* x, void* y, const int64_t* out_shape, const int64_t* in_strides,
+                          int32_t in_dtype, int32_t out_dtype, double scale, int32_t has_scale, void* stream);
+
+/* Transpose of the two innermost dimensions: input [batch, rows, cols] (cols unit-stride, given row
+ * and batch strides) -> contiguous output [batch, cols, rows], through a shared-memory tile.
+ * Replaces pointwise_021e90d9c17d/oracle.py:10-51. */
+int32_t b200_transpose_copy(const void* x, void* y, int64_t batch, int64_t rows, int64_t cols,
+                            int64_t in_batch_stride, int64_t in_row_stride, int32_t in_dtype,
+                            int32_t out_dtype, double scale, int32_t has_scale, void* stream);
+
+/* Contiguous cast / scale of n elements.
+ * Replaces pointwise_8bb40810003c/oracle.py:11-15 and pointwise_95ed2ef35da9/oracle.py:10-44. */
+int32_t b200_cast_scale(const void* x, void* y, int64_t n, int32_t in_dtype, int32_t out_dtype, double scale,
+                        int32_t has_scale, void* stream);
+
 /* b200_batch_norm_fwd for callers that may not allocate device memory (a host framework that owns
  * the only arena and forbids plug-ins to call cudaMalloc, or a caller that owns nothing but the
  * tensors it was handed): the scratch lives in a fixed array inside the library's device image

@@ -1,0 +1,149 @@
+"""Parity of the column-reduce, permuting-copy, transpose and cast kernels against the eager oracle."""
+import pytest
+import torch
+
+from conftest import assert_close, assert_sum_close
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16, torch.float16]
+
+
+def _kernels():
+    from better_benchmark_b200 import kernels
+    return kernels
+
+
+def _rand(shape, dtype, seed):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    return torch.randn(shape, generator=g, device="cuda", dtype=torch.float32).to(dtype)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("op", ["sum", "mean", "amax"])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (7, 5), (64, 256), (1000, 768), (4096, 100), (33, 4099),
+                                       (20000, 64), (3, 1)])
+def test_col_reduce_2d(dtype, op, rows, cols):
+    from oracle import eager
+    x = _rand((rows, cols), dtype, rows * 31 + cols)
+    got = _kernels().col_reduce(x, op)
+    want = eager.ColumnSum(op)(x)
+    if op == "amax":
+        assert torch.equal(got, want)
+    else:
+        anchor = eager.ColumnSum(op)(x.double())
+        assert_sum_close(got, want, anchor, f"col_{op} {rows}x{cols} {dtype}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("n,c,h,w", [(2, 16, 7, 7), (8, 64, 14, 14), (3, 100, 5, 9), (4, 2048, 7, 7)])
+def test_spatial_mean_channels_last_and_nchw(dtype, n, c, h, w):
+    from better_benchmark_b200.families import column_sum
+    from oracle import eager
+    x = _rand((n, c, h, w), dtype, n + c)
+    for t in (x.contiguous(memory_format=torch.channels_last), x):
+        got = column_sum.spatial_mean_forward([t])
+        want = eager.SpatialMean()(t)
+        anchor = eager.SpatialMean()(t.double())
+        assert_sum_close(got, want, anchor, f"spatial mean {tuple(t.shape)} {t.stride()}")
+
+
+def test_col_reduce_batched_strided_rows():
+    from oracle import eager
+    base = _rand((4, 300, 160), torch.float32, 5)
+    x = base[:, :, :96]  # row stride 160, 96 columns kept
+    got = _kernels().col_reduce(x, "sum")
+    want = torch.stack([eager.ColumnSum()(x[i]) for i in range(4)])
+    anchor = torch.stack([eager.ColumnSum()(x[i].double()) for i in range(4)])
+    assert_sum_close(got, want, anchor, "batched strided col sum")
+
+
+def test_col_reduce_zero_rows_and_bad_layout():
+    k = _kernels()
+    x = torch.empty((0, 16), device="cuda")
+    assert torch.equal(k.col_reduce(x, "sum"), torch.zeros(16, device="cuda"))
+    assert torch.isnan(k.col_reduce(x, "mean")).all()
+    with pytest.raises(k.UnsupportedLayout):
+        k.col_reduce(torch.empty((8, 16), device="cuda").t(), "sum")
+
+
+def test_col_reduce_is_bit_reproducible():
+    x = _rand((50000, 384), torch.float32, 9)
+    a = _kernels().col_reduce(x, "sum")
+    for _ in range(3):
+        assert torch.equal(a, _kernels().col_reduce(x, "sum"))
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("b,s,h,d", [(1, 5, 3, 8), (2, 128, 12, 64), (4, 77, 8, 40), (2, 33, 5, 7)])
+@pytest.mark.parametrize("scale", [None, 0.125])
+def test_head_split(dtype, b, s, h, d, scale):
+    from oracle import eager
+    x = _rand((b * s, h * d), dtype, b + s + h + d)
+    got = _kernels().permute_copy(x.view(b, s, h, d), (0, 2, 1, 3), scale=scale)
+    want = eager.HeadSplitPermute(b, s, h, d, scale)(x)
+    assert got.is_contiguous()
+    if scale is None:
+        assert torch.equal(got, want)
+    else:
+        assert_close(got, want, "head split scaled")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 1), (5, 3), (64, 64), (65, 130), (3, 200, 77), (2, 3, 128, 96),
+                                   (1024, 768), (4, 1, 33)])
+def test_transpose_last_two(dtype, shape):
+    from oracle import eager
+    x = _rand(shape, dtype, sum(shape))
+    nd = len(shape)
+    dims = list(range(nd - 2)) + [nd - 1, nd - 2]
+    got = _kernels().permute_copy(x, dims)
+    want = eager.Transpose2D()(x)
+    assert got.is_contiguous() and torch.equal(got, want)
+
+
+@pytest.mark.parametrize("dims", [(3, 2, 1, 0), (1, 0, 2, 3), (0, 3, 1, 2), (2, 0, 3, 1), (0, 1, 2, 3)])
+def test_general_permutations(dims):
+    x = _rand((6, 10, 12, 20), torch.bfloat16, 3)
+    got = _kernels().permute_copy(x, dims)
+    assert torch.equal(got, x.permute(*dims).contiguous())
+
+
+def test_permute_with_conversion_and_strided_source():
+    base = _rand((4, 50, 6, 48), torch.float32, 11)
+    x = base[..., :32]
+    got = _kernels().permute_copy(x, (0, 2, 1, 3), out_dtype=torch.bfloat16, scale=2.0)
+    want = (x * 2.0).permute(0, 2, 1, 3).contiguous().to(torch.bfloat16)
+    assert torch.equal(got, want)
+
+
+def test_permute_rejects_five_unmergeable_dims():
+    k = _kernels()
+    x = _rand((2, 3, 4, 5, 6), torch.float32, 1)
+    with pytest.raises(k.UnsupportedLayout):
+        k.permute_copy(x, (4, 3, 2, 1, 0))
+
+
+@pytest.mark.parametrize("src,dst", [(torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32),
+                                     (torch.float16, torch.float32), (torch.float32, torch.float16),
+                                     (torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("n", [1, 7, 4096, 1_000_003])
+@pytest.mark.parametrize("scale", [None, 0.5, 1.7])
+def test_cast_scale(src, dst, n, scale):
+    x = _rand((n,), src, n)
+    got = _kernels().cast_scale(x, dst, scale=scale)
+    want = x if scale is None else x.float() * scale
+    assert torch.equal(got, want.to(dst))
+
+
+def test_cast_keeps_channels_last_strides():
+    x = _rand((2, 8, 5, 5), torch.bfloat16, 2).contiguous(memory_format=torch.channels_last)
+    got = _kernels().cast_scale(x, torch.float32)
+    assert got.stride() == x.stride() and torch.equal(got, x.float())
+
+
+def test_cast_between_the_two_16_bit_types_is_rejected_loudly():
+    k = _kernels()
+    from better_benchmark_b200.native import KernelArgumentError
+    with pytest.raises(KernelArgumentError):
+        k.cast_scale(_rand((64,), torch.bfloat16, 1), torch.float16)
