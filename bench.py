@@ -118,8 +118,8 @@ class ClockSampler:
 
 
 def dist_env():
-    return (int(os.environ.get("RANK", "0")), int(os.environ.get("LOCAL_RANK", "0")),
-            int(os.environ.get("WORLD_SIZE", "1")))
+    from better_benchmark_b200.replicas import dist_env as env
+    return env()
 
 
 # ---------------------------------------------------------------------------------------------
@@ -271,16 +271,9 @@ def gpu_arm(args, workload):
                          "(use --impl reference for the host baseline)")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    use_dist = world > 1
-    if use_dist:
-        import torch.distributed as dist
-        dist.init_process_group("nccl", device_id=device)
-
-        def barrier():
-            dist.barrier()
-    else:
-        def barrier():
-            return None
+    from better_benchmark_b200.replicas import ReplicaGroup
+    group = ReplicaGroup(device=device)  # NCCL when world > 1; barrier + max-over-ranks only
+    barrier = group.barrier
 
     peak, peak_source = measured_peak()
     sets, per_set = build_input_sets(workload, device, 4 * L2_BYTES_ASSUMED)
@@ -291,11 +284,7 @@ def gpu_arm(args, workload):
         sampler.start()
         time.sleep(0.3)
     total_ms, launches = time_steps(workload, sets, args.steps, args.warmup, barrier)
-    if use_dist:
-        import torch.distributed as dist
-        t = torch.tensor([total_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        total_ms = float(t.item())
+    total_ms = group.max_over_ranks(total_ms)
     ms_per_step = total_ms / args.steps
     # keep the GPU under the same load a little longer so that the clock sampler sees it
     load_graph = torch.cuda.CUDAGraph()
@@ -313,11 +302,7 @@ def gpu_arm(args, workload):
     value = gbps_one * world
 
     e2e_ms, h2d, d2h = time_e2e(workload, device, max(3, min(args.steps, 20)), 2)
-    if use_dist:
-        import torch.distributed as dist
-        t = torch.tensor([e2e_ms], device=device, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_ms = float(t.item())
+    e2e_ms = group.max_over_ranks(e2e_ms)
     e2e_value = workload.algorithmic_bytes / (e2e_ms * 1e-3) / 1e9 * world
 
     per_config = {}
@@ -346,10 +331,7 @@ def gpu_arm(args, workload):
         cpu_baseline = {"value": round(cpu_gbps, 3), "unit": "GB/s", "cores": cores, "kind": "port",
                         "sample": f"full {workload.name} workload per call, eager aten graph of the region, "
                                   f"{done} calls, mean {mean_s * 1e3:.1f} ms"}
-    if use_dist:
-        import torch.distributed as dist
-        dist.barrier()
-        dist.destroy_process_group()
+    group.close()
     if rank != 0:
         return 0
     line = {
