@@ -488,7 +488,7 @@ def _run_anchored_numerics_gate(oracle_forward, instance, compiled, inputs):
         oracle_outs = _normalize_outputs(oracle_forward(_clone_inputs(inputs)))
     _seed_input_generation(1)
     with torch.no_grad():
-        comp_outs = _normalize_outputs((compiled or instance)(*_clone_inputs(inputs)))
+        comp_outs = _normalize_outputs((compiled if compiled is not None else instance)(*_clone_inputs(inputs)))
     if len(oracle_outs) != len(ref) or len(comp_outs) != len(ref):
         return None
     return _anchored_numerics_gate(oracle_outs, comp_outs, ref, stochastic, ref_precision=ref_precision)
@@ -601,10 +601,10 @@ def bench_oracle(oracle_forward, instance, inputs, repro_id, *, warmup=25, rep=2
 
     compiled = g_compile = None
     if compile_reference:
-        import torch._dynamo
+        import torch._dynamo as dynamo
         import torch._inductor.config as inductor_config
         inductor_config.coordinate_descent_tuning = True
-        torch._dynamo.reset()
+        dynamo.reset()
         compiled = torch.compile(instance)
         with torch.no_grad():
             for _ in range(5):
