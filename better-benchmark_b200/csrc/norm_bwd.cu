@@ -20,6 +20,8 @@
 // the partial rows are summed in fp64, in a fixed order, into dw/db. No atomics: results are
 // bit-reproducible. A two-launch variant (main + finalize) does the same without the barrier.
 #include "rowwise.cuh"
+#include <type_traits>
+
 #include "tile_stream.cuh"
 
 #include <cstdlib>
@@ -505,6 +507,295 @@ norm_bwd_stream_kernel(const NormBwdParams p, const int stages) {
   }
 }
 
+// ----------------------------------------------------------------------------------------------
+// Row-tile variant of the streaming kernel for wide rows (one 16-byte vector per thread): a stage
+// holds R consecutive rows of x and of dy, and everything that costs a fixed amount per row and
+// thread - the wait on the stage, the warp reduction, the CTA barrier, the exchange of the warps'
+// partial sums - is paid once per tile:
+//   * the R (or 2R for LayerNorm) row sums of a thread are reduced across the warp together: in
+//     every step a lane keeps one half of its values and hands the other half to its partner, so
+//     R values need log2(R) + ... shuffles instead of 5R;
+//   * the warps' partials of all rows of the tile go to shared memory as one small table
+//     [value][warp] that every warp sums with one load per lane and a short butterfly.
+// The second pass reads the stage again (keeping the vectors in registers costs more than it
+// saves at 64 registers per thread), so a stage is refilled one tile after it was consumed.
+// ----------------------------------------------------------------------------------------------
+template <int N>
+__device__ __forceinline__ float warp_reduce_multi(float (&v)[N], int lane) {
+  // After the call lane l holds the warp total of value l / (32 / N).
+  int off = 16;
+#pragma unroll
+  for (int n = N; n > 1; n >>= 1) {
+    const bool upper = (lane & off) != 0;
+#pragma unroll
+    for (int i = 0; i < n / 2; ++i) {
+      const float send = upper ? v[i] : v[i + n / 2];
+      const float keep = upper ? v[i + n / 2] : v[i];
+      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+    }
+    off >>= 1;
+  }
+#pragma unroll
+  for (int k = 0; k < 5; ++k) {
+    if (off >= 1) {
+      v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
+      off >>= 1;
+    }
+  }
+  return v[0];
+}
+
+template <typename T, int R, bool LN>
+__global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdParams p, const int stages) {
+  constexpr int V = Elem<T>::V;
+  constexpr int NVAL = R * (LN ? 2 : 1);  // row sums per tile: 2, 4 or 8
+  constexpr int LPV = 32 / NVAL;          // lanes that share one value after the warp reduction
+  constexpr int PER = NVAL / 2;           // table entries a lane sums in the second stage
+  static_assert(NVAL == 2 || NVAL == 4 || NVAL == 8, "tile of 1, 2 or 4 rows");
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ __align__(16) float red[2][NVAL][16];
+  __shared__ double fin[16 * 64];
+  __shared__ int bar_ok;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int nv = p.n / V;
+  const bool active = tid < nv;
+  const uint32_t row_bytes = (uint32_t)nv * 16u;
+  const uint32_t stage_bytes = 2u * R * row_bytes;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_bytes);
+  const int rows = (int)p.rows;  // the launcher admits fewer than 2^31 rows
+  const int tiles = (rows + R - 1) / R;
+  const int my_tiles = tiles > (int)blockIdx.x ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int row_step = (int)gridDim.x * R;
+
+  for (int i = tid; i < 2 * NVAL * 16; i += blockDim.x) (&red[0][0][0])[i] = 0.f;
+  if (tid == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_init_fence();
+  }
+  __syncthreads();
+
+  auto issue = [&](int k, int slot) {  // thread 0 only
+    const T* xg = reinterpret_cast<const T*>(p.x);
+    const T* dyg = reinterpret_cast<const T*>(p.dy);
+    const long long row0 = ((long long)blockIdx.x + (long long)k * gridDim.x) * R;
+    const int nrows = p.rows - row0 < R ? (int)(p.rows - row0) : R;
+    uint64_t* bar = &full[slot];
+    unsigned char* dst = smem + (size_t)slot * stage_bytes;
+    mbar_arrive_expect_tx(bar, 2u * nrows * row_bytes);
+    if (p.x_row_stride == p.n && p.dy_row_stride == p.n) {
+      bulk_load(dst, xg + row0 * p.n, nrows * row_bytes, bar);
+      bulk_load(dst + R * row_bytes, dyg + row0 * p.n, nrows * row_bytes, bar);
+    } else {
+      for (int r = 0; r < nrows; ++r) {
+        bulk_load(dst + r * row_bytes, xg + (row0 + r) * p.x_row_stride, row_bytes, bar);
+        bulk_load(dst + (R + r) * row_bytes, dyg + (row0 + r) * p.dy_row_stride, row_bytes, bar);
+      }
+    }
+  };
+  int issued = 0, issue_slot = 0;
+  if (tid == 0) {
+    for (; issued < my_tiles && issued < stages; ++issued) issue(issued, issued);
+    issue_slot = issued % stages;
+  }
+
+  // A thread owns the same V columns in every row: weight slice and gradient sums in registers.
+  f32x2 wv[V / 2], acc_w[V / 2], acc_b[LN ? V / 2 : 1];
+  {
+    float wf[V];
+    if (p.w && active) {
+      load_param<V>(p.w, p.w_dtype, (long long)tid * V, wf);
+    } else {
+#pragma unroll
+      for (int i = 0; i < V; ++i) wf[i] = 1.f;
+    }
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      wv[i] = pack2(wf[2 * i], wf[2 * i + 1]);
+      acc_w[i] = splat2(0.f);
+    }
+#pragma unroll
+    for (int i = 0; i < (LN ? V / 2 : 1); ++i) acc_b[i] = splat2(0.f);
+  }
+  // dx offsets fit 32 bits (checked by the launcher): one 64-bit address per store.
+  const int col = tid * V;
+  const uint32_t dx_col = active ? (uint32_t)(col / p.head_dim) * (uint32_t)p.dx_head_stride + (uint32_t)(col % p.head_dim) : 0u;
+  const bool one_batch_per_tile = p.seq % R == 0;  // tiles start at multiples of R
+  T* const dx_base = reinterpret_cast<T*>(p.dx);
+  const float inv_n = 1.0f / p.n_f;
+  bool failed = false;
+  int parity = 0, st = 0;
+  uint32_t phase = 0;
+  int row0 = (int)blockIdx.x * R;
+
+  for (int k = 0; k < my_tiles; ++k, row0 += row_step) {
+    const int nrows = rows - row0 < R ? rows - row0 : R;
+    float rstd[R], mean[LN ? R : 1];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      rstd[r] = r < nrows ? __ldg(p.rstd + row0 + r) : 0.f;
+      if constexpr (LN) mean[r] = r < nrows ? __ldg(p.mean + row0 + r) : 0.f;
+    }
+    const bool arrived = mbar_wait(&full[st], phase);
+    const unsigned char* sx = smem + (size_t)st * stage_bytes + (size_t)tid * 16;
+    const unsigned char* sy = sx + (size_t)R * row_bytes;
+    const bool whole = active && nrows == R;  // uniform per warp except in the last warp of a ragged row
+
+    // Pass 1: the row sums of this thread's columns.
+    float vals[NVAL];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      f32x2 s1 = splat2(0.f), s2 = splat2(0.f);
+      if (whole || (active && r < nrows)) {
+        f32x2 x2[V / 2], dy2[V / 2];
+        Pairs<T>::unpack(*reinterpret_cast<const uint4*>(sx + (size_t)r * row_bytes), x2);
+        Pairs<T>::unpack(*reinterpret_cast<const uint4*>(sy + (size_t)r * row_bytes), dy2);
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) {
+          const f32x2 g2 = mul2(dy2[i], wv[i]);
+          if constexpr (LN) {
+            s1 = add2(s1, g2);
+            s2 = add2(s2, mul2(g2, mul2(sub2(x2[i], splat2(mean[r])), splat2(rstd[r]))));
+          } else {
+            s2 = add2(s2, mul2(g2, x2[i]));
+          }
+        }
+      }
+      vals[LN ? 2 * r + 1 : r] = hsum2(s2);
+      if constexpr (LN) vals[2 * r] = hsum2(s1);
+    }
+    const float mine = warp_reduce_multi<NVAL>(vals, lane);
+    if ((lane & (LPV - 1)) == 0) red[parity][lane / LPV][warp] = mine;
+
+    if (!__syncthreads_and(arrived)) {
+      failed = true;
+      if (tid == 0) {
+        note_wait_timeout();
+        atomicExch(&p.bar[1], 1u);  // lets the other CTAs leave the grid barrier at once
+        int ds = st;
+        uint32_t dp = phase;
+        for (int d = k; d < issued; ++d) {
+          mbar_wait(&full[ds], dp);
+          if (++ds == stages) { ds = 0; dp ^= 1u; }
+        }
+      }
+      break;
+    }
+    // The second pass reads this stage again; what the barrier proves is that the PREVIOUS tile's
+    // stage has been read to the end by every thread: that one is refilled.
+    if (tid == 0 && k >= 1 && issued < my_tiles) {
+      fence_proxy_async_smem();
+      issue(issued, issue_slot);
+      ++issued;
+      if (++issue_slot == stages) issue_slot = 0;
+    }
+
+    // Second stage of the reduction: lane l sums PER consecutive entries of the [value][warp]
+    // table, a butterfly over the LPV lanes of a value finishes it.
+    float part;
+    {
+      const float* tp = &red[parity][0][0] + lane * PER;
+      if constexpr (PER == 1) {
+        part = tp[0];
+      } else if constexpr (PER == 2) {
+        const float2 t = *reinterpret_cast<const float2*>(tp);
+        part = t.x + t.y;
+      } else {
+        const float4 t = *reinterpret_cast<const float4*>(tp);
+        part = (t.x + t.y) + (t.z + t.w);
+      }
+#pragma unroll
+      for (int off = LPV / 2; off >= 1; off >>= 1) part += __shfl_xor_sync(0xffffffffu, part, off);
+    }
+    parity ^= 1;
+
+    // Pass 2: dx and the gradient sums.
+    uint32_t off0 = 0;
+    if (one_batch_per_tile) {
+      const unsigned int bi = fast_div((unsigned int)row0, p.seq_div);
+      const unsigned int si = (unsigned int)row0 - bi * (unsigned int)p.seq;
+      off0 = bi * (uint32_t)p.dx_batch_stride + si * (uint32_t)p.dx_seq_stride + dx_col;
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float t2 = __shfl_sync(0xffffffffu, part, (LN ? 2 * r + 1 : r) * LPV);
+      const float t1 = LN ? __shfl_sync(0xffffffffu, part, (2 * r) * LPV) : 0.f;
+      if (whole || (active && r < nrows)) {
+        uint32_t off;
+        if (one_batch_per_tile) {
+          off = off0 + (uint32_t)r * (uint32_t)p.dx_seq_stride;
+        } else {
+          const unsigned int row = (unsigned int)(row0 + r);
+          const unsigned int bi = fast_div(row, p.seq_div);
+          const unsigned int si = row - bi * (unsigned int)p.seq;
+          off = bi * (uint32_t)p.dx_batch_stride + si * (uint32_t)p.dx_seq_stride + dx_col;
+        }
+        f32x2 x2[V / 2], dy2[V / 2], o2[V / 2];
+        Pairs<T>::unpack(*reinterpret_cast<const uint4*>(sx + (size_t)r * row_bytes), x2);
+        Pairs<T>::unpack(*reinterpret_cast<const uint4*>(sy + (size_t)r * row_bytes), dy2);
+        const f32x2 rstd2 = splat2(rstd[r]);
+        if constexpr (LN) {
+          // The division by n of the aten graph is a multiplication by 1/n here (exact for
+          // powers of two, otherwise within one fp32 ulp of a per-row coefficient).
+          const f32x2 k2 = splat2(rstd[r] * inv_n), n2 = splat2(p.n_f), s1b = splat2(t1), s2b = splat2(t2);
+          const f32x2 mean2 = splat2(mean[r]);
+#pragma unroll
+          for (int i = 0; i < V / 2; ++i) {
+            const f32x2 g2 = mul2(dy2[i], wv[i]);
+            const f32x2 xhat = mul2(sub2(x2[i], mean2), rstd2);
+            acc_w[i] = add2(acc_w[i], mul2(dy2[i], xhat));
+            acc_b[i] = add2(acc_b[i], dy2[i]);
+            o2[i] = mul2(k2, sub2(sub2(mul2(g2, n2), s1b), mul2(xhat, s2b)));
+          }
+        } else {
+          // dx = g*rstd + k*(x*2), k = (sum * -0.5) * rstd^3 / n; the doubling is exact, so it is
+          // folded into the coefficient.
+          const float kf = ((t2 * -0.5f) * (rstd[r] * rstd[r] * rstd[r])) * inv_n;
+          const f32x2 k2 = splat2(kf * 2.0f);
+#pragma unroll
+          for (int i = 0; i < V / 2; ++i) {
+            const f32x2 g2 = mul2(dy2[i], wv[i]);
+            acc_w[i] = add2(acc_w[i], mul2(dy2[i], mul2(x2[i], rstd2)));
+            o2[i] = add2(mul2(g2, rstd2), mul2(k2, x2[i]));
+          }
+        }
+        st_stream(dx_base + off, Pairs<T>::pack(o2));
+      }
+    }
+    if (++st == stages) {
+      st = 0;
+      phase ^= 1u;
+    }
+  }
+
+  if (!failed && (p.dw || p.db) && active) {
+    float* pw = p.partials + (long long)blockIdx.x * p.n + (long long)tid * V;
+    float* pb = p.partials + ((long long)p.groups + blockIdx.x) * p.n + (long long)tid * V;
+    float f[V];
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) unpack2(acc_w[i], f[2 * i], f[2 * i + 1]);
+#pragma unroll
+    for (int q = 0; q < V / 4; ++q)
+      reinterpret_cast<float4*>(pw)[q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+    if constexpr (LN) {
+      if (p.db) {
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) unpack2(acc_b[i], f[2 * i], f[2 * i + 1]);
+#pragma unroll
+        for (int q = 0; q < V / 4; ++q)
+          reinterpret_cast<float4*>(pb)[q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+      }
+    }
+  }
+  if (p.fused) {
+    const bool ok = !failed && grid_barrier(p.bar, 1u, &bar_ok);
+    if (ok) {
+      if (p.dw) finalize_columns(p.partials, p.groups, p.n, p.dw, fin);
+      if (LN && p.db) finalize_columns(p.partials + (long long)p.groups * p.n, p.groups, p.n, p.db, fin);
+    }
+    grid_barrier_depart(p.bar);
+  }
+}
+
 __global__ void __launch_bounds__(512) norm_bwd_finalize_kernel(const NormBwdParams p) {
   __shared__ double fin[16 * 64];
   if (p.dw) finalize_columns(p.partials, p.groups, p.n, p.dw, fin);
@@ -602,6 +893,16 @@ static bool streaming_disabled() {
   return off;
 }
 
+// B200_NORM_BWD_TILE_ROWS=1|2 caps the rows per tile of the row-tile kernel (1: one row per
+// barrier, the earlier kernel); for measurements.
+static int tile_rows_override() {
+  static const int v = [] {
+    const char* e = getenv("B200_NORM_BWD_TILE_ROWS");
+    return e ? atoi(e) : 0;
+  }();
+  return v;
+}
+
 // CTA-per-row streaming launch; returns false when the shape does not fit (caller falls back).
 template <typename T, int CH, bool LN>
 static bool try_launch_norm_bwd_stream(NormBwdParams p, int threads, size_t scratch_bytes, bool cooperative,
@@ -651,6 +952,68 @@ static bool try_launch_norm_bwd_stream(NormBwdParams p, int threads, size_t scra
   }
   kernel<<<(unsigned)grid, threads, smem, st>>>(p, stages);
   *rc = launch_status("b200_norm_bwd (streaming)");
+  if (*rc == B200_OK && (p.dw || p.db)) {
+    norm_bwd_finalize_kernel<<<(p.n + 63) / 64, 512, 0, st>>>(p);
+    *rc = launch_status("b200_norm_bwd finalize");
+  }
+  return true;
+}
+
+// Row-tile streaming launch (one vector per thread); returns false when the shape does not fit.
+template <typename T, int R, bool LN>
+static bool try_launch_norm_bwd_tile(NormBwdParams p, int threads, size_t scratch_bytes, bool cooperative,
+                                     cudaStream_t st, int* rc) {
+  constexpr int V = Elem<T>::V;
+  if (streaming_disabled() || p.rows < 1024 || threads > 512) return false;
+  {  // the kernel addresses dx with 32-bit element offsets
+    const long long last = (p.rows / p.seq) * p.dx_batch_stride + (long long)(p.seq - 1) * p.dx_seq_stride +
+                           (long long)(p.n / p.head_dim - 1) * p.dx_head_stride + p.head_dim;
+    if (last >= 0x7fffffffLL || p.dx_batch_stride < 0 || p.dx_seq_stride < 0 || p.dx_head_stride < 0) return false;
+  }
+  const DeviceInfo& dev = device_info();
+  const size_t stage_bytes = 2 * (size_t)R * (size_t)(p.n / V) * 16;
+  const size_t static_bytes = 10 * 1024;  // red + fin + flags
+  const size_t per_cta = ((size_t)dev.max_smem_optin - 2048) / 2;  // two CTAs per SM
+  const size_t fixed = 8 * sizeof(uint64_t);
+  if (per_cta < static_bytes + fixed + 3 * stage_bytes) return false;  // at least three stages
+  int stages = (int)((per_cta - static_bytes - fixed) / stage_bytes);
+  if (stages > 8) stages = 8;
+  const size_t smem = (size_t)stages * stage_bytes + fixed;
+  auto kernel = norm_bwd_tile_kernel<T, R, LN>;
+  cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  const int per_sm = cached_occupancy(reinterpret_cast<const void*>(kernel), threads, smem);
+  long long grid = (long long)per_sm * dev.sm_count;
+  const long long tiles = (p.rows + R - 1) / R;
+  if (grid > tiles) grid = tiles;
+  if (p.dw || p.db) {
+    const long long plane = (long long)p.n * sizeof(float);
+    const long long max_groups = ((long long)scratch_bytes - 256) / (2 * plane);
+    if (max_groups < 1) return false;
+    if (grid > max_groups) grid = max_groups;
+  }
+  p.groups = (int)grid;
+  p.fused = cooperative ? 1 : 0;
+  if (cooperative) {
+    int stages_arg = stages;
+    void* args[] = {&p, &stages_arg};
+    e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3((unsigned)grid), dim3(threads),
+                                    args, smem, st);
+    if (e != cudaSuccess) {
+      cudaGetLastError();
+      *rc = fail((int)e, "b200_norm_bwd: cooperative launch failed: %s", cudaGetErrorString(e));
+      return true;
+    }
+    note_launch();
+    *rc = B200_OK;
+    return true;
+  }
+  kernel<<<(unsigned)grid, threads, smem, st>>>(p, stages);
+  *rc = launch_status("b200_norm_bwd (row tiles)");
   if (*rc == B200_OK && (p.dw || p.db)) {
     norm_bwd_finalize_kernel<<<(p.n + 63) / 64, 512, 0, st>>>(p);
     *rc = launch_status("b200_norm_bwd finalize");
@@ -717,6 +1080,11 @@ static int launch_norm_bwd(NormBwdParams p, bool vector_ok, size_t scratch_bytes
     if (nv <= 512) {
       // streaming: one vector per thread (many warps, few registers, the weight slice resident)
       const int wide = (int)((nv + 31) / 32 * 32);
+      if (tile_rows_override() != 1) {
+        if (tile_rows_override() != 2 &&
+            try_launch_norm_bwd_tile<T, 4, LN>(p, wide, scratch_bytes, cooperative, st, &rc)) return rc;
+        if (try_launch_norm_bwd_tile<T, 2, LN>(p, wide, scratch_bytes, cooperative, st, &rc)) return rc;
+      }
       if (try_launch_norm_bwd_stream<T, 1, LN>(p, wide, scratch_bytes, cooperative, st, &rc)) return rc;
       int threads = (int)((nv + 1) / 2);
       threads = (threads + 31) / 32 * 32;

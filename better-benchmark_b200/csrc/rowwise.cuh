@@ -113,6 +113,75 @@ __device__ __forceinline__ f32x2 fma2(f32x2 a, f32x2 b, f32x2 c) {
   return r;
 }
 
+// 16-byte vector <-> packed fp32 pairs, converted word by word so that each pair is born in (and
+// consumed from) an aligned register pair instead of being assembled from two scalars.
+template <typename T>
+struct Pairs;
+
+template <>
+struct Pairs<float> {
+  static __device__ __forceinline__ void unpack(const uint4& r, f32x2 (&v)[2]) {
+    asm("mov.b64 %0, {%1,%2};" : "=l"(v[0]) : "r"(r.x), "r"(r.y));
+    asm("mov.b64 %0, {%1,%2};" : "=l"(v[1]) : "r"(r.z), "r"(r.w));
+  }
+  static __device__ __forceinline__ uint4 pack(const f32x2 (&v)[2]) {
+    uint4 r;
+    asm("mov.b64 {%0,%1}, %2;" : "=r"(r.x), "=r"(r.y) : "l"(v[0]));
+    asm("mov.b64 {%0,%1}, %2;" : "=r"(r.z), "=r"(r.w) : "l"(v[1]));
+    return r;
+  }
+};
+
+template <>
+struct Pairs<__nv_bfloat16> {
+  static __device__ __forceinline__ f32x2 word(uint32_t w) {
+    f32x2 r;  // bf16 -> fp32: the low element is a 16-bit shift, the high one a mask
+    asm("{\n\t.reg .b32 lo, hi;\n\tshl.b32 lo, %1, 16;\n\tand.b32 hi, %1, 0xffff0000;\n\tmov.b64 %0, {lo,hi};\n\t}"
+        : "=l"(r) : "r"(w));
+    return r;
+  }
+  static __device__ __forceinline__ void unpack(const uint4& r, f32x2 (&v)[4]) {
+    v[0] = word(r.x); v[1] = word(r.y); v[2] = word(r.z); v[3] = word(r.w);
+  }
+  static __device__ __forceinline__ uint32_t narrow(f32x2 v) {
+    uint32_t r;
+    asm("{\n\t.reg .b32 lo, hi;\n\tmov.b64 {lo,hi}, %1;\n\tcvt.rn.bf16x2.f32 %0, hi, lo;\n\t}" : "=r"(r) : "l"(v));
+    return r;
+  }
+  static __device__ __forceinline__ uint4 pack(const f32x2 (&v)[4]) {
+    return make_uint4(narrow(v[0]), narrow(v[1]), narrow(v[2]), narrow(v[3]));
+  }
+};
+
+template <>
+struct Pairs<__half> {
+  static __device__ __forceinline__ f32x2 word(uint32_t w) {
+    f32x2 r;
+    asm("{\n\t.reg .b16 a, b;\n\t.reg .b32 lo, hi;\n\tmov.b32 {a,b}, %1;\n\tcvt.f32.f16 lo, a;\n\tcvt.f32.f16 hi, b;\n\t"
+        "mov.b64 %0, {lo,hi};\n\t}"
+        : "=l"(r) : "r"(w));
+    return r;
+  }
+  static __device__ __forceinline__ void unpack(const uint4& r, f32x2 (&v)[4]) {
+    v[0] = word(r.x); v[1] = word(r.y); v[2] = word(r.z); v[3] = word(r.w);
+  }
+  static __device__ __forceinline__ uint32_t narrow(f32x2 v) {
+    uint32_t r;
+    asm("{\n\t.reg .b32 lo, hi;\n\tmov.b64 {lo,hi}, %1;\n\tcvt.rn.f16x2.f32 %0, hi, lo;\n\t}" : "=r"(r) : "l"(v));
+    return r;
+  }
+  static __device__ __forceinline__ uint4 pack(const f32x2 (&v)[4]) {
+    return make_uint4(narrow(v[0]), narrow(v[1]), narrow(v[2]), narrow(v[3]));
+  }
+};
+
+// Sum of the two halves of a pair.
+__device__ __forceinline__ float hsum2(f32x2 v) {
+  float a, b;
+  unpack2(v, a, b);
+  return a + b;
+}
+
 // Natural exponential of a pair, for results that are rounded to a 16-bit type afterwards.
 // y = x*log2(e) is split into its rounded value yh and the exact rounding residual plus the
 // low part of the constant (el); 2^yh comes from the hardware approximation (relative error
