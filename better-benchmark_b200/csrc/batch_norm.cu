@@ -27,6 +27,7 @@
 #include "rowwise.cuh"
 #include "tile_stream.cuh"
 
+#include <cstdlib>
 #include <mutex>
 #include <type_traits>
 
@@ -478,6 +479,456 @@ batch_norm_cl_stream_kernel(const BatchNormParams p, const int stages, const int
 }
 
 // ----------------------------------------------------------------------------------------------
+// Channels-last fused kernel with one private copy ring per WARP and dynamic work distribution
+// (vpr = C / V a power of two <= 32; one CTA of 32 warps per SM, cooperative launch).
+//
+// The CTA-wide ring above costs one CTA barrier per tile, which keeps 32 warps in lock step, and
+// its static split makes every CTA wait for the SM with the least memory bandwidth. Here:
+//   * x is cut into blocks of 32 chunks (a chunk = 32 * U vectors = 512 * U bytes); a CTA takes a
+//     block, warp w of the CTA takes chunk w of it. The first blocks of a CTA are fixed
+//     (b, b + grid, ...), the later ones are claimed from a global counter by thread 0, one claim
+//     in flight per chunk consumed, a few blocks ahead of use; the block numbers go to a queue in
+//     shared memory that all warps of the CTA read. Fast SMs therefore take more blocks.
+//   * each warp streams its chunks through its own ring: lane 0 starts the bulk copies, all lanes
+//     wait on the chunk's mbarrier, consume it, and after a __syncwarp lane 0 refills the slot.
+//     No CTA barrier in either pass; warps drift apart and hide each other's latencies.
+//   pass 1  the CTA's blocks in queue order; a warp's last `stages` chunks are never overwritten.
+//   stats   lanes that share a vector column are folded by shuffles, warps through shared memory,
+//           CTAs through the scratch buffer and one grid barrier (two for many channels), fp64.
+//   pass 2  the same blocks in reverse order: the resident chunks first, then the rest, each
+//           loaded again into the slot its successor freed (most recently read first: the
+//           likeliest to sit in L2).
+// Every wait is bounded (copies: mbar_wait; the queue: a counted spin); a wait that runs out makes
+// the CTA raise the error word of the grid barrier, wait for its own copies, and skip the rest.
+// ----------------------------------------------------------------------------------------------
+constexpr int BN_QUEUE = 128;  // blocks one CTA can take (the launcher keeps the average far below)
+
+template <typename T, int U>
+__global__ void __launch_bounds__(1024, 1)
+batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int red_bytes, const int nblocks,
+                          const int dynamic) {
+  constexpr int V = Elem<T>::V;
+  constexpr uint32_t CHUNK_BYTES = 512u * U;
+  constexpr int CHUNK_VECS = 32 * U;
+  extern __shared__ __align__(128) unsigned char smem[];
+  __shared__ int bar_ok;
+  __shared__ int cta_failed;
+  __shared__ int q_ids[BN_QUEUE];  // block numbers in the order this CTA takes them; -1 ends the list
+  __shared__ int q_count;          // entries of q_ids that are valid
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int T_ = blockDim.x;  // 1024
+  const int vpr = p.channels / V;
+  const int vc = lane & (vpr - 1);  // this lane's vector column, the same in every chunk
+  // layout: [32 warps][stages][CHUNK_BYTES] | reduction area (red_bytes) | mbarriers [32][stages]
+  unsigned char* ring = smem + (size_t)warp * stages * CHUNK_BYTES;
+  float* red = reinterpret_cast<float*>(smem + (size_t)32 * stages * CHUNK_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)32 * stages * CHUNK_BYTES + red_bytes) + warp * stages;
+  const T* x = reinterpret_cast<const T*>(p.x);
+  const long long total_vecs = p.rows * vpr;
+
+  // The shift of the channel this thread finalises later: fetched now, needed after the barrier.
+  const float stat_shift = tid < p.channels ? Elem<T>::to_f32(__ldg(x + tid)) : 0.f;
+
+  // Fixed head of the queue: blocks b, b + grid, ...; with `dynamic` the rest is claimed while the
+  // head is consumed, otherwise the whole list is fixed (and the sums are bit-reproducible).
+  const int head = (dynamic & 1) ? stages + 3 : BN_QUEUE - 1;
+  if (tid == 0) {
+    cta_failed = 0;
+    int n = 0;
+    for (; n < head && n < BN_QUEUE - 1; ++n) {
+      const long long id = (long long)blockIdx.x + (long long)n * gridDim.x;
+      if (id >= nblocks) break;
+      q_ids[n] = (int)id;
+    }
+    if (n < head || !(dynamic & 1)) q_ids[n++] = -1;  // the list ends here
+    q_count = n;
+  }
+  if (lane == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+  }
+  mbar_init_fence();
+  __syncthreads();
+
+  // producer state (thread 0 only)
+  int qc = q_count;
+  bool claims_done = q_ids[qc - 1] < 0;
+  bool have_pending = false;
+  unsigned int pending = 0;
+  const unsigned int dyn_base = (unsigned int)head * gridDim.x;
+  auto publish = [&](int id) {  // thread 0: append one entry (a block number, or -1 to end the list)
+    reinterpret_cast<volatile int*>(q_ids)[qc] = id;
+    __threadfence_block();
+    *reinterpret_cast<volatile int*>(&q_count) = ++qc;
+    if (id < 0) claims_done = true;
+  };
+  auto producer_step = [&](int k) {  // thread 0, once per chunk consumed
+    if (have_pending) {  // a claim is only made when the queue has room for it, so none is ever dropped
+      const unsigned int id = dyn_base + pending;
+      publish(id >= (unsigned int)nblocks ? -1 : (int)id);
+      have_pending = false;
+    }
+    if (!claims_done && qc == BN_QUEUE - 1) publish(-1);  // full: the other CTAs take what is left
+    if (!claims_done && qc < k + stages + 3) {
+      pending = atomicAdd(&p.bar[3], 1u);  // used one chunk later: the round trip is off the critical path
+      have_pending = true;
+    }
+  };
+  // Block number of the k-th block of this CTA; -1: the list ended; -2: the queue did not fill in time.
+  auto block_id = [&](int k) {
+    if (k >= BN_QUEUE) return -1;
+    volatile int* cnt = reinterpret_cast<volatile int*>(&q_count);
+    unsigned int spins = 0;
+    while (*cnt <= k) {
+      if (tid == 0) {  // the producer itself must never wait for its own claim
+        if (have_pending || !claims_done) {
+          producer_step(k);
+          continue;
+        }
+      }
+      if (++spins > (1u << 20)) return -2;
+      __nanosleep(20);
+    }
+    return reinterpret_cast<volatile int*>(q_ids)[k];
+  };
+  auto chunk_first = [&](int id) { return ((long long)id * 32 + warp) * CHUNK_VECS; };
+  auto chunk_vecs = [&](int id) {
+    const long long left = total_vecs - chunk_first(id);
+    return left < CHUNK_VECS ? (left > 0 ? (int)left : 0) : CHUNK_VECS;
+  };
+  const uint64_t keep_policy = (dynamic & 2) ? l2_policy_evict_last() : l2_policy_evict_normal();
+  const uint64_t drop_policy = l2_policy_evict_first();
+  auto issue = [&](int id, int slot, uint64_t policy) {  // lane 0 only; no copy for an empty chunk
+    const int nv = chunk_vecs(id);
+    if (nv <= 0) return;
+    const uint32_t bytes = (uint32_t)nv * 16u;
+    mbar_arrive_expect_tx(&full[slot], bytes);
+    bulk_load_hint(ring + (size_t)slot * CHUNK_BYTES, reinterpret_cast<const uint4*>(p.x) + chunk_first(id), bytes,
+                   &full[slot], policy);
+  };
+
+#ifdef B200_BN_TIMING
+  unsigned long long* tlog = reinterpret_cast<unsigned long long*>(p.stats + 2 * p.channels) + blockIdx.x * 8;
+#define B200_WMARK(i)                                                        \
+  {                                                                          \
+    __syncthreads();                                                         \
+    if (tid == 0) {                                                          \
+      unsigned long long t_;                                                 \
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t_));                 \
+      tlog[i] = t_;                                                          \
+    }                                                                        \
+  }
+#else
+#define B200_WMARK(i)
+#endif
+  B200_WMARK(0)
+  bool failed = false;
+  uint32_t phase_bits = 0;  // bit s: parity of the next completion of slot s
+  uint32_t busy_bits = 0;   // bit s: slot s has a copy that was started and not yet waited for
+  int n_chunks = 0x7fffffff;  // blocks of this CTA; known once the end of the list has been seen
+
+  // ---- pass 1: shifted sums -------------------------------------------------------------------
+  f32x2 shift[V / 2], s1[V / 2], s2[V / 2];
+  {
+    f32x2 f[V / 2];
+    Pairs<T>::unpack(ld_keep(x + (long long)vc * V), f);  // row 0 of this lane's channels
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      shift[i] = f[i];
+      s1[i] = s2[i] = splat2(0.f);
+    }
+  }
+  // Without dynamic claims the list is complete already, and the chunks that will stay in shared
+  // memory (the last `stages`) are known: they are never read from L2 again, so they are loaded
+  // with the evict-first hint and leave L2 to the chunks that are.
+  int keep_until = 0x7fffffff;
+  if (!(dynamic & 1)) {
+    const int listed = *reinterpret_cast<volatile int*>(&q_count) - 1;
+    keep_until = listed - stages;
+  }
+  for (int k = 0; k < stages; ++k) {  // fill the ring
+    const int id = block_id(k);
+    if (id < 0) {
+      if (id == -2) failed = true;
+      n_chunks = k;
+      break;
+    }
+    if (lane == 0) issue(id, k, k < keep_until ? keep_policy : drop_policy);
+    if (chunk_vecs(id) > 0) busy_bits |= 1u << k;
+  }
+  {
+    int slot = 0;
+    for (int k = 0; k < n_chunks && !failed; ++k) {
+      const int id = block_id(k);  // present: it was read when the copy was started
+      const int nv = chunk_vecs(id);
+      if (nv > 0) {
+        const bool arrived = __all_sync(0xffffffffu, mbar_wait(&full[slot], (phase_bits >> slot) & 1u));
+        if (!arrived) {
+          failed = true;
+          break;
+        }
+        phase_bits ^= 1u << slot;
+        busy_bits &= ~(1u << slot);
+        const uint4* src = reinterpret_cast<const uint4*>(ring + (size_t)slot * CHUNK_BYTES);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (u * 32 + lane < nv) {
+            f32x2 f[V / 2];
+            Pairs<T>::unpack(src[u * 32 + lane], f);
+#pragma unroll
+            for (int i = 0; i < V / 2; ++i) {
+              const f32x2 d = sub2(f[i], shift[i]);
+              s1[i] = add2(s1[i], d);
+              s2[i] = fma2(d, d, s2[i]);
+            }
+          }
+        }
+        __syncwarp();
+      }
+      if (tid == 0) producer_step(k);
+      if (k + stages < n_chunks) {  // refill the slot with the chunk `stages` further on
+        const int nid = block_id(k + stages);
+        if (nid < 0) {
+          if (nid == -2) failed = true;
+          n_chunks = k + stages;
+        } else {
+          if (lane == 0 && chunk_vecs(nid) > 0) {
+            fence_proxy_async_smem();
+            issue(nid, slot, k + stages < keep_until ? keep_policy : drop_policy);
+          }
+          if (chunk_vecs(nid) > 0) busy_bits |= 1u << slot;
+        }
+      }
+      if (++slot == stages) slot = 0;
+    }
+  }
+  auto give_up = [&]() {  // after a wait ran out: tell everyone, then wait (bounded) for this warp's copies
+    if (lane == 0) {
+      note_wait_timeout();
+      atomicExch(&p.bar[1], 1u);
+      atomicExch(&cta_failed, 1);
+      for (int s = 0; s < stages; ++s)
+        if ((busy_bits >> s) & 1u) mbar_wait(&full[s], (phase_bits >> s) & 1u);
+    }
+    busy_bits = 0;
+    __syncwarp();
+  };
+  if (failed) give_up();
+
+  B200_WMARK(1)
+  // ---- per-CTA partial sums ---------------------------------------------------------------------
+  {
+    float a1[V], a2[V];
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      unpack2(s1[i], a1[2 * i], a1[2 * i + 1]);
+      unpack2(s2[i], a2[2 * i], a2[2 * i + 1]);
+    }
+    for (int off = vpr; off < 32; off <<= 1) {  // lanes vpr apart share a vector column
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        a1[i] += __shfl_xor_sync(0xffffffffu, a1[i], off);
+        a2[i] += __shfl_xor_sync(0xffffffffu, a2[i], off);
+      }
+    }
+    // red: [32 warps][2][C]; a second, smaller table [4][2][C] follows it
+    const int C2 = 2 * p.channels;
+    if (lane < vpr) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        red[(size_t)warp * C2 + vc * V + i] = a1[i];
+        red[(size_t)warp * C2 + p.channels + vc * V + i] = a2[i];
+      }
+    }
+    __syncthreads();
+    failed = cta_failed != 0;
+    float* red4 = red + (size_t)32 * C2;
+    if (!failed) {
+      // 32 rows -> 4 rows -> 1: consecutive threads take consecutive columns (no bank conflicts)
+      for (int i = tid; i < 4 * C2; i += T_) {
+        const int q = i / C2, c = i - q * C2;
+        float a = 0.f;
+#pragma unroll
+        for (int r = 0; r < 8; ++r) a += red[(size_t)(q * 8 + r) * C2 + c];
+        red4[i] = a;
+      }
+    }
+    __syncthreads();
+    if (!failed) {
+      for (int c = tid; c < C2; c += T_) {
+        const float a = (red4[c] + red4[C2 + c]) + (red4[2 * C2 + c] + red4[3 * C2 + c]);
+        p.partials[(long long)blockIdx.x * C2 + c] = a;  // [cta][2][C]
+      }
+    }
+  }
+  B200_WMARK(2)
+  bool ok = !failed && grid_barrier(p.bar, 1u, &bar_ok);
+  B200_WMARK(3)
+
+  // ---- channel statistics (same scheme as the CTA-ring kernel) -----------------------------------
+  double* dred = reinterpret_cast<double*>(red);
+  float* stats_s = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(red) + (size_t)T_ * 16);
+  const int P = gridDim.x;
+  if (ok && p.local_stats) {
+    const int C = p.channels;
+    const int PG = T_ / C;
+    const int c = tid % C, pg = tid / C;
+    double d1 = 0.0, d2 = 0.0;
+    if (pg < PG) {
+      for (int g0 = pg; g0 < P; g0 += 12 * PG) {  // twelve pairs of loads in flight before any is used
+        float a[12], b[12];
+#pragma unroll
+        for (int u = 0; u < 12; ++u) {
+          const int g = g0 + u * PG;
+          a[u] = g < P ? __ldcg(p.partials + ((long long)g * 2) * C + c) : 0.f;
+          b[u] = g < P ? __ldcg(p.partials + ((long long)g * 2 + 1) * C + c) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 12; ++u) {
+          d1 += (double)a[u];
+          d2 += (double)b[u];
+        }
+      }
+      dred[((size_t)pg * C + c) * 2] = d1;
+      dred[((size_t)pg * C + c) * 2 + 1] = d2;
+    }
+    __syncthreads();
+    if (tid < C) {
+      double t1 = 0.0, t2 = 0.0;
+      for (int g = 0; g < PG; ++g) {
+        t1 += dred[((size_t)g * C + tid) * 2];
+        t2 += dred[((size_t)g * C + tid) * 2 + 1];
+      }
+      float mean, invstd;
+      bn_channel_stats(p, tid, t1, t2, stat_shift, blockIdx.x == 0, &mean, &invstd);
+      stats_s[tid] = mean;
+      stats_s[C + tid] = invstd;
+    }
+    __syncthreads();
+  } else if (ok) {
+    for (int c = blockIdx.x; c < p.channels; c += P) {
+      double d1 = 0.0, d2 = 0.0;
+      for (int g = tid; g < P; g += T_) {
+        d1 += (double)__ldcg(p.partials + ((long long)g * 2) * p.channels + c);
+        d2 += (double)__ldcg(p.partials + ((long long)g * 2 + 1) * p.channels + c);
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+        d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+      }
+      if (lane == 0) {
+        dred[warp * 2] = d1;
+        dred[warp * 2 + 1] = d2;
+      }
+      __syncthreads();
+      if (tid == 0) {
+        double t1 = 0.0, t2 = 0.0;
+        for (int w = 0; w < 32; ++w) {
+          t1 += dred[w * 2];
+          t2 += dred[w * 2 + 1];
+        }
+        float mean, invstd;
+        bn_channel_stats(p, c, t1, t2, Elem<T>::to_f32(__ldg(x + c)), true, &mean, &invstd);
+        p.stats[c] = mean;
+        p.stats[p.channels + c] = invstd;
+      }
+      __syncthreads();
+    }
+    ok = grid_barrier(p.bar, 2u, &bar_ok);
+  }
+
+  B200_WMARK(5)
+  // ---- pass 2: normalise, chunks in reverse order -------------------------------------------------
+  if (ok && p.y && n_chunks > 0) {
+    f32x2 mean2[V / 2], inv2[V / 2], w2[V / 2], b2[V / 2];
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      const int c = vc * V + 2 * i;
+      if (p.local_stats) {
+        mean2[i] = pack2(stats_s[c], stats_s[c + 1]);
+        inv2[i] = pack2(stats_s[p.channels + c], stats_s[p.channels + c + 1]);
+      } else {
+        mean2[i] = pack2(__ldcg(p.stats + c), __ldcg(p.stats + c + 1));
+        inv2[i] = pack2(__ldcg(p.stats + p.channels + c), __ldcg(p.stats + p.channels + c + 1));
+      }
+      w2[i] = p.weight ? pack2(load_param1(p.weight, p.w_dtype, c), load_param1(p.weight, p.w_dtype, c + 1))
+                       : splat2(1.f);
+      b2[i] = p.bias ? pack2(load_param1(p.bias, p.w_dtype, c), load_param1(p.bias, p.w_dtype, c + 1))
+                     : splat2(0.f);
+    }
+    const int* ids = q_ids;  // complete and final by now
+    const int resident_from = n_chunks - (n_chunks < stages ? n_chunks : stages);  // chunks >= this are in smem
+    int slot = (n_chunks - 1) % stages;
+    for (int k = n_chunks - 1; k >= 0; --k) {
+      const int id = ids[k];
+      const int nv = chunk_vecs(id);
+      if (nv > 0) {
+        if (k < resident_from) {
+          const bool arrived = __all_sync(0xffffffffu, mbar_wait(&full[slot], (phase_bits >> slot) & 1u));
+          if (!arrived) {
+            failed = true;
+            break;
+          }
+          phase_bits ^= 1u << slot;
+          busy_bits &= ~(1u << slot);
+        }
+        const uint4* src = reinterpret_cast<const uint4*>(ring + (size_t)slot * CHUNK_BYTES);
+        uint4* dst = reinterpret_cast<uint4*>(p.y) + chunk_first(id);
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+          if (u * 32 + lane < nv) {
+            f32x2 f[V / 2], o[V / 2];
+            Pairs<T>::unpack(src[u * 32 + lane], f);
+#pragma unroll
+            for (int i = 0; i < V / 2; ++i) o[i] = add2(mul2(mul2(sub2(f[i], mean2[i]), inv2[i]), w2[i]), b2[i]);
+            uint4 packed = Pairs<T>::pack(o);
+            if (p.relu) {  // ReLU after the cast, as the graph has it; NaN stays NaN
+              if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+                const __nv_bfloat162 z = __float2bfloat162_rn(0.f);
+                uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  __nv_bfloat162 h = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&w[i]), z);
+                  w[i] = *reinterpret_cast<uint32_t*>(&h);
+                }
+              } else if constexpr (std::is_same<T, __half>::value) {
+                const __half2 z = __float2half2_rn(0.f);
+                uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  __half2 h = __hmax2_nan(*reinterpret_cast<__half2*>(&w[i]), z);
+                  w[i] = *reinterpret_cast<uint32_t*>(&h);
+                }
+              } else {
+                float* w = reinterpret_cast<float*>(&packed);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) w[i] = w[i] < 0.f ? 0.f : w[i];  // NaN < 0 is false: NaN stays
+              }
+            }
+            st_stream(dst + u * 32 + lane, packed);
+          }
+        }
+        __syncwarp();
+      }
+      if (k - stages >= 0) {  // the slot takes the chunk `stages` before this one
+        const int nid = ids[k - stages];
+        if (chunk_vecs(nid) > 0) {
+          if (lane == 0) {
+            fence_proxy_async_smem();
+            issue(nid, slot, drop_policy);
+          }
+          busy_bits |= 1u << slot;
+        }
+      }
+      if (--slot < 0) slot = stages - 1;
+    }
+    if (failed) give_up();
+  }
+  B200_WMARK(6)
+  grid_barrier_depart(p.bar);
+}
+
+// ----------------------------------------------------------------------------------------------
 // General path: x addressed as (n, c, s) with arbitrary strides.
 // ----------------------------------------------------------------------------------------------
 // Geometry of the fused kernel for vpr = C / V vector columns: CTA size (a multiple of both vpr
@@ -564,6 +1015,91 @@ __global__ void __launch_bounds__(256) batch_norm_apply_general_kernel(const Bat
   }
 }
 
+// B200_BN_CTA_RING=1 keeps the CTA-wide ring for every shape (for measurements).
+static bool warp_rings_disabled() {
+  static const bool off = [] {
+    const char* e = getenv("B200_BN_CTA_RING");
+    return e && e[0] == '1';
+  }();
+  return off;
+}
+
+// B200_BN_DYNAMIC=1: CTAs claim blocks from a global counter instead of a fixed list. A few
+// percent faster, but which CTA sums which block then varies from run to run, and with it the
+// last bits of the statistics. Off by default: results are bit-reproducible.
+static bool bn_dynamic_blocks() {
+  static const bool on = [] {
+    const char* e = getenv("B200_BN_DYNAMIC");
+    return e && e[0] == '1';
+  }();
+  return on;
+}
+
+// Per-warp-ring launch; returns false when the shape does not fit (the CTA-ring kernel takes it).
+template <typename T>
+static bool try_launch_batch_norm_warp(BatchNormParams p, size_t scratch_bytes, cudaStream_t st, int* rc) {
+  constexpr int V = Elem<T>::V;
+  const DeviceInfo& dev = device_info();
+  const int threads = 1024;
+  const long long total_vecs = p.rows * (p.channels / V);
+  long long grid = dev.sm_count;
+  const long long stats_floats = 2LL * p.channels;
+  const long long need = 256 + (grid * 2 * p.channels + stats_floats) * (long long)sizeof(float);
+  if ((long long)scratch_bytes < need) return false;  // the caller's path reports the shortage
+  // reduction area: [32 + 4][2][C] fp32, later reused for the fp64 combine + the CTA's stats table
+  size_t red_bytes = 2ull * 36 * p.channels * sizeof(float);
+  const size_t stats_area = (size_t)threads * 16 + 2ull * p.channels * sizeof(float);
+  if (red_bytes < stats_area) red_bytes = stats_area;
+  red_bytes = (red_bytes + 127) / 128 * 128;
+  p.local_stats = (p.channels <= threads && (long long)p.channels * grid <= 32768) ? 1 : 0;
+  const size_t barrier_bytes = 32 * 8 * sizeof(uint64_t);
+  const size_t budget = (size_t)dev.max_smem_optin - 1024;  // static shared variables
+  if (budget < red_bytes + barrier_bytes + 32 * 2 * 1024) return false;
+  const size_t per_warp = (budget - red_bytes - barrier_bytes) / 32;
+  // 2 KB chunks when three or more fit, else 1 KB chunks
+  const bool big = per_warp >= 3 * 2048;
+  const size_t chunk = big ? 2048 : 1024;
+  int stages = (int)(per_warp / chunk);
+  if (stages > 8) stages = 8;
+  if (stages < 2) return false;
+  const size_t smem = 32 * (size_t)stages * chunk + red_bytes + barrier_bytes;
+  // a block = 32 chunks (one per warp); CTAs take blocks dynamically, the queue holds BN_QUEUE of them
+  const long long block_vecs = 32LL * (long long)(chunk / 16);
+  const long long nblocks = (total_vecs + block_vecs - 1) / block_vecs;
+  if (grid > nblocks) grid = nblocks;
+  if (grid < 1) grid = 1;
+  // the queue must hold a CTA's whole list when it is fixed, and four times the average otherwise
+  const long long per_cta = (nblocks + grid - 1) / grid;
+  if (per_cta > (bn_dynamic_blocks() ? BN_QUEUE / 4 : BN_QUEUE - 2) || nblocks > 0x3fffffffLL) return false;
+  {
+    const long long need2 = 256 + (grid * 2 * p.channels + stats_floats) * (long long)sizeof(float);
+    if ((long long)scratch_bytes < need2) return false;
+    p.local_stats = (p.channels <= threads && (long long)p.channels * grid <= 32768) ? 1 : 0;
+  }
+  const void* kernel = big ? reinterpret_cast<const void*>(batch_norm_cl_warp_kernel<T, 4>)
+                           : reinterpret_cast<const void*>(batch_norm_cl_warp_kernel<T, 2>);
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  p.rows_per_cta = 0;
+  p.smem_tiles = stages;
+  p.stats = p.partials + grid * 2 * p.channels;
+  int stages_arg = stages, red_bytes_arg = (int)red_bytes, nblocks_arg = (int)nblocks;
+  int dynamic_arg = (bn_dynamic_blocks() ? 1 : 0) | (getenv("B200_BN_EVICT_LAST") ? 2 : 0);
+  void* args[] = {&p, &stages_arg, &red_bytes_arg, &nblocks_arg, &dynamic_arg};
+  e = cudaLaunchCooperativeKernel(kernel, dim3((unsigned)grid), dim3(threads), args, smem, st);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    *rc = fail((int)e, "b200_batch_norm_fwd: cooperative launch failed: %s", cudaGetErrorString(e));
+    return true;
+  }
+  note_launch();
+  *rc = B200_OK;
+  return true;
+}
+
 template <typename T>
 static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, size_t scratch_bytes,
                              cudaStream_t st) {
@@ -572,6 +1108,10 @@ static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, size_t 
   const long long stats_floats = 2LL * p.channels;
   if (channels_last_fast) {
     const int vpr = p.channels / V;
+    if ((vpr & (vpr - 1)) == 0 && vpr <= 32 && !warp_rings_disabled()) {
+      int rc = B200_OK;
+      if (try_launch_batch_norm_warp<T>(p, scratch_bytes, st, &rc)) return rc;
+    }
     const FusedGeometry geo = fused_geometry(vpr);
     const int threads = geo.threads;
     const int rpp = threads / vpr;

@@ -190,6 +190,11 @@ __device__ __forceinline__ uint64_t l2_policy_evict_last() {
   asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
   return pol;
 }
+__device__ __forceinline__ uint64_t l2_policy_evict_normal() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {
   uint64_t pol;
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
@@ -270,7 +275,8 @@ __device__ __forceinline__ float group_reduce(float v, float* scratch) {
 // ----------------------------------------------------------------------------------------
 // Grid-wide barrier for cooperative (co-resident) launches, with a bounded wait.
 // `bar` points at four 32-bit words of global scratch that are zero before the launch:
-//   [0] arrival counter, [1] error flag, [2] departure counter, [3] unused.
+//   [0] arrival counter, [1] error flag, [2] departure counter, [3] work counter of kernels that
+//   hand out blocks dynamically (reset with the others).
 // Each use of the barrier within one launch passes the next `phase` (1, 2, ..): the arrival
 // counter only grows, and phase p completes when it reaches p * gridDim.x. Every CTA calls
 // grid_barrier_depart() once after its last barrier; the last CTA to depart puts the counters
@@ -315,6 +321,7 @@ __device__ __forceinline__ void grid_barrier_depart(unsigned int* bar) {
       // The error flag is left alone on purpose.
       atomicExch(&bar[0], 0u);
       atomicExch(&bar[2], 0u);
+      atomicExch(&bar[3], 0u);
       __threadfence();
     }
   }
