@@ -200,9 +200,11 @@ norm_fwd_stream_kernel(const NormFwdParams p, const int stages, const int contig
   __syncthreads();
 
   // Thread 0 only: start the copy of this CTA's k-th tile into stage `slot` (= k mod stages,
-  // tracked incrementally: a 64-bit modulo per tile would cost more than the tile's arithmetic).
-  auto issue = [&](long long k, int slot) {
-    const long long r0 = ((long long)blockIdx.x + k * gridDim.x) * R;
+  // tracked incrementally: a modulo per tile would cost more than the tile's arithmetic).
+  const int rows_i = (int)p.rows;  // the launcher admits fewer than 2^31 rows
+  const int num_tiles_i = (int)num_tiles, my_tiles_i = (int)my_tiles;
+  auto issue = [&](int k, int slot) {
+    const long long r0 = ((long long)blockIdx.x + (long long)k * gridDim.x) * R;
     const long long left = p.rows - r0;
     const uint32_t rows_here = (uint32_t)(left < R ? left : R);
     uint64_t* bar = &full[slot];
@@ -215,16 +217,34 @@ norm_fwd_stream_kernel(const NormFwdParams p, const int stages, const int contig
         bulk_load(dst + (size_t)r * row_bytes, xg + (r0 + r) * p.x_row_stride, row_bytes, bar);
     }
   };
-  long long issued = 0;
+  (void)num_tiles_i;
+  int issued = 0;
   int issue_slot = 0;  // stage the next copy goes to
   if (threadIdx.x == 0) {
-    for (; issued < my_tiles && issued < stages; ++issued) issue(issued, (int)issued);
-    issue_slot = (int)(issued % stages);
+    for (; issued < my_tiles_i && issued < stages; ++issued) issue(issued, issued);
+    issue_slot = issued % stages;
   }
+
+  // Everything a tile needs that does not change from tile to tile is set up here, as 32-bit
+  // shared-memory addresses and one running output pointer: the per-tile code is then loads at
+  // [register + constant], arithmetic and stores.
+  const uint32_t x_lane = smem_u32(smem) + (uint32_t)grp * row_bytes + (uint32_t)lane * 16u;
+  uint32_t w_lane[PLANES], b_lane[PLANES];
+#pragma unroll
+  for (int q = 0; q < PLANES; ++q) {
+    w_lane[q] = smem_u32(wsm) + ((uint32_t)q * nv + lane) * 16u;
+    b_lane[q] = smem_u32(bsm) + ((uint32_t)q * nv + lane) * 16u;
+  }
+  const bool has_w = p.w != nullptr, has_b = p.b != nullptr, has_y = p.y != nullptr, rms = p.rms != 0;
+  const int row_step = (int)gridDim.x * R;
+  int row = (int)blockIdx.x * R + grp;
+  Tout* yrow = reinterpret_cast<Tout*>(p.y) + (long long)row * p.y_row_stride + (long long)lane * V;
+  const long long y_step = (long long)row_step * p.y_row_stride;
 
   int st = 0;           // stage of tile k
   uint32_t phase = 0;   // parity of that stage's current use
-  for (long long k = 0; k < my_tiles; ++k) {
+  uint32_t x_stage = x_lane;
+  for (int k = 0; k < my_tiles_i; ++k, row += row_step, yrow += y_step) {
     const bool arrived = mbar_wait(&full[st], phase);
     if (!__syncthreads_and(arrived)) {
       // A copy did not complete within the bound: stop streaming. Thread 0 waits (bounded) for
@@ -233,7 +253,7 @@ norm_fwd_stream_kernel(const NormFwdParams p, const int stages, const int contig
         note_wait_timeout();
         int ds = st;
         uint32_t dp = phase;
-        for (long long d = k; d < issued; ++d) {
+        for (int d = k; d < issued; ++d) {
           mbar_wait(&full[ds], dp);
           if (++ds == stages) { ds = 0; dp ^= 1u; }
         }
@@ -241,37 +261,28 @@ norm_fwd_stream_kernel(const NormFwdParams p, const int stages, const int contig
       return;
     }
     // Everyone has passed the barrier, so everyone is done with tile k-1: refill its stage.
-    if (threadIdx.x == 0 && k >= 1 && issued < my_tiles) {
+    if (threadIdx.x == 0 && k >= 1 && issued < my_tiles_i) {
       fence_proxy_async_smem();
       issue(issued, issue_slot);
       ++issued;
       if (++issue_slot == stages) issue_slot = 0;
     }
-
-    const long long row = ((long long)blockIdx.x + k * gridDim.x) * R + grp;
-    const bool valid = row < p.rows;
-    const unsigned char* rowbase = smem + (size_t)st * tile_bytes + (size_t)grp * row_bytes;
+    const bool valid = row < rows_i;
 
     f32x2 v[CH][V / 2];
-    f32x2 s2 = splat2(0.f);
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
-      const int j = c * G + lane;
-      float f[V];
-      if (EXACT || j < nv) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(rowbase + (size_t)j * 16);
-        Elem<Tin>::unpack(raw, f);
+      if (EXACT || c * G + lane < nv) {
+        Pairs<Tin>::unpack(lds128(x_stage + (uint32_t)(c * G * 16)), v[c]);
       } else {
 #pragma unroll
-        for (int i = 0; i < V; ++i) f[i] = 0.f;
+        for (int i = 0; i < V / 2; ++i) v[c][i] = splat2(0.f);
       }
-#pragma unroll
-      for (int i = 0; i < V / 2; ++i) v[c][i] = pack2(f[2 * i], f[2 * i + 1]);
     }
     // one short chain per slot, combined afterwards: a single chain over the whole row would
     // serialise on the add latency
     f32x2 part[CH];
-    if (p.rms) {
+    if (rms) {
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
         part[c] = mul2(v[c][0], v[c][0]);
@@ -286,15 +297,13 @@ norm_fwd_stream_kernel(const NormFwdParams p, const int stages, const int contig
         for (int i = 1; i < V / 2; ++i) part[c] = add2(part[c], v[c][i]);
       }
     }
-    s2 = part[0];
+    f32x2 s2 = part[0];
 #pragma unroll
     for (int c = 1; c < CH; ++c) s2 = add2(s2, part[c]);
-    float sa, sb;
-    unpack2(s2, sa, sb);
-    const float s = greduce<SumOp, G>(sa + sb, nullptr);
+    const float s = greduce<SumOp, G>(hsum2(s2), nullptr);
 
     float mean = 0.f, var, rstd;
-    if (p.rms) {
+    if (rms) {
       var = s * p.inv_n;
       rstd = precise_rsqrt(var + p.eps);
     } else {
@@ -314,9 +323,7 @@ norm_fwd_stream_kernel(const NormFwdParams p, const int stages, const int contig
       f32x2 q2 = part[0];
 #pragma unroll
       for (int c = 1; c < CH; ++c) q2 = add2(q2, part[c]);
-      float qa, qb;
-      unpack2(q2, qa, qb);
-      const float q = greduce<SumOp, G>(qa + qb, nullptr);
+      const float q = greduce<SumOp, G>(hsum2(q2), nullptr);
       var = q * p.inv_denom;
       rstd = precise_rsqrt(var + p.eps);
     }
@@ -325,42 +332,41 @@ norm_fwd_stream_kernel(const NormFwdParams p, const int stages, const int contig
       if (p.rstd_out) p.rstd_out[row] = rstd;
       if (p.var_out) p.var_out[row] = var;
     }
-    if (p.y != nullptr && valid) {
-      Tout* y = reinterpret_cast<Tout*>(p.y) + row * p.y_row_stride;
+    if (has_y && valid) {
       const f32x2 rstd2 = splat2(rstd);
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
-        const int j = c * G + lane;
-        if (EXACT || j < nv) {
+        if (EXACT || c * G + lane < nv) {
           f32x2 o[V / 2];
 #pragma unroll
           for (int i = 0; i < V / 2; ++i) o[i] = mul2(v[c][i], rstd2);
-          if (p.w) {
+          if (has_w) {
 #pragma unroll
             for (int q = 0; q < PLANES; ++q) {
-              const float4 w4 = *reinterpret_cast<const float4*>(wsm + ((size_t)q * nv + j) * 4);
-              o[2 * q] = mul2(o[2 * q], pack2(w4.x, w4.y));
-              o[2 * q + 1] = mul2(o[2 * q + 1], pack2(w4.z, w4.w));
+              f32x2 w2[2];
+              Pairs<float>::unpack(lds128(w_lane[q] + (uint32_t)(c * G * 16)), w2);
+              o[2 * q] = mul2(o[2 * q], w2[0]);
+              o[2 * q + 1] = mul2(o[2 * q + 1], w2[1]);
             }
           }
-          if (p.b) {
+          if (has_b) {
 #pragma unroll
             for (int q = 0; q < PLANES; ++q) {
-              const float4 b4 = *reinterpret_cast<const float4*>(bsm + ((size_t)q * nv + j) * 4);
-              o[2 * q] = add2(o[2 * q], pack2(b4.x, b4.y));
-              o[2 * q + 1] = add2(o[2 * q + 1], pack2(b4.z, b4.w));
+              f32x2 b2[2];
+              Pairs<float>::unpack(lds128(b_lane[q] + (uint32_t)(c * G * 16)), b2);
+              o[2 * q] = add2(o[2 * q], b2[0]);
+              o[2 * q + 1] = add2(o[2 * q + 1], b2[1]);
             }
           }
-          float of[V];
-#pragma unroll
-          for (int i = 0; i < V / 2; ++i) unpack2(o[i], of[2 * i], of[2 * i + 1]);
-          store_converted<Tout, V>(y + (long long)j * V, of);
+          store_pairs<Tout, V>(yrow + c * G * V, o);
         }
       }
     }
+    x_stage += tile_bytes;
     if (++st == stages) {
       st = 0;
       phase ^= 1u;
+      x_stage = x_lane;
     }
   }
 }
@@ -395,20 +401,25 @@ static bool try_launch_norm_fwd_stream(const NormFwdParams& p, cudaStream_t st, 
   const long long nv = p.n / V;
   int g, ch;
   if (streaming_disabled() || !pick_stream_geometry(nv, &g, &ch)) return false;
+  if (p.rows > 0x7ffff000LL) return false;  // the kernel counts rows and tiles in 32 bits
   const long long total_bytes = p.rows * nv * 16;
   if (total_bytes < (8ll << 20)) return false;  // small problems: the resident kernel is fine
   const DeviceInfo& dev = device_info();
-  const int threads = 256;
+  static const int threads_env = [] { const char* e = getenv("B200_NF_THREADS"); return e ? atoi(e) : 0; }();
+  // 128 threads: eight small CTAs per SM keep each other busy across the per-tile barrier better than
+  // four of 256 (measured on the 32768 x 768 bf16 case: 18.3 us against 19.7 us)
+  const int threads = threads_env ? threads_env : 128;
+  const int ctas_per_sm = 1024 / threads;
   const int R = threads / g;
   const size_t tile_bytes = (size_t)R * nv * 16;
   const size_t fixed = 2 * (size_t)nv * V * sizeof(float) + 8 * sizeof(uint64_t);
-  const size_t per_cta = ((size_t)dev.max_smem_optin - 4096) / 4;  // four CTAs per SM
+  const size_t per_cta = ((size_t)dev.max_smem_optin - 1024 * ctas_per_sm) / ctas_per_sm;
   if (fixed + 2 * tile_bytes > per_cta) return false;
   int stages = (int)((per_cta - fixed) / tile_bytes);
   if (stages > 8) stages = 8;
   const size_t smem = (size_t)stages * tile_bytes + fixed;
   const long long num_tiles = (p.rows + R - 1) / R;
-  long long grid = 4ll * dev.sm_count;
+  long long grid = (long long)ctas_per_sm * dev.sm_count;
   if (grid > num_tiles) grid = num_tiles;
   const int contiguous = p.x_row_stride == p.n ? 1 : 0;
   const bool exact = nv == (long long)g * ch;

@@ -251,6 +251,24 @@ __device__ __forceinline__ void store_converted(Tout* p, const float (&f)[N]) {
   }
 }
 
+// store_converted for values held as packed pairs (N values = N/2 pairs).
+template <typename Tout, int N>
+__device__ __forceinline__ void store_pairs(Tout* p, const f32x2 (&v)[N / 2]) {
+  if constexpr (sizeof(Tout) == 4) {
+#pragma unroll
+    for (int i = 0; i < N / 4; ++i) {
+      const f32x2 two[2] = {v[2 * i], v[2 * i + 1]};
+      st_stream(reinterpret_cast<float*>(p) + 4 * i, Pairs<float>::pack(two));
+    }
+  } else if constexpr (N == 8) {
+    st_stream(p, Pairs<Tout>::pack(v));
+  } else {
+    static_assert(N == 4, "unexpected vector length");
+    const uint32_t w0 = Pairs<Tout>::narrow(v[0]), w1 = Pairs<Tout>::narrow(v[1]);
+    asm volatile("st.global.cs.v2.u32 [%0], {%1,%2};" ::"l"(p), "r"(w0), "r"(w1) : "memory");
+  }
+}
+
 // Load N consecutive parameter values (weight, bias) whose dtype is only known at run time.
 // These operands are tiny and shared by every row, so they come through L1 (ld_keep).
 // `p` + idx must be aligned to min(16, N * element size).
