@@ -182,8 +182,25 @@ __device__ __forceinline__ float hsum2(f32x2 v) {
   return a + b;
 }
 
-// Natural exponential of a pair, for results that are rounded to a 16-bit type afterwards.
-// y = x*log2(e) is split into its rounded value yh and the exact rounding residual plus the
+// Natural exponential of a pair as 2^(x * log2 e) with the hardware approximation, for results that
+// are rounded to a 16-bit type afterwards (this is also what Triton's tl.exp lowers to). Relative
+// error <= 2^-22 + |x * log2 e| * 2^-24 * ln 2: below 1.3e-6 wherever an fp16 result is not zero
+// (x > -17) and below 6e-6 over the whole bf16 range, i.e. at least 80 times finer than half an
+// ulp of the output type. The two halves go through the special-function unit inside one asm
+// block so that they are read from and written to an aligned register pair directly.
+// .ftz: results below 2^-126 become 0 instead of denormals; nothing a 16-bit output or the row sum
+// can see.
+__device__ __forceinline__ f32x2 exp_pair_fast(f32x2 x) {
+  const f32x2 y = mul2(x, splat2(1.4426950216293335f));
+  f32x2 r;
+  asm("{\n\t.reg .f32 a, b, pa, pb;\n\tmov.b64 {a,b}, %1;\n\tex2.approx.ftz.f32 pa, a;\n\t"
+      "ex2.approx.ftz.f32 pb, b;\n\tmov.b64 %0, {pa,pb};\n\t}"
+      : "=l"(r) : "l"(y));
+  return r;
+}
+
+// The same with the rounding of x*log2(e) compensated (build with -DB200_SOFTMAX_COMPENSATED_EXP to
+// use it for 16-bit softmax outputs): y = x*log2(e) is split into its rounded value yh and the exact rounding residual plus the
 // low part of the constant (el); 2^yh comes from the hardware approximation (relative error
 // 2^-22) and is corrected by the factor (1 + el*ln 2). Relative error below 3e-7 over the whole
 // fp32 range, i.e. the accuracy class of expf, and three orders of magnitude below half a

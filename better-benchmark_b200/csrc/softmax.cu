@@ -81,14 +81,18 @@ struct Pair<float> {  // never instantiated for arithmetic; keeps the packed bra
 
 // Final phases shared by both prologues. v holds this thread's fp32 logits as packed pairs.
 // FASTEXP (16-bit outputs) uses the compensated pair exponential; fp32 outputs use expf.
-template <typename Tout, int CH, int V, int G, bool FASTEXP>
+template <typename Tout, int CH, int V, int G, bool FASTEXP, bool EXACT = false>
 __device__ __forceinline__ void softmax_finish(f32x2 (&v)[CH][V / 2], float mx, float mx_raw, Tout* y, int nv,
                                                int lane, int gs, bool log_mode, bool valid, float* red) {
   const f32x2 mx2 = splat2(mx);
   f32x2 s2 = splat2(0.f);
   auto exp_pair = [](f32x2 d) {
     if constexpr (FASTEXP) {
+#ifdef B200_SOFTMAX_COMPENSATED_EXP
       return exp2_pair_compensated(d);
+#else
+      return exp_pair_fast(d);
+#endif
     } else {
       float a, b;
       unpack2(d, a, b);
@@ -98,26 +102,30 @@ __device__ __forceinline__ void softmax_finish(f32x2 (&v)[CH][V / 2], float mx, 
   if (log_mode) {  // keep x - max (it may be -inf); the exponentials only feed the sum
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
-      if (c * gs < nv) {  // group-uniform: skip slots no lane uses
+      if (EXACT || c * gs < nv) {  // group-uniform: skip slots no lane uses
 #pragma unroll
         for (int i = 0; i < V / 2; ++i) {
           v[c][i] = sub2(v[c][i], mx2);
+#ifdef B200_SOFTMAX_COMPENSATED_EXP
           if constexpr (FASTEXP) {
             float a, b;
             unpack2(v[c][i], a, b);
-            a = a < -1e38f ? -1e38f : a;  // finite argument for the pair exponential, NaN kept
+            a = a < -1e38f ? -1e38f : a;  // finite argument for the compensated exponential, NaN kept
             b = b < -1e38f ? -1e38f : b;
             s2 = add2(s2, exp_pair(pack2(a, b)));
           } else {
             s2 = add2(s2, exp_pair(v[c][i]));
           }
+#else
+          s2 = add2(s2, exp_pair(v[c][i]));
+#endif
         }
       }
     }
   } else {
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
-      if (c * gs < nv) {
+      if (EXACT || c * gs < nv) {
 #pragma unroll
         for (int i = 0; i < V / 2; ++i) {
           v[c][i] = exp_pair(sub2(v[c][i], mx2));
@@ -137,33 +145,30 @@ __device__ __forceinline__ void softmax_finish(f32x2 (&v)[CH][V / 2], float mx, 
   } else {
     k2 = splat2(__frcp_rn(s));
   }
+  if (!valid) return;
+  Tout* yl = y + (long long)lane * V;  // slot c of this lane starts c * gs vectors further on
 #pragma unroll
   for (int c = 0; c < CH; ++c) {
-    const int j = c * gs + lane;
-    if (j < nv && valid) {
-      float o[V];
+    if (EXACT || c * gs + lane < nv) {
+      f32x2 o[V / 2];
 #pragma unroll
       for (int i = 0; i < V / 2; ++i) {
-        f32x2 r;
         if (log_mode) {
-          r = sub2(v[c][i], k2);
-          unpack2(r, o[2 * i], o[2 * i + 1]);
+          o[i] = sub2(v[c][i], k2);
         } else if constexpr (sizeof(Tout) == 4) {
           float a, b;
           unpack2(v[c][i], a, b);
-          o[2 * i] = a / s;
-          o[2 * i + 1] = b / s;
+          o[i] = pack2(a / s, b / s);
         } else {
-          r = mul2(v[c][i], k2);
-          unpack2(r, o[2 * i], o[2 * i + 1]);
+          o[i] = mul2(v[c][i], k2);
         }
       }
-      store_converted<Tout, V>(y + (long long)j * V, o);
+      store_pairs<Tout, V>(yl + (long long)c * gs * V, o);
     }
   }
 }
 
-template <typename Tin, typename Tout, int CH, int G, bool PACKED>
+template <typename Tin, typename Tout, int CH, int G, bool PACKED, bool EXACT = false>
 __global__ void __launch_bounds__(G == 0 ? 512 : 256)
 softmax_resident_kernel(const SoftmaxParams p) {
   constexpr int V = Elem<Tin>::V;
@@ -180,24 +185,31 @@ softmax_resident_kernel(const SoftmaxParams p) {
   Tout* y = reinterpret_cast<Tout*>(p.y) + row_offset(p.ymap, row);
   const int nv = p.n / V;
 
+  // slot c of this lane starts c * gs vectors after the lane's first one: one pointer per tensor,
+  // constant offsets per slot (gs is a compile-time constant for sub-warp and warp groups)
+  const Tin* xl = x + (long long)lane * V;
+  const Tin* ml = m ? m + (long long)lane * V : nullptr;
   uint4 raw[CH];
 #pragma unroll
   for (int c = 0; c < CH; ++c) {
-    const int j = c * gs + lane;
-    if (j < nv) raw[c] = ld_stream(x + (long long)j * V);
+    if (EXACT || c * gs + lane < nv) raw[c] = ld_stream(xl + (long long)c * gs * V);
   }
 
   f32x2 v[CH][V / 2];
   float mx = -INFINITY;
 
-  // The pair exponential needs finite arguments (inf - inf inside its compensation step would
+  // The compensated pair exponential (optional build) needs finite arguments (inf - inf inside its compensation step would
   // give NaN where exp(-inf) is 0): logits are clamped to a finite floor AFTER the row maximum was
   // taken from the unclamped values. A row whose maximum is -inf (fully masked with -inf) makes
   // aten return NaN for the whole row; the same happens here through the sum (see below).
   constexpr float kFloor = sizeof(Tin) == 2 && !std::is_same<Tin, __nv_bfloat16>::value ? -60000.f : -1e38f;
   // log_softmax returns x - max - log(sum) itself, which may legitimately be -inf: there only the
   // exponential's argument is clamped (in softmax_finish), not the stored value.
+#ifdef B200_SOFTMAX_COMPENSATED_EXP
   const bool clamp_now = FASTEXP && !p.log_mode;
+#else
+  const bool clamp_now = false;  // 2^(-inf) is 0 in the plain exponential: nothing to protect
+#endif
   if constexpr (PACKED && sizeof(Tin) == 2) {
     using P2 = typename Pair<Tin>::type;
     const P2 neg_inf = Pair<Tin>::splat(-INFINITY);
@@ -213,9 +225,8 @@ softmax_resident_kernel(const SoftmaxParams p) {
       const P2 s2 = Pair<Tin>::splat(p.scale);
 #pragma unroll
       for (int c = 0; c < CH; ++c) {
-        const int j = c * gs + lane;
         P2 t[4];
-        if (j < nv) {
+        if (EXACT || c * gs + lane < nv) {
           const uint32_t w[4] = {raw[c].x, raw[c].y, raw[c].z, raw[c].w};
 #pragma unroll
           for (int i = 0; i < 4; ++i) t[i] = *reinterpret_cast<const P2*>(&w[i]);
@@ -230,7 +241,7 @@ softmax_resident_kernel(const SoftmaxParams p) {
             }
           }
           if constexpr (HM) {
-            const uint4 mr = ld_keep(m + (long long)j * V);
+            const uint4 mr = ld_keep(ml + (long long)c * gs * V);
             const uint32_t mw[4] = {mr.x, mr.y, mr.z, mr.w};
 #pragma unroll
             for (int i = 0; i < 4; ++i) t[i] = __hadd2(t[i], *reinterpret_cast<const P2*>(&mw[i]));
@@ -243,8 +254,8 @@ softmax_resident_kernel(const SoftmaxParams p) {
         }
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const float2 f = Pair<Tin>::widen(CLAMP ? __hmax2_nan(t[i], floor2) : t[i]);  // NaN stays NaN
-          v[c][i] = pack2(f.x, f.y);
+          const P2 u = CLAMP ? __hmax2_nan(t[i], floor2) : t[i];  // NaN stays NaN
+          v[c][i] = Pairs<Tin>::word(*reinterpret_cast<const uint32_t*>(&u));
         }
       }
     };
@@ -268,9 +279,8 @@ softmax_resident_kernel(const SoftmaxParams p) {
   } else {
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
-      const int j = c * gs + lane;
       float f[V];
-      if (j < nv) {
+      if (EXACT || c * gs + lane < nv) {
         Elem<Tin>::unpack(raw[c], f);
         if (p.has_scale) {
 #pragma unroll
@@ -278,7 +288,7 @@ softmax_resident_kernel(const SoftmaxParams p) {
         }
         if (m != nullptr) {
           float mf[V];
-          Elem<Tin>::unpack(ld_keep(m + (long long)j * V), mf);
+          Elem<Tin>::unpack(ld_keep(ml + (long long)c * gs * V), mf);
 #pragma unroll
           for (int i = 0; i < V; ++i) f[i] = f[i] + mf[i];
         }
@@ -302,7 +312,7 @@ softmax_resident_kernel(const SoftmaxParams p) {
   // unclamped maximum still decides whether the whole row was -inf.
   const float mx_raw = mx;
   if (clamp_now) mx = fmaxf(mx, kFloor);
-  softmax_finish<Tout, CH, V, G, FASTEXP>(v, mx, mx_raw, y, nv, lane, gs, p.log_mode != 0, valid, red);
+  softmax_finish<Tout, CH, V, G, FASTEXP, EXACT>(v, mx, mx_raw, y, nv, lane, gs, p.log_mode != 0, valid, red);
 }
 
 // Element-wise kernel for rows that do not fit in registers or break the vector-path alignment
@@ -366,7 +376,13 @@ static int launch_softmax(const SoftmaxParams& p, bool vector_ok, cudaStream_t s
     if (!g.block) {
       const int rows_per_cta = g.threads / g.g;
       const unsigned grid = (unsigned)((p.rows + rows_per_cta - 1) / rows_per_cta);
-#define B200_SM_LAUNCH(GG, CC) softmax_resident_kernel<Tin, Tout, CC, GG, PACKED><<<grid, g.threads, 0, st>>>(p)
+#define B200_SM_LAUNCH(GG, CC)                                                                   \
+  do {                                                                                          \
+    if (GG > 0 && p.n / V == (long long)GG * CC)                                                \
+      softmax_resident_kernel<Tin, Tout, CC, GG, PACKED, (GG > 0)><<<grid, g.threads, 0, st>>>(p); \
+    else                                                                                        \
+      softmax_resident_kernel<Tin, Tout, CC, GG, PACKED, false><<<grid, g.threads, 0, st>>>(p);   \
+  } while (0)
       if (g.g == 8) {
         if (g.ch == 1) B200_SM_LAUNCH(8, 1);
         else if (g.ch == 2) B200_SM_LAUNCH(8, 2);
