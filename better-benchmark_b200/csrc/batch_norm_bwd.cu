@@ -1,0 +1,381 @@
+// BatchNorm2d training backward: per-channel sums of dy and dy * (x - mean), then
+//   dx = ((dy - (x - mean) * k) - sum_dy / N) * (invstd * w),   k = (dot / N) * invstd^2
+//   dweight = dot * invstd,   dbias = sum_dy
+// with an optional activation-backward prologue on dy (leaky ReLU with a given slope; slope 0 is
+// ReLU): dy' = act > 0 ? dy : dy * slope, rounded to the tensor dtype as the captured graphs do.
+//
+// Replaces the Triton plans of the BatchNorm-backward repros of the reference
+// (repros/canonical/sum_sum_183b124c731f/oracle.py: per-channel partial sums, finalize, apply;
+// repros/canonical/sum_sum_12fc8ebf8180/oracle.py: the same behind a leaky-ReLU backward).
+// Evaluation order as in the decomposed aten graph (sum_sum_183b124c731f/repro.py:26-50):
+//   sum_dy = sum(float(dy'));  dot = sum(float(dy') * (float(x) - mean))
+//   c1 = sum_dy * (1/N);  c2 = (dot * (1/N)) * (invstd * invstd);  gs = invstd * w
+//   dx = cast(((float(dy') - (float(x) - mean) * c2) - c1) * gs)
+//
+// Three launches: sums (a thread's own short chain in fp32, everything above it in fp64; per-CTA
+// partials over a fixed split of the rows), finalize (fixed order, coefficient table), apply. No atomics: bit-reproducible.
+// Channels-last tensors with a power-of-two number of 16-byte vectors per row take the vector
+// kernels; every other layout the strided element-wise ones.
+#include "rowwise.cuh"
+
+namespace b200 {
+
+struct BnBwdParams {
+  const void* dy;
+  const void* x;
+  const void* act;     // may be null: no prologue
+  const float* mean;   // [C]
+  const float* invstd; // [C]
+  const void* weight;  // may be null (ones)
+  int w_dtype;
+  void* dx;            // may be null: sums only
+  float* dweight;      // may be null
+  float* dbias;        // may be null
+  long long rows;      // channels-last: N*H*W; general: N
+  long long spatial;   // general: H*W
+  long long sn, sc, ss;  // general: element strides of (n, c, spatial), shared by dy, x, act, dx
+  int channels;
+  float slope;
+  float inv_count;     // 1 / (N*H*W)
+  double* partials;    // [splits][2][C]: everything above a thread's own short fp32 chain is fp64
+  float* coef;         // [4][C]: c1, c2, gs, mean
+  int splits;
+};
+
+template <typename T>
+__device__ __forceinline__ void bn_bwd_prologue(f32x2 (&g)[Elem<T>::V / 2], const uint4& act_raw, float slope) {
+  constexpr int V = Elem<T>::V;
+  f32x2 a[V / 2];
+  Pairs<T>::unpack(act_raw, a);
+  f32x2 scaled[V / 2];
+#pragma unroll
+  for (int i = 0; i < V / 2; ++i) scaled[i] = mul2(g[i], splat2(slope));
+#pragma unroll
+  for (int i = 0; i < V / 2; ++i) {
+    float a0, a1, g0, g1, s0, s1;
+    unpack2(a[i], a0, a1);
+    unpack2(g[i], g0, g1);
+    unpack2(scaled[i], s0, s1);
+    g[i] = pack2(a0 > 0.f ? g0 : s0, a1 > 0.f ? g1 : s1);
+  }
+  if constexpr (sizeof(T) == 2) {  // the graph rounds dy' to the tensor dtype before it is used
+    const uint4 r = Pairs<T>::pack(g);
+    Pairs<T>::unpack(r, g);
+  }
+}
+
+// Channels-last sums: the tensors are flat arrays of 16-byte vectors; blockDim.x is a multiple of
+// vpr, so a thread stays in one vector column. CTA b takes vectors [b*per, (b+1)*per).
+template <typename T>
+__global__ void __launch_bounds__(256) bn_bwd_sums_cl_kernel(const BnBwdParams p, long long vecs_per_cta) {
+  constexpr int V = Elem<T>::V;
+  __shared__ float red[2 * 256 * 8 / 8 * 8];  // [2][threads][V] fp32, V <= 8
+  const int tid = threadIdx.x, T_ = blockDim.x;
+  const int vpr = p.channels / V;
+  const int vc = tid % vpr;
+  const long long total = p.rows * vpr;
+  const long long v0 = (long long)blockIdx.x * vecs_per_cta;
+  long long v1 = v0 + vecs_per_cta;
+  if (v1 > total) v1 = total;
+  const uint4* dy = reinterpret_cast<const uint4*>(p.dy);
+  const uint4* x = reinterpret_cast<const uint4*>(p.x);
+  const uint4* act = reinterpret_cast<const uint4*>(p.act);
+  f32x2 mean2[V / 2], s1[V / 2], s2[V / 2];
+#pragma unroll
+  for (int i = 0; i < V / 2; ++i) {
+    mean2[i] = pack2(__ldg(p.mean + vc * V + 2 * i), __ldg(p.mean + vc * V + 2 * i + 1));
+    s1[i] = s2[i] = splat2(0.f);
+  }
+  constexpr int U = 4;  // vectors of each tensor in flight per thread
+  for (long long v = v0 + tid; v < v1; v += (long long)U * T_) {
+    uint4 rg[U], rx[U], ra[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = v + (long long)u * T_;
+      if (i < v1) {
+        rg[u] = ld_stream(reinterpret_cast<const T*>(dy + i));
+        rx[u] = ld_stream(reinterpret_cast<const T*>(x + i));
+        if (act) ra[u] = ld_stream(reinterpret_cast<const T*>(act + i));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (v + (long long)u * T_ < v1) {
+        f32x2 g[V / 2], xv[V / 2];
+        Pairs<T>::unpack(rg[u], g);
+        Pairs<T>::unpack(rx[u], xv);
+        if (act) bn_bwd_prologue<T>(g, ra[u], p.slope);
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) {
+          s1[i] = add2(s1[i], g[i]);
+          s2[i] = add2(s2[i], mul2(g[i], sub2(xv[i], mean2[i])));
+        }
+      }
+    }
+  }
+  // fold the threads of a column (tid, tid + vpr, ...) in a fixed order
+  float* r1 = red;
+  float* r2 = red + 256 * V;
+#pragma unroll
+  for (int i = 0; i < V / 2; ++i) {
+    unpack2(s1[i], r1[tid * V + 2 * i], r1[tid * V + 2 * i + 1]);
+    unpack2(s2[i], r2[tid * V + 2 * i], r2[tid * V + 2 * i + 1]);
+  }
+  __syncthreads();
+  for (int c = tid; c < p.channels; c += T_) {
+    const int col = c / V, e = c % V;
+    double a = 0.0, b = 0.0;
+    for (int t = col; t < T_; t += vpr) {
+      a += (double)r1[t * V + e];
+      b += (double)r2[t * V + e];
+    }
+    p.partials[((long long)blockIdx.x * 2) * p.channels + c] = a;
+    p.partials[((long long)blockIdx.x * 2 + 1) * p.channels + c] = b;
+  }
+}
+
+// One warp per channel: fp64 combination of the partials, outputs and the coefficient table.
+__global__ void __launch_bounds__(256) bn_bwd_finalize_kernel(const BnBwdParams p) {
+  const int lane = threadIdx.x & 31;
+  const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (c >= p.channels) return;
+  double s1 = 0.0, s2 = 0.0;
+  for (int g = lane; g < p.splits; g += 32) {
+    s1 += p.partials[((long long)g * 2) * p.channels + c];
+    s2 += p.partials[((long long)g * 2 + 1) * p.channels + c];
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s1 += __shfl_xor_sync(0xffffffffu, s1, o);
+    s2 += __shfl_xor_sync(0xffffffffu, s2, o);
+  }
+  if (lane == 0) {
+    const float sum_dy = (float)s1, dot = (float)s2;
+    const float invstd = p.invstd[c];
+    const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
+    if (p.dbias) p.dbias[c] = sum_dy;
+    if (p.dweight) p.dweight[c] = dot * invstd;
+    p.coef[c] = sum_dy * p.inv_count;
+    p.coef[p.channels + c] = (dot * p.inv_count) * (invstd * invstd);
+    p.coef[2 * p.channels + c] = invstd * w;
+    p.coef[3 * p.channels + c] = p.mean[c];
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) bn_bwd_apply_cl_kernel(const BnBwdParams p) {
+  constexpr int V = Elem<T>::V;
+  const int tid = threadIdx.x, T_ = blockDim.x;
+  const int vpr = p.channels / V;
+  const int vc = tid % vpr;
+  const long long total = p.rows * vpr;
+  const uint4* dy = reinterpret_cast<const uint4*>(p.dy);
+  const uint4* x = reinterpret_cast<const uint4*>(p.x);
+  const uint4* act = reinterpret_cast<const uint4*>(p.act);
+  uint4* dx = reinterpret_cast<uint4*>(p.dx);
+  f32x2 c1[V / 2], c2[V / 2], gs[V / 2], mean2[V / 2];
+#pragma unroll
+  for (int i = 0; i < V / 2; ++i) {
+    const int c = vc * V + 2 * i;
+    c1[i] = pack2(p.coef[c], p.coef[c + 1]);
+    c2[i] = pack2(p.coef[p.channels + c], p.coef[p.channels + c + 1]);
+    gs[i] = pack2(p.coef[2 * p.channels + c], p.coef[2 * p.channels + c + 1]);
+    mean2[i] = pack2(p.coef[3 * p.channels + c], p.coef[3 * p.channels + c + 1]);
+  }
+  constexpr int U = 2;
+  const long long stride = (long long)gridDim.x * T_;  // a multiple of vpr: the column is fixed
+  for (long long v = (long long)blockIdx.x * T_ + tid; v < total; v += U * stride) {
+    uint4 rg[U], rx[U], ra[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = v + u * stride;
+      if (i < total) {
+        rg[u] = ld_stream(reinterpret_cast<const T*>(dy + i));
+        rx[u] = ld_stream(reinterpret_cast<const T*>(x + i));
+        if (act) ra[u] = ld_stream(reinterpret_cast<const T*>(act + i));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = v + u * stride;
+      if (i < total) {
+        f32x2 g[V / 2], xv[V / 2], o[V / 2];
+        Pairs<T>::unpack(rg[u], g);
+        Pairs<T>::unpack(rx[u], xv);
+        if (act) bn_bwd_prologue<T>(g, ra[u], p.slope);
+#pragma unroll
+        for (int k = 0; k < V / 2; ++k)
+          o[k] = mul2(sub2(sub2(g[k], mul2(sub2(xv[k], mean2[k]), c2[k])), c1[k]), gs[k]);
+        st_stream(reinterpret_cast<T*>(dx + i), Pairs<T>::pack(o));
+      }
+    }
+  }
+}
+
+// ---- general layout: element-wise, (n, c, s) strides ------------------------------------------
+template <typename T>
+__device__ __forceinline__ float bn_bwd_dy_general(const BnBwdParams& p, long long off) {
+  float g = Elem<T>::to_f32(reinterpret_cast<const T*>(p.dy)[off]);
+  if (p.act) {
+    const float a = Elem<T>::to_f32(reinterpret_cast<const T*>(p.act)[off]);
+    g = a > 0.f ? g : g * p.slope;
+    g = Elem<T>::to_f32(Elem<T>::from_f32(g));
+  }
+  return g;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) bn_bwd_sums_general_kernel(const BnBwdParams p) {
+  __shared__ double red[2][8];
+  const int c = blockIdx.x;
+  const long long total = p.rows * p.spatial;
+  const long long per = (total + gridDim.y - 1) / gridDim.y;
+  const long long e0 = (long long)blockIdx.y * per;
+  const long long e1 = e0 + per < total ? e0 + per : total;
+  const float mean = p.mean[c];
+  float s1 = 0.f, s2 = 0.f;
+  for (long long e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
+    const long long n = e / p.spatial, s = e % p.spatial;
+    const long long off = n * p.sn + (long long)c * p.sc + s * p.ss;
+    const float g = bn_bwd_dy_general<T>(p, off);
+    s1 += g;
+    s2 += g * (Elem<T>::to_f32(reinterpret_cast<const T*>(p.x)[off]) - mean);
+  }
+  double d1 = (double)s1, d2 = (double)s2;  // the threads' short chains are combined in fp64
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+    d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+  }
+  if ((threadIdx.x & 31) == 0) {
+    red[0][threadIdx.x >> 5] = d1;
+    red[1][threadIdx.x >> 5] = d2;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    d1 = d2 = 0.0;
+    for (int w = 0; w < (int)(blockDim.x >> 5); ++w) {
+      d1 += red[0][w];
+      d2 += red[1][w];
+    }
+    p.partials[((long long)blockIdx.y * 2) * p.channels + c] = d1;
+    p.partials[((long long)blockIdx.y * 2 + 1) * p.channels + c] = d2;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) bn_bwd_apply_general_kernel(const BnBwdParams p) {
+  const int c = blockIdx.x;
+  const long long total = p.rows * p.spatial;
+  const long long per = (total + gridDim.y - 1) / gridDim.y;
+  const long long e0 = (long long)blockIdx.y * per;
+  const long long e1 = e0 + per < total ? e0 + per : total;
+  const float c1 = p.coef[c], c2 = p.coef[p.channels + c], gs = p.coef[2 * p.channels + c], mean = p.coef[3 * p.channels + c];
+  for (long long e = e0 + threadIdx.x; e < e1; e += blockDim.x) {
+    const long long n = e / p.spatial, s = e % p.spatial;
+    const long long off = n * p.sn + (long long)c * p.sc + s * p.ss;
+    const float g = bn_bwd_dy_general<T>(p, off);
+    const float xv = Elem<T>::to_f32(reinterpret_cast<const T*>(p.x)[off]);
+    reinterpret_cast<T*>(p.dx)[off] = Elem<T>::from_f32(((g - (xv - mean) * c2) - c1) * gs);
+  }
+}
+
+template <typename T>
+static int launch_bn_bwd(BnBwdParams p, bool fast, size_t scratch_bytes, cudaStream_t st) {
+  constexpr int V = Elem<T>::V;
+  const DeviceInfo& dev = device_info();
+  const long long coef_floats = 4LL * p.channels;
+  if (fast) {
+    const int vpr = p.channels / V;
+    const long long total = p.rows * vpr;
+    long long splits = 8LL * dev.sm_count;  // eight 256-thread CTAs per SM
+    if (splits * 256 * 4 > total) splits = (total + 256 * 4 - 1) / (256 * 4);
+    if (splits < 1) splits = 1;
+    long long per = (total + splits - 1) / splits;
+    per = (per + vpr - 1) / vpr * vpr;  // whole rows per CTA: the column of a thread stays fixed
+    splits = (total + per - 1) / per;
+    const long long need = splits * 2 * p.channels * (long long)sizeof(double) + coef_floats * (long long)sizeof(float);
+    if ((long long)scratch_bytes < need)
+      return fail(B200_ERR_WORKSPACE, "b200_batch_norm_bwd: scratch of %zu bytes, need %lld", scratch_bytes, need);
+    p.splits = (int)splits;
+    p.coef = reinterpret_cast<float*>(p.partials + splits * 2 * p.channels);
+    bn_bwd_sums_cl_kernel<T><<<(unsigned)splits, 256, 0, st>>>(p, per);
+    int rc = launch_status("b200_batch_norm_bwd sums");
+    if (rc != B200_OK) return rc;
+    bn_bwd_finalize_kernel<<<(p.channels + 7) / 8, 256, 0, st>>>(p);
+    rc = launch_status("b200_batch_norm_bwd finalize");
+    if (rc != B200_OK || !p.dx) return rc;
+    long long grid = 8LL * dev.sm_count;
+    if (grid * 256 > total) grid = (total + 255) / 256;
+    bn_bwd_apply_cl_kernel<T><<<(unsigned)grid, 256, 0, st>>>(p);
+    return launch_status("b200_batch_norm_bwd apply");
+  }
+  const long long total = p.rows * p.spatial;
+  long long splits = total / 16384;
+  if (splits < 1) splits = 1;
+  if (splits > 64) splits = 64;
+  const long long need = splits * 2 * p.channels * (long long)sizeof(double) + coef_floats * (long long)sizeof(float);
+  if ((long long)scratch_bytes < need)
+    return fail(B200_ERR_WORKSPACE, "b200_batch_norm_bwd: scratch of %zu bytes, need %lld", scratch_bytes, need);
+  p.splits = (int)splits;
+  p.coef = reinterpret_cast<float*>(p.partials + splits * 2 * p.channels);
+  bn_bwd_sums_general_kernel<T><<<dim3(p.channels, (unsigned)splits), 256, 0, st>>>(p);
+  int rc = launch_status("b200_batch_norm_bwd sums");
+  if (rc != B200_OK) return rc;
+  bn_bwd_finalize_kernel<<<(p.channels + 7) / 8, 256, 0, st>>>(p);
+  rc = launch_status("b200_batch_norm_bwd finalize");
+  if (rc != B200_OK || !p.dx) return rc;
+  bn_bwd_apply_general_kernel<T><<<dim3(p.channels, (unsigned)splits), 256, 0, st>>>(p);
+  return launch_status("b200_batch_norm_bwd apply");
+}
+
+}  // namespace b200
+
+using namespace b200;
+
+extern "C" int64_t b200_batch_norm_bwd_scratch_bytes(int64_t channels) {
+  const int sms = device_info().sm_count;
+  return (int64_t)(8 * sms > 64 ? 8 * sms : 64) * 2 * channels * (int64_t)sizeof(double) +
+         4 * channels * (int64_t)sizeof(float);
+}
+
+extern "C" int b200_batch_norm_bwd(const void* dy, const void* x, const void* act, const float* mean,
+                                   const float* invstd, const void* weight, void* dx, float* dweight,
+                                   float* dbias, int64_t batch, int64_t channels, int64_t spatial,
+                                   int64_t stride_n, int64_t stride_c, int64_t stride_s, int32_t x_dtype,
+                                   int32_t w_dtype, double slope, void* scratch, int64_t scratch_bytes,
+                                   void* stream) {
+  if (!dy || !x || !mean || !invstd) return fail(B200_ERR_INVALID, "b200_batch_norm_bwd: null argument");
+  if (batch < 0 || channels <= 0 || spatial < 0 || channels > 0x7fffffffLL)
+    return fail(B200_ERR_INVALID, "b200_batch_norm_bwd: bad sizes");
+  if (!scratch || scratch_bytes <= 0) return fail(B200_ERR_WORKSPACE, "b200_batch_norm_bwd: needs a scratch buffer");
+  if (!aligned16(scratch)) return fail(B200_ERR_ALIGNMENT, "b200_batch_norm_bwd: scratch must be 16-byte aligned");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long count = batch * spatial;
+  if (count == 0) {
+    if (dweight) cudaMemsetAsync(dweight, 0, channels * sizeof(float), st);
+    if (dbias) cudaMemsetAsync(dbias, 0, channels * sizeof(float), st);
+    return launch_status("b200_batch_norm_bwd (empty)");
+  }
+  BnBwdParams p;
+  p.dy = dy; p.x = x; p.act = act; p.mean = mean; p.invstd = invstd; p.weight = weight; p.w_dtype = w_dtype;
+  p.dx = dx; p.dweight = dweight; p.dbias = dbias;
+  p.spatial = spatial; p.sn = stride_n; p.sc = stride_c; p.ss = stride_s;
+  p.channels = (int)channels; p.slope = (float)slope;
+  p.inv_count = (float)(1.0 / (double)count);
+  p.partials = reinterpret_cast<double*>(scratch);
+  p.coef = nullptr; p.splits = 0;
+  const int eb = dtype_size(x_dtype);
+  const int v = 16 / eb;
+  const bool cl = stride_c == 1 && stride_s == channels && stride_n == spatial * channels;
+  const long long vpr = channels / v;
+  const bool fast = cl && channels % v == 0 && vpr <= 256 && (vpr & (vpr - 1)) == 0 && aligned16(dy) &&
+                    aligned16(x) && (!act || aligned16(act)) && (!dx || aligned16(dx));
+  p.rows = fast ? batch * spatial : batch;
+  switch (x_dtype) {
+    case B200_F32: return launch_bn_bwd<float>(p, fast, (size_t)scratch_bytes, st);
+    case B200_BF16: return launch_bn_bwd<__nv_bfloat16>(p, fast, (size_t)scratch_bytes, st);
+    case B200_F16: return launch_bn_bwd<__half>(p, fast, (size_t)scratch_bytes, st);
+  }
+  return fail(B200_ERR_INVALID, "b200_batch_norm_bwd: unknown dtype %d", x_dtype);
+}

@@ -381,6 +381,49 @@ def batch_norm_fwd(x: torch.Tensor, weight: torch.Tensor | None, bias: torch.Ten
     return y, mean, invstd
 
 
+def batch_norm_bwd(dy: torch.Tensor, x: torch.Tensor, mean: torch.Tensor, invstd: torch.Tensor,
+                   weight: torch.Tensor | None, *, act: torch.Tensor | None = None, slope: float = 0.0,
+                   want_dx: bool = True, scratch: torch.Tensor | None = None):
+    """BatchNorm2d training backward on dense NCHW or channels-last tensors of one layout.
+
+    Returns (dx, dweight, dbias): dx has x's dtype and strides, the other two are fp32 [C].
+    ``mean`` / ``invstd`` are the saved statistics (fp32, C elements, any shape). With ``act`` the
+    gradient first goes through the activation backward ``act > 0 ? dy : dy * slope``.
+    """
+    _require_cuda(dy, x, mean, invstd, weight, act, scratch)
+    if x.dim() != 4 or dy.shape != x.shape or dy.dtype != x.dtype or dy.stride() != x.stride():
+        raise UnsupportedLayout("batch_norm_bwd: dy and x must be 4-D with the same shape, dtype and strides")
+    if act is not None and (act.shape != x.shape or act.dtype != x.dtype or act.stride() != x.stride()):
+        raise UnsupportedLayout("batch_norm_bwd: act must match x in shape, dtype and strides")
+    n, c, h, w = x.shape
+    for t, name in ((mean, "mean"), (invstd, "invstd")):
+        if t.dtype != torch.float32 or t.numel() != c or not t.is_contiguous():
+            raise UnsupportedLayout(f"batch_norm_bwd: {name} must be contiguous fp32 with one value per channel")
+    if weight is not None and (weight.dim() != 1 or weight.shape[0] != c or not weight.is_contiguous()):
+        raise UnsupportedLayout("batch_norm_bwd: weight must be contiguous [C]")
+    sn, sc, sh, sw = x.stride()
+    if w > 1 and h > 1 and sh != sw * w:
+        raise UnsupportedLayout("batch_norm_bwd: H and W must be mergeable into one spatial dimension")
+    ss = sw if w > 1 else (sh if h > 1 else 1)
+    dx = torch.empty_strided(x.shape, x.stride(), dtype=x.dtype, device=x.device) if want_dx else None
+    dw = torch.empty(c, dtype=torch.float32, device=x.device)
+    db = torch.empty(c, dtype=torch.float32, device=x.device)
+    if x.numel() == 0:
+        dw.zero_(); db.zero_()
+        return dx, dw, db
+    lib = load()
+    need = int(lib.b200_batch_norm_bwd_scratch_bytes(c)) + 256
+    if scratch is None:
+        scratch = scratch_buffer(x.device, need)
+    usable = scratch[256:]  # the barrier words at the head of the shared buffer stay untouched
+    check(lib.b200_batch_norm_bwd(_ptr(dy), _ptr(x), _ptr(act), _ptr(mean), _ptr(invstd), _ptr(weight),
+                                  _ptr(dx), _ptr(dw), _ptr(db), n, c, h * w, sn, sc, ss, _code(x),
+                                  _code(weight) if weight is not None else F32, float(slope), _ptr(usable),
+                                  usable.numel(), _stream()),
+          "b200_batch_norm_bwd")
+    return dx, dw, db
+
+
 COL_SUM, COL_MEAN, COL_AMAX = 0, 1, 2
 _COL_CODES = {"sum": COL_SUM, "mean": COL_MEAN, "amax": COL_AMAX}
 

@@ -69,6 +69,9 @@ SIGNATURES = {
                                                      _PF, c_int64, c_int64, c_int64, c_int64, c_int64,
                                                      c_int64, c_int32, c_int32, c_double, c_double, c_int32,
                                                      c_void_p]),
+    "b200_batch_norm_bwd_scratch_bytes": (c_int64, [c_int64]),
+    "b200_batch_norm_bwd": (c_int32, [c_void_p] * 9 + [c_int64] * 6 + [c_int32, c_int32, c_double, c_void_p,
+                                                                       c_int64, c_void_p]),
     "b200_col_reduce": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
                                   c_int32, c_int32, c_int32, c_void_p, c_int64, c_void_p]),
     "b200_permute_copy": (c_int32, [c_void_p, c_void_p, _P64, _P64, c_int32, c_int32, c_double, c_int32,

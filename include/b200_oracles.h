@@ -168,6 +168,22 @@ int32_t b200_transpose_copy(const void* x, void* y, int64_t batch, int64_t rows,
 int32_t b200_cast_scale(const void* x, void* y, int64_t n, int32_t in_dtype, int32_t out_dtype, double scale,
                         int32_t has_scale, void* stream);
 
+/* BatchNorm2d training backward. dy, x, (act) and dx share the element strides (n, c, spatial);
+ * mean / invstd are the statistics saved by the forward pass (fp32 [C]). Outputs: dx (may be NULL:
+ * sums only), dweight = sum(dy * (x - mean)) * invstd and dbias = sum(dy), fp32 [C] (each may be
+ * NULL). `act` (may be NULL) enables the activation-backward prologue dy' = act > 0 ? dy : dy * slope
+ * (slope 0: ReLU), rounded to the tensor dtype. Three launches (sums, fp64 finalize, apply), no
+ * atomics. Scratch: b200_batch_norm_bwd_scratch_bytes(channels), 16-byte aligned, no initial state.
+ * Replaces sum_sum_183b124c731f/oracle.py (partial sums, finalize, apply) and, with the prologue,
+ * sum_sum_12fc8ebf8180/oracle.py. */
+int64_t b200_batch_norm_bwd_scratch_bytes(int64_t channels);
+int32_t b200_batch_norm_bwd(const void* dy, const void* x, const void* act, const float* mean,
+                            const float* invstd, const void* weight, void* dx, float* dweight,
+                            float* dbias, int64_t batch, int64_t channels, int64_t spatial,
+                            int64_t stride_n, int64_t stride_c, int64_t stride_s, int32_t x_dtype,
+                            int32_t w_dtype, double slope, void* scratch, int64_t scratch_bytes,
+                            void* stream);
+
 /* b200_batch_norm_fwd for callers that may not allocate device memory (a host framework that owns
  * the only arena and forbids plug-ins to call cudaMalloc, or a caller that owns nothing but the
  * tensors it was handed): the scratch lives in a fixed array inside the library's device image

@@ -299,3 +299,41 @@ class SpatialMean(nn.Module):
 
     def forward(self, x):
         return aten.mean.dim(x, [2, 3], True)
+
+
+class BatchNormBwd(nn.Module):
+    """BatchNorm2d training backward returning (dbias, dweight, dx), optionally behind a leaky-ReLU
+    backward on dy.
+
+    Graph: reference repros/canonical/sum_sum_183b124c731f/repro.py:26-50 (plain) and
+    repros/canonical/sum_sum_12fc8ebf8180/repro.py:26-58 (with ``where(act > 0, dy, dy * slope)``
+    rounded to the tensor dtype first): sum_dy = sum(dy), dot = sum(dy * (x - mean)),
+    dx = ((dy - (x - mean) * ((dot / N) * invstd^2)) - sum_dy / N) * (invstd * w), dweight = dot * invstd.
+    """
+
+    def __init__(self, slope: float | None = None):
+        super().__init__()
+        self.slope = slope
+
+    def forward(self, dy, x, mean, invstd, weight, act=None):
+        n, c, h, w = x.shape
+        inv_count = 1.0 / (n * h * w)
+        g = _f32(dy) if dy.dtype != torch.float32 else dy
+        if act is not None:
+            a = _f32(act) if act.dtype != torch.float32 else act
+            gt = aten.gt.Scalar(a, 0)
+            scaled = aten.mul.Tensor(g, self.slope)
+            g = aten.where.self(gt, g, scaled)
+            if dy.dtype != torch.float32:
+                g = _f32(prims.convert_element_type.default(g, dy.dtype))
+        sum_1 = aten.sum.dim_IntList(g, [0, 2, 3])
+        xf = _f32(x) if x.dtype != torch.float32 else x
+        sub = aten.sub.Tensor(xf, aten.view.default(mean, [1, c, 1, 1]))
+        sum_2 = aten.sum.dim_IntList(aten.mul.Tensor(g, sub), [0, 2, 3])
+        c1 = aten.view.default(aten.mul.Tensor(sum_1, inv_count), [1, c, 1, 1])
+        c2 = aten.view.default(aten.mul.Tensor(aten.mul.Tensor(sum_2, inv_count), aten.mul.Tensor(invstd, invstd)),
+                               [1, c, 1, 1])
+        gs = aten.view.default(aten.mul.Tensor(invstd, weight), [1, c, 1, 1])
+        dx = aten.mul.Tensor(aten.sub.Tensor(aten.sub.Tensor(g, aten.mul.Tensor(sub, c2)), c1), gs)
+        dx = prims.convert_element_type.default(dx, x.dtype) if x.dtype != torch.float32 else dx
+        return (sum_1, aten.mul.Tensor(sum_2, invstd), dx)

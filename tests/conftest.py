@@ -82,7 +82,7 @@ def assert_sum_close(actual, expected, anchor, what=""):
     err_kernel = (a - ref).abs().max().item()
     err_eager = (expected.detach().double().cpu() - ref).abs().max().item()
     scale = max(ref.abs().max().item(), 1.0)
-    assert err_kernel <= 2.0 * err_eager + 1e-7 * scale, (
+    assert err_kernel <= 2.0 * err_eager + 2.4e-7 * scale, (  # floor: two fp32 ulps of the largest value
         f"{what}: max error vs the fp64 graph {err_kernel:.3e}, eager fp32 module {err_eager:.3e}")
 
 

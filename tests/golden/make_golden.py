@@ -47,6 +47,10 @@ CASES = {
     "transpose_021e90d9c17d": ("pointwise_021e90d9c17d", [[[4, 3, 49, 32], "bf16"], ["S", [4, 96, 7, 7]]]),
     "logsoftmax_d16035e7b826": ("amax_sum_d16035e7b826", [[[24, 520], "bf16"], ["S", [2, 12, 517]]]),
     "softmax_long_7079889cfc04": ("amax_sum_7079889cfc04", [[[6, 5000], "bf16"]]),
+    "bn_bwd_leaky_12fc8ebf8180": ("sum_sum_12fc8ebf8180",
+                                  # N*H*W stays 8192: the captured graph hard-codes 1/8192
+                                  [[[32, 8, 16, 16], "bf16"], [[32, 8, 16, 16], "bf16"], [[32, 8, 16, 16], "bf16"],
+                                   [[1, 8, 1, 1], "f32"], [[8], "f32"], [[8], "f32"]]),
     "spatial_mean_c9e1a8113328": ("mean_c9e1a8113328", [[[4, 48, 5, 5], "bf16", {"st": [1200, 1, 240, 48]}]]),
 }
 

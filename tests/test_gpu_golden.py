@@ -67,6 +67,10 @@ def kernel_cases():
     def spatial_mean(inp):
         return [column_sum.spatial_mean_forward(inp)]
 
+    def bn_bwd_leaky(inp):
+        from better_benchmark_b200.families import batch_norm_bwd
+        return list(batch_norm_bwd.leaky_relu_forward(inp, slope=0.2))
+
     return {
         "ln_fwd_f8ec553e339e": ln_fwd, "rmsnorm_fwd_f667cd8901af": rms_fwd,
         "softmax_bias_20ccc18dda60": softmax_bias, "bn_relu_42fad1ece813": bn_relu,
@@ -74,6 +78,7 @@ def kernel_cases():
         "colsum_eb86a17deab9": colsum, "headsplit_c0d19d490a2f": headsplit,
         "transpose_021e90d9c17d": transpose, "logsoftmax_d16035e7b826": logsoftmax,
         "softmax_long_7079889cfc04": softmax_long, "spatial_mean_c9e1a8113328": spatial_mean,
+        "bn_bwd_leaky_12fc8ebf8180": bn_bwd_leaky,
     }
 
 
@@ -92,7 +97,8 @@ def test_kernels_reproduce_reference_outputs(name):
     want = data["outputs"]
     assert len(got) == len(want)
     for i, (g, w) in enumerate(zip(got, want)):
-        if name in ("colsum_eb86a17deab9", "rms_bwd_2cd99e5eb23e", "ln_bwd_3cac3bbf4e8f") and \
+        if name in ("colsum_eb86a17deab9", "rms_bwd_2cd99e5eb23e", "ln_bwd_3cac3bbf4e8f",
+                    "bn_bwd_leaky_12fc8ebf8180") and \
                 w.dtype == torch.float32 and w.dim() == 1:
             # column sums over the rows: summation order differs from the CPU module's; compare
             # with the tolerance scaled by the magnitude of the summed terms

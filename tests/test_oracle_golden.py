@@ -71,6 +71,10 @@ def golden_cases():
     def spatial_mean(inp):
         return [eager.SpatialMean()(inp[0])]
 
+    def bn_bwd_leaky(inp):
+        dy, act, x, mean, invstd, w = inp
+        return list(eager.BatchNormBwd(slope=0.2)(dy, x, mean.view(-1), invstd, w, act=act))
+
     return {
         "ln_fwd_f8ec553e339e": ln_fwd, "rmsnorm_fwd_f667cd8901af": rms_fwd,
         "softmax_bias_20ccc18dda60": softmax_bias, "bn_relu_42fad1ece813": bn_relu,
@@ -78,6 +82,7 @@ def golden_cases():
         "colsum_eb86a17deab9": colsum, "headsplit_c0d19d490a2f": headsplit,
         "transpose_021e90d9c17d": transpose, "logsoftmax_d16035e7b826": logsoftmax,
         "softmax_long_7079889cfc04": softmax_long, "spatial_mean_c9e1a8113328": spatial_mean,
+        "bn_bwd_leaky_12fc8ebf8180": bn_bwd_leaky,
     }
 
 
