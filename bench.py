@@ -306,6 +306,7 @@ def gpu_arm(args, workload):
     e2e_value = workload.algorithmic_bytes / (e2e_ms * 1e-3) / 1e9 * world
 
     per_config = {}
+    families = {}
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.only_headline:
         del sets
@@ -320,6 +321,18 @@ def gpu_arm(args, workload):
             per_config[name] = {"us_per_step": round(per * 1e3, 2), "gbps": round(g, 1),
                                 "frac_of_peak": round(g / peak, 4), "launches_per_step": n_launch / args.steps,
                                 "algorithmic_bytes": wl.algorithmic_bytes}
+            del s
+            torch.cuda.empty_cache()
+        from better_benchmark_b200.family_cases import FAMILY_CASES
+        for name, wl in FAMILY_CASES.items():
+            s, _ = build_input_sets(wl, device, 4 * L2_BYTES_ASSUMED)
+            ms, n_launch = time_steps(wl, s, min(args.steps, 50), args.warmup, lambda: None)
+            per = ms / min(args.steps, 50)
+            g = wl.algorithmic_bytes / (per * 1e-3) / 1e9
+            families[name] = {"us_per_step": round(per * 1e3, 2), "gbps": round(g, 1),
+                              "frac_of_peak": round(g / peak, 4),
+                              "launches_per_step": n_launch / min(args.steps, 50),
+                              "algorithmic_bytes": wl.algorithmic_bytes, "description": wl.description}
             del s
             torch.cuda.empty_cache()
         per_config[workload.name] = {"us_per_step": round(ms_per_step * 1e3, 2), "gbps": round(gbps_one, 1),
@@ -356,6 +369,8 @@ def gpu_arm(args, workload):
         line["cpu_baseline"] = cpu_baseline
     if per_config:
         line["per_config"] = per_config
+    if families:
+        line["families"] = families
     print(json.dumps(line))
     return 0
 

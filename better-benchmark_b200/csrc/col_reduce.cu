@@ -29,6 +29,7 @@ struct ColReduceParams {
   int splits;
   long long rows_per_split;
   float post_scale;
+  int tx_log2;  // log2 of the lanes per thread row: 32 for wide tensors, fewer when cols / V < 32
 };
 
 __device__ __forceinline__ void store_out(void* out, int dtype, long long idx, float v) {
@@ -37,14 +38,18 @@ __device__ __forceinline__ void store_out(void* out, int dtype, long long idx, f
   else reinterpret_cast<__half*>(out)[idx] = __float2half_rn(v);
 }
 
-// blockDim = (32 vector columns, 8 thread rows); grid = (column chunks, splits, batch)
+// 256 threads = TY thread rows of TX lanes (TX = 32, or the power of two that covers cols / V when
+// that is smaller, so that narrow tensors - a channels-last image with 64 channels is 8 vectors
+// wide - still use every lane); grid = (column chunks of TX vectors, splits of the rows, batch).
 template <typename T, bool IS_MAX, bool VEC>
 __global__ void __launch_bounds__(256) col_reduce_kernel(const ColReduceParams p) {
   constexpr int V = VEC ? Elem<T>::V : 1;
-  constexpr int U = 4;
-  __shared__ float red[8][32 * (VEC ? Elem<T>::V : 1) + 1];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const long long col0 = ((long long)blockIdx.x * 32 + tx) * V;
+  constexpr int U = 8;
+  __shared__ float red[256 * V + 256];  // [TY][TX * V + 1]
+  const int TX = 1 << p.tx_log2, TY = 256 >> p.tx_log2;
+  const int tx = threadIdx.x & (TX - 1), ty = threadIdx.x >> p.tx_log2;
+  const int pitch = TX * V + 1;
+  const long long col0 = ((long long)blockIdx.x * TX + tx) * V;
   const long long b = blockIdx.z;
   const long long r_begin = (long long)blockIdx.y * p.rows_per_split;
   long long r_end = r_begin + p.rows_per_split;
@@ -56,17 +61,17 @@ __global__ void __launch_bounds__(256) col_reduce_kernel(const ColReduceParams p
 #pragma unroll
   for (int i = 0; i < V; ++i) acc[i] = IS_MAX ? -INFINITY : 0.f;
   if (active) {
-    for (long long r0 = r_begin + ty; r0 < r_end; r0 += 8 * U) {
+    for (long long r0 = r_begin + ty; r0 < r_end; r0 += (long long)TY * U) {
       if constexpr (VEC) {
         uint4 raw[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          const long long r = r0 + 8 * u;
+          const long long r = r0 + (long long)TY * u;
           if (r < r_end) raw[u] = ld_stream(base + r * p.x_row_stride);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          const long long r = r0 + 8 * u;
+          const long long r = r0 + (long long)TY * u;
           if (r < r_end) {
             float f[V];
             Elem<T>::unpack(raw[u], f);
@@ -77,7 +82,7 @@ __global__ void __launch_bounds__(256) col_reduce_kernel(const ColReduceParams p
       } else {
 #pragma unroll
         for (int u = 0; u < U; ++u) {
-          const long long r = r0 + 8 * u;
+          const long long r = r0 + (long long)TY * u;
           if (r < r_end) {
             const float f = Elem<T>::to_f32(base[r * p.x_row_stride]);
             acc[0] = IS_MAX ? MaxOp::apply(acc[0], f) : acc[0] + f;
@@ -87,15 +92,21 @@ __global__ void __launch_bounds__(256) col_reduce_kernel(const ColReduceParams p
     }
   }
 #pragma unroll
-  for (int i = 0; i < V; ++i) red[ty][tx * V + i] = acc[i];
+  for (int i = 0; i < V; ++i) red[ty * pitch + tx * V + i] = acc[i];
   __syncthreads();
-  // thread rows are folded by the first V*32 threads, one column each
-  for (int c = threadIdx.x; c < 32 * V; c += 256) {
-    const long long col = (long long)blockIdx.x * 32 * V + c;
+  // thread rows are folded in a fixed order, one column per thread
+  for (int c = threadIdx.x; c < TX * V; c += 256) {
+    const long long col = (long long)blockIdx.x * TX * V + c;
     if (col >= p.cols) continue;
-    float r = red[0][c];
-#pragma unroll
-    for (int k = 1; k < 8; ++k) r = IS_MAX ? MaxOp::apply(r, red[k][c]) : r + red[k][c];
+    float r;
+    if constexpr (IS_MAX) {
+      r = red[c];
+      for (int k = 1; k < TY; ++k) r = MaxOp::apply(r, red[k * pitch + c]);
+    } else {
+      double d = 0.0;  // above a thread's own chain the sum is carried in fp64
+      for (int k = 0; k < TY; ++k) d += (double)red[k * pitch + c];
+      r = (float)d;
+    }
     if (p.splits == 1) {
       store_out(p.out, p.out_dtype, b * p.out_batch_stride + col, r * p.post_scale);
     } else {
@@ -124,11 +135,16 @@ template <typename T>
 static int launch_col_reduce(ColReduceParams p, bool vec, size_t scratch_bytes, cudaStream_t st) {
   const int sms = device_info().sm_count;
   const int v = vec ? Elem<T>::V : 1;
-  const long long chunks = (p.cols + 32 * v - 1) / (32 * v);
+  const long long vcols = (p.cols + v - 1) / v;
+  int tx_log2 = 5;
+  while (tx_log2 > 0 && (1LL << (tx_log2 - 1)) >= vcols) --tx_log2;
+  p.tx_log2 = tx_log2;
+  const long long tx = 1LL << tx_log2, ty = 256 / tx;
+  const long long chunks = (vcols + tx - 1) / tx;
   if (chunks > 0x7fffffffLL || p.batch > 65535) return fail(B200_ERR_UNSUPPORTED, "b200_col_reduce: grid too large");
   // enough CTAs to fill the machine about four times over, at least 64 rows each
   long long splits = (4LL * sms + chunks * p.batch - 1) / (chunks * p.batch);
-  if (splits > (p.rows + 63) / 64) splits = (p.rows + 63) / 64;
+  if (splits > (p.rows + 8 * ty - 1) / (8 * ty)) splits = (p.rows + 8 * ty - 1) / (8 * ty);  // >= 8 rows per thread
   const long long cap = scratch_bytes / ((size_t)p.batch * p.cols * sizeof(float) + 1);
   if (splits > cap) splits = cap;
   if (splits > 65535) splits = 65535;

@@ -554,8 +554,10 @@ __global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdPara
   static_assert(NVAL == 2 || NVAL == 4 || NVAL == 8, "tile of 1, 2 or 4 rows");
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ __align__(16) float red[2][NVAL][16];
-  __shared__ double fin[16 * 64];
   __shared__ int bar_ok;
+  // the fp64 area of the final column sums reuses the ring once the last tile has been consumed
+  // (the launcher keeps the ring at 8 KB or more)
+  double* fin = reinterpret_cast<double*>(smem);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int nv = p.n / V;
   const bool active = tid < nv;
@@ -972,12 +974,18 @@ static bool try_launch_norm_bwd_tile(NormBwdParams p, int threads, size_t scratc
   }
   const DeviceInfo& dev = device_info();
   const size_t stage_bytes = 2 * (size_t)R * (size_t)(p.n / V) * 16;
-  const size_t static_bytes = 10 * 1024;  // red + fin + flags
-  const size_t per_cta = ((size_t)dev.max_smem_optin - 2048) / 2;  // two CTAs per SM
+  // Wide rows: two CTAs of up to 512 threads per SM. Narrow rows: as many small CTAs as 1024
+  // threads (64 registers each) allow, up to 16, so that there are enough warps per SM.
+  int ctas = threads >= 256 ? 2 : 1024 / threads;
+  if (ctas > 16) ctas = 16;
+  const size_t static_bytes = 1024;  // red + flags
+  const size_t per_cta = ((size_t)dev.max_smem_optin - 1024 * (size_t)ctas) / (size_t)ctas;
   const size_t fixed = 8 * sizeof(uint64_t);
-  if (per_cta < static_bytes + fixed + 3 * stage_bytes) return false;  // at least three stages
+  const int min_stages = threads >= 256 ? 3 : 2;
+  if (per_cta < static_bytes + fixed + (size_t)min_stages * stage_bytes) return false;
   int stages = (int)((per_cta - static_bytes - fixed) / stage_bytes);
   if (stages > 8) stages = 8;
+  if ((size_t)stages * stage_bytes < 16 * 64 * sizeof(double)) return false;  // the ring doubles as the fp64 area
   const size_t smem = (size_t)stages * stage_bytes + fixed;
   auto kernel = norm_bwd_tile_kernel<T, R, LN>;
   cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
@@ -1072,6 +1080,12 @@ static int launch_norm_bwd(NormBwdParams p, bool vector_ok, size_t scratch_bytes
   const long long nv = p.n / V;
   if (vector_ok && p.n % V == 0 && p.head_dim % V == 0 && nv <= 2048) {
     if (nv <= 128) {
+      if (nv > 32 && tile_rows_override() != 1) {  // column-owner CTAs of 2..4 warps, several rows per barrier
+        int rc = B200_OK;
+        const int narrow = (int)((nv + 31) / 32 * 32);
+        if (try_launch_norm_bwd_tile<T, 4, LN>(p, narrow, scratch_bytes, cooperative, st, &rc)) return rc;
+        if (try_launch_norm_bwd_tile<T, 2, LN>(p, narrow, scratch_bytes, cooperative, st, &rc)) return rc;
+      }
       if (nv <= 32) return launch_norm_bwd_fast<T, 1, false, LN>(p, 256, scratch_bytes, cooperative, st);
       if (nv <= 64) return launch_norm_bwd_fast<T, 2, false, LN>(p, 256, scratch_bytes, cooperative, st);
       return launch_norm_bwd_fast<T, 4, false, LN>(p, 256, scratch_bytes, cooperative, st);

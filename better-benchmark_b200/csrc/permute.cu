@@ -14,6 +14,8 @@
 // given) and rounded once to the output dtype.
 #include "rowwise.cuh"
 
+#include <type_traits>
+
 namespace b200 {
 
 struct PermuteParams {
@@ -120,6 +122,40 @@ __global__ void __launch_bounds__(256) transpose_tile_kernel(const TransposePara
   }
 }
 
+// Transpose of 16-bit elements without conversion, whole 64 x 64 tiles only: 16-byte accesses on
+// both sides. The tile lives in shared memory as 64 rows of 32 words (two elements per word), row r
+// rotated by 4 * (r / 8) words. A thread then reads, for one pair of input columns and eight
+// consecutive input rows, eight words that fall into eight different banks, and splits them into two
+// output vectors with byte permutes: eight consecutive elements of output row 2c and of row 2c + 1.
+__global__ void __launch_bounds__(256) transpose16_tile_kernel(const TransposeParams p) {
+  __shared__ __align__(16) uint32_t tile[64][32];
+  const long long b = blockIdx.z;
+  const long long p0 = (long long)blockIdx.y * 64, c0 = (long long)blockIdx.x * 64;
+  const unsigned short* src = reinterpret_cast<const unsigned short*>(p.x) + b * p.in_batch_stride;
+  unsigned short* dst = reinterpret_cast<unsigned short*>(p.y) + b * p.P * p.C;
+  const int tid = threadIdx.x;
+#pragma unroll
+  for (int k = 0; k < 2; ++k) {
+    const int q = tid + k * 256;
+    const int r = q >> 3, wv = q & 7;
+    const uint4 v = ld_stream(reinterpret_cast<const __half*>(src + (p0 + r) * p.in_row_stride + c0 + wv * 8));
+    *reinterpret_cast<uint4*>(&tile[r][(wv * 4 + 4 * (r >> 3)) & 31]) = v;
+  }
+  __syncthreads();
+  const int ovc = tid & 7, cpair = tid >> 3;
+  uint32_t w[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) w[j] = tile[ovc * 8 + j][(cpair + 4 * ovc) & 31];
+  uint4 lo, hi;
+  lo.x = __byte_perm(w[0], w[1], 0x5410); hi.x = __byte_perm(w[0], w[1], 0x7632);
+  lo.y = __byte_perm(w[2], w[3], 0x5410); hi.y = __byte_perm(w[2], w[3], 0x7632);
+  lo.z = __byte_perm(w[4], w[5], 0x5410); hi.z = __byte_perm(w[4], w[5], 0x7632);
+  lo.w = __byte_perm(w[6], w[7], 0x5410); hi.w = __byte_perm(w[6], w[7], 0x7632);
+  unsigned short* o = dst + (c0 + 2 * cpair) * p.P + p0 + ovc * 8;
+  st_stream(reinterpret_cast<__half*>(o), lo);
+  st_stream(reinterpret_cast<__half*>(o + p.P), hi);
+}
+
 // Contiguous cast / scale.
 template <typename Tin, typename Tout, bool VEC>
 __global__ void __launch_bounds__(256) cast_scale_kernel(const void* x, void* y, long long n, float scale,
@@ -166,6 +202,14 @@ static int launch_permute(const PermuteParams& p, bool vec, cudaStream_t st) {
 template <typename Tin, typename Tout>
 static int launch_transpose(const TransposeParams& p, cudaStream_t st) {
   dim3 grid((unsigned)((p.C + 63) / 64), (unsigned)((p.P + 63) / 64), (unsigned)p.batch);
+  if constexpr (std::is_same<Tin, Tout>::value && sizeof(Tin) == 2) {
+    const bool whole = p.P % 64 == 0 && p.C % 64 == 0 && !p.has_scale && p.in_row_stride % 8 == 0 &&
+                       p.in_batch_stride % 8 == 0 && aligned16(p.x) && aligned16(p.y);
+    if (whole) {
+      transpose16_tile_kernel<<<grid, 256, 0, st>>>(p);
+      return launch_status("b200_transpose_copy");
+    }
+  }
   transpose_tile_kernel<Tin, Tout><<<grid, 256, 0, st>>>(p);
   return launch_status("b200_transpose_copy");
 }

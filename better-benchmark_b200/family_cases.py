@@ -1,0 +1,118 @@
+"""One measured case per kernel family outside the five benchmark configurations: column
+reductions, row statistics, log_softmax, RMSNorm forward, LayerNorm backward, BatchNorm backward,
+permuting copies, transpose and cast. Same protocol as ``workloads.py`` (seeded synthetic inputs,
+bytes = every input once + every output once); sizes are chosen above the 126 MB L2.
+``bench.py`` times them next to the five configurations (key ``families`` of its JSON line).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import kernels
+from .families import batch_norm_bwd, column_sum, permute
+from .workloads import Workload, _gen
+
+
+def _nbytes(*tensors):
+    return sum(t.numel() * t.element_size() for t in tensors)
+
+
+def _randn(shape, dtype, seed, device):
+    # generated on the device from a seeded generator: these cases are only timed on a GPU
+    g = torch.Generator(device=device).manual_seed(seed)
+    return torch.randn(shape, generator=g, device=device, dtype=torch.float32).to(dtype)
+
+
+def _case(name, description, dtype, nbytes, make_inputs, forward):
+    return Workload(name=name, canonical_id="", shape_hash="", description=description, dtype=dtype,
+                    algorithmic_bytes=int(nbytes), make_inputs=make_inputs, oracle_forward=forward)
+
+
+def _col_sum_inputs(device="cuda", seed=1):
+    return [_randn((16384, 4096), torch.float32, seed, device)]
+
+
+def _spatial_mean_inputs(device="cuda", seed=1):
+    return [_randn((256, 64, 56, 56), torch.bfloat16, seed, device).contiguous(memory_format=torch.channels_last)]
+
+
+def _row_amax_inputs(device="cuda", seed=1):
+    return [_randn((65536, 1024), torch.bfloat16, seed, device)]
+
+
+def _row_var_mean_inputs(device="cuda", seed=1):
+    return [_randn((32768, 1024), torch.float32, seed, device)]
+
+
+def _log_softmax_inputs(device="cuda", seed=1):
+    return [_randn((32768, 1024), torch.bfloat16, seed, device)]
+
+
+def _rms_fwd_inputs(device="cuda", seed=1):
+    return [_randn((16384, 4096), torch.bfloat16, seed, device),
+            (torch.rand(4096, generator=_gen(seed)) + 0.5).to(torch.bfloat16).to(device)]
+
+
+def _ln_bwd_inputs(device="cuda", seed=1):
+    x = _randn((32768, 768), torch.bfloat16, seed, device)
+    dy = _randn((32768, 768), torch.bfloat16, seed + 100, device)
+    w = (torch.rand(768, generator=_gen(seed)) + 0.5).to(device)
+    xf = x.float()
+    mean = xf.mean(dim=1)
+    rstd = torch.rsqrt(xf.var(dim=1, unbiased=False) + 1e-5)
+    return [x, dy, w, mean, rstd]
+
+
+def _bn_bwd_inputs(device="cuda", seed=1):
+    shape = (256, 64, 56, 56)
+    x = _randn(shape, torch.bfloat16, seed, device).contiguous(memory_format=torch.channels_last)
+    dy = _randn(shape, torch.bfloat16, seed + 100, device).contiguous(memory_format=torch.channels_last)
+    mean = torch.zeros(64, device=device)
+    invstd = torch.ones(64, device=device)
+    w = (torch.rand(64, generator=_gen(seed)) + 0.5).to(device)
+    return [dy, x, mean, invstd, w]
+
+
+def _head_split_inputs(device="cuda", seed=1):
+    return [_randn((4 * 4096, 32 * 128), torch.bfloat16, seed, device), [4, 4096, 4096], [4, 4096, 32, 128],
+            [128, 4096, 128]]
+
+
+def _transpose_inputs(device="cuda", seed=1):
+    return [_randn((64, 1024, 768), torch.bfloat16, seed, device), [64, 768, 1024]]
+
+
+def _cast_inputs(device="cuda", seed=1):
+    return [_randn((64 << 20,), torch.bfloat16, seed, device)]
+
+
+MB = 1 << 20
+FAMILY_CASES = {c.name: c for c in [
+    _case("col_sum_f32", "column sum: x f32 [16384, 4096] -> f32 [4096]", "f32",
+          16384 * 4096 * 4 + 4096 * 4, _col_sum_inputs, lambda i: column_sum.oracle_forward(i)),
+    _case("spatial_mean_cl_bf16", "mean over H,W: x bf16 channels_last [256,64,56,56] -> bf16 [256,64,1,1]", "bf16",
+          256 * 64 * 3136 * 2 + 256 * 64 * 2, _spatial_mean_inputs, lambda i: column_sum.spatial_mean_forward(i)),
+    _case("row_amax_bf16", "row amax: x bf16 [65536, 1024] -> bf16 [65536]", "bf16",
+          65536 * 1024 * 2 + 65536 * 2, _row_amax_inputs, lambda i: kernels.row_reduce(i[0], "amax")),
+    _case("row_var_mean_f32", "row var_mean: x f32 [32768, 1024] -> var, mean f32 [32768]", "f32",
+          32768 * 1024 * 4 + 2 * 32768 * 4, _row_var_mean_inputs,
+          lambda i: kernels.norm_fwd(i[0], None, None, eps=0.0, want_y=False, want_mean=True, want_var=True,
+                                     correction=1.0)),
+    _case("log_softmax_bf16_f32", "log_softmax: x bf16 [32768, 1024] -> f32", "bf16",
+          32768 * 1024 * (2 + 4), _log_softmax_inputs,
+          lambda i: kernels.softmax(i[0], log=True, out_dtype=torch.float32)),
+    _case("rms_norm_fwd_bf16", "RMSNorm forward: x bf16 [16384, 4096], w bf16 -> y bf16", "bf16",
+          2 * 16384 * 4096 * 2 + 4096 * 2, _rms_fwd_inputs,
+          lambda i: kernels.norm_fwd(i[0], i[1], None, eps=1e-6, rms=True)[0]),
+    _case("layer_norm_bwd_bf16", "LayerNorm backward: x, dy bf16 [32768, 768] -> dx bf16, dweight, dbias f32", "bf16",
+          3 * 32768 * 768 * 2 + 768 * 4 * 3 + 2 * 32768 * 4, _ln_bwd_inputs,
+          lambda i: kernels.norm_bwd(i[0], i[1], i[2], i[4], mean=i[3], rms=False, want_dbias=True)),
+    _case("batch_norm_bwd_cl_bf16", "BatchNorm backward: dy, x bf16 channels_last [256,64,56,56] -> dx, dweight, dbias",
+          "bf16", 3 * 256 * 64 * 3136 * 2 + 5 * 64 * 4, _bn_bwd_inputs, lambda i: batch_norm_bwd.oracle_forward(i)),
+    _case("head_split_bf16", "[B*S, H*D] -> [B*H, S, D] copy: bf16, B=4 S=4096 H=32 D=128", "bf16",
+          2 * 16384 * 4096 * 2, _head_split_inputs, lambda i: permute.head_split_forward(i)),
+    _case("transpose_bf16", "[64, 1024, 768] -> [64, 768, 1024] contiguous copy, bf16", "bf16",
+          2 * 64 * 1024 * 768 * 2, _transpose_inputs, lambda i: permute.transpose_forward(i)),
+    _case("cast_bf16_f32", "cast bf16 -> f32, 64 Mi elements", "bf16",
+          (64 << 20) * 6, _cast_inputs, lambda i: kernels.cast_scale(i[0], torch.float32)),
+]}
