@@ -545,32 +545,41 @@ __device__ __forceinline__ float warp_reduce_multi(float (&v)[N], int lane) {
   return v[0];
 }
 
-template <typename T, int R, bool LN>
-__global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdParams p, const int stages) {
+template <typename T, int R, bool LN, bool GROUPED>
+__global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdParams p, const int stages, const int TG) {
   constexpr int V = Elem<T>::V;
   constexpr int NVAL = R * (LN ? 2 : 1);  // row sums per tile: 2, 4 or 8
   constexpr int LPV = 32 / NVAL;          // lanes that share one value after the warp reduction
   constexpr int PER = NVAL / 2;           // table entries a lane sums in the second stage
   static_assert(NVAL == 2 || NVAL == 4 || NVAL == 8, "tile of 1, 2 or 4 rows");
+  // Narrow rows: the CTA is GROUPS = blockDim.x / TG row groups of TG threads (TG a multiple of
+  // 32, >= the vectors of a row). A tile is GROUPS * R consecutive rows, group g takes rows
+  // g*R .. g*R+R-1 of it; thread t of every group owns the same columns. Wide rows: one group.
+  constexpr int MAX_GROUPS = GROUPED ? 8 : 1;
   extern __shared__ __align__(128) unsigned char smem[];
-  __shared__ __align__(16) float red[2][NVAL][16];
+  __shared__ __align__(16) float red[2][MAX_GROUPS][NVAL][16];
   __shared__ int bar_ok;
   // the fp64 area of the final column sums reuses the ring once the last tile has been consumed
   // (the launcher keeps the ring at 8 KB or more)
   double* fin = reinterpret_cast<double*>(smem);
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int lane = threadIdx.x & 31;
+  const int GROUPS = GROUPED ? (int)blockDim.x / TG : 1;
+  const int grp = GROUPED ? (int)threadIdx.x / TG : 0;
+  const int tid = threadIdx.x - grp * TG;        // thread within its row group
+  const int warp = tid >> 5;                     // warp within its row group
+  const int TR = GROUPS * R;                     // rows per tile
   const int nv = p.n / V;
   const bool active = tid < nv;
   const uint32_t row_bytes = (uint32_t)nv * 16u;
-  const uint32_t stage_bytes = 2u * R * row_bytes;
+  const uint32_t stage_bytes = 2u * TR * row_bytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_bytes);
   const int rows = (int)p.rows;  // the launcher admits fewer than 2^31 rows
-  const int tiles = (rows + R - 1) / R;
+  const int tiles = (rows + TR - 1) / TR;
   const int my_tiles = tiles > (int)blockIdx.x ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
-  const int row_step = (int)gridDim.x * R;
+  const int row_step = (int)gridDim.x * TR;
 
-  for (int i = tid; i < 2 * NVAL * 16; i += blockDim.x) (&red[0][0][0])[i] = 0.f;
-  if (tid == 0) {
+  for (int i = threadIdx.x; i < 2 * MAX_GROUPS * NVAL * 16; i += blockDim.x) (&red[0][0][0][0])[i] = 0.f;
+  if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
     mbar_init_fence();
   }
@@ -579,23 +588,23 @@ __global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdPara
   auto issue = [&](int k, int slot) {  // thread 0 only
     const T* xg = reinterpret_cast<const T*>(p.x);
     const T* dyg = reinterpret_cast<const T*>(p.dy);
-    const long long row0 = ((long long)blockIdx.x + (long long)k * gridDim.x) * R;
-    const int nrows = p.rows - row0 < R ? (int)(p.rows - row0) : R;
+    const long long row0 = ((long long)blockIdx.x + (long long)k * gridDim.x) * TR;
+    const int nrows = p.rows - row0 < TR ? (int)(p.rows - row0) : TR;
     uint64_t* bar = &full[slot];
     unsigned char* dst = smem + (size_t)slot * stage_bytes;
     mbar_arrive_expect_tx(bar, 2u * nrows * row_bytes);
     if (p.x_row_stride == p.n && p.dy_row_stride == p.n) {
       bulk_load(dst, xg + row0 * p.n, nrows * row_bytes, bar);
-      bulk_load(dst + R * row_bytes, dyg + row0 * p.n, nrows * row_bytes, bar);
+      bulk_load(dst + TR * row_bytes, dyg + row0 * p.n, nrows * row_bytes, bar);
     } else {
       for (int r = 0; r < nrows; ++r) {
         bulk_load(dst + r * row_bytes, xg + (row0 + r) * p.x_row_stride, row_bytes, bar);
-        bulk_load(dst + (R + r) * row_bytes, dyg + (row0 + r) * p.dy_row_stride, row_bytes, bar);
+        bulk_load(dst + (TR + r) * row_bytes, dyg + (row0 + r) * p.dy_row_stride, row_bytes, bar);
       }
     }
   };
   int issued = 0, issue_slot = 0;
-  if (tid == 0) {
+  if (threadIdx.x == 0) {
     for (; issued < my_tiles && issued < stages; ++issued) issue(issued, issued);
     issue_slot = issued % stages;
   }
@@ -627,10 +636,10 @@ __global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdPara
   bool failed = false;
   int parity = 0, st = 0;
   uint32_t phase = 0;
-  int row0 = (int)blockIdx.x * R;
+  int row0 = (int)blockIdx.x * TR + grp * R;  // first row of this group in the current tile
 
   for (int k = 0; k < my_tiles; ++k, row0 += row_step) {
-    const int nrows = rows - row0 < R ? rows - row0 : R;
+    const int nrows = rows - row0 < R ? (rows - row0 > 0 ? rows - row0 : 0) : R;
     float rstd[R], mean[LN ? R : 1];
 #pragma unroll
     for (int r = 0; r < R; ++r) {
@@ -638,8 +647,8 @@ __global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdPara
       if constexpr (LN) mean[r] = r < nrows ? __ldg(p.mean + row0 + r) : 0.f;
     }
     const bool arrived = mbar_wait(&full[st], phase);
-    const unsigned char* sx = smem + (size_t)st * stage_bytes + (size_t)tid * 16;
-    const unsigned char* sy = sx + (size_t)R * row_bytes;
+    const unsigned char* sx = smem + (size_t)st * stage_bytes + (size_t)(grp * R) * row_bytes + (size_t)tid * 16;
+    const unsigned char* sy = sx + (size_t)TR * row_bytes;
     const bool whole = active && nrows == R;  // uniform per warp except in the last warp of a ragged row
 
     // Pass 1: the row sums of this thread's columns.
@@ -666,11 +675,11 @@ __global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdPara
       if constexpr (LN) vals[2 * r] = hsum2(s1);
     }
     const float mine = warp_reduce_multi<NVAL>(vals, lane);
-    if ((lane & (LPV - 1)) == 0) red[parity][lane / LPV][warp] = mine;
+    if ((lane & (LPV - 1)) == 0) red[parity][grp][lane / LPV][warp] = mine;
 
     if (!__syncthreads_and(arrived)) {
       failed = true;
-      if (tid == 0) {
+      if (threadIdx.x == 0) {
         note_wait_timeout();
         atomicExch(&p.bar[1], 1u);  // lets the other CTAs leave the grid barrier at once
         int ds = st;
@@ -684,7 +693,7 @@ __global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdPara
     }
     // The second pass reads this stage again; what the barrier proves is that the PREVIOUS tile's
     // stage has been read to the end by every thread: that one is refilled.
-    if (tid == 0 && k >= 1 && issued < my_tiles) {
+    if (threadIdx.x == 0 && k >= 1 && issued < my_tiles) {
       fence_proxy_async_smem();
       issue(issued, issue_slot);
       ++issued;
@@ -695,7 +704,7 @@ __global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdPara
     // table, a butterfly over the LPV lanes of a value finishes it.
     float part;
     {
-      const float* tp = &red[parity][0][0] + lane * PER;
+      const float* tp = &red[parity][grp][0][0] + lane * PER;
       if constexpr (PER == 1) {
         part = tp[0];
       } else if constexpr (PER == 2) {
@@ -769,22 +778,32 @@ __global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdPara
     }
   }
 
-  if (!failed && (p.dw || p.db) && active) {
-    float* pw = p.partials + (long long)blockIdx.x * p.n + (long long)tid * V;
-    float* pb = p.partials + ((long long)p.groups + blockIdx.x) * p.n + (long long)tid * V;
-    float f[V];
+  // Per-CTA partial rows: the row groups are folded in a fixed order through the ring (free now).
+  if (!failed && (p.dw || p.db)) {
+    __syncthreads();  // every group is done with its last tile
+    float* fold_w = reinterpret_cast<float*>(smem);             // [GROUPS][n]
+    float* fold_b = fold_w + (size_t)GROUPS * p.n;              // [GROUPS][n]
+    if (active) {
 #pragma unroll
-    for (int i = 0; i < V / 2; ++i) unpack2(acc_w[i], f[2 * i], f[2 * i + 1]);
-#pragma unroll
-    for (int q = 0; q < V / 4; ++q)
-      reinterpret_cast<float4*>(pw)[q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
-    if constexpr (LN) {
-      if (p.db) {
-#pragma unroll
-        for (int i = 0; i < V / 2; ++i) unpack2(acc_b[i], f[2 * i], f[2 * i + 1]);
-#pragma unroll
-        for (int q = 0; q < V / 4; ++q)
-          reinterpret_cast<float4*>(pb)[q] = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+      for (int i = 0; i < V / 2; ++i) {
+        unpack2(acc_w[i], fold_w[(size_t)grp * p.n + tid * V + 2 * i], fold_w[(size_t)grp * p.n + tid * V + 2 * i + 1]);
+        if constexpr (LN) unpack2(acc_b[i], fold_b[(size_t)grp * p.n + tid * V + 2 * i],
+                                  fold_b[(size_t)grp * p.n + tid * V + 2 * i + 1]);
+      }
+    }
+    __syncthreads();
+    float* pw = p.partials + (long long)blockIdx.x * p.n;
+    float* pb = p.partials + ((long long)p.groups + blockIdx.x) * p.n;
+    for (int c = threadIdx.x; c < p.n; c += blockDim.x) {
+      float a = fold_w[c];
+      for (int g = 1; g < GROUPS; ++g) a += fold_w[(size_t)g * p.n + c];
+      pw[c] = a;
+      if constexpr (LN) {
+        if (p.db) {
+          float b = fold_b[c];
+          for (int g = 1; g < GROUPS; ++g) b += fold_b[(size_t)g * p.n + c];
+          pb[c] = b;
+        }
       }
     }
   }
@@ -973,21 +992,26 @@ static bool try_launch_norm_bwd_tile(NormBwdParams p, int threads, size_t scratc
     if (last >= 0x7fffffffLL || p.dx_batch_stride < 0 || p.dx_seq_stride < 0 || p.dx_head_stride < 0) return false;
   }
   const DeviceInfo& dev = device_info();
-  const size_t stage_bytes = 2 * (size_t)R * (size_t)(p.n / V) * 16;
-  // Wide rows: two CTAs of up to 512 threads per SM. Narrow rows: as many small CTAs as 1024
-  // threads (64 registers each) allow, up to 16, so that there are enough warps per SM.
-  int ctas = threads >= 256 ? 2 : 1024 / threads;
-  if (ctas > 16) ctas = 16;
-  const size_t static_bytes = 1024;  // red + flags
-  const size_t per_cta = ((size_t)dev.max_smem_optin - 1024 * (size_t)ctas) / (size_t)ctas;
+  // Narrow rows: several row groups of `threads` threads share a CTA of up to 512 threads, so that
+  // there are still only two partial rows per SM to finalize. Wide rows: one group.
+  const int tg = threads;
+  int groups_per_cta = 512 / tg;
+  if (groups_per_cta > 8) groups_per_cta = 8;
+  if (groups_per_cta < 1) groups_per_cta = 1;
+  threads = tg * groups_per_cta;
+  const size_t stage_bytes = 2 * (size_t)groups_per_cta * (size_t)R * (size_t)(p.n / V) * 16;
+  const size_t static_bytes = (groups_per_cta > 1 ? 8 : 1) * 2 * 8 * 16 * sizeof(float) + 256;  // row-sum tables + flags
+  const size_t per_cta = ((size_t)dev.max_smem_optin - 2048) / 2;  // two CTAs per SM
   const size_t fixed = 8 * sizeof(uint64_t);
-  const int min_stages = threads >= 256 ? 3 : 2;
+  const int min_stages = groups_per_cta > 1 ? 2 : 3;
   if (per_cta < static_bytes + fixed + (size_t)min_stages * stage_bytes) return false;
   int stages = (int)((per_cta - static_bytes - fixed) / stage_bytes);
   if (stages > 8) stages = 8;
-  if ((size_t)stages * stage_bytes < 16 * 64 * sizeof(double)) return false;  // the ring doubles as the fp64 area
+  // the ring doubles as the fold area [2][groups][n] fp32 and as the fp64 area of the finalize
+  if ((size_t)stages * stage_bytes < 16 * 64 * sizeof(double) ||
+      (size_t)stages * stage_bytes < 2 * (size_t)groups_per_cta * p.n * sizeof(float)) return false;
   const size_t smem = (size_t)stages * stage_bytes + fixed;
-  auto kernel = norm_bwd_tile_kernel<T, R, LN>;
+  auto kernel = groups_per_cta > 1 ? norm_bwd_tile_kernel<T, R, LN, true> : norm_bwd_tile_kernel<T, R, LN, false>;
   cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
@@ -996,7 +1020,7 @@ static bool try_launch_norm_bwd_tile(NormBwdParams p, int threads, size_t scratc
   }
   const int per_sm = cached_occupancy(reinterpret_cast<const void*>(kernel), threads, smem);
   long long grid = (long long)per_sm * dev.sm_count;
-  const long long tiles = (p.rows + R - 1) / R;
+  const long long tiles = (p.rows + (long long)R * groups_per_cta - 1) / ((long long)R * groups_per_cta);
   if (grid > tiles) grid = tiles;
   if (p.dw || p.db) {
     const long long plane = (long long)p.n * sizeof(float);
@@ -1006,9 +1030,10 @@ static bool try_launch_norm_bwd_tile(NormBwdParams p, int threads, size_t scratc
   }
   p.groups = (int)grid;
   p.fused = cooperative ? 1 : 0;
+  int tg_arg = tg;
   if (cooperative) {
     int stages_arg = stages;
-    void* args[] = {&p, &stages_arg};
+    void* args[] = {&p, &stages_arg, &tg_arg};
     e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3((unsigned)grid), dim3(threads),
                                     args, smem, st);
     if (e != cudaSuccess) {
@@ -1020,7 +1045,7 @@ static bool try_launch_norm_bwd_tile(NormBwdParams p, int threads, size_t scratc
     *rc = B200_OK;
     return true;
   }
-  kernel<<<(unsigned)grid, threads, smem, st>>>(p, stages);
+  kernel<<<(unsigned)grid, threads, smem, st>>>(p, stages, tg_arg);
   *rc = launch_status("b200_norm_bwd (row tiles)");
   if (*rc == B200_OK && (p.dw || p.db)) {
     norm_bwd_finalize_kernel<<<(p.n + 63) / 64, 512, 0, st>>>(p);

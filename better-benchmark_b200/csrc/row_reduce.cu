@@ -9,6 +9,8 @@
 // then a fixed-order shuffle/shared-memory tree. mean multiplies the sum by 1/n, as aten does.
 #include "rowwise.cuh"
 
+#include <type_traits>
+
 namespace b200 {
 
 #define B200_REDUCE_SUM 0
@@ -56,7 +58,42 @@ row_reduce_kernel(const RowReduceParams p) {
   for (int i = 0; i < V; ++i) acc[i] = Op::identity();
 
   long long done = 0;  // elements covered by the vector loop
-  if constexpr (VEC) {
+  if constexpr (VEC && !Op::is_sum && sizeof(Tin) == 2) {
+    // Maximum / minimum of 16-bit elements: exact in the storage type, so the vectors are folded
+    // as packed pairs (one instruction per two elements, no conversion) and only the last pair
+    // of each thread is widened.
+    using P2 = typename std::conditional<std::is_same<Tin, __half>::value, __half2, __nv_bfloat162>::type;
+    const long long nv = p.n / V;
+    P2 m[4];
+    {
+      const Tin id = Elem<Tin>::from_f32(Op::identity());
+      P2 idp;
+      idp.x = id;
+      idp.y = id;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) m[i] = idp;
+    }
+    for (long long j0 = lane; j0 < nv; j0 += (long long)G * U) {
+      uint4 raw[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long j = j0 + (long long)u * G;
+        if (j < nv) raw[u] = ld_stream(x + j * V);
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long j = j0 + (long long)u * G;
+        if (j < nv) {
+          const uint32_t w[4] = {raw[u].x, raw[u].y, raw[u].z, raw[u].w};
+#pragma unroll
+          for (int i = 0; i < 4; ++i) m[i] = Op::apply2(m[i], *reinterpret_cast<const P2*>(&w[i]));
+        }
+      }
+    }
+    const P2 a = Op::apply2(Op::apply2(m[0], m[1]), Op::apply2(m[2], m[3]));
+    acc[0] = Op::apply(Elem<Tin>::to_f32(a.x), Elem<Tin>::to_f32(a.y));
+    done = nv * V;
+  } else if constexpr (VEC) {
     const long long nv = p.n / V;
     for (long long j0 = lane; j0 < nv; j0 += (long long)G * U) {
       uint4 raw[U];
