@@ -375,6 +375,44 @@ def gpu_arm(args, workload):
     return 0
 
 
+def sweep_arm(args):
+    """Aggregate wall time of the corpus sweep (check + bench of every shape point through persistent
+    worker processes, sharded over the first N visible GPUs) on the five benchmark directories."""
+    import shutil
+    import tempfile
+    from better_benchmark_b200 import sweep
+    from better_benchmark_b200.workloads import WORKLOADS
+    peak, _ = measured_peak()
+    root = tempfile.mkdtemp(prefix="b200_sweep_")
+    try:
+        for wl in WORKLOADS.values():
+            dest = os.path.join(root, "repros", "canonical", wl.canonical_id)
+            os.makedirs(dest)
+            for src in (os.path.join(ROOT, "better-benchmark_b200", "canonical", wl.canonical_id),
+                        os.path.join(ROOT, "oracle", "canonical", wl.canonical_id)):  # the eager module is the checker
+                for f in os.listdir(src):
+                    if os.path.isfile(os.path.join(src, f)):
+                        shutil.copy(os.path.join(src, f), os.path.join(dest, f))
+        dirs = sweep.find_oracle_dirs([root])
+        tasks = sweep.expand_shape_tasks(dirs)
+        visible = [d for d in os.environ.get("CUDA_VISIBLE_DEVICES", "").split(",") if d.strip()]
+        gpus = (visible or [str(i) for i in range(args.gpus)])[:args.gpus]
+        out = os.path.join(root, "timings.json")
+        results, failures, summary = sweep.run_sweep(
+            tasks, gpus, options=dict(warmup=5, rep=50, task_timeout=900, peak_gbps=peak, workers_per_gpu=2),
+            output=out, log=lambda *a: print(*a, file=sys.stderr))
+        timed = sweep.write_oracle_timings(out, results, failures, sweep.sweep_metadata(summary))
+        points = {k: {"oracle_us": v["oracle_us"], **{kk: vv for kk, vv in next(iter(v["points"].values())).items()
+                                                       if kk in ("oracle_gbps", "sol_frac", "status")}}
+                  for k, v in timed.items() if k not in sweep.RESERVED_KEYS}
+        print(json.dumps({"metric": "sweep_wall_s", "value": summary["wall_s"], "unit": "s", "n_gpus": len(gpus),
+                          "higher_is_better": False, "points": len(tasks), "failed": len(failures),
+                          "workers": summary["n_workers"], "per_dir": points}))
+        return 0 if not failures else 1
+    finally:
+        shutil.rmtree(root, ignore_errors=True)
+
+
 def main(argv=None):
     from better_benchmark_b200.workloads import HEADLINE, WORKLOADS
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
@@ -384,10 +422,14 @@ def main(argv=None):
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default=HEADLINE, choices=sorted(WORKLOADS))
     ap.add_argument("--only-headline", action="store_true", help="skip the other configurations and the CPU baseline")
+    ap.add_argument("--sweep", action="store_true",
+                    help="run the corpus sweep over the five directories on --gpus GPUs and report its wall time")
     args = ap.parse_args(argv)
     if args.warmup < 3:
         args.warmup = 3
     workload = WORKLOADS[args.workload]
+    if args.sweep:
+        return sweep_arm(args)
     if args.impl == "reference":
         return reference_arm(args, workload)
     return gpu_arm(args, workload)

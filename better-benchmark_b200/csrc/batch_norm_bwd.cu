@@ -134,15 +134,27 @@ __global__ void __launch_bounds__(256) bn_bwd_sums_cl_kernel(const BnBwdParams p
   }
 }
 
-// One warp per channel: fp64 combination of the partials, outputs and the coefficient table.
+// One CTA per channel: the partials are read with every thread (all loads of a thread are in
+// flight together), combined in fp64 in a fixed order; thread 0 writes the outputs and the
+// coefficient table.
 __global__ void __launch_bounds__(256) bn_bwd_finalize_kernel(const BnBwdParams p) {
-  const int lane = threadIdx.x & 31;
-  const int c = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (c >= p.channels) return;
+  __shared__ double red[2][8];
+  const int c = blockIdx.x;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   double s1 = 0.0, s2 = 0.0;
-  for (int g = lane; g < p.splits; g += 32) {
-    s1 += p.partials[((long long)g * 2) * p.channels + c];
-    s2 += p.partials[((long long)g * 2 + 1) * p.channels + c];
+  for (int g0 = tid; g0 < p.splits; g0 += 256 * 4) {
+    double a[4], b[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int g = g0 + u * 256;
+      a[u] = g < p.splits ? p.partials[((long long)g * 2) * p.channels + c] : 0.0;
+      b[u] = g < p.splits ? p.partials[((long long)g * 2 + 1) * p.channels + c] : 0.0;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      s1 += a[u];
+      s2 += b[u];
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -150,6 +162,16 @@ __global__ void __launch_bounds__(256) bn_bwd_finalize_kernel(const BnBwdParams 
     s2 += __shfl_xor_sync(0xffffffffu, s2, o);
   }
   if (lane == 0) {
+    red[0][warp] = s1;
+    red[1][warp] = s2;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    s1 = s2 = 0.0;
+    for (int w = 0; w < 8; ++w) {
+      s1 += red[0][w];
+      s2 += red[1][w];
+    }
     const float sum_dy = (float)s1, dot = (float)s2;
     const float invstd = p.invstd[c];
     const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
@@ -302,7 +324,7 @@ static int launch_bn_bwd(BnBwdParams p, bool fast, size_t scratch_bytes, cudaStr
     bn_bwd_sums_cl_kernel<T><<<(unsigned)splits, 256, 0, st>>>(p, per);
     int rc = launch_status("b200_batch_norm_bwd sums");
     if (rc != B200_OK) return rc;
-    bn_bwd_finalize_kernel<<<(p.channels + 7) / 8, 256, 0, st>>>(p);
+    bn_bwd_finalize_kernel<<<p.channels, 256, 0, st>>>(p);
     rc = launch_status("b200_batch_norm_bwd finalize");
     if (rc != B200_OK || !p.dx) return rc;
     long long grid = 8LL * dev.sm_count;
@@ -322,7 +344,7 @@ static int launch_bn_bwd(BnBwdParams p, bool fast, size_t scratch_bytes, cudaStr
   bn_bwd_sums_general_kernel<T><<<dim3(p.channels, (unsigned)splits), 256, 0, st>>>(p);
   int rc = launch_status("b200_batch_norm_bwd sums");
   if (rc != B200_OK) return rc;
-  bn_bwd_finalize_kernel<<<(p.channels + 7) / 8, 256, 0, st>>>(p);
+  bn_bwd_finalize_kernel<<<p.channels, 256, 0, st>>>(p);
   rc = launch_status("b200_batch_norm_bwd finalize");
   if (rc != B200_OK || !p.dx) return rc;
   bn_bwd_apply_general_kernel<T><<<dim3(p.channels, (unsigned)splits), 256, 0, st>>>(p);

@@ -126,7 +126,14 @@ __global__ void __launch_bounds__(256) col_reduce_finalize_kernel(const ColReduc
     store_out(p.out, p.out_dtype, b * p.out_batch_stride + col, r);
   } else {
     double r = 0.0;
-    for (int s = 0; s < p.splits; ++s) r += (double)p.partials[(long long)s * p.batch * p.cols + idx];
+    for (int s0 = 0; s0 < p.splits; s0 += 8) {  // eight loads in flight, then added in order
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        v[u] = s0 + u < p.splits ? p.partials[(long long)(s0 + u) * p.batch * p.cols + idx] : 0.f;
+#pragma unroll
+      for (int u = 0; u < 8; ++u) r += (double)v[u];
+    }
     store_out(p.out, p.out_dtype, b * p.out_batch_stride + col, (float)r * p.post_scale);
   }
 }

@@ -68,10 +68,20 @@ __device__ __forceinline__ void finalize_columns(const float* partials, int grou
   for (int chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
     const int c0 = chunk * 64 + lane, c1 = c0 + 32;
     double a0 = 0.0, a1 = 0.0;
-    for (int g = warp; g < groups; g += nwarps) {
-      const float* row = partials + (long long)g * n;
-      if (c0 < n) a0 += (double)__ldcg(row + c0);
-      if (c1 < n) a1 += (double)__ldcg(row + c1);
+    for (int g0 = warp; g0 < groups; g0 += 4 * nwarps) {  // eight loads in flight, then added in order
+      float v0[4], v1[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int g = g0 + u * nwarps;
+        const float* row = partials + (long long)g * n;
+        v0[u] = (g < groups && c0 < n) ? __ldcg(row + c0) : 0.f;
+        v1[u] = (g < groups && c1 < n) ? __ldcg(row + c1) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        a0 += (double)v0[u];
+        a1 += (double)v1[u];
+      }
     }
     smem[warp * 64 + lane] = a0;
     smem[warp * 64 + 32 + lane] = a1;
