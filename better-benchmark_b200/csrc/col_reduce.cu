@@ -149,9 +149,25 @@ static int launch_col_reduce(ColReduceParams p, bool vec, size_t scratch_bytes, 
   const long long tx = 1LL << tx_log2, ty = 256 / tx;
   const long long chunks = (vcols + tx - 1) / tx;
   if (chunks > 0x7fffffffLL || p.batch > 65535) return fail(B200_ERR_UNSUPPORTED, "b200_col_reduce: grid too large");
-  // enough CTAs to fill the machine about four times over, at least 64 rows each
-  long long splits = (4LL * sms + chunks * p.batch - 1) / (chunks * p.batch);
-  if (splits > (p.rows + 8 * ty - 1) / (8 * ty)) splits = (p.rows + 8 * ty - 1) / (8 * ty);  // >= 8 rows per thread
+  // Enough CTAs to fill the machine about four times over (256-thread CTAs, eight resident per
+  // SM), every thread keeping at least eight rows. When a somewhat larger split count makes the
+  // CTAs fill whole waves almost exactly, take that one: a grid of 4.1 CTAs per SM runs as long as
+  // one of 5.
+  const long long base = chunks * p.batch;
+  const long long slots = 8LL * sms;
+  long long max_splits = (p.rows + 8 * ty - 1) / (8 * ty);
+  if (max_splits < 1) max_splits = 1;
+  long long splits = (4LL * sms + base - 1) / base;
+  if (splits > max_splits) splits = max_splits;
+  for (long long s = splits; s <= max_splits && s <= 3 * splits; ++s) {
+    const long long ctas = s * base;
+    if (ctas < slots) continue;
+    const long long waves = (ctas + slots - 1) / slots;
+    if ((double)ctas / (double)(waves * slots) >= 0.97) {
+      splits = s;
+      break;
+    }
+  }
   const long long cap = scratch_bytes / ((size_t)p.batch * p.cols * sizeof(float) + 1);
   if (splits > cap) splits = cap;
   if (splits > 65535) splits = 65535;

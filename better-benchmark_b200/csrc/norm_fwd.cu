@@ -375,7 +375,8 @@ norm_fwd_stream_kernel(const NormFwdParams p, const int stages, const int contig
 // At most 32 elements per thread, so that the kernel fits in 64 registers and four 256-thread CTAs
 // (32 warps) share an SM: with fewer warps the per-row dependency chains (two shuffle reductions)
 // leave the schedulers idle.
-static bool pick_stream_geometry(long long nv, int* g, int* ch) {
+// `wide` (fp32 inputs: two register pairs per vector instead of four) allows up to eight vectors per lane.
+static bool pick_stream_geometry(long long nv, bool wide, int* g, int* ch) {
   if (nv <= 8) { *g = 8; *ch = 1; return true; }
   if (nv <= 16) { *g = 8; *ch = 2; return true; }
   if (nv <= 24) { *g = 8; *ch = 3; return true; }
@@ -384,6 +385,8 @@ static bool pick_stream_geometry(long long nv, int* g, int* ch) {
   if (nv <= 64) { *g = 16; *ch = 4; return true; }
   if (nv <= 96) { *g = 32; *ch = 3; return true; }
   if (nv <= 128) { *g = 32; *ch = 4; return true; }
+  if (wide && nv <= 192) { *g = 32; *ch = 6; return true; }
+  if (wide && nv <= 256) { *g = 32; *ch = 8; return true; }
   return false;
 }
 
@@ -400,7 +403,7 @@ static bool try_launch_norm_fwd_stream(const NormFwdParams& p, cudaStream_t st, 
   constexpr int V = Elem<Tin>::V;
   const long long nv = p.n / V;
   int g, ch;
-  if (streaming_disabled() || !pick_stream_geometry(nv, &g, &ch)) return false;
+  if (streaming_disabled() || !pick_stream_geometry(nv, V == 4, &g, &ch)) return false;
   if (p.rows > 0x7ffff000LL) return false;  // the kernel counts rows and tiles in 32 bits
   const long long total_bytes = p.rows * nv * 16;
   if (total_bytes < (8ll << 20)) return false;  // small problems: the resident kernel is fine
@@ -409,11 +412,15 @@ static bool try_launch_norm_fwd_stream(const NormFwdParams& p, cudaStream_t st, 
   // 128 threads: eight small CTAs per SM keep each other busy across the per-tile barrier better than
   // four of 256 (measured on the 32768 x 768 bf16 case: 18.3 us against 19.7 us)
   const int threads = threads_env ? threads_env : 128;
-  const int ctas_per_sm = 1024 / threads;
   const int R = threads / g;
   const size_t tile_bytes = (size_t)R * nv * 16;
   const size_t fixed = 2 * (size_t)nv * V * sizeof(float) + 8 * sizeof(uint64_t);
-  const size_t per_cta = ((size_t)dev.max_smem_optin - 1024 * ctas_per_sm) / ctas_per_sm;
+  // as many CTAs per SM as 1024 threads allow, fewer when two stages of long rows need the room
+  int ctas_per_sm = 1024 / threads;
+  const size_t usable = (size_t)dev.max_smem_optin;
+  while (ctas_per_sm > 2 && (usable - 1024 * (size_t)ctas_per_sm) / (size_t)ctas_per_sm < fixed + 2 * tile_bytes)
+    --ctas_per_sm;
+  const size_t per_cta = (usable - 1024 * (size_t)ctas_per_sm) / (size_t)ctas_per_sm;
   if (fixed + 2 * tile_bytes > per_cta) return false;
   int stages = (int)((per_cta - fixed) / tile_bytes);
   if (stages > 8) stages = 8;
@@ -437,6 +444,9 @@ static bool try_launch_norm_fwd_stream(const NormFwdParams& p, cudaStream_t st, 
   };
 #define B200_NFS(GG, CC)                                                            if (g == GG && ch == CC) {                                                          if (exact) launch(norm_fwd_stream_kernel<Tin, Tout, CC, GG, true>);               else launch(norm_fwd_stream_kernel<Tin, Tout, CC, GG, false>);                    return true;                                                                    }
   B200_NFS(8, 1) B200_NFS(8, 2) B200_NFS(8, 3) B200_NFS(8, 4) B200_NFS(16, 3) B200_NFS(16, 4) B200_NFS(32, 3) B200_NFS(32, 4)
+  if constexpr (V == 4) {
+    B200_NFS(32, 6) B200_NFS(32, 8)
+  }
 #undef B200_NFS
   return false;
 }

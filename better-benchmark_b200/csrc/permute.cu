@@ -41,14 +41,13 @@ __device__ __forceinline__ Tout convert_scaled(Tin v, float scale, int has_scale
 template <typename Tin, typename Tout, bool VEC>
 __global__ void __launch_bounds__(256) permute_general_kernel(const PermuteParams p) {
   constexpr int VIN = VEC ? Elem<Tin>::V : 1;
+  constexpr int U = VEC ? 4 : 1;  // independent 16-byte loads in flight per thread
   const long long units = p.total / VIN;
-  for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < units;
-       u += (long long)gridDim.x * blockDim.x) {
-    // decompose the unit index over (shape[0], shape[1], shape[2], shape[3] / VIN)
-    long long rest = u;
+  // input offset of unit u: decompose u over (shape[0], shape[1], shape[2], shape[3] / VIN)
+  auto in_offset = [&](long long u) {
     long long i3, i2, i1, i0;
-    if (rest < 0x7fffffffLL) {
-      unsigned int r = (unsigned int)rest;
+    if (u < 0x7fffffffLL) {
+      unsigned int r = (unsigned int)u;
       unsigned int q = fast_div(r, p.d3);
       i3 = r - q * p.d3.d; r = q;
       q = fast_div(r, p.d2);
@@ -57,26 +56,45 @@ __global__ void __launch_bounds__(256) permute_general_kernel(const PermuteParam
       i1 = r - q * p.d1.d;
       i0 = q;
     } else {
+      long long rest = u;
       const long long n3 = p.d3.d, n2 = p.d2.d, n1 = p.d1.d;
       i3 = rest % n3; rest /= n3;
       i2 = rest % n2; rest /= n2;
       i1 = rest % n1;
       i0 = rest / n1;
     }
-    const long long in_off = i0 * p.in_stride[0] + i1 * p.in_stride[1] + i2 * p.in_stride[2] +
-                             i3 * VIN * p.in_stride[3];
-    const Tin* src = reinterpret_cast<const Tin*>(p.x) + in_off;
-    Tout* dst = reinterpret_cast<Tout*>(p.y) + u * VIN;
+    return i0 * p.in_stride[0] + i1 * p.in_stride[1] + i2 * p.in_stride[2] + i3 * VIN * p.in_stride[3];
+  };
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long u0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; u0 < units; u0 += U * stride) {
     if constexpr (VEC) {
-      float f[VIN];
-      Elem<Tin>::unpack(ld_stream(src), f);
-      if (p.has_scale) {
+      uint4 raw[U];
 #pragma unroll
-        for (int i = 0; i < VIN; ++i) f[i] = f[i] * p.scale;
+      for (int k = 0; k < U; ++k) {
+        const long long u = u0 + k * stride;
+        if (u < units) raw[k] = ld_stream(reinterpret_cast<const Tin*>(p.x) + in_offset(u));
       }
-      store_converted<Tout, VIN>(dst, f);
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        const long long u = u0 + k * stride;
+        if (u < units) {
+          Tout* dst = reinterpret_cast<Tout*>(p.y) + u * VIN;
+          if (std::is_same<Tin, Tout>::value && !p.has_scale) {
+            st_stream(reinterpret_cast<Tin*>(dst), raw[k]);  // plain copy: no conversion at all
+          } else {
+            float f[VIN];
+            Elem<Tin>::unpack(raw[k], f);
+            if (p.has_scale) {
+#pragma unroll
+              for (int i = 0; i < VIN; ++i) f[i] = f[i] * p.scale;
+            }
+            store_converted<Tout, VIN>(dst, f);
+          }
+        }
+      }
     } else {
-      *dst = convert_scaled<Tin, Tout>(*src, p.scale, p.has_scale);
+      const Tin* src = reinterpret_cast<const Tin*>(p.x) + in_offset(u0);
+      reinterpret_cast<Tout*>(p.y)[u0] = convert_scaled<Tin, Tout>(*src, p.scale, p.has_scale);
     }
   }
 }
