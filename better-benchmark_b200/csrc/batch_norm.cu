@@ -760,6 +760,16 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
       }
     }
   }
+  // weight and bias of this lane's channels: fetched before the grid-wide wait, used after it
+  f32x2 w2[V / 2], b2[V / 2];
+#pragma unroll
+  for (int i = 0; i < V / 2; ++i) {
+    const int c = vc * V + 2 * i;
+    w2[i] = p.weight ? pack2(load_param1(p.weight, p.w_dtype, c), load_param1(p.weight, p.w_dtype, c + 1))
+                     : splat2(1.f);
+    b2[i] = p.bias ? pack2(load_param1(p.bias, p.w_dtype, c), load_param1(p.bias, p.w_dtype, c + 1))
+                   : splat2(0.f);
+  }
   B200_WMARK(2)
   bool ok = !failed && grid_barrier(p.bar, 1u, &bar_ok);
   B200_WMARK(3)
@@ -840,7 +850,7 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
   B200_WMARK(5)
   // ---- pass 2: normalise, chunks in reverse order -------------------------------------------------
   if (ok && p.y && n_chunks > 0) {
-    f32x2 mean2[V / 2], inv2[V / 2], w2[V / 2], b2[V / 2];
+    f32x2 mean2[V / 2], inv2[V / 2];
 #pragma unroll
     for (int i = 0; i < V / 2; ++i) {
       const int c = vc * V + 2 * i;
@@ -851,10 +861,6 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
         mean2[i] = pack2(__ldcg(p.stats + c), __ldcg(p.stats + c + 1));
         inv2[i] = pack2(__ldcg(p.stats + p.channels + c), __ldcg(p.stats + p.channels + c + 1));
       }
-      w2[i] = p.weight ? pack2(load_param1(p.weight, p.w_dtype, c), load_param1(p.weight, p.w_dtype, c + 1))
-                       : splat2(1.f);
-      b2[i] = p.bias ? pack2(load_param1(p.bias, p.w_dtype, c), load_param1(p.bias, p.w_dtype, c + 1))
-                     : splat2(0.f);
     }
     const int* ids = q_ids;  // complete and final by now
     const int resident_from = n_chunks - (n_chunks < stages ? n_chunks : stages);  // chunks >= this are in smem

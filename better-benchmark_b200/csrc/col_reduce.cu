@@ -115,26 +115,34 @@ __global__ void __launch_bounds__(256) col_reduce_kernel(const ColReduceParams p
   }
 }
 
+// Combines the splits: a CTA takes 32 outputs (lanes), its eight warps take the splits w, w+8, ...
+// with all their loads in flight together, and warp 0 adds the eight partial sums in order (fp64).
 template <bool IS_MAX>
 __global__ void __launch_bounds__(256) col_reduce_finalize_kernel(const ColReduceParams p) {
-  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // over batch * cols
-  if (idx >= p.batch * p.cols) return;
-  const long long b = idx / p.cols, col = idx - b * p.cols;
-  if (IS_MAX) {
-    float r = -INFINITY;
-    for (int s = 0; s < p.splits; ++s) r = MaxOp::apply(r, p.partials[(long long)s * p.batch * p.cols + idx]);
-    store_out(p.out, p.out_dtype, b * p.out_batch_stride + col, r);
-  } else {
-    double r = 0.0;
-    for (int s0 = 0; s0 < p.splits; s0 += 8) {  // eight loads in flight, then added in order
-      float v[8];
+  __shared__ double red[8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const long long total = p.batch * p.cols;
+  const long long idx = (long long)blockIdx.x * 32 + lane;  // over batch * cols
+  const bool live = idx < total;
+  double r = IS_MAX ? -INFINITY : 0.0;
+  for (int s0 = warp; s0 < p.splits; s0 += 8 * 8) {
+    float v[8];
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
-        v[u] = s0 + u < p.splits ? p.partials[(long long)(s0 + u) * p.batch * p.cols + idx] : 0.f;
-#pragma unroll
-      for (int u = 0; u < 8; ++u) r += (double)v[u];
+    for (int u = 0; u < 8; ++u) {
+      const int sp = s0 + 8 * u;
+      v[u] = (live && sp < p.splits) ? p.partials[(long long)sp * total + idx] : (IS_MAX ? -INFINITY : 0.f);
     }
-    store_out(p.out, p.out_dtype, b * p.out_batch_stride + col, (float)r * p.post_scale);
+#pragma unroll
+    for (int u = 0; u < 8; ++u) r = IS_MAX ? (double)MaxOp::apply((float)r, v[u]) : r + (double)v[u];
+  }
+  red[warp][lane] = r;
+  __syncthreads();
+  if (warp == 0 && live) {
+    double t = red[0][lane];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) t = IS_MAX ? (double)MaxOp::apply((float)t, (float)red[w][lane]) : t + red[w][lane];
+    const long long b = idx / p.cols, col = idx - b * p.cols;
+    store_out(p.out, p.out_dtype, b * p.out_batch_stride + col, IS_MAX ? (float)t : (float)t * p.post_scale);
   }
 }
 
@@ -159,7 +167,7 @@ static int launch_col_reduce(ColReduceParams p, bool vec, size_t scratch_bytes, 
   if (max_splits < 1) max_splits = 1;
   long long splits = (4LL * sms + base - 1) / base;
   if (splits > max_splits) splits = max_splits;
-  for (long long s = splits; s <= max_splits && s <= 3 * splits; ++s) {
+  for (long long s = splits; s <= max_splits && s <= 2 * splits; ++s) {
     const long long ctas = s * base;
     if (ctas < slots) continue;
     const long long waves = (ctas + slots - 1) / slots;
@@ -186,8 +194,8 @@ static int launch_col_reduce(ColReduceParams p, bool vec, size_t scratch_bytes, 
   int rc = launch_status("b200_col_reduce");
   if (rc != B200_OK || splits == 1) return rc;
   const long long total = p.batch * p.cols;
-  if (is_max) col_reduce_finalize_kernel<true><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p);
-  else col_reduce_finalize_kernel<false><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p);
+  if (is_max) col_reduce_finalize_kernel<true><<<(unsigned)((total + 31) / 32), 256, 0, st>>>(p);
+  else col_reduce_finalize_kernel<false><<<(unsigned)((total + 31) / 32), 256, 0, st>>>(p);
   return launch_status("b200_col_reduce finalize");
 }
 

@@ -48,6 +48,7 @@ struct NormBwdParams {
   long long dx_batch_stride, dx_seq_stride, dx_head_stride;
   float n_f;
   float* partials;    // [groups][n] for dw, followed by [groups][n] for db
+  double* level2;     // [2][slices][n]: second level of the fused finalize (may be null)
   unsigned int* bar;  // grid barrier words (cooperative variant)
   int groups;
   int fused;  // 1: barrier + finalize inside this launch
@@ -97,6 +98,66 @@ __device__ __forceinline__ void finalize_columns(const float* partials, int grou
     }
     __syncthreads();
   }
+}
+
+// Two-level variant for grids much larger than the number of 64-column chunks (narrow rows): with
+// one chunk per CTA only n/64 CTAs would add up all the partial rows while the rest of the grid
+// idles. Level 1: CTA b sums chunk b % chunks over the partial rows slice, slice + slices, ...
+// (slice = b / chunks) and writes fp64 sums; a grid barrier; level 2: the first `chunks` CTAs add
+// the slices in order. `which` selects the dw (0) or db (1) plane of `level2`.
+__device__ __forceinline__ void finalize_level1(const float* partials, int groups, int n, double* level2, int slices,
+                                                double* smem /* [warps][64] */) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  const int chunks = (n + 63) / 64;
+  if ((int)blockIdx.x >= chunks * slices) return;
+  const int chunk = blockIdx.x % chunks, slice = blockIdx.x / chunks;
+  const int c0 = chunk * 64 + lane, c1 = c0 + 32;
+  double a0 = 0.0, a1 = 0.0;
+  for (int k0 = warp; slice + slices * k0 < groups; k0 += 4 * nwarps) {
+    float v0[4], v1[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int g = slice + slices * (k0 + u * nwarps);
+      const float* row = partials + (long long)g * n;
+      v0[u] = (g < groups && c0 < n) ? __ldcg(row + c0) : 0.f;
+      v1[u] = (g < groups && c1 < n) ? __ldcg(row + c1) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      a0 += (double)v0[u];
+      a1 += (double)v1[u];
+    }
+  }
+  smem[warp * 64 + lane] = a0;
+  smem[warp * 64 + 32 + lane] = a1;
+  __syncthreads();
+  if (warp == 0) {
+    double s0 = 0.0, s1 = 0.0;
+    for (int w = 0; w < nwarps; ++w) {
+      s0 += smem[w * 64 + lane];
+      s1 += smem[w * 64 + 32 + lane];
+    }
+    if (c0 < n) level2[(long long)slice * n + c0] = s0;
+    if (c1 < n) level2[(long long)slice * n + c1] = s1;
+  }
+  __syncthreads();
+}
+
+__device__ __forceinline__ void finalize_level2(const double* level2, int slices, int n, float* out) {
+  const int chunks = (n + 63) / 64;
+  if ((int)blockIdx.x >= chunks || threadIdx.x >= 64) return;
+  const int c = blockIdx.x * 64 + threadIdx.x;
+  if (c >= n) return;
+  double s = 0.0;
+  for (int k0 = 0; k0 < slices; k0 += 8) {  // eight loads in flight, added in order
+    double v[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u)
+      v[u] = k0 + u < slices ? __ldcg(level2 + (long long)(k0 + u) * n + c) : 0.0;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) s += v[u];
+  }
+  out[c] = (float)s;
 }
 
 template <typename T, int CH, bool BLOCK, bool LN>
@@ -556,7 +617,8 @@ __device__ __forceinline__ float warp_reduce_multi(float (&v)[N], int lane) {
 }
 
 template <typename T, int R, bool LN, bool GROUPED>
-__global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdParams p, const int stages, const int TG) {
+__global__ void __launch_bounds__(512, 2)
+norm_bwd_tile_kernel(const NormBwdParams p, const int stages, const int TG, const int groups_arg, const int wpg_inv) {
   constexpr int V = Elem<T>::V;
   constexpr int NVAL = R * (LN ? 2 : 1);  // row sums per tile: 2, 4 or 8
   constexpr int LPV = 32 / NVAL;          // lanes that share one value after the warp reduction
@@ -573,8 +635,11 @@ __global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdPara
   // (the launcher keeps the ring at 8 KB or more)
   double* fin = reinterpret_cast<double*>(smem);
   const int lane = threadIdx.x & 31;
-  const int GROUPS = GROUPED ? (int)blockDim.x / TG : 1;
-  const int grp = GROUPED ? (int)threadIdx.x / TG : 0;
+  // group of this thread = (warp index) / (warps per group), as a multiplication by the 16.16
+  // reciprocal the launcher passes: a plain division here gets recomputed in the loop when
+  // registers are short, and costs twenty instructions each time
+  const int GROUPS = GROUPED ? groups_arg : 1;
+  const int grp = GROUPED ? (int)((threadIdx.x >> 5) * (unsigned)wpg_inv) >> 16 : 0;
   const int tid = threadIdx.x - grp * TG;        // thread within its row group
   const int warp = tid >> 5;                     // warp within its row group
   const int TR = GROUPS * R;                     // rows per tile
@@ -818,8 +883,20 @@ __global__ void __launch_bounds__(512, 2) norm_bwd_tile_kernel(const NormBwdPara
     }
   }
   if (p.fused) {
-    const bool ok = !failed && grid_barrier(p.bar, 1u, &bar_ok);
-    if (ok) {
+    bool ok = !failed && grid_barrier(p.bar, 1u, &bar_ok);
+    const int chunks = (p.n + 63) / 64;
+    const int slices = (int)gridDim.x / chunks;
+    if (ok && p.level2 != nullptr && slices >= 2) {
+      double* l2w = p.level2;
+      double* l2b = p.level2 + (long long)slices * p.n;
+      if (p.dw) finalize_level1(p.partials, p.groups, p.n, l2w, slices, fin);
+      if (LN && p.db) finalize_level1(p.partials + (long long)p.groups * p.n, p.groups, p.n, l2b, slices, fin);
+      ok = grid_barrier(p.bar, 2u, &bar_ok);
+      if (ok) {
+        if (p.dw) finalize_level2(l2w, slices, p.n, p.dw);
+        if (LN && p.db) finalize_level2(l2b, slices, p.n, p.db);
+      }
+    } else if (ok) {
       if (p.dw) finalize_columns(p.partials, p.groups, p.n, p.dw, fin);
       if (LN && p.db) finalize_columns(p.partials + (long long)p.groups * p.n, p.groups, p.n, p.db, fin);
     }
@@ -1007,11 +1084,16 @@ static bool try_launch_norm_bwd_tile(NormBwdParams p, int threads, size_t scratc
   const int tg = threads;
   int groups_per_cta = 512 / tg;
   if (groups_per_cta > 8) groups_per_cta = 8;
+  static const int groups_env = [] { const char* e = getenv("B200_NORM_BWD_GROUPS"); return e ? atoi(e) : 0; }();
+  if (groups_env > 0 && groups_env < groups_per_cta) groups_per_cta = groups_env;
   if (groups_per_cta < 1) groups_per_cta = 1;
   threads = tg * groups_per_cta;
   const size_t stage_bytes = 2 * (size_t)groups_per_cta * (size_t)R * (size_t)(p.n / V) * 16;
   const size_t static_bytes = (groups_per_cta > 1 ? 8 : 1) * 2 * 8 * 16 * sizeof(float) + 256;  // row-sum tables + flags
-  const size_t per_cta = ((size_t)dev.max_smem_optin - 2048) / 2;  // two CTAs per SM
+  int ctas_per_sm = 1024 / threads;  // 64 registers per thread: 1024 threads per SM
+  if (ctas_per_sm < 2) ctas_per_sm = 2;
+  if (ctas_per_sm > 8) ctas_per_sm = 8;
+  const size_t per_cta = ((size_t)dev.max_smem_optin - 1024 * (size_t)ctas_per_sm) / (size_t)ctas_per_sm;
   const size_t fixed = 8 * sizeof(uint64_t);
   const int min_stages = groups_per_cta > 1 ? 2 : 3;
   if (per_cta < static_bytes + fixed + (size_t)min_stages * stage_bytes) return false;
@@ -1040,10 +1122,19 @@ static bool try_launch_norm_bwd_tile(NormBwdParams p, int threads, size_t scratc
   }
   p.groups = (int)grid;
   p.fused = cooperative ? 1 : 0;
-  int tg_arg = tg;
+  p.level2 = nullptr;
+  if (cooperative && (p.dw || p.db)) {  // room for the second level of the finalize behind the partial planes?
+    const long long chunks = (p.n + 63) / 64;
+    const long long slices = grid / chunks;
+    const long long planes = 256 + 2LL * grid * p.n * (long long)sizeof(float);
+    const long long need = (planes + 7) / 8 * 8 + 2LL * slices * p.n * (long long)sizeof(double);
+    if (slices >= 2 && (long long)scratch_bytes >= need)
+      p.level2 = reinterpret_cast<double*>(reinterpret_cast<char*>(p.bar) + (planes + 7) / 8 * 8);
+  }
+  int tg_arg = tg, groups_arg = groups_per_cta, wpg_inv_arg = (65536 + tg / 32 - 1) / (tg / 32);
   if (cooperative) {
     int stages_arg = stages;
-    void* args[] = {&p, &stages_arg, &tg_arg};
+    void* args[] = {&p, &stages_arg, &tg_arg, &groups_arg, &wpg_inv_arg};
     e = cudaLaunchCooperativeKernel(reinterpret_cast<const void*>(kernel), dim3((unsigned)grid), dim3(threads),
                                     args, smem, st);
     if (e != cudaSuccess) {
@@ -1055,7 +1146,7 @@ static bool try_launch_norm_bwd_tile(NormBwdParams p, int threads, size_t scratc
     *rc = B200_OK;
     return true;
   }
-  kernel<<<(unsigned)grid, threads, smem, st>>>(p, stages, tg_arg);
+  kernel<<<(unsigned)grid, threads, smem, st>>>(p, stages, tg_arg, groups_arg, wpg_inv_arg);
   *rc = launch_status("b200_norm_bwd (row tiles)");
   if (*rc == B200_OK && (p.dw || p.db)) {
     norm_bwd_finalize_kernel<<<(p.n + 63) / 64, 512, 0, st>>>(p);
@@ -1212,7 +1303,7 @@ extern "C" int b200_norm_bwd(const void* x, const void* dy, const void* weight, 
   p.n_f = (float)n;
   p.bar = reinterpret_cast<unsigned int*>(scratch);
   p.partials = scratch ? reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + 256) : nullptr;
-  p.groups = 0; p.fused = 0;
+  p.groups = 0; p.fused = 0; p.level2 = nullptr;
   const bool cooperative = (flags & 1) == 0 && (dweight || dbias);
 
   const int eb = dtype_size(x_dtype), wb = dtype_size(w_dtype);

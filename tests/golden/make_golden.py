@@ -1,9 +1,9 @@
 """Generate the golden fixtures in this directory from the reference itself.
 
-Run in a container that has the reference checkout (default /root/reference, override with the
-REFERENCE_ROOT environment variable):
+Run where a checkout of the reference exists; give its path as the argument or in the
+REFERENCE_ROOT environment variable:
 
-    python tests/golden/make_golden.py
+    python tests/golden/make_golden.py <path to the better-benchmark checkout>
 
 For every case below the script loads the reference's own ``Repro`` module from
 ``repros/canonical/<dir>/repro.py``, builds inputs with the reference's own
@@ -18,7 +18,10 @@ from pathlib import Path
 
 import torch
 
-REFERENCE_ROOT = Path(os.environ.get("REFERENCE_ROOT", "/root/reference"))
+_root = os.environ.get("REFERENCE_ROOT") or (sys.argv[1] if len(sys.argv) > 1 else "")
+if not _root:
+    raise SystemExit("usage: make_golden.py <path to the reference checkout>  (or set REFERENCE_ROOT)")
+REFERENCE_ROOT = Path(_root)
 HERE = Path(__file__).resolve().parent
 
 # case name -> (canonical dir in the reference, compact input entries at a reduced shape)
