@@ -648,6 +648,9 @@ norm_bwd_tile_kernel(const NormBwdParams p, const int stages, const int TG, cons
   const uint32_t row_bytes = (uint32_t)nv * 16u;
   const uint32_t stage_bytes = 2u * TR * row_bytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)stages * stage_bytes);
+  // LayerNorm keeps three register arrays per thread already (dweight, dbias, and the row data of
+  // the pass at hand): its weight slice lives in shared memory as fp32, behind the barriers.
+  float* wsm = reinterpret_cast<float*>(smem + (size_t)stages * stage_bytes + 8 * sizeof(uint64_t));
   const int rows = (int)p.rows;  // the launcher admits fewer than 2^31 rows
   const int tiles = (rows + TR - 1) / TR;
   const int my_tiles = tiles > (int)blockIdx.x ? (tiles - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
@@ -685,7 +688,7 @@ norm_bwd_tile_kernel(const NormBwdParams p, const int stages, const int TG, cons
   }
 
   // A thread owns the same V columns in every row: weight slice and gradient sums in registers.
-  f32x2 wv[V / 2], acc_w[V / 2], acc_b[LN ? V / 2 : 1];
+  f32x2 wv[LN ? 1 : V / 2], acc_w[V / 2], acc_b[LN ? V / 2 : 1];
   {
     float wf[V];
     if (p.w && active) {
@@ -696,12 +699,25 @@ norm_bwd_tile_kernel(const NormBwdParams p, const int stages, const int TG, cons
     }
 #pragma unroll
     for (int i = 0; i < V / 2; ++i) {
-      wv[i] = pack2(wf[2 * i], wf[2 * i + 1]);
+      if constexpr (LN) {
+        if (grp == 0 && active) {
+          wsm[tid * V + 2 * i] = wf[2 * i];
+          wsm[tid * V + 2 * i + 1] = wf[2 * i + 1];
+        }
+      } else {
+        wv[i] = pack2(wf[2 * i], wf[2 * i + 1]);
+      }
       acc_w[i] = splat2(0.f);
     }
 #pragma unroll
     for (int i = 0; i < (LN ? V / 2 : 1); ++i) acc_b[i] = splat2(0.f);
+    if constexpr (LN) {
+      wv[0] = splat2(0.f);
+      __syncthreads();  // the weight slice is read by every row group
+    }
   }
+  const f32x2* wrow = reinterpret_cast<const f32x2*>(wsm + (size_t)tid * V);
+  auto weight = [&](int i) { return LN ? wrow[i] : wv[LN ? 0 : i]; };
   // dx offsets fit 32 bits (checked by the launcher): one 64-bit address per store.
   const int col = tid * V;
   const uint32_t dx_col = active ? (uint32_t)(col / p.head_dim) * (uint32_t)p.dx_head_stride + (uint32_t)(col % p.head_dim) : 0u;
@@ -737,7 +753,7 @@ norm_bwd_tile_kernel(const NormBwdParams p, const int stages, const int TG, cons
         Pairs<T>::unpack(*reinterpret_cast<const uint4*>(sy + (size_t)r * row_bytes), dy2);
 #pragma unroll
         for (int i = 0; i < V / 2; ++i) {
-          const f32x2 g2 = mul2(dy2[i], wv[i]);
+          const f32x2 g2 = mul2(dy2[i], weight(i));
           if constexpr (LN) {
             s1 = add2(s1, g2);
             s2 = add2(s2, mul2(g2, mul2(sub2(x2[i], splat2(mean[r])), splat2(rstd[r]))));
@@ -826,7 +842,7 @@ norm_bwd_tile_kernel(const NormBwdParams p, const int stages, const int TG, cons
           const f32x2 mean2 = splat2(mean[r]);
 #pragma unroll
           for (int i = 0; i < V / 2; ++i) {
-            const f32x2 g2 = mul2(dy2[i], wv[i]);
+            const f32x2 g2 = mul2(dy2[i], weight(i));
             const f32x2 xhat = mul2(sub2(x2[i], mean2), rstd2);
             acc_w[i] = add2(acc_w[i], mul2(dy2[i], xhat));
             acc_b[i] = add2(acc_b[i], dy2[i]);
@@ -839,7 +855,7 @@ norm_bwd_tile_kernel(const NormBwdParams p, const int stages, const int TG, cons
           const f32x2 k2 = splat2(kf * 2.0f);
 #pragma unroll
           for (int i = 0; i < V / 2; ++i) {
-            const f32x2 g2 = mul2(dy2[i], wv[i]);
+            const f32x2 g2 = mul2(dy2[i], weight(i));
             acc_w[i] = add2(acc_w[i], mul2(dy2[i], mul2(x2[i], rstd2)));
             o2[i] = add2(mul2(g2, rstd2), mul2(k2, x2[i]));
           }
@@ -1094,7 +1110,7 @@ static bool try_launch_norm_bwd_tile(NormBwdParams p, int threads, size_t scratc
   if (ctas_per_sm < 2) ctas_per_sm = 2;
   if (ctas_per_sm > 8) ctas_per_sm = 8;
   const size_t per_cta = ((size_t)dev.max_smem_optin - 1024 * (size_t)ctas_per_sm) / (size_t)ctas_per_sm;
-  const size_t fixed = 8 * sizeof(uint64_t);
+  const size_t fixed = 8 * sizeof(uint64_t) + (LN ? (size_t)p.n * sizeof(float) : 0);  // barriers (+ fp32 weight)
   const int min_stages = groups_per_cta > 1 ? 2 : 3;
   if (per_cta < static_bytes + fixed + (size_t)min_stages * stage_bytes) return false;
   int stages = (int)((per_cta - static_bytes - fixed) / stage_bytes);
