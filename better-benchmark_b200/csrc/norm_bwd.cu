@@ -1086,7 +1086,7 @@ static bool try_launch_norm_bwd_stream(NormBwdParams p, int threads, size_t scra
 // Row-tile streaming launch (one vector per thread); returns false when the shape does not fit.
 template <typename T, int R, bool LN>
 static bool try_launch_norm_bwd_tile(NormBwdParams p, int threads, size_t scratch_bytes, bool cooperative,
-                                     cudaStream_t st, int* rc) {
+                                     cudaStream_t st, int* rc, int want_groups = 0) {
   constexpr int V = Elem<T>::V;
   if (streaming_disabled() || p.rows < 1024 || threads > 512) return false;
   {  // the kernel addresses dx with 32-bit element offsets
@@ -1102,6 +1102,7 @@ static bool try_launch_norm_bwd_tile(NormBwdParams p, int threads, size_t scratc
   if (groups_per_cta > 8) groups_per_cta = 8;
   static const int groups_env = [] { const char* e = getenv("B200_NORM_BWD_GROUPS"); return e ? atoi(e) : 0; }();
   if (groups_env > 0 && groups_env < groups_per_cta) groups_per_cta = groups_env;
+  if (want_groups > 0 && want_groups < groups_per_cta) groups_per_cta = want_groups;
   if (groups_per_cta < 1) groups_per_cta = 1;
   threads = tg * groups_per_cta;
   const size_t stage_bytes = 2 * (size_t)groups_per_cta * (size_t)R * (size_t)(p.n / V) * 16;
@@ -1225,7 +1226,10 @@ static int launch_norm_bwd(NormBwdParams p, bool vector_ok, size_t scratch_bytes
       if (nv > 32 && tile_rows_override() != 1) {  // column-owner CTAs of 2..4 warps, several rows per barrier
         int rc = B200_OK;
         const int narrow = (int)((nv + 31) / 32 * 32);
-        if (try_launch_norm_bwd_tile<T, 4, LN>(p, narrow, scratch_bytes, cooperative, st, &rc)) return rc;
+        // four rows per group and barrier when two stages of that fit (with fewer groups if need
+        // be: more work per barrier beats more groups), else two rows
+        for (int g = 512 / narrow; g >= 3; --g)
+          if (try_launch_norm_bwd_tile<T, 4, LN>(p, narrow, scratch_bytes, cooperative, st, &rc, g)) return rc;
         if (try_launch_norm_bwd_tile<T, 2, LN>(p, narrow, scratch_bytes, cooperative, st, &rc)) return rc;
       }
       if (nv <= 32) return launch_norm_bwd_fast<T, 1, false, LN>(p, 256, scratch_bytes, cooperative, st);
