@@ -545,6 +545,20 @@ def do_bench(fn, *, warmup=25, rep=100, return_mode="min", device="cuda"):
     raise ValueError(f"unknown return_mode {return_mode!r}")
 
 
+def memcpy_sol_us(total_bytes: int, *, device="cuda", warmup=10, rep=50) -> float:
+    """The reference's speed-of-light yardstick for a region of ``total_bytes`` (read + write):
+    ``torch.add(src, 1, out=dst)`` over ``total_bytes // 8`` fp32 elements, i.e. half of the bytes
+    read and half written, timed like everything else (CUDA-graph replay from a flushed L2, min).
+    ``repro_harness.py:952-958``, ``scripts/bench_parallel.py:3712-3719``. Microseconds."""
+    n = max(1, int(total_bytes) // 8)
+    src = torch.empty(n, dtype=torch.float32, device=device)
+    dst = torch.empty_like(src)
+    torch.add(src, 1, out=dst)
+    torch.cuda.synchronize()
+    graph, _ = _capture_graph_checked(lambda: torch.add(src, 1, out=dst))
+    return _time_graph(graph, warmup=warmup, rep=rep)
+
+
 def _time_graph(graph, warmup, rep) -> float:
     """Microseconds of one graph replay from a flushed L2 (min over the repetitions)."""
     return do_bench(lambda: graph.replay(), warmup=warmup, rep=rep, return_mode="min") * 1000.0
@@ -574,7 +588,7 @@ _INVALID_STATUSES = frozenset({"UNVERIFIED_NUMERICS", "INVALID_CUDAGRAPH_WARNING
 
 def bench_oracle(oracle_forward, instance, inputs, repro_id, *, warmup=25, rep=200, rounds=5,
                  _skip_numerics_gate=False, numerics_optout=None, disable_gpu_lock=False,
-                 compile_reference=True, region_bytes=None, peak_gbps=None) -> dict:
+                 compile_reference=True, region_bytes=None, peak_gbps=None, memcpy_sol=False) -> dict:
     """Time the oracle (and, by default, ``torch.compile`` of the eager module) as CUDA-graph
     replays from a flushed L2: min over ``rounds`` interleaved rounds, under the exclusive GPU lock.
 
@@ -669,6 +683,10 @@ def bench_oracle(oracle_forward, instance, inputs, repro_id, *, warmup=25, rep=2
     result["status"] = status
     if gate is not None:
         result["numerics_gate"] = gate
+    if region_bytes and memcpy_sol:
+        sol = memcpy_sol_us(region_bytes, device=_get_device(inputs))
+        result["sol_us"] = round(sol, 2)
+        result["gap"] = round(best_oracle / sol, 3) if sol > 0 else None
     if region_bytes:
         gbps = region_bytes / (best_oracle * 1e-6) / 1e9
         result["region_bytes"] = int(region_bytes)

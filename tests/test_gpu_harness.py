@@ -103,3 +103,13 @@ def test_sweep_of_the_five_directories_on_one_gpu(tmp_path):
         assert point["region_bytes"] == wl.algorithmic_bytes, (wl.name, point["region_bytes"])
         assert 0.05 < point["sol_frac"] < 1.3
     assert summary["n_workers"] == 2 and summary["n_ok"] == 5
+
+
+def test_memcpy_sol_yardstick_and_gap_column(tmp_path):
+    from better_benchmark_b200 import harness
+    us = harness.memcpy_sol_us(200 << 20)
+    assert 20 < us < 80, f"a 200 MiB read+write at {us:.1f} us is not a B200 number"
+    wl, d, fn, harness, label, inputs = _load(tmp_path, "c3_masked_softmax")
+    r = harness.bench_oracle(fn, harness.get_repro_instance(d), inputs, "sol", warmup=3, rep=20,
+                             compile_reference=False, region_bytes=wl.algorithmic_bytes, memcpy_sol=True)
+    assert r["status"] == "TIMED" and r["sol_us"] > 0 and 0.5 < r["gap"] < 3.0
