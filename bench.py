@@ -17,9 +17,14 @@ by rank 0.
   roofline   the dominant (here: only) kernel of the step against the measured HBM peak.
   e2e        the same metric through the public entry point with HOST buffers: every step copies
              the inputs from pinned host memory, runs ``oracle_forward`` and copies every output
-             back to pinned host memory.
+             back to pinned host memory. Upload, kernel and download of neighbouring steps overlap
+             (three streams, two buffer sets); every step's copies are inside the timed region.
   cpu_baseline  the eager module of the same region on the host cores (rank 0, N = 1).
   per_config the other four baseline configurations, timed the same way as ``value``.
+  families   one case per kernel family outside the five configurations (``family_cases.py``).
+
+``--sweep`` runs the corpus sweep (persistent worker processes, tasks sharded over the first N
+visible GPUs) on the five configuration directories and reports its wall time instead.
 
 ``--impl reference`` times only the eager module on the host cores (the reference's own CPU
 path for this region) and prints the same metric with ``"impl": "reference"``.
@@ -225,40 +230,70 @@ def time_steps(workload, input_sets, steps, warmup, barrier):
 
 
 def time_e2e(workload, device, steps, warmup):
-    """Milliseconds per step with host buffers: H2D of every input, the oracle, D2H of every
-    output; returns (ms_per_step, h2d_bytes, d2h_bytes)."""
+    """Milliseconds per step with host buffers: H2D of every input from pinned memory, the oracle,
+    D2H of every output into pinned memory, every step. The three legs run on three streams with two
+    sets of device buffers, so that the upload of step i+1 and the download of step i-1 overlap the
+    kernel of step i (PCIe is full duplex); events order them. Returns (ms_per_step, h2d, d2h)."""
     import torch
     host_inputs = [t.pin_memory() if isinstance(t, torch.Tensor) else t for t in workload.make_inputs("cpu", 1)]
-    dev_inputs = [torch.empty_like(t, device=device) if isinstance(t, torch.Tensor) else t for t in host_inputs]
-    # channels-last and other dense layouts survive empty_like; keep strides identical
-    for h, d in zip(host_inputs, dev_inputs):
+    NBUF = 2
+    dev_inputs = [[torch.empty_like(t, device=device) if isinstance(t, torch.Tensor) else t for t in host_inputs]
+                  for _ in range(NBUF)]
+    for h, d in zip(host_inputs, dev_inputs[0]):  # channels-last and other dense layouts keep their strides
         if isinstance(h, torch.Tensor):
             assert h.stride() == d.stride()
     h2d = sum(t.numel() * t.element_size() for t in host_inputs if isinstance(t, torch.Tensor))
-    host_outputs = None
+    host_outputs = [None] * NBUF
+    s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    s_comp = torch.cuda.current_stream(device)
+    in_ready = [torch.cuda.Event() for _ in range(NBUF)]
+    comp_done = [torch.cuda.Event() for _ in range(NBUF)]
+    out_done = [torch.cuda.Event() for _ in range(NBUF)]
+    used = [False] * NBUF
+    keep = [None] * NBUF  # the outputs of the step that used buffer set b, alive until their download ran
 
-    def step():
-        nonlocal host_outputs
-        for h, d in zip(host_inputs, dev_inputs):
-            if isinstance(h, torch.Tensor):
-                d.copy_(h, non_blocking=True)
-        outs = workload.oracle_forward(dev_inputs)
+    def step(i):
+        b = i % NBUF
+        with torch.cuda.stream(s_in):
+            if used[b]:
+                s_in.wait_event(comp_done[b])  # the kernel of step i-2 has read this buffer set
+            for h, d in zip(host_inputs, dev_inputs[b]):
+                if isinstance(h, torch.Tensor):
+                    d.copy_(h, non_blocking=True)
+            in_ready[b].record(s_in)
+        s_comp.wait_event(in_ready[b])
+        if used[b]:
+            # the download of step i-2 has read its outputs: only now may their memory return to the
+            # allocator (which hands it out again on this stream, in stream order)
+            s_comp.wait_event(out_done[b])
+        keep[b] = None
+        outs = workload.oracle_forward(dev_inputs[b])
         outs = [outs] if isinstance(outs, torch.Tensor) else list(outs)
-        if host_outputs is None:
-            host_outputs = [torch.empty_strided(o.shape, o.stride(), dtype=o.dtype).pin_memory() for o in outs]
-        for o, h in zip(outs, host_outputs):
-            h.copy_(o, non_blocking=True)
+        keep[b] = outs
+        comp_done[b].record(s_comp)
+        if host_outputs[b] is None:
+            host_outputs[b] = [torch.empty_strided(o.shape, o.stride(), dtype=o.dtype).pin_memory() for o in outs]
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(comp_done[b])
+            if used[b]:
+                s_out.wait_event(out_done[b])
+            for o, h in zip(outs, host_outputs[b]):
+                h.copy_(o, non_blocking=True)
+            out_done[b].record(s_out)
+        used[b] = True
 
-    for _ in range(max(1, warmup)):
-        step()
+    for i in range(max(2, warmup)):
+        step(i)
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    for _ in range(steps):
-        step()
-    end.record()
+    start.record(s_in)
+    for i in range(steps):
+        step(i)
+    s_out.wait_stream(s_comp)
+    s_out.wait_stream(s_in)
+    end.record(s_out)
     torch.cuda.synchronize()
-    d2h = sum(t.numel() * t.element_size() for t in host_outputs)
+    d2h = sum(t.numel() * t.element_size() for t in host_outputs[0])
     return start.elapsed_time(end) / steps, h2d, d2h
 
 
