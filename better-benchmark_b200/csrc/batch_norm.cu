@@ -479,42 +479,39 @@ batch_norm_cl_stream_kernel(const BatchNormParams p, const int stages, const int
 }
 
 // ----------------------------------------------------------------------------------------------
-// Channels-last fused kernel with one private copy ring per WARP and dynamic work distribution
-// (vpr = C / V a power of two <= 32; one CTA of 32 warps per SM, cooperative launch).
+// Channels-last fused kernel with one private copy ring per WARP (vpr = C / V a power of two
+// <= 32; one CTA of 32 warps per SM, cooperative launch).
 //
-// The CTA-wide ring above costs one CTA barrier per tile, which keeps 32 warps in lock step, and
-// its static split makes every CTA wait for the SM with the least memory bandwidth. Here:
-//   * x is cut into blocks of 32 chunks (a chunk = 32 * U vectors = 512 * U bytes); a CTA takes a
-//     block, warp w of the CTA takes chunk w of it. The first blocks of a CTA are fixed
-//     (b, b + grid, ...), the later ones are claimed from a global counter by thread 0, one claim
-//     in flight per chunk consumed, a few blocks ahead of use; the block numbers go to a queue in
-//     shared memory that all warps of the CTA read. Fast SMs therefore take more blocks.
+// The CTA-wide ring above costs one CTA barrier per tile, which keeps 32 warps in lock step. Here:
+//   * x is cut into blocks of 32 chunks (a chunk = 32 * U vectors = 512 * U bytes); CTA b takes the
+//     blocks b, b + grid, b + 2 grid, ...; warp w of the CTA takes chunk w of each. The list is
+//     fixed, so which thread sums which element never changes: the statistics are bit-reproducible.
 //   * each warp streams its chunks through its own ring: lane 0 starts the bulk copies, all lanes
 //     wait on the chunk's mbarrier, consume it, and after a __syncwarp lane 0 refills the slot.
 //     No CTA barrier in either pass; warps drift apart and hide each other's latencies.
-//   pass 1  the CTA's blocks in queue order; a warp's last `stages` chunks are never overwritten.
+//   * the per-chunk bookkeeping is 32-bit and incremental (a chunk is 32 elements per lane: every
+//     instruction spent on indices counts), and whole chunks - all but those of the very last
+//     block - take a path without per-vector bounds checks.
+//   pass 1  the CTA's blocks in order; a warp's last `stages` chunks are never overwritten (and are
+//           loaded with the evict-first hint: they will not be read from L2 again).
 //   stats   lanes that share a vector column are folded by shuffles, warps through shared memory,
 //           CTAs through the scratch buffer and one grid barrier (two for many channels), fp64.
 //   pass 2  the same blocks in reverse order: the resident chunks first, then the rest, each
 //           loaded again into the slot its successor freed (most recently read first: the
 //           likeliest to sit in L2).
-// Every wait is bounded (copies: mbar_wait; the queue: a counted spin); a wait that runs out makes
-// the CTA raise the error word of the grid barrier, wait for its own copies, and skip the rest.
+// Every wait is bounded (mbar_wait); a wait that runs out makes the CTA raise the error word of the
+// grid barrier, wait for its own copies, and skip the rest.
 // ----------------------------------------------------------------------------------------------
-constexpr int BN_QUEUE = 128;  // blocks one CTA can take (the launcher keeps the average far below)
-
 template <typename T, int U>
 __global__ void __launch_bounds__(1024, 1)
 batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int red_bytes, const int nblocks,
-                          const int dynamic) {
+                          const int flags) {
   constexpr int V = Elem<T>::V;
   constexpr uint32_t CHUNK_BYTES = 512u * U;
-  constexpr int CHUNK_VECS = 32 * U;
+  constexpr uint32_t CV = 32 * U;  // vectors per chunk
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int bar_ok;
   __shared__ int cta_failed;
-  __shared__ int q_ids[BN_QUEUE];  // block numbers in the order this CTA takes them; -1 ends the list
-  __shared__ int q_count;          // entries of q_ids that are valid
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int T_ = blockDim.x;  // 1024
   const int vpr = p.channels / V;
@@ -524,86 +521,34 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
   float* red = reinterpret_cast<float*>(smem + (size_t)32 * stages * CHUNK_BYTES);
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + (size_t)32 * stages * CHUNK_BYTES + red_bytes) + warp * stages;
   const T* x = reinterpret_cast<const T*>(p.x);
-  const long long total_vecs = p.rows * vpr;
+  const uint32_t total_vecs = (uint32_t)(p.rows * vpr);  // the launcher admits fewer than 2^31 vectors
 
   // The shift of the channel this thread finalises later: fetched now, needed after the barrier.
   const float stat_shift = tid < p.channels ? Elem<T>::to_f32(__ldg(x + tid)) : 0.f;
 
-  // Fixed head of the queue: blocks b, b + grid, ...; with `dynamic` the rest is claimed while the
-  // head is consumed, otherwise the whole list is fixed (and the sums are bit-reproducible).
-  const int head = (dynamic & 1) ? stages + 3 : BN_QUEUE - 1;
-  if (tid == 0) {
-    cta_failed = 0;
-    int n = 0;
-    for (; n < head && n < BN_QUEUE - 1; ++n) {
-      const long long id = (long long)blockIdx.x + (long long)n * gridDim.x;
-      if (id >= nblocks) break;
-      q_ids[n] = (int)id;
-    }
-    if (n < head || !(dynamic & 1)) q_ids[n++] = -1;  // the list ends here
-    q_count = n;
-  }
+  if (tid == 0) cta_failed = 0;
   if (lane == 0) {
     for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
   }
   mbar_init_fence();
   __syncthreads();
 
-  // producer state (thread 0 only)
-  int qc = q_count;
-  bool claims_done = q_ids[qc - 1] < 0;
-  bool have_pending = false;
-  unsigned int pending = 0;
-  const unsigned int dyn_base = (unsigned int)head * gridDim.x;
-  auto publish = [&](int id) {  // thread 0: append one entry (a block number, or -1 to end the list)
-    reinterpret_cast<volatile int*>(q_ids)[qc] = id;
-    __threadfence_block();
-    *reinterpret_cast<volatile int*>(&q_count) = ++qc;
-    if (id < 0) claims_done = true;
+  // chunk k of this warp: vectors [first0 + k * step, ... + CV), clipped in the last block only
+  const int n_chunks = nblocks > (int)blockIdx.x ? (nblocks - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const uint32_t first0 = ((uint32_t)blockIdx.x * 32u + (uint32_t)warp) * CV;
+  const uint32_t step = (uint32_t)gridDim.x * 32u * CV;
+  const int last_k = ((nblocks - 1) % (int)gridDim.x == (int)blockIdx.x) ? n_chunks - 1 : -1;  // chunk of the last block
+  auto vecs_of = [&](int k, uint32_t first) -> int {
+    if (k != last_k) return (int)CV;
+    return first >= total_vecs ? 0 : (total_vecs - first < CV ? (int)(total_vecs - first) : (int)CV);
   };
-  auto producer_step = [&](int k) {  // thread 0, once per chunk consumed
-    if (have_pending) {  // a claim is only made when the queue has room for it, so none is ever dropped
-      const unsigned int id = dyn_base + pending;
-      publish(id >= (unsigned int)nblocks ? -1 : (int)id);
-      have_pending = false;
-    }
-    if (!claims_done && qc == BN_QUEUE - 1) publish(-1);  // full: the other CTAs take what is left
-    if (!claims_done && qc < k + stages + 3) {
-      pending = atomicAdd(&p.bar[3], 1u);  // used one chunk later: the round trip is off the critical path
-      have_pending = true;
-    }
-  };
-  // Block number of the k-th block of this CTA; -1: the list ended; -2: the queue did not fill in time.
-  auto block_id = [&](int k) {
-    if (k >= BN_QUEUE) return -1;
-    volatile int* cnt = reinterpret_cast<volatile int*>(&q_count);
-    unsigned int spins = 0;
-    while (*cnt <= k) {
-      if (tid == 0) {  // the producer itself must never wait for its own claim
-        if (have_pending || !claims_done) {
-          producer_step(k);
-          continue;
-        }
-      }
-      if (++spins > (1u << 20)) return -2;
-      __nanosleep(20);
-    }
-    return reinterpret_cast<volatile int*>(q_ids)[k];
-  };
-  auto chunk_first = [&](int id) { return ((long long)id * 32 + warp) * CHUNK_VECS; };
-  auto chunk_vecs = [&](int id) {
-    const long long left = total_vecs - chunk_first(id);
-    return left < CHUNK_VECS ? (left > 0 ? (int)left : 0) : CHUNK_VECS;
-  };
-  const uint64_t keep_policy = (dynamic & 2) ? l2_policy_evict_last() : l2_policy_evict_normal();
+  const uint64_t keep_policy = (flags & 2) ? l2_policy_evict_last() : l2_policy_evict_normal();
   const uint64_t drop_policy = l2_policy_evict_first();
-  auto issue = [&](int id, int slot, uint64_t policy) {  // lane 0 only; no copy for an empty chunk
-    const int nv = chunk_vecs(id);
-    if (nv <= 0) return;
+  const uint4* xv = reinterpret_cast<const uint4*>(p.x);
+  auto issue = [&](uint32_t first, int nv, int slot, uint64_t policy) {  // lane 0 only, nv > 0
     const uint32_t bytes = (uint32_t)nv * 16u;
     mbar_arrive_expect_tx(&full[slot], bytes);
-    bulk_load_hint(ring + (size_t)slot * CHUNK_BYTES, reinterpret_cast<const uint4*>(p.x) + chunk_first(id), bytes,
-                   &full[slot], policy);
+    bulk_load_hint(ring + (size_t)slot * CHUNK_BYTES, xv + first, bytes, &full[slot], policy);
   };
 
 #ifdef B200_BN_TIMING
@@ -624,7 +569,7 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
   bool failed = false;
   uint32_t phase_bits = 0;  // bit s: parity of the next completion of slot s
   uint32_t busy_bits = 0;   // bit s: slot s has a copy that was started and not yet waited for
-  int n_chunks = 0x7fffffff;  // blocks of this CTA; known once the end of the list has been seen
+  const int keep_until = n_chunks - stages;  // chunks from here on stay in shared memory
 
   // ---- pass 1: shifted sums -------------------------------------------------------------------
   f32x2 shift[V / 2], s1[V / 2], s2[V / 2];
@@ -637,29 +582,32 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
       s1[i] = s2[i] = splat2(0.f);
     }
   }
-  // Without dynamic claims the list is complete already, and the chunks that will stay in shared
-  // memory (the last `stages`) are known: they are never read from L2 again, so they are loaded
-  // with the evict-first hint and leave L2 to the chunks that are.
-  int keep_until = 0x7fffffff;
-  if (!(dynamic & 1)) {
-    const int listed = *reinterpret_cast<volatile int*>(&q_count) - 1;
-    keep_until = listed - stages;
-  }
-  for (int k = 0; k < stages; ++k) {  // fill the ring
-    const int id = block_id(k);
-    if (id < 0) {
-      if (id == -2) failed = true;
-      n_chunks = k;
-      break;
+  {
+    uint32_t f = first0;
+    for (int k = 0; k < stages && k < n_chunks; ++k, f += step) {  // fill the ring
+      const int nv = vecs_of(k, f);
+      if (nv > 0) {
+        if (lane == 0) issue(f, nv, k, k < keep_until ? keep_policy : drop_policy);
+        busy_bits |= 1u << k;
+      }
     }
-    if (lane == 0) issue(id, k, k < keep_until ? keep_policy : drop_policy);
-    if (chunk_vecs(id) > 0) busy_bits |= 1u << k;
   }
+  auto accumulate = [&](const uint4& raw) {
+    f32x2 f[V / 2];
+    Pairs<T>::unpack(raw, f);
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      const f32x2 d = sub2(f[i], shift[i]);
+      s1[i] = add2(s1[i], d);
+      s2[i] = fma2(d, d, s2[i]);
+    }
+  };
   {
     int slot = 0;
-    for (int k = 0; k < n_chunks && !failed; ++k) {
-      const int id = block_id(k);  // present: it was read when the copy was started
-      const int nv = chunk_vecs(id);
+    uint32_t first = first0;
+    const uint32_t ahead = (uint32_t)stages * step;
+    for (int k = 0; k < n_chunks; ++k, first += step) {
+      const int nv = vecs_of(k, first);
       if (nv > 0) {
         const bool arrived = __all_sync(0xffffffffu, mbar_wait(&full[slot], (phase_bits >> slot) & 1u));
         if (!arrived) {
@@ -668,34 +616,25 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
         }
         phase_bits ^= 1u << slot;
         busy_bits &= ~(1u << slot);
-        const uint4* src = reinterpret_cast<const uint4*>(ring + (size_t)slot * CHUNK_BYTES);
+        const uint4* src = reinterpret_cast<const uint4*>(ring + (size_t)slot * CHUNK_BYTES) + lane;
+        if (nv == (int)CV) {  // a whole chunk: no bounds checks
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if (u * 32 + lane < nv) {
-            f32x2 f[V / 2];
-            Pairs<T>::unpack(src[u * 32 + lane], f);
+          for (int u = 0; u < U; ++u) accumulate(src[u * 32]);
+        } else {
 #pragma unroll
-            for (int i = 0; i < V / 2; ++i) {
-              const f32x2 d = sub2(f[i], shift[i]);
-              s1[i] = add2(s1[i], d);
-              s2[i] = fma2(d, d, s2[i]);
-            }
-          }
+          for (int u = 0; u < U; ++u)
+            if (u * 32 + lane < nv) accumulate(src[u * 32]);
         }
         __syncwarp();
       }
-      if (tid == 0) producer_step(k);
       if (k + stages < n_chunks) {  // refill the slot with the chunk `stages` further on
-        const int nid = block_id(k + stages);
-        if (nid < 0) {
-          if (nid == -2) failed = true;
-          n_chunks = k + stages;
-        } else {
-          if (lane == 0 && chunk_vecs(nid) > 0) {
+        const int nnv = vecs_of(k + stages, first + ahead);
+        if (nnv > 0) {
+          if (lane == 0) {
             fence_proxy_async_smem();
-            issue(nid, slot, k + stages < keep_until ? keep_policy : drop_policy);
+            issue(first + ahead, nnv, slot, k + stages < keep_until ? keep_policy : drop_policy);
           }
-          if (chunk_vecs(nid) > 0) busy_bits |= 1u << slot;
+          busy_bits |= 1u << slot;
         }
       }
       if (++slot == stages) slot = 0;
@@ -862,12 +801,45 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
         inv2[i] = pack2(__ldcg(p.stats + p.channels + c), __ldcg(p.stats + p.channels + c + 1));
       }
     }
-    const int* ids = q_ids;  // complete and final by now
+    const bool relu = p.relu != 0;
+    auto normalise = [&](const uint4& raw, uint4* dst) {
+      f32x2 f[V / 2], o[V / 2];
+      Pairs<T>::unpack(raw, f);
+#pragma unroll
+      for (int i = 0; i < V / 2; ++i) o[i] = add2(mul2(mul2(sub2(f[i], mean2[i]), inv2[i]), w2[i]), b2[i]);
+      uint4 packed = Pairs<T>::pack(o);
+      if (relu) {  // ReLU after the cast, as the graph has it; NaN stays NaN
+        if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+          const __nv_bfloat162 z = __float2bfloat162_rn(0.f);
+          uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            __nv_bfloat162 h = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&w[i]), z);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        } else if constexpr (std::is_same<T, __half>::value) {
+          const __half2 z = __float2half2_rn(0.f);
+          uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            __half2 h = __hmax2_nan(*reinterpret_cast<__half2*>(&w[i]), z);
+            w[i] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        } else {
+          float* w = reinterpret_cast<float*>(&packed);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) w[i] = w[i] < 0.f ? 0.f : w[i];  // NaN < 0 is false: NaN stays
+        }
+      }
+      st_stream(reinterpret_cast<T*>(dst), packed);
+    };
     const int resident_from = n_chunks - (n_chunks < stages ? n_chunks : stages);  // chunks >= this are in smem
     int slot = (n_chunks - 1) % stages;
-    for (int k = n_chunks - 1; k >= 0; --k) {
-      const int id = ids[k];
-      const int nv = chunk_vecs(id);
+    uint32_t first = first0 + (uint32_t)(n_chunks - 1) * step;
+    const uint32_t behind = (uint32_t)stages * step;
+    uint4* yv = reinterpret_cast<uint4*>(p.y) + lane;
+    for (int k = n_chunks - 1; k >= 0; --k, first -= step) {
+      const int nv = vecs_of(k, first);
       if (nv > 0) {
         if (k < resident_from) {
           const bool arrived = __all_sync(0xffffffffu, mbar_wait(&full[slot], (phase_bits >> slot) & 1u));
@@ -878,53 +850,24 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
           phase_bits ^= 1u << slot;
           busy_bits &= ~(1u << slot);
         }
-        const uint4* src = reinterpret_cast<const uint4*>(ring + (size_t)slot * CHUNK_BYTES);
-        uint4* dst = reinterpret_cast<uint4*>(p.y) + chunk_first(id);
+        const uint4* src = reinterpret_cast<const uint4*>(ring + (size_t)slot * CHUNK_BYTES) + lane;
+        uint4* dst = yv + first;
+        if (nv == (int)CV) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          if (u * 32 + lane < nv) {
-            f32x2 f[V / 2], o[V / 2];
-            Pairs<T>::unpack(src[u * 32 + lane], f);
+          for (int u = 0; u < U; ++u) normalise(src[u * 32], dst + u * 32);
+        } else {
 #pragma unroll
-            for (int i = 0; i < V / 2; ++i) o[i] = add2(mul2(mul2(sub2(f[i], mean2[i]), inv2[i]), w2[i]), b2[i]);
-            uint4 packed = Pairs<T>::pack(o);
-            if (p.relu) {  // ReLU after the cast, as the graph has it; NaN stays NaN
-              if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-                const __nv_bfloat162 z = __float2bfloat162_rn(0.f);
-                uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  __nv_bfloat162 h = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&w[i]), z);
-                  w[i] = *reinterpret_cast<uint32_t*>(&h);
-                }
-              } else if constexpr (std::is_same<T, __half>::value) {
-                const __half2 z = __float2half2_rn(0.f);
-                uint32_t* w = reinterpret_cast<uint32_t*>(&packed);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  __half2 h = __hmax2_nan(*reinterpret_cast<__half2*>(&w[i]), z);
-                  w[i] = *reinterpret_cast<uint32_t*>(&h);
-                }
-              } else {
-                float* w = reinterpret_cast<float*>(&packed);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) w[i] = w[i] < 0.f ? 0.f : w[i];  // NaN < 0 is false: NaN stays
-              }
-            }
-            st_stream(dst + u * 32 + lane, packed);
-          }
+          for (int u = 0; u < U; ++u)
+            if (u * 32 + lane < nv) normalise(src[u * 32], dst + u * 32);
         }
         __syncwarp();
       }
-      if (k - stages >= 0) {  // the slot takes the chunk `stages` before this one
-        const int nid = ids[k - stages];
-        if (chunk_vecs(nid) > 0) {
-          if (lane == 0) {
-            fence_proxy_async_smem();
-            issue(nid, slot, drop_policy);
-          }
-          busy_bits |= 1u << slot;
+      if (k >= stages) {  // the slot takes the chunk `stages` before this one (never the last block: whole)
+        if (lane == 0) {
+          fence_proxy_async_smem();
+          issue(first - behind, (int)CV, slot, drop_policy);
         }
+        busy_bits |= 1u << slot;
       }
       if (--slot < 0) slot = stages - 1;
     }
@@ -1030,17 +973,6 @@ static bool warp_rings_disabled() {
   return off;
 }
 
-// B200_BN_DYNAMIC=1: CTAs claim blocks from a global counter instead of a fixed list. A few
-// percent faster, but which CTA sums which block then varies from run to run, and with it the
-// last bits of the statistics. Off by default: results are bit-reproducible.
-static bool bn_dynamic_blocks() {
-  static const bool on = [] {
-    const char* e = getenv("B200_BN_DYNAMIC");
-    return e && e[0] == '1';
-  }();
-  return on;
-}
-
 // Per-warp-ring launch; returns false when the shape does not fit (the CTA-ring kernel takes it).
 template <typename T>
 static bool try_launch_batch_norm_warp(BatchNormParams p, size_t scratch_bytes, cudaStream_t st, int* rc) {
@@ -1069,14 +1001,12 @@ static bool try_launch_batch_norm_warp(BatchNormParams p, size_t scratch_bytes, 
   if (stages > 8) stages = 8;
   if (stages < 2) return false;
   const size_t smem = 32 * (size_t)stages * chunk + red_bytes + barrier_bytes;
-  // a block = 32 chunks (one per warp); CTAs take blocks dynamically, the queue holds BN_QUEUE of them
+  // a block = 32 chunks (one per warp); CTA b takes blocks b, b + grid, ...
   const long long block_vecs = 32LL * (long long)(chunk / 16);
   const long long nblocks = (total_vecs + block_vecs - 1) / block_vecs;
   if (grid > nblocks) grid = nblocks;
   if (grid < 1) grid = 1;
-  // the queue must hold a CTA's whole list when it is fixed, and four times the average otherwise
-  const long long per_cta = (nblocks + grid - 1) / grid;
-  if (per_cta > (bn_dynamic_blocks() ? BN_QUEUE / 4 : BN_QUEUE - 2) || nblocks > 0x3fffffffLL) return false;
+  if (total_vecs >= 0x7fffffffLL - 4096) return false;  // the kernel counts vectors in 32 bits
   {
     const long long need2 = 256 + (grid * 2 * p.channels + stats_floats) * (long long)sizeof(float);
     if ((long long)scratch_bytes < need2) return false;
@@ -1093,8 +1023,8 @@ static bool try_launch_batch_norm_warp(BatchNormParams p, size_t scratch_bytes, 
   p.smem_tiles = stages;
   p.stats = p.partials + grid * 2 * p.channels;
   int stages_arg = stages, red_bytes_arg = (int)red_bytes, nblocks_arg = (int)nblocks;
-  int dynamic_arg = (bn_dynamic_blocks() ? 1 : 0) | (getenv("B200_BN_EVICT_LAST") ? 2 : 0);
-  void* args[] = {&p, &stages_arg, &red_bytes_arg, &nblocks_arg, &dynamic_arg};
+  int flags_arg = getenv("B200_BN_EVICT_LAST") ? 2 : 0;
+  void* args[] = {&p, &stages_arg, &red_bytes_arg, &nblocks_arg, &flags_arg};
   e = cudaLaunchCooperativeKernel(kernel, dim3((unsigned)grid), dim3(threads), args, smem, st);
   if (e != cudaSuccess) {
     cudaGetLastError();
