@@ -9,6 +9,8 @@
 
 #include "common.cuh"
 
+#include <cstdlib>
+
 namespace b200 {
 
 // Division by a run-time constant without a divide instruction: q = umulhi(n, mul) >> shr for
@@ -380,7 +382,13 @@ inline bool pick_row_geometry(long long nv, RowGeometry* g) {
   if (nv > 4096) return false;
   g->g = 0;
   g->block = true;
-  g->ch = nv <= 512 ? 2 : (nv <= 2048 ? 4 : 8);
+  // CTAs of about 128 threads for mid-size rows (measured on 4096 bf16 columns: 44.7 us with four
+  // vectors per thread against 49.2 us with two), eight vectors per thread for the longest
+  g->ch = nv <= 256 ? 2 : (nv <= 2048 ? 4 : 8);
+  {
+    static const int ch_env = [] { const char* e = getenv("B200_BLOCK_CH"); return e ? atoi(e) : 0; }();
+    if (ch_env == 2 || ch_env == 4 || ch_env == 8) g->ch = ch_env;
+  }
   long long t = (nv + g->ch - 1) / g->ch;
   t = (t + 31) / 32 * 32;
   g->threads = (int)t;
