@@ -11,6 +11,8 @@
 // atomic variant is not, and its harness would classify such an output as stochastic).
 #include "rowwise.cuh"
 
+#include <cstdlib>
+
 namespace b200 {
 
 #define B200_COL_SUM 0
@@ -179,6 +181,10 @@ static int launch_col_reduce(ColReduceParams p, bool vec, size_t scratch_bytes, 
       splits = s;
       break;
     }
+  }
+  {
+    static const int splits_env = [] { const char* e = getenv("B200_COL_SPLITS"); return e ? atoi(e) : 0; }();
+    if (splits_env > 0 && splits_env <= max_splits) splits = splits_env;
   }
   const long long cap = scratch_bytes / ((size_t)p.batch * p.cols * sizeof(float) + 1);
   if (splits > cap) splits = cap;
