@@ -204,7 +204,7 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_cl_kernel(const BnBwdParams 
     gs[i] = pack2(p.coef[2 * p.channels + c], p.coef[2 * p.channels + c + 1]);
     mean2[i] = pack2(p.coef[3 * p.channels + c], p.coef[3 * p.channels + c + 1]);
   }
-  constexpr int U = 2;
+  constexpr int U = 4;
   const long long stride = (long long)gridDim.x * T_;  // a multiple of vpr: the column is fixed
   for (long long v = (long long)blockIdx.x * T_ + tid; v < total; v += U * stride) {
     uint4 rg[U], rx[U], ra[U];
