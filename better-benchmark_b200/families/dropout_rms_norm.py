@@ -1,0 +1,17 @@
+"""Dropout-fused RMSNorm (family ``mean`` with random masks drawn inside the region).
+
+``oracle_forward`` covers the reference graph dropout(x) + residual -> RMSNorm -> dropout of
+repros/canonical/mean_014afd4984e6/repro.py:24-47 (replaced kernel .../oracle.py:14-130, wrapper
+:201-260): inputs ``(x, seeds, residual, weight, shape, shape, shape, flat_shape)``, outputs
+``(keep0, sum, rstd, keep1, y)``. The masks come from the kernel's own Philox4x32-10 stream keyed by
+``seeds[82]`` / ``seeds[83]``; the reference's check skips them as stochastic outputs."""
+from .. import kernels
+
+DROPOUT_P = 0.1
+EPS = 1e-6
+SEED_INDEX0, SEED_INDEX1 = 82, 83
+
+
+def oracle_forward(inputs, *, p=DROPOUT_P, eps=EPS, seed_index0=SEED_INDEX0, seed_index1=SEED_INDEX1):
+    x, seeds, residual, weight = inputs[:4]
+    return kernels.dropout_rms_norm(x, residual, weight, seeds, seed_index0, seed_index1, p=p, eps=eps)

@@ -9,7 +9,7 @@ from __future__ import annotations
 import torch
 
 from . import kernels
-from .families import batch_norm_bwd, column_sum, permute
+from .families import batch_norm_bwd, column_sum, dropout_rms_norm, permute
 from .workloads import Workload, _gen
 
 
@@ -51,6 +51,15 @@ def _log_softmax_inputs(device="cuda", seed=1):
 def _rms_fwd_inputs(device="cuda", seed=1):
     return [_randn((16384, 4096), torch.bfloat16, seed, device),
             (torch.rand(4096, generator=_gen(seed)) + 0.5).to(torch.bfloat16).to(device)]
+
+
+def _dropout_rms_inputs(device="cuda", seed=1):
+    rows, cols = 32768, 512          # eight times the rows of the reference's point, to exceed the L2
+    seeds = torch.randint(0, 2 ** 62, (84,), generator=_gen(seed), dtype=torch.int64).to(device)
+    return [_randn((rows, cols), torch.bfloat16, seed, device), seeds,
+            _randn((256, 128, cols), torch.float32, seed + 100, device),
+            (torch.rand(cols, generator=_gen(seed)) + 0.5).to(device),
+            [256, 128, cols], [256, 128, cols], [256, 128, cols], [rows, cols]]
 
 
 def _ln_bwd_inputs(device="cuda", seed=1):
@@ -104,6 +113,10 @@ FAMILY_CASES = {c.name: c for c in [
     _case("rms_norm_fwd_bf16", "RMSNorm forward: x bf16 [16384, 4096], w bf16 -> y bf16", "bf16",
           2 * 16384 * 4096 * 2 + 4096 * 2, _rms_fwd_inputs,
           lambda i: kernels.norm_fwd(i[0], i[1], None, eps=1e-6, rms=True)[0]),
+    _case("dropout_rms_norm_bf16",
+          "dropout + residual -> RMSNorm -> dropout: x bf16 [32768, 512], residual f32 -> 2 masks, sum f32, rstd, y bf16",
+          "bf16", 32768 * 512 * (2 + 4 + 1 + 4 + 1 + 2) + 32768 * 4 + 512 * 4, _dropout_rms_inputs,
+          lambda i: dropout_rms_norm.oracle_forward(i)),
     _case("layer_norm_bwd_bf16", "LayerNorm backward: x, dy bf16 [32768, 768] -> dx bf16, dweight, dbias f32", "bf16",
           3 * 32768 * 768 * 2 + 768 * 4 * 3 + 2 * 32768 * 4, _ln_bwd_inputs,
           lambda i: kernels.norm_bwd(i[0], i[1], i[2], i[4], mean=i[3], rms=False, want_dbias=True)),

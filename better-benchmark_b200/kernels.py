@@ -534,3 +534,37 @@ def cast_scale(x: torch.Tensor, out_dtype: torch.dtype, *, scale: float | None =
                               _stream()),
           "b200_cast_scale")
     return out
+
+
+def dropout_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, seeds: torch.Tensor,
+                     seed_index0: int, seed_index1: int, *, p: float, eps: float):
+    """Dropout -> residual add -> RMSNorm -> dropout over the last dimension.
+
+    x [rows, cols] bf16/fp16, residual fp32 with the same number of elements (any leading shape),
+    weight fp32 [cols], seeds int64 (the two seeds are read on the device). Returns
+    ``(keep0, sum, rstd, keep1, y)``: the masks as bool and ``sum`` shaped like ``residual``, ``rstd``
+    as ``residual.shape[:-1] + (1,)``, ``y`` shaped like ``x``."""
+    for t in (x, residual, weight, seeds):
+        _require_cuda(t)
+    cols = x.shape[-1]
+    if residual.shape[-1] != cols or residual.numel() != x.numel() or weight.numel() != cols:
+        raise native.KernelArgumentError("dropout_rms_norm: x, residual and weight disagree on the row length")
+    if residual.dtype != torch.float32 or weight.dtype != torch.float32 or seeds.dtype != torch.int64:
+        raise native.KernelArgumentError("dropout_rms_norm: residual and weight must be fp32, seeds int64")
+    if not (x.is_contiguous() and residual.is_contiguous() and weight.is_contiguous() and seeds.is_contiguous()):
+        raise UnsupportedLayout("dropout_rms_norm: tensors must be contiguous")
+    if not (0 <= seed_index0 < seeds.numel() and 0 <= seed_index1 < seeds.numel()):
+        raise native.KernelArgumentError("dropout_rms_norm: seed index outside the seed tensor")
+    rows = x.numel() // cols if cols else 0
+    dev = x.device
+    keep0 = torch.empty(residual.shape, dtype=torch.bool, device=dev)
+    keep1 = torch.empty(residual.shape, dtype=torch.bool, device=dev)
+    total = torch.empty_like(residual)
+    rstd = torch.empty(tuple(residual.shape[:-1]) + (1,), dtype=torch.float32, device=dev)
+    y = torch.empty_like(x)
+    lib = load()
+    check(lib.b200_dropout_rms_norm(_ptr(x), _ptr(residual), _ptr(weight), _ptr(seeds), int(seed_index0),
+                                    int(seed_index1), float(p), float(eps), _ptr(keep0), _ptr(total),
+                                    _ptr(rstd), _ptr(keep1), _ptr(y), rows, cols, _code(x), _stream()),
+          "b200_dropout_rms_norm")
+    return keep0, total, rstd, keep1, y

@@ -79,6 +79,9 @@ SIGNATURES = {
     "b200_transpose_copy": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
                                       c_int32, c_int32, c_double, c_int32, c_void_p]),
     "b200_cast_scale": (c_int32, [c_void_p, c_void_p, c_int64, c_int32, c_int32, c_double, c_int32, c_void_p]),
+    "b200_dropout_rms_norm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_double,
+                                        c_double, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
+                                        c_int64, c_int32, c_void_p]),
 }
 
 _lib = None

@@ -163,6 +163,20 @@ int32_t b200_transpose_copy(const void* x, void* y, int64_t batch, int64_t rows,
                             int64_t in_batch_stride, int64_t in_row_stride, int32_t in_dtype,
                             int32_t out_dtype, double scale, int32_t has_scale, void* stream);
 
+/* Dropout -> residual add -> RMSNorm -> dropout over rows of `cols` elements (a multiple of 8, at most
+ * 2048): keep0 = T(u0) > p; s = T(T(keep0 * x) * 1/(1-p)); sum = residual + s;
+ * rstd = rsqrt(mean(sum^2) + eps); keep1 = u1 > p; y = T((keep1 * (weight * (sum * rstd))) * 1/(1-p)).
+ * x, y: x_dtype (bf16 or fp16) [rows, cols]; residual, sum: fp32 [rows, cols]; weight: fp32 [cols];
+ * rstd: fp32 [rows]; keep0, keep1: one byte per element (0 or 1). u0, u1 are Philox4x32-10 uniforms keyed by
+ * seeds[seed_index0] and seeds[seed_index1] (read on the device), counter = (element index / 4, mask number).
+ * Replaces mean_014afd4984e6/oracle.py:14-130 (kernel) and :201-260 (wrapper); the masks are stochastic
+ * outputs for the reference's check (oracle_harness.py stochastic-output skip), all other outputs follow
+ * from them. */
+int32_t b200_dropout_rms_norm(const void* x, const void* residual, const void* weight, const int64_t* seeds,
+                              int32_t seed_index0, int32_t seed_index1, double p, double eps, void* keep0,
+                              void* sum, void* rstd, void* keep1, void* y, int64_t rows, int64_t cols,
+                              int32_t x_dtype, void* stream);
+
 /* Contiguous cast / scale of n elements.
  * Replaces pointwise_8bb40810003c/oracle.py:11-15 and pointwise_95ed2ef35da9/oracle.py:10-44. */
 int32_t b200_cast_scale(const void* x, void* y, int64_t n, int32_t in_dtype, int32_t out_dtype, double scale,

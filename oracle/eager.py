@@ -337,3 +337,47 @@ class BatchNormBwd(nn.Module):
         dx = aten.mul.Tensor(aten.sub.Tensor(aten.sub.Tensor(g, aten.mul.Tensor(sub, c2)), c1), gs)
         dx = prims.convert_element_type.default(dx, x.dtype) if x.dtype != torch.float32 else dx
         return (sum_1, aten.mul.Tensor(sum_2, invstd), dx)
+
+
+class DropoutResidualRMSNorm(nn.Module):
+    """dropout(x) + residual -> RMSNorm(weight) -> dropout, returning (keep0, sum, rstd, keep1, y).
+
+    Graph: reference repros/canonical/mean_014afd4984e6/repro.py:24-47. The first uniform tensor is
+    narrowed to x's dtype before the comparison, the second is compared in fp32; both products with
+    1/(1-p) happen after the masking, the first rounded to x's dtype, the second in fp32.
+
+    ``masks`` = (keep0, keep1) replaces the two draws: every other output is a deterministic
+    function of the masks, which is how a kernel with its own generator is checked. Without
+    ``masks`` the module draws with ``prims.inductor_random`` exactly as the captured graph does.
+    """
+
+    def __init__(self, p: float, eps: float, seed_index0: int = 0, seed_index1: int = 1):
+        super().__init__()
+        self.p, self.eps = p, eps
+        self.scale = 1.0 / (1.0 - p)
+        self.seed_index0, self.seed_index1 = seed_index0, seed_index1
+
+    def forward(self, x, seeds, residual, weight, masks=None):
+        import torch._inductor.inductor_prims  # noqa: F401  (registers the two prims used below)
+        shape = list(residual.shape)
+        view = aten.view.default(x, shape)
+        if masks is None:
+            seed0 = prims.inductor_lookup_seed.default(seeds, self.seed_index0)
+            rand0 = prims.inductor_random.default(shape, seed0, "rand")
+            keep0 = aten.gt.Scalar(prims.convert_element_type.default(rand0, x.dtype), self.p)
+        else:
+            keep0 = masks[0]
+        mul = aten.mul.Tensor(keep0, view)
+        mul_1 = aten.mul.Tensor(mul, self.scale)
+        add = aten.add.Tensor(residual, mul_1)
+        mean = aten.mean.dim(aten.pow.Tensor_Scalar(add, 2), [-1], True)
+        rsqrt = aten.rsqrt.default(aten.add.Tensor(mean, self.eps))
+        mul_3 = aten.mul.Tensor(weight, aten.mul.Tensor(add, rsqrt))
+        if masks is None:
+            seed1 = prims.inductor_lookup_seed.default(seeds, self.seed_index1)
+            keep1 = aten.gt.Scalar(prims.inductor_random.default(shape, seed1, "rand"), self.p)
+        else:
+            keep1 = masks[1]
+        mul_5 = aten.mul.Tensor(aten.mul.Tensor(keep1, mul_3), self.scale)
+        y = aten.view.default(prims.convert_element_type.default(mul_5, x.dtype), list(x.shape))
+        return (keep0, add, rsqrt, keep1, y)

@@ -1,0 +1,119 @@
+"""Dropout-fused RMSNorm kernel: the masks against the numpy Philox restatement (bit-exact), every
+other output against the eager oracle evaluated with the kernel's own masks."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import assert_close
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(rows, cols, dtype, seed, lead=None):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    x = (torch.randn(rows, cols, generator=g, device="cuda") * 1.5).to(dtype)
+    shape = (rows, cols) if lead is None else (*lead, cols)
+    residual = torch.randn(shape, generator=g, device="cuda")
+    weight = torch.rand(cols, generator=g, device="cuda") + 0.5
+    seeds = torch.randint(0, 2 ** 62, (84,), generator=g, device="cuda", dtype=torch.int64)
+    return x, seeds, residual, weight
+
+
+def _expected_masks(seeds, numel, p, dtype, i0, i1):
+    from oracle.philox import uniforms
+    s = seeds.cpu().tolist()
+    u0 = torch.from_numpy(uniforms(numel, s[i0], 0))
+    u1 = torch.from_numpy(uniforms(numel, s[i1], 1))
+    return u0.to(dtype) > p, u1 > p      # the first draw is narrowed before the comparison, as in the graph
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,cols,lead", [(64, 512, (2, 32)), (1, 8, None), (7, 264, None), (33, 1024, (3, 11)),
+                                            (5, 2048, None), (130, 768, None), (4096, 512, (32, 128))])
+@pytest.mark.parametrize("p", [0.1, 0.5])
+def test_outputs_follow_from_masks_and_masks_from_philox(dtype, rows, cols, lead, p):
+    from better_benchmark_b200 import kernels
+    from oracle import eager
+    x, seeds, residual, weight = _inputs(rows, cols, dtype, rows + cols, lead)
+    keep0, total, rstd, keep1, y = kernels.dropout_rms_norm(x, residual, weight, seeds, 82, 83, p=p, eps=1e-6)
+    assert keep0.dtype == keep1.dtype == torch.bool and keep0.shape == residual.shape
+    assert total.shape == residual.shape and rstd.shape == (*residual.shape[:-1], 1) and y.shape == x.shape
+
+    want0, want1 = _expected_masks(seeds, rows * cols, p, dtype, 82, 83)
+    assert torch.equal(keep0.cpu().view(-1), want0)
+    assert torch.equal(keep1.cpu().view(-1), want1)
+
+    module = eager.DropoutResidualRMSNorm(p, 1e-6, 82, 83)
+    _, w_total, w_rstd, _, w_y = module(x, seeds, residual, weight, masks=(keep0, keep1))
+    assert torch.equal(total, w_total)            # element-wise, no reduction: exact
+    assert_close(rstd, w_rstd, "rstd")
+    assert_close(y, w_y, "y")
+
+
+def test_keep_rate_independence_and_seed_dependence():
+    from better_benchmark_b200 import kernels
+    x, seeds, residual, weight = _inputs(4096, 512, torch.bfloat16, 3)
+    k0, _, _, k1, y = kernels.dropout_rms_norm(x, residual, weight, seeds, 82, 83, p=0.1, eps=1e-6)
+    n = k0.numel()
+    r0, r1 = k0.float().mean().item(), k1.float().mean().item()
+    sigma = (0.09 / n) ** 0.5
+    assert abs(r1 - 0.9) < 6 * sigma
+    assert abs(r0 - 0.9) < 6 * sigma + 2e-3          # the bf16 rounding of the draw moves the threshold slightly
+    both = (k0 & k1).float().mean().item()
+    assert abs(both - r0 * r1) < 6 * sigma           # the two masks are independent
+    rows_equal = (k0[1:] == k0[:-1]).all(dim=1).any().item()
+    assert not rows_equal                            # no row repeats its neighbour
+    again = kernels.dropout_rms_norm(x, residual, weight, seeds, 82, 83, p=0.1, eps=1e-6)
+    assert torch.equal(again[0], k0) and torch.equal(again[3], k1) and torch.equal(again[4], y)
+    seeds2 = seeds.clone()
+    seeds2[82] += 1
+    other = kernels.dropout_rms_norm(x, residual, weight, seeds2, 82, 83, p=0.1, eps=1e-6)
+    assert not torch.equal(other[0], k0) and torch.equal(other[3], k1)
+    swapped = kernels.dropout_rms_norm(x, residual, weight, seeds, 83, 82, p=0.1, eps=1e-6)
+    assert not torch.equal(swapped[0], k0)
+
+
+def test_p_zero_keeps_everything():
+    from better_benchmark_b200 import kernels
+    from oracle import eager
+    x, seeds, residual, weight = _inputs(16, 256, torch.bfloat16, 5)
+    k0, total, rstd, k1, y = kernels.dropout_rms_norm(x, residual, weight, seeds, 0, 1, p=0.0, eps=1e-6)
+    # a draw of exactly 0 is the only one p = 0 drops
+    assert k0.float().mean().item() > 0.99 and k1.float().mean().item() > 0.999
+    _, w_total, w_rstd, _, w_y = eager.DropoutResidualRMSNorm(0.0, 1e-6)(x, seeds, residual, weight, masks=(k0, k1))
+    assert torch.equal(total, w_total)
+    assert_close(y, w_y, "y")
+
+
+def test_rejected_arguments():
+    from better_benchmark_b200 import kernels, native
+    x, seeds, residual, weight = _inputs(8, 512, torch.bfloat16, 1)
+    with pytest.raises(native.KernelArgumentError):
+        kernels.dropout_rms_norm(x, residual, weight, seeds, 84, 0, p=0.1, eps=1e-6)          # seed index out of range
+    with pytest.raises(native.KernelArgumentError):
+        kernels.dropout_rms_norm(x, residual.half(), weight, seeds, 0, 1, p=0.1, eps=1e-6)   # residual must be fp32
+    with pytest.raises(native.KernelArgumentError):
+        kernels.dropout_rms_norm(x, residual, weight, seeds, 0, 1, p=1.0, eps=1e-6)           # p outside [0, 1)
+    x2, s2, r2, w2 = _inputs(4, 4096, torch.bfloat16, 2)
+    with pytest.raises(native.KernelArgumentError):
+        kernels.dropout_rms_norm(x2, r2, w2, s2, 0, 1, p=0.1, eps=1e-6)                       # row longer than built
+    x3, s3, r3, w3 = _inputs(4, 12, torch.bfloat16, 2)
+    with pytest.raises(native.KernelArgumentError):
+        kernels.dropout_rms_norm(x3, r3, w3, s3, 0, 1, p=0.1, eps=1e-6)                       # not a multiple of 8
+    e = kernels.dropout_rms_norm(x[:0], residual[:0], weight, seeds, 0, 1, p=0.1, eps=1e-6)
+    assert e[4].shape == (0, 512)
+
+
+def test_through_the_shipped_stub_and_harness():
+    """The directory's oracle.py through the harness check: masks are skipped as stochastic or compared
+    by the harness's own rule; here the deterministic outputs are checked with the stub's masks."""
+    from better_benchmark_b200.families import dropout_rms_norm
+    from oracle import eager
+    x, seeds, residual, weight = _inputs(256, 512, torch.bfloat16, 9, (2, 128))
+    inputs = [x, seeds, residual, weight, [2, 128, 512], [2, 128, 512], [2, 128, 512], [256, 512]]
+    k0, total, rstd, k1, y = dropout_rms_norm.oracle_forward(inputs)
+    _, w_total, w_rstd, _, w_y = eager.DropoutResidualRMSNorm(0.1, 1e-6, 82, 83)(x, seeds, residual, weight,
+                                                                                  masks=(k0, k1))
+    assert torch.equal(total, w_total)
+    assert_close(rstd, w_rstd, "rstd")
+    assert_close(y, w_y, "y")

@@ -22,8 +22,10 @@ FIXTURE_DIR = {
     "colsum_eb86a17deab9": "sum_eb86a17deab9", "headsplit_c0d19d490a2f": "pointwise_c0d19d490a2f",
     "transpose_021e90d9c17d": "pointwise_021e90d9c17d", "logsoftmax_d16035e7b826": "amax_sum_d16035e7b826",
     "softmax_long_7079889cfc04": "amax_sum_7079889cfc04", "spatial_mean_c9e1a8113328": "mean_c9e1a8113328",
-    "bn_bwd_leaky_12fc8ebf8180": "sum_sum_12fc8ebf8180",
+    "bn_bwd_leaky_12fc8ebf8180": "sum_sum_12fc8ebf8180", "dropout_rms_014afd4984e6": "mean_014afd4984e6",
 }
+# regions that draw random numbers: output index -> mask index it depends on element by element
+STOCHASTIC = {"dropout_rms_014afd4984e6": {"masks": (0, 3), "elementwise": {1: 0}}}
 
 
 def kernel_cases():
@@ -62,6 +64,20 @@ def test_kernels_reproduce_reference_outputs(name):
     got = kernel_cases()[name](inputs)
     want = data["outputs"]
     assert len(got) == len(want)
+    if name in STOCHASTIC:
+        # The kernel draws its own masks, so only what does not depend on the draw can be compared
+        # with the recorded run: shapes, dtypes, the keep rate, and, where the kernel's mask agrees
+        # with the recorded one, the outputs that depend on the mask element by element.
+        spec = STOCHASTIC[name]
+        for i, (g, w) in enumerate(zip(got, want)):
+            assert g.shape == w.shape and g.dtype == w.dtype, f"{name} output {i}"
+        for m in spec["masks"]:
+            assert abs(got[m].float().mean().item() - want[m].float().mean().item()) < 0.02
+        for out_i, mask_i in spec["elementwise"].items():
+            agree = got[mask_i].cpu() == want[mask_i]
+            assert agree.float().mean().item() > 0.7
+            assert torch.equal(got[out_i].cpu()[agree], want[out_i][agree]), f"{name} output {out_i}"
+        return
     for i, (g, w) in enumerate(zip(got, want)):
         if name in ("colsum_eb86a17deab9", "rms_bwd_2cd99e5eb23e", "ln_bwd_3cac3bbf4e8f",
                     "bn_bwd_leaky_12fc8ebf8180") and \
