@@ -8,12 +8,13 @@
 //
 // The random numbers are Philox4x32-10 (Salmon et al., SC'11): key = the 64-bit seed read from the
 // seed tensor on the device, counter = (element index / 4, mask number); each call yields four
-// consecutive elements' uniforms u = (bits >> 8) * 2^-24 in [0, 1). The reference's check treats
+// consecutive elements' uniforms u = (bits >> 8) * 2^-24 in [0, 1); the comparisons with p are done on
+// the 24-bit integers (thresholds computed on the host), which gives the same masks. The reference's check treats
 // the masks as stochastic outputs; everything else is a deterministic function of them.
 //
 // One warp owns a row: lane l holds vectors l, l+32, .. (8 elements each) in registers between the
 // sum of squares and the normalisation, so x and residual are read once.
-#include "common.cuh"
+#include "rowwise.cuh"
 
 namespace b200 {
 namespace {
@@ -30,20 +31,18 @@ __device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint32_t k0, uint32_t k1
   return c;
 }
 
-__device__ __forceinline__ float uniform01(uint32_t bits) { return (float)(bits >> 8) * 0x1p-24f; }
-
-// Eight uniforms for the elements [e0, e0+8) of mask number `which`; e0 is a multiple of 8.
-__device__ __forceinline__ void uniforms8(unsigned long long e0, uint32_t which, uint32_t k0, uint32_t k1,
-                                          float (&u)[8]) {
+// Random words for the elements [e0, e0+8) of mask number `which`; e0 is a multiple of 8.
+__device__ __forceinline__ void random_words8(unsigned long long e0, uint32_t which, uint32_t k0, uint32_t k1,
+                                              uint32_t (&w)[8]) {
   const unsigned long long g = e0 >> 2;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const unsigned long long gi = g + h;
     const uint4 r = philox4x32_10(make_uint4((uint32_t)gi, (uint32_t)(gi >> 32), which, 0u), k0, k1);
-    u[4 * h + 0] = uniform01(r.x);
-    u[4 * h + 1] = uniform01(r.y);
-    u[4 * h + 2] = uniform01(r.z);
-    u[4 * h + 3] = uniform01(r.w);
+    w[4 * h + 0] = r.x;
+    w[4 * h + 1] = r.y;
+    w[4 * h + 2] = r.z;
+    w[4 * h + 3] = r.w;
   }
 }
 
@@ -53,7 +52,11 @@ struct DropoutNormParams {
   const float* weight;
   const long long* seeds;
   int seed_index0, seed_index1;
-  float p, p_narrow, scale, eps;
+  // An element is kept when the top 24 bits of its random word, n, satisfy n >= keep_from: the
+  // uniform is u = n * 2^-24, and both "T(u) > T(p)" and "u > p" are monotonic in n, so the host
+  // turns each into one integer threshold (see thresholds() below).
+  uint32_t keep_from0, keep_from1;
+  float scale, eps;
   unsigned char* keep0;
   float* sum;
   float* rstd;
@@ -62,6 +65,20 @@ struct DropoutNormParams {
   long long rows;
   int cols;
 };
+
+// Mask bytes (0 / 1) and the same mask as fp32 pairs for eight random words.
+__device__ __forceinline__ void masks8(const uint32_t (&w)[8], uint32_t keep_from, uint2& bytes, f32x2 (&m)[4]) {
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const bool ka = (w[2 * j] >> 8) >= keep_from, kb = (w[2 * j + 1] >> 8) >= keep_from;
+    const uint32_t two = (ka ? 1u : 0u) | (kb ? 0x100u : 0u);
+    if (j < 2) lo |= two << (16 * j);
+    else hi |= two << (16 * (j - 2));
+    m[j] = pack2(ka ? 1.f : 0.f, kb ? 1.f : 0.f);
+  }
+  bytes = make_uint2(lo, hi);
+}
 
 template <typename T, int CH>
 __global__ void __launch_bounds__(128) dropout_rms_norm_kernel(DropoutNormParams p) {
@@ -72,6 +89,7 @@ __global__ void __launch_bounds__(128) dropout_rms_norm_kernel(DropoutNormParams
   const unsigned long long s1 = (unsigned long long)p.seeds[p.seed_index1];
   const uint32_t k00 = (uint32_t)s0, k01 = (uint32_t)(s0 >> 32);
   const uint32_t k10 = (uint32_t)s1, k11 = (uint32_t)(s1 >> 32);
+  const f32x2 scale2 = splat2(p.scale);
 
   for (long long row = (long long)blockIdx.x * warps + (threadIdx.x >> 5); row < p.rows;
        row += (long long)gridDim.x * warps) {
@@ -91,66 +109,84 @@ __global__ void __launch_bounds__(128) dropout_rms_norm_kernel(DropoutNormParams
       }
     }
 
-    float s[CH][8];
-    float sq = 0.f;
+    f32x2 s[CH][4];
+    f32x2 sq2 = pack2(0.f, 0.f);
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
       const int v = lane + 32 * c;
       if (v < nv) {
-        float xf[8], r[8], u[8];
-        Elem<T>::unpack(xv[c], xf);
-        const float4 a = *reinterpret_cast<const float4*>(&ra[c]);
-        const float4 b = *reinterpret_cast<const float4*>(&rb[c]);
-        r[0] = a.x; r[1] = a.y; r[2] = a.z; r[3] = a.w;
-        r[4] = b.x; r[5] = b.y; r[6] = b.z; r[7] = b.w;
-        uniforms8(row0 + 8ull * v, 0u, k00, k01, u);
-        uint32_t m_lo = 0, m_hi = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const bool keep = Elem<T>::to_f32(Elem<T>::from_f32(u[i])) > p.p_narrow;
-          if (i < 4) m_lo |= (keep ? 1u : 0u) << (8 * i);
-          else m_hi |= (keep ? 1u : 0u) << (8 * (i - 4));
-          const float kept = Elem<T>::to_f32(Elem<T>::from_f32(xf[i] * (keep ? 1.f : 0.f)));
-          const float scaled = Elem<T>::to_f32(Elem<T>::from_f32(kept * p.scale));
-          s[c][i] = r[i] + scaled;
-          sq += s[c][i] * s[c][i];
+        f32x2 xp[4], r[4], m[4];
+        Pairs<T>::unpack(xv[c], xp);
+        {
+          f32x2 t[2];
+          Pairs<float>::unpack(ra[c], t);
+          r[0] = t[0]; r[1] = t[1];
+          Pairs<float>::unpack(rb[c], t);
+          r[2] = t[0]; r[3] = t[1];
         }
-        *reinterpret_cast<uint2*>(p.keep0 + row0 + 8 * v) = make_uint2(m_lo, m_hi);
+        uint32_t w[8];
+        random_words8(row0 + 8ull * v, 0u, k00, k01, w);
+        uint2 bytes;
+        masks8(w, p.keep_from0, bytes, m);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // keep * x is already a value of T; its product with 1/(1-p) is rounded to T, as in the graph
+          const f32x2 scaled = Pairs<T>::word(Pairs<T>::narrow(mul2(mul2(xp[j], m[j]), scale2)));
+          s[c][j] = add2(r[j], scaled);
+          sq2 = fma2(s[c][j], s[c][j], sq2);
+        }
+        *reinterpret_cast<uint2*>(p.keep0 + row0 + 8 * v) = bytes;
         float* so = p.sum + row0 + 8 * v;
-        st_stream(so, make_uint4(__float_as_uint(s[c][0]), __float_as_uint(s[c][1]), __float_as_uint(s[c][2]),
-                                 __float_as_uint(s[c][3])));
-        st_stream(so + 4, make_uint4(__float_as_uint(s[c][4]), __float_as_uint(s[c][5]),
-                                     __float_as_uint(s[c][6]), __float_as_uint(s[c][7])));
+        {
+          const f32x2 t0[2] = {s[c][0], s[c][1]}, t1[2] = {s[c][2], s[c][3]};
+          st_stream(so, Pairs<float>::pack(t0));
+          st_stream(so + 4, Pairs<float>::pack(t1));
+        }
       }
     }
-    sq = warp_reduce<SumOp>(sq);
+    const float sq = warp_reduce<SumOp>(hsum2(sq2));
     const float rstd = rsqrtf(sq / (float)p.cols + p.eps);
     if (lane == 0) p.rstd[row] = rstd;
+    const f32x2 rstd2 = splat2(rstd);
 
     T* yr = reinterpret_cast<T*>(p.y) + row0;
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
       const int v = lane + 32 * c;
       if (v < nv) {
-        float u[8], o[8];
-        uniforms8(row0 + 8ull * v, 1u, k10, k11, u);
-        const float4 wa = __ldg(reinterpret_cast<const float4*>(p.weight + 8 * v));
-        const float4 wb = __ldg(reinterpret_cast<const float4*>(p.weight + 8 * v + 4));
-        const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-        uint32_t m_lo = 0, m_hi = 0;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const bool keep = u[i] > p.p;
-          if (i < 4) m_lo |= (keep ? 1u : 0u) << (8 * i);
-          else m_hi |= (keep ? 1u : 0u) << (8 * (i - 4));
-          const float normed = w[i] * (s[c][i] * rstd);
-          o[i] = (normed * (keep ? 1.f : 0.f)) * p.scale;
+        uint32_t w[8];
+        random_words8(row0 + 8ull * v, 1u, k10, k11, w);
+        uint2 bytes;
+        f32x2 m[4], wt[4];
+        masks8(w, p.keep_from1, bytes, m);
+        {
+          f32x2 t[2];
+          Pairs<float>::unpack(ld_keep(p.weight + 8 * v), t);
+          wt[0] = t[0]; wt[1] = t[1];
+          Pairs<float>::unpack(ld_keep(p.weight + 8 * v + 4), t);
+          wt[2] = t[0]; wt[3] = t[1];
         }
-        *reinterpret_cast<uint2*>(p.keep1 + row0 + 8 * v) = make_uint2(m_lo, m_hi);
-        st_stream(yr + 8 * v, Elem<T>::pack(o));
+        uint32_t o[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          o[j] = Pairs<T>::narrow(mul2(mul2(mul2(wt[j], mul2(s[c][j], rstd2)), m[j]), scale2));
+        *reinterpret_cast<uint2*>(p.keep1 + row0 + 8 * v) = bytes;
+        st_stream(yr + 8 * v, make_uint4(o[0], o[1], o[2], o[3]));
       }
     }
   }
+}
+
+// Smallest n in [0, 2^24] whose uniform n * 2^-24 is kept, for a predicate that is monotonic in n.
+template <typename Keep>
+uint32_t first_kept(Keep keep) {
+  uint32_t lo = 0, hi = 1u << 24;  // the answer lies in [lo, hi]; hi = 2^24 means "never kept"
+  while (lo < hi) {
+    const uint32_t mid = lo + (hi - lo) / 2;
+    if (keep((float)mid * 0x1p-24f)) hi = mid;
+    else lo = mid + 1;
+  }
+  return lo;
 }
 
 template <typename T>
@@ -197,7 +233,7 @@ extern "C" int b200_dropout_rms_norm(const void* x, const void* residual, const 
   q.seeds = reinterpret_cast<const long long*>(seeds);
   q.seed_index0 = seed_index0;
   q.seed_index1 = seed_index1;
-  q.p = (float)p;
+  const float pf = (float)p;
   q.scale = (float)(1.0 / (1.0 - p));
   q.eps = (float)eps;
   q.keep0 = static_cast<unsigned char*>(keep0);
@@ -208,10 +244,17 @@ extern "C" int b200_dropout_rms_norm(const void* x, const void* residual, const 
   q.rows = rows;
   q.cols = (int)cols;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  // second mask: u > p in fp32; first mask: the draw and p are both narrowed to T before the comparison
+  q.keep_from1 = first_kept([&](float u) { return u > pf; });
   if (x_dtype == B200_BF16) {
-    q.p_narrow = __bfloat162float(__float2bfloat16_rn((float)p));
-    return launch_dropout_rms_norm<__nv_bfloat16>(q, st);
+    const float pn = __bfloat162float(__float2bfloat16_rn(pf));
+    q.keep_from0 = first_kept([&](float u) { return __bfloat162float(__float2bfloat16_rn(u)) > pn; });
+  } else {
+    const float pn = __half2float(__float2half_rn(pf));
+    q.keep_from0 = first_kept([&](float u) { return __half2float(__float2half_rn(u)) > pn; });
   }
-  q.p_narrow = __half2float(__float2half_rn((float)p));
+  if (q.keep_from0 >= (1u << 24) || q.keep_from1 >= (1u << 24))
+    return fail(B200_ERR_UNSUPPORTED, "b200_dropout_rms_norm: p = %g keeps nothing at 24-bit resolution", p);
+  if (x_dtype == B200_BF16) return launch_dropout_rms_norm<__nv_bfloat16>(q, st);
   return launch_dropout_rms_norm<__half>(q, st);
 }
