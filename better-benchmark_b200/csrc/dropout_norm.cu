@@ -177,6 +177,134 @@ __global__ void __launch_bounds__(128) dropout_rms_norm_kernel(DropoutNormParams
   }
 }
 
+struct DropoutLayerNormParams {
+  const void* x;
+  const float* residual;
+  const float* weight;
+  const float* bias;
+  const long long* seeds;
+  int seed_index;
+  uint32_t keep_from;  // as in DropoutNormParams
+  float scale, eps;
+  unsigned char* keep;
+  float* xhat;
+  float* y;
+  float* rstd_over_n;
+  long long rows;
+  int cols;
+};
+
+// Dropout -> residual add -> LayerNorm (reference repros/canonical/var_mean_01fbd6c1b27f/repro.py:24-44):
+//   keep = T(rand(seed[i])) > p;  sum = float(T(T(keep * x) * scale)) + residual;
+//   var, mean = var_mean(sum);  rstd = rsqrt(var + eps);  xhat = (sum - mean) * rstd;
+//   y = xhat * w + b;  outputs (keep, xhat, y, rstd / cols).
+// Same row ownership as above; the variance is the centred sum of squares of the row in registers.
+template <typename T, int CH>
+__global__ void __launch_bounds__(128) dropout_layer_norm_kernel(DropoutLayerNormParams p) {
+  const int lane = threadIdx.x & 31;
+  const int warps = blockDim.x >> 5;
+  const int nv = p.cols >> 3;
+  const unsigned long long seed = (unsigned long long)p.seeds[p.seed_index];
+  const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+  const f32x2 scale2 = splat2(p.scale);
+  const float n = (float)p.cols;
+
+  for (long long row = (long long)blockIdx.x * warps + (threadIdx.x >> 5); row < p.rows;
+       row += (long long)gridDim.x * warps) {
+    const unsigned long long row0 = (unsigned long long)row * (unsigned long long)p.cols;
+    const T* xr = reinterpret_cast<const T*>(p.x) + row0;
+    const float* rr = p.residual + row0;
+
+    uint4 xv[CH], ra[CH], rb[CH];
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int v = lane + 32 * c;
+      if (v < nv) {
+        xv[c] = ld_stream(xr + 8 * v);
+        ra[c] = ld_stream(rr + 8 * v);
+        rb[c] = ld_stream(rr + 8 * v + 4);
+      }
+    }
+
+    f32x2 s[CH][4];
+    f32x2 sum2 = pack2(0.f, 0.f);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int v = lane + 32 * c;
+      if (v < nv) {
+        f32x2 xp[4], r[4], m[4];
+        Pairs<T>::unpack(xv[c], xp);
+        {
+          f32x2 t[2];
+          Pairs<float>::unpack(ra[c], t);
+          r[0] = t[0]; r[1] = t[1];
+          Pairs<float>::unpack(rb[c], t);
+          r[2] = t[0]; r[3] = t[1];
+        }
+        uint32_t w[8];
+        random_words8(row0 + 8ull * v, 0u, k0, k1, w);
+        uint2 bytes;
+        masks8(w, p.keep_from, bytes, m);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const f32x2 scaled = Pairs<T>::word(Pairs<T>::narrow(mul2(mul2(xp[j], m[j]), scale2)));
+          s[c][j] = add2(scaled, r[j]);
+          sum2 = add2(sum2, s[c][j]);
+        }
+        *reinterpret_cast<uint2*>(p.keep + row0 + 8 * v) = bytes;
+      }
+    }
+    const float mean = warp_reduce<SumOp>(hsum2(sum2)) / n;
+    const f32x2 mean2 = splat2(mean);
+    f32x2 sq2 = pack2(0.f, 0.f);
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      if (lane + 32 * c < nv) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          s[c][j] = sub2(s[c][j], mean2);
+          sq2 = fma2(s[c][j], s[c][j], sq2);
+        }
+      }
+    }
+    const float rstd = rsqrtf(warp_reduce<SumOp>(hsum2(sq2)) / n + p.eps);
+    if (lane == 0) p.rstd_over_n[row] = rstd / n;
+    const f32x2 rstd2 = splat2(rstd);
+
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int v = lane + 32 * c;
+      if (v < nv) {
+        f32x2 wt[4], bs[4], xh[4], out[4];
+        {
+          f32x2 t[2];
+          Pairs<float>::unpack(ld_keep(p.weight + 8 * v), t);
+          wt[0] = t[0]; wt[1] = t[1];
+          Pairs<float>::unpack(ld_keep(p.weight + 8 * v + 4), t);
+          wt[2] = t[0]; wt[3] = t[1];
+          Pairs<float>::unpack(ld_keep(p.bias + 8 * v), t);
+          bs[0] = t[0]; bs[1] = t[1];
+          Pairs<float>::unpack(ld_keep(p.bias + 8 * v + 4), t);
+          bs[2] = t[0]; bs[3] = t[1];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          xh[j] = mul2(s[c][j], rstd2);
+          out[j] = add2(mul2(xh[j], wt[j]), bs[j]);
+        }
+        float* xo = p.xhat + row0 + 8 * v;
+        float* yo = p.y + row0 + 8 * v;
+        const f32x2 a0[2] = {xh[0], xh[1]}, a1[2] = {xh[2], xh[3]};
+        const f32x2 b0[2] = {out[0], out[1]}, b1[2] = {out[2], out[3]};
+        st_stream(xo, Pairs<float>::pack(a0));
+        st_stream(xo + 4, Pairs<float>::pack(a1));
+        st_stream(yo, Pairs<float>::pack(b0));
+        st_stream(yo + 4, Pairs<float>::pack(b1));
+      }
+    }
+  }
+}
+
 // Smallest n in [0, 2^24] whose uniform n * 2^-24 is kept, for a predicate that is monotonic in n.
 template <typename Keep>
 uint32_t first_kept(Keep keep) {
@@ -201,6 +329,30 @@ int launch_dropout_rms_norm(const DropoutNormParams& p, cudaStream_t st) {
   else if (nv <= 128) dropout_rms_norm_kernel<T, 4><<<grid, 32 * warps, 0, st>>>(p);
   else dropout_rms_norm_kernel<T, 8><<<grid, 32 * warps, 0, st>>>(p);
   return launch_status("b200_dropout_rms_norm");
+}
+
+template <typename T>
+int launch_dropout_layer_norm(const DropoutLayerNormParams& p, cudaStream_t st) {
+  const int nv = p.cols >> 3;
+  const int warps = 4;
+  const long long want = (p.rows + warps - 1) / warps;
+  const long long cap = (long long)device_info().sm_count * 32;
+  const int grid = (int)(want < cap ? want : cap);
+  if (nv <= 32) dropout_layer_norm_kernel<T, 1><<<grid, 32 * warps, 0, st>>>(p);
+  else if (nv <= 64) dropout_layer_norm_kernel<T, 2><<<grid, 32 * warps, 0, st>>>(p);
+  else if (nv <= 128) dropout_layer_norm_kernel<T, 4><<<grid, 32 * warps, 0, st>>>(p);
+  else dropout_layer_norm_kernel<T, 8><<<grid, 32 * warps, 0, st>>>(p);
+  return launch_status("b200_dropout_layer_norm");
+}
+
+// Threshold of the mask whose draw is narrowed to the tensor dtype before the comparison with p.
+uint32_t narrowed_keep_from(float pf, int x_dtype) {
+  if (x_dtype == B200_BF16) {
+    const float pn = __bfloat162float(__float2bfloat16_rn(pf));
+    return first_kept([&](float u) { return __bfloat162float(__float2bfloat16_rn(u)) > pn; });
+  }
+  const float pn = __half2float(__float2half_rn(pf));
+  return first_kept([&](float u) { return __half2float(__float2half_rn(u)) > pn; });
 }
 
 }  // namespace
@@ -246,15 +398,50 @@ extern "C" int b200_dropout_rms_norm(const void* x, const void* residual, const 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   // second mask: u > p in fp32; first mask: the draw and p are both narrowed to T before the comparison
   q.keep_from1 = first_kept([&](float u) { return u > pf; });
-  if (x_dtype == B200_BF16) {
-    const float pn = __bfloat162float(__float2bfloat16_rn(pf));
-    q.keep_from0 = first_kept([&](float u) { return __bfloat162float(__float2bfloat16_rn(u)) > pn; });
-  } else {
-    const float pn = __half2float(__float2half_rn(pf));
-    q.keep_from0 = first_kept([&](float u) { return __half2float(__float2half_rn(u)) > pn; });
-  }
+  q.keep_from0 = narrowed_keep_from(pf, x_dtype);
   if (q.keep_from0 >= (1u << 24) || q.keep_from1 >= (1u << 24))
     return fail(B200_ERR_UNSUPPORTED, "b200_dropout_rms_norm: p = %g keeps nothing at 24-bit resolution", p);
   if (x_dtype == B200_BF16) return launch_dropout_rms_norm<__nv_bfloat16>(q, st);
   return launch_dropout_rms_norm<__half>(q, st);
+}
+
+extern "C" int b200_dropout_layer_norm(const void* x, const void* residual, const void* weight, const void* bias,
+                                       const int64_t* seeds, int32_t seed_index, double p, double eps, void* keep,
+                                       void* xhat, void* y, void* rstd_over_n, int64_t rows, int64_t cols,
+                                       int32_t x_dtype, void* stream) {
+  if (rows < 0 || cols < 0) return fail(B200_ERR_INVALID, "b200_dropout_layer_norm: negative size");
+  if (rows == 0) return B200_OK;
+  if (!x || !residual || !weight || !bias || !seeds || !keep || !xhat || !y || !rstd_over_n)
+    return fail(B200_ERR_INVALID, "b200_dropout_layer_norm: null argument");
+  if (seed_index < 0) return fail(B200_ERR_INVALID, "b200_dropout_layer_norm: negative seed index");
+  if (!(p >= 0.0 && p < 1.0)) return fail(B200_ERR_INVALID, "b200_dropout_layer_norm: p must be in [0, 1)");
+  if (x_dtype != B200_BF16 && x_dtype != B200_F16)
+    return fail(B200_ERR_UNSUPPORTED, "b200_dropout_layer_norm: x must be bf16 or fp16 (dtype %d)", x_dtype);
+  if (cols == 0 || cols % 8 != 0 || cols > 2048)
+    return fail(B200_ERR_UNSUPPORTED,
+                "b200_dropout_layer_norm: row length %lld (supported: multiples of 8 up to 2048)", (long long)cols);
+  if (!aligned16(x) || !aligned16(residual) || !aligned16(weight) || !aligned16(bias) || !aligned16(xhat) ||
+      !aligned16(y) || (reinterpret_cast<uintptr_t>(keep) & 7u))
+    return fail(B200_ERR_ALIGNMENT, "b200_dropout_layer_norm: tensors must be 16-byte aligned (mask 8-byte)");
+  DropoutLayerNormParams q;
+  q.x = x;
+  q.residual = static_cast<const float*>(residual);
+  q.weight = static_cast<const float*>(weight);
+  q.bias = static_cast<const float*>(bias);
+  q.seeds = reinterpret_cast<const long long*>(seeds);
+  q.seed_index = seed_index;
+  q.keep_from = narrowed_keep_from((float)p, x_dtype);
+  if (q.keep_from >= (1u << 24))
+    return fail(B200_ERR_UNSUPPORTED, "b200_dropout_layer_norm: p = %g keeps nothing at 24-bit resolution", p);
+  q.scale = (float)(1.0 / (1.0 - p));
+  q.eps = (float)eps;
+  q.keep = static_cast<unsigned char*>(keep);
+  q.xhat = static_cast<float*>(xhat);
+  q.y = static_cast<float*>(y);
+  q.rstd_over_n = static_cast<float*>(rstd_over_n);
+  q.rows = rows;
+  q.cols = (int)cols;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (x_dtype == B200_BF16) return launch_dropout_layer_norm<__nv_bfloat16>(q, st);
+  return launch_dropout_layer_norm<__half>(q, st);
 }

@@ -62,6 +62,16 @@ def _dropout_rms_inputs(device="cuda", seed=1):
             [256, 128, cols], [256, 128, cols], [256, 128, cols], [rows, cols]]
 
 
+def _dropout_ln_inputs(device="cuda", seed=1):
+    rows, cols = 32768, 768          # four times the rows of the reference's point, to exceed the L2
+    seeds = torch.randint(0, 2 ** 62, (36,), generator=_gen(seed), dtype=torch.int64).to(device)
+    return [_randn((rows, cols), torch.bfloat16, seed, device), seeds,
+            _randn((32, 1024, cols), torch.float32, seed + 100, device),
+            (torch.rand(cols, generator=_gen(seed)) + 0.5).to(device),
+            (torch.rand(cols, generator=_gen(seed + 1)) - 0.5).to(device),
+            [32, 1024, cols], [32, 1024, cols]]
+
+
 def _ln_bwd_inputs(device="cuda", seed=1):
     x = _randn((32768, 768), torch.bfloat16, seed, device)
     dy = _randn((32768, 768), torch.bfloat16, seed + 100, device)
@@ -117,6 +127,10 @@ FAMILY_CASES = {c.name: c for c in [
           "dropout + residual -> RMSNorm -> dropout: x bf16 [32768, 512], residual f32 -> 2 masks, sum f32, rstd, y bf16",
           "bf16", 32768 * 512 * (2 + 4 + 1 + 4 + 1 + 2) + 32768 * 4 + 512 * 4, _dropout_rms_inputs,
           lambda i: dropout_rms_norm.oracle_forward(i)),
+    _case("dropout_layer_norm_bf16",
+          "dropout + residual -> LayerNorm: x bf16 [32768, 768], residual f32 -> mask, xhat f32, y f32, rstd/n",
+          "bf16", 32768 * 768 * (2 + 4 + 1 + 4 + 4) + 32768 * 4 + 2 * 768 * 4, _dropout_ln_inputs,
+          lambda i: dropout_rms_norm.layer_norm_forward(i)),
     _case("layer_norm_bwd_bf16", "LayerNorm backward: x, dy bf16 [32768, 768] -> dx bf16, dweight, dbias f32", "bf16",
           3 * 32768 * 768 * 2 + 768 * 4 * 3 + 2 * 32768 * 4, _ln_bwd_inputs,
           lambda i: kernels.norm_bwd(i[0], i[1], i[2], i[4], mean=i[3], rms=False, want_dbias=True)),

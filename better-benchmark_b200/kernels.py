@@ -568,3 +568,37 @@ def dropout_rms_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tens
                                     _ptr(rstd), _ptr(keep1), _ptr(y), rows, cols, _code(x), _stream()),
           "b200_dropout_rms_norm")
     return keep0, total, rstd, keep1, y
+
+
+def dropout_layer_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor,
+                       seeds: torch.Tensor, seed_index: int, *, p: float, eps: float):
+    """Dropout -> residual add -> LayerNorm over the last dimension.
+
+    x [rows, cols] bf16/fp16, residual fp32 with the same number of elements (any leading shape),
+    weight and bias fp32 [cols], seeds int64. Returns ``(keep, xhat, y, rstd_over_n)``: the mask as
+    bool, ``xhat`` and ``y`` fp32 shaped like ``residual``, ``rstd / cols`` as
+    ``residual.shape[:-1] + (1,)``."""
+    for t in (x, residual, weight, bias, seeds):
+        _require_cuda(t)
+    cols = x.shape[-1]
+    if residual.shape[-1] != cols or residual.numel() != x.numel() or weight.numel() != cols \
+            or bias.numel() != cols:
+        raise native.KernelArgumentError("dropout_layer_norm: tensors disagree on the row length")
+    if any(t.dtype != torch.float32 for t in (residual, weight, bias)) or seeds.dtype != torch.int64:
+        raise native.KernelArgumentError("dropout_layer_norm: residual, weight and bias must be fp32, seeds int64")
+    if not all(t.is_contiguous() for t in (x, residual, weight, bias, seeds)):
+        raise UnsupportedLayout("dropout_layer_norm: tensors must be contiguous")
+    if not 0 <= seed_index < seeds.numel():
+        raise native.KernelArgumentError("dropout_layer_norm: seed index outside the seed tensor")
+    rows = x.numel() // cols if cols else 0
+    dev = x.device
+    keep = torch.empty(residual.shape, dtype=torch.bool, device=dev)
+    xhat = torch.empty_like(residual)
+    y = torch.empty_like(residual)
+    rstd_over_n = torch.empty(tuple(residual.shape[:-1]) + (1,), dtype=torch.float32, device=dev)
+    lib = load()
+    check(lib.b200_dropout_layer_norm(_ptr(x), _ptr(residual), _ptr(weight), _ptr(bias), _ptr(seeds),
+                                      int(seed_index), float(p), float(eps), _ptr(keep), _ptr(xhat), _ptr(y),
+                                      _ptr(rstd_over_n), rows, cols, _code(x), _stream()),
+          "b200_dropout_layer_norm")
+    return keep, xhat, y, rstd_over_n

@@ -177,6 +177,18 @@ int32_t b200_dropout_rms_norm(const void* x, const void* residual, const void* w
                               void* sum, void* rstd, void* keep1, void* y, int64_t rows, int64_t cols,
                               int32_t x_dtype, void* stream);
 
+/* Dropout -> residual add -> LayerNorm over rows of `cols` elements (a multiple of 8, at most 2048):
+ * keep = T(u) > p; sum = T(T(keep * x) * 1/(1-p)) + residual; var, mean = var_mean(sum);
+ * rstd = rsqrt(var + eps); xhat = (sum - mean) * rstd; y = xhat * weight + bias.
+ * x: x_dtype (bf16 or fp16) [rows, cols]; residual, xhat, y: fp32 [rows, cols]; weight, bias: fp32 [cols];
+ * rstd_over_n: fp32 [rows] = rstd / cols; keep: one byte per element. u as in b200_dropout_rms_norm (mask
+ * number 0, key seeds[seed_index]).
+ * Replaces var_mean_01fbd6c1b27f/oracle.py (kernel and wrapper); graph var_mean_01fbd6c1b27f/repro.py:24-44. */
+int32_t b200_dropout_layer_norm(const void* x, const void* residual, const void* weight, const void* bias,
+                                const int64_t* seeds, int32_t seed_index, double p, double eps, void* keep,
+                                void* xhat, void* y, void* rstd_over_n, int64_t rows, int64_t cols,
+                                int32_t x_dtype, void* stream);
+
 /* Contiguous cast / scale of n elements.
  * Replaces pointwise_8bb40810003c/oracle.py:11-15 and pointwise_95ed2ef35da9/oracle.py:10-44. */
 int32_t b200_cast_scale(const void* x, void* y, int64_t n, int32_t in_dtype, int32_t out_dtype, double scale,

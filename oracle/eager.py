@@ -381,3 +381,33 @@ class DropoutResidualRMSNorm(nn.Module):
         mul_5 = aten.mul.Tensor(aten.mul.Tensor(keep1, mul_3), self.scale)
         y = aten.view.default(prims.convert_element_type.default(mul_5, x.dtype), list(x.shape))
         return (keep0, add, rsqrt, keep1, y)
+
+
+class DropoutResidualLayerNorm(nn.Module):
+    """dropout(x) + residual -> LayerNorm, returning (keep, xhat, y, rstd / cols).
+
+    Graph: reference repros/canonical/var_mean_01fbd6c1b27f/repro.py:24-44 (the uniform tensor is
+    narrowed to x's dtype before the comparison; var_mean with correction 0; the affine output and
+    the normalised values stay fp32). ``mask`` replaces the draw, as in ``DropoutResidualRMSNorm``.
+    """
+
+    def __init__(self, p: float, eps: float, seed_index: int = 0):
+        super().__init__()
+        self.p, self.eps, self.seed_index = p, eps, seed_index
+        self.scale = 1.0 / (1.0 - p)
+
+    def forward(self, x, seeds, residual, weight, bias, mask=None):
+        import torch._inductor.inductor_prims  # noqa: F401
+        shape = list(residual.shape)
+        view = aten.view.default(x, shape)
+        if mask is None:
+            seed = prims.inductor_lookup_seed.default(seeds, self.seed_index)
+            rand = prims.inductor_random.default(shape, seed, "rand")
+            mask = aten.gt.Scalar(prims.convert_element_type.default(rand, x.dtype), self.p)
+        mul_1 = aten.mul.Tensor(aten.mul.Tensor(mask, view), self.scale)
+        add = aten.add.Tensor(mul_1, residual)
+        var, mean = aten.var_mean.correction(add, [len(shape) - 1], correction=0, keepdim=True)
+        rsqrt = aten.rsqrt.default(aten.add.Tensor(var, self.eps))
+        xhat = aten.mul.Tensor(aten.sub.Tensor(add, mean), rsqrt)
+        y = aten.add.Tensor(aten.mul.Tensor(xhat, weight), bias)
+        return (mask, xhat, y, aten.div.Tensor(rsqrt, shape[-1]))

@@ -59,6 +59,10 @@ CASES = {
     "dropout_rms_014afd4984e6": ("mean_014afd4984e6",
                                  [[[64, 512], "bf16"], [[84], "i64"], [[2, 32, 512], "f32"], [[512], "f32"],
                                   ["S", [2, 32, 512]], ["S", [2, 32, 512]], ["S", [2, 32, 512]], ["S", [64, 512]]]),
+    # the row length stays 768: the captured graph hard-codes it as a divisor
+    "dropout_ln_01fbd6c1b27f": ("var_mean_01fbd6c1b27f",
+                                [[[64, 768], "bf16"], [[36], "i64"], [[2, 32, 768], "f32"], [[768], "f32"],
+                                 [[768], "f32"], ["S", [2, 32, 768]], ["S", [2, 32, 768]]]),
 }
 
 

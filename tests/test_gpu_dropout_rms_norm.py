@@ -117,3 +117,44 @@ def test_through_the_shipped_stub_and_harness():
     assert torch.equal(total, w_total)
     assert_close(rstd, w_rstd, "rstd")
     assert_close(y, w_y, "y")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,cols,lead", [(64, 768, (2, 32)), (1, 8, None), (9, 264, None), (33, 1024, (3, 11)),
+                                            (5, 2048, None), (8192, 768, (8, 1024))])
+@pytest.mark.parametrize("p", [0.1, 0.3])
+def test_dropout_layer_norm(dtype, rows, cols, lead, p):
+    from better_benchmark_b200 import kernels
+    from oracle import eager
+    from oracle.philox import uniforms
+    x, seeds, residual, weight = _inputs(rows, cols, dtype, rows * 3 + cols, lead)
+    bias = torch.randn(cols, device="cuda") * 0.1
+    keep, xhat, y, rstd_n = kernels.dropout_layer_norm(x, residual, weight, bias, seeds, 35, p=p, eps=1e-5)
+    assert keep.dtype == torch.bool and keep.shape == residual.shape
+    assert xhat.dtype == y.dtype == torch.float32 and xhat.shape == y.shape == residual.shape
+    assert rstd_n.shape == (*residual.shape[:-1], 1)
+
+    u = torch.from_numpy(uniforms(rows * cols, seeds.cpu().tolist()[35], 0))
+    assert torch.equal(keep.cpu().view(-1), u.to(dtype) > p)
+
+    _, w_xhat, w_y, w_rstd_n = eager.DropoutResidualLayerNorm(p, 1e-5, 35)(x, seeds, residual, weight, bias, mask=keep)
+    assert_close(rstd_n, w_rstd_n, "rstd / n")
+    # fp32 outputs of a normalisation: the row statistics differ in their last bits with the
+    # summation order, which every element inherits
+    assert (xhat - w_xhat).abs().max().item() <= 2e-5 * max(1.0, w_xhat.abs().max().item())
+    assert (y - w_y).abs().max().item() <= 2e-5 * max(1.0, w_y.abs().max().item())
+
+
+def test_dropout_layer_norm_through_the_family_and_rejections():
+    from better_benchmark_b200 import kernels, native
+    from better_benchmark_b200.families import dropout_rms_norm
+    x, seeds, residual, weight = _inputs(128, 768, torch.bfloat16, 4, (2, 64))
+    bias = torch.zeros(768, device="cuda")
+    out = dropout_rms_norm.layer_norm_forward([x, seeds, residual, weight, bias, [2, 64, 768], [2, 64, 768]])
+    assert len(out) == 4 and abs(out[0].float().mean().item() - 0.9) < 0.01
+    again = dropout_rms_norm.layer_norm_forward([x, seeds, residual, weight, bias, [2, 64, 768], [2, 64, 768]])
+    assert all(torch.equal(a, b) for a, b in zip(out, again))
+    with pytest.raises(native.KernelArgumentError):
+        kernels.dropout_layer_norm(x, residual, weight, bias, seeds, 84, p=0.1, eps=1e-5)
+    with pytest.raises(native.KernelArgumentError):
+        kernels.dropout_layer_norm(x, residual, weight, bias[:-8], seeds, 0, p=0.1, eps=1e-5)

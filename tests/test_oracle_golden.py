@@ -80,7 +80,13 @@ def golden_cases():
         masks = (recorded[0], recorded[3]) if recorded is not None else None
         return list(eager.DropoutResidualRMSNorm(0.1, 1e-6, 82, 83)(x, seeds, residual, w, masks=masks))
 
+    def dropout_ln(inp, recorded=None):
+        x, seeds, residual, w, b, _s0, _s1 = inp
+        mask = recorded[0] if recorded is not None else None
+        return list(eager.DropoutResidualLayerNorm(0.1, 1e-5, 35)(x, seeds, residual, w, b, mask=mask))
+
     return {
+        "dropout_ln_01fbd6c1b27f": dropout_ln,
         "dropout_rms_014afd4984e6": dropout_rms,
         "ln_fwd_f8ec553e339e": ln_fwd, "rmsnorm_fwd_f667cd8901af": rms_fwd,
         "softmax_bias_20ccc18dda60": softmax_bias, "bn_relu_42fad1ece813": bn_relu,
@@ -93,7 +99,7 @@ def golden_cases():
 
 
 CASE_NAMES = sorted(p.stem for p in GOLDEN.glob("*.pt"))
-STOCHASTIC = {"dropout_rms_014afd4984e6"}   # cases whose region draws random numbers
+STOCHASTIC = {"dropout_rms_014afd4984e6", "dropout_ln_01fbd6c1b27f"}   # cases whose region draws random numbers
 
 
 def _clone(inputs):
