@@ -326,7 +326,9 @@ int launch_dropout_rms_norm(const DropoutNormParams& p, cudaStream_t st) {
   const int grid = (int)(want < cap ? want : cap);
   if (nv <= 32) dropout_rms_norm_kernel<T, 1><<<grid, 32 * warps, 0, st>>>(p);
   else if (nv <= 64) dropout_rms_norm_kernel<T, 2><<<grid, 32 * warps, 0, st>>>(p);
+  else if (nv <= 96) dropout_rms_norm_kernel<T, 3><<<grid, 32 * warps, 0, st>>>(p);
   else if (nv <= 128) dropout_rms_norm_kernel<T, 4><<<grid, 32 * warps, 0, st>>>(p);
+  else if (nv <= 192) dropout_rms_norm_kernel<T, 6><<<grid, 32 * warps, 0, st>>>(p);
   else dropout_rms_norm_kernel<T, 8><<<grid, 32 * warps, 0, st>>>(p);
   return launch_status("b200_dropout_rms_norm");
 }
@@ -340,7 +342,9 @@ int launch_dropout_layer_norm(const DropoutLayerNormParams& p, cudaStream_t st) 
   const int grid = (int)(want < cap ? want : cap);
   if (nv <= 32) dropout_layer_norm_kernel<T, 1><<<grid, 32 * warps, 0, st>>>(p);
   else if (nv <= 64) dropout_layer_norm_kernel<T, 2><<<grid, 32 * warps, 0, st>>>(p);
+  else if (nv <= 96) dropout_layer_norm_kernel<T, 3><<<grid, 32 * warps, 0, st>>>(p);
   else if (nv <= 128) dropout_layer_norm_kernel<T, 4><<<grid, 32 * warps, 0, st>>>(p);
+  else if (nv <= 192) dropout_layer_norm_kernel<T, 6><<<grid, 32 * warps, 0, st>>>(p);
   else dropout_layer_norm_kernel<T, 8><<<grid, 32 * warps, 0, st>>>(p);
   return launch_status("b200_dropout_layer_norm");
 }
