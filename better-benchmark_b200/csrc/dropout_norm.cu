@@ -19,26 +19,42 @@
 namespace b200 {
 namespace {
 
-__device__ __forceinline__ uint4 philox4x32_10(uint4 c, uint32_t k0, uint32_t k1) {
+// The ten round keys of one seed: key + r * (0x9E3779B9, 0xBB67AE85). They are the same for every
+// element, so a kernel computes them once and every call only multiplies and xors.
+struct PhiloxKeys {
+  uint32_t k0[10], k1[10];
+};
+__device__ __forceinline__ PhiloxKeys philox_keys(unsigned long long seed) {
+  PhiloxKeys k;
+  uint32_t a = (uint32_t)seed, b = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    k.k0[r] = a;
+    k.k1[r] = b;
+    a += 0x9E3779B9u;
+    b += 0xBB67AE85u;
+  }
+  return k;
+}
+
+__device__ __forceinline__ uint4 philox4x32_10(uint4 c, const PhiloxKeys& k) {
 #pragma unroll
   for (int r = 0; r < 10; ++r) {
     const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
     const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
-    c = make_uint4(hi1 ^ c.y ^ k0, lo1, hi0 ^ c.w ^ k1, lo0);
-    k0 += 0x9E3779B9u;
-    k1 += 0xBB67AE85u;
+    c = make_uint4(hi1 ^ c.y ^ k.k0[r], lo1, hi0 ^ c.w ^ k.k1[r], lo0);
   }
   return c;
 }
 
 // Random words for the elements [e0, e0+8) of mask number `which`; e0 is a multiple of 8.
-__device__ __forceinline__ void random_words8(unsigned long long e0, uint32_t which, uint32_t k0, uint32_t k1,
+__device__ __forceinline__ void random_words8(unsigned long long e0, uint32_t which, const PhiloxKeys& k,
                                               uint32_t (&w)[8]) {
   const unsigned long long g = e0 >> 2;
 #pragma unroll
   for (int h = 0; h < 2; ++h) {
     const unsigned long long gi = g + h;
-    const uint4 r = philox4x32_10(make_uint4((uint32_t)gi, (uint32_t)(gi >> 32), which, 0u), k0, k1);
+    const uint4 r = philox4x32_10(make_uint4((uint32_t)gi, (uint32_t)(gi >> 32), which, 0u), k);
     w[4 * h + 0] = r.x;
     w[4 * h + 1] = r.y;
     w[4 * h + 2] = r.z;
@@ -87,8 +103,7 @@ __global__ void __launch_bounds__(128) dropout_rms_norm_kernel(DropoutNormParams
   const int nv = p.cols >> 3;  // vectors of 8 elements per row
   const unsigned long long s0 = (unsigned long long)p.seeds[p.seed_index0];
   const unsigned long long s1 = (unsigned long long)p.seeds[p.seed_index1];
-  const uint32_t k00 = (uint32_t)s0, k01 = (uint32_t)(s0 >> 32);
-  const uint32_t k10 = (uint32_t)s1, k11 = (uint32_t)(s1 >> 32);
+  const PhiloxKeys keys0 = philox_keys(s0), keys1 = philox_keys(s1);
   const f32x2 scale2 = splat2(p.scale);
 
   for (long long row = (long long)blockIdx.x * warps + (threadIdx.x >> 5); row < p.rows;
@@ -125,7 +140,7 @@ __global__ void __launch_bounds__(128) dropout_rms_norm_kernel(DropoutNormParams
           r[2] = t[0]; r[3] = t[1];
         }
         uint32_t w[8];
-        random_words8(row0 + 8ull * v, 0u, k00, k01, w);
+        random_words8(row0 + 8ull * v, 0u, keys0, w);
         uint2 bytes;
         masks8(w, p.keep_from0, bytes, m);
 #pragma unroll
@@ -155,7 +170,7 @@ __global__ void __launch_bounds__(128) dropout_rms_norm_kernel(DropoutNormParams
       const int v = lane + 32 * c;
       if (v < nv) {
         uint32_t w[8];
-        random_words8(row0 + 8ull * v, 1u, k10, k11, w);
+        random_words8(row0 + 8ull * v, 1u, keys1, w);
         uint2 bytes;
         f32x2 m[4], wt[4];
         masks8(w, p.keep_from1, bytes, m);
@@ -176,6 +191,9 @@ __global__ void __launch_bounds__(128) dropout_rms_norm_kernel(DropoutNormParams
     }
   }
 }
+
+// CTAs per SM that the register allocation has to leave room for, by chunks per lane.
+constexpr int min_ctas(int ch) { return ch <= 1 ? 7 : ch <= 3 ? 5 : ch == 4 ? 4 : 1; }
 
 struct DropoutLayerNormParams {
   const void* x;
@@ -200,12 +218,12 @@ struct DropoutLayerNormParams {
 //   y = xhat * w + b;  outputs (keep, xhat, y, rstd / cols).
 // Same row ownership as above; the variance is the centred sum of squares of the row in registers.
 template <typename T, int CH>
-__global__ void __launch_bounds__(128) dropout_layer_norm_kernel(DropoutLayerNormParams p) {
+__global__ void __launch_bounds__(128, min_ctas(CH)) dropout_layer_norm_kernel(DropoutLayerNormParams p) {
   const int lane = threadIdx.x & 31;
   const int warps = blockDim.x >> 5;
   const int nv = p.cols >> 3;
   const unsigned long long seed = (unsigned long long)p.seeds[p.seed_index];
-  const uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+  const PhiloxKeys keys = philox_keys(seed);
   const f32x2 scale2 = splat2(p.scale);
   const float n = (float)p.cols;
 
@@ -242,7 +260,7 @@ __global__ void __launch_bounds__(128) dropout_layer_norm_kernel(DropoutLayerNor
           r[2] = t[0]; r[3] = t[1];
         }
         uint32_t w[8];
-        random_words8(row0 + 8ull * v, 0u, k0, k1, w);
+        random_words8(row0 + 8ull * v, 0u, keys, w);
         uint2 bytes;
         masks8(w, p.keep_from, bytes, m);
 #pragma unroll
