@@ -323,6 +323,66 @@ __global__ void __launch_bounds__(128, min_ctas(CH)) dropout_layer_norm_kernel(D
   }
 }
 
+struct DropoutAddParams {
+  const void* x;
+  const float* residual;
+  const long long* seeds;
+  int seed_index;
+  uint32_t keep_from;
+  float scale;
+  unsigned char* keep;
+  float* sum;
+  long long vecs;  // vectors of 8 elements
+};
+
+// Dropout -> residual add with no reduction (reference repros/canonical/pointwise_4b076ed1ff41/repro.py:24-32):
+//   keep = T(rand(seed[i])) > p;  sum = residual + float(T(T(keep * x) * scale)).
+// Flat over the elements, two vectors of 8 in flight per thread.
+template <typename T>
+__global__ void __launch_bounds__(256) dropout_add_kernel(DropoutAddParams p) {
+  const PhiloxKeys keys = philox_keys((unsigned long long)p.seeds[p.seed_index]);
+  const f32x2 scale2 = splat2(p.scale);
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const T* x = reinterpret_cast<const T*>(p.x);
+  for (long long v0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; v0 < p.vecs; v0 += 2 * stride) {
+    const long long vi[2] = {v0, v0 + stride};
+    uint4 xv[2], ra[2], rb[2];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (vi[u] < p.vecs) {
+        xv[u] = ld_stream(x + 8 * vi[u]);
+        ra[u] = ld_stream(p.residual + 8 * vi[u]);
+        rb[u] = ld_stream(p.residual + 8 * vi[u] + 4);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (vi[u] < p.vecs) {
+        f32x2 xp[4], r[4], m[4], s[4];
+        Pairs<T>::unpack(xv[u], xp);
+        {
+          f32x2 t[2];
+          Pairs<float>::unpack(ra[u], t);
+          r[0] = t[0]; r[1] = t[1];
+          Pairs<float>::unpack(rb[u], t);
+          r[2] = t[0]; r[3] = t[1];
+        }
+        uint32_t w[8];
+        random_words8(8ull * (unsigned long long)vi[u], 0u, keys, w);
+        uint2 bytes;
+        masks8(w, p.keep_from, bytes, m);
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          s[j] = add2(r[j], Pairs<T>::word(Pairs<T>::narrow(mul2(mul2(xp[j], m[j]), scale2))));
+        *reinterpret_cast<uint2*>(p.keep + 8 * vi[u]) = bytes;
+        const f32x2 t0[2] = {s[0], s[1]}, t1[2] = {s[2], s[3]};
+        st_stream(p.sum + 8 * vi[u], Pairs<float>::pack(t0));
+        st_stream(p.sum + 8 * vi[u] + 4, Pairs<float>::pack(t1));
+      }
+    }
+  }
+}
+
 // Smallest n in [0, 2^24] whose uniform n * 2^-24 is kept, for a predicate that is monotonic in n.
 template <typename Keep>
 uint32_t first_kept(Keep keep) {
@@ -466,4 +526,37 @@ extern "C" int b200_dropout_layer_norm(const void* x, const void* residual, cons
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (x_dtype == B200_BF16) return launch_dropout_layer_norm<__nv_bfloat16>(q, st);
   return launch_dropout_layer_norm<__half>(q, st);
+}
+
+extern "C" int b200_dropout_add(const void* x, const void* residual, const int64_t* seeds, int32_t seed_index,
+                                double p, void* keep, void* sum, int64_t n, int32_t x_dtype, void* stream) {
+  if (n < 0) return fail(B200_ERR_INVALID, "b200_dropout_add: negative size");
+  if (n == 0) return B200_OK;
+  if (!x || !residual || !seeds || !keep || !sum) return fail(B200_ERR_INVALID, "b200_dropout_add: null argument");
+  if (seed_index < 0) return fail(B200_ERR_INVALID, "b200_dropout_add: negative seed index");
+  if (!(p >= 0.0 && p < 1.0)) return fail(B200_ERR_INVALID, "b200_dropout_add: p must be in [0, 1)");
+  if (x_dtype != B200_BF16 && x_dtype != B200_F16)
+    return fail(B200_ERR_UNSUPPORTED, "b200_dropout_add: x must be bf16 or fp16 (dtype %d)", x_dtype);
+  if (n % 8 != 0) return fail(B200_ERR_UNSUPPORTED, "b200_dropout_add: %lld elements (supported: multiples of 8)", (long long)n);
+  if (!aligned16(x) || !aligned16(residual) || !aligned16(sum) || (reinterpret_cast<uintptr_t>(keep) & 7u))
+    return fail(B200_ERR_ALIGNMENT, "b200_dropout_add: tensors must be 16-byte aligned (mask 8-byte)");
+  DropoutAddParams q;
+  q.x = x;
+  q.residual = static_cast<const float*>(residual);
+  q.seeds = reinterpret_cast<const long long*>(seeds);
+  q.seed_index = seed_index;
+  q.keep_from = narrowed_keep_from((float)p, x_dtype);
+  if (q.keep_from >= (1u << 24))
+    return fail(B200_ERR_UNSUPPORTED, "b200_dropout_add: p = %g keeps nothing at 24-bit resolution", p);
+  q.scale = (float)(1.0 / (1.0 - p));
+  q.keep = static_cast<unsigned char*>(keep);
+  q.sum = static_cast<float*>(sum);
+  q.vecs = n / 8;
+  const long long want = (q.vecs + 2 * 256 - 1) / (2 * 256);
+  const long long cap = (long long)device_info().sm_count * 32;
+  const int grid = (int)(want < cap ? want : cap);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (x_dtype == B200_BF16) dropout_add_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(q);
+  else dropout_add_kernel<__half><<<grid, 256, 0, st>>>(q);
+  return launch_status("b200_dropout_add");
 }

@@ -8,7 +8,11 @@ repros/canonical/mean_014afd4984e6/repro.py:24-47 (replaced kernel .../oracle.py
 
 ``layer_norm_forward`` covers dropout(x) + residual -> LayerNorm of
 repros/canonical/var_mean_01fbd6c1b27f/repro.py:24-44: inputs ``(x, seeds, residual, weight, bias, shape,
-shape)``, outputs ``(keep, xhat, y, rstd / cols)``, seed ``seeds[35]``, eps 1e-5."""
+shape)``, outputs ``(keep, xhat, y, rstd / cols)``, seed ``seeds[35]``, eps 1e-5.
+
+``add_forward`` covers dropout(x) + residual without a norm
+(repros/canonical/pointwise_4b076ed1ff41/repro.py:24-32 and its siblings): outputs ``(keep, sum)`` shaped
+like the residual (or like the trailing shape parameter when the graph reshapes the sum)."""
 from .. import kernels
 
 DROPOUT_P = 0.1
@@ -24,3 +28,9 @@ def oracle_forward(inputs, *, p=DROPOUT_P, eps=EPS, seed_index0=SEED_INDEX0, see
 def layer_norm_forward(inputs, *, p=DROPOUT_P, eps=1e-5, seed_index=35):
     x, seeds, residual, weight, bias = inputs[:5]
     return kernels.dropout_layer_norm(x, residual, weight, bias, seeds, seed_index, p=p, eps=eps)
+
+
+def add_forward(inputs, *, p=DROPOUT_P, seed_index=1, order=("x", "seeds", "residual"), out_shape=None):
+    named = dict(zip(order, inputs[:3]))
+    keep, total = kernels.dropout_add(named["x"], named["residual"], named["seeds"], seed_index, p=p)
+    return keep, (total.view(list(out_shape)) if out_shape is not None else total)

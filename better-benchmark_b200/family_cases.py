@@ -62,6 +62,13 @@ def _dropout_rms_inputs(device="cuda", seed=1):
             [256, 128, cols], [256, 128, cols], [256, 128, cols], [rows, cols]]
 
 
+def _dropout_add_inputs(device="cuda", seed=1):
+    rows, cols = 16384, 2560         # four times the rows of the reference's largest point
+    seeds = torch.randint(0, 2 ** 62, (2,), generator=_gen(seed), dtype=torch.int64).to(device)
+    return [_randn((rows, cols), torch.bfloat16, seed, device), seeds,
+            _randn((128, 128, cols), torch.float32, seed + 100, device), [128, 128, cols], [128, 128, cols]]
+
+
 def _dropout_ln_inputs(device="cuda", seed=1):
     rows, cols = 32768, 768          # four times the rows of the reference's point, to exceed the L2
     seeds = torch.randint(0, 2 ** 62, (36,), generator=_gen(seed), dtype=torch.int64).to(device)
@@ -127,6 +134,8 @@ FAMILY_CASES = {c.name: c for c in [
           "dropout + residual -> RMSNorm -> dropout: x bf16 [32768, 512], residual f32 -> 2 masks, sum f32, rstd, y bf16",
           "bf16", 32768 * 512 * (2 + 4 + 1 + 4 + 1 + 2) + 32768 * 4 + 512 * 4, _dropout_rms_inputs,
           lambda i: dropout_rms_norm.oracle_forward(i)),
+    _case("dropout_add_bf16", "dropout + residual: x bf16 [16384, 2560], residual f32 -> mask, sum f32", "bf16",
+          16384 * 2560 * (2 + 4 + 1 + 4), _dropout_add_inputs, lambda i: dropout_rms_norm.add_forward(i)),
     _case("dropout_layer_norm_bf16",
           "dropout + residual -> LayerNorm: x bf16 [32768, 768], residual f32 -> mask, xhat f32, y f32, rstd/n",
           "bf16", 32768 * 768 * (2 + 4 + 1 + 4 + 4) + 32768 * 4 + 2 * 768 * 4, _dropout_ln_inputs,

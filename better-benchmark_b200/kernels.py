@@ -602,3 +602,24 @@ def dropout_layer_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Te
                                       _ptr(rstd_over_n), rows, cols, _code(x), _stream()),
           "b200_dropout_layer_norm")
     return keep, xhat, y, rstd_over_n
+
+
+def dropout_add(x: torch.Tensor, residual: torch.Tensor, seeds: torch.Tensor, seed_index: int, *, p: float):
+    """``residual + dropout(x)``: x bf16/fp16, residual fp32 with the same number of elements. Returns
+    ``(keep, sum)`` shaped like ``residual`` (bool, fp32)."""
+    for t in (x, residual, seeds):
+        _require_cuda(t)
+    if residual.numel() != x.numel():
+        raise native.KernelArgumentError("dropout_add: x and residual differ in size")
+    if residual.dtype != torch.float32 or seeds.dtype != torch.int64:
+        raise native.KernelArgumentError("dropout_add: residual must be fp32, seeds int64")
+    if not all(t.is_contiguous() for t in (x, residual, seeds)):
+        raise UnsupportedLayout("dropout_add: tensors must be contiguous")
+    if not 0 <= seed_index < seeds.numel():
+        raise native.KernelArgumentError("dropout_add: seed index outside the seed tensor")
+    keep = torch.empty(residual.shape, dtype=torch.bool, device=x.device)
+    total = torch.empty_like(residual)
+    lib = load()
+    check(lib.b200_dropout_add(_ptr(x), _ptr(residual), _ptr(seeds), int(seed_index), float(p), _ptr(keep),
+                               _ptr(total), x.numel(), _code(x), _stream()), "b200_dropout_add")
+    return keep, total

@@ -189,6 +189,14 @@ int32_t b200_dropout_layer_norm(const void* x, const void* residual, const void*
                                 void* xhat, void* y, void* rstd_over_n, int64_t rows, int64_t cols,
                                 int32_t x_dtype, void* stream);
 
+/* Dropout -> residual add over n elements (a multiple of 8): keep = T(u) > p;
+ * sum = residual + T(T(keep * x) * 1/(1-p)). x: x_dtype (bf16 or fp16); residual, sum: fp32; keep: one byte per
+ * element; u as in b200_dropout_rms_norm (mask number 0, key seeds[seed_index]).
+ * Replaces pointwise_4b076ed1ff41/oracle.py, pointwise_7bd204513fbb/oracle.py, pointwise_6e7efb08a440/oracle.py
+ * (kernel and wrapper); graph pointwise_4b076ed1ff41/repro.py:24-32. */
+int32_t b200_dropout_add(const void* x, const void* residual, const int64_t* seeds, int32_t seed_index, double p,
+                         void* keep, void* sum, int64_t n, int32_t x_dtype, void* stream);
+
 /* Contiguous cast / scale of n elements.
  * Replaces pointwise_8bb40810003c/oracle.py:11-15 and pointwise_95ed2ef35da9/oracle.py:10-44. */
 int32_t b200_cast_scale(const void* x, void* y, int64_t n, int32_t in_dtype, int32_t out_dtype, double scale,

@@ -411,3 +411,28 @@ class DropoutResidualLayerNorm(nn.Module):
         xhat = aten.mul.Tensor(aten.sub.Tensor(add, mean), rsqrt)
         y = aten.add.Tensor(aten.mul.Tensor(xhat, weight), bias)
         return (mask, xhat, y, aten.div.Tensor(rsqrt, shape[-1]))
+
+
+class DropoutAdd(nn.Module):
+    """residual + dropout(x), returning (keep, sum).
+
+    Graph: reference repros/canonical/pointwise_4b076ed1ff41/repro.py:24-32 (the uniform tensor is
+    narrowed to x's dtype before the comparison; the scaled product is rounded to x's dtype before
+    the fp32 addition). ``mask`` replaces the draw, as in ``DropoutResidualRMSNorm``.
+    """
+
+    def __init__(self, p: float, seed_index: int = 0):
+        super().__init__()
+        self.p, self.seed_index = p, seed_index
+        self.scale = 1.0 / (1.0 - p)
+
+    def forward(self, x, seeds, residual, mask=None):
+        import torch._inductor.inductor_prims  # noqa: F401
+        shape = list(residual.shape)
+        view = aten.view.default(x, shape)
+        if mask is None:
+            seed = prims.inductor_lookup_seed.default(seeds, self.seed_index)
+            rand = prims.inductor_random.default(shape, seed, "rand")
+            mask = aten.gt.Scalar(prims.convert_element_type.default(rand, x.dtype), self.p)
+        mul_1 = aten.mul.Tensor(aten.mul.Tensor(mask, view), self.scale)
+        return (mask, aten.add.Tensor(residual, mul_1))

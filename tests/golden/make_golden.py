@@ -63,6 +63,9 @@ CASES = {
     "dropout_ln_01fbd6c1b27f": ("var_mean_01fbd6c1b27f",
                                 [[[64, 768], "bf16"], [[36], "i64"], [[2, 32, 768], "f32"], [[768], "f32"],
                                  [[768], "f32"], ["S", [2, 32, 768]], ["S", [2, 32, 768]]]),
+    "dropout_add_4b076ed1ff41": ("pointwise_4b076ed1ff41",
+                                 [[[48, 320], "bf16"], [[2], "i64"], [[3, 16, 320], "f32"],
+                                  ["S", [3, 16, 320]], ["S", [3, 16, 320]]]),
 }
 
 

@@ -158,3 +158,42 @@ def test_dropout_layer_norm_through_the_family_and_rejections():
         kernels.dropout_layer_norm(x, residual, weight, bias, seeds, 84, p=0.1, eps=1e-5)
     with pytest.raises(native.KernelArgumentError):
         kernels.dropout_layer_norm(x, residual, weight, bias[:-8], seeds, 0, p=0.1, eps=1e-5)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("shape", [(1, 8), (3, 16, 320), (48, 2560), (7, 33, 8), (4096, 1024)])
+@pytest.mark.parametrize("p", [0.1, 0.5])
+def test_dropout_add(dtype, shape, p):
+    from better_benchmark_b200 import kernels
+    from oracle import eager
+    from oracle.philox import uniforms
+    g = torch.Generator(device="cuda").manual_seed(sum(shape))
+    n = 1
+    for d in shape:
+        n *= d
+    x = (torch.randn(n // shape[-1], shape[-1], generator=g, device="cuda") * 2).to(dtype)
+    residual = torch.randn(shape, generator=g, device="cuda")
+    seeds = torch.randint(0, 2 ** 62, (4,), generator=g, device="cuda", dtype=torch.int64)
+    keep, total = kernels.dropout_add(x, residual, seeds, 3, p=p)
+    assert keep.shape == total.shape == residual.shape and keep.dtype == torch.bool
+    u = torch.from_numpy(uniforms(n, seeds.cpu().tolist()[3], 0))
+    assert torch.equal(keep.cpu().view(-1), u.to(dtype) > p)
+    _, want = eager.DropoutAdd(p, 3)(x, seeds, residual, mask=keep)
+    assert torch.equal(total, want)
+
+
+def test_dropout_add_stub_argument_orders_and_rejections():
+    from better_benchmark_b200 import kernels, native
+    from better_benchmark_b200.families import dropout_rms_norm
+    g = torch.Generator(device="cuda").manual_seed(11)
+    x = torch.randn(64, 768, generator=g, device="cuda").to(torch.bfloat16)
+    residual = torch.randn(64, 768, generator=g, device="cuda")
+    seeds = torch.randint(0, 2 ** 62, (2,), generator=g, device="cuda", dtype=torch.int64)
+    a = dropout_rms_norm.add_forward([x, seeds, residual, [64, 768], [64, 768]])
+    b = dropout_rms_norm.add_forward([seeds, x, residual, [64, 768], [4, 16, 768]], order=("seeds", "x", "residual"),
+                                     out_shape=[4, 16, 768])
+    assert b[1].shape == (4, 16, 768) and torch.equal(a[1].view(-1), b[1].view(-1)) and torch.equal(a[0], b[0])
+    with pytest.raises(native.KernelArgumentError):
+        kernels.dropout_add(x, residual[:32], seeds, 0, p=0.1)
+    with pytest.raises(native.KernelArgumentError):
+        kernels.dropout_add(x[:1, :4], residual[:1, :4].contiguous(), seeds, 0, p=0.1)   # not a multiple of 8

@@ -23,11 +23,12 @@ FIXTURE_DIR = {
     "transpose_021e90d9c17d": "pointwise_021e90d9c17d", "logsoftmax_d16035e7b826": "amax_sum_d16035e7b826",
     "softmax_long_7079889cfc04": "amax_sum_7079889cfc04", "spatial_mean_c9e1a8113328": "mean_c9e1a8113328",
     "bn_bwd_leaky_12fc8ebf8180": "sum_sum_12fc8ebf8180", "dropout_rms_014afd4984e6": "mean_014afd4984e6",
-    "dropout_ln_01fbd6c1b27f": "var_mean_01fbd6c1b27f",
+    "dropout_ln_01fbd6c1b27f": "var_mean_01fbd6c1b27f", "dropout_add_4b076ed1ff41": "pointwise_4b076ed1ff41",
 }
 # regions that draw random numbers: output index -> mask index it depends on element by element
 STOCHASTIC = {"dropout_rms_014afd4984e6": {"masks": (0, 3), "elementwise": {1: 0}},
-              "dropout_ln_01fbd6c1b27f": {"masks": (0,), "elementwise": {}}}
+              "dropout_ln_01fbd6c1b27f": {"masks": (0,), "elementwise": {}},
+              "dropout_add_4b076ed1ff41": {"masks": (0,), "elementwise": {1: 0}}}
 
 
 def kernel_cases():

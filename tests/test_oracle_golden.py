@@ -85,7 +85,13 @@ def golden_cases():
         mask = recorded[0] if recorded is not None else None
         return list(eager.DropoutResidualLayerNorm(0.1, 1e-5, 35)(x, seeds, residual, w, b, mask=mask))
 
+    def dropout_add(inp, recorded=None):
+        x, seeds, residual, _s0, _s1 = inp
+        mask = recorded[0] if recorded is not None else None
+        return list(eager.DropoutAdd(0.1, 1)(x, seeds, residual, mask=mask))
+
     return {
+        "dropout_add_4b076ed1ff41": dropout_add,
         "dropout_ln_01fbd6c1b27f": dropout_ln,
         "dropout_rms_014afd4984e6": dropout_rms,
         "ln_fwd_f8ec553e339e": ln_fwd, "rmsnorm_fwd_f667cd8901af": rms_fwd,
@@ -99,7 +105,7 @@ def golden_cases():
 
 
 CASE_NAMES = sorted(p.stem for p in GOLDEN.glob("*.pt"))
-STOCHASTIC = {"dropout_rms_014afd4984e6", "dropout_ln_01fbd6c1b27f"}   # cases whose region draws random numbers
+STOCHASTIC = {"dropout_rms_014afd4984e6", "dropout_ln_01fbd6c1b27f", "dropout_add_4b076ed1ff41"}   # cases whose region draws random numbers
 
 
 def _clone(inputs):
