@@ -10,17 +10,23 @@ step finds its input there. The metric is achieved HBM bandwidth: the region's m
 (every input once plus every output once) divided by the time per step. One JSON line is printed
 by rank 0.
 
-  value      K timed steps (captured into one CUDA graph, replayed once) between CUDA events on the
-             launching stream, barrier + synchronize on both sides; with N > 1 every rank runs the same configuration on its own GPU
-             (independent replicas, no collective in the data path) and the time is the maximum
-             over ranks, so value is the aggregate over the N GPUs.
-  roofline   the dominant (here: only) kernel of the step against the measured HBM peak.
+  value      K timed steps (captured into one CUDA graph) between CUDA events on the launching
+             stream, barrier + synchronize on both sides. The graph is replayed several times, each
+             replay timed by its own event pair; value is the MEDIAN replay (min and max are
+             reported beside it). Outputs of the last steps stay alive during the capture, so the
+             output blocks rotate over more than 4x the L2 as the inputs do and every step's
+             results really go to DRAM. With N > 1 every rank runs the same configuration on its
+             own GPU (independent replicas, no collective in the data path) and the time is the
+             maximum over ranks, so value is the aggregate over the N GPUs.
+  roofline   the dominant (here: only) kernel of the step against the measured HBM peak; its
+             ``per_config`` map holds all five configurations: back-to-back microseconds and
+             fraction (``us``, ``frac``) and one replay from a flushed L2 as the reference's
+             ``bench_oracle`` times it (``cold_us``, ``cold_frac``).
   e2e        the same metric through the public entry point with HOST buffers: every step copies
              the inputs from pinned host memory, runs ``oracle_forward`` and copies every output
              back to pinned host memory. Upload, kernel and download of neighbouring steps overlap
              (three streams, two buffer sets); every step's copies are inside the timed region.
   cpu_baseline  the eager module of the same region on the host cores (rank 0, N = 1).
-  per_config the other four baseline configurations, timed the same way as ``value``.
   families   one case per kernel family outside the five configurations (``family_cases.py``).
 
 ``--sweep`` runs the corpus sweep (persistent worker processes, tasks sharded over the first N
@@ -44,7 +50,7 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-FALLBACK_HBM_GBS = 6650.0  # earlier measurement on this pool, used only without MEASURED_PEAKS.json
+FALLBACK_HBM_GBS = 6650.0  # used only when MEASURED_PEAKS.json is absent
 L2_BYTES_ASSUMED = 126 * 1024 * 1024
 
 
@@ -54,16 +60,30 @@ def measured_peak():
         with open(path) as f:
             return float(json.load(f)["hbm_gbs"]), "measured (MEASURED_PEAKS.json hbm_gbs)"
     except Exception:
-        return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, earlier measurement on this pool)"
+        return FALLBACK_HBM_GBS, "fallback (6.65 TB/s, no MEASURED_PEAKS.json)"
 
 
 def recorded_traffic(workload):
-    """DRAM bytes per launch from the committed ncu capture of this workload's kernel, or None."""
+    """The committed ncu capture of this workload's kernel (one launch from a flushed L2):
+    {"traffic": read + write DRAM bytes, "traffic_read", "traffic_write", "input_bytes",
+    "output_bytes"}, or {} without a capture. A capture ends with the kernel, when part of the
+    output is still dirty in L2, so only the read side can be compared with the algorithmic bytes
+    (traffic_read against input_bytes); the write side is bounded below by what was seen."""
     try:
         with open(os.path.join(ROOT, "profiles", "dram_traffic.json")) as f:
-            return json.load(f).get(workload, {}).get("dram_bytes_per_launch")
+            rec = json.load(f).get(workload, {})
     except Exception:
-        return None
+        return {}
+    if not rec:
+        return {}
+    out = {"traffic": rec.get("dram_bytes_per_launch"), "traffic_read": rec.get("dram_read_bytes"),
+           "traffic_write": rec.get("dram_write_bytes")}
+    if rec.get("input_bytes") is not None:
+        out["input_bytes"] = rec["input_bytes"]
+        out["output_bytes"] = rec.get("output_bytes")
+        if rec.get("dram_read_bytes"):
+            out["read_over_input"] = round(rec["dram_read_bytes"] / rec["input_bytes"], 3)
+    return out
 
 
 class ClockSampler:
@@ -195,14 +215,24 @@ def build_input_sets(workload, device, min_total_bytes):
     return sets, per_set
 
 
-def time_steps(workload, input_sets, steps, warmup, barrier):
-    """(milliseconds for `steps` steps, kernels launched inside the timed region).
+REPLAYS = 21  # timed replays of the K-step graph (median reported)
 
-    The K steps are captured into one CUDA graph (step i uses input set i mod n) and the timed
+
+def time_steps(workload, input_sets, steps, warmup, barrier, replays=REPLAYS,
+               min_output_bytes=4 * L2_BYTES_ASSUMED):
+    """Times `steps` steps, `replays` times. Returns {"ms": median, "ms_min", "ms_max", "replays",
+    "launches": kernels this library launched per replay}.
+
+    The K steps are captured into one CUDA graph (step i uses input set i mod n) and a timed
     region is one replay of that graph between two events: the kernels are 20-100 us long, and a
-    Python loop cannot issue them fast enough to keep the GPU busy. The launch count is what the
-    library launched while the graph was being captured, i.e. per replay.
+    Python loop cannot issue them fast enough to keep the GPU busy. While capturing, the outputs of
+    the most recent steps are kept alive until they add up to `min_output_bytes`, so the allocator
+    hands every step a block that has not been written for at least that many bytes: a step's
+    results are evicted to DRAM like in real use instead of being overwritten in L2 by the next
+    step. The launch count is what the library launched while the graph was being captured.
     """
+    import collections
+
     import torch
     from better_benchmark_b200 import native
     lib = native.load()
@@ -210,23 +240,66 @@ def time_steps(workload, input_sets, steps, warmup, barrier):
     for i in range(warmup):
         workload.oracle_forward(input_sets[i % n])
     torch.cuda.synchronize()
+    input_ptrs = {t.data_ptr() for s in input_sets for t in s if isinstance(t, torch.Tensor)}
     graph = torch.cuda.CUDAGraph()
     launches0 = lib.b200_launch_count()
     with torch.cuda.graph(graph):
+        window, held = collections.deque(), 0
         for i in range(steps):
-            workload.oracle_forward(input_sets[i % n])
+            outs = workload.oracle_forward(input_sets[i % n])
+            outs = [outs] if isinstance(outs, torch.Tensor) else list(outs)
+            nbytes = sum(o.numel() * o.element_size() for o in outs
+                         if isinstance(o, torch.Tensor) and o.data_ptr() not in input_ptrs)
+            window.append((outs, nbytes))
+            held += nbytes
+            while len(window) > 1 and held - window[0][1] >= min_output_bytes:
+                held -= window.popleft()[1]
+            del outs
+        window.clear()
     launches = lib.b200_launch_count() - launches0
     torch.cuda.synchronize()
     graph.replay()  # untimed: instantiates everything the first replay touches
     torch.cuda.synchronize()
+    times = []
+    for _ in range(max(1, replays)):
+        barrier()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end))
     barrier()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    start.record()
-    graph.replay()
-    end.record()
-    torch.cuda.synchronize()
-    barrier()
-    return start.elapsed_time(end), int(launches)
+    check_device_waits()
+    return {"ms": statistics.median(times), "ms_min": min(times), "ms_max": max(times),
+            "replays": len(times), "launches": int(launches)}
+
+
+def check_device_waits():
+    """Raise if a bounded device-side wait ran out during what was just timed: such a kernel skips
+    its remaining work, and a region that timed skipped work must not be reported."""
+    from better_benchmark_b200 import kernels, native
+    lib = native.load()
+    kernels.check_scratch_status()
+    gave_up = {name: int(getattr(lib, name)()) for name in
+               ("b200_norm_fwd_wait_timeouts", "b200_norm_bwd_wait_timeouts", "b200_batch_norm_wait_timeouts")}
+    if any(gave_up.values()):
+        raise RuntimeError(f"device-side waits ran out during the timed region: {gave_up}")
+
+
+def time_cold(workload, inputs):
+    """Microseconds of ONE launch of the region from a flushed L2, graph launch included, as the
+    reference's bench_oracle times it (min over its repetitions; no comparison arm, no gate)."""
+    import torch
+    from better_benchmark_b200 import harness
+    with torch.no_grad():
+        for _ in range(3):
+            workload.oracle_forward(inputs)
+        torch.cuda.synchronize()
+    graph, _ = harness._capture_graph_checked(lambda: workload.oracle_forward(inputs))
+    best = min(harness._time_graph(graph, warmup=10, rep=60) for _ in range(2))
+    del graph
+    return best
 
 
 def time_e2e(workload, device, steps, warmup):
@@ -318,8 +391,9 @@ def gpu_arm(args, workload):
     if rank == 0:
         sampler.start()
         time.sleep(0.3)
-    total_ms, launches = time_steps(workload, sets, args.steps, args.warmup, barrier)
-    total_ms = group.max_over_ranks(total_ms)
+    timing = time_steps(workload, sets, args.steps, args.warmup, barrier)
+    launches = timing["launches"]
+    total_ms = group.max_over_ranks(timing["ms"])
     ms_per_step = total_ms / args.steps
     # keep the GPU under the same load a little longer so that the clock sampler sees it
     load_graph = torch.cuda.CUDAGraph()
@@ -333,6 +407,9 @@ def gpu_arm(args, workload):
         torch.cuda.synchronize()
     del load_graph
     clocks = sampler.stop() if rank == 0 else None
+    if clocks is not None:
+        clocks["window"] = (f"sampled every 100 ms from before the {timing['replays']} timed replays to the end of "
+                            "a 1 s continuation under the same load")
     gbps_one = workload.algorithmic_bytes / (ms_per_step * 1e-3) / 1e9
     value = gbps_one * world
 
@@ -340,40 +417,39 @@ def gpu_arm(args, workload):
     e2e_ms = group.max_over_ranks(e2e_ms)
     e2e_value = workload.algorithmic_bytes / (e2e_ms * 1e-3) / 1e9 * world
 
+    def entry(wl, t, k):
+        per = t["ms"] / k
+        return {"us": round(per * 1e3, 2), "frac": round(wl.algorithmic_bytes / (per * 1e-3) / 1e9 / peak, 4),
+                "us_min": round(t["ms_min"] / k * 1e3, 2), "us_max": round(t["ms_max"] / k * 1e3, 2),
+                "launches": round(t["launches"] / k, 2), "bytes": wl.algorithmic_bytes}
+
     per_config = {}
     families = {}
     cpu_baseline = None
     if rank == 0 and world == 1 and not args.only_headline:
+        per_config[workload.name] = entry(workload, timing, args.steps)
+        cold = time_cold(workload, sets[0])
+        per_config[workload.name].update(cold_us=round(cold, 2),
+                                         cold_frac=round(workload.algorithmic_bytes / (cold * 1e-6) / 1e9 / peak, 4))
         del sets
         torch.cuda.empty_cache()
         for name, wl in WORKLOADS.items():
             if name == workload.name:
                 continue
             s, _ = build_input_sets(wl, device, 4 * L2_BYTES_ASSUMED)
-            ms, n_launch = time_steps(wl, s, args.steps, args.warmup, lambda: None)
-            per = ms / args.steps
-            g = wl.algorithmic_bytes / (per * 1e-3) / 1e9
-            per_config[name] = {"us_per_step": round(per * 1e3, 2), "gbps": round(g, 1),
-                                "frac_of_peak": round(g / peak, 4), "launches_per_step": n_launch / args.steps,
-                                "algorithmic_bytes": wl.algorithmic_bytes}
+            per_config[name] = entry(wl, time_steps(wl, s, args.steps, args.warmup, lambda: None), args.steps)
+            cold = time_cold(wl, s[0])
+            per_config[name].update(cold_us=round(cold, 2),
+                                    cold_frac=round(wl.algorithmic_bytes / (cold * 1e-6) / 1e9 / peak, 4))
             del s
             torch.cuda.empty_cache()
         from better_benchmark_b200.family_cases import FAMILY_CASES
         for name, wl in FAMILY_CASES.items():
             s, _ = build_input_sets(wl, device, 4 * L2_BYTES_ASSUMED)
-            ms, n_launch = time_steps(wl, s, min(args.steps, 50), args.warmup, lambda: None)
-            per = ms / min(args.steps, 50)
-            g = wl.algorithmic_bytes / (per * 1e-3) / 1e9
-            families[name] = {"us_per_step": round(per * 1e3, 2), "gbps": round(g, 1),
-                              "frac_of_peak": round(g / peak, 4),
-                              "launches_per_step": n_launch / min(args.steps, 50),
-                              "algorithmic_bytes": wl.algorithmic_bytes, "description": wl.description}
+            k = min(args.steps, 50)
+            families[name] = entry(wl, time_steps(wl, s, k, args.warmup, lambda: None, replays=7), k)
             del s
             torch.cuda.empty_cache()
-        per_config[workload.name] = {"us_per_step": round(ms_per_step * 1e3, 2), "gbps": round(gbps_one, 1),
-                                     "frac_of_peak": round(gbps_one / peak, 4),
-                                     "launches_per_step": launches / args.steps,
-                                     "algorithmic_bytes": workload.algorithmic_bytes}
         mean_s, best_s, done, cores = time_eager_cpu(workload, 20, 2, budget_s=20)
         cpu_gbps = workload.algorithmic_bytes / mean_s / 1e9
         cpu_baseline = {"value": round(cpu_gbps, 3), "unit": "GB/s", "cores": cores, "kind": "port",
@@ -382,6 +458,13 @@ def gpu_arm(args, workload):
     group.close()
     if rank != 0:
         return 0
+    roofline = {"bound": "hbm", "achieved": round(gbps_one, 1), "peak": peak, "unit": "GB/s",
+                "frac": round(gbps_one / peak, 4), "traffic": None,
+                "peak_source": peak_source, "algorithmic_bytes_per_launch": workload.algorithmic_bytes,
+                "launches_per_step": launches / args.steps}
+    roofline.update(recorded_traffic(workload.name))
+    if per_config:
+        roofline["per_config"] = per_config
     line = {
         "metric": "achieved_hbm_gbps", "value": round(value, 1), "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(ms_per_step, 6),
@@ -390,20 +473,18 @@ def gpu_arm(args, workload):
         "config": {"workload": workload.name, "description": workload.description,
                    "replicas": world,
                    "l2": f"inputs rotate over {n_sets} resident buffer sets "
-                         f"({per_set / 1e6:.0f} MB each) totalling more than 4x the 126 MB L2"},
+                         f"({per_set / 1e6:.0f} MB each) and outputs over as many bytes, each more than 4x the 126 MB L2",
+                   "timing": f"median of {timing['replays']} replays of the {args.steps}-step graph"},
+        "ms_per_step_min": round(timing["ms_min"] / args.steps, 6),
+        "ms_per_step_max": round(timing["ms_max"] / args.steps, 6),
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": int(h2d),
                 "d2h_bytes_per_step": int(d2h), "ms_per_step": round(e2e_ms, 4)},
         "gpu_launches": launches,
-        "roofline": {"bound": "hbm", "achieved": round(gbps_one, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(gbps_one / peak, 4), "traffic": recorded_traffic(workload.name),
-                     "peak_source": peak_source, "algorithmic_bytes_per_launch": workload.algorithmic_bytes,
-                     "launches_per_step": launches / args.steps},
+        "roofline": roofline,
     }
     if cpu_baseline is not None:
         line["cpu_baseline"] = cpu_baseline
-    if per_config:
-        line["per_config"] = per_config
     if families:
         line["families"] = families
     print(json.dumps(line))

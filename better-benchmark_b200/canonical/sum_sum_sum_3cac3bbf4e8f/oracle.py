@@ -1,18 +1,19 @@
 """LayerNorm backward: dx rows and the fp32 weight gradient (broadcast-scalar incoming gradient, materialised once).
 
 B200 oracle for the reference's canonical directory ``repros/canonical/sum_sum_sum_3cac3bbf4e8f``: copy this file
-there as ``oracle.py`` (library built, this repository on PYTHONPATH). Registered for every shape
-point of the directory; the kernels behind it are hand-written sm_100a CUDA behind the C ABI.
+there as ``oracle.py`` (library built, this repository on PYTHONPATH). Registered under the shape hash of every
+point in the directory's shapes.json (and shape-general for other inputs); the kernels behind it are hand-written sm_100a CUDA behind the C ABI.
 """
 try:  # inside the reference checkout
     from oracle_harness import oracle_impl
 except ImportError:  # stand-alone: this repository's mirror of the same contract
     from better_benchmark_b200.harness import oracle_impl
 
+from better_benchmark_b200.registration import every_point
 from better_benchmark_b200 import kernels
 
 
-@oracle_impl(hardware="B200")
+@every_point(oracle_impl, hardware="B200")
 def oracle_forward(inputs):
     rstd, dy, weight, x, mean, dy_shape = inputs[:6]
     dx, dweight, _ = kernels.norm_bwd(x, dy.expand(dy_shape).contiguous(), weight, rstd.reshape(-1),

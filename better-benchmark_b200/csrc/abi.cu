@@ -34,12 +34,29 @@ const DeviceInfo& device_info() {
 }
 
 static std::atomic<long long> g_launches{0};
-void note_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+static thread_local const char* t_path_tag = nullptr;
+static thread_local char t_last_kernel[160] = {0};
+
+void set_path_tag(const char* tag) { t_path_tag = tag; }
+
+void note_launch(const char* what) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (t_path_tag)
+    snprintf(t_last_kernel, sizeof(t_last_kernel), "%s [%s]", what, t_path_tag);
+  else
+    snprintf(t_last_kernel, sizeof(t_last_kernel), "%s", what);
+  t_path_tag = nullptr;
+}
 
 }  // namespace b200
 
 // Number of kernels this library has launched in this process (cooperative launches included).
 extern "C" int64_t b200_launch_count(void) { return b200::g_launches.load(std::memory_order_relaxed); }
+
+// Name of the kernel this thread launched last, with the variant the launcher chose in brackets
+// (e.g. "b200_row_reduce [vector, warp per row]"); "" before the first launch. A diagnostic: sweep
+// reports use it to tell tuned paths from the element-wise ones.
+extern "C" const char* b200_last_kernel(void) { return b200::t_last_kernel; }
 
 extern "C" const char* b200_last_error(void) { return b200::last_error_buffer(); }
 

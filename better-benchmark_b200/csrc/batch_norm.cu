@@ -1031,7 +1031,7 @@ static bool try_launch_batch_norm_warp(BatchNormParams p, size_t scratch_bytes, 
     *rc = fail((int)e, "b200_batch_norm_fwd: cooperative launch failed: %s", cudaGetErrorString(e));
     return true;
   }
-  note_launch();
+  note_launch("b200_batch_norm_fwd [fused, channels-last, warp rings]");
   *rc = B200_OK;
   return true;
 }
@@ -1095,7 +1095,7 @@ static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, size_t 
       cudaGetLastError();
       return fail((int)e, "b200_batch_norm_fwd: cooperative launch failed: %s", cudaGetErrorString(e));
     }
-    note_launch();
+    note_launch("b200_batch_norm_fwd [fused, channels-last, CTA ring]");
     return B200_OK;
   }
   // general path
@@ -1108,14 +1108,14 @@ static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, size_t 
     return fail(B200_ERR_WORKSPACE, "b200_batch_norm_fwd: scratch of %zu bytes, need %lld", scratch_bytes, need);
   p.stats = p.partials + splits * 2 * p.channels;
   batch_norm_stats_general_kernel<T><<<dim3(p.channels, (unsigned)splits), 256, 0, st>>>(p);
-  int rc = launch_status("b200_batch_norm_fwd stats");
+  int rc = launch_status("b200_batch_norm_fwd stats [strided, element-wise]");
   if (rc != B200_OK) return rc;
   batch_norm_finalize_general_kernel<T><<<(p.channels + 7) / 8, 256, 0, st>>>(p, (int)splits);
   rc = launch_status("b200_batch_norm_fwd finalize");
   if (rc != B200_OK) return rc;
   if (p.y) {
     batch_norm_apply_general_kernel<T><<<dim3(p.channels, (unsigned)splits), 256, 0, st>>>(p);
-    rc = launch_status("b200_batch_norm_fwd apply");
+    rc = launch_status("b200_batch_norm_fwd apply [strided, element-wise]");
   }
   return rc;
 }

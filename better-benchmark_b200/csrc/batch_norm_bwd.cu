@@ -330,7 +330,7 @@ static int launch_bn_bwd(BnBwdParams p, bool fast, size_t scratch_bytes, cudaStr
     long long grid = 8LL * dev.sm_count;
     if (grid * 256 > total) grid = (total + 255) / 256;
     bn_bwd_apply_cl_kernel<T><<<(unsigned)grid, 256, 0, st>>>(p);
-    return launch_status("b200_batch_norm_bwd apply");
+    return launch_status("b200_batch_norm_bwd apply [channels-last, vector]");
   }
   const long long total = p.rows * p.spatial;
   long long splits = total / 16384;
@@ -348,7 +348,7 @@ static int launch_bn_bwd(BnBwdParams p, bool fast, size_t scratch_bytes, cudaStr
   rc = launch_status("b200_batch_norm_bwd finalize");
   if (rc != B200_OK || !p.dx) return rc;
   bn_bwd_apply_general_kernel<T><<<dim3(p.channels, (unsigned)splits), 256, 0, st>>>(p);
-  return launch_status("b200_batch_norm_bwd apply");
+  return launch_status("b200_batch_norm_bwd apply [strided, element-wise]");
 }
 
 }  // namespace b200

@@ -194,6 +194,7 @@ static int launch_col_reduce(ColReduceParams p, bool vec, size_t scratch_bytes, 
   p.rows_per_split = (p.rows + splits - 1) / splits;
   const bool is_max = p.op == B200_COL_AMAX;
   dim3 grid((unsigned)chunks, (unsigned)splits, (unsigned)p.batch);
+  set_path_tag(vec ? "vector" : "element-wise");
   if (is_max) {
     if (vec) col_reduce_kernel<T, true, true><<<grid, threads, 0, st>>>(p);
     else col_reduce_kernel<T, true, false><<<grid, threads, 0, st>>>(p);

@@ -47,7 +47,12 @@ inline int fail(int code, const char* fmt, ...) {
   return code;
 }
 
-void note_launch();  // defined in abi.cu: counts kernel launches for b200_launch_count()
+// Defined in abi.cu. note_launch counts a kernel launch for b200_launch_count() and remembers
+// its name (with the path tag, if one was set since the previous launch) for b200_last_kernel().
+// set_path_tag names the variant a launcher chose ("vector", "element-wise", "streaming", ...):
+// a pointer to a string literal, consumed by the next note_launch on this thread.
+void note_launch(const char* what);
+void set_path_tag(const char* tag);
 
 // Call after every kernel launch: counts it and reports a rejected launch.
 inline int launch_status(const char* what) {
@@ -56,7 +61,7 @@ inline int launch_status(const char* what) {
     fail((int)e, "%s: launch failed: %s", what, cudaGetErrorString(e));
     return (int)e;
   }
-  note_launch();
+  note_launch(what);
   return B200_OK;
 }
 

@@ -1070,7 +1070,7 @@ static bool try_launch_norm_bwd_stream(NormBwdParams p, int threads, size_t scra
       *rc = fail((int)e, "b200_norm_bwd: cooperative launch failed: %s", cudaGetErrorString(e));
       return true;
     }
-    note_launch();
+    note_launch("b200_norm_bwd [streaming, CTA per row, fused finalize]");
     *rc = B200_OK;
     return true;
   }
@@ -1159,7 +1159,7 @@ static bool try_launch_norm_bwd_tile(NormBwdParams p, int threads, size_t scratc
       *rc = fail((int)e, "b200_norm_bwd: cooperative launch failed: %s", cudaGetErrorString(e));
       return true;
     }
-    note_launch();
+    note_launch(groups_per_cta > 1 ? "b200_norm_bwd [row tiles, row groups, fused finalize]" : "b200_norm_bwd [row tiles, fused finalize]");
     *rc = B200_OK;
     return true;
   }
@@ -1201,7 +1201,7 @@ static int launch_norm_bwd_fast(NormBwdParams p, int threads, size_t scratch_byt
       cudaGetLastError();
       return fail((int)e, "b200_norm_bwd: cooperative launch failed: %s", cudaGetErrorString(e));
     }
-    note_launch();
+    note_launch(BLOCK ? "b200_norm_bwd [registers, CTA per row, fused finalize]" : "b200_norm_bwd [registers, warp per row, fused finalize]");
     return B200_OK;
   }
   kernel<<<(unsigned)grid, threads, 0, st>>>(p);
@@ -1262,7 +1262,7 @@ static int launch_norm_bwd(NormBwdParams p, bool vector_ok, size_t scratch_bytes
   }
   // general path: rows kernel + column kernel + finalize
   norm_bwd_rows_general_kernel<T, LN><<<(unsigned)p.rows, 256, 0, st>>>(p);
-  int rc = launch_status("b200_norm_bwd rows");
+  int rc = launch_status("b200_norm_bwd rows [element-wise]");
   if (rc != B200_OK || !(p.dw || p.db)) return rc;
   const long long plane = (long long)p.n * sizeof(float);
   long long splits = ((long long)scratch_bytes - 256) / (2 * plane);
@@ -1285,11 +1285,18 @@ using namespace b200;
 // operation). Synchronises the device.
 extern "C" int64_t b200_norm_bwd_wait_timeouts(void) { return (int64_t)read_wait_timeouts(); }
 
-// Bytes of scratch that let the fast path run its largest grid for rows of n elements.
+// Bytes of scratch that let every path run its largest grid for rows of n elements: the barrier
+// words, two planes (dweight, dbias) of one fp32 partial row per group, and the fp64 second level
+// of the fused finalize. A group is a CTA (at most eight resident per SM), except in the
+// warp-per-row register kernel that takes rows of up to 256 elements, where it is a warp (64 per
+// SM). The launchers shrink their grids to whatever scratch they are given, so a smaller buffer
+// costs speed, never correctness.
 extern "C" int64_t b200_norm_bwd_scratch_bytes(int64_t n) {
-  const int sms = device_info().sm_count;
-  // up to 8 resident 256-thread CTAs per SM, 8 warps each, two planes of fp32 partial rows
-  return 256 + 2LL * (int64_t)sms * 64 * n * (int64_t)sizeof(float);
+  const int64_t sms = device_info().sm_count;
+  const int64_t groups = (n <= 256 ? 64 : 8) * sms;
+  const int64_t planes = 2 * groups * n * (int64_t)sizeof(float);
+  const int64_t level2 = 2 * groups * 64 * (int64_t)sizeof(double);
+  return 256 + planes + 64 + level2;
 }
 
 extern "C" int b200_norm_bwd(const void* x, const void* dy, const void* weight, const float* mean,

@@ -440,7 +440,7 @@ static bool try_launch_norm_fwd_stream(const NormFwdParams& p, cudaStream_t st, 
       return;
     }
     kernel<<<(unsigned)grid, threads, smem, st>>>(p, stages, contiguous);
-    *rc = launch_status("b200_norm_fwd (streaming)");
+    *rc = launch_status("b200_norm_fwd [streaming ring, sub-warp rows]");
   };
 #define B200_NFS(GG, CC)                                                            if (g == GG && ch == CC) {                                                          if (exact) launch(norm_fwd_stream_kernel<Tin, Tout, CC, GG, true>);               else launch(norm_fwd_stream_kernel<Tin, Tout, CC, GG, false>);                    return true;                                                                    }
   B200_NFS(8, 1) B200_NFS(8, 2) B200_NFS(8, 3) B200_NFS(8, 4) B200_NFS(16, 3) B200_NFS(16, 4) B200_NFS(32, 3) B200_NFS(32, 4)
@@ -504,6 +504,7 @@ static int launch_norm_fwd(const NormFwdParams& p, bool vector_ok, cudaStream_t 
     if (try_launch_norm_fwd_stream<Tin, Tout>(p, st, &rc)) return rc;
   }
   if (vector_ok && p.n % V == 0 && pick_row_geometry(p.n / V, &g)) {
+    set_path_tag(g.block ? "vector, row resident, CTA per row" : "vector, row resident, sub-warp rows");
 #define B200_NF_LAUNCH(GG, CC) norm_fwd_resident_kernel<Tin, Tout, CC, GG><<<grid, g.threads, 0, st>>>(p)
     if (!g.block) {
       const int rows_per_cta = g.threads / g.g;
@@ -527,6 +528,7 @@ static int launch_norm_fwd(const NormFwdParams& p, bool vector_ok, cudaStream_t 
   } else {
     int threads = 1024;
     while (threads > 64 && threads / 2 >= p.n) threads /= 2;
+    set_path_tag("element-wise, CTA per row");
     norm_fwd_streaming_kernel<Tin, Tout><<<(unsigned)p.rows, threads, 0, st>>>(p);
   }
   return launch_status("b200_norm_fwd");

@@ -212,6 +212,7 @@ static unsigned streaming_grid(long long units) {
 template <typename Tin, typename Tout>
 static int launch_permute(const PermuteParams& p, bool vec, cudaStream_t st) {
   const long long units = vec ? p.total / Elem<Tin>::V : p.total;
+  set_path_tag(vec ? "vector gather" : "element-wise gather");
   if (vec) permute_general_kernel<Tin, Tout, true><<<streaming_grid(units), 256, 0, st>>>(p);
   else permute_general_kernel<Tin, Tout, false><<<streaming_grid(units), 256, 0, st>>>(p);
   return launch_status("b200_permute_copy");
@@ -225,16 +226,17 @@ static int launch_transpose(const TransposeParams& p, cudaStream_t st) {
                        p.in_batch_stride % 8 == 0 && aligned16(p.x) && aligned16(p.y);
     if (whole) {
       transpose16_tile_kernel<<<grid, 256, 0, st>>>(p);
-      return launch_status("b200_transpose_copy");
+      return launch_status("b200_transpose_copy [16-byte tiles]");
     }
   }
   transpose_tile_kernel<Tin, Tout><<<grid, 256, 0, st>>>(p);
-  return launch_status("b200_transpose_copy");
+  return launch_status("b200_transpose_copy [element tiles]");
 }
 
 template <typename Tin, typename Tout>
 static int launch_cast(const void* x, void* y, long long n, float scale, int has_scale, bool vec, cudaStream_t st) {
   const long long units = vec ? n / Elem<Tin>::V : n;
+  set_path_tag(vec ? "vector" : "element-wise");
   if (vec) cast_scale_kernel<Tin, Tout, true><<<streaming_grid(units > 0 ? units : 1), 256, 0, st>>>(x, y, n, scale, has_scale);
   else cast_scale_kernel<Tin, Tout, false><<<streaming_grid(units > 0 ? units : 1), 256, 0, st>>>(x, y, n, scale, has_scale);
   return launch_status("b200_cast_scale");

@@ -165,6 +165,8 @@ static int launch_row_reduce(const RowReduceParams& p, bool vec, cudaStream_t st
   const double eff_warp = efficiency((double)((p.rows + 7) / 8), 8.0);
   const double eff_block = efficiency((double)p.rows, (double)(2048 / threads > 32 ? 32 : 2048 / threads));
   const bool warp_mode = p.rows >= (long long)sms * 16 && p.n <= 16384 && eff_warp + 0.02 >= eff_block;
+  set_path_tag(vec ? (warp_mode ? "vector, warp per row" : "vector, CTA per row")
+                   : (warp_mode ? "element-wise, warp per row" : "element-wise, CTA per row"));
   if (warp_mode) {
     const long long grid = (p.rows + 7) / 8;
     if (grid > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "row_reduce: too many rows");

@@ -184,14 +184,32 @@ __device__ __forceinline__ float hsum2(f32x2 v) {
   return a + b;
 }
 
-// Natural exponential of a pair as 2^(x * log2 e) with the hardware approximation, for results that
-// are rounded to a 16-bit type afterwards (this is also what Triton's tl.exp lowers to). Relative
-// error <= 2^-22 + |x * log2 e| * 2^-24 * ln 2: below 1.3e-6 wherever an fp16 result is not zero
-// (x > -17) and below 6e-6 over the whole bf16 range, i.e. at least 80 times finer than half an
-// ulp of the output type. The two halves go through the special-function unit inside one asm
-// block so that they are read from and written to an aligned register pair directly.
+// Natural exponential of a pair for results that are rounded to a 16-bit type afterwards.
+//
+// exp_pair_compensated (the default): y = x * log2(e) is rounded to fp32 (yh); what that rounding
+// and the rounding of the constant lost is recovered exactly as r = x - yh * ln 2 with one fused
+// multiply-add (the product is exact inside the fma; r is the error of the exponent in natural
+// units, |r| < 2^-20), 2^yh comes from the hardware approximation (relative error 2^-22) and the
+// result is 2^yh * (1 + r). Relative error below 3.5e-7 for arguments down to -17 (below 6e-7 over
+// the whole range): the accuracy class of expf (2 ulp), three orders of magnitude below half a
+// bf16/fp16 ulp. The argument must be finite (inf - inf inside the fma would give NaN where
+// exp(-inf) is 0): callers clamp to a finite floor first; NaN stays NaN.
 // .ftz: results below 2^-126 become 0 instead of denormals; nothing a 16-bit output or the row sum
 // can see.
+__device__ __forceinline__ f32x2 exp_pair_compensated(f32x2 x) {
+  const f32x2 yh = mul2(x, splat2(1.4426950216293335f));   // x * fl(log2 e), rounded
+  const f32x2 r = fma2(yh, splat2(-0.6931471824645996f), x);  // x - yh * ln 2
+  f32x2 p;
+  asm("{\n\t.reg .f32 a, b, pa, pb;\n\tmov.b64 {a,b}, %1;\n\tex2.approx.ftz.f32 pa, a;\n\t"
+      "ex2.approx.ftz.f32 pb, b;\n\tmov.b64 %0, {pa,pb};\n\t}"
+      : "=l"(p) : "l"(yh));
+  return fma2(p, r, p);
+}
+
+// exp_pair_fast (opt-in, -DB200_SOFTMAX_FAST_EXP): 2^(x * log2 e) with the hardware approximation
+// alone, which is what Triton's tl.exp lowers to. Relative error <= 2^-22 + |x * log2 e| * 2^-24 * ln 2:
+// below 1.3e-6 wherever an fp16 result is not zero (x > -17) and below 6e-6 over the whole bf16
+// range. Not the natural-exponential accuracy the eager graphs have; kept for measurements.
 __device__ __forceinline__ f32x2 exp_pair_fast(f32x2 x) {
   const f32x2 y = mul2(x, splat2(1.4426950216293335f));
   f32x2 r;
@@ -199,32 +217,6 @@ __device__ __forceinline__ f32x2 exp_pair_fast(f32x2 x) {
       "ex2.approx.ftz.f32 pb, b;\n\tmov.b64 %0, {pa,pb};\n\t}"
       : "=l"(r) : "l"(y));
   return r;
-}
-
-// The same with the rounding of x*log2(e) compensated (build with -DB200_SOFTMAX_COMPENSATED_EXP to
-// use it for 16-bit softmax outputs): y = x*log2(e) is split into its rounded value yh and the exact rounding residual plus the
-// low part of the constant (el); 2^yh comes from the hardware approximation (relative error
-// 2^-22) and is corrected by the factor (1 + el*ln 2). Relative error below 3e-7 over the whole
-// fp32 range, i.e. the accuracy class of expf, and three orders of magnitude below half a
-// bf16/fp16 ulp.
-__device__ __forceinline__ f32x2 exp2_pair_compensated(f32x2 x) {
-  const f32x2 neg_l2e = splat2(-1.4426950216293335f);      // -fl(log2 e)
-  const f32x2 l2e = splat2(1.4426950216293335f);
-  const f32x2 l2e_lo = splat2(1.9259629911266175e-8f);     // log2 e - fl(log2 e)
-  const f32x2 ln2 = splat2(0.6931471824645996f);
-  const f32x2 nyh = mul2(x, neg_l2e);                      // -(x*L2E), rounded
-  f32x2 el = fma2(x, l2e, nyh);                            // exact residual of that product
-  el = fma2(x, l2e_lo, el);
-  float a, b;
-  unpack2(nyh, a, b);
-  float pa, pb;
-  // .ftz: results below 2^-126 become 0 instead of denormals; they are 38 orders of magnitude
-  // below anything a 16-bit output (or the row sum) can see, and the plain form costs two extra
-  // multiplies, a compare and a select per element for the denormal range.
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pa) : "f"(-a));
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(pb) : "f"(-b));
-  const f32x2 p = pack2(pa, pb);
-  return fma2(p, mul2(el, ln2), p);
 }
 
 template <bool BLOCK>

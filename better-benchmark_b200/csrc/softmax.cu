@@ -19,9 +19,11 @@
 //            once, where aten rounds the fp32 sum; the two differ only when the fp32 sum lands
 //            exactly on a 16-bit rounding tie, by one 16-bit ulp of a logit.
 // fp32 outputs: expf / logf and the IEEE division. 16-bit outputs: the natural exponential is
-// evaluated pairwise with a compensated base-2 split (same accuracy class as expf, see
-// exp2_pair_compensated) and e / s as e * (1 / s) with a correctly rounded reciprocal; both
-// deviations are three orders of magnitude below half a 16-bit ulp.
+// evaluated pairwise as a hardware 2^y with the rounding of y compensated (the accuracy class of
+// expf, see exp_pair_compensated in rowwise.cuh) and e / s as e * (1 / s) with a correctly rounded
+// reciprocal; both deviations are three orders of magnitude below half a 16-bit ulp. Building with
+// -DB200_SOFTMAX_FAST_EXP drops the compensation (the bare ex2.approx that Triton's tl.exp emits);
+// that build is for measurements only.
 #include "rowwise.cuh"
 
 #include <type_traits>
@@ -80,7 +82,8 @@ struct Pair<float> {  // never instantiated for arithmetic; keeps the packed bra
 };
 
 // Final phases shared by both prologues. v holds this thread's fp32 logits as packed pairs.
-// FASTEXP (16-bit outputs) uses the compensated pair exponential; fp32 outputs use expf.
+// FASTEXP (16-bit outputs) uses the compensated pair exponential (exp_pair_compensated, the
+// accuracy class of expf); fp32 outputs use expf itself.
 template <typename Tout, int CH, int V, int G, bool FASTEXP, bool EXACT = false>
 __device__ __forceinline__ void softmax_finish(f32x2 (&v)[CH][V / 2], float mx, float mx_raw, Tout* y, int nv,
                                                int lane, int gs, bool log_mode, bool valid, float* red) {
@@ -88,10 +91,10 @@ __device__ __forceinline__ void softmax_finish(f32x2 (&v)[CH][V / 2], float mx, 
   f32x2 s2 = splat2(0.f);
   auto exp_pair = [](f32x2 d) {
     if constexpr (FASTEXP) {
-#ifdef B200_SOFTMAX_COMPENSATED_EXP
-      return exp2_pair_compensated(d);
-#else
+#ifdef B200_SOFTMAX_FAST_EXP
       return exp_pair_fast(d);
+#else
+      return exp_pair_compensated(d);
 #endif
     } else {
       float a, b;
@@ -106,7 +109,7 @@ __device__ __forceinline__ void softmax_finish(f32x2 (&v)[CH][V / 2], float mx, 
 #pragma unroll
         for (int i = 0; i < V / 2; ++i) {
           v[c][i] = sub2(v[c][i], mx2);
-#ifdef B200_SOFTMAX_COMPENSATED_EXP
+#ifndef B200_SOFTMAX_FAST_EXP
           if constexpr (FASTEXP) {
             float a, b;
             unpack2(v[c][i], a, b);
@@ -198,17 +201,17 @@ softmax_resident_kernel(const SoftmaxParams p) {
   f32x2 v[CH][V / 2];
   float mx = -INFINITY;
 
-  // The compensated pair exponential (optional build) needs finite arguments (inf - inf inside its compensation step would
+  // The compensated pair exponential needs finite arguments (inf - inf inside its compensation step would
   // give NaN where exp(-inf) is 0): logits are clamped to a finite floor AFTER the row maximum was
   // taken from the unclamped values. A row whose maximum is -inf (fully masked with -inf) makes
   // aten return NaN for the whole row; the same happens here through the sum (see below).
   constexpr float kFloor = sizeof(Tin) == 2 && !std::is_same<Tin, __nv_bfloat16>::value ? -60000.f : -1e38f;
   // log_softmax returns x - max - log(sum) itself, which may legitimately be -inf: there only the
   // exponential's argument is clamped (in softmax_finish), not the stored value.
-#ifdef B200_SOFTMAX_COMPENSATED_EXP
-  const bool clamp_now = FASTEXP && !p.log_mode;
-#else
+#ifdef B200_SOFTMAX_FAST_EXP
   const bool clamp_now = false;  // 2^(-inf) is 0 in the plain exponential: nothing to protect
+#else
+  const bool clamp_now = FASTEXP && !p.log_mode;
 #endif
   if constexpr (PACKED && sizeof(Tin) == 2) {
     using P2 = typename Pair<Tin>::type;
@@ -373,6 +376,7 @@ static int launch_softmax(const SoftmaxParams& p, bool vector_ok, cudaStream_t s
   RowGeometry g;
   if (p.rows > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "softmax: too many rows");
   if (vector_ok && p.n % V == 0 && pick_row_geometry(p.n / V, &g)) {
+    set_path_tag(g.block ? "vector, row resident, CTA per row" : "vector, row resident, sub-warp rows");
     if (!g.block) {
       const int rows_per_cta = g.threads / g.g;
       const unsigned grid = (unsigned)((p.rows + rows_per_cta - 1) / rows_per_cta);
@@ -402,6 +406,7 @@ static int launch_softmax(const SoftmaxParams& p, bool vector_ok, cudaStream_t s
   } else {
     int threads = 1024;
     while (threads > 64 && threads / 2 >= p.n) threads /= 2;
+    set_path_tag("element-wise, three passes");
     softmax_streaming_kernel<Tin, Tout, PACKED><<<(unsigned)p.rows, threads, 0, st>>>(p);
   }
   return launch_status("b200_softmax");

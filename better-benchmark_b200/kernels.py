@@ -45,6 +45,12 @@ def _require_cuda(*tensors: torch.Tensor) -> torch.device:
             dev = t.device
         elif t.device != dev:
             raise native.KernelArgumentError("all tensors must be on one device")
+    if dev is not None and dev.index is not None and dev.index != torch.cuda.current_device():
+        # the library launches on the current device's current stream and reads that device's
+        # properties: pointers of another GPU would fault there, or silently cross NVLink
+        raise native.KernelArgumentError(
+            f"tensors live on cuda:{dev.index} but the current device is cuda:{torch.cuda.current_device()}; "
+            "make their device current first (torch.cuda.set_device or `with torch.cuda.device(...)`)")
     return dev
 
 
@@ -243,35 +249,44 @@ def norm_fwd(x: torch.Tensor, weight: torch.Tensor | None, bias: torch.Tensor | 
 
 # ---------------------------------------------------------------------------------------------
 # Scratch memory. Kernels that combine per-CTA partial results take a caller-provided scratch
-# buffer. One zero-initialised buffer per device is kept here and grown on demand; the first 256
-# bytes hold the grid-barrier words, which every kernel leaves at zero when it finishes. Kernels
-# on one stream run in order, so sharing the buffer is safe there; callers that launch on several
-# streams at once must pass their own ``scratch``.
+# buffer. One zero-initialised buffer per device is kept here; the first 256 bytes hold the
+# grid-barrier words, which every kernel leaves at zero when it finishes. Kernels on one stream run
+# in order, so sharing the buffer is safe there; callers that launch on several streams at once must
+# pass their own ``scratch``. A request for more bytes than the buffer holds allocates a larger one,
+# but the smaller ones are never released: a CUDA graph captured earlier still holds their address.
+# Growing while the current stream is being captured is refused (the new buffer would belong to
+# that graph's private pool while later, uncaptured calls keep using it).
 # ---------------------------------------------------------------------------------------------
-_scratch_by_device: dict = {}
+_scratch_by_device: dict = {}   # (type, index) -> [buffers, newest and largest last]
+SCRATCH_DEFAULT_BYTES = 64 << 20  # covers every kernel of the library for rows of up to 4096 elements
+
+
+def _device_key(device: torch.device):
+    return device.type, device.index if device.index is not None else torch.cuda.current_device()
 
 
 def scratch_buffer(device: torch.device, nbytes: int) -> torch.Tensor:
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
-    buf = _scratch_by_device.get(key)
-    if buf is None or buf.numel() < nbytes:
-        buf = torch.zeros(max(int(nbytes), 1 << 20), dtype=torch.uint8, device=device)
-        _scratch_by_device[key] = buf
+    bufs = _scratch_by_device.setdefault(_device_key(device), [])
+    if bufs and bufs[-1].numel() >= nbytes:
+        return bufs[-1]
+    if torch.cuda.is_current_stream_capturing():
+        raise RuntimeError(
+            f"the shared scratch buffer would have to grow to {int(nbytes)} bytes during CUDA graph capture; "
+            "run the call once before capturing, or pass scratch= explicitly")
+    buf = torch.zeros(max(int(nbytes), SCRATCH_DEFAULT_BYTES), dtype=torch.uint8, device=device)
+    bufs.append(buf)  # superseded buffers stay alive: captured graphs may still point at them
     return buf
 
 
 def check_scratch_status(device: torch.device | None = None) -> None:
     """Raise if a cooperative kernel on this device gave up a grid-wide wait (synchronises)."""
     device = device or torch.device("cuda", torch.cuda.current_device())
-    key = (device.type, device.index if device.index is not None else torch.cuda.current_device())
-    buf = _scratch_by_device.get(key)
-    if buf is None:
-        return
     lib = load()
-    status = lib.b200_check_status(_ptr(buf), _stream())
-    if status != 0:
-        buf[:16].zero_()
-        check(status, "b200_check_status")
+    for buf in _scratch_by_device.get(_device_key(device), []):
+        status = lib.b200_check_status(_ptr(buf), _stream())
+        if status != 0:
+            buf[:16].zero_()
+            check(status, "b200_check_status")
 
 
 NORM_BWD_TWO_LAUNCH = 1  # flag: main kernel + finalize kernel instead of one cooperative launch

@@ -44,6 +44,7 @@ SIGNATURES = {
     "b200_sm_count": (c_int32, []),
     "b200_l2_bytes": (c_int32, []),
     "b200_launch_count": (c_int64, []),
+    "b200_last_kernel": (c_char_p, []),
     "b200_check_status": (c_int32, [c_void_p, c_void_p]),
     "b200_row_reduce": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, _P64,
                                   c_int64, c_int32, c_int32, c_int32, c_void_p]),

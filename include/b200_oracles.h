@@ -60,6 +60,12 @@ int32_t b200_l2_bytes(void);
  * benchmark reports the count of launches inside its timed region. */
 int64_t b200_launch_count(void);
 
+/* Name of the kernel the calling thread launched last, with the variant its launcher chose in
+ * brackets ("b200_row_reduce [vector, warp per row]"); "" before the first launch. No counterpart
+ * in the reference (its oracle files name their Triton kernels in source); sweep reports use it to
+ * tell the tuned paths from the element-wise ones. */
+const char* b200_last_kernel(void);
+
 /* Reads the status words of a scratch buffer; returns B200_ERR_DEVICE_WAIT if a grid-wide wait
  * inside a cooperative kernel ran out. Synchronises `stream`: diagnostic use only. No
  * counterpart in the reference (its kernels never wait on one another). */
