@@ -13,6 +13,10 @@ from better_benchmark_b200.registration import every_point
 from better_benchmark_b200.families import batch_norm_bwd
 
 
-@every_point(oracle_impl, hardware="B200")
-def oracle_forward(inputs):
-    return batch_norm_bwd.leaky_relu_forward(inputs, slope=0.2)
+# 1 / (32 * 16 * 16): a literal of the captured graph (repro.py:38, :42), applied at every shape point
+INV_COUNT = 0.0001220703125
+
+
+@every_point(oracle_impl, hardware="B200", inv_count=INV_COUNT)
+def oracle_forward(inputs, *, inv_count):
+    return batch_norm_bwd.leaky_relu_forward(inputs, slope=0.2, inv_count=inv_count)

@@ -13,6 +13,11 @@ from better_benchmark_b200.registration import every_point
 from better_benchmark_b200.families import batch_norm_bwd
 
 
-@every_point(oracle_impl, hardware="B200")
-def oracle_forward(inputs):
-    return batch_norm_bwd.oracle_forward(inputs)
+# 1 / (512 * 56 * 56): a literal of the captured graph (repro.py:33, :37), applied at every shape
+# point, as in the reference's oracle (oracle.py:10)
+INV_COUNT = 6.228077168367346e-07
+
+
+@every_point(oracle_impl, hardware="B200", inv_count=INV_COUNT)
+def oracle_forward(inputs, *, inv_count):
+    return batch_norm_bwd.oracle_forward(inputs, inv_count=inv_count)

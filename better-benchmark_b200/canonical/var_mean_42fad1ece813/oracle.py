@@ -13,9 +13,14 @@ from better_benchmark_b200.registration import every_point
 from better_benchmark_b200 import kernels
 
 
+# 8192 / 8191: the unbiased-variance factor is a literal of the captured graph (repro.py:40), applied
+# at every shape point
+UNBIASED_FACTOR = 1.0001220852154804
+
+
 @every_point(oracle_impl, hardware="B200")
 def oracle_forward(inputs):
     x, running_mean, running_var, weight, bias = inputs[:5]
     y, mean, invstd = kernels.batch_norm_fwd(x, weight, bias, running_mean, running_var, eps=1e-3, momentum=0.1,
-                                             relu=True)
+                                             relu=True, unbiased_factor=UNBIASED_FACTOR)
     return (invstd, y, mean.view(1, -1, 1, 1), running_mean, running_var)

@@ -1133,12 +1133,17 @@ extern "C" int64_t b200_batch_norm_scratch_bytes(int64_t channels) {
   return 256 + ((int64_t)(sms > 64 ? sms : 64) * 2 * channels + 2 * channels) * (int64_t)sizeof(float);
 }
 
-extern "C" int b200_batch_norm_fwd(const void* x, void* y, const void* weight, const void* bias,
-                                   float* running_mean, float* running_var, float* save_mean,
-                                   float* save_invstd, int64_t batch, int64_t channels, int64_t spatial,
-                                   int64_t stride_n, int64_t stride_c, int64_t stride_s,
-                                   int32_t x_dtype, int32_t w_dtype, double eps, double momentum,
-                                   int32_t relu, void* scratch, int64_t scratch_bytes, void* stream) {
+// b200_batch_norm_fwd with the factor that turns the biased batch variance into the value blended
+// into running_var given by the caller (unbiased_factor > 0) instead of n / (n - 1). A captured
+// graph carries that factor as a literal of the shape it was captured at and applies it at every
+// other shape point too; an oracle for such a graph has to do the same.
+extern "C" int b200_batch_norm_fwd_ex(const void* x, void* y, const void* weight, const void* bias,
+                                      float* running_mean, float* running_var, float* save_mean,
+                                      float* save_invstd, int64_t batch, int64_t channels, int64_t spatial,
+                                      int64_t stride_n, int64_t stride_c, int64_t stride_s,
+                                      int32_t x_dtype, int32_t w_dtype, double eps, double momentum,
+                                      double unbiased_factor, int32_t relu, void* scratch,
+                                      int64_t scratch_bytes, void* stream) {
   if (!x || !y || !scratch) return fail(B200_ERR_INVALID, "b200_batch_norm_fwd: null argument");
   if (batch <= 0 || channels <= 0 || spatial <= 0 || channels > 0x7fffffffLL)
     return fail(B200_ERR_INVALID, "b200_batch_norm_fwd: bad sizes N=%lld C=%lld HW=%lld", (long long)batch,
@@ -1157,7 +1162,7 @@ extern "C" int b200_batch_norm_fwd(const void* x, void* y, const void* weight, c
   p.eps = (float)eps; p.momentum = (float)momentum; p.one_minus_momentum = (float)(1.0 - momentum);
   const double count = (double)batch * (double)spatial;
   p.count = count;
-  p.unbias = (float)(count / (count - 1.0));
+  p.unbias = unbiased_factor > 0.0 ? (float)unbiased_factor : (float)(count / (count - 1.0));
   p.relu = relu ? 1 : 0;
   p.bar = reinterpret_cast<unsigned int*>(scratch);
   p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + 256);
@@ -1181,6 +1186,17 @@ extern "C" int b200_batch_norm_fwd(const void* x, void* y, const void* weight, c
     case B200_F16: return launch_batch_norm<__half>(p, fast, (size_t)scratch_bytes, st);
   }
   return fail(B200_ERR_INVALID, "b200_batch_norm_fwd: unknown dtype %d", x_dtype);
+}
+
+extern "C" int b200_batch_norm_fwd(const void* x, void* y, const void* weight, const void* bias,
+                                   float* running_mean, float* running_var, float* save_mean,
+                                   float* save_invstd, int64_t batch, int64_t channels, int64_t spatial,
+                                   int64_t stride_n, int64_t stride_c, int64_t stride_s,
+                                   int32_t x_dtype, int32_t w_dtype, double eps, double momentum,
+                                   int32_t relu, void* scratch, int64_t scratch_bytes, void* stream) {
+  return b200_batch_norm_fwd_ex(x, y, weight, bias, running_mean, running_var, save_mean, save_invstd, batch,
+                                channels, spatial, stride_n, stride_c, stride_s, x_dtype, w_dtype, eps, momentum,
+                                0.0, relu, scratch, scratch_bytes, stream);
 }
 
 // ----------------------------------------------------------------------------------------------

@@ -13,7 +13,9 @@
 //   dx = cast(((float(dy') - (float(x) - mean) * c2) - c1) * gs)
 //
 // Three launches: sums (a thread's own short chain in fp32, everything above it in fp64; per-CTA
-// partials over a fixed split of the rows), finalize (fixed order, coefficient table), apply. No atomics: bit-reproducible.
+// partials over a fixed split of the rows), finalize (fixed order, coefficient table), apply (each
+// CTA walks its part of the rows backwards, so that it starts in what the sums pass left in L2).
+// No atomics: bit-reproducible.
 // Channels-last tensors with a power-of-two number of 16-byte vectors per row take the vector
 // kernels; every other layout the strided element-wise ones.
 #include "rowwise.cuh"
@@ -184,13 +186,21 @@ __global__ void __launch_bounds__(256) bn_bwd_finalize_kernel(const BnBwdParams 
   }
 }
 
+// Apply pass. CTA b takes the same vectors [b*per, (b+1)*per) as in the sums pass but walks them
+// from the end to the start: what the sums pass read last is what is still in L2, so the first
+// part of this pass is served from there instead of DRAM (the two inputs together are larger than
+// the L2, so walking forward again would find nothing). blockDim.x and `per` are multiples of vpr,
+// so a thread stays in one vector column here too.
 template <typename T>
-__global__ void __launch_bounds__(256) bn_bwd_apply_cl_kernel(const BnBwdParams p) {
+__global__ void __launch_bounds__(256) bn_bwd_apply_cl_kernel(const BnBwdParams p, long long vecs_per_cta) {
   constexpr int V = Elem<T>::V;
   const int tid = threadIdx.x, T_ = blockDim.x;
   const int vpr = p.channels / V;
-  const int vc = tid % vpr;
+  const int vc = vpr - 1 - tid % vpr;  // the chunk ends on a row boundary: its last vector is column vpr - 1
   const long long total = p.rows * vpr;
+  const long long v0 = (long long)blockIdx.x * vecs_per_cta;
+  long long v1 = v0 + vecs_per_cta;
+  if (v1 > total) v1 = total;
   const uint4* dy = reinterpret_cast<const uint4*>(p.dy);
   const uint4* x = reinterpret_cast<const uint4*>(p.x);
   const uint4* act = reinterpret_cast<const uint4*>(p.act);
@@ -205,13 +215,12 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_cl_kernel(const BnBwdParams 
     mean2[i] = pack2(p.coef[3 * p.channels + c], p.coef[3 * p.channels + c + 1]);
   }
   constexpr int U = 4;
-  const long long stride = (long long)gridDim.x * T_;  // a multiple of vpr: the column is fixed
-  for (long long v = (long long)blockIdx.x * T_ + tid; v < total; v += U * stride) {
+  for (long long v = v1 - 1 - tid; v >= v0; v -= (long long)U * T_) {
     uint4 rg[U], rx[U], ra[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const long long i = v + u * stride;
-      if (i < total) {
+      const long long i = v - (long long)u * T_;
+      if (i >= v0) {
         rg[u] = ld_stream(reinterpret_cast<const T*>(dy + i));
         rx[u] = ld_stream(reinterpret_cast<const T*>(x + i));
         if (act) ra[u] = ld_stream(reinterpret_cast<const T*>(act + i));
@@ -219,8 +228,8 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_cl_kernel(const BnBwdParams 
     }
 #pragma unroll
     for (int u = 0; u < U; ++u) {
-      const long long i = v + u * stride;
-      if (i < total) {
+      const long long i = v - (long long)u * T_;
+      if (i >= v0) {
         f32x2 g[V / 2], xv[V / 2], o[V / 2];
         Pairs<T>::unpack(rg[u], g);
         Pairs<T>::unpack(rx[u], xv);
@@ -327,9 +336,7 @@ static int launch_bn_bwd(BnBwdParams p, bool fast, size_t scratch_bytes, cudaStr
     bn_bwd_finalize_kernel<<<p.channels, 256, 0, st>>>(p);
     rc = launch_status("b200_batch_norm_bwd finalize");
     if (rc != B200_OK || !p.dx) return rc;
-    long long grid = 8LL * dev.sm_count;
-    if (grid * 256 > total) grid = (total + 255) / 256;
-    bn_bwd_apply_cl_kernel<T><<<(unsigned)grid, 256, 0, st>>>(p);
+    bn_bwd_apply_cl_kernel<T><<<(unsigned)splits, 256, 0, st>>>(p, per);
     return launch_status("b200_batch_norm_bwd apply [channels-last, vector]");
   }
   const long long total = p.rows * p.spatial;
@@ -361,12 +368,15 @@ extern "C" int64_t b200_batch_norm_bwd_scratch_bytes(int64_t channels) {
          4 * channels * (int64_t)sizeof(float);
 }
 
-extern "C" int b200_batch_norm_bwd(const void* dy, const void* x, const void* act, const float* mean,
-                                   const float* invstd, const void* weight, void* dx, float* dweight,
-                                   float* dbias, int64_t batch, int64_t channels, int64_t spatial,
-                                   int64_t stride_n, int64_t stride_c, int64_t stride_s, int32_t x_dtype,
-                                   int32_t w_dtype, double slope, void* scratch, int64_t scratch_bytes,
-                                   void* stream) {
+// b200_batch_norm_bwd with the reciprocal element count given by the caller (inv_count > 0) instead
+// of 1 / (batch * spatial). A captured graph carries 1/N as a literal of the shape it was captured
+// at and applies it at every other shape point too; an oracle for such a graph has to do the same.
+extern "C" int b200_batch_norm_bwd_ex(const void* dy, const void* x, const void* act, const float* mean,
+                                      const float* invstd, const void* weight, void* dx, float* dweight,
+                                      float* dbias, int64_t batch, int64_t channels, int64_t spatial,
+                                      int64_t stride_n, int64_t stride_c, int64_t stride_s, int32_t x_dtype,
+                                      int32_t w_dtype, double slope, double inv_count, void* scratch,
+                                      int64_t scratch_bytes, void* stream) {
   if (!dy || !x || !mean || !invstd) return fail(B200_ERR_INVALID, "b200_batch_norm_bwd: null argument");
   if (batch < 0 || channels <= 0 || spatial < 0 || channels > 0x7fffffffLL)
     return fail(B200_ERR_INVALID, "b200_batch_norm_bwd: bad sizes");
@@ -384,7 +394,7 @@ extern "C" int b200_batch_norm_bwd(const void* dy, const void* x, const void* ac
   p.dx = dx; p.dweight = dweight; p.dbias = dbias;
   p.spatial = spatial; p.sn = stride_n; p.sc = stride_c; p.ss = stride_s;
   p.channels = (int)channels; p.slope = (float)slope;
-  p.inv_count = (float)(1.0 / (double)count);
+  p.inv_count = inv_count > 0.0 ? (float)inv_count : (float)(1.0 / (double)count);
   p.partials = reinterpret_cast<double*>(scratch);
   p.coef = nullptr; p.splits = 0;
   const int eb = dtype_size(x_dtype);
@@ -400,4 +410,15 @@ extern "C" int b200_batch_norm_bwd(const void* dy, const void* x, const void* ac
     case B200_F16: return launch_bn_bwd<__half>(p, fast, (size_t)scratch_bytes, st);
   }
   return fail(B200_ERR_INVALID, "b200_batch_norm_bwd: unknown dtype %d", x_dtype);
+}
+
+extern "C" int b200_batch_norm_bwd(const void* dy, const void* x, const void* act, const float* mean,
+                                   const float* invstd, const void* weight, void* dx, float* dweight,
+                                   float* dbias, int64_t batch, int64_t channels, int64_t spatial,
+                                   int64_t stride_n, int64_t stride_c, int64_t stride_s, int32_t x_dtype,
+                                   int32_t w_dtype, double slope, void* scratch, int64_t scratch_bytes,
+                                   void* stream) {
+  return b200_batch_norm_bwd_ex(dy, x, act, mean, invstd, weight, dx, dweight, dbias, batch, channels, spatial,
+                                stride_n, stride_c, stride_s, x_dtype, w_dtype, slope, 0.0, scratch, scratch_bytes,
+                                stream);
 }

@@ -6,10 +6,16 @@
 // of mean_c9e1a8113328/oracle.py:11-76 ([N, H*W, C] -> [N, C]).
 //
 // A thread owns one 16-byte vector column; the CTA's thread rows and, for tall inputs, several
-// CTAs split the rows. Partial results of different CTAs go to scratch as fp32 and are combined in
-// fp64 in a fixed order by a second launch: no float atomics, bit-reproducible (the reference's
-// atomic variant is not, and its harness would classify such an output as stochastic).
+// CTAs split the rows. With 2, 4 or 8 splits the CTAs of one reduction form a thread-block cluster:
+// each leaves its folded partial result in its own shared memory and the first CTA of the cluster
+// reads the others' through distributed shared memory, adds them in fp64 in a fixed order and
+// writes the output - one launch, no scratch traffic. With more splits the partial results go to
+// scratch as fp32 and a second launch combines them the same way. No float atomics either way:
+// bit-reproducible (the reference's atomic variant is not, and its harness would classify such an
+// output as stochastic).
 #include "rowwise.cuh"
+
+#include <cooperative_groups.h>
 
 #include <cstdlib>
 
@@ -43,11 +49,13 @@ __device__ __forceinline__ void store_out(void* out, int dtype, long long idx, f
 // 256 threads = TY thread rows of TX lanes (TX = 32, or the power of two that covers cols / V when
 // that is smaller, so that narrow tensors - a channels-last image with 64 channels is 8 vectors
 // wide - still use every lane); grid = (column chunks of TX vectors, splits of the rows, batch).
-template <typename T, bool IS_MAX, bool VEC>
+// CLUSTER: the gridDim.y CTAs that split one reduction are one cluster (cluster dims (1, splits, 1)).
+template <typename T, bool IS_MAX, bool VEC, bool CLUSTER>
 __global__ void __launch_bounds__(512) col_reduce_kernel(const ColReduceParams p) {
   constexpr int V = VEC ? Elem<T>::V : 1;
   constexpr int U = 8;
   __shared__ float red[512 * V + 512];  // [TY][TX * V + 1]
+  __shared__ float fold[CLUSTER ? 32 * V : 1];  // this CTA's folded columns, read by the cluster's first CTA
   const int TX = 1 << p.tx_log2, TY = (int)blockDim.x >> p.tx_log2;
   const int tx = threadIdx.x & (TX - 1), ty = threadIdx.x >> p.tx_log2;
   const int pitch = TX * V + 1;
@@ -99,7 +107,10 @@ __global__ void __launch_bounds__(512) col_reduce_kernel(const ColReduceParams p
   // thread rows are folded in a fixed order, one column per thread
   for (int c = threadIdx.x; c < TX * V; c += blockDim.x) {
     const long long col = (long long)blockIdx.x * TX * V + c;
-    if (col >= p.cols) continue;
+    if (col >= p.cols) {
+      if constexpr (CLUSTER) fold[c] = IS_MAX ? -INFINITY : 0.f;
+      continue;
+    }
     float r;
     if constexpr (IS_MAX) {
       r = red[c];
@@ -109,11 +120,36 @@ __global__ void __launch_bounds__(512) col_reduce_kernel(const ColReduceParams p
       for (int k = 0; k < TY; ++k) d += (double)red[k * pitch + c];
       r = (float)d;
     }
-    if (p.splits == 1) {
+    if constexpr (CLUSTER) {
+      fold[c] = r;
+    } else if (p.splits == 1) {
       store_out(p.out, p.out_dtype, b * p.out_batch_stride + col, r * p.post_scale);
     } else {
       p.partials[((long long)blockIdx.y * p.batch + b) * p.cols + col] = r;
     }
+  }
+  if constexpr (CLUSTER) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();  // every CTA of the cluster has written its fold[]
+    if (cluster.block_rank() == 0) {
+      const unsigned int nblocks = cluster.num_blocks();
+      for (int c = threadIdx.x; c < TX * V; c += blockDim.x) {
+        const long long col = (long long)blockIdx.x * TX * V + c;
+        if (col >= p.cols) continue;
+        float r;
+        if constexpr (IS_MAX) {
+          r = fold[c];
+          for (unsigned int k = 1; k < nblocks; ++k) r = MaxOp::apply(r, cluster.map_shared_rank(fold, k)[c]);
+          store_out(p.out, p.out_dtype, b * p.out_batch_stride + col, r);
+        } else {
+          double d = (double)fold[c];
+          for (unsigned int k = 1; k < nblocks; ++k) d += (double)cluster.map_shared_rank(fold, k)[c];
+          store_out(p.out, p.out_dtype, b * p.out_batch_stride + col, (float)d * p.post_scale);
+        }
+      }
+    }
+    cluster.sync();  // nobody leaves (and gives up its shared memory) before the first CTA has read it
   }
 }
 
@@ -193,14 +229,41 @@ static int launch_col_reduce(ColReduceParams p, bool vec, size_t scratch_bytes, 
   p.splits = (int)splits;
   p.rows_per_split = (p.rows + splits - 1) / splits;
   const bool is_max = p.op == B200_COL_AMAX;
+  // 2..8 splits: one cluster per reduction, combined through distributed shared memory
+  static const bool clusters_off = [] { const char* e = getenv("B200_COL_NO_CLUSTER"); return e && e[0] == '1'; }();
+  if (vec && !clusters_off && splits >= 2 && splits <= 8) {
+    long long cs = splits <= 2 ? 2 : (splits <= 4 ? 4 : 8);
+    while (cs > max_splits && cs > 2) cs /= 2;
+    if (cs <= max_splits) {
+      ColReduceParams q = p;
+      q.splits = (int)cs;
+      q.rows_per_split = (p.rows + cs - 1) / cs;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)chunks, (unsigned)cs, (unsigned)p.batch);
+      cfg.blockDim = dim3(threads);
+      cfg.dynamicSmemBytes = 0;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1;
+      attr[0].val.clusterDim.y = (unsigned)cs;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      cudaError_t e = is_max ? cudaLaunchKernelEx(&cfg, col_reduce_kernel<T, true, true, true>, q)
+                             : cudaLaunchKernelEx(&cfg, col_reduce_kernel<T, false, true, true>, q);
+      if (e == cudaSuccess) return launch_status("b200_col_reduce [vector, cluster of splits, DSMEM combine]");
+      cudaGetLastError();  // the cluster launch was refused: take the two-launch path
+    }
+  }
   dim3 grid((unsigned)chunks, (unsigned)splits, (unsigned)p.batch);
   set_path_tag(vec ? "vector" : "element-wise");
   if (is_max) {
-    if (vec) col_reduce_kernel<T, true, true><<<grid, threads, 0, st>>>(p);
-    else col_reduce_kernel<T, true, false><<<grid, threads, 0, st>>>(p);
+    if (vec) col_reduce_kernel<T, true, true, false><<<grid, threads, 0, st>>>(p);
+    else col_reduce_kernel<T, true, false, false><<<grid, threads, 0, st>>>(p);
   } else {
-    if (vec) col_reduce_kernel<T, false, true><<<grid, threads, 0, st>>>(p);
-    else col_reduce_kernel<T, false, false><<<grid, threads, 0, st>>>(p);
+    if (vec) col_reduce_kernel<T, false, true, false><<<grid, threads, 0, st>>>(p);
+    else col_reduce_kernel<T, false, false, false><<<grid, threads, 0, st>>>(p);
   }
   int rc = launch_status("b200_col_reduce");
   if (rc != B200_OK || splits == 1) return rc;

@@ -19,146 +19,12 @@
 // then writes one fp32 partial row to scratch; after a grid-wide barrier (cooperative launch)
 // the partial rows are summed in fp64, in a fixed order, into dw/db. No atomics: results are
 // bit-reproducible. A two-launch variant (main + finalize) does the same without the barrier.
-#include "rowwise.cuh"
-#include <type_traits>
-
-#include "tile_stream.cuh"
+#include "norm_bwd.cuh"
 
 #include <cstdlib>
+#include <type_traits>
 
 namespace b200 {
-
-struct NormBwdParams {
-  const void* x;
-  const void* dy;
-  const void* w;      // may be null (treated as ones)
-  const float* mean;  // LayerNorm only
-  const float* rstd;
-  void* dx;
-  float* dw;  // may be null
-  float* db;  // may be null
-  long long rows;
-  int n;
-  long long x_row_stride, dy_row_stride;
-  int w_dtype;
-  // dx element (r, c) lives at (r / seq) * dx_batch_stride + (r % seq) * dx_seq_stride
-  //                            + (c / head_dim) * dx_head_stride + (c % head_dim)
-  int seq, head_dim;
-  FastDiv seq_div;  // rows < 2^31, so row / seq is a 32-bit fast division
-  long long dx_batch_stride, dx_seq_stride, dx_head_stride;
-  float n_f;
-  float* partials;    // [groups][n] for dw, followed by [groups][n] for db
-  double* level2;     // [2][slices][n]: second level of the fused finalize (may be null)
-  unsigned int* bar;  // grid barrier words (cooperative variant)
-  int groups;
-  int fused;  // 1: barrier + finalize inside this launch
-};
-
-template <int V>
-__device__ __forceinline__ void zero(float (&a)[V]) {
-#pragma unroll
-  for (int i = 0; i < V; ++i) a[i] = 0.f;
-}
-
-// Sum `groups` partial rows into out[0..n): each CTA takes 64-column chunks, its warps split the
-// partial rows, fp64 accumulation, fixed order.
-__device__ __forceinline__ void finalize_columns(const float* partials, int groups, int n, float* out,
-                                                 double* smem /* [warps][64] */) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const int chunks = (n + 63) / 64;
-  for (int chunk = blockIdx.x; chunk < chunks; chunk += gridDim.x) {
-    const int c0 = chunk * 64 + lane, c1 = c0 + 32;
-    double a0 = 0.0, a1 = 0.0;
-    for (int g0 = warp; g0 < groups; g0 += 4 * nwarps) {  // eight loads in flight, then added in order
-      float v0[4], v1[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int g = g0 + u * nwarps;
-        const float* row = partials + (long long)g * n;
-        v0[u] = (g < groups && c0 < n) ? __ldcg(row + c0) : 0.f;
-        v1[u] = (g < groups && c1 < n) ? __ldcg(row + c1) : 0.f;
-      }
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        a0 += (double)v0[u];
-        a1 += (double)v1[u];
-      }
-    }
-    smem[warp * 64 + lane] = a0;
-    smem[warp * 64 + 32 + lane] = a1;
-    __syncthreads();
-    if (warp == 0) {
-      double s0 = 0.0, s1 = 0.0;
-      for (int w = 0; w < nwarps; ++w) {
-        s0 += smem[w * 64 + lane];
-        s1 += smem[w * 64 + 32 + lane];
-      }
-      if (c0 < n) out[c0] = (float)s0;
-      if (c1 < n) out[c1] = (float)s1;
-    }
-    __syncthreads();
-  }
-}
-
-// Two-level variant for grids much larger than the number of 64-column chunks (narrow rows): with
-// one chunk per CTA only n/64 CTAs would add up all the partial rows while the rest of the grid
-// idles. Level 1: CTA b sums chunk b % chunks over the partial rows slice, slice + slices, ...
-// (slice = b / chunks) and writes fp64 sums; a grid barrier; level 2: the first `chunks` CTAs add
-// the slices in order. `which` selects the dw (0) or db (1) plane of `level2`.
-__device__ __forceinline__ void finalize_level1(const float* partials, int groups, int n, double* level2, int slices,
-                                                double* smem /* [warps][64] */) {
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const int chunks = (n + 63) / 64;
-  if ((int)blockIdx.x >= chunks * slices) return;
-  const int chunk = blockIdx.x % chunks, slice = blockIdx.x / chunks;
-  const int c0 = chunk * 64 + lane, c1 = c0 + 32;
-  double a0 = 0.0, a1 = 0.0;
-  for (int k0 = warp; slice + slices * k0 < groups; k0 += 4 * nwarps) {
-    float v0[4], v1[4];
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      const int g = slice + slices * (k0 + u * nwarps);
-      const float* row = partials + (long long)g * n;
-      v0[u] = (g < groups && c0 < n) ? __ldcg(row + c0) : 0.f;
-      v1[u] = (g < groups && c1 < n) ? __ldcg(row + c1) : 0.f;
-    }
-#pragma unroll
-    for (int u = 0; u < 4; ++u) {
-      a0 += (double)v0[u];
-      a1 += (double)v1[u];
-    }
-  }
-  smem[warp * 64 + lane] = a0;
-  smem[warp * 64 + 32 + lane] = a1;
-  __syncthreads();
-  if (warp == 0) {
-    double s0 = 0.0, s1 = 0.0;
-    for (int w = 0; w < nwarps; ++w) {
-      s0 += smem[w * 64 + lane];
-      s1 += smem[w * 64 + 32 + lane];
-    }
-    if (c0 < n) level2[(long long)slice * n + c0] = s0;
-    if (c1 < n) level2[(long long)slice * n + c1] = s1;
-  }
-  __syncthreads();
-}
-
-__device__ __forceinline__ void finalize_level2(const double* level2, int slices, int n, float* out) {
-  const int chunks = (n + 63) / 64;
-  if ((int)blockIdx.x >= chunks || threadIdx.x >= 64) return;
-  const int c = blockIdx.x * 64 + threadIdx.x;
-  if (c >= n) return;
-  double s = 0.0;
-  for (int k0 = 0; k0 < slices; k0 += 8) {  // eight loads in flight, added in order
-    double v[8];
-#pragma unroll
-    for (int u = 0; u < 8; ++u)
-      v[u] = k0 + u < slices ? __ldcg(level2 + (long long)(k0 + u) * n + c) : 0.0;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) s += v[u];
-  }
-  out[c] = (float)s;
-}
 
 template <typename T, int CH, bool BLOCK, bool LN>
 __global__ void __launch_bounds__(BLOCK ? 512 : 256)
@@ -591,31 +457,6 @@ norm_bwd_stream_kernel(const NormBwdParams p, const int stages) {
 // The second pass reads the stage again (keeping the vectors in registers costs more than it
 // saves at 64 registers per thread), so a stage is refilled one tile after it was consumed.
 // ----------------------------------------------------------------------------------------------
-template <int N>
-__device__ __forceinline__ float warp_reduce_multi(float (&v)[N], int lane) {
-  // After the call lane l holds the warp total of value l / (32 / N).
-  int off = 16;
-#pragma unroll
-  for (int n = N; n > 1; n >>= 1) {
-    const bool upper = (lane & off) != 0;
-#pragma unroll
-    for (int i = 0; i < n / 2; ++i) {
-      const float send = upper ? v[i] : v[i + n / 2];
-      const float keep = upper ? v[i + n / 2] : v[i];
-      v[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-    }
-    off >>= 1;
-  }
-#pragma unroll
-  for (int k = 0; k < 5; ++k) {
-    if (off >= 1) {
-      v[0] += __shfl_xor_sync(0xffffffffu, v[0], off);
-      off >>= 1;
-    }
-  }
-  return v[0];
-}
-
 template <typename T, int R, bool LN, bool GROUPED>
 __global__ void __launch_bounds__(512, 2)
 norm_bwd_tile_kernel(const NormBwdParams p, const int stages, const int TG, const int groups_arg, const int wpg_inv) {
@@ -992,23 +833,6 @@ __global__ void __launch_bounds__(128) norm_bwd_cols_general_kernel(const NormBw
   if (LN) p.partials[((long long)p.groups + blockIdx.y) * p.n + col] = ab;
 }
 
-static int cached_occupancy(const void* fn, int threads, size_t smem = 0) {
-  // The occupancy query is a host-side calculation; cache it per (kernel, block size, smem).
-  struct Entry { const void* fn; int threads; size_t smem; int blocks; };
-  static Entry cache[128];
-  static int used = 0;
-  for (int i = 0; i < used; ++i)
-    if (cache[i].fn == fn && cache[i].threads == threads && cache[i].smem == smem) return cache[i].blocks;
-  int blocks = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, fn, threads, smem) != cudaSuccess) {
-    cudaGetLastError();
-    blocks = 1;
-  }
-  if (blocks < 1) blocks = 1;
-  if (used < 128) cache[used++] = Entry{fn, threads, smem, blocks};
-  return blocks;
-}
-
 static bool streaming_disabled() {
   static const bool off = [] {
     const char* e = getenv("B200_DISABLE_STREAMING");
@@ -1222,6 +1046,10 @@ static int launch_norm_bwd(NormBwdParams p, bool vector_ok, size_t scratch_bytes
   if (p.rows > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "norm_bwd: too many rows");
   const long long nv = p.n / V;
   if (vector_ok && p.n % V == 0 && p.head_dim % V == 0 && nv <= 2048) {
+    {  // rows of 33..256 vectors: warp per row, per-warp copy rings (norm_bwd_warp.cu)
+      int rc = B200_OK;
+      if (try_launch_norm_bwd_warp<T, LN>(p, scratch_bytes, cooperative, st, &rc)) return rc;
+    }
     if (nv <= 128) {
       if (nv > 32 && tile_rows_override() != 1) {  // column-owner CTAs of 2..4 warps, several rows per barrier
         int rc = B200_OK;
@@ -1283,7 +1111,9 @@ using namespace b200;
 
 // Bounded waits of the streaming kernel that ran out since the library was loaded (0 in normal
 // operation). Synchronises the device.
-extern "C" int64_t b200_norm_bwd_wait_timeouts(void) { return (int64_t)read_wait_timeouts(); }
+extern "C" int64_t b200_norm_bwd_wait_timeouts(void) {
+  return (int64_t)read_wait_timeouts() + (int64_t)norm_bwd_warp_wait_timeouts();
+}
 
 // Bytes of scratch that let every path run its largest grid for rows of n elements: the barrier
 // words, two planes (dweight, dbias) of one fp32 partial row per group, and the fp64 second level

@@ -178,27 +178,6 @@ norm_fwd_stream_kernel(const NormFwdParams p, const int stages, const int contig
       num_tiles > blockIdx.x ? (num_tiles - blockIdx.x + gridDim.x - 1) / gridDim.x : 0;
   const Tin* xg = reinterpret_cast<const Tin*>(p.x);
 
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
-    mbar_init_fence();
-  }
-  for (int j = threadIdx.x; j < nv; j += blockDim.x) {
-    float f[V];
-    if (p.w) {
-      load_param<V>(p.w, p.w_dtype, (long long)j * V, f);
-#pragma unroll
-      for (int q = 0; q < PLANES; ++q)
-        *reinterpret_cast<float4*>(wsm + ((size_t)q * nv + j) * 4) = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
-    }
-    if (p.b) {
-      load_param<V>(p.b, p.w_dtype, (long long)j * V, f);
-#pragma unroll
-      for (int q = 0; q < PLANES; ++q)
-        *reinterpret_cast<float4*>(bsm + ((size_t)q * nv + j) * 4) = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
-    }
-  }
-  __syncthreads();
-
   // Thread 0 only: start the copy of this CTA's k-th tile into stage `slot` (= k mod stages,
   // tracked incrementally: a modulo per tile would cost more than the tile's arithmetic).
   const int rows_i = (int)p.rows;  // the launcher admits fewer than 2^31 rows
@@ -218,12 +197,34 @@ norm_fwd_stream_kernel(const NormFwdParams p, const int stages, const int contig
     }
   };
   (void)num_tiles_i;
+  // Thread 0 sets up the stage barriers and starts the first copies at once, before the CTA
+  // converts weight and bias: HBM traffic begins with the CTA instead of after its prologue. (The
+  // other threads first touch a barrier after the __syncthreads below.)
   int issued = 0;
   int issue_slot = 0;  // stage the next copy goes to
   if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) mbar_init(&full[s], 1);
+    mbar_init_fence();
     for (; issued < my_tiles_i && issued < stages; ++issued) issue(issued, issued);
     issue_slot = issued % stages;
   }
+
+  for (int j = threadIdx.x; j < nv; j += blockDim.x) {
+    float f[V];
+    if (p.w) {
+      load_param<V>(p.w, p.w_dtype, (long long)j * V, f);
+#pragma unroll
+      for (int q = 0; q < PLANES; ++q)
+        *reinterpret_cast<float4*>(wsm + ((size_t)q * nv + j) * 4) = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+    }
+    if (p.b) {
+      load_param<V>(p.b, p.w_dtype, (long long)j * V, f);
+#pragma unroll
+      for (int q = 0; q < PLANES; ++q)
+        *reinterpret_cast<float4*>(bsm + ((size_t)q * nv + j) * 4) = make_float4(f[4 * q], f[4 * q + 1], f[4 * q + 2], f[4 * q + 3]);
+    }
+  }
+  __syncthreads();
 
   // Everything a tile needs that does not change from tile to tile is set up here, as 32-bit
   // shared-memory addresses and one running output pointer: the per-tile code is then loads at

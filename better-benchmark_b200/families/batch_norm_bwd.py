@@ -5,13 +5,16 @@ the two oracle.py files). Returns (dbias, dweight, dx) in the eager module's ord
 from .. import kernels
 
 
-def oracle_forward(inputs):
+def oracle_forward(inputs, *, inv_count=None):
+    """``inv_count``: the literal the captured graph multiplies the sums by (1/N of the shape it was
+    captured at); None derives it from the tensor."""
     dy, x, mean, invstd, weight = inputs[:5]
-    dx, dw, db = kernels.batch_norm_bwd(dy, x, mean.reshape(-1), invstd, weight)
+    dx, dw, db = kernels.batch_norm_bwd(dy, x, mean.reshape(-1), invstd, weight, inv_count=inv_count)
     return (db, dw, dx)
 
 
-def leaky_relu_forward(inputs, *, slope=0.2):
+def leaky_relu_forward(inputs, *, slope=0.2, inv_count=None):
     dy, act, x, mean, invstd, weight = inputs[:6]
-    dx, dw, db = kernels.batch_norm_bwd(dy, x, mean.reshape(-1), invstd, weight, act=act, slope=slope)
+    dx, dw, db = kernels.batch_norm_bwd(dy, x, mean.reshape(-1), invstd, weight, act=act, slope=slope,
+                                        inv_count=inv_count)
     return (db, dw, dx)

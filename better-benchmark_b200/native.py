@@ -66,6 +66,12 @@ SIGNATURES = {
                                       c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32,
                                       c_int32, c_double, c_double, c_int32, c_void_p, c_int64,
                                       c_void_p]),
+    "b200_batch_norm_fwd_ex": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, _PF, _PF, _PF, _PF,
+                                         c_int64, c_int64, c_int64, c_int64, c_int64, c_int64, c_int32,
+                                         c_int32, c_double, c_double, c_double, c_int32, c_void_p, c_int64,
+                                         c_void_p]),
+    "b200_batch_norm_bwd_ex": (c_int32, [c_void_p] * 9 + [c_int64] * 6 + [c_int32, c_int32, c_double, c_double,
+                                                                          c_void_p, c_int64, c_void_p]),
     "b200_batch_norm_fwd_static_scratch": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, _PF, _PF, _PF,
                                                      _PF, c_int64, c_int64, c_int64, c_int64, c_int64,
                                                      c_int64, c_int32, c_int32, c_double, c_double, c_int32,

@@ -91,9 +91,12 @@ def stage(reference: Path, dest: Path, extra=()) -> dict:
 # Assembling this backend's directories beside the staged ones
 # ---------------------------------------------------------------------------------------------
 def assemble_b200_dirs(ref_root: Path, out_root: Path) -> dict:
-    """``out_root/<id>/`` = the eager module and shape points of the directory + this backend's
+    """``out_root/<id>_b200/`` = the eager module and shape points of the directory + this backend's
     stub as ``oracle.py``. Returns {id: path}. Directories whose eager module is neither staged nor
-    one of the five benchmark configurations are left out."""
+    one of the five benchmark configurations are left out. (The directory name differs from the
+    staged one on purpose: the reference names an oracle module after its directory and keeps the
+    registrations per module name, so two directories of one name would share a registry and the
+    file loaded first would answer for both.)"""
     out_root.mkdir(parents=True, exist_ok=True)
     made = {}
     for name in stub_ids():
@@ -105,7 +108,7 @@ def assemble_b200_dirs(ref_root: Path, out_root: Path) -> dict:
             sources = {"repro.py": own / "repro.py"}
         else:
             continue
-        d = out_root / name
+        d = out_root / f"{name}_b200"
         d.mkdir(exist_ok=True)
         for f, src in sources.items():
             shutil.copyfile(src, d / f)

@@ -224,6 +224,26 @@ int32_t b200_batch_norm_bwd(const void* dy, const void* x, const void* act, cons
                             int32_t w_dtype, double slope, void* scratch, int64_t scratch_bytes,
                             void* stream);
 
+/* The two entry points above with a constant of the captured graph passed in instead of derived
+ * from the sizes. The reference's eager modules are graphs captured at ONE shape point; numbers that
+ * depended on that shape are literals in them (var_mean_42fad1ece813/repro.py:40 multiplies the
+ * batch variance by 1.0001220852154804 = 8192/8191, sum_sum_183b124c731f/repro.py:33 multiplies the
+ * sums by 6.228077168367346e-07 = 1/1605632) and are applied unchanged at every other point of
+ * shapes.json, as the reference's own oracles do (sum_sum_183b124c731f/oracle.py:10). unbiased_factor
+ * / inv_count <= 0 select the value derived from the sizes. */
+int32_t b200_batch_norm_fwd_ex(const void* x, void* y, const void* weight, const void* bias,
+                               float* running_mean, float* running_var, float* save_mean,
+                               float* save_invstd, int64_t batch, int64_t channels, int64_t spatial,
+                               int64_t stride_n, int64_t stride_c, int64_t stride_s, int32_t x_dtype,
+                               int32_t w_dtype, double eps, double momentum, double unbiased_factor,
+                               int32_t relu, void* scratch, int64_t scratch_bytes, void* stream);
+int32_t b200_batch_norm_bwd_ex(const void* dy, const void* x, const void* act, const float* mean,
+                               const float* invstd, const void* weight, void* dx, float* dweight,
+                               float* dbias, int64_t batch, int64_t channels, int64_t spatial,
+                               int64_t stride_n, int64_t stride_c, int64_t stride_s, int32_t x_dtype,
+                               int32_t w_dtype, double slope, double inv_count, void* scratch,
+                               int64_t scratch_bytes, void* stream);
+
 /* b200_batch_norm_fwd for callers that may not allocate device memory (a host framework that owns
  * the only arena and forbids plug-ins to call cudaMalloc, or a caller that owns nothing but the
  * tensors it was handed): the scratch lives in a fixed array inside the library's device image

@@ -111,3 +111,37 @@ def test_norm_bwd_is_bit_reproducible():
         again = k.norm_bwd(x, dy, w, rstd, rms=True)
         assert torch.equal(first[0], again[0]) and torch.equal(first[1], again[1])
     k.check_scratch_status()
+
+
+@pytest.mark.parametrize("rows,n,dtype,ln", [(20011, 768, torch.bfloat16, True), (9001, 520, torch.float32, False),
+                                             (30000, 512, torch.bfloat16, False), (12345, 1000, torch.float16, True),
+                                             (5000, 1024, torch.float32, True)])
+def test_norm_bwd_many_narrow_rows(rows, n, dtype, ln):
+    """Rows of 33..256 vectors, enough of them that every warp of the warp-per-row kernel walks its
+    copy ring around several times (ragged last chunk and a row count that is no multiple of the
+    grid included)."""
+    k = _kernels()
+    x = _rand((rows, n), dtype, 21, scale=1.5)
+    dy = _rand((rows, n), dtype, 22)
+    w = (torch.rand(n, generator=torch.Generator().manual_seed(23)) + 0.5)
+    mean, rstd, rrms = _stats(x)
+    before = k.load().b200_launch_count()
+    if ln:
+        want = _ln_reference(x, dy, w, mean, rstd)
+        anchor = _ln_reference(x.double(), dy.double(), w.double(), mean.double(), rstd.double())
+        dx, dw, db = k.norm_bwd(x.cuda(), dy.cuda(), w.cuda(), rstd.cuda(), mean=mean.cuda(), rms=False,
+                                want_dbias=True)
+        _close_columns(db, want[2], anchor[2], f"ln db {rows}x{n}")
+    else:
+        want = _rms_reference(x, dy, w.to(dtype), rrms)
+        anchor = _rms_reference(x.double(), dy.double(), w.to(dtype).double(), rrms.double())
+        dx, dw, _ = k.norm_bwd(x.cuda(), dy.cuda(), w.to(dtype).cuda(), rrms.cuda(), rms=True)
+    assert k.load().b200_launch_count() - before == 1, "one fused launch expected"
+    assert b"warp per row" in k.load().b200_last_kernel()
+    assert_close(dx, want[0], f"dx {rows}x{n} {dtype}")
+    _close_columns(dw, want[1], anchor[1], f"dw {rows}x{n}")
+    again = k.norm_bwd(x.cuda(), dy.cuda(), w.cuda() if ln else w.to(dtype).cuda(), (rstd if ln else rrms).cuda(),
+                       mean=mean.cuda() if ln else None, rms=not ln, want_dbias=ln)
+    assert torch.equal(again[0], dx) and torch.equal(again[1], dw), "bit-reproducible"
+    k.check_scratch_status()
+    assert k.load().b200_norm_bwd_wait_timeouts() == 0

@@ -58,6 +58,28 @@ def test_col_reduce_batched_strided_rows():
     assert_sum_close(got, want, anchor, "batched strided col sum")
 
 
+@pytest.mark.parametrize("op", ["sum", "mean", "amax"])
+@pytest.mark.parametrize("batch,rows,cols,dtype", [(128, 3136, 64, torch.bfloat16), (96, 784, 256, torch.float16),
+                                                   (3, 2000, 4096, torch.float32), (20, 1500, 1000, torch.float32)])
+def test_col_reduce_cluster_combine(op, batch, rows, cols, dtype):
+    """Shapes that split every reduction over 2, 4 or 8 CTAs: those form a thread-block cluster and
+    are combined through distributed shared memory in one launch."""
+    from oracle import eager
+    k = _kernels()
+    x = _rand((batch, rows, cols), dtype, batch + rows)
+    before = k.load().b200_launch_count()
+    got = k.col_reduce(x, op)
+    launched = k.load().b200_launch_count() - before
+    assert launched == 1 and b"cluster" in k.load().b200_last_kernel(), k.load().b200_last_kernel()
+    want = torch.stack([eager.ColumnSum(op)(x[i]) for i in range(batch)])
+    if op == "amax":
+        assert torch.equal(got, want)
+    else:
+        anchor = torch.stack([eager.ColumnSum(op)(x[i].double()) for i in range(batch)])
+        assert_sum_close(got, want, anchor, f"cluster col_{op} {batch}x{rows}x{cols} {dtype}")
+    assert torch.equal(got, k.col_reduce(x, op)), "bit-reproducible"
+
+
 def test_col_reduce_zero_rows_and_bad_layout():
     k = _kernels()
     x = torch.empty((0, 16), device="cuda")
