@@ -16,6 +16,6 @@ from better_benchmark_b200 import kernels
 @every_point(oracle_impl, hardware="B200")
 def oracle_forward(inputs):
     rstd, dy, weight, x, mean, dy_shape = inputs[:6]
-    dx, dweight, _ = kernels.norm_bwd(x, dy.expand(dy_shape).contiguous(), weight, rstd.reshape(-1),
+    dx, dweight, _ = kernels.norm_bwd(x, dy, weight, rstd.reshape(-1),  # dy: 0-dim, read as a scalar
                                       mean=mean.reshape(-1), rms=False)
     return (dx, dweight)

@@ -16,8 +16,8 @@
 // partials over a fixed split of the rows), finalize (fixed order, coefficient table), apply (each
 // CTA walks its part of the rows backwards, so that it starts in what the sums pass left in L2).
 // No atomics: bit-reproducible.
-// Channels-last tensors with a power-of-two number of 16-byte vectors per row take the vector
-// kernels; every other layout the strided element-wise ones.
+// Channels-last tensors whose channel count is a multiple of the 16-byte vector (at most 256
+// vectors per row) take the vector kernels; every other layout the strided element-wise ones.
 #include "rowwise.cuh"
 
 namespace b200 {
@@ -318,9 +318,10 @@ static int launch_bn_bwd(BnBwdParams p, bool fast, size_t scratch_bytes, cudaStr
   const long long coef_floats = 4LL * p.channels;
   if (fast) {
     const int vpr = p.channels / V;
+    const int threads = 256 / vpr * vpr;  // a multiple of vpr: a thread stays in one vector column
     const long long total = p.rows * vpr;
-    long long splits = 8LL * dev.sm_count;  // eight 256-thread CTAs per SM
-    if (splits * 256 * 4 > total) splits = (total + 256 * 4 - 1) / (256 * 4);
+    long long splits = 8LL * dev.sm_count;  // eight CTAs per SM
+    if (splits * threads * 4 > total) splits = (total + threads * 4 - 1) / (threads * 4);
     if (splits < 1) splits = 1;
     long long per = (total + splits - 1) / splits;
     per = (per + vpr - 1) / vpr * vpr;  // whole rows per CTA: the column of a thread stays fixed
@@ -330,13 +331,13 @@ static int launch_bn_bwd(BnBwdParams p, bool fast, size_t scratch_bytes, cudaStr
       return fail(B200_ERR_WORKSPACE, "b200_batch_norm_bwd: scratch of %zu bytes, need %lld", scratch_bytes, need);
     p.splits = (int)splits;
     p.coef = reinterpret_cast<float*>(p.partials + splits * 2 * p.channels);
-    bn_bwd_sums_cl_kernel<T><<<(unsigned)splits, 256, 0, st>>>(p, per);
+    bn_bwd_sums_cl_kernel<T><<<(unsigned)splits, threads, 0, st>>>(p, per);
     int rc = launch_status("b200_batch_norm_bwd sums");
     if (rc != B200_OK) return rc;
     bn_bwd_finalize_kernel<<<p.channels, 256, 0, st>>>(p);
     rc = launch_status("b200_batch_norm_bwd finalize");
     if (rc != B200_OK || !p.dx) return rc;
-    bn_bwd_apply_cl_kernel<T><<<(unsigned)splits, 256, 0, st>>>(p, per);
+    bn_bwd_apply_cl_kernel<T><<<(unsigned)splits, threads, 0, st>>>(p, per);
     return launch_status("b200_batch_norm_bwd apply [channels-last, vector]");
   }
   const long long total = p.rows * p.spatial;
@@ -401,7 +402,7 @@ extern "C" int b200_batch_norm_bwd_ex(const void* dy, const void* x, const void*
   const int v = 16 / eb;
   const bool cl = stride_c == 1 && stride_s == channels && stride_n == spatial * channels;
   const long long vpr = channels / v;
-  const bool fast = cl && channels % v == 0 && vpr <= 256 && (vpr & (vpr - 1)) == 0 && aligned16(dy) &&
+  const bool fast = cl && channels % v == 0 && vpr >= 1 && vpr <= 256 && aligned16(dy) &&
                     aligned16(x) && (!act || aligned16(act)) && (!dx || aligned16(dx));
   p.rows = fast ? batch * spatial : batch;
   switch (x_dtype) {

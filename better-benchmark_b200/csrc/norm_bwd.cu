@@ -780,7 +780,7 @@ __global__ void __launch_bounds__(256) norm_bwd_rows_general_kernel(const NormBw
   float s1 = 0.f, s2 = 0.f;
   for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
     const float w = p.w ? load_param1(p.w, p.w_dtype, i) : 1.f;
-    const float g = Elem<T>::to_f32(dy[i]) * w;
+    const float g = Elem<T>::to_f32(dy[(long long)i * p.dy_elem_stride]) * w;
     const float xv = Elem<T>::to_f32(x[i]);
     if (LN) {
       const float xhat = (xv - mean) * rstd;
@@ -796,7 +796,7 @@ __global__ void __launch_bounds__(256) norm_bwd_rows_general_kernel(const NormBw
   const float k = LN ? rstd / p.n_f : ((s2 * -0.5f) * (rstd * rstd * rstd)) / p.n_f;
   for (int i = threadIdx.x; i < p.n; i += blockDim.x) {
     const float w = p.w ? load_param1(p.w, p.w_dtype, i) : 1.f;
-    const float g = Elem<T>::to_f32(dy[i]) * w;
+    const float g = Elem<T>::to_f32(dy[(long long)i * p.dy_elem_stride]) * w;
     const float xv = Elem<T>::to_f32(x[i]);
     float o;
     if (LN) {
@@ -820,7 +820,7 @@ __global__ void __launch_bounds__(128) norm_bwd_cols_general_kernel(const NormBw
   float aw = 0.f, ab = 0.f;
   for (long long r = r0; r < r1; ++r) {
     const float xv = Elem<T>::to_f32(reinterpret_cast<const T*>(p.x)[r * p.x_row_stride + col]);
-    const float dyv = Elem<T>::to_f32(reinterpret_cast<const T*>(p.dy)[r * p.dy_row_stride + col]);
+    const float dyv = Elem<T>::to_f32(reinterpret_cast<const T*>(p.dy)[r * p.dy_row_stride + (long long)col * p.dy_elem_stride]);
     const float rstd = p.rstd[r];
     if (LN) {
       aw += dyv * ((xv - p.mean[r]) * rstd);
@@ -1050,6 +1050,10 @@ static int launch_norm_bwd(NormBwdParams p, bool vector_ok, size_t scratch_bytes
       int rc = B200_OK;
       if (try_launch_norm_bwd_warp<T, LN>(p, scratch_bytes, cooperative, st, &rc)) return rc;
     }
+  }
+  // a broadcast scalar dy is read by the warp-per-row kernel above and by the element-wise kernels
+  // below; the other vector kernels stream dy rows
+  if (p.dy_elem_stride != 0 && vector_ok && p.n % V == 0 && p.head_dim % V == 0 && nv <= 2048) {
     if (nv <= 128) {
       if (nv > 32 && tile_rows_override() != 1) {  // column-owner CTAs of 2..4 warps, several rows per barrier
         int rc = B200_OK;
@@ -1154,6 +1158,9 @@ extern "C" int b200_norm_bwd(const void* x, const void* dy, const void* weight, 
   NormBwdParams p;
   p.x = x; p.dy = dy; p.w = weight; p.mean = mean; p.rstd = rstd; p.dx = dx; p.dw = dweight; p.db = dbias;
   p.rows = rows; p.n = (int)n; p.x_row_stride = x_row_stride; p.dy_row_stride = dy_row_stride;
+  const bool dy_scalar = (flags & 2) != 0;  // dy points at ONE element that stands for the whole tensor
+  p.dy_elem_stride = dy_scalar ? 0 : 1;
+  if (dy_scalar) p.dy_row_stride = 0;
   p.w_dtype = w_dtype; p.seq = (int)seq; p.head_dim = (int)head_dim;
   p.seq_div = make_fast_div(seq);
   p.dx_batch_stride = dx_batch_stride; p.dx_seq_stride = dx_seq_stride; p.dx_head_stride = dx_head_stride;
@@ -1166,8 +1173,8 @@ extern "C" int b200_norm_bwd(const void* x, const void* dy, const void* weight, 
   const int eb = dtype_size(x_dtype), wb = dtype_size(w_dtype);
   const int v = 16 / eb;
   const int w_chunk = v * wb < 16 ? v * wb : 16;
-  bool vec = aligned16(x) && aligned16(dy) && aligned16(dx) && (x_row_stride * eb) % 16 == 0 &&
-             (dy_row_stride * eb) % 16 == 0 && (dx_batch_stride * eb) % 16 == 0 &&
+  bool vec = aligned16(x) && (dy_scalar || aligned16(dy)) && aligned16(dx) && (x_row_stride * eb) % 16 == 0 &&
+             (p.dy_row_stride * eb) % 16 == 0 && (dx_batch_stride * eb) % 16 == 0 &&
              (dx_seq_stride * eb) % 16 == 0 && (dx_head_stride * eb) % 16 == 0;
   if (weight) vec = vec && reinterpret_cast<uintptr_t>(weight) % w_chunk == 0;
 

@@ -19,6 +19,7 @@ struct NormBwdParams {
   long long rows;
   int n;
   long long x_row_stride, dy_row_stride;
+  int dy_elem_stride;  // 1, or 0 when dy is one element broadcast over the whole tensor (dy_row_stride 0 too)
   int w_dtype;
   // dx element (r, c) lives at (r / seq) * dx_batch_stride + (r % seq) * dx_seq_stride
   //                            + (c / head_dim) * dx_head_stride + (c % head_dim)

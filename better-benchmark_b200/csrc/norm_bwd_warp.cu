@@ -32,7 +32,10 @@ namespace {
 
 constexpr int kWarps = 8;  // warps per CTA
 
-template <typename T, int CH, bool LN>
+// DYS: dy is ONE element broadcast over the whole tensor (the captured graphs of the reference's
+// norm-backward directories expand a 0-dim gradient, repros/canonical/sum_sum_2cd99e5eb23e/repro.py:26);
+// nothing is read for it and a stage holds the row of x only.
+template <typename T, int CH, bool LN, bool DYS>
 __global__ void __launch_bounds__(kWarps * 32, 2)
 norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_bytes) {
   constexpr int V = Elem<T>::V;
@@ -43,7 +46,7 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nv = p.n / V;
   const uint32_t row_bytes = (uint32_t)nv * 16u;
-  const uint32_t stage_bytes = 2u * row_bytes;
+  const uint32_t stage_bytes = (DYS ? 1u : 2u) * row_bytes;
   // layout: [kWarps][stages][x row | dy row] | pad to ring_bytes | mbarriers [kWarps][8] | fp32 weight [n] (LayerNorm)
   unsigned char* ring = smem + (size_t)warp * stages * stage_bytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + ring_bytes) + warp * 8;
@@ -66,8 +69,9 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
     unsigned char* dst = ring + (size_t)slot * stage_bytes;
     mbar_arrive_expect_tx(&full[slot], stage_bytes);
     bulk_load(dst, xg + row * p.x_row_stride, row_bytes, &full[slot]);
-    bulk_load(dst + row_bytes, dyg + row * p.dy_row_stride, row_bytes, &full[slot]);
+    if constexpr (!DYS) bulk_load(dst + row_bytes, dyg + row * p.dy_row_stride, row_bytes, &full[slot]);
   };
+  const f32x2 dy_all = splat2(DYS ? Elem<T>::to_f32(__ldg(dyg)) : 0.f);
 
   // weight slice: registers (RMSNorm) or shared memory (LayerNorm, which already keeps two
   // gradient sums per column in registers)
@@ -175,7 +179,12 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
       if (c * 32 + lane < nv) {
         f32x2 x2[P], dy2[P];
         Pairs<T>::unpack(lds128(sx + c * 512), x2);
-        Pairs<T>::unpack(lds128(sy + c * 512), dy2);
+        if constexpr (DYS) {
+#pragma unroll
+          for (int i = 0; i < P; ++i) dy2[i] = dy_all;
+        } else {
+          Pairs<T>::unpack(lds128(sy + c * 512), dy2);
+        }
 #pragma unroll
         for (int i = 0; i < P; ++i) {
           const f32x2 g2 = mul2(dy2[i], weight(c, i));
@@ -214,7 +223,12 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
         if (c * 32 + lane < nv) {
           f32x2 x2[P], dy2[P], o2[P];
           Pairs<T>::unpack(lds128(sx + c * 512), x2);
-          Pairs<T>::unpack(lds128(sy + c * 512), dy2);
+          if constexpr (DYS) {
+#pragma unroll
+            for (int i = 0; i < P; ++i) dy2[i] = dy_all;
+          } else {
+            Pairs<T>::unpack(lds128(sy + c * 512), dy2);
+          }
 #pragma unroll
           for (int i = 0; i < P; ++i) {
             const f32x2 g2 = mul2(dy2[i], weight(c, i));
@@ -236,7 +250,12 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
         if (c * 32 + lane < nv) {
           f32x2 x2[P], dy2[P], o2[P];
           Pairs<T>::unpack(lds128(sx + c * 512), x2);
-          Pairs<T>::unpack(lds128(sy + c * 512), dy2);
+          if constexpr (DYS) {
+#pragma unroll
+            for (int i = 0; i < P; ++i) dy2[i] = dy_all;
+          } else {
+            Pairs<T>::unpack(lds128(sy + c * 512), dy2);
+          }
 #pragma unroll
           for (int i = 0; i < P; ++i) {
             const f32x2 g2 = mul2(dy2[i], weight(c, i));
@@ -325,12 +344,12 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
   }
 }
 
-template <typename T, int CH, bool LN>
-bool launch_warp_kernel(NormBwdParams p, size_t scratch_bytes, cudaStream_t st, int* rc) {
+template <typename T, int CH, bool LN, bool DYS>
+bool launch_warp_kernel_impl(NormBwdParams p, size_t scratch_bytes, cudaStream_t st, int* rc) {
   constexpr int V = Elem<T>::V;
   const DeviceInfo& dev = device_info();
   const int nv = p.n / V;
-  const size_t stage_bytes = 2 * (size_t)nv * 16;
+  const size_t stage_bytes = (DYS ? 1 : 2) * (size_t)nv * 16;
   const size_t fixed = kWarps * 8 * sizeof(uint64_t) + (LN ? (size_t)p.n * sizeof(float) : 0);
   // the ring doubles as the fold area [2][kWarps][n] fp32 and as the fp64 area of the finalize
   size_t floor_bytes = 2 * (size_t)kWarps * p.n * sizeof(float);
@@ -349,7 +368,7 @@ bool launch_warp_kernel(NormBwdParams p, size_t scratch_bytes, cudaStream_t st, 
   ring_bytes = (ring_bytes + 127) / 128 * 128;
   const size_t smem = ring_bytes + fixed;
   if (smem > (size_t)dev.max_smem_optin) return false;
-  auto kernel = norm_bwd_warp_kernel<T, CH, LN>;
+  auto kernel = norm_bwd_warp_kernel<T, CH, LN, DYS>;
   cudaError_t e = cudaFuncSetAttribute(reinterpret_cast<const void*>(kernel),
                                        cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
   if (e != cudaSuccess) {
@@ -386,9 +405,16 @@ bool launch_warp_kernel(NormBwdParams p, size_t scratch_bytes, cudaStream_t st, 
     *rc = fail((int)e, "b200_norm_bwd: cooperative launch failed: %s", cudaGetErrorString(e));
     return true;
   }
-  note_launch("b200_norm_bwd [warp per row, warp rings, fused finalize]");
+  note_launch(DYS ? "b200_norm_bwd [warp per row, warp rings, scalar dy, fused finalize]"
+                  : "b200_norm_bwd [warp per row, warp rings, fused finalize]");
   *rc = B200_OK;
   return true;
+}
+
+template <typename T, int CH, bool LN>
+bool launch_warp_kernel(NormBwdParams p, size_t scratch_bytes, cudaStream_t st, int* rc) {
+  return p.dy_elem_stride == 0 ? launch_warp_kernel_impl<T, CH, LN, true>(p, scratch_bytes, st, rc)
+                               : launch_warp_kernel_impl<T, CH, LN, false>(p, scratch_bytes, st, rc);
 }
 
 }  // namespace

@@ -370,6 +370,183 @@ __global__ void __launch_bounds__(1024) softmax_streaming_kernel(const SoftmaxPa
   }
 }
 
+// ----------------------------------------------------------------------------------------------
+// Long or ragged rows (rows that do not fit the register-resident kernel, or whose length is not a
+// whole number of 16-byte vectors): one CTA per row, two sweeps instead of three.
+//   sweep 1: every thread keeps a running maximum m and the sum of exp(t - m) of its elements,
+//            rescaling the sum when the maximum grows; the CTA then combines the (m, s) pairs:
+//            M = max m_i, S = sum s_i * exp(m_i - M)
+//   sweep 2: the row is read again - it was just read by this CTA, so for rows up to a few hundred
+//            KB it comes from L2 - and y = exp(t - M) / S (or t - M - log S) is written.
+// Both sweeps use 16-byte loads when the row starts on a 16-byte boundary (the ragged tail is read
+// element by element) and 16-byte stores when the output row does. No mask; the optional scale is
+// applied in fp32.
+// ----------------------------------------------------------------------------------------------
+template <typename Tout>
+__device__ __forceinline__ f32x2 long_row_exp(f32x2 d) {
+  if constexpr (sizeof(Tout) == 2) {
+    return exp_pair_compensated(d);
+  } else {
+    float a, b;
+    unpack2(d, a, b);
+    return pack2(expf(a), expf(b));
+  }
+}
+
+template <typename Tin, typename Tout>
+__global__ void __launch_bounds__(1024) softmax_long_kernel(const SoftmaxParams p) {
+  constexpr int V = Elem<Tin>::V;
+  constexpr int P = V / 2;
+  constexpr int U = 4;  // vectors in flight per thread
+  constexpr float kFloor = -1e30f;  // finite stand-in for -inf inside the compensated exponential
+  __shared__ float red[64];
+  const long long row = blockIdx.x;
+  const Tin* x = reinterpret_cast<const Tin*>(p.x) + row_offset(p.xmap, row);
+  Tout* y = reinterpret_cast<Tout*>(p.y) + row_offset(p.ymap, row);
+  const int tid = threadIdx.x, T_ = blockDim.x;
+  const bool x_vec = (reinterpret_cast<uintptr_t>(x) & 15u) == 0;
+  const int nvec = x_vec ? p.n / V : 0;
+  const int body = nvec * V;  // elements covered by whole vectors
+  const f32x2 scale2 = splat2(p.has_scale ? p.scale : 1.0f);
+  const bool scaled = p.has_scale != 0;
+
+  // ---- sweep 1 ----------------------------------------------------------------------------------
+  float m = -INFINITY, s = 0.f;
+  auto absorb = [&](const f32x2 (&t)[P]) {  // one vector of logits into (m, s)
+    float vm = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      float a, b;
+      unpack2(t[i], a, b);
+      vm = fmaxf(vm, fmaxf(a, b));
+    }
+    if (vm > m) {
+      s = s * expf(fmaxf(m, kFloor) - vm);  // m = -inf the first time: the sum is still zero
+      m = vm;
+    }
+    const f32x2 m2 = splat2(fmaxf(m, kFloor));
+    f32x2 acc = splat2(0.f);
+#pragma unroll
+    for (int i = 0; i < P; ++i) {
+      float a, b;
+      unpack2(t[i], a, b);
+      a = fmaxf(a, kFloor);  // NaN would be lost here, so NaN rows are caught through the maximum below
+      b = fmaxf(b, kFloor);
+      acc = add2(acc, long_row_exp<Tout>(sub2(pack2(a, b), m2)));
+    }
+    s += hsum2(acc);
+  };
+  bool saw_nan = false;
+  for (int j0 = tid; j0 < nvec; j0 += U * T_) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + u * T_;
+      if (j < nvec) raw[u] = ld_keep(x + (long long)j * V);  // read again in sweep 2: keep it cached
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + u * T_;
+      if (j < nvec) {
+        f32x2 t[P];
+        Pairs<Tin>::unpack(raw[u], t);
+        if (scaled) {
+#pragma unroll
+          for (int i = 0; i < P; ++i) t[i] = mul2(t[i], scale2);
+        }
+#pragma unroll
+        for (int i = 0; i < P; ++i) {
+          float a, b;
+          unpack2(t[i], a, b);
+          saw_nan |= (a != a) | (b != b);
+        }
+        absorb(t);
+      }
+    }
+  }
+  for (int i = body + tid; i < p.n; i += T_) {  // ragged tail, or the whole row when it is unaligned
+    float t = Elem<Tin>::to_f32(x[i]);
+    if (scaled) t = t * p.scale;
+    saw_nan |= t != t;
+    if (t > m) {
+      s = s * expf(fmaxf(m, kFloor) - t);
+      m = t;
+    }
+    s += expf(fmaxf(t, kFloor) - fmaxf(m, kFloor));
+  }
+  // CTA-wide (M, S)
+  const float M = block_reduce<FastMax>(m, red);
+  const float contrib = (m == -INFINITY) ? 0.f : s * expf(m - fmaxf(M, kFloor));
+  float S = block_reduce<SumOp>(contrib, red);
+  const float nan_any = block_reduce<FastMax>(saw_nan ? 1.f : 0.f, red);
+  if (M == -INFINITY || nan_any > 0.f) S = NAN;  // aten: x - max is NaN for a row of -inf; NaN logits poison the row
+
+  // ---- sweep 2 ----------------------------------------------------------------------------------
+  const float logS = logf(S);
+  const float inv = __frcp_rn(S);
+  const float Mf = fmaxf(M, kFloor);
+  const bool log_mode = p.log_mode != 0;
+  auto finish = [&](float t) -> float {  // one logit -> one output value
+    if (log_mode) return (t - M) - logS;
+    const float e = expf(fmaxf(t, kFloor) - Mf);
+    return sizeof(Tout) == 4 ? e / S : e * inv;
+  };
+  constexpr int VO = 16 / (int)sizeof(Tout);           // output elements per 16-byte store
+  const bool y_vec = x_vec && (reinterpret_cast<uintptr_t>(y) & 15u) == 0 && V % VO == 0;
+  const f32x2 M2 = splat2(Mf), inv2 = splat2(inv), logS2 = splat2(logS), Mraw2 = splat2(M);
+  for (int j0 = tid; j0 < nvec; j0 += U * T_) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + u * T_;
+      if (j < nvec) raw[u] = ld_stream(x + (long long)j * V);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = j0 + u * T_;
+      if (j < nvec) {
+        f32x2 t[P], o[P];
+        Pairs<Tin>::unpack(raw[u], t);
+#pragma unroll
+        for (int i = 0; i < P; ++i) {
+          if (scaled) t[i] = mul2(t[i], scale2);
+          if (log_mode) {
+            o[i] = sub2(sub2(t[i], Mraw2), logS2);
+          } else {
+            float a, b;
+            unpack2(t[i], a, b);
+            const f32x2 e = long_row_exp<Tout>(sub2(pack2(fmaxf(a, kFloor), fmaxf(b, kFloor)), M2));
+            if constexpr (sizeof(Tout) == 4) {
+              float ea, eb;
+              unpack2(e, ea, eb);
+              o[i] = pack2(ea / S, eb / S);
+            } else {
+              o[i] = mul2(e, inv2);
+            }
+          }
+        }
+        Tout* dst = y + (long long)j * V;
+        if (y_vec) {
+          store_pairs<Tout, V>(dst, o);
+        } else {
+#pragma unroll
+          for (int i = 0; i < P; ++i) {
+            float a, b;
+            unpack2(o[i], a, b);
+            dst[2 * i] = Elem<Tout>::from_f32(a);
+            dst[2 * i + 1] = Elem<Tout>::from_f32(b);
+          }
+        }
+      }
+    }
+  }
+  for (int i = body + tid; i < p.n; i += T_) {
+    float t = Elem<Tin>::to_f32(x[i]);
+    if (scaled) t = t * p.scale;
+    y[i] = Elem<Tout>::from_f32(finish(t));
+  }
+}
+
 template <typename Tin, typename Tout, bool PACKED>
 static int launch_softmax(const SoftmaxParams& p, bool vector_ok, cudaStream_t st) {
   constexpr int V = Elem<Tin>::V;
@@ -403,6 +580,12 @@ static int launch_softmax(const SoftmaxParams& p, bool vector_ok, cudaStream_t s
       else B200_SM_LAUNCH(0, 8);
 #undef B200_SM_LAUNCH
     }
+  } else if (p.mask == nullptr && !PACKED && p.n >= 256) {
+    int threads = (int)((p.n / V + 3) / 4);
+    threads = (threads + 31) / 32 * 32;
+    threads = threads < 128 ? 128 : (threads > 1024 ? 1024 : threads);
+    set_path_tag("two sweeps, CTA per row");
+    softmax_long_kernel<Tin, Tout><<<(unsigned)p.rows, threads, 0, st>>>(p);
   } else {
     int threads = 1024;
     while (threads > 64 && threads / 2 >= p.n) threads /= 2;

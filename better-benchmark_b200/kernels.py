@@ -293,6 +293,7 @@ def check_scratch_status(device: torch.device | None = None) -> None:
 
 
 NORM_BWD_TWO_LAUNCH = 1  # flag: main kernel + finalize kernel instead of one cooperative launch
+NORM_BWD_DY_SCALAR = 2   # flag: dy is one element that stands for the whole tensor (an expanded 0-dim gradient)
 
 
 def norm_bwd(x: torch.Tensor, dy: torch.Tensor, weight: torch.Tensor | None, rstd: torch.Tensor, *,
@@ -301,16 +302,19 @@ def norm_bwd(x: torch.Tensor, dy: torch.Tensor, weight: torch.Tensor | None, rst
              scratch: torch.Tensor | None = None):
     """LayerNorm / RMSNorm backward over the last dimension (flattened over trailing dims for 4-D).
 
-    ``x`` and ``dy`` are [..., n] or, with ``heads``, [B, S, H, D] (n = H*D): dx is then returned
+    ``dy`` may also be a single element (0-dim, or expanded to x's shape with zero strides): the
+    kernels then read it as a scalar. ``x`` and ``dy`` are [..., n] or, with ``heads``, [B, S, H, D] (n = H*D): dx is then returned
     as a contiguous [B, H, S, D] tensor, the permute fused into the store. ``rstd`` (and ``mean``
     for LayerNorm) are fp32 with one value per row. Returns (dx, dweight, dbias); the gradients of
     weight and bias are fp32 [n].
     """
     _require_cuda(x, dy, weight, rstd, mean, scratch)
-    if x.shape != dy.shape or x.dtype != dy.dtype:
+    # a 0-dim (or fully expanded one-element) dy is read as a scalar by the kernel: nothing is materialised
+    dy_scalar = dy.numel() == 1 or (dy.shape == x.shape and all(st == 0 for st in dy.stride()))
+    if x.dtype != dy.dtype or (not dy_scalar and x.shape != dy.shape):
         raise UnsupportedLayout("norm_bwd: x and dy must agree in shape and dtype")
     if heads is not None:
-        if x.dim() != 4 or x.shape[2] != heads or not x.is_contiguous() or not dy.is_contiguous():
+        if x.dim() != 4 or x.shape[2] != heads or not x.is_contiguous() or not (dy_scalar or dy.is_contiguous()):
             raise UnsupportedLayout("norm_bwd: heads= needs contiguous [B, S, H, D] inputs")
         b, s, h, d = x.shape
         rows, n = b * s, h * d
@@ -320,7 +324,7 @@ def norm_bwd(x: torch.Tensor, dy: torch.Tensor, weight: torch.Tensor | None, rst
         dx_batch, dx_seq, dx_head = h * s * d, d, s * d
     else:
         rows, n, x_stride = _rows_2d(x, "norm_bwd")
-        _, _, dy_stride = _rows_2d(dy, "norm_bwd")
+        dy_stride = 0 if dy_scalar else _rows_2d(dy, "norm_bwd")[2]
         dx = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         seq, head_dim = 1, n
         dx_batch, dx_seq, dx_head = n, 0, n
@@ -346,7 +350,8 @@ def norm_bwd(x: torch.Tensor, dy: torch.Tensor, weight: torch.Tensor | None, rst
     check(lib.b200_norm_bwd(_ptr(x), _ptr(dy), _ptr(weight), _ptr(mean), _ptr(rstd), _ptr(dx),
                             _ptr(dw), _ptr(db), rows, n, x_stride, dy_stride, _code(x), w_code,
                             1 if rms else 0, seq, head_dim, dx_batch, dx_seq, dx_head,
-                            _ptr(scratch), nbytes, NORM_BWD_TWO_LAUNCH if two_launch else 0,
+                            _ptr(scratch), nbytes,
+                            (NORM_BWD_TWO_LAUNCH if two_launch else 0) | (NORM_BWD_DY_SCALAR if dy_scalar else 0),
                             _stream()),
           "b200_norm_bwd")
     return dx, dw, db

@@ -117,7 +117,9 @@ int64_t b200_norm_bwd_scratch_bytes(int64_t n);
  *   (r / seq) * dx_batch_stride + (r % seq) * dx_seq_stride + (c / head_dim) * dx_head_stride + c % head_dim
  * which covers both the plain [rows, n] layout (seq = 1, head_dim = n, dx_batch_stride = n) and the
  * fused head-major (B,S,H,D) -> (B,H,S,D) store. flags: 1 = two launches (main + finalize)
- * instead of one cooperative launch.
+ * instead of one cooperative launch; 2 = dy points at ONE element that stands for the whole
+ * tensor (the reference's captured graphs expand a 0-dim gradient,
+ * sum_sum_2cd99e5eb23e/repro.py:26): dy_row_stride is ignored and nothing but that element is read.
  * Replaces sum_sum_2cd99e5eb23e/oracle.py:48-117, sum_sum_sum_3cac3bbf4e8f/oracle.py:100-193 and
  * the head-split copy of pointwise_c0d19d490a2f/oracle.py:10-33. */
 int32_t b200_norm_bwd(const void* x, const void* dy, const void* weight, const float* mean,

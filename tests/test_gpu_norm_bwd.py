@@ -145,3 +145,33 @@ def test_norm_bwd_many_narrow_rows(rows, n, dtype, ln):
     assert torch.equal(again[0], dx) and torch.equal(again[1], dw), "bit-reproducible"
     k.check_scratch_status()
     assert k.load().b200_norm_bwd_wait_timeouts() == 0
+
+
+@pytest.mark.parametrize("rows,n,dtype,ln", [(9000, 512, torch.bfloat16, False), (7000, 768, torch.bfloat16, True),
+                                             (50, 100, torch.float32, False), (300, 4096, torch.bfloat16, True),
+                                             (33, 64, torch.float16, False)])
+def test_norm_bwd_scalar_dy(rows, n, dtype, ln):
+    """dy given as ONE element (the captured graphs expand a 0-dim gradient): read as a scalar by
+    the kernels, whatever path the row length takes; same results as the materialised expansion."""
+    k = _kernels()
+    x = _rand((rows, n), dtype, 31, scale=1.5)
+    dy0 = torch.tensor(0.75, dtype=dtype)
+    dy_full = dy0.expand(rows, n)
+    w = (torch.rand(n, generator=torch.Generator().manual_seed(33)) + 0.5)
+    mean, rstd, rrms = _stats(x)
+    if ln:
+        want = _ln_reference(x, dy_full, w, mean, rstd)
+        anchor = _ln_reference(x.double(), dy_full.double(), w.double(), mean.double(), rstd.double())
+        got = k.norm_bwd(x.cuda(), dy0.cuda(), w.cuda(), rstd.cuda(), mean=mean.cuda(), rms=False, want_dbias=True)
+        via_view = k.norm_bwd(x.cuda(), dy0.cuda().expand(rows, n), w.cuda(), rstd.cuda(), mean=mean.cuda(), rms=False,
+                              want_dbias=True)
+        _close_columns(got[2], want[2], anchor[2], f"scalar-dy ln db {rows}x{n}")
+    else:
+        want = _rms_reference(x, dy_full.contiguous(), w.to(dtype), rrms)
+        anchor = _rms_reference(x.double(), dy_full.double().contiguous(), w.to(dtype).double(), rrms.double())
+        got = k.norm_bwd(x.cuda(), dy0.cuda(), w.to(dtype).cuda(), rrms.cuda(), rms=True)
+        via_view = k.norm_bwd(x.cuda(), dy0.cuda().expand(rows, n), w.to(dtype).cuda(), rrms.cuda(), rms=True)
+    assert_close(got[0], want[0], f"scalar-dy dx {rows}x{n} {dtype}")
+    _close_columns(got[1], want[1], anchor[1], f"scalar-dy dw {rows}x{n}")
+    assert torch.equal(got[0], via_view[0]) and torch.equal(got[1], via_view[1])
+    k.check_scratch_status()

@@ -130,6 +130,36 @@ def test_softmax_output_dtype_and_strided_rows():
     assert_close(got, MaskedScaledSoftmax()(base[:, 1:513]), "unaligned rows")
 
 
+@pytest.mark.parametrize("log", [False, True])
+@pytest.mark.parametrize("rows,n,stride,offset,dtype,out_dtype", [
+    (64, 20005, 20008, 0, torch.bfloat16, torch.float32),   # ragged length, aligned padded rows
+    (12, 262144, 262144, 0, torch.bfloat16, torch.bfloat16),  # rows far beyond the register-resident kernel
+    (33, 5000, 5000, 0, torch.float32, torch.float32),
+    (20, 4001, 4100, 3, torch.float16, torch.float16),     # unaligned row starts: element-wise sweeps
+    (7, 70000, 70000, 0, torch.float32, torch.bfloat16),
+])
+def test_softmax_long_and_ragged_rows(rows, n, stride, offset, dtype, out_dtype, log):
+    """Rows the register-resident kernel cannot take go through the two-sweep kernel (running maximum
+    and rescaled sum, then a second read of the row)."""
+    from oracle.eager import MaskedScaledSoftmax
+    k = _kernels()
+    base = _randn((rows, stride + offset), dtype, n % 97, scale=3.0)
+    view = base[:, offset:offset + n]
+    got = k.softmax(base.cuda()[:, offset:offset + n], log=log, out_dtype=out_dtype)
+    assert b"two sweeps" in k.load().b200_last_kernel(), k.load().b200_last_kernel()
+    want = MaskedScaledSoftmax(log=log, out_dtype=out_dtype)(view)
+    assert_close(got, want, f"long softmax log={log} {dtype}->{out_dtype} {rows}x{n}")
+    special = view.clone().float()
+    special[0, :] = float("-inf")
+    special[1, 5] = float("inf")
+    special[2, 7] = float("nan")
+    special[3, : n // 2] = float("-inf")
+    special = special.to(dtype)
+    got = k.softmax(special.cuda(), log=log, out_dtype=out_dtype)
+    want = MaskedScaledSoftmax(log=log, out_dtype=out_dtype)(special)
+    assert torch.allclose(got.float().cpu(), want.float(), equal_nan=True, atol=1e-2, rtol=1.6e-2)
+
+
 def test_softmax_fully_masked_and_inf_rows():
     k = _kernels()
     x = torch.zeros((3, 64), dtype=torch.float32)
