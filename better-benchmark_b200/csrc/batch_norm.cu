@@ -22,9 +22,9 @@
 //           the most recently read ones, which are the likeliest to still be in L2; y is written
 //           with streaming stores so that it does not push x out of L2.
 // DRAM traffic therefore approaches one read of x plus one write of y.
-// Any other layout (NCHW, channel counts that are not a multiple of the vector width) takes the
-// three-launch general path: strided statistics, finalize, strided normalise.
-#include "rowwise.cuh"
+// Contiguous NCHW tensors take the single-launch cluster kernel of batch_norm_nchw.cu. Any other
+// layout takes the three-launch general path: strided statistics, finalize, strided normalise.
+#include "batch_norm.cuh"
 #include "tile_stream.cuh"
 
 #include <cstdlib>
@@ -32,31 +32,6 @@
 #include <type_traits>
 
 namespace b200 {
-
-struct BatchNormParams {
-  const void* x;
-  void* y;
-  const void* weight;  // may be null
-  const void* bias;    // may be null
-  float* running_mean;  // may be null (no update)
-  float* running_var;
-  float* save_mean;    // [C] fp32 out (may be null)
-  float* save_invstd;  // [C] fp32 out (may be null)
-  long long rows;      // N*H*W for channels-last; N for the general path
-  int channels;
-  long long spatial;   // general path: H*W
-  long long sn, sc, ss;  // general path: element strides of (n, c, spatial)
-  int w_dtype;
-  float eps, momentum, one_minus_momentum, unbias;
-  double count;  // elements per channel
-  int relu;
-  float* partials;  // [P][2][C]
-  float* stats;     // [2][C] mean, invstd (scratch copy every CTA reads)
-  unsigned int* bar;
-  long long rows_per_cta;  // contiguous row range of each CTA
-  int smem_tiles;          // stages of the shared-memory ring
-  int local_stats;         // 1: every CTA combines all partials itself (one grid barrier instead of two)
-};
 
 template <typename T, bool VECTOR>
 __device__ __forceinline__ void bn_finalize_channel(const BatchNormParams& p, int c, int num_partials,
@@ -82,28 +57,6 @@ __device__ __forceinline__ void bn_finalize_channel(const BatchNormParams& p, in
     const float invstd = rsqrtf(varf + p.eps);
     p.stats[c] = mean;
     p.stats[p.channels + c] = invstd;
-    if (p.save_mean) p.save_mean[c] = mean;
-    if (p.save_invstd) p.save_invstd[c] = invstd;
-    if (p.running_mean) {
-      p.running_mean[c] = mean * p.momentum + p.running_mean[c] * p.one_minus_momentum;
-      p.running_var[c] = (varf * p.unbias) * p.momentum + p.running_var[c] * p.one_minus_momentum;
-    }
-  }
-}
-
-// Turns the fp64 totals of the shifted sums of one channel into mean / invstd and, for the one
-// caller that owns the channel's global outputs, writes the saved and running statistics.
-__device__ __forceinline__ void bn_channel_stats(const BatchNormParams& p, int c, double s1, double s2, float shift,
-                                                 bool write_global, float* mean_out, float* invstd_out) {
-  const double mean_shifted = s1 / p.count;
-  double var = (s2 - s1 * mean_shifted) / p.count;
-  if (var < 0.0) var = 0.0;
-  const float mean = (float)((double)shift + mean_shifted);
-  const float varf = (float)var;
-  const float invstd = rsqrtf(varf + p.eps);
-  *mean_out = mean;
-  *invstd_out = invstd;
-  if (write_global) {
     if (p.save_mean) p.save_mean[c] = mean;
     if (p.save_invstd) p.save_invstd[c] = invstd;
     if (p.running_mean) {
@@ -1097,6 +1050,10 @@ static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, size_t 
     }
     note_launch("b200_batch_norm_fwd [fused, channels-last, CTA ring]");
     return B200_OK;
+  }
+  {  // contiguous NCHW: one launch, a cluster of CTAs per channel (batch_norm_nchw.cu)
+    int rc = B200_OK;
+    if (try_launch_batch_norm_nchw<T>(p, st, &rc)) return rc;
   }
   // general path
   const long long total = p.rows * p.spatial;

@@ -20,6 +20,10 @@
 // vectors per row) take the vector kernels; every other layout the strided element-wise ones.
 #include "rowwise.cuh"
 
+#include <cooperative_groups.h>
+
+#include <cstdlib>
+
 namespace b200 {
 
 struct BnBwdParams {
@@ -311,6 +315,231 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_general_kernel(const BnBwdPa
   }
 }
 
+// ---- contiguous NCHW: one launch, a cluster of CTAs per channel ---------------------------------
+// grid (S, C), cluster (S, 1, 1): CTA (s, c) owns images [s * ipc, (s + 1) * ipc) of channel c. A
+// plane (the H*W contiguous elements of one image and channel) is walked by a group of G lanes: the
+// unaligned head and tail element by element, the body with 16-byte accesses (dy, x, act and dx
+// share the layout, hence the alignment). Pass 1 sums dy' and dy' * (x - mean); the CTA totals (fp64)
+// are exchanged through distributed shared memory after a cluster barrier and every CTA derives the
+// coefficients itself; pass 2 walks the planes backwards (what was read last is still cached) and
+// writes dx. No scratch, no atomics.
+template <typename T>
+__global__ void __launch_bounds__(256)
+bn_bwd_nchw_cluster_kernel(const BnBwdParams p, const int imgs_per_cta, const int G) {
+  namespace cg = cooperative_groups;
+  constexpr int V = Elem<T>::V;
+  constexpr int P = V / 2;
+  constexpr int U = 2;  // vectors of each tensor in flight per lane
+  __shared__ double warp_tot[8][2];
+  __shared__ double cta_tot[2];  // read by the other CTAs of the cluster
+  __shared__ float coef[2];      // c1, c2 of this channel
+  cg::cluster_group cluster = cg::this_cluster();
+  const int tid = threadIdx.x, lane = tid % G, grp = tid / G, groups = 256 / G;
+  const int c = blockIdx.y;
+  const int hw = (int)p.spatial;
+  const int n_total = (int)p.rows;
+  const int n0 = (int)blockIdx.x * imgs_per_cta;
+  const int n1 = n0 + imgs_per_cta < n_total ? n0 + imgs_per_cta : n_total;
+  const long long plane_stride = (long long)p.channels * hw;
+  const T* dyc = reinterpret_cast<const T*>(p.dy) + (long long)c * hw;
+  const T* xc = reinterpret_cast<const T*>(p.x) + (long long)c * hw;
+  const T* actc = p.act ? reinterpret_cast<const T*>(p.act) + (long long)c * hw : nullptr;
+  T* dxc = p.dx ? reinterpret_cast<T*>(p.dx) + (long long)c * hw : nullptr;
+  const float mean = __ldg(p.mean + c);
+  const f32x2 mean2 = splat2(mean);
+  const bool has_act = actc != nullptr;
+  const float slope = p.slope;
+
+  auto grad_scalar = [&](const T* dyp, const T* actp, int i) -> float {
+    float g = Elem<T>::to_f32(dyp[i]);
+    if (has_act) {
+      const float a = Elem<T>::to_f32(actp[i]);
+      g = a > 0.f ? g : g * slope;
+      g = Elem<T>::to_f32(Elem<T>::from_f32(g));  // the graph rounds dy' to the tensor dtype
+    }
+    return g;
+  };
+  // head / body / tail split of a plane (the same for every tensor: same layout, 16-byte aligned bases)
+  auto split = [&](const T* plane, int& head, int& nvec) {
+    const int mis = (int)((reinterpret_cast<uintptr_t>(plane) / sizeof(T)) & (V - 1));
+    head = mis ? V - mis : 0;
+    if (head > hw) head = hw;
+    nvec = (hw - head) / V;
+  };
+
+  // ---- pass 1 ----------------------------------------------------------------------------------
+  double d1 = 0.0, d2 = 0.0;
+  for (int n = n0 + grp; n < n1; n += groups) {
+    const long long off = (long long)n * plane_stride;
+    const T* dyp = dyc + off;
+    const T* xp = xc + off;
+    const T* ap = has_act ? actc + off : nullptr;
+    int head, nvec;
+    split(xp, head, nvec);
+    float s1 = 0.f, s2 = 0.f;
+    f32x2 a1 = splat2(0.f), a2 = splat2(0.f);
+    auto scalar = [&](int i) {
+      const float g = grad_scalar(dyp, ap, i);
+      s1 += g;
+      s2 += g * (Elem<T>::to_f32(xp[i]) - mean);
+    };
+    for (int i = lane; i < head; i += G) scalar(i);
+    for (int v0 = lane; v0 < nvec; v0 += U * G) {
+      uint4 rg[U], rx[U], ra[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * G;
+        if (v < nvec) {
+          rg[u] = ld_keep(dyp + head + v * V);
+          rx[u] = ld_keep(xp + head + v * V);
+          if (has_act) ra[u] = ld_keep(ap + head + v * V);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (v0 + u * G < nvec) {
+          f32x2 g[P], xv[P];
+          Pairs<T>::unpack(rg[u], g);
+          Pairs<T>::unpack(rx[u], xv);
+          if (has_act) bn_bwd_prologue<T>(g, ra[u], slope);
+#pragma unroll
+          for (int k = 0; k < P; ++k) {
+            a1 = add2(a1, g[k]);
+            a2 = add2(a2, mul2(g[k], sub2(xv[k], mean2)));
+          }
+        }
+      }
+    }
+    for (int i = head + nvec * V + lane; i < hw; i += G) scalar(i);
+    d1 += (double)s1 + (double)hsum2(a1);
+    d2 += (double)s2 + (double)hsum2(a2);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+    d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+  }
+  if ((tid & 31) == 0) {
+    warp_tot[tid >> 5][0] = d1;
+    warp_tot[tid >> 5][1] = d2;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    double t1 = 0.0, t2 = 0.0;
+    for (int w = 0; w < 8; ++w) {
+      t1 += warp_tot[w][0];
+      t2 += warp_tot[w][1];
+    }
+    cta_tot[0] = t1;
+    cta_tot[1] = t2;
+  }
+  cluster.sync();
+  const float invstd = __ldg(p.invstd + c);
+  const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
+  if (tid == 0) {
+    double t1 = 0.0, t2 = 0.0;
+    const unsigned int nb = cluster.num_blocks();
+    for (unsigned int r = 0; r < nb; ++r) {  // rank order: the same sums in every CTA
+      const double* remote = cluster.map_shared_rank(cta_tot, r);
+      t1 += remote[0];
+      t2 += remote[1];
+    }
+    const float sum_dy = (float)t1, dot = (float)t2;
+    if (cluster.block_rank() == 0) {
+      if (p.dbias) p.dbias[c] = sum_dy;
+      if (p.dweight) p.dweight[c] = dot * invstd;
+    }
+    coef[0] = sum_dy * p.inv_count;
+    coef[1] = (dot * p.inv_count) * (invstd * invstd);
+  }
+  cluster.sync();  // nobody leaves before its totals were read; coef[] is visible
+  if (dxc == nullptr) return;
+
+  // ---- pass 2 ----------------------------------------------------------------------------------
+  const float c1 = coef[0], c2 = coef[1], gs = invstd * w;
+  const f32x2 c1v = splat2(c1), c2v = splat2(c2), gsv = splat2(gs);
+  for (int n = n1 - 1 - grp; n >= n0; n -= groups) {
+    const long long off = (long long)n * plane_stride;
+    const T* dyp = dyc + off;
+    const T* xp = xc + off;
+    const T* ap = has_act ? actc + off : nullptr;
+    T* out = dxc + off;
+    int head, nvec;
+    split(xp, head, nvec);
+    auto scalar = [&](int i) {
+      const float g = grad_scalar(dyp, ap, i);
+      const float xv = Elem<T>::to_f32(xp[i]);
+      out[i] = Elem<T>::from_f32(((g - (xv - mean) * c2) - c1) * gs);
+    };
+    for (int i = lane; i < head; i += G) scalar(i);
+    for (int v0 = lane; v0 < nvec; v0 += U * G) {
+      uint4 rg[U], rx[U], ra[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * G;
+        if (v < nvec) {
+          rg[u] = ld_stream(dyp + head + v * V);
+          rx[u] = ld_stream(xp + head + v * V);
+          if (has_act) ra[u] = ld_stream(ap + head + v * V);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const int v = v0 + u * G;
+        if (v < nvec) {
+          f32x2 g[P], xv[P], o[P];
+          Pairs<T>::unpack(rg[u], g);
+          Pairs<T>::unpack(rx[u], xv);
+          if (has_act) bn_bwd_prologue<T>(g, ra[u], slope);
+#pragma unroll
+          for (int k = 0; k < P; ++k)
+            o[k] = mul2(sub2(sub2(g[k], mul2(sub2(xv[k], mean2), c2v)), c1v), gsv);
+          st_stream(out + head + v * V, Pairs<T>::pack(o));
+        }
+      }
+    }
+    for (int i = head + nvec * V + lane; i < hw; i += G) scalar(i);
+  }
+}
+
+template <typename T>
+static bool try_launch_bn_bwd_nchw(const BnBwdParams& p, cudaStream_t st, int* rc) {
+  static const bool off = [] {
+    const char* e = getenv("B200_BN_NO_NCHW_CLUSTER");
+    return e && e[0] == '1';
+  }();
+  if (off) return false;
+  if (p.ss != 1 || p.sc != p.spatial || p.sn != (long long)p.channels * p.spatial) return false;
+  if (p.rows < 1 || p.rows > 0x7fffffffLL || p.spatial < 1 || p.spatial > 0x3fffffffLL || p.channels > 65535) return false;
+  if (!aligned16(p.dy) || !aligned16(p.x) || (p.act && !aligned16(p.act)) || (p.dx && !aligned16(p.dx))) return false;
+  const DeviceInfo& dev = device_info();
+  int S = 1;
+  while (S < 8 && (long long)p.channels * S < 2LL * dev.sm_count && 2 * S <= p.rows) S *= 2;
+  const int ipc = (int)((p.rows + S - 1) / S);  // a CTA whose range starts beyond the last image has no planes
+  const long long plane_bytes = p.spatial * (long long)sizeof(T);
+  int G = 1;
+  while (G < 32 && plane_bytes / G > 96) G *= 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)S, (unsigned)p.channels, 1);
+  cfg.blockDim = dim3(256);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, bn_bwd_nchw_cluster_kernel<T>, p, ipc, G);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return false;
+  }
+  *rc = launch_status("b200_batch_norm_bwd [NCHW, one launch, cluster per channel, DSMEM combine]");
+  return true;
+}
+
 template <typename T>
 static int launch_bn_bwd(BnBwdParams p, bool fast, size_t scratch_bytes, cudaStream_t st) {
   constexpr int V = Elem<T>::V;
@@ -339,6 +568,10 @@ static int launch_bn_bwd(BnBwdParams p, bool fast, size_t scratch_bytes, cudaStr
     if (rc != B200_OK || !p.dx) return rc;
     bn_bwd_apply_cl_kernel<T><<<(unsigned)splits, threads, 0, st>>>(p, per);
     return launch_status("b200_batch_norm_bwd apply [channels-last, vector]");
+  }
+  {  // contiguous NCHW: one launch, a cluster of CTAs per channel
+    int rc = B200_OK;
+    if (try_launch_bn_bwd_nchw<T>(p, st, &rc)) return rc;
   }
   const long long total = p.rows * p.spatial;
   long long splits = total / 16384;

@@ -1,0 +1,227 @@
+// BatchNorm2d training forward (+ReLU, running statistics) on a contiguous NCHW tensor, in ONE
+// launch: the CTAs that share a channel form a thread-block cluster and exchange their partial
+// sums through distributed shared memory.
+//
+// Most BatchNorm points of the reference's corpus are NCHW (95 of the 121 shape points of
+// repros/canonical/var_mean_42fad1ece813/shapes.json), from 50 KB to 100 MB. Its Triton plan for
+// them is three launches (partial sums, finalize, normalise; oracle.py:11-119). Here:
+//
+//   grid (S, C), cluster (S, 1, 1): CTA (s, c) owns images [s * ipc, (s + 1) * ipc) of channel c.
+//   pass 1  every plane (the H*W contiguous elements of one image and channel) is walked by a
+//           group of G lanes (G = 1 .. 32, chosen so that a lane gets at least ~64 bytes of a
+//           plane): the unaligned head and tail of a plane element by element, its body with
+//           16-byte loads. Shifted sums S1 = sum(x - K), S2 = sum((x - K)^2), K = x[0, c, 0, 0];
+//           a lane's fp32 chain ends with its plane, everything above it is fp64.
+//   combine the CTA's fp64 totals go to its shared memory; after a cluster barrier every CTA of the
+//           cluster reads all S totals through distributed shared memory, in rank order, and
+//           derives mean / invstd itself; rank 0 writes the saved and running statistics.
+//   pass 2  the planes are walked again, LAST plane first (what pass 1 read last is what L1 / L2
+//           still hold), and y is written with the same head / body / tail split, since y has x's
+//           layout and therefore x's alignment.
+// No global scratch, no grid-wide barrier, no atomics: bit-reproducible.
+#include "batch_norm.cuh"
+
+#include <cooperative_groups.h>
+
+namespace b200 {
+
+namespace {
+
+namespace cg = cooperative_groups;
+
+constexpr int kThreads = 256;
+
+// Visits the HW elements of one plane with `G` lanes (lane = 0 .. G-1): scalar(i) for the
+// elements before the first and after the last 16-byte boundary, vec(i, raw) for the aligned
+// 16-byte vectors in between (i = element index of the vector's first element), four in flight.
+template <typename T, typename FS, typename FV>
+__device__ __forceinline__ void visit_plane(const T* plane, int hw, int lane, int G, FS&& scalar, FV&& vec) {
+  constexpr int V = Elem<T>::V;
+  const int mis = (int)((reinterpret_cast<uintptr_t>(plane) / sizeof(T)) & (V - 1));
+  int head = mis ? V - mis : 0;
+  if (head > hw) head = hw;
+  const int nvec = (hw - head) / V;
+  const int tail0 = head + nvec * V;
+  for (int i = lane; i < head; i += G) scalar(i);
+  for (int v0 = lane; v0 < nvec; v0 += 4 * G) {
+    uint4 raw[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + u * G;
+      if (v < nvec) raw[u] = ld_keep(plane + head + v * V);
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int v = v0 + u * G;
+      if (v < nvec) vec(head + v * V, raw[u]);
+    }
+  }
+  for (int i = tail0 + lane; i < hw; i += G) scalar(i);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, const int G) {
+  constexpr int V = Elem<T>::V;
+  constexpr int P = V / 2;
+  __shared__ double warp_tot[kThreads / 32][2];
+  __shared__ double cta_tot[2];   // read by the other CTAs of the cluster
+  __shared__ float stat[2];       // mean, invstd of this channel
+  cg::cluster_group cluster = cg::this_cluster();
+  const int tid = threadIdx.x, lane = tid % G, grp = tid / G, groups = kThreads / G;
+  const int c = blockIdx.y;
+  const int hw = (int)p.spatial;
+  const int n_total = (int)p.rows;
+  const int n0 = (int)blockIdx.x * imgs_per_cta;
+  const int n1 = n0 + imgs_per_cta < n_total ? n0 + imgs_per_cta : n_total;
+  const T* x = reinterpret_cast<const T*>(p.x);
+  T* y = reinterpret_cast<T*>(p.y);
+  const long long plane_stride = (long long)p.channels * hw;  // between images of one channel
+  const T* xc = x + (long long)c * hw;
+  T* yc = y + (long long)c * hw;
+  const float shift = Elem<T>::to_f32(__ldg(xc));  // the channel's first element: every CTA of the cluster reads the same one
+  const f32x2 shift2 = splat2(shift);
+
+  // ---- pass 1 ----------------------------------------------------------------------------------
+  double d1 = 0.0, d2 = 0.0;
+  for (int n = n0 + grp; n < n1; n += groups) {
+    const T* plane = xc + (long long)n * plane_stride;
+    float s1 = 0.f, s2 = 0.f;
+    f32x2 a1 = splat2(0.f), a2 = splat2(0.f);
+    visit_plane<T>(
+        plane, hw, lane, G,
+        [&](int i) {
+          const float d = Elem<T>::to_f32(plane[i]) - shift;
+          s1 += d;
+          s2 += d * d;
+        },
+        [&](int, const uint4& raw) {
+          f32x2 f[P];
+          Pairs<T>::unpack(raw, f);
+#pragma unroll
+          for (int k = 0; k < P; ++k) {
+            const f32x2 d = sub2(f[k], shift2);
+            a1 = add2(a1, d);
+            a2 = fma2(d, d, a2);
+          }
+        });
+    d1 += (double)s1 + (double)hsum2(a1);
+    d2 += (double)s2 + (double)hsum2(a2);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+    d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+  }
+  if ((tid & 31) == 0) {
+    warp_tot[tid >> 5][0] = d1;
+    warp_tot[tid >> 5][1] = d2;
+  }
+  __syncthreads();
+  if (tid == 0) {
+    double t1 = 0.0, t2 = 0.0;
+    for (int w = 0; w < kThreads / 32; ++w) {
+      t1 += warp_tot[w][0];
+      t2 += warp_tot[w][1];
+    }
+    cta_tot[0] = t1;
+    cta_tot[1] = t2;
+  }
+  cluster.sync();  // every CTA of the cluster has published its totals
+  if (tid == 0) {
+    double t1 = 0.0, t2 = 0.0;
+    const unsigned int nb = cluster.num_blocks();
+    for (unsigned int r = 0; r < nb; ++r) {  // rank order: the same sum in every CTA
+      const double* remote = cluster.map_shared_rank(cta_tot, r);
+      t1 += remote[0];
+      t2 += remote[1];
+    }
+    float mean, invstd;
+    bn_channel_stats(p, c, t1, t2, shift, cluster.block_rank() == 0, &mean, &invstd);
+    stat[0] = mean;
+    stat[1] = invstd;
+  }
+  cluster.sync();  // nobody leaves (and gives up its shared memory) before everyone has read it; stat[] is visible
+  if (p.y == nullptr) return;
+
+  // ---- pass 2 ----------------------------------------------------------------------------------
+  const float mean = stat[0], invstd = stat[1];
+  const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
+  const float b = p.bias ? load_param1(p.bias, p.w_dtype, c) : 0.f;
+  const f32x2 mean2 = splat2(mean), invstd2 = splat2(invstd), w2 = splat2(w), b2 = splat2(b);
+  const bool relu = p.relu != 0;
+  // the groups walk the CTA's images from the last to the first
+  for (int n = n1 - 1 - grp; n >= n0; n -= groups) {
+    const T* plane = xc + (long long)n * plane_stride;
+    T* out = yc + (long long)n * plane_stride;
+    visit_plane<T>(
+        plane, hw, lane, G,
+        [&](int i) {
+          float o = ((Elem<T>::to_f32(plane[i]) - mean) * invstd) * w + b;
+          if (relu) o = o < 0.f ? 0.f : o;
+          out[i] = Elem<T>::from_f32(o);
+        },
+        [&](int i, const uint4& raw) {
+          f32x2 f[P];
+          Pairs<T>::unpack(raw, f);
+#pragma unroll
+          for (int k = 0; k < P; ++k) {
+            f[k] = add2(mul2(mul2(sub2(f[k], mean2), invstd2), w2), b2);
+            if (relu) {
+              float lo, hi;
+              unpack2(f[k], lo, hi);
+              f[k] = pack2(lo < 0.f ? 0.f : lo, hi < 0.f ? 0.f : hi);
+            }
+          }
+          st_stream(out + i, Pairs<T>::pack(f));
+        });
+  }
+}
+
+}  // namespace
+
+template <typename T>
+bool try_launch_batch_norm_nchw(const BatchNormParams& p, cudaStream_t st, int* rc) {
+  static const bool off = [] {
+    const char* e = getenv("B200_BN_NO_NCHW_CLUSTER");
+    return e && e[0] == '1';
+  }();
+  if (off) return false;
+  // contiguous NCHW only: planes of `spatial` contiguous elements, channel after channel
+  if (p.ss != 1 || p.sc != p.spatial || p.sn != (long long)p.channels * p.spatial) return false;
+  if (p.rows < 1 || p.rows > 0x7fffffffLL || p.spatial < 1 || p.spatial > 0x3fffffffLL || p.channels > 65535) return false;
+  const DeviceInfo& dev = device_info();
+  // cluster size: enough CTAs to fill the machine twice over, at most 8 per channel, at most one per image
+  int S = 1;
+  while (S < 8 && (long long)p.channels * S < 2LL * dev.sm_count && 2 * S <= p.rows) S *= 2;
+  const int ipc = (int)((p.rows + S - 1) / S);  // a CTA whose range starts beyond the last image simply has no planes
+  // lanes per plane: a lane should get about 64 bytes of a plane or more
+  const long long plane_bytes = p.spatial * (long long)sizeof(T);
+  int G = 1;
+  while (G < 32 && plane_bytes / G > 96) G *= 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)S, (unsigned)p.channels, 1);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = (unsigned)S;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cudaError_t e = cudaLaunchKernelEx(&cfg, batch_norm_nchw_cluster_kernel<T>, p, ipc, G);
+  if (e != cudaSuccess) {
+    cudaGetLastError();
+    return false;  // the cluster launch was refused: the caller takes the three-launch path
+  }
+  *rc = launch_status("b200_batch_norm_fwd [NCHW, one launch, cluster per channel, DSMEM combine]");
+  return true;
+}
+
+template bool try_launch_batch_norm_nchw<float>(const BatchNormParams&, cudaStream_t, int*);
+template bool try_launch_batch_norm_nchw<__nv_bfloat16>(const BatchNormParams&, cudaStream_t, int*);
+template bool try_launch_batch_norm_nchw<__half>(const BatchNormParams&, cudaStream_t, int*);
+
+}  // namespace b200

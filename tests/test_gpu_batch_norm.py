@@ -80,3 +80,26 @@ def test_batch_norm_repeated_calls_update_running_stats_and_reproduce():
     k.batch_norm_fwd(xd, wd, bd, rm2, rv2, eps=1e-5, momentum=0.1, relu=True)
     assert not torch.equal(rm1, rm2)       # a second step moves the running statistics again
     k.check_scratch_status()
+
+
+@pytest.mark.parametrize("shape,dtype", [((64, 32, 56, 56), torch.bfloat16), ((128, 16, 35, 35), torch.float16),
+                                         ((5, 700, 7, 7), torch.bfloat16), ((40, 96, 28, 28), torch.float32),
+                                         ((3, 8, 149, 149), torch.bfloat16)])
+def test_batch_norm_nchw_cluster_kernel(shape, dtype):
+    """Contiguous NCHW takes the single-launch kernel whose CTAs of one channel form a cluster: planes
+    with unaligned starts, more CTAs than images, one and several CTAs per channel."""
+    from oracle.eager import BatchNormReluFwd
+    k = _kernels()
+    x, rm, rv, w, b = _inputs(shape, dtype, False, seed=sum(shape))
+    want = BatchNormReluFwd(1e-3, 0.1, relu=True)(x, rm.clone(), rv.clone(), w, b)
+    rm_d, rv_d = rm.cuda(), rv.cuda()
+    before = k.load().b200_launch_count()
+    y, mean, invstd = k.batch_norm_fwd(x.cuda(), w.cuda(), b.cuda(), rm_d, rv_d, eps=1e-3, momentum=0.1, relu=True)
+    assert k.load().b200_launch_count() - before == 1 and b"NCHW" in k.load().b200_last_kernel()
+    assert_close(y, want[0], f"bn nchw y {shape} {dtype}")
+    assert_close(mean, want[1], f"bn nchw mean {shape}")
+    assert_close(invstd, want[2], f"bn nchw invstd {shape}")
+    assert_close(rm_d, want[3], f"bn nchw running_mean {shape}")
+    assert_close(rv_d, want[4], f"bn nchw running_var {shape}")
+    y2, mean2, _ = k.batch_norm_fwd(x.cuda(), w.cuda(), b.cuda(), None, None, eps=1e-3, momentum=0.1, relu=True)
+    assert torch.equal(y, y2) and torch.equal(mean, mean2), "bit-reproducible"

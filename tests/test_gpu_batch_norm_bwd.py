@@ -73,3 +73,47 @@ def test_batch_norm_bwd_rejects_mismatched_layouts():
         kernels.batch_norm_bwd(dy.contiguous(), x, mean, invstd, w)
     with pytest.raises(kernels.UnsupportedLayout):
         kernels.batch_norm_bwd(dy, x, mean.double(), invstd, w)
+
+
+@pytest.mark.parametrize("shape,channels_last,dtype,slope", [
+    ((64, 40, 28, 28), True, torch.bfloat16, None),     # channels-last, 5 vectors per row (not a power of two)
+    ((128, 112, 7, 7), True, torch.bfloat16, None),     # 14 vectors per row
+    ((16, 240, 14, 14), True, torch.float16, 0.0),      # 30 vectors per row
+    ((32, 128, 16, 16), False, torch.bfloat16, 0.2),    # NCHW: one cluster of CTAs per channel
+    ((64, 24, 35, 35), False, torch.bfloat16, None),    # NCHW, planes with unaligned starts
+    ((6, 520, 7, 7), False, torch.float32, None),       # NCHW, more channels than the machine has CTA slots
+])
+def test_batch_norm_bwd_corpus_layouts(shape, channels_last, dtype, slope):
+    from better_benchmark_b200 import kernels
+    from oracle import eager
+    dy, x, act, mean, invstd, w = _case(shape, dtype, channels_last, sum(shape))
+    use_act = act if slope is not None else None
+    before = kernels.load().b200_launch_count()
+    dx, dw, db = kernels.batch_norm_bwd(dy, x, mean, invstd, w, act=use_act, slope=slope or 0.0)
+    launched = kernels.load().b200_launch_count() - before
+    name = kernels.load().b200_last_kernel()
+    if channels_last:
+        assert b"channels-last, vector" in name, name
+    else:
+        assert launched == 1 and b"NCHW" in name, name
+    module = eager.BatchNormBwd(slope=slope)
+    want_db, want_dw, want_dx = module(dy, x, mean, invstd, w, act=use_act)
+    d64 = [t.double() if t.is_floating_point() else t for t in (dy, x, mean, invstd, w)]
+    if use_act is None:
+        a_db, a_dw, _ = module(*d64)
+    else:
+        g = torch.where(act.float() > 0, dy.float(), dy.float() * slope).to(dtype).double()
+        a_db, a_dw, _ = eager.BatchNormBwd()(g, *d64[1:])
+    assert_sum_close(db, want_db, a_db, "dbias")
+    assert_sum_close(dw, want_dw, a_dw, "dweight")
+    if dtype == torch.float32:
+        scale = max(1.0, want_dx.abs().max().item())
+        assert (dx - want_dx).abs().max().item() <= 2e-5 * scale
+    else:
+        assert_close(dx, want_dx, "dx")
+    again = kernels.batch_norm_bwd(dy, x, mean, invstd, w, act=use_act, slope=slope or 0.0)
+    assert all(torch.equal(u, v) for u, v in zip((dx, dw, db), again)), "bit-reproducible"
+    # the literal 1/N of a captured graph replaces the one derived from the shape
+    half = kernels.batch_norm_bwd(dy, x, mean, invstd, w, act=use_act, slope=slope or 0.0,
+                                  inv_count=0.5 / (shape[0] * shape[2] * shape[3]))
+    assert torch.equal(half[1], dw) and not torch.equal(half[0], dx)
