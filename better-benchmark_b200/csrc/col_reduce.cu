@@ -256,6 +256,39 @@ static int launch_col_reduce(ColReduceParams p, bool vec, size_t scratch_bytes, 
       cudaGetLastError();  // the cluster launch was refused: take the two-launch path
     }
   }
+  // More than 8 splits would need a second launch to combine them. For inputs up to about the size
+  // of the L2, where a launch costs as much as the reduction itself, narrower column chunks (8
+  // vectors = 128 contiguous bytes per row instead of 32) give enough CTAs with clusters of at most
+  // 8 splits, and the reduction stays one launch.
+  if (vec && !clusters_off && splits > 8 && p.tx_log2 > 3 &&
+      (double)p.batch * (double)p.rows * (double)p.cols * sizeof(T) <= 128.0 * 1024 * 1024) {
+    const long long chunks2 = (vcols + 7) / 8;
+    const long long max_splits2 = (p.rows + 8 * 32 - 1) / (8 * 32);
+    long long cs = 8;
+    while (cs > max_splits2 && cs > 1) cs /= 2;
+    if (cs >= 2 && chunks2 * p.batch * cs >= sms && chunks2 <= 0x7fffffffLL) {
+      ColReduceParams q = p;
+      q.tx_log2 = 3;
+      q.splits = (int)cs;
+      q.rows_per_split = (p.rows + cs - 1) / cs;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)chunks2, (unsigned)cs, (unsigned)p.batch);
+      cfg.blockDim = dim3(threads);
+      cfg.dynamicSmemBytes = 0;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeClusterDimension;
+      attr[0].val.clusterDim.x = 1;
+      attr[0].val.clusterDim.y = (unsigned)cs;
+      attr[0].val.clusterDim.z = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      cudaError_t e = is_max ? cudaLaunchKernelEx(&cfg, col_reduce_kernel<T, true, true, true>, q)
+                             : cudaLaunchKernelEx(&cfg, col_reduce_kernel<T, false, true, true>, q);
+      if (e == cudaSuccess) return launch_status("b200_col_reduce [vector, narrow chunks, cluster of splits, DSMEM combine]");
+      cudaGetLastError();
+    }
+  }
   dim3 grid((unsigned)chunks, (unsigned)splits, (unsigned)p.batch);
   set_path_tag(vec ? "vector" : "element-wise");
   if (is_max) {

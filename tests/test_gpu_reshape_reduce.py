@@ -60,7 +60,8 @@ def test_col_reduce_batched_strided_rows():
 
 @pytest.mark.parametrize("op", ["sum", "mean", "amax"])
 @pytest.mark.parametrize("batch,rows,cols,dtype", [(128, 3136, 64, torch.bfloat16), (96, 784, 256, torch.float16),
-                                                   (3, 2000, 4096, torch.float32), (20, 1500, 1000, torch.float32)])
+                                                   (3, 2000, 4096, torch.float32), (20, 1500, 1000, torch.float32),
+                                                   (1, 8192, 768, torch.float32), (1, 16384, 1024, torch.bfloat16)])  # narrow chunks
 def test_col_reduce_cluster_combine(op, batch, rows, cols, dtype):
     """Shapes that split every reduction over 2, 4 or 8 CTAs: those form a thread-block cluster and
     are combined through distributed shared memory in one launch."""
