@@ -174,6 +174,67 @@ __global__ void __launch_bounds__(256) transpose16_tile_kernel(const TransposePa
   st_stream(reinterpret_cast<__half*>(o + p.P), hi);
 }
 
+// Batched transpose of SMALL matrices without conversion (a [P, C] matrix and its transpose fit in
+// shared memory; e.g. the [49, 128] and [196, 64] attention tiles of
+// repros/canonical/pointwise_021e90d9c17d/shapes.json, whose 49 rows fill a 64 x 64 tile only to
+// three quarters and whose output rows of 49 elements do not start on 16-byte boundaries). The
+// input matrix and the output matrix of one batch entry are each ONE contiguous block, so both are
+// moved with 16-byte accesses as flat arrays; the transposition is the shared-memory gather in
+// between: output element o = c * P + p comes from [p][c]. A CTA takes matrices b, b + grid, ...
+template <typename E>  // E: unsigned short (16-bit elements) or unsigned int (32-bit elements)
+__global__ void __launch_bounds__(256) transpose_small_kernel(const TransposeParams p, const int pitch) {
+  constexpr int VE = 16 / (int)sizeof(E);
+  extern __shared__ __align__(16) unsigned char small_smem[];
+  E* tile = reinterpret_cast<E*>(small_smem);  // [P][pitch]
+  const int P = (int)p.P, C = (int)p.C;
+  const int nvec = P * C / VE;
+  for (long long b = blockIdx.x; b < p.batch; b += gridDim.x) {
+    const E* src = reinterpret_cast<const E*>(p.x) + b * p.in_batch_stride;
+    E* dst = reinterpret_cast<E*>(p.y) + b * (long long)P * C;
+    for (int j = threadIdx.x; j < nvec; j += 256) {
+      const uint4 raw = ld_stream(reinterpret_cast<const float*>(src) + (size_t)j * 4);
+      const int e0 = j * VE;
+      const int r = e0 / C, c0 = e0 - r * C;  // C is a multiple of VE: the vector stays in one row
+      E* t = tile + r * pitch + c0;
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+      if constexpr (sizeof(E) == 2) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          t[2 * k] = (E)(w[k] & 0xffffu);
+          t[2 * k + 1] = (E)(w[k] >> 16);
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) t[k] = (E)w[k];
+      }
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < nvec; j += 256) {
+      int o = j * VE;
+      int c = o / P, r = o - c * P;
+      uint32_t w[4];
+      if constexpr (sizeof(E) == 2) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint32_t lo = tile[r * pitch + c];
+          if (++r == P) { r = 0; ++c; }
+          const uint32_t hi = tile[r * pitch + c];
+          if (++r == P) { r = 0; ++c; }
+          w[k] = lo | (hi << 16);
+        }
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          w[k] = tile[r * pitch + c];
+          if (++r == P) { r = 0; ++c; }
+        }
+      }
+      st_stream(reinterpret_cast<float*>(dst) + (size_t)j * 4, make_uint4(w[0], w[1], w[2], w[3]));
+    }
+    __syncthreads();  // the tile is overwritten by the next matrix
+  }
+}
+
 // Contiguous cast / scale.
 template <typename Tin, typename Tout, bool VEC>
 __global__ void __launch_bounds__(256) cast_scale_kernel(const void* x, void* y, long long n, float scale,
@@ -220,6 +281,26 @@ static int launch_permute(const PermuteParams& p, bool vec, cudaStream_t st) {
 
 template <typename Tin, typename Tout>
 static int launch_transpose(const TransposeParams& p, cudaStream_t st) {
+  if constexpr (std::is_same<Tin, Tout>::value) {
+    // small matrices that are not made of whole 64 x 64 tiles: flat 16-byte copies around a
+    // shared-memory gather
+    constexpr int VE = 16 / (int)sizeof(Tin);
+    const long long elems = p.P * p.C;
+    const bool tiles64 = sizeof(Tin) == 2 && p.P % 64 == 0 && p.C % 64 == 0;
+    if (!p.has_scale && !tiles64 && elems * (long long)sizeof(Tin) <= 32 * 1024 && p.C % VE == 0 && elems % VE == 0 &&
+        p.in_row_stride == p.C && p.in_batch_stride % VE == 0 && aligned16(p.x) && aligned16(p.y) && p.batch >= 1) {
+      const int pitch = (int)p.C + 1;
+      const size_t smem = (size_t)p.P * pitch * sizeof(Tin);
+      if (smem <= 48 * 1024) {
+        long long grid = p.batch;
+        const long long cap = (long long)device_info().sm_count * 8;
+        if (grid > cap) grid = cap;
+        if constexpr (sizeof(Tin) == 2) transpose_small_kernel<unsigned short><<<(unsigned)grid, 256, smem, st>>>(p, pitch);
+        else transpose_small_kernel<unsigned int><<<(unsigned)grid, 256, smem, st>>>(p, pitch);
+        return launch_status("b200_transpose_copy [small matrices, flat 16-byte copies]");
+      }
+    }
+  }
   dim3 grid((unsigned)((p.C + 63) / 64), (unsigned)((p.P + 63) / 64), (unsigned)p.batch);
   if constexpr (std::is_same<Tin, Tout>::value && sizeof(Tin) == 2) {
     const bool whole = p.P % 64 == 0 && p.C % 64 == 0 && !p.has_scale && p.in_row_stride % 8 == 0 &&

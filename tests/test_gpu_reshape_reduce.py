@@ -125,6 +125,20 @@ def test_transpose_last_two(dtype, shape):
     assert got.is_contiguous() and torch.equal(got, want)
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(768, 49, 128), (128, 6, 196, 64), (300, 7, 8), (5, 33, 40), (1000, 25, 64),
+                                   (9, 100, 80)])
+def test_transpose_small_matrices(dtype, shape):
+    """Batches of small matrices whose sides are no multiples of 64: flat 16-byte copies on both
+    sides with the transposition done as a shared-memory gather."""
+    k = _kernels()
+    x = _rand(shape, dtype, sum(shape))
+    nd = len(shape)
+    got = k.permute_copy(x, list(range(nd - 2)) + [nd - 1, nd - 2])
+    assert b"small matrices" in k.load().b200_last_kernel(), k.load().b200_last_kernel()
+    assert got.is_contiguous() and torch.equal(got, x.transpose(-1, -2).contiguous())
+
+
 @pytest.mark.parametrize("dims", [(3, 2, 1, 0), (1, 0, 2, 3), (0, 3, 1, 2), (2, 0, 3, 1), (0, 1, 2, 3)])
 def test_general_permutations(dims):
     x = _rand((6, 10, 12, 20), torch.bfloat16, 3)
