@@ -135,7 +135,8 @@ def test_transpose_small_matrices(dtype, shape):
     x = _rand(shape, dtype, sum(shape))
     nd = len(shape)
     got = k.permute_copy(x, list(range(nd - 2)) + [nd - 1, nd - 2])
-    assert b"small matrices" in k.load().b200_last_kernel(), k.load().b200_last_kernel()
+    if shape[-1] * shape[-2] * x.element_size() <= 32 * 1024:
+        assert b"small matrices" in k.load().b200_last_kernel(), k.load().b200_last_kernel()
     assert got.is_contiguous() and torch.equal(got, x.transpose(-1, -2).contiguous())
 
 
