@@ -436,3 +436,42 @@ class DropoutAdd(nn.Module):
             mask = aten.gt.Scalar(prims.convert_element_type.default(rand, x.dtype), self.p)
         mul_1 = aten.mul.Tensor(aten.mul.Tensor(mask, view), self.scale)
         return (mask, aten.add.Tensor(residual, mul_1))
+
+
+class CastWithTransposedAlias(nn.Module):
+    """Reference graph: repros/canonical/pointwise_8bb40810003c/repro.py:23-29. One cast; the two
+    outputs are views of the same buffer (its transpose and itself)."""
+
+    def forward(self, x):
+        c = prims.convert_element_type.default(x, torch.bfloat16)
+        t = aten.permute.default(c, [1, 0])
+        return (t, aten.permute.default(t, [1, 0]))
+
+
+class ScaleIntoHeadView(nn.Module):
+    """Reference graph: repros/canonical/pointwise_95ed2ef35da9/repro.py:23-30. The multiply runs in
+    the input dtype; the output is the permuted VIEW of its result (strided)."""
+
+    def __init__(self, scale: float = 0.125):
+        super().__init__()
+        self.scale = scale
+
+    def forward(self, x, shape3, shape4):
+        v = aten.view.default(x, shape3)
+        m = aten.mul.Tensor(v, self.scale)
+        return aten.permute.default(aten.view.default(m, shape4), [0, 2, 1, 3])
+
+
+class QkvSplitViews(nn.Module):
+    """Reference graph: repros/canonical/pointwise_1611fb0c7845/repro.py:23-37. No arithmetic: three
+    views of the input."""
+
+    def __init__(self, width: int = 768):
+        super().__init__()
+        self.width = width  # a literal of the captured graph
+
+    def forward(self, x, shape3, shape_q, shape_k, shape_v):
+        v = aten.view.default(x, shape3)
+        parts = aten.split.Tensor(v, self.width, 2)
+        return tuple(aten.permute.default(aten.view.default(part, shp), [0, 2, 1, 3])
+                     for part, shp in zip(parts, (shape_q, shape_k, shape_v)))

@@ -63,6 +63,14 @@ CASES = {
     "dropout_ln_01fbd6c1b27f": ("var_mean_01fbd6c1b27f",
                                 [[[64, 768], "bf16"], [[36], "i64"], [[2, 32, 768], "f32"], [[768], "f32"],
                                  [[768], "f32"], ["S", [2, 32, 768]], ["S", [2, 32, 768]]]),
+    # outputs that are views: values here, the aliasing structure in tests/test_gpu_aliasing.py
+    "cast_alias_8bb40810003c": ("pointwise_8bb40810003c", [[[40, 96], "f32"]]),
+    "scale_view_95ed2ef35da9": ("pointwise_95ed2ef35da9",
+                                [[[64, 96], "bf16"], ["S", [4, 16, 96]], ["S", [4, -1, 3, 32]]]),
+    # the packed width stays 3 * 768: the captured graph splits at the literal 768
+    "qkv_views_1611fb0c7845": ("pointwise_1611fb0c7845",
+                               [[[32, 2304], "bf16"], ["S", [2, 16, 2304]], ["S", [2, 16, 12, 64]],
+                                ["S", [2, 16, 12, 64]], ["S", [2, 16, 12, 64]]]),
     "dropout_add_4b076ed1ff41": ("pointwise_4b076ed1ff41",
                                  [[[48, 320], "bf16"], [[2], "i64"], [[3, 16, 320], "f32"],
                                   ["S", [3, 16, 320]], ["S", [3, 16, 320]]]),

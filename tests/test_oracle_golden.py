@@ -90,7 +90,18 @@ def golden_cases():
         mask = recorded[0] if recorded is not None else None
         return list(eager.DropoutAdd(0.1, 1)(x, seeds, residual, mask=mask))
 
+    def cast_alias(inp):
+        return list(eager.CastWithTransposedAlias()(inp[0]))
+
+    def scale_view(inp):
+        return [eager.ScaleIntoHeadView(0.125)(*inp)]
+
+    def qkv_views(inp):
+        return list(eager.QkvSplitViews(768)(*inp))
+
     return {
+        "cast_alias_8bb40810003c": cast_alias, "scale_view_95ed2ef35da9": scale_view,
+        "qkv_views_1611fb0c7845": qkv_views,
         "dropout_add_4b076ed1ff41": dropout_add,
         "dropout_ln_01fbd6c1b27f": dropout_ln,
         "dropout_rms_014afd4984e6": dropout_rms,
