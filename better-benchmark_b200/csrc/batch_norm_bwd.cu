@@ -319,17 +319,86 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_general_kernel(const BnBwdPa
 // grid (S, C), cluster (S, 1, 1): CTA (s, c) owns images [s * ipc, (s + 1) * ipc) of channel c. A
 // plane (the H*W contiguous elements of one image and channel) is walked by a group of G lanes: the
 // unaligned head and tail element by element, the body with 16-byte accesses (dy, x, act and dx
-// share the layout, hence the alignment). Pass 1 sums dy' and dy' * (x - mean); the CTA totals (fp64)
-// are exchanged through distributed shared memory after a cluster barrier and every CTA derives the
-// coefficients itself; pass 2 walks the planes backwards (what was read last is still cached) and
-// writes dx. No scratch, no atomics.
-template <typename T>
+// share the layout, hence the alignment); all loads of the head, the tail and the first four body
+// vectors of a lane are issued before any is consumed, so a small plane costs one round trip to
+// memory. Pass 1 sums dy' and dy' * (x - mean); the CTA totals (fp64) are exchanged through
+// distributed shared memory after a cluster barrier and every CTA derives the coefficients itself;
+// pass 2 walks the planes backwards (what was read last is still cached) and writes dx. No scratch,
+// no atomics.
+template <typename T, bool HAS_ACT, typename FS, typename FV>
+__device__ __forceinline__ void bn_bwd_visit_plane(const T* dyp, const T* xp, const T* ap, int hw, int lane, int G,
+                                                   float slope, FS&& scalar, FV&& vec) {
+  constexpr int V = Elem<T>::V;
+  constexpr int P = V / 2;
+  constexpr int SU = V / 2;  // head and tail hold at most V - 1 elements: V / 2 per lane when G >= 2
+  constexpr int U = 4;
+  const int mis = (int)((reinterpret_cast<uintptr_t>(xp) / sizeof(T)) & (V - 1));
+  int head = mis ? V - mis : 0;
+  if (head > hw) head = hw;
+  const int nvec = (hw - head) / V;
+  const int tail0 = head + nvec * V;
+  T sg[2 * SU], sx[2 * SU], sa[2 * SU];
+  uint4 rg[U], rx[U], ra[U];
+  auto sidx = [&](int u) { return u < SU ? lane + u * G : tail0 + lane + (u - SU) * G; };
+  auto slive = [&](int u) { return u < SU ? lane + u * G < head : tail0 + lane + (u - SU) * G < hw; };
+#pragma unroll
+  for (int u = 0; u < 2 * SU; ++u) {
+    if (slive(u)) {
+      const int i = sidx(u);
+      sg[u] = dyp[i];
+      sx[u] = xp[i];
+      if constexpr (HAS_ACT) sa[u] = ap[i];
+    }
+  }
+  auto load_batch = [&](int v0) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * G;
+      if (v < nvec) {
+        rg[u] = ld_keep(dyp + head + v * V);
+        rx[u] = ld_keep(xp + head + v * V);
+        if constexpr (HAS_ACT) ra[u] = ld_keep(ap + head + v * V);
+      }
+    }
+  };
+  auto use_batch = [&](int v0) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * G;
+      if (v < nvec) {
+        f32x2 g[P], xv[P];
+        Pairs<T>::unpack(rg[u], g);
+        Pairs<T>::unpack(rx[u], xv);
+        if constexpr (HAS_ACT) bn_bwd_prologue<T>(g, ra[u], slope);
+        vec(head + v * V, g, xv);
+      }
+    }
+  };
+  load_batch(lane);
+#pragma unroll
+  for (int u = 0; u < 2 * SU; ++u) {
+    if (slive(u)) {
+      float g = Elem<T>::to_f32(sg[u]);
+      if constexpr (HAS_ACT) {
+        g = Elem<T>::to_f32(sa[u]) > 0.f ? g : g * slope;
+        g = Elem<T>::to_f32(Elem<T>::from_f32(g));  // the graph rounds dy' to the tensor dtype
+      }
+      scalar(sidx(u), g, Elem<T>::to_f32(sx[u]));
+    }
+  }
+  use_batch(lane);
+  for (int v0 = lane + U * G; v0 < nvec; v0 += U * G) {
+    load_batch(v0);
+    use_batch(v0);
+  }
+}
+
+template <typename T, bool HAS_ACT>
 __global__ void __launch_bounds__(256)
 bn_bwd_nchw_cluster_kernel(const BnBwdParams p, const int imgs_per_cta, const int G) {
   namespace cg = cooperative_groups;
   constexpr int V = Elem<T>::V;
   constexpr int P = V / 2;
-  constexpr int U = 2;  // vectors of each tensor in flight per lane
   __shared__ double warp_tot[8][2];
   __shared__ double cta_tot[2];  // read by the other CTAs of the cluster
   __shared__ float coef[2];      // c1, c2 of this channel
@@ -343,74 +412,31 @@ bn_bwd_nchw_cluster_kernel(const BnBwdParams p, const int imgs_per_cta, const in
   const long long plane_stride = (long long)p.channels * hw;
   const T* dyc = reinterpret_cast<const T*>(p.dy) + (long long)c * hw;
   const T* xc = reinterpret_cast<const T*>(p.x) + (long long)c * hw;
-  const T* actc = p.act ? reinterpret_cast<const T*>(p.act) + (long long)c * hw : nullptr;
+  const T* actc = HAS_ACT ? reinterpret_cast<const T*>(p.act) + (long long)c * hw : nullptr;
   T* dxc = p.dx ? reinterpret_cast<T*>(p.dx) + (long long)c * hw : nullptr;
   const float mean = __ldg(p.mean + c);
   const f32x2 mean2 = splat2(mean);
-  const bool has_act = actc != nullptr;
   const float slope = p.slope;
-
-  auto grad_scalar = [&](const T* dyp, const T* actp, int i) -> float {
-    float g = Elem<T>::to_f32(dyp[i]);
-    if (has_act) {
-      const float a = Elem<T>::to_f32(actp[i]);
-      g = a > 0.f ? g : g * slope;
-      g = Elem<T>::to_f32(Elem<T>::from_f32(g));  // the graph rounds dy' to the tensor dtype
-    }
-    return g;
-  };
-  // head / body / tail split of a plane (the same for every tensor: same layout, 16-byte aligned bases)
-  auto split = [&](const T* plane, int& head, int& nvec) {
-    const int mis = (int)((reinterpret_cast<uintptr_t>(plane) / sizeof(T)) & (V - 1));
-    head = mis ? V - mis : 0;
-    if (head > hw) head = hw;
-    nvec = (hw - head) / V;
-  };
 
   // ---- pass 1 ----------------------------------------------------------------------------------
   double d1 = 0.0, d2 = 0.0;
   for (int n = n0 + grp; n < n1; n += groups) {
     const long long off = (long long)n * plane_stride;
-    const T* dyp = dyc + off;
-    const T* xp = xc + off;
-    const T* ap = has_act ? actc + off : nullptr;
-    int head, nvec;
-    split(xp, head, nvec);
     float s1 = 0.f, s2 = 0.f;
     f32x2 a1 = splat2(0.f), a2 = splat2(0.f);
-    auto scalar = [&](int i) {
-      const float g = grad_scalar(dyp, ap, i);
-      s1 += g;
-      s2 += g * (Elem<T>::to_f32(xp[i]) - mean);
-    };
-    for (int i = lane; i < head; i += G) scalar(i);
-    for (int v0 = lane; v0 < nvec; v0 += U * G) {
-      uint4 rg[U], rx[U], ra[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int v = v0 + u * G;
-        if (v < nvec) {
-          rg[u] = ld_keep(dyp + head + v * V);
-          rx[u] = ld_keep(xp + head + v * V);
-          if (has_act) ra[u] = ld_keep(ap + head + v * V);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (v0 + u * G < nvec) {
-          f32x2 g[P], xv[P];
-          Pairs<T>::unpack(rg[u], g);
-          Pairs<T>::unpack(rx[u], xv);
-          if (has_act) bn_bwd_prologue<T>(g, ra[u], slope);
+    bn_bwd_visit_plane<T, HAS_ACT>(
+        dyc + off, xc + off, HAS_ACT ? actc + off : nullptr, hw, lane, G, slope,
+        [&](int, float g, float xv) {
+          s1 += g;
+          s2 += g * (xv - mean);
+        },
+        [&](int, const f32x2 (&g)[P], const f32x2 (&xv)[P]) {
 #pragma unroll
           for (int k = 0; k < P; ++k) {
             a1 = add2(a1, g[k]);
             a2 = add2(a2, mul2(g[k], sub2(xv[k], mean2)));
           }
-        }
-      }
-    }
-    for (int i = head + nvec * V + lane; i < hw; i += G) scalar(i);
+        });
     d1 += (double)s1 + (double)hsum2(a1);
     d2 += (double)s2 + (double)hsum2(a2);
   }
@@ -460,45 +486,17 @@ bn_bwd_nchw_cluster_kernel(const BnBwdParams p, const int imgs_per_cta, const in
   const f32x2 c1v = splat2(c1), c2v = splat2(c2), gsv = splat2(gs);
   for (int n = n1 - 1 - grp; n >= n0; n -= groups) {
     const long long off = (long long)n * plane_stride;
-    const T* dyp = dyc + off;
-    const T* xp = xc + off;
-    const T* ap = has_act ? actc + off : nullptr;
     T* out = dxc + off;
-    int head, nvec;
-    split(xp, head, nvec);
-    auto scalar = [&](int i) {
-      const float g = grad_scalar(dyp, ap, i);
-      const float xv = Elem<T>::to_f32(xp[i]);
-      out[i] = Elem<T>::from_f32(((g - (xv - mean) * c2) - c1) * gs);
-    };
-    for (int i = lane; i < head; i += G) scalar(i);
-    for (int v0 = lane; v0 < nvec; v0 += U * G) {
-      uint4 rg[U], rx[U], ra[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int v = v0 + u * G;
-        if (v < nvec) {
-          rg[u] = ld_stream(dyp + head + v * V);
-          rx[u] = ld_stream(xp + head + v * V);
-          if (has_act) ra[u] = ld_stream(ap + head + v * V);
-        }
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int v = v0 + u * G;
-        if (v < nvec) {
-          f32x2 g[P], xv[P], o[P];
-          Pairs<T>::unpack(rg[u], g);
-          Pairs<T>::unpack(rx[u], xv);
-          if (has_act) bn_bwd_prologue<T>(g, ra[u], slope);
+    bn_bwd_visit_plane<T, HAS_ACT>(
+        dyc + off, xc + off, HAS_ACT ? actc + off : nullptr, hw, lane, G, slope,
+        [&](int i, float g, float xv) { out[i] = Elem<T>::from_f32(((g - (xv - mean) * c2) - c1) * gs); },
+        [&](int i, const f32x2 (&g)[P], const f32x2 (&xv)[P]) {
+          f32x2 o[P];
 #pragma unroll
           for (int k = 0; k < P; ++k)
             o[k] = mul2(sub2(sub2(g[k], mul2(sub2(xv[k], mean2), c2v)), c1v), gsv);
-          st_stream(out + head + v * V, Pairs<T>::pack(o));
-        }
-      }
-    }
-    for (int i = head + nvec * V + lane; i < hw; i += G) scalar(i);
+          st_stream(out + i, Pairs<T>::pack(o));
+        });
   }
 }
 
@@ -516,9 +514,11 @@ static bool try_launch_bn_bwd_nchw(const BnBwdParams& p, cudaStream_t st, int* r
   int S = 1;
   while (S < 8 && (long long)p.channels * S < 2LL * dev.sm_count && 2 * S <= p.rows) S *= 2;
   const int ipc = (int)((p.rows + S - 1) / S);  // a CTA whose range starts beyond the last image has no planes
-  const long long plane_bytes = p.spatial * (long long)sizeof(T);
-  int G = 1;
-  while (G < 32 && plane_bytes / G > 96) G *= 2;
+  // lanes per plane: as few as give every plane of the CTA its own group, but enough that a lane
+  // holds at most four vectors of each tensor of a plane (see batch_norm_nchw.cu)
+  const long long plane_vecs = (p.spatial * (long long)sizeof(T) + 15) / 16;
+  int G = 32;
+  while (G > 2 && 256 / (G / 2) <= 2 * ipc && plane_vecs <= 4LL * (G / 2)) G /= 2;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)S, (unsigned)p.channels, 1);
   cfg.blockDim = dim3(256);
@@ -531,7 +531,8 @@ static bool try_launch_bn_bwd_nchw(const BnBwdParams& p, cudaStream_t st, int* r
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, bn_bwd_nchw_cluster_kernel<T>, p, ipc, G);
+  cudaError_t e = p.act ? cudaLaunchKernelEx(&cfg, bn_bwd_nchw_cluster_kernel<T, true>, p, ipc, G)
+                        : cudaLaunchKernelEx(&cfg, bn_bwd_nchw_cluster_kernel<T, false>, p, ipc, G);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return false;

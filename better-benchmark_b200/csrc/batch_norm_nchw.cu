@@ -31,32 +31,57 @@ namespace cg = cooperative_groups;
 
 constexpr int kThreads = 256;
 
-// Visits the HW elements of one plane with `G` lanes (lane = 0 .. G-1): scalar(i) for the
-// elements before the first and after the last 16-byte boundary, vec(i, raw) for the aligned
-// 16-byte vectors in between (i = element index of the vector's first element), four in flight.
+// Visits the HW elements of one plane with `G` lanes (lane = 0 .. G-1, G >= 2): scalar(i, value)
+// for the elements before the first and after the last 16-byte boundary, vec(i, raw) for the
+// aligned 16-byte vectors in between (i = element index of the vector's first element). All loads
+// of the head, of the tail and of the first eight vectors of a lane are issued before any of them
+// is consumed: a small plane costs ONE round trip to memory, not one per loop iteration.
 template <typename T, typename FS, typename FV>
 __device__ __forceinline__ void visit_plane(const T* plane, int hw, int lane, int G, FS&& scalar, FV&& vec) {
   constexpr int V = Elem<T>::V;
+  constexpr int SU = V / 2;  // head and tail hold at most V - 1 elements: V / 2 per lane when G >= 2
+  constexpr int U = 8;
   const int mis = (int)((reinterpret_cast<uintptr_t>(plane) / sizeof(T)) & (V - 1));
   int head = mis ? V - mis : 0;
   if (head > hw) head = hw;
   const int nvec = (hw - head) / V;
   const int tail0 = head + nvec * V;
-  for (int i = lane; i < head; i += G) scalar(i);
-  for (int v0 = lane; v0 < nvec; v0 += 4 * G) {
-    uint4 raw[4];
+  T hs[SU], ts[SU];
+  uint4 raw[U];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+  for (int u = 0; u < SU; ++u) {
+    const int i = lane + u * G;
+    if (i < head) hs[u] = plane[i];
+    if (tail0 + i < hw) ts[u] = plane[tail0 + i];
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int v = lane + u * G;
+    if (v < nvec) raw[u] = ld_keep(plane + head + v * V);
+  }
+#pragma unroll
+  for (int u = 0; u < SU; ++u) {
+    const int i = lane + u * G;
+    if (i < head) scalar(i, Elem<T>::to_f32(hs[u]));
+    if (tail0 + i < hw) scalar(tail0 + i, Elem<T>::to_f32(ts[u]));
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int v = lane + u * G;
+    if (v < nvec) vec(head + v * V, raw[u]);
+  }
+  for (int v0 = lane + U * G; v0 < nvec; v0 += U * G) {
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
       const int v = v0 + u * G;
       if (v < nvec) raw[u] = ld_keep(plane + head + v * V);
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < U; ++u) {
       const int v = v0 + u * G;
       if (v < nvec) vec(head + v * V, raw[u]);
     }
   }
-  for (int i = tail0 + lane; i < hw; i += G) scalar(i);
 }
 
 template <typename T>
@@ -90,8 +115,8 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
     f32x2 a1 = splat2(0.f), a2 = splat2(0.f);
     visit_plane<T>(
         plane, hw, lane, G,
-        [&](int i) {
-          const float d = Elem<T>::to_f32(plane[i]) - shift;
+        [&](int, float xv) {
+          const float d = xv - shift;
           s1 += d;
           s2 += d * d;
         },
@@ -156,8 +181,8 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
     T* out = yc + (long long)n * plane_stride;
     visit_plane<T>(
         plane, hw, lane, G,
-        [&](int i) {
-          float o = ((Elem<T>::to_f32(plane[i]) - mean) * invstd) * w + b;
+        [&](int i, float xv) {
+          float o = ((xv - mean) * invstd) * w + b;
           if (relu) o = o < 0.f ? 0.f : o;
           out[i] = Elem<T>::from_f32(o);
         },
@@ -195,10 +220,13 @@ bool try_launch_batch_norm_nchw(const BatchNormParams& p, cudaStream_t st, int* 
   int S = 1;
   while (S < 8 && (long long)p.channels * S < 2LL * dev.sm_count && 2 * S <= p.rows) S *= 2;
   const int ipc = (int)((p.rows + S - 1) / S);  // a CTA whose range starts beyond the last image simply has no planes
-  // lanes per plane: a lane should get about 64 bytes of a plane or more
-  const long long plane_bytes = p.spatial * (long long)sizeof(T);
-  int G = 1;
-  while (G < 32 && plane_bytes / G > 96) G *= 2;
+  // Lanes per plane. Few lanes per plane mean many planes in flight per CTA (a group walks its
+  // planes one after the other, each a round trip to memory), many lanes mean few vectors per lane
+  // and round: as few lanes as give every plane of the CTA its own group, but enough that a lane
+  // holds at most eight vectors of a plane.
+  const long long plane_vecs = (p.spatial * (long long)sizeof(T) + 15) / 16;
+  int G = 32;
+  while (G > 2 && kThreads / (G / 2) <= 2 * ipc && plane_vecs <= 8LL * (G / 2)) G /= 2;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)S, (unsigned)p.channels, 1);
   cfg.blockDim = dim3(kThreads);

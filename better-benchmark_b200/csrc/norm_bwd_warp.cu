@@ -47,7 +47,7 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
   const int nv = p.n / V;
   const uint32_t row_bytes = (uint32_t)nv * 16u;
   const uint32_t stage_bytes = (DYS ? 1u : 2u) * row_bytes;
-  // layout: [kWarps][stages][x row | dy row] | pad to ring_bytes | mbarriers [kWarps][8] | fp32 weight [n] (LayerNorm)
+  // layout: [kWarps][stages][x row | dy row] | pad to ring_bytes | mbarriers [kWarps][8] | fp32 weight [CH][V/2][32] pairs (LayerNorm)
   unsigned char* ring = smem + (size_t)warp * stages * stage_bytes;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + ring_bytes) + warp * 8;
   float* wsm = reinterpret_cast<float*>(smem + ring_bytes + kWarps * 8 * sizeof(uint64_t));
@@ -77,16 +77,22 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
   // gradient sums per column in registers)
   f32x2 wv[LN ? 1 : CH][P];
   if constexpr (LN) {
-    for (int c = threadIdx.x; c < nv; c += blockDim.x) {
+    // layout [vector slot c][pair i][lane] of fp32 pairs: the 32 lanes of a warp read 32 consecutive
+    // 8-byte words, one shared-memory wavefront without bank conflicts
+    for (int q = threadIdx.x; q < CH * 32; q += blockDim.x) {  // q = c * 32 + lane: vector q of the row
       float wf[V];
-      if (p.w) {
-        load_param<V>(p.w, p.w_dtype, (long long)c * V, wf);
+      if (p.w && q < nv) {
+        load_param<V>(p.w, p.w_dtype, (long long)q * V, wf);
       } else {
 #pragma unroll
         for (int i = 0; i < V; ++i) wf[i] = 1.f;
       }
+      const int c = q >> 5, l = q & 31;
 #pragma unroll
-      for (int i = 0; i < V; ++i) wsm[c * V + i] = wf[i];
+      for (int i = 0; i < P; ++i) {
+        wsm[((c * P + i) * 32 + l) * 2] = wf[2 * i];
+        wsm[((c * P + i) * 32 + l) * 2 + 1] = wf[2 * i + 1];
+      }
     }
 #pragma unroll
     for (int i = 0; i < P; ++i) wv[0][i] = splat2(0.f);
@@ -128,12 +134,10 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
     for (int i = 0; i < P; ++i) acc_b[c][i] = splat2(0.f);
 
   const uint32_t ring_addr = smem_u32(ring) + (uint32_t)lane * 16u;
-  const uint32_t w_addr = smem_u32(wsm) + (uint32_t)lane * (uint32_t)(V * sizeof(float));
+  const f32x2* w_lane = reinterpret_cast<const f32x2*>(wsm) + lane;
   auto weight = [&](int c, int i) -> f32x2 {
     if constexpr (LN) {
-      f32x2 r;  // two consecutive fp32 weights of this lane's vector c
-      asm volatile("ld.shared.b64 %0, [%1];" : "=l"(r) : "r"(w_addr + (uint32_t)(c * 32 * V * sizeof(float) + i * 8)));
-      return r;
+      return w_lane[(c * P + i) * 32];
     } else {
       return wv[c][i];
     }
@@ -350,7 +354,7 @@ bool launch_warp_kernel_impl(NormBwdParams p, size_t scratch_bytes, cudaStream_t
   const DeviceInfo& dev = device_info();
   const int nv = p.n / V;
   const size_t stage_bytes = (DYS ? 1 : 2) * (size_t)nv * 16;
-  const size_t fixed = kWarps * 8 * sizeof(uint64_t) + (LN ? (size_t)p.n * sizeof(float) : 0);
+  const size_t fixed = kWarps * 8 * sizeof(uint64_t) + (LN ? (size_t)CH * 32 * V * sizeof(float) : 0);  // barriers (+ fp32 weight slots)
   // the ring doubles as the fold area [2][kWarps][n] fp32 and as the fp64 area of the finalize
   size_t floor_bytes = 2 * (size_t)kWarps * p.n * sizeof(float);
   if (floor_bytes < 16 * 64 * sizeof(double)) floor_bytes = 16 * 64 * sizeof(double);

@@ -494,6 +494,38 @@ __global__ void __launch_bounds__(1024) softmax_long_kernel(const SoftmaxParams 
   constexpr int VO = 16 / (int)sizeof(Tout);           // output elements per 16-byte store
   const bool y_vec = x_vec && (reinterpret_cast<uintptr_t>(y) & 15u) == 0 && V % VO == 0;
   const f32x2 M2 = splat2(Mf), inv2 = splat2(inv), logS2 = splat2(logS), Mraw2 = splat2(M);
+  if (!y_vec) {
+    // The output row does not start on a 16-byte boundary where the input row does (a ragged row
+    // length, another element size): vectors are formed on the OUTPUT side - up to the first
+    // boundary element by element, then 16-byte stores whose inputs are read element by element
+    // (they were read a moment ago and come from L1 / L2), then the rest.
+    int ho = (int)(((16u - (unsigned)(reinterpret_cast<uintptr_t>(y) & 15u)) & 15u) / sizeof(Tout));
+    if (ho > p.n) ho = p.n;
+    const int nout = (p.n - ho) / VO;
+    for (int i = tid; i < ho; i += T_) {
+      float t = Elem<Tin>::to_f32(x[i]);
+      if (scaled) t = t * p.scale;
+      y[i] = Elem<Tout>::from_f32(finish(t));
+    }
+    for (int j = tid; j < nout; j += T_) {
+      const int i0 = ho + j * VO;
+      float o[VO];
+#pragma unroll
+      for (int k = 0; k < VO; ++k) o[k] = Elem<Tin>::to_f32(x[i0 + k]);
+#pragma unroll
+      for (int k = 0; k < VO; ++k) {
+        if (scaled) o[k] = o[k] * p.scale;
+        o[k] = finish(o[k]);
+      }
+      store_converted<Tout, VO>(y + i0, o);
+    }
+    for (int i = ho + nout * VO + tid; i < p.n; i += T_) {
+      float t = Elem<Tin>::to_f32(x[i]);
+      if (scaled) t = t * p.scale;
+      y[i] = Elem<Tout>::from_f32(finish(t));
+    }
+    return;
+  }
   for (int j0 = tid; j0 < nvec; j0 += U * T_) {
     uint4 raw[U];
 #pragma unroll
@@ -525,18 +557,7 @@ __global__ void __launch_bounds__(1024) softmax_long_kernel(const SoftmaxParams 
             }
           }
         }
-        Tout* dst = y + (long long)j * V;
-        if (y_vec) {
-          store_pairs<Tout, V>(dst, o);
-        } else {
-#pragma unroll
-          for (int i = 0; i < P; ++i) {
-            float a, b;
-            unpack2(o[i], a, b);
-            dst[2 * i] = Elem<Tout>::from_f32(a);
-            dst[2 * i + 1] = Elem<Tout>::from_f32(b);
-          }
-        }
+        store_pairs<Tout, V>(y + (long long)j * V, o);
       }
     }
   }

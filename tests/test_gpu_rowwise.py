@@ -134,7 +134,7 @@ def test_softmax_output_dtype_and_strided_rows():
 @pytest.mark.parametrize("rows,n,stride,offset,dtype,out_dtype", [
     (64, 20005, 20008, 0, torch.bfloat16, torch.float32),   # ragged length, aligned padded rows
     (12, 262144, 262144, 0, torch.bfloat16, torch.bfloat16),  # rows far beyond the register-resident kernel
-    (33, 5000, 5000, 0, torch.float32, torch.float32),
+    (33, 5001, 5004, 0, torch.float32, torch.float32),
     (20, 4001, 4100, 3, torch.float16, torch.float16),     # unaligned row starts: element-wise sweeps
     (7, 70000, 70000, 0, torch.float32, torch.bfloat16),
 ])
