@@ -34,7 +34,24 @@ struct NormFwdParams {
   float inv_n;      // 1 / n
   float inv_denom;  // 1 / (n - correction)
   int rms;
+  int prologue;     // 0: none; 1: exact (erf) GELU of x, rounded to x's dtype, is what gets normalised
 };
+
+// Pointwise prologue of the LayerNorm regions that normalise an activation
+// (repros/canonical/var_mean_af505388b035/repro.py:27-33): (x * 0.5) * (erf(x * 0.7071067811865476) + 1)
+// in fp32, in that order, then rounded to the tensor dtype - the graph materialises the
+// activation as a 16-bit tensor before the statistics are taken.
+template <typename Tin>
+__device__ __forceinline__ float gelu_erf_rounded(float x) {
+  const float g = (x * 0.5f) * (erff(x * 0.7071067811865476f) + 1.0f);
+  return round_through<Tin>(g);
+}
+template <typename Tin>
+__device__ __forceinline__ f32x2 gelu_erf_rounded2(f32x2 v) {
+  float a, b;
+  unpack2(v, a, b);
+  return pack2(gelu_erf_rounded<Tin>(a), gelu_erf_rounded<Tin>(b));
+}
 
 // rsqrtf is the 2-ulp hardware approximation aten's CUDA rsqrt uses as well.
 __device__ __forceinline__ float precise_rsqrt(float v) { return rsqrtf(v); }
@@ -73,6 +90,12 @@ norm_fwd_resident_kernel(const NormFwdParams p) {
     }
 #pragma unroll
     for (int i = 0; i < V / 2; ++i) v[c][i] = pack2(f[2 * i], f[2 * i + 1]);
+  }
+  if (p.prologue == 1) {  // gelu(0) = 0: the padding slots stay zero
+#pragma unroll
+    for (int c = 0; c < CH; ++c)
+#pragma unroll
+      for (int i = 0; i < V / 2; ++i) v[c][i] = gelu_erf_rounded2<Tin>(v[c][i]);
   }
   if (p.rms) {
 #pragma unroll
@@ -280,6 +303,12 @@ norm_fwd_stream_kernel(const NormFwdParams p, const int stages, const int contig
         for (int i = 0; i < V / 2; ++i) v[c][i] = splat2(0.f);
       }
     }
+    if (p.prologue == 1) {  // gelu(0) = 0: the padding slots stay zero
+#pragma unroll
+      for (int c = 0; c < CH; ++c)
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) v[c][i] = gelu_erf_rounded2<Tin>(v[c][i]);
+    }
     // one short chain per slot, combined afterwards: a single chain over the whole row would
     // serialise on the add latency
     f32x2 part[CH];
@@ -460,9 +489,13 @@ __global__ void __launch_bounds__(1024) norm_fwd_streaming_kernel(const NormFwdP
   const long long row = blockIdx.x;
   const Tin* x = reinterpret_cast<const Tin*>(p.x) + row * p.x_row_stride;
 
+  auto value = [&](long long i) {
+    const float f = Elem<Tin>::to_f32(x[i]);
+    return p.prologue == 1 ? gelu_erf_rounded<Tin>(f) : f;
+  };
   float s = 0.f;
   for (long long i = threadIdx.x; i < p.n; i += blockDim.x) {
-    const float f = Elem<Tin>::to_f32(x[i]);
+    const float f = value(i);
     s += p.rms ? f * f : f;
   }
   s = block_reduce<SumOp>(s, red);
@@ -473,7 +506,7 @@ __global__ void __launch_bounds__(1024) norm_fwd_streaming_kernel(const NormFwdP
     mean = s * p.inv_n;
     float q = 0.f;
     for (long long i = threadIdx.x; i < p.n; i += blockDim.x) {
-      const float d = Elem<Tin>::to_f32(x[i]) - mean;
+      const float d = value(i) - mean;
       q += d * d;
     }
     q = block_reduce<SumOp>(q, red);
@@ -488,7 +521,7 @@ __global__ void __launch_bounds__(1024) norm_fwd_streaming_kernel(const NormFwdP
   if (p.y == nullptr) return;
   Tout* y = reinterpret_cast<Tout*>(p.y) + row * p.y_row_stride;
   for (long long i = threadIdx.x; i < p.n; i += blockDim.x) {
-    float o = (Elem<Tin>::to_f32(x[i]) - mean) * rstd;
+    float o = (value(i) - mean) * rstd;
     if (p.w) o = o * load_param1(p.w, p.w_dtype, i);
     if (p.b) o = o + load_param1(p.b, p.w_dtype, i);
     y[i] = Elem<Tout>::from_f32(o);
@@ -560,7 +593,8 @@ extern "C" int b200_norm_fwd(const void* x, const void* weight, const void* bias
   p.mean_out = mean_out; p.rstd_out = rstd_out; p.var_out = var_out;
   p.rows = rows; p.n = (int)n;
   p.x_row_stride = x_row_stride; p.y_row_stride = y_row_stride;
-  p.w_dtype = w_dtype; p.eps = (float)eps; p.rms = rms ? 1 : 0;
+  p.w_dtype = w_dtype; p.eps = (float)eps; p.rms = (rms & 1) ? 1 : 0;
+  p.prologue = (rms & 2) ? 1 : 0;  // bit 1 of the mode word: exact GELU of x, rounded to x's dtype, first
   p.inv_n = (float)(1.0 / (double)n);
   p.inv_denom = (float)(1.0 / ((double)n - correction));  // inf/NaN for n <= correction, as aten
 

@@ -198,6 +198,9 @@ def softmax(x: torch.Tensor, *, mask: torch.Tensor | None = None, scale: float |
     return out
 
 
+_NORM_PROLOGUES = {None: 0, "gelu_erf": 2}
+
+
 def _rows_2d(t: torch.Tensor, what: str):
     """View a tensor as [rows, n] with one uniform row stride; no copy."""
     n = t.shape[-1]
@@ -214,8 +217,12 @@ def _rows_2d(t: torch.Tensor, what: str):
 def norm_fwd(x: torch.Tensor, weight: torch.Tensor | None, bias: torch.Tensor | None, *,
              eps: float, rms: bool = False, out_dtype: torch.dtype | None = None,
              want_y: bool = True, want_mean: bool = False, want_rstd: bool = False,
-             want_var: bool = False, correction: float = 0.0, keepdim: bool = True):
+             want_var: bool = False, correction: float = 0.0, keepdim: bool = True,
+             prologue: str | None = None):
     """LayerNorm (rms=False) or RMSNorm (rms=True) forward over the last dimension.
+
+    ``prologue="gelu_erf"`` normalises ``gelu(x)`` (exact, erf form) rounded to x's dtype instead
+    of x: the activation that the graph materialises in front of the norm is fused into the load.
 
     Returns (y, mean, rstd, var) with None for the outputs not requested. Statistics are fp32 with
     x's outer shape (plus a trailing 1 when ``keepdim``).
@@ -244,8 +251,8 @@ def norm_fwd(x: torch.Tensor, weight: torch.Tensor | None, bias: torch.Tensor | 
     lib = load()
     check(lib.b200_norm_fwd(_ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _ptr(mean), _ptr(rstd),
                             _ptr(var), rows, n, x_stride, y_stride, _code(x), w_code,
-                            _DTYPE_CODE[out_dtype], float(eps), float(correction), 1 if rms else 0,
-                            _stream()),
+                            _DTYPE_CODE[out_dtype], float(eps), float(correction),
+                            (1 if rms else 0) | _NORM_PROLOGUES[prologue], _stream()),
           "b200_norm_fwd")
     return y, mean, rstd, var
 

@@ -52,7 +52,7 @@ DIR_FILES = ("repro.py", "oracle.py", "shapes.json", "shapes.txt", "meta.json")
 
 # Directories without a stub here that are still worth timing: the nearest corpus points of the
 # benchmark configurations (the reference's Triton oracle and torch.compile only).
-EXTRA_REFERENCE_DIRS = ("var_mean_af505388b035",)
+EXTRA_REFERENCE_DIRS = ()
 
 
 def stub_ids() -> list:

@@ -93,7 +93,9 @@ int32_t b200_softmax(const void* x, const void* mask, void* y, int64_t rows, int
 
 /* LayerNorm (rms = 0) / RMSNorm (rms = 1) forward over the last dimension; also row var_mean
  * (y = NULL). weight, bias, y, mean_out, rstd_out, var_out may each be NULL; statistics are fp32
- * [rows]. var uses the divisor n - correction.
+ * [rows]. var uses the divisor n - correction. Adding 2 to rms puts the exact (erf) GELU in front:
+ * the rows that are normalised are gelu(x) rounded to x's dtype, as the graph of
+ * var_mean_af505388b035/repro.py:27-33 materialises them.
  * Replaces var_mean_f8ec553e339e/oracle.py:50-84, var_mean_af505388b035/oracle.py:11-40,
  * var_mean_f7906a6c6957/oracle.py:14-50, mean_f667cd8901af/oracle.py:36-72. */
 int32_t b200_norm_fwd(const void* x, const void* weight, const void* bias, void* y, float* mean_out,

@@ -475,3 +475,23 @@ class QkvSplitViews(nn.Module):
         parts = aten.split.Tensor(v, self.width, 2)
         return tuple(aten.permute.default(aten.view.default(part, shp), [0, 2, 1, 3])
                      for part, shp in zip(parts, (shape_q, shape_k, shape_v)))
+
+
+class GeluLayerNormFwd(nn.Module):
+    """Reference graph: repros/canonical/var_mean_af505388b035/repro.py:23-46. Exact GELU in fp32,
+    rounded to the input dtype (the graph materialises the activation), then LayerNorm; y only."""
+
+    def __init__(self, eps: float = 1e-12):
+        super().__init__()
+        self.eps = eps
+
+    def forward(self, x, weight, bias):
+        xf = _f32(x)
+        mul = aten.mul.Tensor(xf, 0.5)
+        erf = aten.erf.default(aten.mul.Tensor(xf, 0.7071067811865476))
+        act = prims.convert_element_type.default(aten.mul.Tensor(mul, aten.add.Tensor(erf, 1)), x.dtype)
+        af = _f32(act)
+        var_mean = aten.var_mean.correction(af, [-1], correction=0, keepdim=True)
+        rstd = aten.rsqrt.default(aten.add.Tensor(var_mean[0], self.eps))
+        out = aten.add.Tensor(aten.mul.Tensor(aten.mul.Tensor(aten.sub.Tensor(af, var_mean[1]), rstd), weight), bias)
+        return prims.convert_element_type.default(out, x.dtype)

@@ -63,6 +63,8 @@ CASES = {
     "dropout_ln_01fbd6c1b27f": ("var_mean_01fbd6c1b27f",
                                 [[[64, 768], "bf16"], [[36], "i64"], [[2, 32, 768], "f32"], [[768], "f32"],
                                  [[768], "f32"], ["S", [2, 32, 768]], ["S", [2, 32, 768]]]),
+    "gelu_ln_af505388b035": ("var_mean_af505388b035",
+                             [[[96, 768], "bf16"], [[768], "bf16"], [[768], "bf16"], ["S", [4, 24, 768]], ["S", [96, 768]]]),
     # outputs that are views: values here, the aliasing structure in tests/test_gpu_aliasing.py
     "cast_alias_8bb40810003c": ("pointwise_8bb40810003c", [[[40, 96], "f32"]]),
     "scale_view_95ed2ef35da9": ("pointwise_95ed2ef35da9",

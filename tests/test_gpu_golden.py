@@ -25,7 +25,7 @@ FIXTURE_DIR = {
     "bn_bwd_leaky_12fc8ebf8180": "sum_sum_12fc8ebf8180", "dropout_rms_014afd4984e6": "mean_014afd4984e6",
     "dropout_ln_01fbd6c1b27f": "var_mean_01fbd6c1b27f", "dropout_add_4b076ed1ff41": "pointwise_4b076ed1ff41",
     "cast_alias_8bb40810003c": "pointwise_8bb40810003c", "scale_view_95ed2ef35da9": "pointwise_95ed2ef35da9",
-    "qkv_views_1611fb0c7845": "pointwise_1611fb0c7845",
+    "qkv_views_1611fb0c7845": "pointwise_1611fb0c7845", "gelu_ln_af505388b035": "var_mean_af505388b035",
 }
 # regions that draw random numbers: output index -> mask index it depends on element by element
 STOCHASTIC = {"dropout_rms_014afd4984e6": {"masks": (0, 3), "elementwise": {1: 0}},

@@ -270,3 +270,17 @@ def test_compensated_exponential_accuracy_against_fp64():
     want = torch.softmax(x.double(), -1)
     rel = ((got.double() - want).abs() / want).max().item()
     assert rel <= 2 ** -8, rel        # half a bf16 ulp is 2^-9 relative; the exponential adds ~3e-7
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,n", [(300, 768), (64, 128), (8, 5000), (5, 1001), (20000, 768), (4096, 1536)])
+def test_gelu_prologue_layer_norm_matches_eager(rows, n, dtype):
+    """Exact GELU, rounded to the tensor dtype, fused into the load of the LayerNorm kernels."""
+    from oracle.eager import GeluLayerNormFwd
+    x = _randn((rows, n), dtype, seed=n, scale=1.5)
+    g = torch.Generator().manual_seed(1)
+    w = (torch.rand(n, generator=g) + 0.5).to(dtype)
+    b = (0.1 * torch.randn(n, generator=g)).to(dtype)
+    want = GeluLayerNormFwd(1e-12)(x, w, b)
+    y, _, _, _ = _kernels().norm_fwd(x.cuda(), w.cuda(), b.cuda(), eps=1e-12, prologue="gelu_erf")
+    assert_close(y, want, f"gelu + layer norm {rows}x{n} {dtype}")

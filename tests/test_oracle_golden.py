@@ -90,6 +90,10 @@ def golden_cases():
         mask = recorded[0] if recorded is not None else None
         return list(eager.DropoutAdd(0.1, 1)(x, seeds, residual, mask=mask))
 
+    def gelu_ln(inp):
+        x, w, b, s0, s1 = inp
+        return [eager.GeluLayerNormFwd(1e-12)(x.view(s0), w, b).view(s1)]
+
     def cast_alias(inp):
         return list(eager.CastWithTransposedAlias()(inp[0]))
 
@@ -101,7 +105,7 @@ def golden_cases():
 
     return {
         "cast_alias_8bb40810003c": cast_alias, "scale_view_95ed2ef35da9": scale_view,
-        "qkv_views_1611fb0c7845": qkv_views,
+        "qkv_views_1611fb0c7845": qkv_views, "gelu_ln_af505388b035": gelu_ln,
         "dropout_add_4b076ed1ff41": dropout_add,
         "dropout_ln_01fbd6c1b27f": dropout_ln,
         "dropout_rms_014afd4984e6": dropout_rms,
