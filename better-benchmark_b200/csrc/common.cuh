@@ -159,9 +159,18 @@ struct Elem<__half> {
 // ----------------------------------------------------------------------------------------
 __device__ __forceinline__ uint4 ld_stream(const void* p) {
   uint4 r;
+#ifdef B200_LD_STREAM_L2_EVICT_FIRST
+  // build variant for measurements: read-once data is also the first candidate for eviction from L2
+  uint64_t pol;
+  asm("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.v4.u32 {%0,%1,%2,%3}, [%4], %5;"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+               : "l"(p), "l"(pol));
+#else
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
                : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
                : "l"(p));
+#endif
   return r;
 }
 

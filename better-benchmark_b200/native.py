@@ -11,7 +11,10 @@ import threading
 from ctypes import c_char_p, c_double, c_int32, c_int64, c_void_p
 from pathlib import Path
 
-LIB_PATH = Path(__file__).resolve().parent / "csrc" / "libb200_oracles.so"
+import os
+
+# B200_ORACLES_LIB names another build of the library (a measurement variant); default: the in-tree one
+LIB_PATH = Path(os.environ.get("B200_ORACLES_LIB") or Path(__file__).resolve().parent / "csrc" / "libb200_oracles.so")
 
 # dtype codes shared with csrc/common.cuh
 F32, BF16, F16 = 0, 1, 2

@@ -27,6 +27,7 @@ it after a crash or a time-out and goes on with the next task, so one bad point 
     python -m better_benchmark_b200.reference_arm check   --out results.jsonl
     python -m better_benchmark_b200.reference_arm compare --out results.jsonl --max-points 2
     python -m better_benchmark_b200.reference_arm report  results.jsonl > table.md
+    python -m better_benchmark_b200.reference_arm tree --workdir /tmp/tree     # directories for the sweep
 """
 from __future__ import annotations
 
@@ -117,6 +118,23 @@ def assemble_b200_dirs(ref_root: Path, out_root: Path) -> dict:
                 shutil.copyfile(f, d / f.name)
         made[name] = d
     return made
+
+
+def build_sweep_tree(ref_root: Path, out_root: Path) -> dict:
+    """A directory tree for ``python -m better_benchmark_b200.sweep``: this backend's directories
+    (see assemble_b200_dirs) under ``out_root/canonical`` and, under ``out_root/support``, links to
+    the three reference modules a staged ``repro.py`` imports (repro_harness, byte_accounting,
+    input_codec) - but not to oracle_harness, so that the stubs register with this package's
+    harness, which is the one the sweep's workers dispatch through. Put ``support`` on PYTHONPATH."""
+    dirs = assemble_b200_dirs(ref_root, out_root / "canonical")
+    support = out_root / "support"
+    support.mkdir(parents=True, exist_ok=True)
+    for name in ("repro_harness.py", "byte_accounting.py", "input_codec.py"):
+        target = support / name
+        if target.exists() or target.is_symlink():
+            target.unlink()
+        shutil.copyfile(ref_root / name, target)
+    return {"canonical": str(out_root / "canonical"), "pythonpath": str(support), "directories": len(dirs)}
 
 
 def _import_reference(ref_root: Path):
@@ -408,7 +426,7 @@ def report(paths, peak_gbps=None) -> str:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="python -m better_benchmark_b200.reference_arm")
-    ap.add_argument("mode", choices=["stage", "check", "compare", "report", "tasks"])
+    ap.add_argument("mode", choices=["stage", "check", "compare", "report", "tasks", "tree"])
     ap.add_argument("inputs", nargs="*", help="report: result files")
     ap.add_argument("--child", action="store_true", help="internal: run the tasks in this process")
     ap.add_argument("--reference", default="/root/reference", help="stage: the reference checkout")
@@ -426,6 +444,9 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     if args.mode == "stage":
         print(json.dumps(stage(Path(args.reference), Path(args.ref)), indent=1))
+        return 0
+    if args.mode == "tree":
+        print(json.dumps(build_sweep_tree(Path(args.ref), Path(args.workdir))))
         return 0
     if args.mode == "report":
         print(report(args.inputs))
