@@ -112,6 +112,46 @@ def _cast_inputs(device="cuda", seed=1):
     return [_randn((64 << 20,), torch.bfloat16, seed, device)]
 
 
+def _softmax_long_inputs(device="cuda", seed=1):
+    return [_randn((1024, 131072), torch.bfloat16, seed, device)]
+
+
+def _log_softmax_ragged_inputs(device="cuda", seed=1):
+    return [_randn((4096, 20008), torch.bfloat16, seed, device)]  # the softmax runs over the first 20005 columns
+
+
+def _bn_nchw_inputs(device="cuda", seed=1):
+    c = 128
+    return [_randn((128, c, 56, 56), torch.bfloat16, seed, device), torch.zeros(c, device=device),
+            torch.ones(c, device=device), (torch.rand(c, generator=_gen(seed)) + 0.5).to(device),
+            (torch.rand(c, generator=_gen(seed + 1)) - 0.5).to(device)]
+
+
+def _bn_bwd_nchw_inputs(device="cuda", seed=1):
+    shape = (128, 128, 56, 56)
+    x = _randn(shape, torch.bfloat16, seed, device)
+    dy = _randn(shape, torch.bfloat16, seed + 100, device)
+    return [dy, x, torch.zeros(128, device=device), torch.ones(128, device=device),
+            (torch.rand(128, generator=_gen(seed)) + 0.5).to(device)]
+
+
+def _gelu_ln_inputs(device="cuda", seed=1):
+    return [_randn((65536, 768), torch.bfloat16, seed, device),
+            (torch.rand(768, generator=_gen(seed)) + 0.5).to(torch.bfloat16).to(device),
+            (torch.rand(768, generator=_gen(seed + 1)) - 0.5).to(torch.bfloat16).to(device)]
+
+
+def _rms_bwd_scalar_inputs(device="cuda", seed=1):
+    x = _randn((262144, 512), torch.bfloat16, seed, device)
+    rstd = torch.rsqrt(x.float().pow(2).mean(dim=1) + 1e-6)
+    return [x, torch.tensor(0.75, dtype=torch.bfloat16, device=device),
+            (torch.rand(512, generator=_gen(seed)) + 0.5).to(device), rstd]
+
+
+def _transpose_small_inputs(device="cuda", seed=1):
+    return [_randn((16384, 49, 128), torch.bfloat16, seed, device), [16384, 128, 49]]
+
+
 MB = 1 << 20
 FAMILY_CASES = {c.name: c for c in [
     _case("col_sum_f32", "column sum: x f32 [16384, 4096] -> f32 [4096]", "f32",
@@ -151,4 +191,22 @@ FAMILY_CASES = {c.name: c for c in [
           2 * 64 * 1024 * 768 * 2, _transpose_inputs, lambda i: permute.transpose_forward(i)),
     _case("cast_bf16_f32", "cast bf16 -> f32, 64 Mi elements", "bf16",
           (64 << 20) * 6, _cast_inputs, lambda i: kernels.cast_scale(i[0], torch.float32)),
+    _case("softmax_long_rows_bf16", "softmax over rows of 131072: x bf16 [1024, 131072] -> bf16", "bf16",
+          2 * 1024 * 131072 * 2, _softmax_long_inputs, lambda i: kernels.softmax(i[0])),
+    _case("log_softmax_ragged_bf16_f32", "log_softmax over 20005 of 20008 columns: x bf16 [4096, 20005] -> f32", "bf16",
+          4096 * 20005 * (2 + 4), _log_softmax_ragged_inputs,
+          lambda i: kernels.softmax(i[0][:, :20005], log=True, out_dtype=torch.float32)),
+    _case("batch_norm_relu_nchw_bf16", "BatchNorm2d train fwd + ReLU: x bf16 NCHW [128,128,56,56]", "bf16",
+          2 * 128 * 128 * 3136 * 2 + 6 * 128 * 4, _bn_nchw_inputs,
+          lambda i: kernels.batch_norm_fwd(i[0], i[3], i[4], i[1], i[2], eps=1e-3, momentum=0.1, relu=True)),
+    _case("batch_norm_bwd_nchw_bf16", "BatchNorm backward: dy, x bf16 NCHW [128,128,56,56] -> dx, dweight, dbias", "bf16",
+          3 * 128 * 128 * 3136 * 2 + 5 * 128 * 4, _bn_bwd_nchw_inputs, lambda i: batch_norm_bwd.oracle_forward(i)),
+    _case("gelu_layer_norm_bf16", "exact GELU -> bf16 -> LayerNorm: x bf16 [65536, 768], w/b bf16 -> y bf16", "bf16",
+          2 * 65536 * 768 * 2 + 2 * 768 * 2, _gelu_ln_inputs,
+          lambda i: kernels.norm_fwd(i[0], i[1], i[2], eps=1e-12, prologue="gelu_erf")[0]),
+    _case("rms_norm_bwd_scalar_dy_bf16", "RMSNorm backward, dy a broadcast scalar: x bf16 [262144, 512] -> dx bf16, dweight f32",
+          "bf16", 2 * 262144 * 512 * 2 + 262144 * 4 + 2 * 512 * 4, _rms_bwd_scalar_inputs,
+          lambda i: kernels.norm_bwd(i[0], i[1], i[2], i[3], rms=True)),
+    _case("transpose_small_bf16", "[16384, 49, 128] -> [16384, 128, 49] contiguous copy, bf16", "bf16",
+          2 * 16384 * 49 * 128 * 2, _transpose_small_inputs, lambda i: permute.transpose_forward(i)),
 ]}
