@@ -23,6 +23,8 @@
 
 #include <cooperative_groups.h>
 
+#include <cstdlib>
+
 namespace b200 {
 
 namespace {
@@ -84,7 +86,8 @@ __device__ __forceinline__ void visit_plane(const T* plane, int hw, int lane, in
   }
 }
 
-template <typename T>
+// CLUSTER false: one CTA per channel, launched without a cluster (grid (1, C)).
+template <typename T, bool CLUSTER>
 __global__ void __launch_bounds__(kThreads)
 batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, const int G) {
   constexpr int V = Elem<T>::V;
@@ -92,7 +95,6 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
   __shared__ double warp_tot[kThreads / 32][2];
   __shared__ double cta_tot[2];   // read by the other CTAs of the cluster
   __shared__ float stat[2];       // mean, invstd of this channel
-  cg::cluster_group cluster = cg::this_cluster();
   const int tid = threadIdx.x, lane = tid % G, grp = tid / G, groups = kThreads / G;
   const int c = blockIdx.y;
   const int hw = (int)p.spatial;
@@ -152,21 +154,32 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
     cta_tot[0] = t1;
     cta_tot[1] = t2;
   }
-  cluster.sync();  // every CTA of the cluster has published its totals
-  if (tid == 0) {
-    double t1 = 0.0, t2 = 0.0;
-    const unsigned int nb = cluster.num_blocks();
-    for (unsigned int r = 0; r < nb; ++r) {  // rank order: the same sum in every CTA
-      const double* remote = cluster.map_shared_rank(cta_tot, r);
-      t1 += remote[0];
-      t2 += remote[1];
+  if constexpr (CLUSTER) {
+    cg::cluster_group cluster = cg::this_cluster();
+    cluster.sync();  // every CTA of the cluster has published its totals
+    if (tid == 0) {
+      double t1 = 0.0, t2 = 0.0;
+      const unsigned int nb = cluster.num_blocks();
+      for (unsigned int r = 0; r < nb; ++r) {  // rank order: the same sum in every CTA
+        const double* remote = cluster.map_shared_rank(cta_tot, r);
+        t1 += remote[0];
+        t2 += remote[1];
+      }
+      float mean, invstd;
+      bn_channel_stats(p, c, t1, t2, shift, cluster.block_rank() == 0, &mean, &invstd);
+      stat[0] = mean;
+      stat[1] = invstd;
     }
-    float mean, invstd;
-    bn_channel_stats(p, c, t1, t2, shift, cluster.block_rank() == 0, &mean, &invstd);
-    stat[0] = mean;
-    stat[1] = invstd;
+    cluster.sync();  // nobody leaves (and gives up its shared memory) before everyone has read it; stat[] is visible
+  } else {
+    if (tid == 0) {
+      float mean, invstd;
+      bn_channel_stats(p, c, cta_tot[0], cta_tot[1], shift, true, &mean, &invstd);
+      stat[0] = mean;
+      stat[1] = invstd;
+    }
+    __syncthreads();
   }
-  cluster.sync();  // nobody leaves (and gives up its shared memory) before everyone has read it; stat[] is visible
   if (p.y == nullptr) return;
 
   // ---- pass 2 ----------------------------------------------------------------------------------
@@ -177,6 +190,95 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
   const bool relu = p.relu != 0;
   // the groups walk the CTA's images from the last to the first
   for (int n = n1 - 1 - grp; n >= n0; n -= groups) {
+    const T* plane = xc + (long long)n * plane_stride;
+    T* out = yc + (long long)n * plane_stride;
+    visit_plane<T>(
+        plane, hw, lane, G,
+        [&](int i, float xv) {
+          float o = ((xv - mean) * invstd) * w + b;
+          if (relu) o = o < 0.f ? 0.f : o;
+          out[i] = Elem<T>::from_f32(o);
+        },
+        [&](int i, const uint4& raw) {
+          f32x2 f[P];
+          Pairs<T>::unpack(raw, f);
+#pragma unroll
+          for (int k = 0; k < P; ++k) {
+            f[k] = add2(mul2(mul2(sub2(f[k], mean2), invstd2), w2), b2);
+            if (relu) {
+              float lo, hi;
+              unpack2(f[k], lo, hi);
+              f[k] = pack2(lo < 0.f ? 0.f : lo, hi < 0.f ? 0.f : hi);
+            }
+          }
+          st_stream(out + i, Pairs<T>::pack(f));
+        });
+  }
+}
+
+// Channels with little data (a few thousand elements over all images): a WARP per channel, eight
+// channels per CTA, no shared memory and no barrier at all. With a CTA per channel such a tensor
+// (hundreds of channels of a few hundred bytes each) is a grid of hundreds of CTAs that each wait
+// for three round trips to memory; here it is a fraction of a wave. Groups of G lanes walk the
+// planes of the channel side by side; the warp combines with shuffles (fp64, fixed order).
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+batch_norm_nchw_warp_kernel(const BatchNormParams p, const int G) {
+  constexpr int V = Elem<T>::V;
+  constexpr int P = V / 2;
+  const int lane32 = threadIdx.x & 31;
+  const int c = (int)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  if (c >= p.channels) return;  // whole warps leave; nothing below synchronises across warps
+  const int lane = lane32 % G, grp = lane32 / G, groups = 32 / G;
+  const int hw = (int)p.spatial;
+  const int n_total = (int)p.rows;
+  const long long plane_stride = (long long)p.channels * hw;
+  const T* xc = reinterpret_cast<const T*>(p.x) + (long long)c * hw;
+  T* yc = reinterpret_cast<T*>(p.y) + (long long)c * hw;
+  const float shift = Elem<T>::to_f32(__ldg(xc));
+  const f32x2 shift2 = splat2(shift);
+
+  double d1 = 0.0, d2 = 0.0;
+  for (int n = grp; n < n_total; n += groups) {
+    const T* plane = xc + (long long)n * plane_stride;
+    float s1 = 0.f, s2 = 0.f;
+    f32x2 a1 = splat2(0.f), a2 = splat2(0.f);
+    visit_plane<T>(
+        plane, hw, lane, G,
+        [&](int, float xv) {
+          const float d = xv - shift;
+          s1 += d;
+          s2 += d * d;
+        },
+        [&](int, const uint4& raw) {
+          f32x2 f[P];
+          Pairs<T>::unpack(raw, f);
+#pragma unroll
+          for (int k = 0; k < P; ++k) {
+            const f32x2 d = sub2(f[k], shift2);
+            a1 = add2(a1, d);
+            a2 = fma2(d, d, a2);
+          }
+        });
+    d1 += (double)s1 + (double)hsum2(a1);
+    d2 += (double)s2 + (double)hsum2(a2);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+    d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+  }
+  float mean = 0.f, invstd = 0.f;
+  if (lane32 == 0) bn_channel_stats(p, c, d1, d2, shift, true, &mean, &invstd);
+  mean = __shfl_sync(0xffffffffu, mean, 0);
+  invstd = __shfl_sync(0xffffffffu, invstd, 0);
+  if (p.y == nullptr) return;
+
+  const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
+  const float b = p.bias ? load_param1(p.bias, p.w_dtype, c) : 0.f;
+  const f32x2 mean2 = splat2(mean), invstd2 = splat2(invstd), w2 = splat2(w), b2 = splat2(b);
+  const bool relu = p.relu != 0;
+  for (int n = n_total - 1 - grp; n >= 0; n -= groups) {
     const T* plane = xc + (long long)n * plane_stride;
     T* out = yc + (long long)n * plane_stride;
     visit_plane<T>(
@@ -216,17 +318,41 @@ bool try_launch_batch_norm_nchw(const BatchNormParams& p, cudaStream_t st, int* 
   if (p.ss != 1 || p.sc != p.spatial || p.sn != (long long)p.channels * p.spatial) return false;
   if (p.rows < 1 || p.rows > 0x7fffffffLL || p.spatial < 1 || p.spatial > 0x3fffffffLL || p.channels > 65535) return false;
   const DeviceInfo& dev = device_info();
+  const long long plane_vecs = (p.spatial * (long long)sizeof(T) + 15) / 16;
+  // little data per channel and enough channels: a warp per channel
+  // measurement switch: B200_BN_NCHW_FORCE=warp|cta|cluster picks the variant whatever the shape
+  static const int force = [] {
+    const char* e = getenv("B200_BN_NCHW_FORCE");
+    if (!e) return 0;
+    return e[0] == 'w' ? 1 : (e[0] == 'c' && e[1] == 't' ? 2 : (e[0] == 'c' ? 3 : 0));
+  }();
+  // very little data per channel (one round of loads for a warp) and enough channels: a warp per channel
+  const bool small = p.rows * p.spatial * (long long)sizeof(T) <= 4096 && p.channels >= 64;
+  if (force == 1 || (force == 0 && small)) {
+    int G = 32;  // as few lanes per plane as keep every group busy, at most eight vectors per lane
+    while (G > 2 && 32 / (G / 2) <= 2 * p.rows && plane_vecs <= 8LL * (G / 2)) G /= 2;
+    const unsigned grid = (unsigned)((p.channels + kThreads / 32 - 1) / (kThreads / 32));
+    batch_norm_nchw_warp_kernel<T><<<grid, kThreads, 0, st>>>(p, G);
+    *rc = launch_status("b200_batch_norm_fwd [NCHW, one launch, warp per channel]");
+    return true;
+  }
   // cluster size: enough CTAs to fill the machine twice over, at most 8 per channel, at most one per image
   int S = 1;
   while (S < 8 && (long long)p.channels * S < 2LL * dev.sm_count && 2 * S <= p.rows) S *= 2;
+  if (force == 2) S = 1;
+  if (force == 3 && S == 1 && p.rows >= 2) S = 2;
   const int ipc = (int)((p.rows + S - 1) / S);  // a CTA whose range starts beyond the last image simply has no planes
   // Lanes per plane. Few lanes per plane mean many planes in flight per CTA (a group walks its
   // planes one after the other, each a round trip to memory), many lanes mean few vectors per lane
   // and round: as few lanes as give every plane of the CTA its own group, but enough that a lane
   // holds at most eight vectors of a plane.
-  const long long plane_vecs = (p.spatial * (long long)sizeof(T) + 15) / 16;
   int G = 32;
   while (G > 2 && kThreads / (G / 2) <= 2 * ipc && plane_vecs <= 8LL * (G / 2)) G /= 2;
+  if (S == 1) {
+    batch_norm_nchw_cluster_kernel<T, false><<<dim3(1, (unsigned)p.channels, 1), kThreads, 0, st>>>(p, ipc, G);
+    *rc = launch_status("b200_batch_norm_fwd [NCHW, one launch, CTA per channel]");
+    return true;
+  }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3((unsigned)S, (unsigned)p.channels, 1);
   cfg.blockDim = dim3(kThreads);
@@ -239,7 +365,7 @@ bool try_launch_batch_norm_nchw(const BatchNormParams& p, cudaStream_t st, int* 
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  cudaError_t e = cudaLaunchKernelEx(&cfg, batch_norm_nchw_cluster_kernel<T>, p, ipc, G);
+  cudaError_t e = cudaLaunchKernelEx(&cfg, batch_norm_nchw_cluster_kernel<T, true>, p, ipc, G);
   if (e != cudaSuccess) {
     cudaGetLastError();
     return false;  // the cluster launch was refused: the caller takes the three-launch path

@@ -266,7 +266,7 @@ static int launch_col_reduce(ColReduceParams p, bool vec, size_t scratch_bytes, 
     const long long max_splits2 = (p.rows + 8 * 32 - 1) / (8 * 32);
     long long cs = 8;
     while (cs > max_splits2 && cs > 1) cs /= 2;
-    if (cs >= 2 && chunks2 * p.batch * cs >= sms && chunks2 <= 0x7fffffffLL) {
+    if (cs >= 2 && 2 * chunks2 * p.batch * cs >= sms && chunks2 <= 0x7fffffffLL) {
       ColReduceParams q = p;
       q.tx_log2 = 3;
       q.splits = (int)cs;

@@ -189,9 +189,14 @@ __device__ __forceinline__ uint4 ld_coherent(const void* p) {
 }
 
 __device__ __forceinline__ void st_stream(void* p, const uint4& v) {
+#ifdef B200_ST_STREAM_DEFAULT
+  // build variant for measurements: write-once results with the default cache policy
+  asm volatile("st.global.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+#else
   asm volatile("st.global.cs.v4.u32 [%0], {%1,%2,%3,%4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z),
                "r"(v.w)
                : "memory");
+#endif
 }
 
 __device__ __forceinline__ void st_default(void* p, const uint4& v) {

@@ -191,21 +191,32 @@ __global__ void __launch_bounds__(256) transpose_small_kernel(const TransposePar
   for (long long b = blockIdx.x; b < p.batch; b += gridDim.x) {
     const E* src = reinterpret_cast<const E*>(p.x) + b * p.in_batch_stride;
     E* dst = reinterpret_cast<E*>(p.y) + b * (long long)P * C;
-    for (int j = threadIdx.x; j < nvec; j += 256) {
-      const uint4 raw = ld_stream(reinterpret_cast<const float*>(src) + (size_t)j * 4);
-      const int e0 = j * VE;
-      const int r = e0 / C, c0 = e0 - r * C;  // C is a multiple of VE: the vector stays in one row
-      E* t = tile + r * pitch + c0;
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-      if constexpr (sizeof(E) == 2) {
+    for (int j0 = threadIdx.x; j0 < nvec; j0 += 4 * 256) {  // four loads in flight per thread
+      uint4 raws[4];
 #pragma unroll
-        for (int k = 0; k < 4; ++k) {
-          t[2 * k] = (E)(w[k] & 0xffffu);
-          t[2 * k + 1] = (E)(w[k] >> 16);
+      for (int u = 0; u < 4; ++u) {
+        const int j = j0 + u * 256;
+        if (j < nvec) raws[u] = ld_stream(reinterpret_cast<const float*>(src) + (size_t)j * 4);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int j = j0 + u * 256;
+        if (j >= nvec) continue;
+        const uint4 raw = raws[u];
+        const int e0 = j * VE;
+        const int r = e0 / C, c0 = e0 - r * C;  // C is a multiple of VE: the vector stays in one row
+        E* t = tile + r * pitch + c0;
+        const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+        if constexpr (sizeof(E) == 2) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            t[2 * k] = (E)(w[k] & 0xffffu);
+            t[2 * k + 1] = (E)(w[k] >> 16);
+          }
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) t[k] = (E)w[k];
         }
-      } else {
-#pragma unroll
-        for (int k = 0; k < 4; ++k) t[k] = (E)w[k];
       }
     }
     __syncthreads();

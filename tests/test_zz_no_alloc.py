@@ -49,7 +49,8 @@ def _inputs(shape, dtype, channels_last, seed):
 
 @pytest.mark.parametrize("shape,dtype,channels_last", [
     ((16, 64, 28, 28), torch.bfloat16, True),     # fused cooperative path
-    ((8, 40, 13, 13), torch.float32, False),      # general three-launch path
+    ((8, 40, 13, 13), torch.float32, False),      # NCHW path (needs no scratch at all)
+    ((6, 20, 5, 5), torch.float32, True),         # channel count that is no multiple of the vector: three-launch path
 ])
 def test_static_scratch_entry_point_matches_the_ordinary_one_twice(shape, dtype, channels_last):
     from better_benchmark_b200 import native
@@ -63,6 +64,13 @@ def test_static_scratch_entry_point_matches_the_ordinary_one_twice(shape, dtype,
         for name, g, w in zip(("y", "mean", "invstd", "running_mean", "running_var"), got, want):
             tol = dict(rtol=1.6e-2, atol=1e-2) if g.dtype != torch.float32 else dict(rtol=1.3e-6, atol=1e-5)
             assert torch.allclose(g.float(), w.float(), **tol), f"call {attempt}: {name} differs"
+    # and against the eager module itself: a defect common to both entry points must not pass
+    from oracle.eager import BatchNormReluFwd
+    xc = x.cpu()
+    eager = BatchNormReluFwd(1e-5, 0.1, relu=True)(xc, torch.zeros(shape[1]), torch.ones(shape[1]), weight.cpu(), bias.cpu())
+    for name, g, w in zip(("y", "mean", "invstd", "running_mean", "running_var"), got, eager):
+        tol = dict(rtol=1.6e-2, atol=1e-2) if g.dtype != torch.float32 else dict(rtol=1.3e-6, atol=1e-5)
+        assert torch.allclose(g.float().cpu(), w.float(), **tol), f"{name} differs from the eager module"
     # a different problem right after: stale partial sums of the previous shape must not leak in
     x2, w2, b2 = _inputs((4, 24, 9, 9), torch.float16, True, seed=12)
     _, want2 = _call("b200_batch_norm_fwd", x2, w2, b2, 1e-5, 0.1, False, with_scratch=True)
