@@ -256,6 +256,9 @@ int32_t b200_batch_norm_bwd_ex(const void* dy, const void* x, const void* act, c
  * (about 1.3 MB) until the process exits. The first call on each device looks up the array's
  * device address and should be made before any stream capture. All calls on a device share the
  * array: calls that overlap on the GPU race and must be ordered by the caller. Allocates nothing.
+ * The caller has no scratch pointer to hand to b200_check_status here (and the barrier words are
+ * cleared at every call): a bounded device-side wait that ran out shows in
+ * b200_batch_norm_wait_timeouts(), which stays at 0 in normal operation.
  * This entry point has no counterpart in the reference. */
 int32_t b200_batch_norm_fwd_static_scratch(const void* x, void* y, const void* weight, const void* bias,
                                            float* running_mean, float* running_var, float* save_mean,
