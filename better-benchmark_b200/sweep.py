@@ -127,7 +127,7 @@ def compute_worker_count(*, num_tasks: int, num_gpus: int, max_workers=None, wor
 # Worker process (child side)
 # ---------------------------------------------------------------------------------------------
 def bench_point(canonical_dir: str, label: str, *, warmup: int, rep: int, skip_check: bool,
-                compile_reference: bool, peak_gbps) -> dict:
+                compile_reference: bool, peak_gbps, dtype_tolerance: bool = False) -> dict:
     """Check, then time, ONE shape point of one canonical directory. Returns {label: point}."""
     from . import harness
     from .byte_model import count_bytes_effective
@@ -142,8 +142,12 @@ def bench_point(canonical_dir: str, label: str, *, warmup: int, rep: int, skip_c
     out_label = "default" if default else label
     point_id = repro_id if default else f"{repro_id}_{label}"
     if not skip_check:
+        # dtype_tolerance: this backend's per-dtype acceptance (fp32 1.3e-6 / 1e-5, 16-bit 1.6e-2 / 1e-2)
+        # instead of the reference's blanket 1e-2. Outputs that draw random numbers are skipped by the
+        # check either way; those regions are verified by the Philox restatement in the test-suite.
+        tol = dict(atol=None, rtol=None) if dtype_tolerance else {}
         verdicts = harness.check_oracle_all_shapes(fn, d, repro_id, skip_stochastic=True,
-                                                   point=None if default else label, device="cuda")
+                                                   point=None if default else label, device="cuda", **tol)
         if not all(v not in ("fail", False) for v in verdicts.values()):
             return {out_label: {"repro_id": point_id, "status": "UNVERIFIED_NUMERICS"}}
     inputs = harness.get_inputs(d) if default else make_inputs_from_config(configs[label], "cuda")
@@ -177,7 +181,8 @@ def worker_main(args) -> int:
     os.dup2(2, 1)
     sys.stdout = sys.stderr
     kw = dict(warmup=args.warmup, rep=args.rep, skip_check=args.skip_check,
-              compile_reference=args.compile_reference, peak_gbps=args.peak_gbps)
+              compile_reference=args.compile_reference, peak_gbps=args.peak_gbps,
+              dtype_tolerance=args.dtype_tolerance)
 
     def send(text: str) -> None:
         result_pipe.write(text + "\n")
@@ -296,6 +301,8 @@ def default_worker_command(options: dict) -> list:
         cmd.append("--compile-reference")
     if options.get("peak_gbps"):
         cmd += ["--peak-gbps", str(options["peak_gbps"])]
+    if options.get("dtype_tolerance"):
+        cmd.append("--dtype-tolerance")
     return cmd
 
 
@@ -601,6 +608,8 @@ def main(argv=None) -> int:
     ap.add_argument("--compile-reference", action="store_true",
                     help="also time torch.compile of the eager module (adds compile_us and ratio)")
     ap.add_argument("--peak-gbps", type=float, default=None, help="HBM peak for the sol_frac column")
+    ap.add_argument("--dtype-tolerance", action="store_true",
+                    help="check with this backend's per-dtype tolerances instead of the reference's 1e-2")
     ap.add_argument("--task-timeout", type=float, default=600.0)
     ap.add_argument("--workers-per-gpu", type=int, default=None)
     ap.add_argument("--max-workers", type=int, default=None)
@@ -616,7 +625,7 @@ def main(argv=None) -> int:
     options = dict(warmup=args.warmup, rep=args.rep, skip_check=args.skip_check,
                    compile_reference=args.compile_reference, peak_gbps=args.peak_gbps,
                    task_timeout=args.task_timeout, workers_per_gpu=args.workers_per_gpu,
-                   max_workers=args.max_workers)
+                   max_workers=args.max_workers, dtype_tolerance=args.dtype_tolerance)
     gpus = [g.strip() for g in args.gpus.split(",") if g.strip()]
     print(f"[sweep] {len(tasks)} points in {len(dirs)} directories on GPUs {gpus}")
     all_results, failures, summary = run_sweep(tasks, gpus, options=options, output=args.output)
