@@ -595,7 +595,8 @@ _INVALID_STATUSES = frozenset({"UNVERIFIED_NUMERICS", "INVALID_CUDAGRAPH_WARNING
 
 def bench_oracle(oracle_forward, instance, inputs, repro_id, *, warmup=25, rep=200, rounds=5,
                  _skip_numerics_gate=False, numerics_optout=None, disable_gpu_lock=False,
-                 compile_reference=True, region_bytes=None, peak_gbps=None, memcpy_sol=False) -> dict:
+                 compile_reference=True, region_bytes=None, peak_gbps=None, memcpy_sol=False,
+                 adaptive_rep=True) -> dict:
     """Time the oracle (and, by default, ``torch.compile`` of the eager module) as CUDA-graph
     replays from a flushed L2: min over ``rounds`` interleaved rounds, under the exclusive GPU lock.
 
@@ -660,10 +661,11 @@ def bench_oracle(oracle_forward, instance, inputs, repro_id, *, warmup=25, rep=2
     quick = _time_graph(g_oracle, warmup=5, rep=10)
     if g_compile is not None:
         quick = min(quick, _time_graph(g_compile, warmup=5, rep=10))
-    if quick < 50:
-        rep = max(rep, 500)
-    elif quick < 200:
-        rep = max(rep, 300)
+    if adaptive_rep:  # the reference lengthens the timing window of fast kernels; a sweep may keep it fixed
+        if quick < 50:
+            rep = max(rep, 500)
+        elif quick < 200:
+            rep = max(rep, 300)
 
     best_oracle = best_compile = math.inf
     with gpu_exclusive_lock(repro_id, disabled=disable_gpu_lock):

@@ -127,7 +127,8 @@ def compute_worker_count(*, num_tasks: int, num_gpus: int, max_workers=None, wor
 # Worker process (child side)
 # ---------------------------------------------------------------------------------------------
 def bench_point(canonical_dir: str, label: str, *, warmup: int, rep: int, skip_check: bool,
-                compile_reference: bool, peak_gbps, dtype_tolerance: bool = False) -> dict:
+                compile_reference: bool, peak_gbps, dtype_tolerance: bool = False, rounds: int = 5,
+                fixed_rep: bool = False) -> dict:
     """Check, then time, ONE shape point of one canonical directory. Returns {label: point}."""
     from . import harness
     from .byte_model import count_bytes_effective
@@ -159,7 +160,8 @@ def bench_point(canonical_dir: str, label: str, *, warmup: int, rep: int, skip_c
         pass  # the byte count is an annotation; the timing stands without it
     return {out_label: harness.bench_oracle(fn, instance, inputs, point_id, warmup=warmup, rep=rep,
                                             numerics_optout=harness.load_numerics_optout(d),
-                                            compile_reference=compile_reference,
+                                            compile_reference=compile_reference, rounds=rounds,
+                                            adaptive_rep=not fixed_rep,
                                             region_bytes=region_bytes, peak_gbps=peak_gbps)}
 
 
@@ -182,7 +184,7 @@ def worker_main(args) -> int:
     sys.stdout = sys.stderr
     kw = dict(warmup=args.warmup, rep=args.rep, skip_check=args.skip_check,
               compile_reference=args.compile_reference, peak_gbps=args.peak_gbps,
-              dtype_tolerance=args.dtype_tolerance)
+              dtype_tolerance=args.dtype_tolerance, rounds=args.rounds, fixed_rep=args.fixed_rep)
 
     def send(text: str) -> None:
         result_pipe.write(text + "\n")
@@ -303,6 +305,9 @@ def default_worker_command(options: dict) -> list:
         cmd += ["--peak-gbps", str(options["peak_gbps"])]
     if options.get("dtype_tolerance"):
         cmd.append("--dtype-tolerance")
+    if options.get("fixed_rep"):
+        cmd.append("--fixed-rep")
+    cmd += ["--rounds", str(options.get("rounds", 5))]
     return cmd
 
 
@@ -608,6 +613,9 @@ def main(argv=None) -> int:
     ap.add_argument("--compile-reference", action="store_true",
                     help="also time torch.compile of the eager module (adds compile_us and ratio)")
     ap.add_argument("--peak-gbps", type=float, default=None, help="HBM peak for the sol_frac column")
+    ap.add_argument("--rounds", type=int, default=5, help="interleaved timing rounds per point (min over them)")
+    ap.add_argument("--fixed-rep", action="store_true",
+                    help="keep --rep as given instead of lengthening the window of fast kernels (quick sweeps)")
     ap.add_argument("--dtype-tolerance", action="store_true",
                     help="check with this backend's per-dtype tolerances instead of the reference's 1e-2")
     ap.add_argument("--task-timeout", type=float, default=600.0)
@@ -625,7 +633,8 @@ def main(argv=None) -> int:
     options = dict(warmup=args.warmup, rep=args.rep, skip_check=args.skip_check,
                    compile_reference=args.compile_reference, peak_gbps=args.peak_gbps,
                    task_timeout=args.task_timeout, workers_per_gpu=args.workers_per_gpu,
-                   max_workers=args.max_workers, dtype_tolerance=args.dtype_tolerance)
+                   max_workers=args.max_workers, dtype_tolerance=args.dtype_tolerance, rounds=args.rounds,
+                   fixed_rep=args.fixed_rep)
     gpus = [g.strip() for g in args.gpus.split(",") if g.strip()]
     print(f"[sweep] {len(tasks)} points in {len(dirs)} directories on GPUs {gpus}")
     all_results, failures, summary = run_sweep(tasks, gpus, options=options, output=args.output)
