@@ -417,6 +417,8 @@ bn_bwd_nchw_cluster_kernel(const BnBwdParams p, const int imgs_per_cta, const in
   const float mean = __ldg(p.mean + c);
   const f32x2 mean2 = splat2(mean);
   const float slope = p.slope;
+  const float invstd = __ldg(p.invstd + c);  // needed after the sums: requested now
+  const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
 
   // ---- pass 1 ----------------------------------------------------------------------------------
   double d1 = 0.0, d2 = 0.0;
@@ -459,8 +461,6 @@ bn_bwd_nchw_cluster_kernel(const BnBwdParams p, const int imgs_per_cta, const in
     cta_tot[0] = t1;
     cta_tot[1] = t2;
   }
-  const float invstd = __ldg(p.invstd + c);
-  const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
   bool first = true;  // this CTA writes the channel's global outputs
   if constexpr (CLUSTER) {
     cg::cluster_group cluster = cg::this_cluster();
@@ -603,7 +603,7 @@ static bool try_launch_bn_bwd_nchw(const BnBwdParams& p, cudaStream_t st, int* r
     return e[0] == 'w' ? 1 : (e[0] == 'c' && e[1] == 't' ? 2 : (e[0] == 'c' ? 3 : 0));
   }();
   // very little data per channel (one round of loads for a warp) and enough channels: a warp per channel
-  const bool small = p.rows * p.spatial * (long long)sizeof(T) <= 2048 && p.channels >= 64;
+  const bool small = p.rows * p.spatial * (long long)sizeof(T) <= 2048 && p.channels >= 256;
   if (force == 1 || (force == 0 && small)) {  // little data per channel: a warp per channel
     int G = 32;
     while (G > 2 && 32 / (G / 2) <= 2 * p.rows && plane_vecs <= 4LL * (G / 2)) G /= 2;
@@ -613,8 +613,9 @@ static bool try_launch_bn_bwd_nchw(const BnBwdParams& p, cudaStream_t st, int* r
     *rc = launch_status("b200_batch_norm_bwd [NCHW, one launch, warp per channel]");
     return true;
   }
-  int S = 1;
-  while (S < 8 && (long long)p.channels * S < 2LL * dev.sm_count && 2 * S <= p.rows) S *= 2;
+  int S = 1;  // several CTAs per channel only when a channel holds enough data (see batch_norm_nchw.cu)
+  if (p.rows * p.spatial * (long long)sizeof(T) >= 128 * 1024)
+    while (S < 8 && (long long)p.channels * S < 2LL * dev.sm_count && 2 * S <= p.rows) S *= 2;
   if (force == 2) S = 1;
   if (force == 3 && S == 1 && p.rows >= 2) S = 2;
   const int ipc = (int)((p.rows + S - 1) / S);  // a CTA whose range starts beyond the last image has no planes

@@ -108,6 +108,14 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
   T* yc = y + (long long)c * hw;
   const float shift = Elem<T>::to_f32(__ldg(xc));  // the channel's first element: every CTA of the cluster reads the same one
   const f32x2 shift2 = splat2(shift);
+  // everything pass 2 and the statistics need besides x is requested now, so that it arrives
+  // while pass 1 runs instead of costing a round trip of its own later
+  const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
+  const float b = p.bias ? load_param1(p.bias, p.w_dtype, c) : 0.f;
+  if (tid == 0 && p.running_mean) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.running_mean + c));
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.running_var + c));
+  }
 
   // ---- pass 1 ----------------------------------------------------------------------------------
   double d1 = 0.0, d2 = 0.0;
@@ -184,8 +192,6 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
 
   // ---- pass 2 ----------------------------------------------------------------------------------
   const float mean = stat[0], invstd = stat[1];
-  const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
-  const float b = p.bias ? load_param1(p.bias, p.w_dtype, c) : 0.f;
   const f32x2 mean2 = splat2(mean), invstd2 = splat2(invstd), w2 = splat2(w), b2 = splat2(b);
   const bool relu = p.relu != 0;
   // the groups walk the CTA's images from the last to the first
@@ -237,6 +243,12 @@ batch_norm_nchw_warp_kernel(const BatchNormParams p, const int G) {
   T* yc = reinterpret_cast<T*>(p.y) + (long long)c * hw;
   const float shift = Elem<T>::to_f32(__ldg(xc));
   const f32x2 shift2 = splat2(shift);
+  const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;  // requested now, needed after the statistics
+  const float b = p.bias ? load_param1(p.bias, p.w_dtype, c) : 0.f;
+  if (lane32 == 0 && p.running_mean) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.running_mean + c));
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.running_var + c));
+  }
 
   double d1 = 0.0, d2 = 0.0;
   for (int n = grp; n < n_total; n += groups) {
@@ -274,8 +286,6 @@ batch_norm_nchw_warp_kernel(const BatchNormParams p, const int G) {
   invstd = __shfl_sync(0xffffffffu, invstd, 0);
   if (p.y == nullptr) return;
 
-  const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
-  const float b = p.bias ? load_param1(p.bias, p.w_dtype, c) : 0.f;
   const f32x2 mean2 = splat2(mean), invstd2 = splat2(invstd), w2 = splat2(w), b2 = splat2(b);
   const bool relu = p.relu != 0;
   for (int n = n_total - 1 - grp; n >= 0; n -= groups) {
@@ -327,7 +337,7 @@ bool try_launch_batch_norm_nchw(const BatchNormParams& p, cudaStream_t st, int* 
     return e[0] == 'w' ? 1 : (e[0] == 'c' && e[1] == 't' ? 2 : (e[0] == 'c' ? 3 : 0));
   }();
   // very little data per channel (one round of loads for a warp) and enough channels: a warp per channel
-  const bool small = p.rows * p.spatial * (long long)sizeof(T) <= 4096 && p.channels >= 64;
+  const bool small = p.rows * p.spatial * (long long)sizeof(T) <= 4096 && p.channels >= 256;
   if (force == 1 || (force == 0 && small)) {
     int G = 32;  // as few lanes per plane as keep every group busy, at most eight vectors per lane
     while (G > 2 && 32 / (G / 2) <= 2 * p.rows && plane_vecs <= 8LL * (G / 2)) G /= 2;
@@ -337,8 +347,12 @@ bool try_launch_batch_norm_nchw(const BatchNormParams& p, cudaStream_t st, int* 
     return true;
   }
   // cluster size: enough CTAs to fill the machine twice over, at most 8 per channel, at most one per image
+  // Several CTAs per channel (a cluster) only pay when a channel holds enough data to keep them
+  // busy: launching clusters costs more than launching plain CTAs, and for channels of a few tens of
+  // KB one CTA per channel was measured faster even when the channels do not fill the machine.
   int S = 1;
-  while (S < 8 && (long long)p.channels * S < 2LL * dev.sm_count && 2 * S <= p.rows) S *= 2;
+  if (p.rows * p.spatial * (long long)sizeof(T) >= 128 * 1024)
+    while (S < 8 && (long long)p.channels * S < 2LL * dev.sm_count && 2 * S <= p.rows) S *= 2;
   if (force == 2) S = 1;
   if (force == 3 && S == 1 && p.rows >= 2) S = 2;
   const int ipc = (int)((p.rows + S - 1) / S);  // a CTA whose range starts beyond the last image simply has no planes

@@ -254,19 +254,37 @@ __global__ void __launch_bounds__(256) cast_scale_kernel(const void* x, void* y,
   const long long units = n / VIN;
   const Tin* src = reinterpret_cast<const Tin*>(x);
   Tout* dst = reinterpret_cast<Tout*>(y);
-  for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < units;
-       u += (long long)gridDim.x * blockDim.x) {
-    if constexpr (VEC) {
-      float f[VIN];
-      Elem<Tin>::unpack(ld_stream(src + u * VIN), f);
-      if (has_scale) {
+  if constexpr (VEC) {
+    // A CTA takes blocks of U * blockDim consecutive vectors (block b, b + grid, ...): its U loads
+    // in flight per thread fall into one contiguous stretch of memory.
+    constexpr int U = 4;
+    const long long stride = blockDim.x;
+    const long long block = (long long)U * blockDim.x;
+    for (long long u0 = (long long)blockIdx.x * block + threadIdx.x; u0 < units; u0 += (long long)gridDim.x * block) {
+      uint4 raw[U];
 #pragma unroll
-        for (int i = 0; i < VIN; ++i) f[i] = f[i] * scale;
+      for (int k = 0; k < U; ++k) {
+        const long long u = u0 + k * stride;
+        if (u < units) raw[k] = ld_stream(src + u * VIN);
       }
-      store_converted<Tout, VIN>(dst + u * VIN, f);
-    } else {
-      dst[u] = convert_scaled<Tin, Tout>(src[u], scale, has_scale);
+#pragma unroll
+      for (int k = 0; k < U; ++k) {
+        const long long u = u0 + k * stride;
+        if (u < units) {
+          float f[VIN];
+          Elem<Tin>::unpack(raw[k], f);
+          if (has_scale) {
+#pragma unroll
+            for (int i = 0; i < VIN; ++i) f[i] = f[i] * scale;
+          }
+          store_converted<Tout, VIN>(dst + u * VIN, f);
+        }
+      }
     }
+  } else {
+    for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < units;
+         u += (long long)gridDim.x * blockDim.x)
+      dst[u] = convert_scaled<Tin, Tout>(src[u], scale, has_scale);
   }
   if constexpr (VEC) {  // ragged tail
     const long long done = units * VIN;
