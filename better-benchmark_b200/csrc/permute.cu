@@ -65,8 +65,11 @@ __global__ void __launch_bounds__(256) permute_general_kernel(const PermuteParam
     }
     return i0 * p.in_stride[0] + i1 * p.in_stride[1] + i2 * p.in_stride[2] + i3 * VIN * p.in_stride[3];
   };
-  const long long stride = (long long)gridDim.x * blockDim.x;
-  for (long long u0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; u0 < units; u0 += U * stride) {
+  // a CTA takes blocks of U * blockDim consecutive output units (block b, b + grid, ...), so that
+  // its U stores (and, for most layouts, loads) in flight per thread fall into one stretch of memory
+  const long long stride = blockDim.x;
+  const long long block = (long long)U * blockDim.x;
+  for (long long u0 = (long long)blockIdx.x * block + threadIdx.x; u0 < units; u0 += (long long)gridDim.x * block) {
     if constexpr (VEC) {
       uint4 raw[U];
 #pragma unroll
