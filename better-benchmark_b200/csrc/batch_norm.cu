@@ -49,20 +49,10 @@ __device__ __forceinline__ void bn_finalize_channel(const BatchNormParams& p, in
     s2 += __shfl_xor_sync(0xffffffffu, s2, o);
   }
   if (lane == 0) {
-    const double mean_shifted = s1 / p.count;
-    double var = (s2 - s1 * mean_shifted) / p.count;
-    if (var < 0.0) var = 0.0;
-    const float mean = (float)((double)shift + mean_shifted);
-    const float varf = (float)var;
-    const float invstd = rsqrtf(varf + p.eps);
+    float mean, invstd;
+    bn_channel_stats(p, c, s1, s2, shift, true, &mean, &invstd);
     p.stats[c] = mean;
     p.stats[p.channels + c] = invstd;
-    if (p.save_mean) p.save_mean[c] = mean;
-    if (p.save_invstd) p.save_invstd[c] = invstd;
-    if (p.running_mean) {
-      p.running_mean[c] = mean * p.momentum + p.running_mean[c] * p.one_minus_momentum;
-      p.running_var[c] = (varf * p.unbias) * p.momentum + p.running_var[c] * p.one_minus_momentum;
-    }
   }
 }
 
@@ -150,15 +140,26 @@ batch_norm_cl_stream_kernel(const BatchNormParams p, const int stages, const int
 
   // ---- pass 1: shifted sums -------------------------------------------------------------------
   f32x2 shift[V / 2], s1[V / 2], s2[V / 2];
-  {
-    float f[V];
-    Elem<T>::unpack(ld_keep(x + (long long)vc * V), f);  // row 0 of this thread's channels
+  bn_shift_pairs<T>(x, vc, p.channels, p.rows, shift);
+#pragma unroll
+  for (int i = 0; i < V / 2; ++i) s1[i] = s2[i] = splat2(0.f);
+  // Long chains (huge tensors): every 8 tiles the thread moves its sums of squares into fp64 slots
+  // of its own in the reduction area, which nothing else uses before the first pass ends.
+  double* deep_acc = reinterpret_cast<double*>(red);  // [V][T_]
+  if (p.deep) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) deep_acc[i * T_ + tid] = 0.0;
+  }
+  auto deep_flush = [&]() {
 #pragma unroll
     for (int i = 0; i < V / 2; ++i) {
-      shift[i] = pack2(f[2 * i], f[2 * i + 1]);
-      s1[i] = s2[i] = splat2(0.f);
+      float a, b;
+      unpack2(s2[i], a, b);
+      deep_acc[(2 * i) * T_ + tid] += (double)a;
+      deep_acc[(2 * i + 1) * T_ + tid] += (double)b;
+      s2[i] = splat2(0.f);
     }
-  }
+  };
   {
     int st = 0, issue_slot = issued % (stages > 0 ? stages : 1);
     for (int k = 0; k < my_tiles; ++k) {
@@ -194,8 +195,16 @@ batch_norm_cl_stream_kernel(const BatchNormParams p, const int stages, const int
           }
         }
       }
+      if (p.deep && (k & 7) == 7) deep_flush();
       if (++st == stages) st = 0;
     }
+  }
+  if (p.deep) {  // the rest of the chain joins the fp64 part; from here on the sums are fp32 again
+    deep_flush();
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i)
+      s2[i] = pack2((float)deep_acc[(2 * i) * T_ + tid], (float)deep_acc[(2 * i + 1) * T_ + tid]);
+    __syncthreads();  // the reduction area is about to be rewritten
   }
   if (failed && tid == 0) {
     note_wait_timeout();
@@ -292,7 +301,7 @@ batch_norm_cl_stream_kernel(const BatchNormParams p, const int stages, const int
         t2 += dred[((size_t)g * C + tid) * 2 + 1];
       }
       float mean, invstd;
-      bn_channel_stats(p, tid, t1, t2, Elem<T>::to_f32(__ldg(x + tid)), blockIdx.x == 0, &mean, &invstd);
+      bn_channel_stats(p, tid, t1, t2, bn_shift_scalar<T>(x, tid, p.channels, p.rows), blockIdx.x == 0, &mean, &invstd);
       stats_s[tid] = mean;
       stats_s[C + tid] = invstd;
     }
@@ -321,7 +330,7 @@ batch_norm_cl_stream_kernel(const BatchNormParams p, const int stages, const int
           t2 += dred[w * 2 + 1];
         }
         float mean, invstd;
-        bn_channel_stats(p, c, t1, t2, Elem<T>::to_f32(__ldg(x + c)), true, &mean, &invstd);
+        bn_channel_stats(p, c, t1, t2, bn_shift_scalar<T>(x, c, p.channels, p.rows), true, &mean, &invstd);
         p.stats[c] = mean;
         p.stats[p.channels + c] = invstd;
       }
@@ -477,7 +486,7 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
   const uint32_t total_vecs = (uint32_t)(p.rows * vpr);  // the launcher admits fewer than 2^31 vectors
 
   // The shift of the channel this thread finalises later: fetched now, needed after the barrier.
-  const float stat_shift = tid < p.channels ? Elem<T>::to_f32(__ldg(x + tid)) : 0.f;
+  const float stat_shift = tid < p.channels ? bn_shift_scalar<T>(x, tid, p.channels, p.rows) : 0.f;
 
   if (tid == 0) cta_failed = 0;
   if (lane == 0) {
@@ -526,15 +535,26 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
 
   // ---- pass 1: shifted sums -------------------------------------------------------------------
   f32x2 shift[V / 2], s1[V / 2], s2[V / 2];
-  {
-    f32x2 f[V / 2];
-    Pairs<T>::unpack(ld_keep(x + (long long)vc * V), f);  // row 0 of this lane's channels
+  bn_shift_pairs<T>(x, vc, p.channels, p.rows, shift);
+#pragma unroll
+  for (int i = 0; i < V / 2; ++i) s1[i] = s2[i] = splat2(0.f);
+  // Long chains (huge tensors): every 8 chunks the lane moves its sums of squares into fp64 slots
+  // of its own in the reduction area, which nothing else uses before the first pass ends.
+  double* deep_acc = reinterpret_cast<double*>(red);  // [V][1024]
+  if (p.deep) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) deep_acc[i * 1024 + tid] = 0.0;
+  }
+  auto deep_flush = [&]() {
 #pragma unroll
     for (int i = 0; i < V / 2; ++i) {
-      shift[i] = f[i];
-      s1[i] = s2[i] = splat2(0.f);
+      float a, b;
+      unpack2(s2[i], a, b);
+      deep_acc[(2 * i) * 1024 + tid] += (double)a;
+      deep_acc[(2 * i + 1) * 1024 + tid] += (double)b;
+      s2[i] = splat2(0.f);
     }
-  }
+  };
   {
     uint32_t f = first0;
     for (int k = 0; k < stages && k < n_chunks; ++k, f += step) {  // fill the ring
@@ -580,6 +600,7 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
         }
         __syncwarp();
       }
+      if (p.deep && (k & 7) == 7) deep_flush();
       if (k + stages < n_chunks) {  // refill the slot with the chunk `stages` further on
         const int nnv = vecs_of(k + stages, first + ahead);
         if (nnv > 0) {
@@ -605,6 +626,13 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
     __syncwarp();
   };
   if (failed) give_up();
+  if (p.deep) {  // the rest of the chain joins the fp64 part; from here on the sums are fp32 again
+    deep_flush();
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i)
+      s2[i] = pack2((float)deep_acc[(2 * i) * 1024 + tid], (float)deep_acc[(2 * i + 1) * 1024 + tid]);
+    __syncthreads();  // the reduction area is about to be rewritten
+  }
 
   B200_WMARK(1)
   // ---- per-CTA partial sums ---------------------------------------------------------------------
@@ -730,7 +758,7 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
           t2 += dred[w * 2 + 1];
         }
         float mean, invstd;
-        bn_channel_stats(p, c, t1, t2, Elem<T>::to_f32(__ldg(x + c)), true, &mean, &invstd);
+        bn_channel_stats(p, c, t1, t2, bn_shift_scalar<T>(x, c, p.channels, p.rows), true, &mean, &invstd);
         p.stats[c] = mean;
         p.stats[p.channels + c] = invstd;
       }
@@ -941,6 +969,9 @@ static bool try_launch_batch_norm_warp(BatchNormParams p, size_t scratch_bytes, 
   size_t red_bytes = 2ull * 36 * p.channels * sizeof(float);
   const size_t stats_area = (size_t)threads * 16 + 2ull * p.channels * sizeof(float);
   if (red_bytes < stats_area) red_bytes = stats_area;
+  // more than 64 vectors per lane: the squares are carried in fp64, 8 bytes per channel of every lane
+  p.deep = total_vecs > 64LL * threads * grid ? 1 : 0;
+  if (p.deep && red_bytes < (size_t)threads * V * sizeof(double)) red_bytes = (size_t)threads * V * sizeof(double);
   red_bytes = (red_bytes + 127) / 128 * 128;
   p.local_stats = (p.channels <= threads && (long long)p.channels * grid <= 32768) ? 1 : 0;
   const size_t barrier_bytes = 32 * 8 * sizeof(uint64_t);
@@ -1023,6 +1054,8 @@ static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, size_t 
     size_t red_bytes = 2ull * geo.red_rows * p.channels * sizeof(float);
     const size_t stats_area = (size_t)threads * 16 + 2ull * p.channels * sizeof(float);
     if (red_bytes < stats_area) red_bytes = stats_area;
+    p.deep = total_tiles * passes > 64LL * grid ? 1 : 0;  // more than 64 vectors per thread
+    if (p.deep && red_bytes < (size_t)threads * V * sizeof(double)) red_bytes = (size_t)threads * V * sizeof(double);
     red_bytes = (red_bytes + 15) / 16 * 16;
     p.local_stats = (p.channels <= threads && (long long)p.channels * grid <= 32768) ? 1 : 0;
     const size_t fixed = red_bytes + 8 * sizeof(uint64_t) + 256;
@@ -1119,11 +1152,12 @@ extern "C" int b200_batch_norm_fwd_ex(const void* x, void* y, const void* weight
   p.eps = (float)eps; p.momentum = (float)momentum; p.one_minus_momentum = (float)(1.0 - momentum);
   const double count = (double)batch * (double)spatial;
   p.count = count;
+  p.inv_count = 1.0 / count;
   p.unbias = unbiased_factor > 0.0 ? (float)unbiased_factor : (float)(count / (count - 1.0));
   p.relu = relu ? 1 : 0;
   p.bar = reinterpret_cast<unsigned int*>(scratch);
   p.partials = reinterpret_cast<float*>(reinterpret_cast<char*>(scratch) + 256);
-  p.stats = nullptr; p.rows_per_cta = 0; p.smem_tiles = 0; p.local_stats = 0;
+  p.stats = nullptr; p.rows_per_cta = 0; p.smem_tiles = 0; p.local_stats = 0; p.deep = 0;
 
   const int eb = dtype_size(x_dtype);
   const int v = 16 / eb;

@@ -22,6 +22,7 @@ struct BatchNormParams {
   int w_dtype;
   float eps, momentum, one_minus_momentum, unbias;
   double count;  // elements per channel
+  double inv_count;  // 1 / count (a multiplication by it replaces two fp64 divisions per channel)
   int relu;
   float* partials;  // [P][2][C]
   float* stats;     // [2][C] mean, invstd (scratch copy every CTA reads)
@@ -29,18 +30,70 @@ struct BatchNormParams {
   long long rows_per_cta;  // contiguous row range of each CTA
   int smem_tiles;          // stages of the shared-memory ring
   int local_stats;         // 1: every CTA combines all partials itself (one grid barrier instead of two)
+  int deep;                // 1: a thread's chain of squares is long; it is carried in fp64 every 16 vectors
 };
+
+// The value every sum of a channel is shifted by. Any value works as long as all threads of all
+// CTAs use the same one; the closer it is to the channel's mean, the less the variance
+// (s2 - s1 * s1 / n) / n cancels, and the cancellation multiplies the rounding error of s2 by
+// 1 + (shift - mean)^2 / var. The first element of the channel can sit three standard deviations
+// away (a factor of ten); the mean of the channel's first sixteen rows (rows beyond the last one
+// repeat it) rarely sits more than one. Both forms below add the same sixteen values in the same
+// order with the same roundings, so they agree to the bit.
+constexpr int BN_SHIFT_ROWS = 16;
+
+template <typename T>
+__device__ __forceinline__ float bn_shift_scalar(const T* x, int c, int channels, long long rows) {
+  float v[BN_SHIFT_ROWS];
+#pragma unroll
+  for (int r = 0; r < BN_SHIFT_ROWS; ++r) {
+    const long long rr = r < rows ? r : rows - 1;
+    v[r] = Elem<T>::to_f32(__ldg(x + rr * channels + c));
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int r = 0; r < BN_SHIFT_ROWS; ++r) s = __fadd_rn(s, v[r]);
+  return __fmul_rn(s, 1.0f / BN_SHIFT_ROWS);
+}
+
+// The same for the Elem<T>::V channels of vector column vc, as fp32 pairs.
+template <typename T>
+__device__ __forceinline__ void bn_shift_pairs(const T* x, int vc, int channels, long long rows,
+                                               f32x2 (&shift)[Elem<T>::V / 2]) {
+  constexpr int V = Elem<T>::V;
+  uint4 raw[BN_SHIFT_ROWS];
+#pragma unroll
+  for (int r = 0; r < BN_SHIFT_ROWS; ++r) {
+    const long long rr = r < rows ? r : rows - 1;
+    raw[r] = ld_keep(x + rr * channels + (long long)vc * V);
+  }
+#pragma unroll
+  for (int i = 0; i < V / 2; ++i) shift[i] = splat2(0.f);
+#pragma unroll
+  for (int r = 0; r < BN_SHIFT_ROWS; ++r) {
+    f32x2 f[V / 2];
+    Pairs<T>::unpack(raw[r], f);
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) shift[i] = add2(shift[i], f[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < V / 2; ++i) shift[i] = mul2(shift[i], splat2(1.0f / BN_SHIFT_ROWS));
+}
 
 // Turns the fp64 totals of the shifted sums of one channel into mean / invstd and, for the one
 // caller that owns the channel's global outputs, writes the saved and running statistics.
 __device__ __forceinline__ void bn_channel_stats(const BatchNormParams& p, int c, double s1, double s2, float shift,
                                                  bool write_global, float* mean_out, float* invstd_out) {
-  const double mean_shifted = s1 / p.count;
-  double var = (s2 - s1 * mean_shifted) / p.count;
+  // On the critical path of every launch (one thread per channel computes this while the others
+  // wait), so no fp64 division or square root: a product with 1/count and the fp64 rsqrt.
+  const double mean_shifted = s1 * p.inv_count;
+  double var = (s2 - s1 * mean_shifted) * p.inv_count;
   if (var < 0.0) var = 0.0;
   const float mean = (float)((double)shift + mean_shifted);
   const float varf = (float)var;
-  const float invstd = rsqrtf(varf + p.eps);
+  // 1 / sqrt(var + eps) from the fp64 variance, rounded once: within an ulp or two of the graph's
+  // rsqrt(fp32(var) + eps), and the closest fp32 value to what the graph gives in fp64
+  const float invstd = (float)rsqrt(var + (double)p.eps);
   *mean_out = mean;
   *invstd_out = invstd;
   if (write_global) {

@@ -106,6 +106,14 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
   const long long plane_stride = (long long)p.channels * hw;  // between images of one channel
   const T* xc = x + (long long)c * hw;
   T* yc = y + (long long)c * hw;
+#ifdef B200_BN_TIMING
+  long long tmark[8];
+#define B200_NMARK(i) \
+  if (tid == 0) tmark[i] = clock64();
+#else
+#define B200_NMARK(i)
+#endif
+  B200_NMARK(0)
   const float shift = Elem<T>::to_f32(__ldg(xc));  // the channel's first element: every CTA of the cluster reads the same one
   const f32x2 shift2 = splat2(shift);
   // everything pass 2 and the statistics need besides x is requested now, so that it arrives
@@ -143,6 +151,7 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
     d1 += (double)s1 + (double)hsum2(a1);
     d2 += (double)s2 + (double)hsum2(a2);
   }
+  B200_NMARK(1)
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
     d1 += __shfl_xor_sync(0xffffffffu, d1, o);
@@ -153,6 +162,7 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
     warp_tot[tid >> 5][1] = d2;
   }
   __syncthreads();
+  B200_NMARK(2)
   if (tid == 0) {
     double t1 = 0.0, t2 = 0.0;
     for (int w = 0; w < kThreads / 32; ++w) {
@@ -186,8 +196,10 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
       stat[0] = mean;
       stat[1] = invstd;
     }
+    B200_NMARK(3)
     __syncthreads();
   }
+  B200_NMARK(4)
   if (p.y == nullptr) return;
 
   // ---- pass 2 ----------------------------------------------------------------------------------
@@ -220,6 +232,13 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
           st_stream(out + i, Pairs<T>::pack(f));
         });
   }
+  B200_NMARK(5)
+#ifdef B200_BN_TIMING
+  if (tid == 0 && blockIdx.x == 0 && p.partials) {
+    long long* log = reinterpret_cast<long long*>(p.partials) + (long long)blockIdx.y * 8;
+    for (int i = 0; i < 6; ++i) log[i] = tmark[i];
+  }
+#endif
 }
 
 // Channels with little data (a few thousand elements over all images): a WARP per channel, eight

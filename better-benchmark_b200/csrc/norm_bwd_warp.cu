@@ -36,7 +36,7 @@ constexpr int kWarps = 8;  // warps per CTA
 // norm-backward directories expand a 0-dim gradient, repros/canonical/sum_sum_2cd99e5eb23e/repro.py:26);
 // nothing is read for it and a stage holds the row of x only.
 template <typename T, int CH, bool LN, bool DYS>
-__global__ void __launch_bounds__(kWarps * 32, 2)
+__global__ void __launch_bounds__(kWarps * 32, (LN && DYS) ? 3 : 2)
 norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_bytes) {
   constexpr int V = Elem<T>::V;
   constexpr int P = V / 2;  // fp32 pairs per vector
@@ -87,6 +87,11 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
 #pragma unroll
         for (int i = 0; i < V; ++i) wf[i] = 1.f;
       }
+      if constexpr (DYS) {  // one dy for the whole tensor: g = dy * w does not depend on the row
+        const float dyf = Elem<T>::to_f32(__ldg(dyg));
+#pragma unroll
+        for (int i = 0; i < V; ++i) wf[i] = __fmul_rn(dyf, wf[i]);
+      }
       const int c = q >> 5, l = q & 31;
 #pragma unroll
       for (int i = 0; i < P; ++i) {
@@ -112,6 +117,29 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
     }
   }
   __syncthreads();  // barriers initialised, weight slice in place
+
+  // LayerNorm with a scalar dy: g = dy * w is the same in every row, and so are sum(g) and the
+  // term g * n - sum(g) of dx. They are computed once: sum(g) by every warp (same order, same
+  // result), the per-column term into a second table behind the first.
+  float g_sum = 0.f;
+  float* asm_tab = wsm + CH * 32 * V;  // [CH][P][32] fp32 pairs, the layout of wsm
+  if constexpr (LN && DYS) {
+    f32x2 s1 = splat2(0.f);
+    const f32x2* g_lane = reinterpret_cast<const f32x2*>(wsm) + lane;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      if (c * 32 + lane < nv) {
+#pragma unroll
+        for (int i = 0; i < P; ++i) s1 = add2(s1, g_lane[(c * P + i) * 32]);
+      }
+    }
+    g_sum = warp_reduce<SumOp>(hsum2(s1));
+    for (int q = threadIdx.x; q < CH * 32 * P; q += blockDim.x) {  // q = (c * P + i) * 32 + lane
+      asm_tab[q * 2] = __fsub_rn(__fmul_rn(wsm[q * 2], p.n_f), g_sum);
+      asm_tab[q * 2 + 1] = __fsub_rn(__fmul_rn(wsm[q * 2 + 1], p.n_f), g_sum);
+    }
+    __syncthreads();
+  }
 
   int issued = 0;
   if (lane == 0) {
@@ -178,6 +206,17 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
 
     // Sweep 1: the row sums of this lane's columns.
     f32x2 s1 = splat2(0.f), s2 = splat2(0.f);
+    if constexpr (LN && DYS) {
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        if (c * 32 + lane < nv) {
+          f32x2 x2[P];
+          Pairs<T>::unpack(lds128(sx + c * 512), x2);
+#pragma unroll
+          for (int i = 0; i < P; ++i) s2 = add2(s2, mul2(weight(c, i), mul2(sub2(x2[i], mean2), rstd2)));
+        }
+      }
+    } else {
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
       if (c * 32 + lane < nv) {
@@ -201,8 +240,12 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
         }
       }
     }
+    }
     float t1 = 0.f, t2;
-    if constexpr (LN) {
+    if constexpr (LN && DYS) {
+      t1 = g_sum;
+      t2 = warp_reduce<SumOp>(hsum2(s2));
+    } else if constexpr (LN) {
       float vals[2] = {hsum2(s1), hsum2(s2)};
       const float mine = warp_reduce_multi<2>(vals, lane);  // lanes 0..15 hold sum 1, lanes 16..31 sum 2
       t1 = __shfl_sync(0xffffffffu, mine, 0);
@@ -218,7 +261,25 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
       const unsigned int si = (unsigned int)row - bi * (unsigned int)p.seq;
       off0 = bi * (uint32_t)p.dx_batch_stride + si * (uint32_t)p.dx_seq_stride;
     }
-    if constexpr (LN) {
+    if constexpr (LN && DYS) {
+      // dweight = dy * sum(xhat): the sum of xhat is kept, the product is taken once at the end.
+      const f32x2 k2 = splat2(rstd * inv_n), s2b = splat2(t2);
+      const f32x2* a_lane = reinterpret_cast<const f32x2*>(asm_tab) + lane;
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+        if (c * 32 + lane < nv) {
+          f32x2 x2[P], o2[P];
+          Pairs<T>::unpack(lds128(sx + c * 512), x2);
+#pragma unroll
+          for (int i = 0; i < P; ++i) {
+            const f32x2 xhat = mul2(sub2(x2[i], mean2), rstd2);
+            acc_w[c][i] = add2(acc_w[c][i], xhat);
+            o2[i] = mul2(k2, sub2(a_lane[(c * P + i) * 32], mul2(xhat, s2b)));
+          }
+          st_stream(dx_base + off0 + dx_col[c], Pairs<T>::pack(o2));
+        }
+      }
+    } else if constexpr (LN) {
       // The division by n of the aten graph is a multiplication by 1/n here (exact for powers of
       // two, otherwise within one fp32 ulp of a per-row coefficient).
       const f32x2 k2 = splat2(rstd * inv_n), n2 = splat2(p.n_f), s1b = splat2(t1), s2b = splat2(t2);
@@ -292,6 +353,16 @@ norm_bwd_warp_kernel(const NormBwdParams p, const int stages, const int ring_byt
   if (!any_failed && (p.dw || p.db)) {
     float* fold_w = reinterpret_cast<float*>(smem);   // [kWarps][n]
     float* fold_b = fold_w + (size_t)kWarps * p.n;    // [kWarps][n]
+    if constexpr (LN && DYS) {
+#pragma unroll
+      for (int c = 0; c < CH; ++c) {
+#pragma unroll
+        for (int i = 0; i < P; ++i) {
+          acc_w[c][i] = mul2(acc_w[c][i], dy_all);
+          acc_b[c][i] = mul2(splat2((float)my_rows), dy_all);  // this warp's rows, each adding dy
+        }
+      }
+    }
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
       const int j = c * 32 + lane;
@@ -354,11 +425,12 @@ bool launch_warp_kernel_impl(NormBwdParams p, size_t scratch_bytes, cudaStream_t
   const DeviceInfo& dev = device_info();
   const int nv = p.n / V;
   const size_t stage_bytes = (DYS ? 1 : 2) * (size_t)nv * 16;
-  const size_t fixed = kWarps * 8 * sizeof(uint64_t) + (LN ? (size_t)CH * 32 * V * sizeof(float) : 0);  // barriers (+ fp32 weight slots)
+  // barriers (+ fp32 weight slots; a second table of the same size for LayerNorm with a scalar dy)
+  const size_t fixed = kWarps * 8 * sizeof(uint64_t) + (LN ? (size_t)(DYS ? 2 : 1) * CH * 32 * V * sizeof(float) : 0);
   // the ring doubles as the fold area [2][kWarps][n] fp32 and as the fp64 area of the finalize
   size_t floor_bytes = 2 * (size_t)kWarps * p.n * sizeof(float);
   if (floor_bytes < 16 * 64 * sizeof(double)) floor_bytes = 16 * 64 * sizeof(double);
-  int stages = 0, ctas_per_sm = 2;
+  int stages = 0, ctas_per_sm = (LN && DYS) ? 3 : 2;  // the scalar-dy LayerNorm form needs fewer registers
   for (; ctas_per_sm >= 1; --ctas_per_sm) {
     const size_t per_cta = ((size_t)dev.max_smem_optin - 1024 * (size_t)ctas_per_sm) / (size_t)ctas_per_sm;
     if (per_cta <= fixed + 256) continue;

@@ -149,7 +149,9 @@ def test_norm_bwd_many_narrow_rows(rows, n, dtype, ln):
 
 @pytest.mark.parametrize("rows,n,dtype,ln", [(9000, 512, torch.bfloat16, False), (7000, 768, torch.bfloat16, True),
                                              (50, 100, torch.float32, False), (300, 4096, torch.bfloat16, True),
-                                             (33, 64, torch.float16, False)])
+                                             (33, 64, torch.float16, False),
+                                             (5000, 512, torch.bfloat16, True), (700, 1024, torch.float32, True),
+                                             (2100, 384, torch.float16, True)])
 def test_norm_bwd_scalar_dy(rows, n, dtype, ln):
     """dy given as ONE element (the captured graphs expand a 0-dim gradient): read as a scalar by
     the kernels, whatever path the row length takes; same results as the materialised expansion."""
