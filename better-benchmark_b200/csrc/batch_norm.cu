@@ -38,10 +38,25 @@ __device__ __forceinline__ void bn_finalize_channel(const BatchNormParams& p, in
                                                     float shift) {
   // Called by one warp per channel: lanes split the partials, fp64 accumulation, fixed order.
   const int lane = threadIdx.x & 31;
+  float old_mean = 0.f, old_var = 0.f;  // requested now, so that they do not cost a round trip after the sums
+  if (lane == 0 && p.running_mean) {
+    old_mean = __ldcg(p.running_mean + c);
+    old_var = __ldcg(p.running_var + c);
+  }
   double s1 = 0.0, s2 = 0.0;
-  for (int g = lane; g < num_partials; g += 32) {
-    s1 += (double)__ldcg(p.partials + ((long long)g * 2) * p.channels + c);
-    s2 += (double)__ldcg(p.partials + ((long long)g * 2 + 1) * p.channels + c);
+  for (int g0 = lane; g0 < num_partials; g0 += 8 * 32) {  // eight pairs of loads in flight before any is used
+    float a[8], b[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      const int g = g0 + u * 32;
+      a[u] = g < num_partials ? __ldcg(p.partials + ((long long)g * 2) * p.channels + c) : 0.f;
+      b[u] = g < num_partials ? __ldcg(p.partials + ((long long)g * 2 + 1) * p.channels + c) : 0.f;
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      s1 += (double)a[u];
+      s2 += (double)b[u];
+    }
   }
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) {
@@ -50,7 +65,7 @@ __device__ __forceinline__ void bn_finalize_channel(const BatchNormParams& p, in
   }
   if (lane == 0) {
     float mean, invstd;
-    bn_channel_stats(p, c, s1, s2, shift, true, &mean, &invstd);
+    bn_channel_stats(p, c, s1, s2, shift, true, &mean, &invstd, true, old_mean, old_var);
     p.stats[c] = mean;
     p.stats[p.channels + c] = invstd;
   }
@@ -307,35 +322,7 @@ batch_norm_cl_stream_kernel(const BatchNormParams p, const int stages, const int
     }
     __syncthreads();
   } else if (ok) {
-    for (int c = blockIdx.x; c < p.channels; c += P) {
-      double d1 = 0.0, d2 = 0.0;
-      for (int g = tid; g < P; g += T_) {
-        d1 += (double)__ldcg(p.partials + ((long long)g * 2) * p.channels + c);
-        d2 += (double)__ldcg(p.partials + ((long long)g * 2 + 1) * p.channels + c);
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        d1 += __shfl_xor_sync(0xffffffffu, d1, o);
-        d2 += __shfl_xor_sync(0xffffffffu, d2, o);
-      }
-      if ((tid & 31) == 0) {
-        dred[(tid >> 5) * 2] = d1;
-        dred[(tid >> 5) * 2 + 1] = d2;
-      }
-      __syncthreads();
-      if (tid == 0) {
-        double t1 = 0.0, t2 = 0.0;
-        for (int w = 0; w < (T_ >> 5); ++w) {
-          t1 += dred[w * 2];
-          t2 += dred[w * 2 + 1];
-        }
-        float mean, invstd;
-        bn_channel_stats(p, c, t1, t2, bn_shift_scalar<T>(x, c, p.channels, p.rows), true, &mean, &invstd);
-        p.stats[c] = mean;
-        p.stats[p.channels + c] = invstd;
-      }
-      __syncthreads();
-    }
+    bn_stats_by_warps<T>(p, x, P);
     B200_TMARK(4)
     ok = grid_barrier(p.bar, 2u, &bar_ok);
   }
@@ -735,35 +722,7 @@ batch_norm_cl_warp_kernel(const BatchNormParams p, const int stages, const int r
     }
     __syncthreads();
   } else if (ok) {
-    for (int c = blockIdx.x; c < p.channels; c += P) {
-      double d1 = 0.0, d2 = 0.0;
-      for (int g = tid; g < P; g += T_) {
-        d1 += (double)__ldcg(p.partials + ((long long)g * 2) * p.channels + c);
-        d2 += (double)__ldcg(p.partials + ((long long)g * 2 + 1) * p.channels + c);
-      }
-#pragma unroll
-      for (int o = 16; o > 0; o >>= 1) {
-        d1 += __shfl_xor_sync(0xffffffffu, d1, o);
-        d2 += __shfl_xor_sync(0xffffffffu, d2, o);
-      }
-      if (lane == 0) {
-        dred[warp * 2] = d1;
-        dred[warp * 2 + 1] = d2;
-      }
-      __syncthreads();
-      if (tid == 0) {
-        double t1 = 0.0, t2 = 0.0;
-        for (int w = 0; w < 32; ++w) {
-          t1 += dred[w * 2];
-          t2 += dred[w * 2 + 1];
-        }
-        float mean, invstd;
-        bn_channel_stats(p, c, t1, t2, bn_shift_scalar<T>(x, c, p.channels, p.rows), true, &mean, &invstd);
-        p.stats[c] = mean;
-        p.stats[p.channels + c] = invstd;
-      }
-      __syncthreads();
-    }
+    bn_stats_by_warps<T>(p, x, P);
     ok = grid_barrier(p.bar, 2u, &bar_ok);
   }
 
@@ -945,6 +904,175 @@ __global__ void __launch_bounds__(256) batch_norm_apply_general_kernel(const Bat
   }
 }
 
+// ----------------------------------------------------------------------------------------------
+// Channels-last tensors with ANY channel count: three launches over the tensor as a flat array of
+// 16-byte vectors (the corpus of the reference has channels-last BatchNorm points with 24, 36, 60,
+// 92, 100, 480 ... channels; repros/canonical/var_mean_42fad1ece813/shapes.json).
+//
+// A vector holds V consecutive elements of the flat [rows * C] array, so it may straddle the end
+// of a row. The pattern of channels under a vector repeats every PV = C / gcd(C, V) vectors
+// (lcm(C, V) elements): vector i has phase i % PV and its element j belongs to channel
+// (phase * V + j) % C. The CTA's vector range starts at a multiple of PV and blockDim.x is a
+// multiple of PV, so a thread keeps its phase - its V channels - for the whole launch and its
+// sums, and later its mean / invstd / weight / bias, stay in registers.
+//   sums      CTA b takes vectors [b * per, (b + 1) * per): shifted sums per thread, the threads of
+//             a phase folded in a fixed order (fp64), one fp32 partial row per CTA
+//   finalize  a warp per channel (batch_norm_finalize_general_kernel)
+//   apply     the same ranges walked from the end (what the sums pass read last is what L2 still
+//             holds), y written with streaming stores
+// ----------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) batch_norm_sums_cl_flat_kernel(const BatchNormParams p, long long vecs_per_cta,
+                                                                      int PV) {
+  constexpr int V = Elem<T>::V;
+  __shared__ float red[2 * 256 * V];  // [2][threads][V]
+  const int tid = threadIdx.x, T_ = blockDim.x, C = p.channels;
+  const int ph = tid % PV;
+  const long long total = p.rows * C / V;
+  const long long v0 = (long long)blockIdx.x * vecs_per_cta;
+  long long v1 = v0 + vecs_per_cta;
+  if (v1 > total) v1 = total;
+  const T* xe = reinterpret_cast<const T*>(p.x);
+  const uint4* x = reinterpret_cast<const uint4*>(p.x);
+  f32x2 shift[V / 2], s1[V / 2], s2[V / 2];
+#pragma unroll
+  for (int i = 0; i < V / 2; ++i) {  // the channel's element of row 0, as the finalize kernel assumes
+    shift[i] = pack2(Elem<T>::to_f32(__ldg(xe + (ph * V + 2 * i) % C)), Elem<T>::to_f32(__ldg(xe + (ph * V + 2 * i + 1) % C)));
+    s1[i] = s2[i] = splat2(0.f);
+  }
+  constexpr int U = 8;  // vectors in flight per thread
+  for (long long v = v0 + tid; v < v1; v += (long long)U * T_) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = v + (long long)u * T_;
+      if (i < v1) raw[u] = ld_stream(reinterpret_cast<const T*>(x + i));
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (v + (long long)u * T_ < v1) {
+        f32x2 f[V / 2];
+        Pairs<T>::unpack(raw[u], f);
+#pragma unroll
+        for (int i = 0; i < V / 2; ++i) {
+          const f32x2 d = sub2(f[i], shift[i]);
+          s1[i] = add2(s1[i], d);
+          s2[i] = fma2(d, d, s2[i]);
+        }
+      }
+    }
+  }
+  float* r1 = red;
+  float* r2 = red + 256 * V;
+#pragma unroll
+  for (int i = 0; i < V / 2; ++i) {
+    unpack2(s1[i], r1[tid * V + 2 * i], r1[tid * V + 2 * i + 1]);
+    unpack2(s2[i], r2[tid * V + 2 * i], r2[tid * V + 2 * i + 1]);
+  }
+  __syncthreads();
+  const int period = PV * V;  // elements; a multiple of C
+  for (int c = tid; c < C; c += T_) {
+    double a = 0.0, b = 0.0;
+    for (int idx = c; idx < period; idx += C) {  // every (phase, element) that lands on channel c
+      const int col = idx / V, e = idx % V;
+      for (int t = col; t < T_; t += PV) {
+        a += (double)r1[t * V + e];
+        b += (double)r2[t * V + e];
+      }
+    }
+    p.partials[((long long)blockIdx.x * 2) * C + c] = (float)a;
+    p.partials[((long long)blockIdx.x * 2 + 1) * C + c] = (float)b;
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256) batch_norm_apply_cl_flat_kernel(const BatchNormParams p, long long vecs_per_cta,
+                                                                       int PV) {
+  constexpr int V = Elem<T>::V;
+  const int tid = threadIdx.x, T_ = blockDim.x, C = p.channels;
+  const int ph = PV - 1 - tid % PV;  // the range ends on a multiple of PV: its last vector has phase PV - 1
+  const long long total = p.rows * C / V;
+  const long long v0 = (long long)blockIdx.x * vecs_per_cta;
+  long long v1 = v0 + vecs_per_cta;
+  if (v1 > total) v1 = total;  // total is a multiple of PV as well (the launcher checks)
+  const uint4* x = reinterpret_cast<const uint4*>(p.x);
+  uint4* y = reinterpret_cast<uint4*>(p.y);
+  f32x2 mean2[V / 2], inv2[V / 2], w2[V / 2], b2[V / 2];
+#pragma unroll
+  for (int i = 0; i < V / 2; ++i) {
+    const int c0 = (ph * V + 2 * i) % C, c1 = (ph * V + 2 * i + 1) % C;
+    mean2[i] = pack2(p.stats[c0], p.stats[c1]);
+    inv2[i] = pack2(p.stats[C + c0], p.stats[C + c1]);
+    w2[i] = p.weight ? pack2(load_param1(p.weight, p.w_dtype, c0), load_param1(p.weight, p.w_dtype, c1)) : splat2(1.f);
+    b2[i] = p.bias ? pack2(load_param1(p.bias, p.w_dtype, c0), load_param1(p.bias, p.w_dtype, c1)) : splat2(0.f);
+  }
+  const bool relu = p.relu != 0;
+  constexpr int U = 8;
+  for (long long v = v1 - 1 - tid; v >= v0; v -= (long long)U * T_) {
+    uint4 raw[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = v - (long long)u * T_;
+      if (i >= v0) raw[u] = ld_stream(reinterpret_cast<const T*>(x + i));
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long i = v - (long long)u * T_;
+      if (i >= v0) {
+        f32x2 f[V / 2];
+        Pairs<T>::unpack(raw[u], f);
+#pragma unroll
+        for (int k = 0; k < V / 2; ++k) {
+          f[k] = add2(mul2(mul2(sub2(f[k], mean2[k]), inv2[k]), w2[k]), b2[k]);
+          if (relu) {
+            float lo, hi;
+            unpack2(f[k], lo, hi);
+            f[k] = pack2(lo < 0.f ? 0.f : lo, hi < 0.f ? 0.f : hi);
+          }
+        }
+        st_stream(reinterpret_cast<T*>(y + i), Pairs<T>::pack(f));
+      }
+    }
+  }
+}
+
+// Returns false when the shape does not fit (the caller takes the element-wise path).
+template <typename T>
+static bool try_launch_batch_norm_cl_flat(BatchNormParams p, size_t scratch_bytes, cudaStream_t st, int* rc) {
+  constexpr int V = Elem<T>::V;
+  const DeviceInfo& dev = device_info();
+  const long long C = p.channels;
+  long long g = C, h = V;  // gcd(C, V)
+  while (h) { const long long t = g % h; g = h; h = t; }
+  const long long PV = C / g;
+  const long long elems = p.rows * C;
+  if (PV > 256 || elems % (PV * V) != 0) return false;  // whole periods only: every range ends on a multiple of PV
+  const long long total = elems / V;
+  const int threads = (int)(256 / PV * PV);
+  const long long stats_floats = 2 * C;
+  const long long room = ((long long)scratch_bytes - 256) / (long long)sizeof(float) - stats_floats;
+  if (room < 2 * C) return false;
+  long long splits = 8LL * dev.sm_count;
+  if (splits > room / (2 * C)) splits = room / (2 * C);
+  // at least one full round of loads (8 vectors) per thread: small tensors get few partial rows and a
+  // short finalize
+  if (splits * threads * 8 > total) splits = (total + threads * 8 - 1) / (threads * 8);
+  if (splits < 1) splits = 1;
+  long long per = (total + splits - 1) / splits;
+  per = (per + PV - 1) / PV * PV;
+  splits = (total + per - 1) / per;
+  p.stats = p.partials + splits * 2 * C;
+  batch_norm_sums_cl_flat_kernel<T><<<(unsigned)splits, threads, 0, st>>>(p, per, (int)PV);
+  *rc = launch_status("b200_batch_norm_fwd sums [channels-last, flat vectors]");
+  if (*rc != B200_OK) return true;
+  batch_norm_finalize_general_kernel<T><<<(p.channels + 7) / 8, 256, 0, st>>>(p, (int)splits);
+  *rc = launch_status("b200_batch_norm_fwd finalize");
+  if (*rc != B200_OK || !p.y) return true;
+  batch_norm_apply_cl_flat_kernel<T><<<(unsigned)splits, threads, 0, st>>>(p, per, (int)PV);
+  *rc = launch_status("b200_batch_norm_fwd apply [channels-last, flat vectors]");
+  return true;
+}
+
 // B200_BN_CTA_RING=1 keeps the CTA-wide ring for every shape (for measurements).
 static bool warp_rings_disabled() {
   static const bool off = [] {
@@ -1021,7 +1149,7 @@ static bool try_launch_batch_norm_warp(BatchNormParams p, size_t scratch_bytes, 
 }
 
 template <typename T>
-static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, size_t scratch_bytes,
+static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, bool channels_last, size_t scratch_bytes,
                              cudaStream_t st) {
   constexpr int V = Elem<T>::V;
   const DeviceInfo& dev = device_info();
@@ -1083,6 +1211,12 @@ static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, size_t 
     }
     note_launch("b200_batch_norm_fwd [fused, channels-last, CTA ring]");
     return B200_OK;
+  }
+  if (channels_last) {  // any channel count: the tensor as a flat array of vectors, three launches
+    BatchNormParams q = p;
+    q.rows = p.rows * p.spatial;
+    int rc = B200_OK;
+    if (try_launch_batch_norm_cl_flat<T>(q, scratch_bytes, st, &rc)) return rc;
   }
   {  // contiguous NCHW: one launch, a cluster of CTAs per channel (batch_norm_nchw.cu)
     int rc = B200_OK;
@@ -1163,8 +1297,17 @@ extern "C" int b200_batch_norm_fwd_ex(const void* x, void* y, const void* weight
   const int v = 16 / eb;
   // channels-last: c is the unit-stride dimension, rows are (n, s) pairs with a uniform stride of C
   const bool cl = stride_c == 1 && stride_s == channels && stride_n == spatial * channels;
-  const bool fast = cl && channels % v == 0 && fused_geometry((int)(channels / v)).threads > 0 &&
+  // the fused cooperative kernels take channel counts that make a power-of-two number (<= 32) of
+  // vectors per row; B200_BN_CL_RING=1 sends every count the CTA-ring kernel can lay out there too
+  static const bool ring_all = [] {
+    const char* e = getenv("B200_BN_CL_RING");
+    return e && e[0] == '1';
+  }();
+  const long long vpr = channels % v == 0 ? channels / v : 0;
+  const bool pow2 = vpr > 0 && vpr <= 32 && (vpr & (vpr - 1)) == 0;
+  const bool fast = cl && vpr > 0 && (pow2 || ring_all) && fused_geometry((int)vpr).threads > 0 &&
                     aligned16(x) && aligned16(y);
+  const bool cl_flat = cl && !fast && aligned16(x) && aligned16(y);
   if (fast) {
     p.rows = batch * spatial;
   } else {
@@ -1172,9 +1315,9 @@ extern "C" int b200_batch_norm_fwd_ex(const void* x, void* y, const void* weight
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (x_dtype) {
-    case B200_F32: return launch_batch_norm<float>(p, fast, (size_t)scratch_bytes, st);
-    case B200_BF16: return launch_batch_norm<__nv_bfloat16>(p, fast, (size_t)scratch_bytes, st);
-    case B200_F16: return launch_batch_norm<__half>(p, fast, (size_t)scratch_bytes, st);
+    case B200_F32: return launch_batch_norm<float>(p, fast, cl_flat, (size_t)scratch_bytes, st);
+    case B200_BF16: return launch_batch_norm<__nv_bfloat16>(p, fast, cl_flat, (size_t)scratch_bytes, st);
+    case B200_F16: return launch_batch_norm<__half>(p, fast, cl_flat, (size_t)scratch_bytes, st);
   }
   return fail(B200_ERR_INVALID, "b200_batch_norm_fwd: unknown dtype %d", x_dtype);
 }

@@ -42,6 +42,14 @@ struct BatchNormParams {
 // order with the same roundings, so they agree to the bit.
 constexpr int BN_SHIFT_ROWS = 16;
 
+// The shift is cut to eight significant bits (a bf16 value). With 16-bit inputs x - shift then
+// has so few bits that the sums of the differences are exact or nearly so; with a full fp32 shift
+// every addition would drop the same low bits of the shift and the errors would add up instead
+// of cancelling (measured: the mean of 6.4 M bf16 values off by 2e-6 instead of 1e-8).
+__device__ __forceinline__ float bn_round_shift(float v) {
+  return __uint_as_float((__float_as_uint(v) + 0x8000u) & 0xffff0000u);
+}
+
 template <typename T>
 __device__ __forceinline__ float bn_shift_scalar(const T* x, int c, int channels, long long rows) {
   float v[BN_SHIFT_ROWS];
@@ -53,7 +61,7 @@ __device__ __forceinline__ float bn_shift_scalar(const T* x, int c, int channels
   float s = 0.f;
 #pragma unroll
   for (int r = 0; r < BN_SHIFT_ROWS; ++r) s = __fadd_rn(s, v[r]);
-  return __fmul_rn(s, 1.0f / BN_SHIFT_ROWS);
+  return bn_round_shift(__fmul_rn(s, 1.0f / BN_SHIFT_ROWS));
 }
 
 // The same for the Elem<T>::V channels of vector column vc, as fp32 pairs.
@@ -77,13 +85,20 @@ __device__ __forceinline__ void bn_shift_pairs(const T* x, int vc, int channels,
     for (int i = 0; i < V / 2; ++i) shift[i] = add2(shift[i], f[i]);
   }
 #pragma unroll
-  for (int i = 0; i < V / 2; ++i) shift[i] = mul2(shift[i], splat2(1.0f / BN_SHIFT_ROWS));
+  for (int i = 0; i < V / 2; ++i) {
+    float lo, hi;
+    unpack2(mul2(shift[i], splat2(1.0f / BN_SHIFT_ROWS)), lo, hi);
+    shift[i] = pack2(bn_round_shift(lo), bn_round_shift(hi));
+  }
 }
 
 // Turns the fp64 totals of the shifted sums of one channel into mean / invstd and, for the one
 // caller that owns the channel's global outputs, writes the saved and running statistics.
+// have_old: the caller already holds the channel's running statistics (fetched while the sums
+// were being formed, so that their latency is not waited for here).
 __device__ __forceinline__ void bn_channel_stats(const BatchNormParams& p, int c, double s1, double s2, float shift,
-                                                 bool write_global, float* mean_out, float* invstd_out) {
+                                                 bool write_global, float* mean_out, float* invstd_out,
+                                                 bool have_old = false, float old_mean = 0.f, float old_var = 0.f) {
   // On the critical path of every launch (one thread per channel computes this while the others
   // wait), so no fp64 division or square root: a product with 1/count and the fp64 rsqrt.
   const double mean_shifted = s1 * p.inv_count;
@@ -100,8 +115,51 @@ __device__ __forceinline__ void bn_channel_stats(const BatchNormParams& p, int c
     if (p.save_mean) p.save_mean[c] = mean;
     if (p.save_invstd) p.save_invstd[c] = invstd;
     if (p.running_mean) {
-      p.running_mean[c] = mean * p.momentum + p.running_mean[c] * p.one_minus_momentum;
-      p.running_var[c] = (varf * p.unbias) * p.momentum + p.running_var[c] * p.one_minus_momentum;
+      if (!have_old) {
+        old_mean = p.running_mean[c];
+        old_var = p.running_var[c];
+      }
+      p.running_mean[c] = mean * p.momentum + old_mean * p.one_minus_momentum;
+      p.running_var[c] = (varf * p.unbias) * p.momentum + old_var * p.one_minus_momentum;
+    }
+  }
+}
+
+// Many channels: the channels are dealt out to the WARPS of the grid (channel c to warp c / P of
+// CTA c % P, P = CTAs = partial rows), so that all of them are combined at the same time and no
+// CTA barrier is involved. The lanes split the partial rows, eight loads in flight each, fp64,
+// fixed order; lane 0 derives the statistics and publishes them in p.stats for the second grid barrier.
+template <typename T>
+__device__ __forceinline__ void bn_stats_by_warps(const BatchNormParams& p, const T* x, int P) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  // a trailing partial warp (block sizes that are no multiple of 32) takes no channel
+  for (int c = (int)blockIdx.x + warp * P; c < p.channels && warp < nwarps; c += P * nwarps) {
+    const float shift = lane == 0 ? bn_shift_scalar<T>(x, c, p.channels, p.rows) : 0.f;
+    double d1 = 0.0, d2 = 0.0;
+    for (int g0 = lane; g0 < P; g0 += 8 * 32) {
+      float a[8], b[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const int g = g0 + u * 32;
+        a[u] = g < P ? __ldcg(p.partials + ((long long)g * 2) * p.channels + c) : 0.f;
+        b[u] = g < P ? __ldcg(p.partials + ((long long)g * 2 + 1) * p.channels + c) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        d1 += (double)a[u];
+        d2 += (double)b[u];
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      d1 += __shfl_xor_sync(0xffffffffu, d1, o);
+      d2 += __shfl_xor_sync(0xffffffffu, d2, o);
+    }
+    if (lane == 0) {
+      float mean, invstd;
+      bn_channel_stats(p, c, d1, d2, shift, true, &mean, &invstd);
+      p.stats[c] = mean;
+      p.stats[p.channels + c] = invstd;
     }
   }
 }

@@ -70,16 +70,18 @@ __device__ __forceinline__ void bn_bwd_prologue(f32x2 (&g)[Elem<T>::V / 2], cons
   }
 }
 
-// Channels-last sums: the tensors are flat arrays of 16-byte vectors; blockDim.x is a multiple of
-// vpr, so a thread stays in one vector column. CTA b takes vectors [b*per, (b+1)*per).
+// Channels-last sums: the tensors are flat [rows * C] arrays of 16-byte vectors, whatever C is. A
+// vector may straddle the end of a row; the pattern of channels under a vector repeats every
+// PV = C / gcd(C, V) vectors: vector i has phase i % PV and its element j belongs to channel
+// (phase * V + j) % C. blockDim.x and the CTA's range [b*per, (b+1)*per) are multiples of PV, so a
+// thread keeps its phase - its V channels - for the whole launch.
 template <typename T>
-__global__ void __launch_bounds__(256) bn_bwd_sums_cl_kernel(const BnBwdParams p, long long vecs_per_cta) {
+__global__ void __launch_bounds__(256) bn_bwd_sums_cl_kernel(const BnBwdParams p, long long vecs_per_cta, int PV) {
   constexpr int V = Elem<T>::V;
   __shared__ float red[2 * 256 * 8 / 8 * 8];  // [2][threads][V] fp32, V <= 8
-  const int tid = threadIdx.x, T_ = blockDim.x;
-  const int vpr = p.channels / V;
-  const int vc = tid % vpr;
-  const long long total = p.rows * vpr;
+  const int tid = threadIdx.x, T_ = blockDim.x, C = p.channels;
+  const int ph = tid % PV;
+  const long long total = p.rows * C / V;
   const long long v0 = (long long)blockIdx.x * vecs_per_cta;
   long long v1 = v0 + vecs_per_cta;
   if (v1 > total) v1 = total;
@@ -89,7 +91,7 @@ __global__ void __launch_bounds__(256) bn_bwd_sums_cl_kernel(const BnBwdParams p
   f32x2 mean2[V / 2], s1[V / 2], s2[V / 2];
 #pragma unroll
   for (int i = 0; i < V / 2; ++i) {
-    mean2[i] = pack2(__ldg(p.mean + vc * V + 2 * i), __ldg(p.mean + vc * V + 2 * i + 1));
+    mean2[i] = pack2(__ldg(p.mean + (ph * V + 2 * i) % C), __ldg(p.mean + (ph * V + 2 * i + 1) % C));
     s1[i] = s2[i] = splat2(0.f);
   }
   constexpr int U = 4;  // vectors of each tensor in flight per thread
@@ -128,12 +130,15 @@ __global__ void __launch_bounds__(256) bn_bwd_sums_cl_kernel(const BnBwdParams p
     unpack2(s2[i], r2[tid * V + 2 * i], r2[tid * V + 2 * i + 1]);
   }
   __syncthreads();
+  const int period = PV * V;  // elements; a multiple of C
   for (int c = tid; c < p.channels; c += T_) {
-    const int col = c / V, e = c % V;
     double a = 0.0, b = 0.0;
-    for (int t = col; t < T_; t += vpr) {
-      a += (double)r1[t * V + e];
-      b += (double)r2[t * V + e];
+    for (int idx = c; idx < period; idx += C) {  // every (phase, element) that lands on channel c
+      const int col = idx / V, e = idx % V;
+      for (int t = col; t < T_; t += PV) {
+        a += (double)r1[t * V + e];
+        b += (double)r2[t * V + e];
+      }
     }
     p.partials[((long long)blockIdx.x * 2) * p.channels + c] = a;
     p.partials[((long long)blockIdx.x * 2 + 1) * p.channels + c] = b;
@@ -147,6 +152,13 @@ __global__ void __launch_bounds__(256) bn_bwd_finalize_kernel(const BnBwdParams 
   __shared__ double red[2][8];
   const int c = blockIdx.x;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // what thread 0 needs after the sums: requested now, so that it does not cost a round trip then
+  float invstd = 0.f, w = 1.f, mean = 0.f;
+  if (tid == 0) {
+    invstd = __ldg(p.invstd + c);
+    mean = __ldg(p.mean + c);
+    if (p.weight) w = load_param1(p.weight, p.w_dtype, c);
+  }
   double s1 = 0.0, s2 = 0.0;
   for (int g0 = tid; g0 < p.splits; g0 += 256 * 4) {
     double a[4], b[4];
@@ -179,14 +191,12 @@ __global__ void __launch_bounds__(256) bn_bwd_finalize_kernel(const BnBwdParams 
       s2 += red[1][w];
     }
     const float sum_dy = (float)s1, dot = (float)s2;
-    const float invstd = p.invstd[c];
-    const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
     if (p.dbias) p.dbias[c] = sum_dy;
     if (p.dweight) p.dweight[c] = dot * invstd;
     p.coef[c] = sum_dy * p.inv_count;
     p.coef[p.channels + c] = (dot * p.inv_count) * (invstd * invstd);
     p.coef[2 * p.channels + c] = invstd * w;
-    p.coef[3 * p.channels + c] = p.mean[c];
+    p.coef[3 * p.channels + c] = mean;
   }
 }
 
@@ -196,12 +206,11 @@ __global__ void __launch_bounds__(256) bn_bwd_finalize_kernel(const BnBwdParams 
 // the L2, so walking forward again would find nothing). blockDim.x and `per` are multiples of vpr,
 // so a thread stays in one vector column here too.
 template <typename T>
-__global__ void __launch_bounds__(256) bn_bwd_apply_cl_kernel(const BnBwdParams p, long long vecs_per_cta) {
+__global__ void __launch_bounds__(256) bn_bwd_apply_cl_kernel(const BnBwdParams p, long long vecs_per_cta, int PV) {
   constexpr int V = Elem<T>::V;
-  const int tid = threadIdx.x, T_ = blockDim.x;
-  const int vpr = p.channels / V;
-  const int vc = vpr - 1 - tid % vpr;  // the chunk ends on a row boundary: its last vector is column vpr - 1
-  const long long total = p.rows * vpr;
+  const int tid = threadIdx.x, T_ = blockDim.x, C = p.channels;
+  const int ph = PV - 1 - tid % PV;  // the range ends on a multiple of PV: its last vector has phase PV - 1
+  const long long total = p.rows * C / V;
   const long long v0 = (long long)blockIdx.x * vecs_per_cta;
   long long v1 = v0 + vecs_per_cta;
   if (v1 > total) v1 = total;
@@ -212,11 +221,11 @@ __global__ void __launch_bounds__(256) bn_bwd_apply_cl_kernel(const BnBwdParams 
   f32x2 c1[V / 2], c2[V / 2], gs[V / 2], mean2[V / 2];
 #pragma unroll
   for (int i = 0; i < V / 2; ++i) {
-    const int c = vc * V + 2 * i;
-    c1[i] = pack2(p.coef[c], p.coef[c + 1]);
-    c2[i] = pack2(p.coef[p.channels + c], p.coef[p.channels + c + 1]);
-    gs[i] = pack2(p.coef[2 * p.channels + c], p.coef[2 * p.channels + c + 1]);
-    mean2[i] = pack2(p.coef[3 * p.channels + c], p.coef[3 * p.channels + c + 1]);
+    const int c = (ph * V + 2 * i) % C, d = (ph * V + 2 * i + 1) % C;
+    c1[i] = pack2(p.coef[c], p.coef[d]);
+    c2[i] = pack2(p.coef[C + c], p.coef[C + d]);
+    gs[i] = pack2(p.coef[2 * C + c], p.coef[2 * C + d]);
+    mean2[i] = pack2(p.coef[3 * C + c], p.coef[3 * C + d]);
   }
   constexpr int U = 4;
   for (long long v = v1 - 1 - tid; v >= v0; v -= (long long)U * T_) {
@@ -584,6 +593,122 @@ __global__ void __launch_bounds__(256) bn_bwd_nchw_warp_kernel(const BnBwdParams
   }
 }
 
+// ---- contiguous NCHW, channels of at most 8 K elements: the channel in registers ----------------
+// A CTA per channel; a thread keeps its K * W elements of dy (after the activation prologue) and of
+// x in registers, so both are read once, and the launch is load -> two sums -> coefficients -> dx.
+// A plane (H * W contiguous elements) is cut into vectors of W elements (the largest of 8, 4, 2, 1
+// that divides H * W: no vector crosses a plane, every vector is aligned); vector e of the channel
+// belongs to thread e % blockDim, slot e / blockDim. For tensors of a few hundred KB a launch is a
+// handful of dependent steps, and what counts is how few instructions lie on that path, not bytes.
+// Both sums go through one pair of shuffle trees (fixed order, fp32: a thread adds at most 8 terms
+// and the trees above it have ten levels).
+template <typename T, int W>
+struct alignas(W * sizeof(T)) BwdPlaneVec {
+  T v[W];
+};
+
+template <typename T, int K, int W, bool HAS_ACT>
+__global__ void __launch_bounds__(1024) bn_bwd_nchw_small_kernel(const BnBwdParams p, const FastDiv vpp_div) {
+  __shared__ float part[2][32];
+  using Vec = BwdPlaneVec<T, W>;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = (int)blockDim.x >> 5;
+  const int c = blockIdx.x;
+  const unsigned int hw = (unsigned int)p.spatial;
+  const unsigned int vpp = hw / W;  // vectors per plane
+  const unsigned int nvec = (unsigned int)p.rows * vpp;
+  const unsigned int plane_stride = (unsigned int)p.channels * hw;  // the launcher admits < 2^31 elements in all
+  const size_t base = (size_t)c * hw;
+  const T* dyc = reinterpret_cast<const T*>(p.dy) + base;
+  const T* xc = reinterpret_cast<const T*>(p.x) + base;
+  const T* actc = HAS_ACT ? reinterpret_cast<const T*>(p.act) + base : nullptr;
+  unsigned int off[K];
+  Vec g_raw[K], x_raw[K], a_raw[HAS_ACT ? K : 1];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const unsigned int e = (unsigned int)k * blockDim.x + (unsigned int)tid;
+    const unsigned int n = fast_div(e, vpp_div);
+    off[k] = n * plane_stride + (e - n * vpp) * W;
+    if (e < nvec) {
+      g_raw[k] = *reinterpret_cast<const Vec*>(dyc + off[k]);
+      x_raw[k] = *reinterpret_cast<const Vec*>(xc + off[k]);
+      if constexpr (HAS_ACT) a_raw[k] = *reinterpret_cast<const Vec*>(actc + off[k]);
+    }
+  }
+  const float mean = __ldg(p.mean + c);
+  const float invstd = __ldg(p.invstd + c);
+  const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
+  float g[K][W], xm[K][W];
+  float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const unsigned int e = (unsigned int)k * blockDim.x + (unsigned int)tid;
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      g[k][j] = 0.f;
+      xm[k][j] = 0.f;
+      if (e < nvec) {
+        float gv = Elem<T>::to_f32(g_raw[k].v[j]);
+        if constexpr (HAS_ACT) {
+          gv = Elem<T>::to_f32(a_raw[k].v[j]) > 0.f ? gv : gv * p.slope;
+          gv = Elem<T>::to_f32(Elem<T>::from_f32(gv));  // the graph rounds dy' to the tensor dtype
+        }
+        g[k][j] = gv;
+        xm[k][j] = Elem<T>::to_f32(x_raw[k].v[j]) - mean;
+      }
+      s1 += g[k][j];
+      s2 += g[k][j] * xm[k][j];
+    }
+  }
+  s1 = warp_reduce<SumOp>(s1);
+  s2 = warp_reduce<SumOp>(s2);
+  if (nwarps > 1) {
+    if (lane == 0) {
+      part[0][warp] = s1;
+      part[1][warp] = s2;
+    }
+    __syncthreads();
+    s1 = warp_reduce<SumOp>(lane < nwarps ? part[0][lane] : 0.f);
+    s2 = warp_reduce<SumOp>(lane < nwarps ? part[1][lane] : 0.f);
+  }
+  if (tid == 0) {
+    if (p.dbias) p.dbias[c] = s1;
+    if (p.dweight) p.dweight[c] = s2 * invstd;
+  }
+  if (p.dx == nullptr) return;
+  const float c1 = s1 * p.inv_count, c2 = (s2 * p.inv_count) * (invstd * invstd), gs = invstd * w;
+  T* dxc = reinterpret_cast<T*>(p.dx) + base;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const unsigned int e = (unsigned int)k * blockDim.x + (unsigned int)tid;
+    Vec out;
+#pragma unroll
+    for (int j = 0; j < W; ++j) out.v[j] = Elem<T>::from_f32(((g[k][j] - xm[k][j] * c2) - c1) * gs);
+    if (e < nvec) *reinterpret_cast<Vec*>(dxc + off[k]) = out;
+  }
+}
+
+template <typename T, int K, int W>
+static void launch_bn_bwd_small_k(const BnBwdParams& p, int threads, const FastDiv& d, cudaStream_t st) {
+  if (p.act) bn_bwd_nchw_small_kernel<T, K, W, true><<<(unsigned)p.channels, threads, 0, st>>>(p, d);
+  else bn_bwd_nchw_small_kernel<T, K, W, false><<<(unsigned)p.channels, threads, 0, st>>>(p, d);
+}
+
+// At most 8 elements of each tensor per thread; as few vectors per thread as 512 threads allow.
+template <typename T, int W>
+static void launch_bn_bwd_small(const BnBwdParams& p, cudaStream_t st) {
+  const long long nvec = p.rows * p.spatial / W;
+  constexpr int KMAX = 8 / W;
+  int K = 1;
+  while (K < KMAX && nvec > 512LL * K) K *= 2;
+  int threads = (int)((nvec + K - 1) / K);
+  threads = (threads + 31) / 32 * 32;
+  const FastDiv d = make_fast_div(p.spatial / W);
+  if (K == 1) launch_bn_bwd_small_k<T, 1, W>(p, threads, d, st);
+  if constexpr (KMAX >= 2) if (K == 2) launch_bn_bwd_small_k<T, 2, W>(p, threads, d, st);
+  if constexpr (KMAX >= 4) if (K == 4) launch_bn_bwd_small_k<T, 4, W>(p, threads, d, st);
+  if constexpr (KMAX >= 8) if (K == 8) launch_bn_bwd_small_k<T, 8, W>(p, threads, d, st);
+}
+
 template <typename T>
 static bool try_launch_bn_bwd_nchw(const BnBwdParams& p, cudaStream_t st, int* rc) {
   static const bool off = [] {
@@ -600,8 +725,22 @@ static bool try_launch_bn_bwd_nchw(const BnBwdParams& p, cudaStream_t st, int* r
   static const int force = [] {
     const char* e = getenv("B200_BN_NCHW_FORCE");
     if (!e) return 0;
-    return e[0] == 'w' ? 1 : (e[0] == 'c' && e[1] == 't' ? 2 : (e[0] == 'c' ? 3 : 0));
+    return e[0] == 'w' ? 1 : (e[0] == 'c' && e[1] == 't' ? 2 : (e[0] == 'c' ? 3 : (e[0] == 'r' ? 4 : 0)));
   }();
+  {  // channels of at most 8 K elements: the register-resident kernel, as few elements per thread as 512 threads allow
+    const long long elems = p.rows * p.spatial;
+    if ((force == 0 || force == 4) && elems <= 8192 && elems * p.channels < 0x7fffffffLL) {
+      constexpr int WMAX = 16 / (int)sizeof(T);  // elements of a 16-byte access
+      int W = WMAX;
+      while (W > 1 && p.spatial % W != 0) W /= 2;  // the tensors are 16-byte aligned (checked above)
+      if (W == 8) { if constexpr (WMAX >= 8) launch_bn_bwd_small<T, 8>(p, st); }
+      else if (W == 4) launch_bn_bwd_small<T, 4>(p, st);
+      else if (W == 2) launch_bn_bwd_small<T, 2>(p, st);
+      else launch_bn_bwd_small<T, 1>(p, st);
+      *rc = launch_status("b200_batch_norm_bwd [NCHW, one launch, CTA per channel, channel in registers]");
+      return true;
+    }
+  }
   // very little data per channel (one round of loads for a warp) and enough channels: a warp per channel
   const bool small = p.rows * p.spatial * (long long)sizeof(T) <= 2048 && p.channels >= 256;
   if (force == 1 || (force == 0 && small)) {  // little data per channel: a warp per channel
@@ -658,11 +797,15 @@ static int launch_bn_bwd(BnBwdParams p, bool fast, size_t scratch_bytes, cudaStr
   const DeviceInfo& dev = device_info();
   const long long coef_floats = 4LL * p.channels;
   if (fast) {
-    const int vpr = p.channels / V;
-    const int threads = 256 / vpr * vpr;  // a multiple of vpr: a thread stays in one vector column
-    const long long total = p.rows * vpr;
+    long long g = p.channels, h = V;  // gcd(C, V)
+    while (h) { const long long t = g % h; g = h; h = t; }
+    const int vpr = (int)(p.channels / g);  // PV: vectors after which the channel pattern repeats
+    const int threads = 256 / vpr * vpr;  // a multiple of PV: a thread keeps its phase
+    const long long total = p.rows * p.channels / V;
     long long splits = 8LL * dev.sm_count;  // eight CTAs per SM
-    if (splits * threads * 4 > total) splits = (total + threads * 4 - 1) / (threads * 4);
+    // at least two rounds of loads (8 vectors of each tensor) per thread: small tensors get few
+    // partial rows and a short finalize
+    if (splits * threads * 8 > total) splits = (total + threads * 8 - 1) / (threads * 8);
     if (splits < 1) splits = 1;
     long long per = (total + splits - 1) / splits;
     per = (per + vpr - 1) / vpr * vpr;  // whole rows per CTA: the column of a thread stays fixed
@@ -672,13 +815,13 @@ static int launch_bn_bwd(BnBwdParams p, bool fast, size_t scratch_bytes, cudaStr
       return fail(B200_ERR_WORKSPACE, "b200_batch_norm_bwd: scratch of %zu bytes, need %lld", scratch_bytes, need);
     p.splits = (int)splits;
     p.coef = reinterpret_cast<float*>(p.partials + splits * 2 * p.channels);
-    bn_bwd_sums_cl_kernel<T><<<(unsigned)splits, threads, 0, st>>>(p, per);
+    bn_bwd_sums_cl_kernel<T><<<(unsigned)splits, threads, 0, st>>>(p, per, vpr);
     int rc = launch_status("b200_batch_norm_bwd sums");
     if (rc != B200_OK) return rc;
     bn_bwd_finalize_kernel<<<p.channels, 256, 0, st>>>(p);
     rc = launch_status("b200_batch_norm_bwd finalize");
     if (rc != B200_OK || !p.dx) return rc;
-    bn_bwd_apply_cl_kernel<T><<<(unsigned)splits, threads, 0, st>>>(p, per);
+    bn_bwd_apply_cl_kernel<T><<<(unsigned)splits, threads, 0, st>>>(p, per, vpr);
     return launch_status("b200_batch_norm_bwd apply [channels-last, vector]");
   }
   {  // contiguous NCHW: one launch, a cluster of CTAs per channel
@@ -746,8 +889,12 @@ extern "C" int b200_batch_norm_bwd_ex(const void* dy, const void* x, const void*
   const int eb = dtype_size(x_dtype);
   const int v = 16 / eb;
   const bool cl = stride_c == 1 && stride_s == channels && stride_n == spatial * channels;
-  const long long vpr = channels / v;
-  const bool fast = cl && channels % v == 0 && vpr >= 1 && vpr <= 256 && aligned16(dy) &&
+  // vectors after which the pattern of channels under a vector repeats: C / gcd(C, v); the flat
+  // kernels need whole periods and at most 256 vectors in one
+  long long g = channels, h = v;
+  while (h) { const long long t = g % h; g = h; h = t; }
+  const long long pv = channels / g;
+  const bool fast = cl && pv >= 1 && pv <= 256 && (batch * spatial * channels) % (pv * v) == 0 && aligned16(dy) &&
                     aligned16(x) && (!act || aligned16(act)) && (!dx || aligned16(dx));
   p.rows = fast ? batch * spatial : batch;
   switch (x_dtype) {

@@ -120,9 +120,10 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
   // while pass 1 runs instead of costing a round trip of its own later
   const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
   const float b = p.bias ? load_param1(p.bias, p.w_dtype, c) : 0.f;
+  float old_mean = 0.f, old_var = 0.f;
   if (tid == 0 && p.running_mean) {
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.running_mean + c));
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.running_var + c));
+    old_mean = __ldcg(p.running_mean + c);
+    old_var = __ldcg(p.running_var + c);
   }
 
   // ---- pass 1 ----------------------------------------------------------------------------------
@@ -184,7 +185,7 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
         t2 += remote[1];
       }
       float mean, invstd;
-      bn_channel_stats(p, c, t1, t2, shift, cluster.block_rank() == 0, &mean, &invstd);
+      bn_channel_stats(p, c, t1, t2, shift, cluster.block_rank() == 0, &mean, &invstd, true, old_mean, old_var);
       stat[0] = mean;
       stat[1] = invstd;
     }
@@ -192,7 +193,7 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
   } else {
     if (tid == 0) {
       float mean, invstd;
-      bn_channel_stats(p, c, cta_tot[0], cta_tot[1], shift, true, &mean, &invstd);
+      bn_channel_stats(p, c, cta_tot[0], cta_tot[1], shift, true, &mean, &invstd, true, old_mean, old_var);
       stat[0] = mean;
       stat[1] = invstd;
     }
@@ -264,9 +265,10 @@ batch_norm_nchw_warp_kernel(const BatchNormParams p, const int G) {
   const f32x2 shift2 = splat2(shift);
   const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;  // requested now, needed after the statistics
   const float b = p.bias ? load_param1(p.bias, p.w_dtype, c) : 0.f;
+  float old_mean = 0.f, old_var = 0.f;
   if (lane32 == 0 && p.running_mean) {
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.running_mean + c));
-    asm volatile("prefetch.global.L2 [%0];" ::"l"(p.running_var + c));
+    old_mean = __ldcg(p.running_mean + c);
+    old_var = __ldcg(p.running_var + c);
   }
 
   double d1 = 0.0, d2 = 0.0;
@@ -300,7 +302,7 @@ batch_norm_nchw_warp_kernel(const BatchNormParams p, const int G) {
     d2 += __shfl_xor_sync(0xffffffffu, d2, o);
   }
   float mean = 0.f, invstd = 0.f;
-  if (lane32 == 0) bn_channel_stats(p, c, d1, d2, shift, true, &mean, &invstd);
+  if (lane32 == 0) bn_channel_stats(p, c, d1, d2, shift, true, &mean, &invstd, true, old_mean, old_var);
   mean = __shfl_sync(0xffffffffu, mean, 0);
   invstd = __shfl_sync(0xffffffffu, invstd, 0);
   if (p.y == nullptr) return;
@@ -334,6 +336,132 @@ batch_norm_nchw_warp_kernel(const BatchNormParams p, const int G) {
   }
 }
 
+
+// Sum over the CTA, the same value in every thread: a shuffle tree inside each warp, one word per
+// warp through shared memory, and the same tree again over those words in every warp. Fixed
+// order, so the result is reproducible. `part` belongs to this call alone (32 floats).
+__device__ __forceinline__ float cta_sum_all(float v, float* part, int lane, int warp, int nwarps) {
+  v = warp_reduce<SumOp>(v);
+  if (nwarps == 1) return v;
+  if (lane == 0) part[warp] = v;
+  __syncthreads();
+  return warp_reduce<SumOp>(lane < nwarps ? part[lane] : 0.f);
+}
+
+// W consecutive elements of a plane, moved with one access of W * sizeof(T) bytes.
+template <typename T, int W>
+struct alignas(W * sizeof(T)) PlaneVec {
+  T v[W];
+};
+
+// Channels of at most 16 K elements (N * H * W): the shape class of two thirds of the BatchNorm
+// points of the reference's corpus (tensors of 50 KB to a few MB, where a launch is a handful of
+// dependent steps and every instruction on that path counts, not bytes). A CTA per channel; a
+// thread keeps its K * W elements in registers, so x is read once, and it does nothing but
+//   load -> sum -> mean -> centred sum of squares -> invstd -> normalise -> store
+// with two CTA-wide sums. A plane (H * W contiguous elements) is cut into vectors of W elements
+// (W = 8, 4, 2 or 1, the largest that divides H * W, so that no vector crosses a plane and every
+// vector is aligned); vector e of the channel belongs to thread e % blockDim (slot e / blockDim).
+// The two-pass form needs no shift and keeps everything in fp32: a thread adds at most 16 terms
+// and the trees above it have ten levels.
+template <typename T, int K, int W>
+__global__ void __launch_bounds__(1024)
+batch_norm_nchw_small_kernel(const BatchNormParams p, const FastDiv vpp_div) {
+  __shared__ float part[2][32];
+  using Vec = PlaneVec<T, W>;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = (int)blockDim.x >> 5;
+  const int c = blockIdx.x;
+  const unsigned int hw = (unsigned int)p.spatial;
+  const unsigned int vpp = hw / W;  // vectors per plane
+  const unsigned int nvec = (unsigned int)p.rows * vpp;
+  const unsigned int plane_stride = (unsigned int)p.channels * hw;  // the launcher admits < 2^31 elements in all
+  const T* xc = reinterpret_cast<const T*>(p.x) + (size_t)c * hw;
+  unsigned int off[K];
+  Vec raw[K];
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const unsigned int e = (unsigned int)k * blockDim.x + (unsigned int)tid;
+    const unsigned int n = fast_div(e, vpp_div);
+    off[k] = n * plane_stride + (e - n * vpp) * W;
+    if (e < nvec) raw[k] = *reinterpret_cast<const Vec*>(xc + off[k]);
+  }
+  // what the end of the kernel needs besides x: requested now, used after the statistics
+  const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
+  const float b = p.bias ? load_param1(p.bias, p.w_dtype, c) : 0.f;
+  float old_mean = 0.f, old_var = 0.f;
+  if (tid == 0 && p.running_mean) {
+    old_mean = __ldcg(p.running_mean + c);
+    old_var = __ldcg(p.running_var + c);
+  }
+  float v[K][W];
+  float s = 0.f;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const unsigned int e = (unsigned int)k * blockDim.x + (unsigned int)tid;
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      v[k][j] = e < nvec ? Elem<T>::to_f32(raw[k].v[j]) : 0.f;
+      s += v[k][j];
+    }
+  }
+  const float inv_count = (float)p.inv_count;
+  const float mean = cta_sum_all(s, part[0], lane, warp, nwarps) * inv_count;
+  float q = 0.f;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const unsigned int e = (unsigned int)k * blockDim.x + (unsigned int)tid;
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      const float d = e < nvec ? v[k][j] - mean : 0.f;
+      q += d * d;
+    }
+  }
+  const float var = cta_sum_all(q, part[1], lane, warp, nwarps) * inv_count;
+  const float invstd = __frsqrt_rn(var + p.eps);
+  if (tid == 0) {
+    if (p.save_mean) p.save_mean[c] = mean;
+    if (p.save_invstd) p.save_invstd[c] = invstd;
+    if (p.running_mean) {
+      p.running_mean[c] = mean * p.momentum + old_mean * p.one_minus_momentum;
+      p.running_var[c] = (var * p.unbias) * p.momentum + old_var * p.one_minus_momentum;
+    }
+  }
+  if (p.y == nullptr) return;
+  T* yc = reinterpret_cast<T*>(p.y) + (size_t)c * hw;
+  const bool relu = p.relu != 0;
+#pragma unroll
+  for (int k = 0; k < K; ++k) {
+    const unsigned int e = (unsigned int)k * blockDim.x + (unsigned int)tid;
+    Vec out;
+#pragma unroll
+    for (int j = 0; j < W; ++j) {
+      float o = ((v[k][j] - mean) * invstd) * w + b;
+      if (relu) o = o < 0.f ? 0.f : o;
+      out.v[j] = Elem<T>::from_f32(o);
+    }
+    if (e < nvec) *reinterpret_cast<Vec*>(yc + off[k]) = out;
+  }
+}
+
+// At most 16 elements per thread; as few vectors per thread as 512 threads allow (1024 threads for
+// the largest channels).
+template <typename T, int W>
+static void launch_small(const BatchNormParams& p, cudaStream_t st) {
+  const long long nvec = p.rows * p.spatial / W;
+  constexpr int KMAX = 16 / W;
+  int K = 1;
+  while (K < KMAX && nvec > 512LL * K) K *= 2;
+  int threads = (int)((nvec + K - 1) / K);
+  threads = (threads + 31) / 32 * 32;
+  const FastDiv d = make_fast_div(p.spatial / W);
+  const unsigned grid = (unsigned)p.channels;
+  if (K == 1) batch_norm_nchw_small_kernel<T, 1, W><<<grid, threads, 0, st>>>(p, d);
+  if constexpr (KMAX >= 2) if (K == 2) batch_norm_nchw_small_kernel<T, 2, W><<<grid, threads, 0, st>>>(p, d);
+  if constexpr (KMAX >= 4) if (K == 4) batch_norm_nchw_small_kernel<T, 4, W><<<grid, threads, 0, st>>>(p, d);
+  if constexpr (KMAX >= 8) if (K == 8) batch_norm_nchw_small_kernel<T, 8, W><<<grid, threads, 0, st>>>(p, d);
+  if constexpr (KMAX >= 16) if (K == 16) batch_norm_nchw_small_kernel<T, 16, W><<<grid, threads, 0, st>>>(p, d);
+}
+
 }  // namespace
 
 template <typename T>
@@ -349,12 +477,31 @@ bool try_launch_batch_norm_nchw(const BatchNormParams& p, cudaStream_t st, int* 
   const DeviceInfo& dev = device_info();
   const long long plane_vecs = (p.spatial * (long long)sizeof(T) + 15) / 16;
   // little data per channel and enough channels: a warp per channel
-  // measurement switch: B200_BN_NCHW_FORCE=warp|cta|cluster picks the variant whatever the shape
+  // measurement switch: B200_BN_NCHW_FORCE=warp|cta|cluster|registers picks the variant whatever the shape
   static const int force = [] {
     const char* e = getenv("B200_BN_NCHW_FORCE");
     if (!e) return 0;
-    return e[0] == 'w' ? 1 : (e[0] == 'c' && e[1] == 't' ? 2 : (e[0] == 'c' ? 3 : 0));
+    return e[0] == 'w' ? 1 : (e[0] == 'c' && e[1] == 't' ? 2 : (e[0] == 'c' ? 3 : (e[0] == 'r' ? 4 : 0)));
   }();
+  // channels of at most 16 K elements: the register-resident kernel, as few elements per thread as
+  // 512 threads allow (1024 threads for the largest channels)
+  {
+    const long long elems = p.rows * p.spatial;
+    const long long total = elems * p.channels;
+    if ((force == 0 || force == 4) && elems <= 16384 && total < 0x7fffffffLL) {
+      constexpr int WMAX = 16 / (int)sizeof(T);  // elements of a 16-byte access
+      int W = WMAX;
+      while (W > 1 && (p.spatial % W != 0 || reinterpret_cast<uintptr_t>(p.x) % (W * sizeof(T)) != 0 ||
+                       reinterpret_cast<uintptr_t>(p.y) % (W * sizeof(T)) != 0))
+        W /= 2;
+      if (W == 8) { if constexpr (WMAX >= 8) launch_small<T, 8>(p, st); }
+      else if (W == 4) launch_small<T, 4>(p, st);
+      else if (W == 2) launch_small<T, 2>(p, st);
+      else launch_small<T, 1>(p, st);
+      *rc = launch_status("b200_batch_norm_fwd [NCHW, one launch, CTA per channel, channel in registers]");
+      return true;
+    }
+  }
   // very little data per channel (one round of loads for a warp) and enough channels: a warp per channel
   const bool small = p.rows * p.spatial * (long long)sizeof(T) <= 4096 && p.channels >= 256;
   if (force == 1 || (force == 0 && small)) {

@@ -169,23 +169,6 @@ __device__ __forceinline__ float warp_reduce_multi(float (&v)[N], int lane) {
   return v[0];
 }
 
-// The occupancy query is a host-side calculation; cached per (kernel, block size, smem).
-inline int cached_occupancy(const void* fn, int threads, size_t smem = 0) {
-  struct Entry { const void* fn; int threads; size_t smem; int blocks; };
-  static Entry cache[256];
-  static int used = 0;
-  for (int i = 0; i < used; ++i)
-    if (cache[i].fn == fn && cache[i].threads == threads && cache[i].smem == smem) return cache[i].blocks;
-  int blocks = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&blocks, fn, threads, smem) != cudaSuccess) {
-    cudaGetLastError();
-    blocks = 1;
-  }
-  if (blocks < 1) blocks = 1;
-  if (used < 256) cache[used++] = Entry{fn, threads, smem, blocks};
-  return blocks;
-}
-
 // Warp-per-row kernel with per-warp copy rings (norm_bwd_warp.cu): rows of 33..256 vectors.
 // Returns false when the shape does not fit (the caller takes another kernel); otherwise *rc is
 // the launch status.

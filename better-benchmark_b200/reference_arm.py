@@ -321,6 +321,13 @@ def run_parent(args) -> int:
     out_path.parent.mkdir(parents=True, exist_ok=True)
     only = set(args.dirs.split(",")) if args.dirs else None
     tasks = list_tasks(ref_root, args.mode, only, args.max_points)
+    if args.tasks:  # an explicit list: any point of the staged directories, not only the sampled ones
+        wanted = [t for t in args.tasks.split(",") if t]
+        every = set(list_tasks(ref_root, "check", only, 0))
+        unknown = [t for t in wanted if t not in every]
+        if unknown:
+            raise SystemExit(f"unknown task(s): {unknown}")
+        tasks = wanted
     deadline = time.time() + args.budget_s if args.budget_s else None
     env = os.environ.copy()
     env["PYTHONPATH"] = os.pathsep.join(
@@ -434,7 +441,7 @@ def main(argv=None) -> int:
     ap.add_argument("--out", default="reference_arm.jsonl")
     ap.add_argument("--workdir", default="/tmp/b200_reference_arm")
     ap.add_argument("--dirs", default="", help="comma-separated directory names (default: all)")
-    ap.add_argument("--tasks", default="")
+    ap.add_argument("--tasks", default="", help="comma-separated <directory>::<label> tasks instead of the sampled ones")
     ap.add_argument("--max-points", type=int, default=2, help="compare: points per directory (0 = all)")
     ap.add_argument("--warmup", type=int, default=25)
     ap.add_argument("--rep", type=int, default=100)

@@ -216,8 +216,9 @@ int32_t b200_cast_scale(const void* x, void* y, int64_t n, int32_t in_dtype, int
  * mean / invstd are the statistics saved by the forward pass (fp32 [C]). Outputs: dx (may be NULL:
  * sums only), dweight = sum(dy * (x - mean)) * invstd and dbias = sum(dy), fp32 [C] (each may be
  * NULL). `act` (may be NULL) enables the activation-backward prologue dy' = act > 0 ? dy : dy * slope
- * (slope 0: ReLU), rounded to the tensor dtype. Three launches (sums, fp64 finalize, apply), no
- * atomics. Scratch: b200_batch_norm_bwd_scratch_bytes(channels), 16-byte aligned, no initial state.
+ * (slope 0: ReLU), rounded to the tensor dtype. One launch for contiguous NCHW tensors; three
+ * launches (sums, fp64 finalize, apply) for channels-last tensors (flat 16-byte vectors, any channel
+ * count) and for other strides (element-wise). No atomics. Scratch: b200_batch_norm_bwd_scratch_bytes(channels), 16-byte aligned, no initial state.
  * Replaces sum_sum_183b124c731f/oracle.py (partial sums, finalize, apply) and, with the prologue,
  * sum_sum_12fc8ebf8180/oracle.py. */
 int64_t b200_batch_norm_bwd_scratch_bytes(int64_t channels);

@@ -103,3 +103,53 @@ def test_batch_norm_nchw_cluster_kernel(shape, dtype):
     assert_close(rv_d, want[4], f"bn nchw running_var {shape}")
     y2, mean2, _ = k.batch_norm_fwd(x.cuda(), w.cuda(), b.cuda(), None, None, eps=1e-3, momentum=0.1, relu=True)
     assert torch.equal(y, y2) and torch.equal(mean, mean2), "bit-reproducible"
+
+
+@pytest.mark.parametrize("shape,dtype", [((4, 128, 7, 7), torch.bfloat16), ((32, 256, 14, 14), torch.bfloat16),
+                                         ((128, 40, 8, 8), torch.bfloat16), ((16, 24, 9, 9), torch.float32),
+                                         ((1, 5, 3, 3), torch.float16), ((2, 3, 1, 1), torch.float32),
+                                         ((128, 8, 11, 11), torch.float16), ((33, 17, 5, 3), torch.bfloat16)])
+def test_batch_norm_nchw_channel_in_registers(shape, dtype):
+    """Channels of at most 16 K elements take the kernel that keeps a channel in the registers of
+    one CTA (one to sixteen elements per thread, one to thirty-two warps)."""
+    from oracle.eager import BatchNormReluFwd
+    k = _kernels()
+    x, rm, rv, w, b = _inputs(shape, dtype, False, seed=sum(shape) + 3)
+    want = BatchNormReluFwd(1e-3, 0.1, relu=True)(x, rm.clone(), rv.clone(), w, b)
+    rm_d, rv_d = rm.cuda(), rv.cuda()
+    before = k.load().b200_launch_count()
+    y, mean, invstd = k.batch_norm_fwd(x.cuda(), w.cuda(), b.cuda(), rm_d, rv_d, eps=1e-3, momentum=0.1, relu=True)
+    assert k.load().b200_launch_count() - before == 1 and b"channel in registers" in k.load().b200_last_kernel()
+    assert_close(y, want[0], f"bn small y {shape} {dtype}")
+    assert_close(mean, want[1], f"bn small mean {shape}")
+    assert_close(invstd, want[2], f"bn small invstd {shape}")
+    assert_close(rm_d, want[3], f"bn small running_mean {shape}")
+    assert_close(rv_d, want[4], f"bn small running_var {shape}")
+    y2, mean2, _ = k.batch_norm_fwd(x.cuda(), w.cuda(), b.cuda(), None, None, eps=1e-3, momentum=0.1, relu=False)
+    assert torch.equal(mean, mean2), "bit-reproducible"
+    want2 = BatchNormReluFwd(1e-3, 0.1, relu=False)(x, rm.clone(), rv.clone(), w, b)
+    assert_close(y2, want2[0], f"bn small y without relu {shape} {dtype}")
+
+
+@pytest.mark.parametrize("shape,dtype", [((8, 92, 14, 14), torch.bfloat16), ((4, 60, 7, 8), torch.bfloat16),
+                                         ((16, 36, 6, 6), torch.bfloat16), ((8, 100, 5, 4), torch.float32),
+                                         ((6, 58, 4, 4), torch.float16), ((3, 24, 5, 5), torch.bfloat16),
+                                         ((64, 480, 7, 7), torch.bfloat16), ((32, 48, 35, 35), torch.bfloat16)])
+def test_batch_norm_channels_last_any_channel_count(shape, dtype):
+    """Channels-last tensors whose channel count does not make a power-of-two number of vectors per
+    row take the three-launch path over flat vectors (a vector may straddle the end of a row)."""
+    from oracle.eager import BatchNormReluFwd
+    k = _kernels()
+    x, rm, rv, w, b = _inputs(shape, dtype, True, seed=sum(shape) + 5)
+    want = BatchNormReluFwd(1e-3, 0.1, relu=True)(x, rm.clone(), rv.clone(), w, b)
+    rm_d, rv_d = rm.cuda(), rv.cuda()
+    y, mean, invstd = k.batch_norm_fwd(x.cuda(), w.cuda(), b.cuda(), rm_d, rv_d, eps=1e-3, momentum=0.1, relu=True)
+    assert b"flat vectors" in k.load().b200_last_kernel(), k.load().b200_last_kernel()
+    assert y.stride() == x.stride()
+    assert_close(y, want[0], f"bn cl flat y {shape} {dtype}")
+    assert_close(mean, want[1], f"bn cl flat mean {shape}")
+    assert_close(invstd, want[2], f"bn cl flat invstd {shape}")
+    assert_close(rm_d, want[3], f"bn cl flat running_mean {shape}")
+    assert_close(rv_d, want[4], f"bn cl flat running_var {shape}")
+    y2, mean2, _ = k.batch_norm_fwd(x.cuda(), w.cuda(), b.cuda(), None, None, eps=1e-3, momentum=0.1, relu=True)
+    assert torch.equal(y, y2) and torch.equal(mean, mean2), "bit-reproducible"

@@ -82,6 +82,13 @@ def test_batch_norm_bwd_rejects_mismatched_layouts():
     ((32, 128, 16, 16), False, torch.bfloat16, 0.2),    # NCHW: one cluster of CTAs per channel
     ((64, 24, 35, 35), False, torch.bfloat16, None),    # NCHW, planes with unaligned starts
     ((6, 520, 7, 7), False, torch.float32, None),       # NCHW, more channels than the machine has CTA slots
+    ((8, 92, 14, 14), True, torch.bfloat16, 0.1),       # channels-last, 92 channels: vectors straddle rows (period 23 vectors)
+    ((16, 58, 6, 6), True, torch.float16, None),        # 58 channels: period 29 vectors = 4 rows
+    ((4, 100, 5, 4), True, torch.float32, None),        # fp32, 100 channels: period 25 vectors = one row
+    ((32, 512, 4, 4), False, torch.bfloat16, 0.2),      # NCHW, channel in registers: one element per thread
+    ((32, 256, 8, 8), False, torch.bfloat16, None),     # four elements per thread
+    ((3, 7, 5, 5), False, torch.float16, 0.1),          # three warps, ragged
+    ((2, 3, 1, 1), False, torch.float32, None),         # two elements per channel
 ])
 def test_batch_norm_bwd_corpus_layouts(shape, channels_last, dtype, slope):
     from better_benchmark_b200 import kernels
