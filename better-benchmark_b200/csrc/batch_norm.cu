@@ -873,14 +873,17 @@ __global__ void __launch_bounds__(256) batch_norm_stats_general_kernel(const Bat
   }
 }
 
+// rows_shift: the sums were shifted by bn_shift_scalar (channels-last flat path, p.rows = N*H*W)
+// instead of by the channel's first element.
 template <typename T>
 __global__ void __launch_bounds__(256) batch_norm_finalize_general_kernel(const BatchNormParams p,
-                                                                          int num_partials) {
+                                                                          int num_partials, int rows_shift) {
   const int warps = blockDim.x >> 5;
   const int c = blockIdx.x * warps + (threadIdx.x >> 5);
   if (c >= p.channels) return;
   const T* x = reinterpret_cast<const T*>(p.x);
-  bn_finalize_channel<T, false>(p, c, num_partials, Elem<T>::to_f32(x[(long long)c * p.sc]));
+  const float shift = rows_shift ? bn_shift_scalar<T>(x, c, p.channels, p.rows) : Elem<T>::to_f32(x[(long long)c * p.sc]);
+  bn_finalize_channel<T, false>(p, c, num_partials, shift);
 }
 
 template <typename T>
@@ -923,7 +926,7 @@ __global__ void __launch_bounds__(256) batch_norm_apply_general_kernel(const Bat
 // ----------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) batch_norm_sums_cl_flat_kernel(const BatchNormParams p, long long vecs_per_cta,
-                                                                      int PV) {
+                                                                      int PV, int rows_shift) {
   constexpr int V = Elem<T>::V;
   __shared__ float red[2 * 256 * V];  // [2][threads][V]
   const int tid = threadIdx.x, T_ = blockDim.x, C = p.channels;
@@ -934,13 +937,36 @@ __global__ void __launch_bounds__(256) batch_norm_sums_cl_flat_kernel(const Batc
   if (v1 > total) v1 = total;
   const T* xe = reinterpret_cast<const T*>(p.x);
   const uint4* x = reinterpret_cast<const uint4*>(p.x);
+  // The shift of every channel (bn_shift_scalar: mean of its first sixteen rows, eight significant
+  // bits; the finalize kernel forms the same value) is computed once per CTA into shared memory,
+  // at most 2 * 256 * V channels per round, and every thread picks up its V channels.
   f32x2 shift[V / 2], s1[V / 2], s2[V / 2];
+  double deep[V];  // a thread's sum of squares moves here every 16 vectors
 #pragma unroll
-  for (int i = 0; i < V / 2; ++i) {  // the channel's element of row 0, as the finalize kernel assumes
-    shift[i] = pack2(Elem<T>::to_f32(__ldg(xe + (ph * V + 2 * i) % C)), Elem<T>::to_f32(__ldg(xe + (ph * V + 2 * i + 1) % C)));
-    s1[i] = s2[i] = splat2(0.f);
+  for (int i = 0; i < V / 2; ++i) shift[i] = s1[i] = s2[i] = splat2(0.f);
+#pragma unroll
+  for (int i = 0; i < V; ++i) deep[i] = 0.0;
+  if (!rows_shift) {  // short chains (small tensors): the channel's element of row 0 will do
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i)
+      shift[i] = pack2(Elem<T>::to_f32(__ldg(xe + (ph * V + 2 * i) % C)), Elem<T>::to_f32(__ldg(xe + (ph * V + 2 * i + 1) % C)));
+  }
+  for (int c0 = 0; rows_shift && c0 < C; c0 += 2 * 256 * V) {
+    for (int c = c0 + tid; c < C && c < c0 + 2 * 256 * V; c += T_) red[c - c0] = bn_shift_scalar<T>(xe, c, C, p.rows);
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < V / 2; ++i) {
+      const int ca = (ph * V + 2 * i) % C, cb = (ph * V + 2 * i + 1) % C;
+      float lo, hi;
+      unpack2(shift[i], lo, hi);
+      if (ca >= c0 && ca < c0 + 2 * 256 * V) lo = red[ca - c0];
+      if (cb >= c0 && cb < c0 + 2 * 256 * V) hi = red[cb - c0];
+      shift[i] = pack2(lo, hi);
+    }
+    __syncthreads();
   }
   constexpr int U = 8;  // vectors in flight per thread
+  int round = 0;
   for (long long v = v0 + tid; v < v1; v += (long long)U * T_) {
     uint4 raw[U];
 #pragma unroll
@@ -961,13 +987,26 @@ __global__ void __launch_bounds__(256) batch_norm_sums_cl_flat_kernel(const Batc
         }
       }
     }
+    if ((++round & 1) == 0) {
+#pragma unroll
+      for (int i = 0; i < V / 2; ++i) {
+        float lo, hi;
+        unpack2(s2[i], lo, hi);
+        deep[2 * i] += (double)lo;
+        deep[2 * i + 1] += (double)hi;
+        s2[i] = splat2(0.f);
+      }
+    }
   }
   float* r1 = red;
   float* r2 = red + 256 * V;
 #pragma unroll
   for (int i = 0; i < V / 2; ++i) {
+    float lo, hi;
+    unpack2(s2[i], lo, hi);
     unpack2(s1[i], r1[tid * V + 2 * i], r1[tid * V + 2 * i + 1]);
-    unpack2(s2[i], r2[tid * V + 2 * i], r2[tid * V + 2 * i + 1]);
+    r2[tid * V + 2 * i] = (float)(deep[2 * i] + (double)lo);
+    r2[tid * V + 2 * i + 1] = (float)(deep[2 * i + 1] + (double)hi);
   }
   __syncthreads();
   const int period = PV * V;  // elements; a multiple of C
@@ -1062,10 +1101,11 @@ static bool try_launch_batch_norm_cl_flat(BatchNormParams p, size_t scratch_byte
   per = (per + PV - 1) / PV * PV;
   splits = (total + per - 1) / per;
   p.stats = p.partials + splits * 2 * C;
-  batch_norm_sums_cl_flat_kernel<T><<<(unsigned)splits, threads, 0, st>>>(p, per, (int)PV);
+  const int rows_shift = per > 32LL * threads ? 1 : 0;  // more than 32 vectors per thread
+  batch_norm_sums_cl_flat_kernel<T><<<(unsigned)splits, threads, 0, st>>>(p, per, (int)PV, rows_shift);
   *rc = launch_status("b200_batch_norm_fwd sums [channels-last, flat vectors]");
   if (*rc != B200_OK) return true;
-  batch_norm_finalize_general_kernel<T><<<(p.channels + 7) / 8, 256, 0, st>>>(p, (int)splits);
+  batch_norm_finalize_general_kernel<T><<<(p.channels + 7) / 8, 256, 0, st>>>(p, (int)splits, rows_shift);
   *rc = launch_status("b200_batch_norm_fwd finalize");
   if (*rc != B200_OK || !p.y) return true;
   batch_norm_apply_cl_flat_kernel<T><<<(unsigned)splits, threads, 0, st>>>(p, per, (int)PV);
@@ -1234,7 +1274,7 @@ static int launch_batch_norm(BatchNormParams p, bool channels_last_fast, bool ch
   batch_norm_stats_general_kernel<T><<<dim3(p.channels, (unsigned)splits), 256, 0, st>>>(p);
   int rc = launch_status("b200_batch_norm_fwd stats [strided, element-wise]");
   if (rc != B200_OK) return rc;
-  batch_norm_finalize_general_kernel<T><<<(p.channels + 7) / 8, 256, 0, st>>>(p, (int)splits);
+  batch_norm_finalize_general_kernel<T><<<(p.channels + 7) / 8, 256, 0, st>>>(p, (int)splits, 0);
   rc = launch_status("b200_batch_norm_fwd finalize");
   if (rc != B200_OK) return rc;
   if (p.y) {

@@ -148,6 +148,29 @@ def _rms_bwd_scalar_inputs(device="cuda", seed=1):
             (torch.rand(512, generator=_gen(seed)) + 0.5).to(device), rstd]
 
 
+def _bn_nchw_small_inputs(device="cuda", seed=1):
+    c = 384
+    return [_randn((128, c, 8, 8), torch.bfloat16, seed, device), torch.zeros(c, device=device),
+            torch.ones(c, device=device), (torch.rand(c, generator=_gen(seed)) + 0.5).to(device),
+            (torch.rand(c, generator=_gen(seed + 1)) - 0.5).to(device)]
+
+
+def _bn_cl_odd_inputs(device="cuda", seed=1):
+    c = 92
+    x = _randn((512, c, 14, 14), torch.bfloat16, seed, device).contiguous(memory_format=torch.channels_last)
+    return [x, torch.zeros(c, device=device), torch.ones(c, device=device),
+            (torch.rand(c, generator=_gen(seed)) + 0.5).to(device), (torch.rand(c, generator=_gen(seed + 1)) - 0.5).to(device)]
+
+
+def _ln_bwd_scalar_inputs(device="cuda", seed=1):
+    x = _randn((262144, 512), torch.bfloat16, seed, device)
+    xf = x.float()
+    mean = xf.mean(dim=1)
+    rstd = torch.rsqrt(xf.var(dim=1, unbiased=False) + 1e-5)
+    return [x, torch.tensor(0.75, dtype=torch.bfloat16, device=device),
+            (torch.rand(512, generator=_gen(seed)) + 0.5).to(device), mean, rstd]
+
+
 def _transpose_small_inputs(device="cuda", seed=1):
     return [_randn((16384, 49, 128), torch.bfloat16, seed, device), [16384, 128, 49]]
 
@@ -207,6 +230,15 @@ FAMILY_CASES = {c.name: c for c in [
     _case("rms_norm_bwd_scalar_dy_bf16", "RMSNorm backward, dy a broadcast scalar: x bf16 [262144, 512] -> dx bf16, dweight f32",
           "bf16", 2 * 262144 * 512 * 2 + 262144 * 4 + 2 * 512 * 4, _rms_bwd_scalar_inputs,
           lambda i: kernels.norm_bwd(i[0], i[1], i[2], i[3], rms=True)),
+    _case("batch_norm_relu_nchw_small_bf16", "BatchNorm2d train fwd + ReLU, channel in registers: x bf16 NCHW [128,384,8,8]", "bf16",
+          2 * 128 * 384 * 64 * 2 + 6 * 384 * 4, _bn_nchw_small_inputs,
+          lambda i: kernels.batch_norm_fwd(i[0], i[3], i[4], i[1], i[2], eps=1e-3, momentum=0.1, relu=True)),
+    _case("batch_norm_relu_cl_c92_bf16", "BatchNorm2d train fwd + ReLU, 92 channels: x bf16 channels_last [512,92,14,14]", "bf16",
+          2 * 512 * 92 * 196 * 2 + 6 * 92 * 4, _bn_cl_odd_inputs,
+          lambda i: kernels.batch_norm_fwd(i[0], i[3], i[4], i[1], i[2], eps=1e-3, momentum=0.1, relu=True)),
+    _case("layer_norm_bwd_scalar_dy_bf16", "LayerNorm backward, dy a broadcast scalar: x bf16 [262144, 512] -> dx bf16, dweight, dbias f32",
+          "bf16", 2 * 262144 * 512 * 2 + 2 * 262144 * 4 + 3 * 512 * 4, _ln_bwd_scalar_inputs,
+          lambda i: kernels.norm_bwd(i[0], i[1], i[2], i[4], mean=i[3], rms=False, want_dbias=True)),
     _case("transpose_small_bf16", "[16384, 49, 128] -> [16384, 128, 49] contiguous copy, bf16", "bf16",
           2 * 16384 * 49 * 128 * 2, _transpose_small_inputs, lambda i: permute.transpose_forward(i)),
 ]}
