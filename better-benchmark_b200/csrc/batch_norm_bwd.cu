@@ -520,79 +520,6 @@ bn_bwd_nchw_cluster_kernel(const BnBwdParams p, const int imgs_per_cta, const in
   }
 }
 
-// Channels with little data: a warp per channel, eight channels per CTA, no shared memory, no
-// barrier (see batch_norm_nchw_warp_kernel in batch_norm_nchw.cu for the reasoning).
-template <typename T, bool HAS_ACT>
-__global__ void __launch_bounds__(256) bn_bwd_nchw_warp_kernel(const BnBwdParams p, const int G) {
-  constexpr int V = Elem<T>::V;
-  constexpr int P = V / 2;
-  const int lane32 = threadIdx.x & 31;
-  const int c = (int)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (c >= p.channels) return;  // whole warps leave; nothing below synchronises across warps
-  const int lane = lane32 % G, grp = lane32 / G, groups = 32 / G;
-  const int hw = (int)p.spatial;
-  const int n_total = (int)p.rows;
-  const long long plane_stride = (long long)p.channels * hw;
-  const T* dyc = reinterpret_cast<const T*>(p.dy) + (long long)c * hw;
-  const T* xc = reinterpret_cast<const T*>(p.x) + (long long)c * hw;
-  const T* actc = HAS_ACT ? reinterpret_cast<const T*>(p.act) + (long long)c * hw : nullptr;
-  T* dxc = p.dx ? reinterpret_cast<T*>(p.dx) + (long long)c * hw : nullptr;
-  const float mean = __ldg(p.mean + c);
-  const float invstd = __ldg(p.invstd + c);
-  const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;
-  const f32x2 mean2 = splat2(mean);
-  const float slope = p.slope;
-
-  double d1 = 0.0, d2 = 0.0;
-  for (int n = grp; n < n_total; n += groups) {
-    const long long off = (long long)n * plane_stride;
-    float s1 = 0.f, s2 = 0.f;
-    f32x2 a1 = splat2(0.f), a2 = splat2(0.f);
-    bn_bwd_visit_plane<T, HAS_ACT>(
-        dyc + off, xc + off, HAS_ACT ? actc + off : nullptr, hw, lane, G, slope,
-        [&](int, float g, float xv) {
-          s1 += g;
-          s2 += g * (xv - mean);
-        },
-        [&](int, const f32x2 (&g)[P], const f32x2 (&xv)[P]) {
-#pragma unroll
-          for (int k = 0; k < P; ++k) {
-            a1 = add2(a1, g[k]);
-            a2 = add2(a2, mul2(g[k], sub2(xv[k], mean2)));
-          }
-        });
-    d1 += (double)s1 + (double)hsum2(a1);
-    d2 += (double)s2 + (double)hsum2(a2);
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    d1 += __shfl_xor_sync(0xffffffffu, d1, o);
-    d2 += __shfl_xor_sync(0xffffffffu, d2, o);
-  }
-  const float sum_dy = (float)d1, dot = (float)d2;  // every lane holds the warp totals
-  if (lane32 == 0) {
-    if (p.dbias) p.dbias[c] = sum_dy;
-    if (p.dweight) p.dweight[c] = dot * invstd;
-  }
-  if (dxc == nullptr) return;
-  const float c1 = sum_dy * p.inv_count, c2 = (dot * p.inv_count) * (invstd * invstd), gs = invstd * w;
-  const f32x2 c1v = splat2(c1), c2v = splat2(c2), gsv = splat2(gs);
-  for (int n = n_total - 1 - grp; n >= 0; n -= groups) {
-    const long long off = (long long)n * plane_stride;
-    T* out = dxc + off;
-    bn_bwd_visit_plane<T, HAS_ACT>(
-        dyc + off, xc + off, HAS_ACT ? actc + off : nullptr, hw, lane, G, slope,
-        [&](int i, float g, float xv) { out[i] = Elem<T>::from_f32(((g - (xv - mean) * c2) - c1) * gs); },
-        [&](int i, const f32x2 (&g)[P], const f32x2 (&xv)[P]) {
-          f32x2 o[P];
-#pragma unroll
-          for (int k = 0; k < P; ++k)
-            o[k] = mul2(sub2(sub2(g[k], mul2(sub2(xv[k], mean2), c2v)), c1v), gsv);
-          st_stream(out + i, Pairs<T>::pack(o));
-        });
-  }
-}
-
 // ---- contiguous NCHW, channels of at most 8 K elements: the channel in registers ----------------
 // A CTA per channel; a thread keeps its K * W elements of dy (after the activation prologue) and of
 // x in registers, so both are read once, and the launch is load -> two sums -> coefficients -> dx.
@@ -721,11 +648,11 @@ static bool try_launch_bn_bwd_nchw(const BnBwdParams& p, cudaStream_t st, int* r
   if (!aligned16(p.dy) || !aligned16(p.x) || (p.act && !aligned16(p.act)) || (p.dx && !aligned16(p.dx))) return false;
   const DeviceInfo& dev = device_info();
   const long long plane_vecs = (p.spatial * (long long)sizeof(T) + 15) / 16;
-  // measurement switch: B200_BN_NCHW_FORCE=warp|cta|cluster picks the variant whatever the shape
+  // measurement switch: B200_BN_NCHW_FORCE=cta|cluster|registers picks the variant whatever the shape
   static const int force = [] {
     const char* e = getenv("B200_BN_NCHW_FORCE");
     if (!e) return 0;
-    return e[0] == 'w' ? 1 : (e[0] == 'c' && e[1] == 't' ? 2 : (e[0] == 'c' ? 3 : (e[0] == 'r' ? 4 : 0)));
+    return e[0] == 'c' && e[1] == 't' ? 2 : (e[0] == 'c' ? 3 : (e[0] == 'r' ? 4 : 0));
   }();
   {  // channels of at most 8 K elements: the register-resident kernel, as few elements per thread as 512 threads allow
     const long long elems = p.rows * p.spatial;
@@ -740,17 +667,6 @@ static bool try_launch_bn_bwd_nchw(const BnBwdParams& p, cudaStream_t st, int* r
       *rc = launch_status("b200_batch_norm_bwd [NCHW, one launch, CTA per channel, channel in registers]");
       return true;
     }
-  }
-  // very little data per channel (one round of loads for a warp) and enough channels: a warp per channel
-  const bool small = p.rows * p.spatial * (long long)sizeof(T) <= 2048 && p.channels >= 256;
-  if (force == 1 || (force == 0 && small)) {  // little data per channel: a warp per channel
-    int G = 32;
-    while (G > 2 && 32 / (G / 2) <= 2 * p.rows && plane_vecs <= 4LL * (G / 2)) G /= 2;
-    const unsigned grid = (unsigned)((p.channels + 7) / 8);
-    if (p.act) bn_bwd_nchw_warp_kernel<T, true><<<grid, 256, 0, st>>>(p, G);
-    else bn_bwd_nchw_warp_kernel<T, false><<<grid, 256, 0, st>>>(p, G);
-    *rc = launch_status("b200_batch_norm_bwd [NCHW, one launch, warp per channel]");
-    return true;
   }
   int S = 1;  // several CTAs per channel only when a channel holds enough data (see batch_norm_nchw.cu)
   if (p.rows * p.spatial * (long long)sizeof(T) >= 128 * 1024)

@@ -1,10 +1,13 @@
 // BatchNorm2d training forward (+ReLU, running statistics) on a contiguous NCHW tensor, in ONE
-// launch: the CTAs that share a channel form a thread-block cluster and exchange their partial
-// sums through distributed shared memory.
+// launch.
 //
 // Most BatchNorm points of the reference's corpus are NCHW (95 of the 121 shape points of
 // repros/canonical/var_mean_42fad1ece813/shapes.json), from 50 KB to 100 MB. Its Triton plan for
-// them is three launches (partial sums, finalize, normalise; oracle.py:11-119). Here:
+// them is one launch up to 1024 elements per channel and three launches (partial sums, finalize,
+// normalise; oracle.py:11-119) above. Here a channel of at most 16 K elements is kept in the
+// registers of one CTA (batch_norm_nchw_small_kernel, further down); larger channels take the
+// two-pass kernel below, whose CTAs of one channel form a thread-block cluster and exchange their
+// partial sums through distributed shared memory:
 //
 //   grid (S, C), cluster (S, 1, 1): CTA (s, c) owns images [s * ipc, (s + 1) * ipc) of channel c.
 //   pass 1  every plane (the H*W contiguous elements of one image and channel) is walked by a
@@ -242,101 +245,6 @@ batch_norm_nchw_cluster_kernel(const BatchNormParams p, const int imgs_per_cta, 
 #endif
 }
 
-// Channels with little data (a few thousand elements over all images): a WARP per channel, eight
-// channels per CTA, no shared memory and no barrier at all. With a CTA per channel such a tensor
-// (hundreds of channels of a few hundred bytes each) is a grid of hundreds of CTAs that each wait
-// for three round trips to memory; here it is a fraction of a wave. Groups of G lanes walk the
-// planes of the channel side by side; the warp combines with shuffles (fp64, fixed order).
-template <typename T>
-__global__ void __launch_bounds__(kThreads)
-batch_norm_nchw_warp_kernel(const BatchNormParams p, const int G) {
-  constexpr int V = Elem<T>::V;
-  constexpr int P = V / 2;
-  const int lane32 = threadIdx.x & 31;
-  const int c = (int)blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
-  if (c >= p.channels) return;  // whole warps leave; nothing below synchronises across warps
-  const int lane = lane32 % G, grp = lane32 / G, groups = 32 / G;
-  const int hw = (int)p.spatial;
-  const int n_total = (int)p.rows;
-  const long long plane_stride = (long long)p.channels * hw;
-  const T* xc = reinterpret_cast<const T*>(p.x) + (long long)c * hw;
-  T* yc = reinterpret_cast<T*>(p.y) + (long long)c * hw;
-  const float shift = Elem<T>::to_f32(__ldg(xc));
-  const f32x2 shift2 = splat2(shift);
-  const float w = p.weight ? load_param1(p.weight, p.w_dtype, c) : 1.f;  // requested now, needed after the statistics
-  const float b = p.bias ? load_param1(p.bias, p.w_dtype, c) : 0.f;
-  float old_mean = 0.f, old_var = 0.f;
-  if (lane32 == 0 && p.running_mean) {
-    old_mean = __ldcg(p.running_mean + c);
-    old_var = __ldcg(p.running_var + c);
-  }
-
-  double d1 = 0.0, d2 = 0.0;
-  for (int n = grp; n < n_total; n += groups) {
-    const T* plane = xc + (long long)n * plane_stride;
-    float s1 = 0.f, s2 = 0.f;
-    f32x2 a1 = splat2(0.f), a2 = splat2(0.f);
-    visit_plane<T>(
-        plane, hw, lane, G,
-        [&](int, float xv) {
-          const float d = xv - shift;
-          s1 += d;
-          s2 += d * d;
-        },
-        [&](int, const uint4& raw) {
-          f32x2 f[P];
-          Pairs<T>::unpack(raw, f);
-#pragma unroll
-          for (int k = 0; k < P; ++k) {
-            const f32x2 d = sub2(f[k], shift2);
-            a1 = add2(a1, d);
-            a2 = fma2(d, d, a2);
-          }
-        });
-    d1 += (double)s1 + (double)hsum2(a1);
-    d2 += (double)s2 + (double)hsum2(a2);
-  }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    d1 += __shfl_xor_sync(0xffffffffu, d1, o);
-    d2 += __shfl_xor_sync(0xffffffffu, d2, o);
-  }
-  float mean = 0.f, invstd = 0.f;
-  if (lane32 == 0) bn_channel_stats(p, c, d1, d2, shift, true, &mean, &invstd, true, old_mean, old_var);
-  mean = __shfl_sync(0xffffffffu, mean, 0);
-  invstd = __shfl_sync(0xffffffffu, invstd, 0);
-  if (p.y == nullptr) return;
-
-  const f32x2 mean2 = splat2(mean), invstd2 = splat2(invstd), w2 = splat2(w), b2 = splat2(b);
-  const bool relu = p.relu != 0;
-  for (int n = n_total - 1 - grp; n >= 0; n -= groups) {
-    const T* plane = xc + (long long)n * plane_stride;
-    T* out = yc + (long long)n * plane_stride;
-    visit_plane<T>(
-        plane, hw, lane, G,
-        [&](int i, float xv) {
-          float o = ((xv - mean) * invstd) * w + b;
-          if (relu) o = o < 0.f ? 0.f : o;
-          out[i] = Elem<T>::from_f32(o);
-        },
-        [&](int i, const uint4& raw) {
-          f32x2 f[P];
-          Pairs<T>::unpack(raw, f);
-#pragma unroll
-          for (int k = 0; k < P; ++k) {
-            f[k] = add2(mul2(mul2(sub2(f[k], mean2), invstd2), w2), b2);
-            if (relu) {
-              float lo, hi;
-              unpack2(f[k], lo, hi);
-              f[k] = pack2(lo < 0.f ? 0.f : lo, hi < 0.f ? 0.f : hi);
-            }
-          }
-          st_stream(out + i, Pairs<T>::pack(f));
-        });
-  }
-}
-
-
 // Sum over the CTA, the same value in every thread: a shuffle tree inside each warp, one word per
 // warp through shared memory, and the same tree again over those words in every warp. Fixed
 // order, so the result is reproducible. `part` belongs to this call alone (32 floats).
@@ -476,12 +384,11 @@ bool try_launch_batch_norm_nchw(const BatchNormParams& p, cudaStream_t st, int* 
   if (p.rows < 1 || p.rows > 0x7fffffffLL || p.spatial < 1 || p.spatial > 0x3fffffffLL || p.channels > 65535) return false;
   const DeviceInfo& dev = device_info();
   const long long plane_vecs = (p.spatial * (long long)sizeof(T) + 15) / 16;
-  // little data per channel and enough channels: a warp per channel
-  // measurement switch: B200_BN_NCHW_FORCE=warp|cta|cluster|registers picks the variant whatever the shape
+  // measurement switch: B200_BN_NCHW_FORCE=cta|cluster|registers picks the variant whatever the shape
   static const int force = [] {
     const char* e = getenv("B200_BN_NCHW_FORCE");
     if (!e) return 0;
-    return e[0] == 'w' ? 1 : (e[0] == 'c' && e[1] == 't' ? 2 : (e[0] == 'c' ? 3 : (e[0] == 'r' ? 4 : 0)));
+    return e[0] == 'c' && e[1] == 't' ? 2 : (e[0] == 'c' ? 3 : (e[0] == 'r' ? 4 : 0));
   }();
   // channels of at most 16 K elements: the register-resident kernel, as few elements per thread as
   // 512 threads allow (1024 threads for the largest channels)
@@ -501,16 +408,6 @@ bool try_launch_batch_norm_nchw(const BatchNormParams& p, cudaStream_t st, int* 
       *rc = launch_status("b200_batch_norm_fwd [NCHW, one launch, CTA per channel, channel in registers]");
       return true;
     }
-  }
-  // very little data per channel (one round of loads for a warp) and enough channels: a warp per channel
-  const bool small = p.rows * p.spatial * (long long)sizeof(T) <= 4096 && p.channels >= 256;
-  if (force == 1 || (force == 0 && small)) {
-    int G = 32;  // as few lanes per plane as keep every group busy, at most eight vectors per lane
-    while (G > 2 && 32 / (G / 2) <= 2 * p.rows && plane_vecs <= 8LL * (G / 2)) G /= 2;
-    const unsigned grid = (unsigned)((p.channels + kThreads / 32 - 1) / (kThreads / 32));
-    batch_norm_nchw_warp_kernel<T><<<grid, kThreads, 0, st>>>(p, G);
-    *rc = launch_status("b200_batch_norm_fwd [NCHW, one launch, warp per channel]");
-    return true;
   }
   // cluster size: enough CTAs to fill the machine twice over, at most 8 per channel, at most one per image
   // Several CTAs per channel (a cluster) only pay when a channel holds enough data to keep them
