@@ -925,7 +925,7 @@ __global__ void __launch_bounds__(256) batch_norm_apply_general_kernel(const Bat
 //             holds), y written with streaming stores
 // ----------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void __launch_bounds__(256) batch_norm_sums_cl_flat_kernel(const BatchNormParams p, long long vecs_per_cta,
+__global__ void __launch_bounds__(256, 3) batch_norm_sums_cl_flat_kernel(const BatchNormParams p, long long vecs_per_cta,
                                                                       int PV, int rows_shift) {
   constexpr int V = Elem<T>::V;
   __shared__ float red[2 * 256 * V];  // [2][threads][V]
@@ -941,11 +941,9 @@ __global__ void __launch_bounds__(256) batch_norm_sums_cl_flat_kernel(const Batc
   // bits; the finalize kernel forms the same value) is computed once per CTA into shared memory,
   // at most 2 * 256 * V channels per round, and every thread picks up its V channels.
   f32x2 shift[V / 2], s1[V / 2], s2[V / 2];
-  double deep[V];  // a thread's sum of squares moves here every 16 vectors
+  f32x2 upper[V / 2];  // a thread's sum of squares moves here every 16 vectors: two short chains instead of one long one
 #pragma unroll
-  for (int i = 0; i < V / 2; ++i) shift[i] = s1[i] = s2[i] = splat2(0.f);
-#pragma unroll
-  for (int i = 0; i < V; ++i) deep[i] = 0.0;
+  for (int i = 0; i < V / 2; ++i) shift[i] = s1[i] = s2[i] = upper[i] = splat2(0.f);
   if (!rows_shift) {  // short chains (small tensors): the channel's element of row 0 will do
 #pragma unroll
     for (int i = 0; i < V / 2; ++i)
@@ -965,7 +963,7 @@ __global__ void __launch_bounds__(256) batch_norm_sums_cl_flat_kernel(const Batc
     }
     __syncthreads();
   }
-  constexpr int U = 8;  // vectors in flight per thread
+  constexpr int U = 4;  // vectors in flight per thread (three CTAs per SM)
   int round = 0;
   for (long long v = v0 + tid; v < v1; v += (long long)U * T_) {
     uint4 raw[U];
@@ -987,13 +985,10 @@ __global__ void __launch_bounds__(256) batch_norm_sums_cl_flat_kernel(const Batc
         }
       }
     }
-    if ((++round & 1) == 0) {
+    if ((++round & 3) == 0) {
 #pragma unroll
       for (int i = 0; i < V / 2; ++i) {
-        float lo, hi;
-        unpack2(s2[i], lo, hi);
-        deep[2 * i] += (double)lo;
-        deep[2 * i + 1] += (double)hi;
+        upper[i] = add2(upper[i], s2[i]);
         s2[i] = splat2(0.f);
       }
     }
@@ -1002,11 +997,8 @@ __global__ void __launch_bounds__(256) batch_norm_sums_cl_flat_kernel(const Batc
   float* r2 = red + 256 * V;
 #pragma unroll
   for (int i = 0; i < V / 2; ++i) {
-    float lo, hi;
-    unpack2(s2[i], lo, hi);
     unpack2(s1[i], r1[tid * V + 2 * i], r1[tid * V + 2 * i + 1]);
-    r2[tid * V + 2 * i] = (float)(deep[2 * i] + (double)lo);
-    r2[tid * V + 2 * i + 1] = (float)(deep[2 * i + 1] + (double)hi);
+    unpack2(add2(upper[i], s2[i]), r2[tid * V + 2 * i], r2[tid * V + 2 * i + 1]);
   }
   __syncthreads();
   const int period = PV * V;  // elements; a multiple of C
@@ -1025,7 +1017,7 @@ __global__ void __launch_bounds__(256) batch_norm_sums_cl_flat_kernel(const Batc
 }
 
 template <typename T>
-__global__ void __launch_bounds__(256) batch_norm_apply_cl_flat_kernel(const BatchNormParams p, long long vecs_per_cta,
+__global__ void __launch_bounds__(256, 3) batch_norm_apply_cl_flat_kernel(const BatchNormParams p, long long vecs_per_cta,
                                                                        int PV) {
   constexpr int V = Elem<T>::V;
   const int tid = threadIdx.x, T_ = blockDim.x, C = p.channels;
@@ -1112,6 +1104,10 @@ static bool try_launch_batch_norm_cl_flat(BatchNormParams p, size_t scratch_byte
   *rc = launch_status("b200_batch_norm_fwd apply [channels-last, flat vectors]");
   return true;
 }
+
+// Channels-last tensors smaller than this take the three flat launches: a cooperative launch with
+// its grid-wide barriers costs more than two extra plain launches until the tensor is tens of MB.
+constexpr long long kFlatBelowBytes = 8000000;  // measured: 3.2 MB 16.3 us flat / 21.3 us fused, 12.8 MB 27.5 / 24.1
 
 // B200_BN_CTA_RING=1 keeps the CTA-wide ring for every shape (for measurements).
 static bool warp_rings_disabled() {
@@ -1343,9 +1339,16 @@ extern "C" int b200_batch_norm_fwd_ex(const void* x, void* y, const void* weight
     const char* e = getenv("B200_BN_CL_RING");
     return e && e[0] == '1';
   }();
+  // B200_BN_CL_FLAT_BELOW_MB=<n>: tensors below n MB take the three flat launches even when the fused
+  // kernels could (measurement switch; the default threshold is kFlatBelowBytes)
+  static const long long flat_below = [] {
+    const char* e = getenv("B200_BN_CL_FLAT_BELOW_MB");
+    return e ? atoll(e) * 1000000LL : kFlatBelowBytes;
+  }();
   const long long vpr = channels % v == 0 ? channels / v : 0;
   const bool pow2 = vpr > 0 && vpr <= 32 && (vpr & (vpr - 1)) == 0;
-  const bool fast = cl && vpr > 0 && (pow2 || ring_all) && fused_geometry((int)vpr).threads > 0 &&
+  const bool small_tensor = batch * channels * spatial * (long long)eb < flat_below;
+  const bool fast = cl && vpr > 0 && ((pow2 && !small_tensor) || ring_all) && fused_geometry((int)vpr).threads > 0 &&
                     aligned16(x) && aligned16(y);
   const bool cl_flat = cl && !fast && aligned16(x) && aligned16(y);
   if (fast) {
