@@ -427,6 +427,124 @@ int launch_dropout_layer_norm(const DropoutLayerNormParams& p, cudaStream_t st) 
   return launch_status("b200_dropout_layer_norm");
 }
 
+// ---- softmax(x + bias) followed by dropout -----------------------------------------------------
+// The region (reference repros/canonical/amax_sum_089fdab8f22b/repro.py:24-46, attention
+// probabilities of a T5 block in training), per row of `cols` scores:
+//   logits = T(float(x) + bias)            amax = max(logits)       e = exp(logits - amax)
+//   sum = sum(e)                           prob = T(e / sum)
+//   keep = T(rand(seed[i])) > p            y = T(T(keep * prob) * scale)
+// with outputs (logits, amax, sum, keep, y). x is a contiguous [B*H, Sq, cols] tensor of 16-bit
+// elements; bias is fp32 [B, H, Sq, cols] with arbitrary element strides (the captured graph hands
+// over a permuted tensor whose head dimension is the unit-stride one); all outputs are contiguous.
+// A warp owns a row, a lane the 8-element vectors l, l + 32, ..; the row stays in registers from
+// the load to the last store. Random numbers as in the kernels above (counter = flat element
+// index / 4, mask number 0).
+struct SoftmaxDropoutParams {
+  const void* x;
+  const float* bias;
+  long long sb, sh, sq, sk;  // element strides of bias
+  int heads, seq_q, cols;
+  long long rows;            // B * H * Sq
+  const long long* seeds;
+  int seed_index;
+  uint32_t keep_from;
+  float scale;
+  void* logits;
+  float* amax;
+  float* sum;
+  unsigned char* keep;
+  void* y;
+};
+
+template <typename T, int CH>
+__global__ void __launch_bounds__(128) softmax_dropout_kernel(SoftmaxDropoutParams p) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const PhiloxKeys keys = philox_keys((unsigned long long)p.seeds[p.seed_index]);
+  const int nv = p.cols >> 3;
+  const T* x = reinterpret_cast<const T*>(p.x);
+  T* logits = reinterpret_cast<T*>(p.logits);
+  T* y = reinterpret_cast<T*>(p.y);
+  for (long long row = (long long)blockIdx.x * 4 + warp; row < p.rows; row += (long long)gridDim.x * 4) {
+    const long long bh = row / p.seq_q;
+    const int q = (int)(row - bh * p.seq_q);
+    const long long b = bh / p.heads;
+    const int h = (int)(bh - b * p.heads);
+    const float* brow = p.bias + b * p.sb + h * p.sh + q * p.sq;
+    const long long base = row * p.cols;
+    float l[CH][8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int v = lane + 32 * c;
+      if (v < nv) {
+        float f[8], bv[8];
+        const uint4 raw = ld_stream(x + base + 8 * v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) bv[j] = __ldg(brow + (long long)(8 * v + j) * p.sk);
+        Elem<T>::unpack(raw, f);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          l[c][j] = Elem<T>::to_f32(Elem<T>::from_f32(f[j] + bv[j]));  // the graph rounds the logits to T
+          mx = fmaxf(mx, l[c][j]);
+        }
+        st_stream(logits + base + 8 * v, Elem<T>::pack(l[c]));
+      }
+    }
+    mx = warp_reduce<MaxOp>(mx);
+    float s = 0.f;
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      if (lane + 32 * c < nv) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          l[c][j] = expf(l[c][j] - mx);
+          s += l[c][j];
+        }
+      }
+    }
+    s = warp_reduce<SumOp>(s);
+    if (lane == 0) {
+      p.amax[row] = mx;
+      p.sum[row] = s;
+    }
+#pragma unroll
+    for (int c = 0; c < CH; ++c) {
+      const int v = lane + 32 * c;
+      if (v < nv) {
+        uint32_t w[8];
+        random_words8((unsigned long long)(base + 8 * v), 0u, keys, w);
+        uint2 bytes;
+        f32x2 m[4];
+        masks8(w, p.keep_from, bytes, m);
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          float ma, mb;
+          unpack2(m[j], ma, mb);
+          const float pa = Elem<T>::to_f32(Elem<T>::from_f32(l[c][2 * j] / s));
+          const float pb = Elem<T>::to_f32(Elem<T>::from_f32(l[c][2 * j + 1] / s));
+          o[2 * j] = (ma * pa) * p.scale;      // keep * prob is exact in T; one rounding at the end
+          o[2 * j + 1] = (mb * pb) * p.scale;
+        }
+        *reinterpret_cast<uint2*>(p.keep + base + 8 * v) = bytes;
+        st_stream(y + base + 8 * v, Elem<T>::pack(o));
+      }
+    }
+  }
+}
+
+template <typename T>
+int launch_softmax_dropout(const SoftmaxDropoutParams& p, cudaStream_t st) {
+  const int nv = p.cols >> 3;
+  const long long want = (p.rows + 3) / 4;
+  const long long cap = (long long)device_info().sm_count * 32;
+  const int grid = (int)(want < cap ? want : cap);
+  if (nv <= 32) softmax_dropout_kernel<T, 1><<<grid, 128, 0, st>>>(p);
+  else if (nv <= 64) softmax_dropout_kernel<T, 2><<<grid, 128, 0, st>>>(p);
+  else softmax_dropout_kernel<T, 4><<<grid, 128, 0, st>>>(p);
+  return launch_status("b200_softmax_dropout");
+}
+
 // Threshold of the mask whose draw is narrowed to the tensor dtype before the comparison with p.
 uint32_t narrowed_keep_from(float pf, int x_dtype) {
   if (x_dtype == B200_BF16) {
@@ -559,4 +677,44 @@ extern "C" int b200_dropout_add(const void* x, const void* residual, const int64
   if (x_dtype == B200_BF16) dropout_add_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(q);
   else dropout_add_kernel<__half><<<grid, 256, 0, st>>>(q);
   return launch_status("b200_dropout_add");
+}
+
+extern "C" int b200_softmax_dropout(const void* x, const void* bias, int64_t batch, int64_t heads, int64_t seq_q,
+                                    int64_t cols, int64_t bias_stride_b, int64_t bias_stride_h,
+                                    int64_t bias_stride_q, int64_t bias_stride_k, const int64_t* seeds,
+                                    int32_t seed_index, double p, void* logits, void* amax, void* sum, void* keep,
+                                    void* y, int32_t x_dtype, void* stream) {
+  if (batch < 0 || heads < 0 || seq_q < 0 || cols < 0) return fail(B200_ERR_INVALID, "b200_softmax_dropout: negative size");
+  const long long rows = batch * heads * seq_q;
+  if (rows == 0 || cols == 0) return B200_OK;
+  if (!x || !bias || !seeds || !logits || !amax || !sum || !keep || !y)
+    return fail(B200_ERR_INVALID, "b200_softmax_dropout: null argument");
+  if (seed_index < 0) return fail(B200_ERR_INVALID, "b200_softmax_dropout: negative seed index");
+  if (!(p >= 0.0 && p < 1.0)) return fail(B200_ERR_INVALID, "b200_softmax_dropout: p must be in [0, 1)");
+  if (x_dtype != B200_BF16 && x_dtype != B200_F16)
+    return fail(B200_ERR_UNSUPPORTED, "b200_softmax_dropout: x must be bf16 or fp16 (dtype %d)", x_dtype);
+  if (cols % 8 != 0 || cols > 1024)
+    return fail(B200_ERR_UNSUPPORTED, "b200_softmax_dropout: %lld columns (supported: multiples of 8 up to 1024)",
+                (long long)cols);
+  if (!aligned16(x) || !aligned16(logits) || !aligned16(y) || (reinterpret_cast<uintptr_t>(keep) & 7u))
+    return fail(B200_ERR_ALIGNMENT, "b200_softmax_dropout: tensors must be 16-byte aligned (mask 8-byte)");
+  SoftmaxDropoutParams q;
+  q.x = x;
+  q.bias = static_cast<const float*>(bias);
+  q.sb = bias_stride_b; q.sh = bias_stride_h; q.sq = bias_stride_q; q.sk = bias_stride_k;
+  q.heads = (int)heads; q.seq_q = (int)seq_q; q.cols = (int)cols;
+  q.rows = rows;
+  q.seeds = reinterpret_cast<const long long*>(seeds);
+  q.seed_index = seed_index;
+  q.keep_from = narrowed_keep_from((float)p, x_dtype);
+  if (q.keep_from >= (1u << 24))
+    return fail(B200_ERR_UNSUPPORTED, "b200_softmax_dropout: p = %g keeps nothing at 24-bit resolution", p);
+  q.scale = (float)(1.0 / (1.0 - p));
+  q.logits = logits;
+  q.amax = static_cast<float*>(amax);
+  q.sum = static_cast<float*>(sum);
+  q.keep = static_cast<unsigned char*>(keep);
+  q.y = y;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return x_dtype == B200_BF16 ? launch_softmax_dropout<__nv_bfloat16>(q, st) : launch_softmax_dropout<__half>(q, st);
 }

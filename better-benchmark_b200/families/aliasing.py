@@ -44,11 +44,14 @@ def scale_into_head_view(inputs, *, scale=0.125):
     return scaled.view(b, s, hidden).view(b, s, h, d).permute(0, 2, 1, 3)
 
 
-def qkv_split_views(inputs, *, width=768):
-    """``width``: the split size, a literal of the captured graph (repro.py:27)."""
+def qkv_split_views(inputs, *, width=768, order=None):
+    """``width``: the split size, a literal of the captured graph (repro.py:27). ``order``: which
+    chunk each output is (default 0, 1, 2 ...; repros/canonical/pointwise_d5a413a2c233/repro.py:28-36
+    returns chunks 1, 2, 0)."""
     x, shape3 = inputs[0], inputs[1]
     b, s, packed = _resolve(shape3, x.numel())
     chunks = packed // width
     _, _, h, d = _resolve(inputs[2], b * s * width)
     v = x.view(b, s, packed)
-    return tuple(v[:, :, i * width:(i + 1) * width].view(b, s, h, d).permute(0, 2, 1, 3) for i in range(chunks))
+    picks = range(chunks) if order is None else order
+    return tuple(v[:, :, i * width:(i + 1) * width].view(b, s, h, d).permute(0, 2, 1, 3) for i in picks)

@@ -639,6 +639,40 @@ def dropout_layer_norm(x: torch.Tensor, residual: torch.Tensor, weight: torch.Te
     return keep, xhat, y, rstd_over_n
 
 
+def softmax_dropout(x: torch.Tensor, bias: torch.Tensor, seeds: torch.Tensor, seed_index: int, *, p: float):
+    """``dropout(softmax(x + bias))`` over the last dimension, mask drawn in the kernel.
+
+    x: contiguous bf16/fp16 ``[B*H, Sq, Sk]``; bias: fp32 ``[B, H, Sq, Sk]`` with ANY strides (read in
+    place); seeds int64. Returns ``(logits, amax, sum, keep, y)``: the rounded logits ``[B, H, Sq, Sk]``
+    in x's dtype, row maximum and row sum of the exponentials fp32 ``[B, H, Sq, 1]``, the mask as bool
+    ``[B, H, Sq, Sk]`` and the dropped probabilities ``[B*H, Sq, Sk]`` in x's dtype, all contiguous."""
+    for t in (x, bias, seeds):
+        _require_cuda(t)
+    if x.dim() != 3 or bias.dim() != 4:
+        raise native.KernelArgumentError("softmax_dropout: x must be [B*H, Sq, Sk] and bias [B, H, Sq, Sk]")
+    b, h, sq, sk = bias.shape
+    if tuple(x.shape) != (b * h, sq, sk):
+        raise native.KernelArgumentError(f"softmax_dropout: x {tuple(x.shape)} does not match bias {tuple(bias.shape)}")
+    if bias.dtype != torch.float32 or seeds.dtype != torch.int64:
+        raise native.KernelArgumentError("softmax_dropout: bias must be fp32, seeds int64")
+    if not x.is_contiguous() or not seeds.is_contiguous():
+        raise UnsupportedLayout("softmax_dropout: x and seeds must be contiguous")
+    if not 0 <= seed_index < seeds.numel():
+        raise native.KernelArgumentError("softmax_dropout: seed index outside the seed tensor")
+    dev = x.device
+    logits = torch.empty((b, h, sq, sk), dtype=x.dtype, device=dev)
+    amax = torch.empty((b, h, sq, 1), dtype=torch.float32, device=dev)
+    total = torch.empty((b, h, sq, 1), dtype=torch.float32, device=dev)
+    keep = torch.empty((b, h, sq, sk), dtype=torch.bool, device=dev)
+    y = torch.empty_like(x)
+    lib = load()
+    sb, sh, ssq, ssk = bias.stride()
+    check(lib.b200_softmax_dropout(_ptr(x), _ptr(bias), b, h, sq, sk, sb, sh, ssq, ssk, _ptr(seeds), int(seed_index),
+                                   float(p), _ptr(logits), _ptr(amax), _ptr(total), _ptr(keep), _ptr(y), _code(x),
+                                   _stream()), "b200_softmax_dropout")
+    return logits, amax, total, keep, y
+
+
 def dropout_add(x: torch.Tensor, residual: torch.Tensor, seeds: torch.Tensor, seed_index: int, *, p: float):
     """``residual + dropout(x)``: x bf16/fp16, residual fp32 with the same number of elements. Returns
     ``(keep, sum)`` shaped like ``residual`` (bool, fp32)."""

@@ -92,6 +92,9 @@ SIGNATURES = {
     "b200_dropout_rms_norm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_int32, c_double,
                                         c_double, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64,
                                         c_int64, c_int32, c_void_p]),
+    "b200_softmax_dropout": (c_int32, [c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64, c_int64,
+                                       c_int64, c_int64, c_void_p, c_int32, c_double, c_void_p, c_void_p, c_void_p,
+                                       c_void_p, c_void_p, c_int32, c_void_p]),
     "b200_dropout_add": (c_int32, [c_void_p, c_void_p, c_void_p, c_int32, c_double, c_void_p, c_void_p, c_int64,
                                    c_int32, c_void_p]),
     "b200_dropout_layer_norm": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int32, c_double,

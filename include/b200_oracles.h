@@ -207,6 +207,20 @@ int32_t b200_dropout_layer_norm(const void* x, const void* residual, const void*
 int32_t b200_dropout_add(const void* x, const void* residual, const int64_t* seeds, int32_t seed_index, double p,
                          void* keep, void* sum, int64_t n, int32_t x_dtype, void* stream);
 
+/* softmax(x + bias) -> dropout over rows of `cols` scores (a multiple of 8, at most 1024):
+ *   logits = T(x + bias); amax = max(logits); sum = sum(exp(logits - amax)); prob = T(exp(..) / sum);
+ *   keep = T(u) > p; y = T(T(keep * prob) * 1/(1-p)).
+ * x: contiguous [batch*heads, seq_q, cols], x_dtype (bf16 or fp16); bias: fp32 [batch, heads, seq_q, cols] with
+ * the four element strides given (any layout); outputs contiguous: logits and y x_dtype, amax and sum fp32
+ * [batch*heads*seq_q], keep one byte per element. u as in b200_dropout_rms_norm (mask number 0, key
+ * seeds[seed_index], counter = flat element index).
+ * Replaces amax_sum_089fdab8f22b/oracle.py (kernels and wrapper); graph amax_sum_089fdab8f22b/repro.py:24-46. */
+int32_t b200_softmax_dropout(const void* x, const void* bias, int64_t batch, int64_t heads, int64_t seq_q,
+                             int64_t cols, int64_t bias_stride_b, int64_t bias_stride_h, int64_t bias_stride_q,
+                             int64_t bias_stride_k, const int64_t* seeds, int32_t seed_index, double p,
+                             void* logits, void* amax, void* sum, void* keep, void* y, int32_t x_dtype,
+                             void* stream);
+
 /* Contiguous cast / scale of n elements.
  * Replaces pointwise_8bb40810003c/oracle.py:11-15 and pointwise_95ed2ef35da9/oracle.py:10-44. */
 int32_t b200_cast_scale(const void* x, void* y, int64_t n, int32_t in_dtype, int32_t out_dtype, double scale,

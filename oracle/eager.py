@@ -247,6 +247,16 @@ class HeadSplitPermute(nn.Module):
         return aten.clone.default(p, memory_format=torch.contiguous_format)
 
 
+class HeadMergePermute(nn.Module):
+    """[B*H, S, D] -> [B*S, H*D] contiguous copy, the inverse of the head split. Graph: reference
+    repros/canonical/pointwise_e87d6ebc9ded/repro.py:24-31 (view, permute, clone, view, view)."""
+
+    def forward(self, x, split4, merged3, flat2):
+        v = aten.view.default(x, split4)
+        c = aten.clone.default(aten.permute.default(v, [0, 2, 1, 3]), memory_format=torch.contiguous_format)
+        return aten.view.default(aten.view.default(c, merged3), flat2)
+
+
 class Transpose2D(nn.Module):
     """[..., P, C] -> [..., C, P] contiguous copy (reference
     repros/canonical/pointwise_021e90d9c17d/repro.py: permute + clone)."""
@@ -438,6 +448,38 @@ class DropoutAdd(nn.Module):
         return (mask, aten.add.Tensor(residual, mul_1))
 
 
+class SoftmaxDropout(nn.Module):
+    """dropout(softmax(x + bias)), returning (logits, amax, sum, keep, y, y transposed).
+
+    Graph: reference repros/canonical/amax_sum_089fdab8f22b/repro.py:24-46 (the logits are rounded to
+    x's dtype before the softmax, the probabilities before the dropout; the uniform tensor is
+    narrowed to x's dtype before the comparison). ``mask`` replaces the draw, as in
+    ``DropoutResidualRMSNorm``.
+    """
+
+    def __init__(self, p: float = 0.1, seed_index: int = 29):
+        super().__init__()
+        self.p, self.seed_index = p, seed_index
+        self.scale = 1.0 / (1.0 - p)
+
+    def forward(self, x, bias, seeds, mask=None):
+        import torch._inductor.inductor_prims  # noqa: F401
+        shape = list(bias.shape)
+        logits = prims.convert_element_type.default(aten.add.Tensor(aten.view.default(x, shape), bias), x.dtype)
+        lf = _f32(logits)
+        amax = aten.amax.default(lf, [-1], True)
+        e = aten.exp.default(aten.sub.Tensor(lf, amax))
+        total = aten.sum.dim_IntList(e, [-1], True)
+        prob = prims.convert_element_type.default(aten.div.Tensor(e, total), x.dtype)
+        if mask is None:
+            seed = prims.inductor_lookup_seed.default(seeds, self.seed_index)
+            rand = prims.inductor_random.default(shape, seed, "rand")
+            mask = aten.gt.Scalar(prims.convert_element_type.default(rand, x.dtype), self.p)
+        y = aten.mul.Tensor(aten.mul.Tensor(mask, prob), self.scale)
+        y3 = aten.view.default(y, list(x.shape))
+        return (logits, amax, total, mask, y3, aten.permute.default(y3, [0, 2, 1]))
+
+
 class CastWithTransposedAlias(nn.Module):
     """Reference graph: repros/canonical/pointwise_8bb40810003c/repro.py:23-29. One cast; the two
     outputs are views of the same buffer (its transpose and itself)."""
@@ -470,20 +512,25 @@ class QkvSplitViews(nn.Module):
         super().__init__()
         self.width = width  # a literal of the captured graph
 
-    def forward(self, x, shape3, shape_q, shape_k, shape_v):
+    def forward(self, x, shape3, shape_q, shape_k, shape_v, order=(0, 1, 2)):
+        """``order``: which chunk each output is; repros/canonical/pointwise_d5a413a2c233/repro.py:28-36
+        returns chunks 1, 2, 0 (its three lifted shapes then belong to those chunks in that order)."""
         v = aten.view.default(x, shape3)
         parts = aten.split.Tensor(v, self.width, 2)
-        return tuple(aten.permute.default(aten.view.default(part, shp), [0, 2, 1, 3])
-                     for part, shp in zip(parts, (shape_q, shape_k, shape_v)))
+        return tuple(aten.permute.default(aten.view.default(parts[i], shp), [0, 2, 1, 3])
+                     for i, shp in zip(order, (shape_q, shape_k, shape_v)))
 
 
 class GeluLayerNormFwd(nn.Module):
     """Reference graph: repros/canonical/var_mean_af505388b035/repro.py:23-46. Exact GELU in fp32,
     rounded to the input dtype (the graph materialises the activation), then LayerNorm; y only."""
 
-    def __init__(self, eps: float = 1e-12):
+    def __init__(self, eps: float = 1e-12, with_stats: bool = False):
         super().__init__()
         self.eps = eps
+        # repros/canonical/var_mean_21faaccf749d/repro.py:24-46 is the same graph with eps 1e-7 that
+        # also returns the row mean and rstd: (mean, rstd, y)
+        self.with_stats = with_stats
 
     def forward(self, x, weight, bias):
         xf = _f32(x)
@@ -494,4 +541,5 @@ class GeluLayerNormFwd(nn.Module):
         var_mean = aten.var_mean.correction(af, [-1], correction=0, keepdim=True)
         rstd = aten.rsqrt.default(aten.add.Tensor(var_mean[0], self.eps))
         out = aten.add.Tensor(aten.mul.Tensor(aten.mul.Tensor(aten.sub.Tensor(af, var_mean[1]), rstd), weight), bias)
-        return prims.convert_element_type.default(out, x.dtype)
+        y = prims.convert_element_type.default(out, x.dtype)
+        return (var_mean[1], rstd, y) if self.with_stats else y

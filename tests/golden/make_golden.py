@@ -73,6 +73,19 @@ CASES = {
     "qkv_views_1611fb0c7845": ("pointwise_1611fb0c7845",
                                [[[32, 2304], "bf16"], ["S", [2, 16, 2304]], ["S", [2, 16, 12, 64]],
                                 ["S", [2, 16, 12, 64]], ["S", [2, 16, 12, 64]]]),
+    "headmerge_e87d6ebc9ded": ("pointwise_e87d6ebc9ded",
+                               [[[12, 16, 32], "bf16"], ["S", [4, 3, 16, 32]], ["S", [4, -1, 96]], ["S", [64, 96]]]),
+    # returned as k, v, q; the packed width stays 3 * 768 (the graph splits at the literal 768)
+    "qkv_views_d5a413a2c233": ("pointwise_d5a413a2c233",
+                               [[[32, 2304], "bf16"], ["S", [2, 16, 2304]], ["S", [2, 16, 12, 64]],
+                                ["S", [2, 16, 12, 64]], ["S", [2, 16, 12, 64]]]),
+    "gelu_ln_stats_21faaccf749d": ("var_mean_21faaccf749d",
+                                   [[[96, 768], "bf16"], [[768], "f32"], [[768], "f32"], ["S", [4, 24, 768]], ["S", [96, 768]]]),
+    # the bias is handed over permuted (head dimension unit-stride), as in the captured shape point
+    "softmax_dropout_089fdab8f22b": ("amax_sum_089fdab8f22b",
+                                     [[[12, 16, 64], "bf16"], [[4, 3, 16, 64], "f32", {"st": [3072, 1, 192, 3]}],
+                                      [[84], "i64"], ["S", [4, 3, 16, 64]], ["S", [4, 3, 16, 64]],
+                                      ["S", [4, 3, 16, 64]], ["S", [12, 16, 64]]]),
     "dropout_add_4b076ed1ff41": ("pointwise_4b076ed1ff41",
                                  [[[48, 320], "bf16"], [[2], "i64"], [[3, 16, 320], "f32"],
                                   ["S", [3, 16, 320]], ["S", [3, 16, 320]]]),

@@ -197,3 +197,51 @@ def test_dropout_add_stub_argument_orders_and_rejections():
         kernels.dropout_add(x, residual[:32], seeds, 0, p=0.1)
     with pytest.raises(native.KernelArgumentError):
         kernels.dropout_add(x[:1, :4], residual[:1, :4].contiguous(), seeds, 0, p=0.1)   # not a multiple of 8
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("dims,permuted", [((4, 3, 16, 64), True), ((2, 6, 128, 128), True), ((1, 2, 5, 8), False),
+                                           ((3, 4, 7, 520), False), ((2, 2, 9, 1024), True)])
+def test_softmax_dropout(dtype, dims, permuted):
+    """softmax(x + bias) -> dropout: the mask bit for bit against the Philox restatement, everything
+    else against the eager module evaluated with the kernel's own mask. The bias is read in place,
+    also when the head dimension is its unit-stride one (the layout of the captured shape point)."""
+    from better_benchmark_b200 import kernels
+    from oracle import eager
+    from oracle.philox import uniforms
+    b, h, sq, sk = dims
+    g = torch.Generator(device="cuda").manual_seed(sum(dims))
+    x = (torch.randn(b * h, sq, sk, generator=g, device="cuda") * 2).to(dtype)
+    if permuted:
+        bias = torch.randn(b, sq, sk, h, generator=g, device="cuda").permute(0, 3, 1, 2)
+        assert bias.stride(1) == 1
+    else:
+        bias = torch.randn(b, h, sq, sk, generator=g, device="cuda")
+    seeds = torch.randint(0, 2 ** 62, (32,), generator=g, device="cuda", dtype=torch.int64)
+    p = 0.1
+    logits, amax, total, keep, y = kernels.softmax_dropout(x, bias, seeds, 29, p=p)
+    assert b"b200_softmax_dropout" in kernels.load().b200_last_kernel()
+    assert logits.shape == keep.shape == (b, h, sq, sk) and keep.dtype == torch.bool and y.shape == x.shape
+    n = b * h * sq * sk
+    u = torch.from_numpy(uniforms(n, seeds.cpu().tolist()[29], 0))
+    assert torch.equal(keep.cpu().view(-1), u.to(dtype) > p)
+    want = eager.SoftmaxDropout(p, 29)(x.cpu(), bias.cpu(), seeds.cpu(), mask=keep.cpu())
+    assert torch.equal(logits.cpu(), want[0]), "rounded logits"
+    assert torch.equal(amax.cpu(), want[1]), "row maximum"
+    assert_close(total, want[2], "row sum of the exponentials")
+    assert_close(y, want[4], "dropped probabilities")
+    again = kernels.softmax_dropout(x, bias, seeds, 29, p=p)
+    assert all(torch.equal(u_, v_) for u_, v_ in zip((logits, amax, total, keep, y), again)), "bit-reproducible"
+
+
+def test_softmax_dropout_rejections():
+    from better_benchmark_b200 import kernels, native
+    x = torch.zeros(6, 4, 12, device="cuda", dtype=torch.bfloat16)
+    bias = torch.zeros(2, 3, 4, 12, device="cuda")
+    seeds = torch.zeros(4, device="cuda", dtype=torch.int64)
+    with pytest.raises(native.KernelArgumentError):
+        kernels.softmax_dropout(x, bias, seeds, 0, p=0.1)            # 12 columns: not a multiple of 8
+    with pytest.raises(native.KernelArgumentError):
+        kernels.softmax_dropout(x, bias[:, :2], seeds, 0, p=0.1)     # shapes disagree
+    with pytest.raises(native.KernelArgumentError):
+        kernels.softmax_dropout(x, bias, seeds, 9, p=0.1)            # seed slot outside the tensor

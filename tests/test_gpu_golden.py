@@ -26,11 +26,15 @@ FIXTURE_DIR = {
     "dropout_ln_01fbd6c1b27f": "var_mean_01fbd6c1b27f", "dropout_add_4b076ed1ff41": "pointwise_4b076ed1ff41",
     "cast_alias_8bb40810003c": "pointwise_8bb40810003c", "scale_view_95ed2ef35da9": "pointwise_95ed2ef35da9",
     "qkv_views_1611fb0c7845": "pointwise_1611fb0c7845", "gelu_ln_af505388b035": "var_mean_af505388b035",
+    "gelu_ln_stats_21faaccf749d": "var_mean_21faaccf749d", "headmerge_e87d6ebc9ded": "pointwise_e87d6ebc9ded",
+    "qkv_views_d5a413a2c233": "pointwise_d5a413a2c233", "softmax_dropout_089fdab8f22b": "amax_sum_089fdab8f22b",
 }
 # regions that draw random numbers: output index -> mask index it depends on element by element
 STOCHASTIC = {"dropout_rms_014afd4984e6": {"masks": (0, 3), "elementwise": {1: 0}},
               "dropout_ln_01fbd6c1b27f": {"masks": (0,), "elementwise": {}},
-              "dropout_add_4b076ed1ff41": {"masks": (0,), "elementwise": {1: 0}}}
+              "dropout_add_4b076ed1ff41": {"masks": (0,), "elementwise": {1: 0}},
+              # logits, row maximum and row sum do not depend on the draw at all
+              "softmax_dropout_089fdab8f22b": {"masks": (3,), "elementwise": {4: 3}, "deterministic": (0, 1, 2)}}
 
 
 def kernel_cases():
@@ -76,6 +80,8 @@ def test_kernels_reproduce_reference_outputs(name):
         spec = STOCHASTIC[name]
         for i, (g, w) in enumerate(zip(got, want)):
             assert g.shape == w.shape and g.dtype == w.dtype, f"{name} output {i}"
+        for i in spec.get("deterministic", ()):
+            assert_close(got[i], want[i], f"{name} output {i}")
         for m in spec["masks"]:
             assert abs(got[m].float().mean().item() - want[m].float().mean().item()) < 0.02
         for out_i, mask_i in spec["elementwise"].items():

@@ -90,9 +90,25 @@ def golden_cases():
         mask = recorded[0] if recorded is not None else None
         return list(eager.DropoutAdd(0.1, 1)(x, seeds, residual, mask=mask))
 
+    def softmax_dropout(inp, recorded=None):
+        x, bias, seeds = inp[:3]
+        mask = recorded[3] if recorded is not None else None
+        return list(eager.SoftmaxDropout(0.1, 29)(x, bias, seeds, mask=mask))
+
     def gelu_ln(inp):
         x, w, b, s0, s1 = inp
         return [eager.GeluLayerNormFwd(1e-12)(x.view(s0), w, b).view(s1)]
+
+    def gelu_ln_stats(inp):
+        x, w, b, s0, s1 = inp
+        mean, rstd, y = eager.GeluLayerNormFwd(1e-7, with_stats=True)(x.view(s0), w, b)
+        return [mean, rstd, y.view(s1)]
+
+    def headmerge(inp):
+        return [eager.HeadMergePermute()(*inp)]
+
+    def qkv_views_kvq(inp):
+        return list(eager.QkvSplitViews(768)(*inp, order=(1, 2, 0)))
 
     def cast_alias(inp):
         return list(eager.CastWithTransposedAlias()(inp[0]))
@@ -106,7 +122,9 @@ def golden_cases():
     return {
         "cast_alias_8bb40810003c": cast_alias, "scale_view_95ed2ef35da9": scale_view,
         "qkv_views_1611fb0c7845": qkv_views, "gelu_ln_af505388b035": gelu_ln,
-        "dropout_add_4b076ed1ff41": dropout_add,
+        "dropout_add_4b076ed1ff41": dropout_add, "softmax_dropout_089fdab8f22b": softmax_dropout,
+        "gelu_ln_stats_21faaccf749d": gelu_ln_stats, "headmerge_e87d6ebc9ded": headmerge,
+        "qkv_views_d5a413a2c233": qkv_views_kvq,
         "dropout_ln_01fbd6c1b27f": dropout_ln,
         "dropout_rms_014afd4984e6": dropout_rms,
         "ln_fwd_f8ec553e339e": ln_fwd, "rmsnorm_fwd_f667cd8901af": rms_fwd,
@@ -120,7 +138,8 @@ def golden_cases():
 
 
 CASE_NAMES = sorted(p.stem for p in GOLDEN.glob("*.pt"))
-STOCHASTIC = {"dropout_rms_014afd4984e6", "dropout_ln_01fbd6c1b27f", "dropout_add_4b076ed1ff41"}   # cases whose region draws random numbers
+STOCHASTIC = {"dropout_rms_014afd4984e6", "dropout_ln_01fbd6c1b27f", "dropout_add_4b076ed1ff41",
+              "softmax_dropout_089fdab8f22b"}   # cases whose region draws random numbers
 
 
 def _clone(inputs):
