@@ -35,6 +35,11 @@ struct NormFwdParams {
   float inv_denom;  // 1 / (n - correction)
   int rms;
   int prologue;     // 0: none; 1: exact (erf) GELU of x, rounded to x's dtype, is what gets normalised
+  // Residual prologue (the post-LayerNorm blocks, repros/canonical/var_mean_0ada225c0a04/repro.py:26-27):
+  // what gets normalised is T(x + res); res has x's dtype and row stride. sum_out (may be null)
+  // receives that rounded sum, rows of n elements, contiguous.
+  const void* res;
+  void* sum_out;
 };
 
 // Pointwise prologue of the LayerNorm regions that normalise an activation
@@ -56,7 +61,7 @@ __device__ __forceinline__ f32x2 gelu_erf_rounded2(f32x2 v) {
 // rsqrtf is the 2-ulp hardware approximation aten's CUDA rsqrt uses as well.
 __device__ __forceinline__ float precise_rsqrt(float v) { return rsqrtf(v); }
 
-template <typename Tin, typename Tout, int CH, int G>
+template <typename Tin, typename Tout, int CH, int G, bool RES = false>
 __global__ void __launch_bounds__(G == 0 ? 512 : 256)
 norm_fwd_resident_kernel(const NormFwdParams p) {
   constexpr int V = Elem<Tin>::V;
@@ -70,11 +75,15 @@ norm_fwd_resident_kernel(const NormFwdParams p) {
   const Tin* x = reinterpret_cast<const Tin*>(p.x) + row * p.x_row_stride;
   const int nv = p.n / V;
 
-  uint4 raw[CH];
+  uint4 raw[CH], rraw[RES ? CH : 1];
 #pragma unroll
   for (int c = 0; c < CH; ++c) {
     const int j = c * gs + lane;
-    if (j < nv) raw[c] = ld_stream(x + (long long)j * V);
+    if (j < nv) {
+      raw[c] = ld_stream(x + (long long)j * V);
+      if constexpr (RES)
+        rraw[c] = ld_stream(reinterpret_cast<const Tin*>(p.res) + row * p.x_row_stride + (long long)j * V);
+    }
   }
   // The row as packed fp32 pairs; slots past the end of the row hold zeros and add nothing.
   f32x2 v[CH][V / 2];
@@ -84,6 +93,15 @@ norm_fwd_resident_kernel(const NormFwdParams p) {
     float f[V];
     if (c * gs + lane < nv) {
       Elem<Tin>::unpack(raw[c], f);
+      if constexpr (RES) {  // T(x + res): the graph materialises the sum in the tensor dtype
+        float r[V];
+        Elem<Tin>::unpack(rraw[c], r);
+#pragma unroll
+        for (int i = 0; i < V; ++i) f[i] = round_through<Tin>(f[i] + r[i]);
+        if (p.sum_out && valid)
+          st_stream(reinterpret_cast<Tin*>(p.sum_out) + row * (long long)p.n + (long long)(c * gs + lane) * V,
+                    Elem<Tin>::pack(f));
+      }
     } else {
 #pragma unroll
       for (int i = 0; i < V; ++i) f[i] = 0.f;
@@ -489,10 +507,16 @@ __global__ void __launch_bounds__(1024) norm_fwd_streaming_kernel(const NormFwdP
   const long long row = blockIdx.x;
   const Tin* x = reinterpret_cast<const Tin*>(p.x) + row * p.x_row_stride;
 
+  const Tin* res = p.res ? reinterpret_cast<const Tin*>(p.res) + row * p.x_row_stride : nullptr;
   auto value = [&](long long i) {
-    const float f = Elem<Tin>::to_f32(x[i]);
+    float f = Elem<Tin>::to_f32(x[i]);
+    if (res) f = round_through<Tin>(f + Elem<Tin>::to_f32(res[i]));
     return p.prologue == 1 ? gelu_erf_rounded<Tin>(f) : f;
   };
+  if (res && p.sum_out) {
+    Tin* so = reinterpret_cast<Tin*>(p.sum_out) + row * (long long)p.n;
+    for (long long i = threadIdx.x; i < p.n; i += blockDim.x) so[i] = Elem<Tin>::from_f32(value(i));
+  }
   float s = 0.f;
   for (long long i = threadIdx.x; i < p.n; i += blockDim.x) {
     const float f = value(i);
@@ -533,13 +557,25 @@ static int launch_norm_fwd(const NormFwdParams& p, bool vector_ok, cudaStream_t 
   constexpr int V = Elem<Tin>::V;
   if (p.rows > 0x7fffffffLL) return fail(B200_ERR_UNSUPPORTED, "norm_fwd: too many rows");
   RowGeometry g;
-  if (vector_ok && p.n % V == 0) {
+  constexpr bool kResBuilt = std::is_same<Tin, Tout>::value;  // the residual prologue: same-dtype pairs only
+  if (p.res && !kResBuilt) return fail(B200_ERR_UNSUPPORTED, "norm_fwd: the residual prologue needs y in x's dtype");
+  if (vector_ok && p.n % V == 0 && !p.res) {  // the ring kernel streams one tensor
     int rc = B200_OK;
     if (try_launch_norm_fwd_stream<Tin, Tout>(p, st, &rc)) return rc;
   }
   if (vector_ok && p.n % V == 0 && pick_row_geometry(p.n / V, &g)) {
-    set_path_tag(g.block ? "vector, row resident, CTA per row" : "vector, row resident, sub-warp rows");
-#define B200_NF_LAUNCH(GG, CC) norm_fwd_resident_kernel<Tin, Tout, CC, GG><<<grid, g.threads, 0, st>>>(p)
+    set_path_tag(g.block ? (p.res ? "residual add, vector, row resident, CTA per row" : "vector, row resident, CTA per row")
+                         : (p.res ? "residual add, vector, row resident, sub-warp rows" : "vector, row resident, sub-warp rows"));
+#define B200_NF_LAUNCH(GG, CC)                                                                       \
+  do {                                                                                               \
+    if constexpr (kResBuilt) {                                                                       \
+      if (p.res) {                                                                                   \
+        norm_fwd_resident_kernel<Tin, Tout, CC, GG, true><<<grid, g.threads, 0, st>>>(p);            \
+        break;                                                                                       \
+      }                                                                                              \
+    }                                                                                                \
+    norm_fwd_resident_kernel<Tin, Tout, CC, GG><<<grid, g.threads, 0, st>>>(p);                      \
+  } while (0)
     if (!g.block) {
       const int rows_per_cta = g.threads / g.g;
       const unsigned grid = (unsigned)((p.rows + rows_per_cta - 1) / rows_per_cta);
@@ -562,7 +598,7 @@ static int launch_norm_fwd(const NormFwdParams& p, bool vector_ok, cudaStream_t 
   } else {
     int threads = 1024;
     while (threads > 64 && threads / 2 >= p.n) threads /= 2;
-    set_path_tag("element-wise, CTA per row");
+    set_path_tag(p.res ? "residual add, element-wise, CTA per row" : "element-wise, CTA per row");
     norm_fwd_streaming_kernel<Tin, Tout><<<(unsigned)p.rows, threads, 0, st>>>(p);
   }
   return launch_status("b200_norm_fwd");
@@ -576,12 +612,13 @@ using namespace b200;
 // operation). Synchronises the device.
 extern "C" int64_t b200_norm_fwd_wait_timeouts(void) { return (int64_t)read_wait_timeouts(); }
 
-extern "C" int b200_norm_fwd(const void* x, const void* weight, const void* bias, void* y,
-                             float* mean_out, float* rstd_out, float* var_out, int64_t rows,
-                             int64_t n, int64_t x_row_stride, int64_t y_row_stride,
-                             int32_t x_dtype, int32_t w_dtype, int32_t y_dtype, double eps,
-                             double correction, int32_t rms, void* stream) {
+extern "C" int b200_norm_fwd_residual(const void* x, const void* residual, void* sum_out, const void* weight,
+                                      const void* bias, void* y, float* mean_out, float* rstd_out, float* var_out,
+                                      int64_t rows, int64_t n, int64_t x_row_stride, int64_t y_row_stride,
+                                      int32_t x_dtype, int32_t w_dtype, int32_t y_dtype, double eps,
+                                      double correction, int32_t rms, void* stream) {
   if (!x) return fail(B200_ERR_INVALID, "b200_norm_fwd: null x");
+  if (sum_out && !residual) return fail(B200_ERR_INVALID, "b200_norm_fwd_residual: sum_out without residual");
   if (rows < 0 || n < 0 || n > 0x7fffffffLL)
     return fail(B200_ERR_INVALID, "b200_norm_fwd: bad sizes rows=%lld n=%lld", (long long)rows, (long long)n);
   if (rows == 0) return B200_OK;
@@ -595,6 +632,7 @@ extern "C" int b200_norm_fwd(const void* x, const void* weight, const void* bias
   p.x_row_stride = x_row_stride; p.y_row_stride = y_row_stride;
   p.w_dtype = w_dtype; p.eps = (float)eps; p.rms = (rms & 1) ? 1 : 0;
   p.prologue = (rms & 2) ? 1 : 0;  // bit 1 of the mode word: exact GELU of x, rounded to x's dtype, first
+  p.res = residual; p.sum_out = sum_out;
   p.inv_n = (float)(1.0 / (double)n);
   p.inv_denom = (float)(1.0 / ((double)n - correction));  // inf/NaN for n <= correction, as aten
 
@@ -603,6 +641,7 @@ extern "C" int b200_norm_fwd(const void* x, const void* weight, const void* bias
   const int out_chunk = v_in * ob < 16 ? v_in * ob : 16;
   const int w_chunk = v_in * wb < 16 ? v_in * wb : 16;
   bool vec = aligned16(x) && (x_row_stride * ib) % 16 == 0;
+  if (residual) vec = vec && aligned16(residual) && (!sum_out || (aligned16(sum_out) && (n * ib) % 16 == 0));
   if (y) vec = vec && reinterpret_cast<uintptr_t>(y) % out_chunk == 0 && (y_row_stride * ob) % out_chunk == 0;
   if (weight) vec = vec && reinterpret_cast<uintptr_t>(weight) % w_chunk == 0;
   if (bias) vec = vec && reinterpret_cast<uintptr_t>(bias) % w_chunk == 0;
@@ -619,4 +658,13 @@ extern "C" int b200_norm_fwd(const void* x, const void* weight, const void* bias
   B200_NORM_CASE(float, __half, B200_F32, B200_F16)
 #undef B200_NORM_CASE
   return fail(B200_ERR_UNSUPPORTED, "b200_norm_fwd: dtype pair (%d -> %d) not built", x_dtype, y_dtype);
+}
+
+extern "C" int b200_norm_fwd(const void* x, const void* weight, const void* bias, void* y,
+                             float* mean_out, float* rstd_out, float* var_out, int64_t rows,
+                             int64_t n, int64_t x_row_stride, int64_t y_row_stride,
+                             int32_t x_dtype, int32_t w_dtype, int32_t y_dtype, double eps,
+                             double correction, int32_t rms, void* stream) {
+  return b200_norm_fwd_residual(x, nullptr, nullptr, weight, bias, y, mean_out, rstd_out, var_out, rows, n,
+                                x_row_stride, y_row_stride, x_dtype, w_dtype, y_dtype, eps, correction, rms, stream);
 }

@@ -8,3 +8,36 @@ def oracle_forward(inputs, *, eps=1e-12, out_dtype=None, keepdim=False):
     y, mean, rstd, _ = kernels.norm_fwd(x, weight, bias, eps=eps, out_dtype=out_dtype or x.dtype,
                                         want_mean=True, want_rstd=True, keepdim=keepdim)
     return (y, mean, rstd)
+
+
+def _resolve(shape, numel):
+    dims = [int(d) for d in shape]
+    if -1 in dims:
+        known = 1
+        for d in dims:
+            if d != -1:
+                known *= d
+        dims[dims.index(-1)] = numel // known if known else 0
+    return dims
+
+
+def residual_forward(inputs, *, eps, returns=("y2",)):
+    """Residual add -> LayerNorm, the post-LayerNorm block
+    (repros/canonical/var_mean_0ada225c0a04/repro.py:24-40 and its siblings): the rows that are
+    normalised are ``T(x + residual)``. Inputs: x ``[rows, n]``, residual (``[B, S, n]`` or
+    ``[rows, n]``), weight, bias, the lifted 3-D and 2-D shapes. ``returns`` names what the graph
+    returns, in its order: ``sum3`` / ``sum2`` (the rounded sum, 3-D / 2-D), ``mean`` / ``rstd``
+    (``[B, S, 1]`` fp32), ``y3`` / ``y2`` (the output, 3-D / its 2-D view - the same buffer)."""
+    x, res, weight, bias, shape3, shape2 = inputs[:6]
+    x3 = x.view(_resolve(shape3, x.numel()))
+    want_sum = "sum3" in returns or "sum2" in returns
+    out = kernels.norm_fwd(x3, weight, bias, eps=eps, residual=res.view(x3.shape), want_sum=want_sum,
+                           want_mean="mean" in returns, want_rstd="rstd" in returns)
+    y3, mean, rstd = out[0], out[1], out[2]
+    shape2 = _resolve(shape2, x.numel())
+    pick = {"y3": y3, "y2": y3.view(shape2), "mean": mean, "rstd": rstd}
+    if want_sum:
+        pick["sum3"], pick["sum2"] = out[4], out[4].view(shape2)
+    got = tuple(pick[name] for name in returns)
+    return got[0] if len(got) == 1 else got
+

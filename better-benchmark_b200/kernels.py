@@ -218,17 +218,26 @@ def norm_fwd(x: torch.Tensor, weight: torch.Tensor | None, bias: torch.Tensor | 
              eps: float, rms: bool = False, out_dtype: torch.dtype | None = None,
              want_y: bool = True, want_mean: bool = False, want_rstd: bool = False,
              want_var: bool = False, correction: float = 0.0, keepdim: bool = True,
-             prologue: str | None = None):
+             prologue: str | None = None, residual: torch.Tensor | None = None, want_sum: bool = False):
     """LayerNorm (rms=False) or RMSNorm (rms=True) forward over the last dimension.
 
     ``prologue="gelu_erf"`` normalises ``gelu(x)`` (exact, erf form) rounded to x's dtype instead
     of x: the activation that the graph materialises in front of the norm is fused into the load.
+    ``residual`` (x's shape, dtype and strides) normalises ``x + residual`` rounded to x's dtype, the
+    sum a post-LayerNorm block materialises; ``want_sum`` returns that sum as a fifth value.
 
     Returns (y, mean, rstd, var) with None for the outputs not requested. Statistics are fp32 with
     x's outer shape (plus a trailing 1 when ``keepdim``).
     """
-    _require_cuda(x, weight, bias)
+    _require_cuda(x, weight, bias, residual)
     rows, n, x_stride = _rows_2d(x, "norm_fwd")
+    if residual is not None:
+        if residual.shape != x.shape or residual.dtype != x.dtype or residual.stride() != x.stride():
+            raise UnsupportedLayout("norm_fwd: residual must have x's shape, dtype and strides")
+        if out_dtype not in (None, x.dtype):
+            raise UnsupportedLayout("norm_fwd: with a residual y has x's dtype")
+    elif want_sum:
+        raise native.KernelArgumentError("norm_fwd: want_sum needs a residual")
     out_dtype = out_dtype or x.dtype
     w_code = F32
     for p in (weight, bias):
@@ -249,12 +258,20 @@ def norm_fwd(x: torch.Tensor, weight: torch.Tensor | None, bias: torch.Tensor | 
 
     mean, rstd, var = stat(want_mean and not rms), stat(want_rstd), stat(want_var)
     lib = load()
-    check(lib.b200_norm_fwd(_ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _ptr(mean), _ptr(rstd),
-                            _ptr(var), rows, n, x_stride, y_stride, _code(x), w_code,
-                            _DTYPE_CODE[out_dtype], float(eps), float(correction),
-                            (1 if rms else 0) | _NORM_PROLOGUES[prologue], _stream()),
-          "b200_norm_fwd")
-    return y, mean, rstd, var
+    if residual is None:
+        check(lib.b200_norm_fwd(_ptr(x), _ptr(weight), _ptr(bias), _ptr(y), _ptr(mean), _ptr(rstd),
+                                _ptr(var), rows, n, x_stride, y_stride, _code(x), w_code,
+                                _DTYPE_CODE[out_dtype], float(eps), float(correction),
+                                (1 if rms else 0) | _NORM_PROLOGUES[prologue], _stream()),
+              "b200_norm_fwd")
+        return y, mean, rstd, var
+    total = torch.empty(x.shape, dtype=x.dtype, device=x.device) if want_sum else None
+    check(lib.b200_norm_fwd_residual(_ptr(x), _ptr(residual), _ptr(total), _ptr(weight), _ptr(bias), _ptr(y),
+                                     _ptr(mean), _ptr(rstd), _ptr(var), rows, n, x_stride, y_stride, _code(x),
+                                     w_code, _DTYPE_CODE[out_dtype], float(eps), float(correction),
+                                     (1 if rms else 0) | _NORM_PROLOGUES[prologue], _stream()),
+          "b200_norm_fwd_residual")
+    return (y, mean, rstd, var, total) if want_sum else (y, mean, rstd, var)
 
 
 # ---------------------------------------------------------------------------------------------

@@ -56,6 +56,9 @@ SIGNATURES = {
     "b200_norm_fwd": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, _PF, _PF, _PF, c_int64,
                                 c_int64, c_int64, c_int64, c_int32, c_int32, c_int32, c_double,
                                 c_double, c_int32, c_void_p]),
+    "b200_norm_fwd_residual": (c_int32, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, _PF, _PF, _PF,
+                                         c_int64, c_int64, c_int64, c_int64, c_int32, c_int32, c_int32, c_double,
+                                         c_double, c_int32, c_void_p]),
     "b200_norm_fwd_wait_timeouts": (c_int64, []),
     "b200_norm_bwd_wait_timeouts": (c_int64, []),
     "b200_norm_bwd_scratch_bytes": (c_int64, [c_int64]),

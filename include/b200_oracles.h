@@ -103,6 +103,17 @@ int32_t b200_norm_fwd(const void* x, const void* weight, const void* bias, void*
                       int64_t y_row_stride, int32_t x_dtype, int32_t w_dtype, int32_t y_dtype,
                       double eps, double correction, int32_t rms, void* stream);
 
+/* b200_norm_fwd with a residual prologue: the rows that are normalised are T(x + residual), the sum
+ * rounded to x's dtype as the graphs of the post-LayerNorm blocks materialise it
+ * (var_mean_0ada225c0a04/repro.py:26-27). residual: x's dtype, x's row stride; sum_out (may be NULL):
+ * receives the rounded sum, x's dtype, rows of n contiguous elements; y must have x's dtype.
+ * residual = NULL is b200_norm_fwd. Replaces var_mean_0ada225c0a04/oracle.py, var_mean_f4578c128d74/oracle.py. */
+int32_t b200_norm_fwd_residual(const void* x, const void* residual, void* sum_out, const void* weight,
+                               const void* bias, void* y, float* mean_out, float* rstd_out, float* var_out,
+                               int64_t rows, int64_t n, int64_t x_row_stride, int64_t y_row_stride,
+                               int32_t x_dtype, int32_t w_dtype, int32_t y_dtype, double eps, double correction,
+                               int32_t rms, void* stream);
+
 /* Number of bounded device-side waits of b200_norm_fwd's streaming kernel that ran out since the
  * library was loaded: 0 in normal operation. Synchronises the device (diagnostic). No counterpart
  * in the reference. */

@@ -448,6 +448,31 @@ class DropoutAdd(nn.Module):
         return (mask, aten.add.Tensor(residual, mul_1))
 
 
+class ResidualLayerNormFwd(nn.Module):
+    """Residual add -> LayerNorm, the post-LayerNorm block. Graph: reference
+    repros/canonical/var_mean_0ada225c0a04/repro.py:24-40 (the sum of the two 16-bit tensors is a
+    16-bit tensor; statistics and normalisation in fp32; y rounded to the tensor dtype). The sibling
+    directories differ in eps and in what they return (``returns``: sum3 / sum2 = the rounded sum as
+    a 3-D / 2-D tensor, mean, rstd, y3, y2 = y and its 2-D view)."""
+
+    def __init__(self, eps: float, returns=("y2",)):
+        super().__init__()
+        self.eps, self.returns = eps, tuple(returns)
+
+    def forward(self, x, residual, weight, bias, shape3, shape2):
+        view = aten.view.default(x, shape3)
+        add = aten.add.Tensor(aten.view.default(residual, list(view.shape)), view)
+        af = _f32(add)
+        var_mean = aten.var_mean.correction(af, [-1], correction=0, keepdim=True)
+        rstd = aten.rsqrt.default(aten.add.Tensor(var_mean[0], self.eps))
+        out = aten.add.Tensor(aten.mul.Tensor(aten.mul.Tensor(aten.sub.Tensor(af, var_mean[1]), rstd), weight), bias)
+        y3 = prims.convert_element_type.default(out, x.dtype)
+        pick = {"sum3": add, "sum2": aten.view.default(add, shape2), "mean": var_mean[1], "rstd": rstd,
+                "y3": y3, "y2": aten.view.default(y3, shape2)}
+        got = tuple(pick[name] for name in self.returns)
+        return got[0] if len(got) == 1 else got
+
+
 class SoftmaxDropout(nn.Module):
     """dropout(softmax(x + bias)), returning (logits, amax, sum, keep, y, y transposed).
 

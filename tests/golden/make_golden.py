@@ -86,6 +86,22 @@ CASES = {
                                      [[[12, 16, 64], "bf16"], [[4, 3, 16, 64], "f32", {"st": [3072, 1, 192, 3]}],
                                       [[84], "i64"], ["S", [4, 3, 16, 64]], ["S", [4, 3, 16, 64]],
                                       ["S", [4, 3, 16, 64]], ["S", [12, 16, 64]]]),
+    # residual add -> LayerNorm and four of its siblings (other eps, other outputs, fp32 weights)
+    "res_ln_0ada225c0a04": ("var_mean_0ada225c0a04",
+                            [[[96, 768], "bf16"], [[4, 24, 768], "bf16"], [[768], "bf16"], [[768], "bf16"],
+                             ["S", [4, 24, 768]], ["S", [96, 768]]]),
+    "res_ln_sum_f4578c128d74": ("var_mean_f4578c128d74",
+                                [[[66, 320], "bf16"], [[2, 33, 320], "bf16"], [[320], "bf16"], [[320], "bf16"],
+                                 ["S", [2, 33, 320]], ["S", [66, 320]]]),
+    "res_ln_alias_45f7dfd4a983": ("var_mean_45f7dfd4a983",
+                                  [[[24, 4096], "bf16"], [[2, 12, 4096], "bf16"], [[4096], "bf16"], [[4096], "bf16"],
+                                   ["S", [2, 12, 4096]], ["S", [24, 4096]]]),
+    "res_ln_sum2_49afc8635b79": ("var_mean_49afc8635b79",
+                                 [[[96, 768], "bf16"], [[4, 24, 768], "bf16"], [[768], "bf16"], [[768], "bf16"],
+                                  ["S", [4, 24, 768]], ["S", [-1, 768]]]),
+    "res_ln_stats_547bcc63004b": ("var_mean_547bcc63004b",
+                                  [[[80, 240], "bf16"], [[5, 16, 240], "bf16"], [[240], "f32"], [[240], "f32"],
+                                   ["S", [5, 16, 240]], ["S", [80, 240]]]),
     "dropout_add_4b076ed1ff41": ("pointwise_4b076ed1ff41",
                                  [[[48, 320], "bf16"], [[2], "i64"], [[3, 16, 320], "f32"],
                                   ["S", [3, 16, 320]], ["S", [3, 16, 320]]]),

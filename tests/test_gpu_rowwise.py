@@ -284,3 +284,43 @@ def test_gelu_prologue_layer_norm_matches_eager(rows, n, dtype):
     want = GeluLayerNormFwd(1e-12)(x, w, b)
     y, _, _, _ = _kernels().norm_fwd(x.cuda(), w.cuda(), b.cuda(), eps=1e-12, prologue="gelu_erf")
     assert_close(y, want, f"gelu + layer norm {rows}x{n} {dtype}")
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("rows,n", [(300, 768), (64, 128), (96, 4096), (40, 240), (5, 1001), (7, 10000), (20000, 768)])
+def test_residual_prologue_layer_norm_matches_eager(rows, n, dtype):
+    """x + residual, rounded to the tensor dtype, fused into the load of the LayerNorm kernels; the
+    rounded sum is an optional output. Row lengths that take the resident vector kernels and ones
+    that take the element-wise kernel (odd length, very long rows)."""
+    from oracle.eager import ResidualLayerNormFwd
+    k = _kernels()
+    x = _randn((rows, n), dtype, seed=n, scale=1.5)
+    r = _randn((rows, n), dtype, seed=n + 1, scale=1.0)
+    g = torch.Generator().manual_seed(1)
+    w = (torch.rand(n, generator=g) + 0.5)
+    b = (0.1 * torch.randn(n, generator=g))
+    if n % 2 == 0:       # 16-bit weights for half of the cases, fp32 weights for the rest
+        w, b = w.to(dtype), b.to(dtype)
+    want = ResidualLayerNormFwd(1e-6, ("sum3", "mean", "rstd", "y3"))(x, r, w, b, [1, rows, n], [rows, n])
+    y, mean, rstd, _, total = k.norm_fwd(x.cuda().view(1, rows, n), w.cuda(), b.cuda(), eps=1e-6,
+                                         residual=r.cuda().view(1, rows, n), want_sum=True, want_mean=True,
+                                         want_rstd=True)
+    assert b"residual add" in k.load().b200_last_kernel()
+    assert torch.equal(total.cpu(), want[0]), "the rounded sum"
+    assert_close(mean, want[1], f"mean {rows}x{n} {dtype}")
+    assert_close(rstd, want[2], f"rstd {rows}x{n} {dtype}")
+    assert_close(y, want[3], f"residual + layer norm {rows}x{n} {dtype}")
+    y2 = k.norm_fwd(x.cuda(), w.cuda(), b.cuda(), eps=1e-6, residual=r.cuda())[0]
+    assert torch.equal(y2.view(-1), y.view(-1)), "the same without the optional outputs"
+
+
+def test_residual_prologue_rejections():
+    from better_benchmark_b200 import kernels as kk
+    k = _kernels()
+    x = torch.zeros(8, 64, device="cuda", dtype=torch.bfloat16)
+    with pytest.raises(kk.UnsupportedLayout):
+        k.norm_fwd(x, None, None, eps=1e-5, residual=torch.zeros(8, 64, device="cuda"))          # dtype differs
+    with pytest.raises(kk.UnsupportedLayout):
+        k.norm_fwd(x, None, None, eps=1e-5, residual=torch.zeros(4, 64, device="cuda", dtype=torch.bfloat16))
+    with pytest.raises(kk.UnsupportedLayout):
+        k.norm_fwd(x, None, None, eps=1e-5, residual=x.clone(), out_dtype=torch.float32)        # y in another dtype

@@ -95,6 +95,12 @@ def golden_cases():
         mask = recorded[3] if recorded is not None else None
         return list(eager.SoftmaxDropout(0.1, 29)(x, bias, seeds, mask=mask))
 
+    def res_ln(eps, returns):
+        def run(inp):
+            out = eager.ResidualLayerNormFwd(eps, returns)(*inp)
+            return [out] if isinstance(out, torch.Tensor) else list(out)
+        return run
+
     def gelu_ln(inp):
         x, w, b, s0, s1 = inp
         return [eager.GeluLayerNormFwd(1e-12)(x.view(s0), w, b).view(s1)]
@@ -123,6 +129,9 @@ def golden_cases():
         "cast_alias_8bb40810003c": cast_alias, "scale_view_95ed2ef35da9": scale_view,
         "qkv_views_1611fb0c7845": qkv_views, "gelu_ln_af505388b035": gelu_ln,
         "dropout_add_4b076ed1ff41": dropout_add, "softmax_dropout_089fdab8f22b": softmax_dropout,
+        "res_ln_0ada225c0a04": res_ln(1e-6, ("y2",)), "res_ln_sum_f4578c128d74": res_ln(1e-6, ("sum3", "y2")),
+        "res_ln_alias_45f7dfd4a983": res_ln(1e-12, ("y3", "y2")), "res_ln_sum2_49afc8635b79": res_ln(1e-5, ("sum2", "y2")),
+        "res_ln_stats_547bcc63004b": res_ln(1e-5, ("sum3", "mean", "rstd", "y2")),
         "gelu_ln_stats_21faaccf749d": gelu_ln_stats, "headmerge_e87d6ebc9ded": headmerge,
         "qkv_views_d5a413a2c233": qkv_views_kvq,
         "dropout_ln_01fbd6c1b27f": dropout_ln,
