@@ -32,7 +32,8 @@ struct PermuteParams {
 template <typename Tin, typename Tout>
 __device__ __forceinline__ Tout convert_scaled(Tin v, float scale, int has_scale) {
   float f = Elem<Tin>::to_f32(v);
-  if (has_scale) f = f * scale;
+  if (has_scale & 1) f = f * scale;
+  if (has_scale & 2) f = f < 0.f ? 0.f : f;  // ReLU; a NaN stays a NaN, as aten's
   return Elem<Tout>::from_f32(f);
 }
 
@@ -249,7 +250,7 @@ __global__ void __launch_bounds__(256) transpose_small_kernel(const TransposePar
   }
 }
 
-// Contiguous cast / scale.
+// Contiguous cast / scale / ReLU (has_scale: bit 0 multiply by scale, bit 1 ReLU after it).
 template <typename Tin, typename Tout, bool VEC>
 __global__ void __launch_bounds__(256) cast_scale_kernel(const void* x, void* y, long long n, float scale,
                                                          int has_scale) {
@@ -276,9 +277,13 @@ __global__ void __launch_bounds__(256) cast_scale_kernel(const void* x, void* y,
         if (u < units) {
           float f[VIN];
           Elem<Tin>::unpack(raw[k], f);
-          if (has_scale) {
+          if (has_scale & 1) {
 #pragma unroll
             for (int i = 0; i < VIN; ++i) f[i] = f[i] * scale;
+          }
+          if (has_scale & 2) {
+#pragma unroll
+            for (int i = 0; i < VIN; ++i) f[i] = f[i] < 0.f ? 0.f : f[i];
           }
           store_converted<Tout, VIN>(dst + u * VIN, f);
         }
@@ -430,7 +435,7 @@ extern "C" int b200_cast_scale(const void* x, void* y, int64_t n, int32_t in_dty
   const bool vec = aligned16(x) && reinterpret_cast<uintptr_t>(y) % out_chunk == 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define B200_CASE(TI, TO, DI, DO) \
-  if (in_dtype == DI && out_dtype == DO) return launch_cast<TI, TO>(x, y, n, (float)scale, has_scale ? 1 : 0, vec, st);
+  if (in_dtype == DI && out_dtype == DO) return launch_cast<TI, TO>(x, y, n, (float)scale, has_scale & 3, vec, st);
   B200_DTYPE_PAIRS(B200_CASE)
 #undef B200_CASE
   return fail(B200_ERR_UNSUPPORTED, "b200_cast_scale: dtype pair (%d -> %d) not built", in_dtype, out_dtype);

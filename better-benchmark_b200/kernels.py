@@ -574,16 +574,17 @@ def _collapse_all(shape, strides_list):
     return dims, strs
 
 
-def cast_scale(x: torch.Tensor, out_dtype: torch.dtype, *, scale: float | None = None) -> torch.Tensor:
-    """Element-wise ``(x * scale).to(out_dtype)`` for a dense tensor; the result keeps x's strides."""
+def cast_scale(x: torch.Tensor, out_dtype: torch.dtype, *, scale: float | None = None, relu: bool = False) -> torch.Tensor:
+    """Element-wise ``relu(x * scale).to(out_dtype)`` (scale and relu optional) for a dense tensor in
+    any dimension order; the result keeps x's strides."""
     _require_cuda(x)
     if not _is_dense(x):
         raise UnsupportedLayout("cast_scale: x must be dense")
     out = torch.empty_strided(x.shape, x.stride(), dtype=out_dtype, device=x.device)
     lib = load()
     check(lib.b200_cast_scale(_ptr(x), _ptr(out), x.numel(), _code(x), _DTYPE_CODE[out_dtype],
-                              float(scale) if scale is not None else 1.0, 1 if scale is not None else 0,
-                              _stream()),
+                              float(scale) if scale is not None else 1.0,
+                              (1 if scale is not None else 0) | (2 if relu else 0), _stream()),
           "b200_cast_scale")
     return out
 

@@ -505,6 +505,26 @@ class SoftmaxDropout(nn.Module):
         return (logits, amax, total, mask, y3, aten.permute.default(y3, [0, 2, 1]))
 
 
+class ParameterCast(nn.Module):
+    """One ``convert_element_type`` (reference repros/canonical/pointwise_04d85912d998/repro.py:24-27
+    bf16 -> f32 and pointwise_ccd411f2a45d/repro.py:24-27 f32 -> bf16: the casts of a model's
+    parameters). The result keeps the strides of a dense input (channels-last weights)."""
+
+    def __init__(self, out_dtype):
+        super().__init__()
+        self.out_dtype = out_dtype
+
+    def forward(self, x):
+        return prims.convert_element_type.default(x, self.out_dtype)
+
+
+class Relu(nn.Module):
+    """``aten.relu`` (reference repros/canonical/pointwise_3abc926270f6/repro.py:24-27)."""
+
+    def forward(self, x):
+        return aten.relu.default(x)
+
+
 class CastWithTransposedAlias(nn.Module):
     """Reference graph: repros/canonical/pointwise_8bb40810003c/repro.py:23-29. One cast; the two
     outputs are views of the same buffer (its transpose and itself)."""

@@ -102,6 +102,10 @@ CASES = {
     "res_ln_stats_547bcc63004b": ("var_mean_547bcc63004b",
                                   [[[80, 240], "bf16"], [[5, 16, 240], "bf16"], [[240], "f32"], [[240], "f32"],
                                    ["S", [5, 16, 240]], ["S", [80, 240]]]),
+    # parameter casts (a channels-last weight keeps its strides) and ReLU, all in storage order
+    "cast_param_04d85912d998": ("pointwise_04d85912d998", [[[8, 3, 3, 3], "bf16", {"st": [27, 1, 9, 3]}]]),
+    "cast_param_ccd411f2a45d": ("pointwise_ccd411f2a45d", [[[1003], "f32"]]),
+    "relu_3abc926270f6": ("pointwise_3abc926270f6", [[[4, 24, 5, 5], "bf16"]]),
     "dropout_add_4b076ed1ff41": ("pointwise_4b076ed1ff41",
                                  [[[48, 320], "bf16"], [[2], "i64"], [[3, 16, 320], "f32"],
                                   ["S", [3, 16, 320]], ["S", [3, 16, 320]]]),

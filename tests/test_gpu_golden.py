@@ -30,7 +30,8 @@ FIXTURE_DIR = {
     "qkv_views_d5a413a2c233": "pointwise_d5a413a2c233", "softmax_dropout_089fdab8f22b": "amax_sum_089fdab8f22b",
     "res_ln_0ada225c0a04": "var_mean_0ada225c0a04", "res_ln_sum_f4578c128d74": "var_mean_f4578c128d74",
     "res_ln_alias_45f7dfd4a983": "var_mean_45f7dfd4a983", "res_ln_sum2_49afc8635b79": "var_mean_49afc8635b79",
-    "res_ln_stats_547bcc63004b": "var_mean_547bcc63004b",
+    "res_ln_stats_547bcc63004b": "var_mean_547bcc63004b", "cast_param_04d85912d998": "pointwise_04d85912d998",
+    "cast_param_ccd411f2a45d": "pointwise_ccd411f2a45d", "relu_3abc926270f6": "pointwise_3abc926270f6",
 }
 # regions that draw random numbers: output index -> mask index it depends on element by element
 STOCHASTIC = {"dropout_rms_014afd4984e6": {"masks": (0, 3), "elementwise": {1: 0}},

@@ -185,3 +185,35 @@ def test_cast_between_the_two_16_bit_types_is_rejected_loudly():
     from better_benchmark_b200.native import KernelArgumentError
     with pytest.raises(KernelArgumentError):
         k.cast_scale(_rand((64,), torch.bfloat16, 1), torch.float16)
+
+
+@pytest.mark.parametrize("shape,strides", [((8, 3, 3, 3), (27, 1, 9, 3)), ((64, 32, 3, 3), None), ((1003,), None),
+                                           ((1,), None), ((5, 7, 1, 1), (7, 1, 7, 7)), ((2, 16, 33), None)])
+@pytest.mark.parametrize("src,dst", [(torch.bfloat16, torch.float32), (torch.float32, torch.bfloat16),
+                                     (torch.float16, torch.float32)])
+def test_parameter_casts_keep_the_strides_of_dense_tensors(shape, strides, src, dst):
+    """convert_element_type of a model's parameters: storage order, so a channels-last weight comes
+    back channels-last; sizes that are no multiple of the vector, down to one element."""
+    from better_benchmark_b200 import kernels
+    n = 1
+    for d in shape:
+        n *= d
+    base = (torch.randn(n, generator=torch.Generator().manual_seed(n)) * 3).to(src).cuda()
+    x = torch.as_strided(base, shape, strides) if strides else base.view(shape)
+    y = kernels.cast_scale(x, dst)
+    assert y.stride() == x.stride() and y.dtype == dst
+    assert torch.equal(y, x.to(dst))
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("shape", [(128, 768, 1, 1), (4, 24, 5, 5), (3, 1001), (7,)])
+def test_relu_in_storage_order(dtype, shape):
+    from better_benchmark_b200 import kernels
+    n = 1
+    for d in shape:
+        n *= d
+    x = (torch.randn(n, generator=torch.Generator().manual_seed(n + 1)) * 2).to(dtype).view(shape).cuda()
+    x.view(-1)[0] = float("nan")
+    y = kernels.cast_scale(x, dtype, relu=True)
+    want = torch.relu(x)
+    assert torch.equal(torch.isnan(y), torch.isnan(want)) and torch.equal(torch.nan_to_num(y), torch.nan_to_num(want))

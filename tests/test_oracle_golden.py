@@ -132,6 +132,9 @@ def golden_cases():
         "res_ln_0ada225c0a04": res_ln(1e-6, ("y2",)), "res_ln_sum_f4578c128d74": res_ln(1e-6, ("sum3", "y2")),
         "res_ln_alias_45f7dfd4a983": res_ln(1e-12, ("y3", "y2")), "res_ln_sum2_49afc8635b79": res_ln(1e-5, ("sum2", "y2")),
         "res_ln_stats_547bcc63004b": res_ln(1e-5, ("sum3", "mean", "rstd", "y2")),
+        "cast_param_04d85912d998": lambda inp: [eager.ParameterCast(torch.float32)(inp[0])],
+        "cast_param_ccd411f2a45d": lambda inp: [eager.ParameterCast(torch.bfloat16)(inp[0])],
+        "relu_3abc926270f6": lambda inp: [eager.Relu()(inp[0])],
         "gelu_ln_stats_21faaccf749d": gelu_ln_stats, "headmerge_e87d6ebc9ded": headmerge,
         "qkv_views_d5a413a2c233": qkv_views_kvq,
         "dropout_ln_01fbd6c1b27f": dropout_ln,
