@@ -29,11 +29,22 @@ struct PermuteParams {
   int has_scale;
 };
 
+// Activation bits of the mode word (after the optional scaling), each the fp32 expression of the
+// decomposed aten graph: 2 ReLU (a NaN stays a NaN); 4 exact GELU, (x * 0.5) * (erf(x * 0.7071067811865476) + 1)
+// (repros/canonical/pointwise_826ea0b5f6e4/repro.py:27-31); 8 SiLU, x / (exp(-x) + 1)
+// (repros/canonical/pointwise_795cdbe23b17/repro.py:26-29).
+__device__ __forceinline__ float apply_activation(float f, int mode) {
+  if (mode & 2) f = f < 0.f ? 0.f : f;
+  if (mode & 4) f = (f * 0.5f) * (erff(f * 0.7071067811865476f) + 1.0f);
+  if (mode & 8) f = f / (expf(-f) + 1.0f);
+  return f;
+}
+
 template <typename Tin, typename Tout>
 __device__ __forceinline__ Tout convert_scaled(Tin v, float scale, int has_scale) {
   float f = Elem<Tin>::to_f32(v);
   if (has_scale & 1) f = f * scale;
-  if (has_scale & 2) f = f < 0.f ? 0.f : f;  // ReLU; a NaN stays a NaN, as aten's
+  f = apply_activation(f, has_scale);
   return Elem<Tout>::from_f32(f);
 }
 
@@ -250,7 +261,7 @@ __global__ void __launch_bounds__(256) transpose_small_kernel(const TransposePar
   }
 }
 
-// Contiguous cast / scale / ReLU (has_scale: bit 0 multiply by scale, bit 1 ReLU after it).
+// Contiguous cast / scale / activation (has_scale: bit 0 multiply by scale; bits 1..3 ReLU, exact GELU, SiLU after it).
 template <typename Tin, typename Tout, bool VEC>
 __global__ void __launch_bounds__(256) cast_scale_kernel(const void* x, void* y, long long n, float scale,
                                                          int has_scale) {
@@ -281,9 +292,9 @@ __global__ void __launch_bounds__(256) cast_scale_kernel(const void* x, void* y,
 #pragma unroll
             for (int i = 0; i < VIN; ++i) f[i] = f[i] * scale;
           }
-          if (has_scale & 2) {
+          if (has_scale & 14) {
 #pragma unroll
-            for (int i = 0; i < VIN; ++i) f[i] = f[i] < 0.f ? 0.f : f[i];
+            for (int i = 0; i < VIN; ++i) f[i] = apply_activation(f[i], has_scale);
           }
           store_converted<Tout, VIN>(dst + u * VIN, f);
         }
@@ -435,7 +446,7 @@ extern "C" int b200_cast_scale(const void* x, void* y, int64_t n, int32_t in_dty
   const bool vec = aligned16(x) && reinterpret_cast<uintptr_t>(y) % out_chunk == 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
 #define B200_CASE(TI, TO, DI, DO) \
-  if (in_dtype == DI && out_dtype == DO) return launch_cast<TI, TO>(x, y, n, (float)scale, has_scale & 3, vec, st);
+  if (in_dtype == DI && out_dtype == DO) return launch_cast<TI, TO>(x, y, n, (float)scale, has_scale & 15, vec, st);
   B200_DTYPE_PAIRS(B200_CASE)
 #undef B200_CASE
   return fail(B200_ERR_UNSUPPORTED, "b200_cast_scale: dtype pair (%d -> %d) not built", in_dtype, out_dtype);

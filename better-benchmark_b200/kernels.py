@@ -574,9 +574,16 @@ def _collapse_all(shape, strides_list):
     return dims, strs
 
 
-def cast_scale(x: torch.Tensor, out_dtype: torch.dtype, *, scale: float | None = None, relu: bool = False) -> torch.Tensor:
-    """Element-wise ``relu(x * scale).to(out_dtype)`` (scale and relu optional) for a dense tensor in
-    any dimension order; the result keeps x's strides."""
+_ACTIVATIONS = {None: 0, "relu": 2, "gelu_erf": 4, "silu": 8}
+
+
+def cast_scale(x: torch.Tensor, out_dtype: torch.dtype, *, scale: float | None = None, relu: bool = False,
+               activation: str | None = None) -> torch.Tensor:
+    """Element-wise ``act(x * scale).to(out_dtype)`` (scale and the activation optional; ``relu=True``
+    is ``activation="relu"``; also "gelu_erf", "silu") in fp32 for a dense tensor in any dimension
+    order; the result keeps x's strides."""
+    if relu:
+        activation = "relu"
     _require_cuda(x)
     if not _is_dense(x):
         raise UnsupportedLayout("cast_scale: x must be dense")
@@ -584,7 +591,7 @@ def cast_scale(x: torch.Tensor, out_dtype: torch.dtype, *, scale: float | None =
     lib = load()
     check(lib.b200_cast_scale(_ptr(x), _ptr(out), x.numel(), _code(x), _DTYPE_CODE[out_dtype],
                               float(scale) if scale is not None else 1.0,
-                              (1 if scale is not None else 0) | (2 if relu else 0), _stream()),
+                              (1 if scale is not None else 0) | _ACTIVATIONS[activation], _stream()),
           "b200_cast_scale")
     return out
 

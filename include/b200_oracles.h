@@ -232,11 +232,13 @@ int32_t b200_softmax_dropout(const void* x, const void* bias, int64_t batch, int
                              void* logits, void* amax, void* sum, void* keep, void* y, int32_t x_dtype,
                              void* stream);
 
-/* Contiguous cast / scale / ReLU of n elements: y = Tout(op(x)). has_scale is a mode word: bit 0
- * multiplies by scale (in fp32), bit 1 applies ReLU afterwards (a NaN stays a NaN).
+/* Contiguous cast / scale / activation of n elements: y = Tout(op(x)). has_scale is a mode word: bit 0
+ * multiplies by scale (in fp32); then bit 1 applies ReLU (a NaN stays a NaN), bit 2 the exact GELU
+ * (x * 0.5) * (erf(x * 0.7071067811865476) + 1), bit 3 SiLU x / (exp(-x) + 1), all in fp32.
  * Replaces pointwise_8bb40810003c/oracle.py:11-15, pointwise_95ed2ef35da9/oracle.py:10-44, and the
  * storage-order kernels of pointwise_04d85912d998/oracle.py, pointwise_ccd411f2a45d/oracle.py
- * (parameter casts) and pointwise_3abc926270f6/oracle.py (ReLU). */
+ * (parameter casts), pointwise_3abc926270f6/oracle.py (ReLU), pointwise_826ea0b5f6e4/oracle.py (GELU) and
+ * pointwise_795cdbe23b17/oracle.py (SiLU). */
 int32_t b200_cast_scale(const void* x, void* y, int64_t n, int32_t in_dtype, int32_t out_dtype, double scale,
                         int32_t has_scale, void* stream);
 

@@ -525,6 +525,26 @@ class Relu(nn.Module):
         return aten.relu.default(x)
 
 
+class GeluErf(nn.Module):
+    """Exact GELU of a 16-bit tensor in fp32 (reference
+    repros/canonical/pointwise_826ea0b5f6e4/repro.py:24-33: view, GELU, view back)."""
+
+    def forward(self, x, shape3, shape2):
+        xf = _f32(aten.view.default(x, shape3))
+        erf = aten.erf.default(aten.mul.Tensor(xf, 0.7071067811865476))
+        out = aten.mul.Tensor(aten.mul.Tensor(xf, 0.5), aten.add.Tensor(erf, 1))
+        return aten.view.default(prims.convert_element_type.default(out, x.dtype), shape2)
+
+
+class Silu(nn.Module):
+    """x / (exp(-x) + 1) in fp32 (reference repros/canonical/pointwise_795cdbe23b17/repro.py:24-30)."""
+
+    def forward(self, x):
+        xf = _f32(x)
+        out = aten.div.Tensor(xf, aten.add.Tensor(aten.exp.default(aten.neg.default(xf)), 1))
+        return prims.convert_element_type.default(out, x.dtype)
+
+
 class CastWithTransposedAlias(nn.Module):
     """Reference graph: repros/canonical/pointwise_8bb40810003c/repro.py:23-29. One cast; the two
     outputs are views of the same buffer (its transpose and itself)."""

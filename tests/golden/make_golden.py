@@ -106,6 +106,8 @@ CASES = {
     "cast_param_04d85912d998": ("pointwise_04d85912d998", [[[8, 3, 3, 3], "bf16", {"st": [27, 1, 9, 3]}]]),
     "cast_param_ccd411f2a45d": ("pointwise_ccd411f2a45d", [[[1003], "f32"]]),
     "relu_3abc926270f6": ("pointwise_3abc926270f6", [[[4, 24, 5, 5], "bf16"]]),
+    "gelu_826ea0b5f6e4": ("pointwise_826ea0b5f6e4", [[[66, 96], "bf16"], ["S", [2, 33, 96]], ["S", [66, 96]]]),
+    "silu_795cdbe23b17": ("pointwise_795cdbe23b17", [[[4, 24, 9, 9], "bf16", {"st": [1944, 1, 216, 24]}]]),
     "dropout_add_4b076ed1ff41": ("pointwise_4b076ed1ff41",
                                  [[[48, 320], "bf16"], [[2], "i64"], [[3, 16, 320], "f32"],
                                   ["S", [3, 16, 320]], ["S", [3, 16, 320]]]),

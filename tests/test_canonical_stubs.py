@@ -9,7 +9,7 @@ DIRS = sorted(p.name for p in CANONICAL.iterdir() if (p / "oracle.py").is_file()
 
 
 def test_the_expected_directories_are_shipped():
-    assert len(DIRS) == 46
+    assert len(DIRS) == 48
     assert sum("b200c" in d for d in DIRS) == 5
     for needed in ("var_mean_f8ec553e339e", "sum_sum_183b124c731f", "pointwise_021e90d9c17d", "mean_c9e1a8113328",
                    "mean_014afd4984e6", "var_mean_01fbd6c1b27f", "pointwise_4b076ed1ff41",

@@ -32,6 +32,7 @@ FIXTURE_DIR = {
     "res_ln_alias_45f7dfd4a983": "var_mean_45f7dfd4a983", "res_ln_sum2_49afc8635b79": "var_mean_49afc8635b79",
     "res_ln_stats_547bcc63004b": "var_mean_547bcc63004b", "cast_param_04d85912d998": "pointwise_04d85912d998",
     "cast_param_ccd411f2a45d": "pointwise_ccd411f2a45d", "relu_3abc926270f6": "pointwise_3abc926270f6",
+    "gelu_826ea0b5f6e4": "pointwise_826ea0b5f6e4", "silu_795cdbe23b17": "pointwise_795cdbe23b17",
 }
 # regions that draw random numbers: output index -> mask index it depends on element by element
 STOCHASTIC = {"dropout_rms_014afd4984e6": {"masks": (0, 3), "elementwise": {1: 0}},

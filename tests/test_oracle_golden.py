@@ -135,6 +135,7 @@ def golden_cases():
         "cast_param_04d85912d998": lambda inp: [eager.ParameterCast(torch.float32)(inp[0])],
         "cast_param_ccd411f2a45d": lambda inp: [eager.ParameterCast(torch.bfloat16)(inp[0])],
         "relu_3abc926270f6": lambda inp: [eager.Relu()(inp[0])],
+        "gelu_826ea0b5f6e4": lambda inp: [eager.GeluErf()(*inp)], "silu_795cdbe23b17": lambda inp: [eager.Silu()(inp[0])],
         "gelu_ln_stats_21faaccf749d": gelu_ln_stats, "headmerge_e87d6ebc9ded": headmerge,
         "qkv_views_d5a413a2c233": qkv_views_kvq,
         "dropout_ln_01fbd6c1b27f": dropout_ln,
