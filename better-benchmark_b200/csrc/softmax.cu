@@ -280,43 +280,33 @@ softmax_resident_kernel(const SoftmaxParams p) {
     const float2 mf = Pair<Tin>::widen(mx2);
     mx = greduce<FastMax, G>(fmaxf(mf.x, mf.y), red);
   } else {
-    // fp32 prologue on packed pairs: x * scale and + mask are one packed operation per two elements
-    // each; the row maximum takes one three-input max per pair and the clamp one NaN-keeping max
-    // per element (there is no packed max).
-    const f32x2 sc2 = splat2(p.scale);
-    const f32x2 ninf2 = splat2(-INFINITY);
 #pragma unroll
     for (int c = 0; c < CH; ++c) {
-      f32x2 f2[V / 2];
+      float f[V];
       if (EXACT || c * gs + lane < nv) {
-        Pairs<Tin>::unpack(raw[c], f2);
+        Elem<Tin>::unpack(raw[c], f);
         if (p.has_scale) {
 #pragma unroll
-          for (int i = 0; i < V / 2; ++i) f2[i] = mul2(f2[i], sc2);
+          for (int i = 0; i < V; ++i) f[i] = f[i] * p.scale;
         }
         if (m != nullptr) {
-          f32x2 m2[V / 2];
-          Pairs<Tin>::unpack(ld_keep(ml + (long long)c * gs * V), m2);
+          float mf[V];
+          Elem<Tin>::unpack(ld_keep(ml + (long long)c * gs * V), mf);
 #pragma unroll
-          for (int i = 0; i < V / 2; ++i) f2[i] = add2(f2[i], m2[i]);
+          for (int i = 0; i < V; ++i) f[i] = f[i] + mf[i];
         }
 #pragma unroll
-        for (int i = 0; i < V / 2; ++i) {
-          float lo, hi;
-          unpack2(f2[i], lo, hi);
-          asm("max.f32 %0, %1, %2, %3;" : "=f"(mx) : "f"(mx), "f"(lo), "f"(hi));
-          if (clamp_now) {  // a NaN logit stays NaN
-            asm("max.NaN.f32 %0, %1, %2;" : "=f"(lo) : "f"(lo), "f"(kFloor));
-            asm("max.NaN.f32 %0, %1, %2;" : "=f"(hi) : "f"(hi), "f"(kFloor));
-            f2[i] = pack2(lo, hi);
-          }
-        }
+        for (int i = 0; i < V; ++i) mx = fmaxf(mx, f[i]);
       } else {
 #pragma unroll
-        for (int i = 0; i < V / 2; ++i) f2[i] = clamp_now ? splat2(kFloor) : ninf2;
+        for (int i = 0; i < V; ++i) f[i] = -INFINITY;
+      }
+      if (clamp_now) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) f[i] = f[i] < kFloor ? kFloor : f[i];  // a NaN logit stays NaN
       }
 #pragma unroll
-      for (int i = 0; i < V / 2; ++i) v[c][i] = f2[i];
+      for (int i = 0; i < V / 2; ++i) v[c][i] = pack2(f[2 * i], f[2 * i + 1]);
     }
     mx = greduce<FastMax, G>(mx, red);
   }
