@@ -40,6 +40,10 @@ struct NormFwdParams {
   // receives that rounded sum, rows of n elements, contiguous.
   const void* res;
   void* sum_out;
+  // 1: the sum is rounded to x's dtype before it is normalised, as the eager graph materialises it;
+  // 0 (what the stubs use): it stays in fp32, as in Inductor's fused kernel - the form the
+  // reference's fp64-anchored gate accepts (the fp64 evaluation of the graph has no such rounding).
+  int res_round;
 };
 
 // Pointwise prologue of the LayerNorm regions that normalise an activation
@@ -93,14 +97,18 @@ norm_fwd_resident_kernel(const NormFwdParams p) {
     float f[V];
     if (c * gs + lane < nv) {
       Elem<Tin>::unpack(raw[c], f);
-      if constexpr (RES) {  // T(x + res): the graph materialises the sum in the tensor dtype
+      if constexpr (RES) {  // x + res in fp32; sum_out receives it rounded to the tensor dtype
         float r[V];
         Elem<Tin>::unpack(rraw[c], r);
 #pragma unroll
-        for (int i = 0; i < V; ++i) f[i] = round_through<Tin>(f[i] + r[i]);
+        for (int i = 0; i < V; ++i) f[i] = f[i] + r[i];
         if (p.sum_out && valid)
           st_stream(reinterpret_cast<Tin*>(p.sum_out) + row * (long long)p.n + (long long)(c * gs + lane) * V,
                     Elem<Tin>::pack(f));
+        if (p.res_round) {
+#pragma unroll
+          for (int i = 0; i < V; ++i) f[i] = round_through<Tin>(f[i]);
+        }
       }
     } else {
 #pragma unroll
@@ -510,12 +518,16 @@ __global__ void __launch_bounds__(1024) norm_fwd_streaming_kernel(const NormFwdP
   const Tin* res = p.res ? reinterpret_cast<const Tin*>(p.res) + row * p.x_row_stride : nullptr;
   auto value = [&](long long i) {
     float f = Elem<Tin>::to_f32(x[i]);
-    if (res) f = round_through<Tin>(f + Elem<Tin>::to_f32(res[i]));
+    if (res) {
+      f = f + Elem<Tin>::to_f32(res[i]);
+      if (p.res_round) f = round_through<Tin>(f);
+    }
     return p.prologue == 1 ? gelu_erf_rounded<Tin>(f) : f;
   };
   if (res && p.sum_out) {
     Tin* so = reinterpret_cast<Tin*>(p.sum_out) + row * (long long)p.n;
-    for (long long i = threadIdx.x; i < p.n; i += blockDim.x) so[i] = Elem<Tin>::from_f32(value(i));
+    for (long long i = threadIdx.x; i < p.n; i += blockDim.x)
+      so[i] = Elem<Tin>::from_f32(Elem<Tin>::to_f32(x[i]) + Elem<Tin>::to_f32(res[i]));
   }
   float s = 0.f;
   for (long long i = threadIdx.x; i < p.n; i += blockDim.x) {
@@ -633,6 +645,7 @@ extern "C" int b200_norm_fwd_residual(const void* x, const void* residual, void*
   p.w_dtype = w_dtype; p.eps = (float)eps; p.rms = (rms & 1) ? 1 : 0;
   p.prologue = (rms & 2) ? 1 : 0;  // bit 1 of the mode word: exact GELU of x, rounded to x's dtype, first
   p.res = residual; p.sum_out = sum_out;
+  p.res_round = (rms & 4) ? 1 : 0;  // bit 2 of the mode word: round the residual sum to x's dtype first
   p.inv_n = (float)(1.0 / (double)n);
   p.inv_denom = (float)(1.0 / ((double)n - correction));  // inf/NaN for n <= correction, as aten
 

@@ -33,18 +33,21 @@ struct PermuteParams {
 // decomposed aten graph: 2 ReLU (a NaN stays a NaN); 4 exact GELU, (x * 0.5) * (erf(x * 0.7071067811865476) + 1)
 // (repros/canonical/pointwise_826ea0b5f6e4/repro.py:27-31); 8 SiLU, x / (exp(-x) + 1)
 // (repros/canonical/pointwise_795cdbe23b17/repro.py:26-29).
-__device__ __forceinline__ float apply_activation(float f, int mode) {
-  if (mode & 2) f = f < 0.f ? 0.f : f;
-  if (mode & 4) f = (f * 0.5f) * (erff(f * 0.7071067811865476f) + 1.0f);
-  if (mode & 8) f = f / (expf(-f) + 1.0f);
+// One activation per launch; ACT is its bit (0: none), so that each instantiation carries only the
+// code it uses.
+template <int ACT>
+__device__ __forceinline__ float apply_activation(float f) {
+  if constexpr (ACT == 2) f = f < 0.f ? 0.f : f;
+  if constexpr (ACT == 4) f = (f * 0.5f) * (erff(f * 0.7071067811865476f) + 1.0f);
+  if constexpr (ACT == 8) f = f / (expf(-f) + 1.0f);
   return f;
 }
 
-template <typename Tin, typename Tout>
+template <typename Tin, typename Tout, int ACT = 0>
 __device__ __forceinline__ Tout convert_scaled(Tin v, float scale, int has_scale) {
   float f = Elem<Tin>::to_f32(v);
   if (has_scale & 1) f = f * scale;
-  f = apply_activation(f, has_scale);
+  f = apply_activation<ACT>(f);
   return Elem<Tout>::from_f32(f);
 }
 
@@ -262,9 +265,13 @@ __global__ void __launch_bounds__(256) transpose_small_kernel(const TransposePar
 }
 
 // Contiguous cast / scale / activation (has_scale: bit 0 multiply by scale; bits 1..3 ReLU, exact GELU, SiLU after it).
-template <typename Tin, typename Tout, bool VEC>
-__global__ void __launch_bounds__(256) cast_scale_kernel(const void* x, void* y, long long n, float scale,
-                                                         int has_scale) {
+// ACT: the activation bit of the mode word (0: none); the plain cast / scale instantiation carries none of
+// the activations' code (the erf and exp sequences cost registers and instruction-cache lines that a 5 us
+// parameter cast would pay for without using them).
+template <typename Tin, typename Tout, bool VEC, int ACT>
+__global__ void __launch_bounds__(256, ACT >= 4 ? 3 : 4) cast_scale_kernel(const void* x, void* y, long long n, float scale,
+                                                                            int mode_word) {
+  const int has_scale = mode_word & 1;
   constexpr int VIN = VEC ? Elem<Tin>::V : 1;
   const long long units = n / VIN;
   const Tin* src = reinterpret_cast<const Tin*>(x);
@@ -292,9 +299,23 @@ __global__ void __launch_bounds__(256) cast_scale_kernel(const void* x, void* y,
 #pragma unroll
             for (int i = 0; i < VIN; ++i) f[i] = f[i] * scale;
           }
-          if (has_scale & 14) {
+          if constexpr (ACT == 8 && sizeof(Tout) == 2) {
+            // SiLU for a 16-bit result: exp(-x) from the compensated pair exponential (the accuracy
+            // class of expf) and x * (1 / (e + 1)) with a correctly rounded reciprocal: 1.5 fp32 ulp,
+            // three orders of magnitude below half an ulp of the output, at a third of the
+            // instructions of expf and an IEEE division. The argument is clamped to the range in
+            // which the result does not depend on it any more (the exponential needs finite inputs).
 #pragma unroll
-            for (int i = 0; i < VIN; ++i) f[i] = apply_activation(f[i], has_scale);
+            for (int i = 0; i < VIN / 2; ++i) {
+              const float a = f[2 * i], b = f[2 * i + 1];
+              float ea, eb;
+              unpack2(exp_pair_compensated(pack2(fminf(fmaxf(-a, -87.f), 88.f), fminf(fmaxf(-b, -87.f), 88.f))), ea, eb);
+              f[2 * i] = a * __frcp_rn(ea + 1.0f);
+              f[2 * i + 1] = b * __frcp_rn(eb + 1.0f);
+            }
+          } else if constexpr (ACT != 0) {
+#pragma unroll
+            for (int i = 0; i < VIN; ++i) f[i] = apply_activation<ACT>(f[i]);
           }
           store_converted<Tout, VIN>(dst + u * VIN, f);
         }
@@ -303,12 +324,12 @@ __global__ void __launch_bounds__(256) cast_scale_kernel(const void* x, void* y,
   } else {
     for (long long u = (long long)blockIdx.x * blockDim.x + threadIdx.x; u < units;
          u += (long long)gridDim.x * blockDim.x)
-      dst[u] = convert_scaled<Tin, Tout>(src[u], scale, has_scale);
+      dst[u] = convert_scaled<Tin, Tout, ACT>(src[u], scale, has_scale);
   }
   if constexpr (VEC) {  // ragged tail
     const long long done = units * VIN;
     const long long t = done + (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (t < n) dst[t] = convert_scaled<Tin, Tout>(src[t], scale, has_scale);
+    if (t < n) dst[t] = convert_scaled<Tin, Tout, ACT>(src[t], scale, has_scale);
   }
 }
 
@@ -366,8 +387,19 @@ template <typename Tin, typename Tout>
 static int launch_cast(const void* x, void* y, long long n, float scale, int has_scale, bool vec, cudaStream_t st) {
   const long long units = vec ? n / Elem<Tin>::V : n;
   set_path_tag(vec ? "vector" : "element-wise");
-  if (vec) cast_scale_kernel<Tin, Tout, true><<<streaming_grid(units > 0 ? units : 1), 256, 0, st>>>(x, y, n, scale, has_scale);
-  else cast_scale_kernel<Tin, Tout, false><<<streaming_grid(units > 0 ? units : 1), 256, 0, st>>>(x, y, n, scale, has_scale);
+  const unsigned grid = streaming_grid(units > 0 ? units : 1);
+  auto go = [&](auto act_tag) {
+    constexpr int ACT = decltype(act_tag)::value;
+    if (vec) cast_scale_kernel<Tin, Tout, true, ACT><<<grid, 256, 0, st>>>(x, y, n, scale, has_scale);
+    else cast_scale_kernel<Tin, Tout, false, ACT><<<grid, 256, 0, st>>>(x, y, n, scale, has_scale);
+  };
+  switch (has_scale & 14) {
+    case 0: go(std::integral_constant<int, 0>{}); break;
+    case 2: go(std::integral_constant<int, 2>{}); break;
+    case 4: go(std::integral_constant<int, 4>{}); break;
+    case 8: go(std::integral_constant<int, 8>{}); break;
+    default: return fail(B200_ERR_INVALID, "b200_cast_scale: one activation at a time (mode %d)", has_scale);
+  }
   return launch_status("b200_cast_scale");
 }
 

@@ -103,10 +103,11 @@ int32_t b200_norm_fwd(const void* x, const void* weight, const void* bias, void*
                       int64_t y_row_stride, int32_t x_dtype, int32_t w_dtype, int32_t y_dtype,
                       double eps, double correction, int32_t rms, void* stream);
 
-/* b200_norm_fwd with a residual prologue: the rows that are normalised are T(x + residual), the sum
- * rounded to x's dtype as the graphs of the post-LayerNorm blocks materialise it
- * (var_mean_0ada225c0a04/repro.py:26-27). residual: x's dtype, x's row stride; sum_out (may be NULL):
- * receives the rounded sum, x's dtype, rows of n contiguous elements; y must have x's dtype.
+/* b200_norm_fwd with a residual prologue: the rows that are normalised are x + residual
+ * (var_mean_0ada225c0a04/repro.py:26-27). The sum stays in fp32, as in Inductor's fused kernel (the
+ * form the reference's fp64-anchored gate accepts); adding 4 to rms rounds it to x's dtype first, as
+ * the eager graph materialises it. residual: x's dtype, x's row stride; sum_out (may be NULL):
+ * receives the sum rounded to x's dtype, rows of n contiguous elements; y must have x's dtype.
  * residual = NULL is b200_norm_fwd. Replaces var_mean_0ada225c0a04/oracle.py, var_mean_f4578c128d74/oracle.py. */
 int32_t b200_norm_fwd_residual(const void* x, const void* residual, void* sum_out, const void* weight,
                                const void* bias, void* y, float* mean_out, float* rstd_out, float* var_out,
