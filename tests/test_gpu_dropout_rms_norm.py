@@ -228,7 +228,8 @@ def test_softmax_dropout(dtype, dims, permuted):
     want = eager.SoftmaxDropout(p, 29)(x.cpu(), bias.cpu(), seeds.cpu(), mask=keep.cpu())
     assert torch.equal(logits.cpu(), want[0]), "rounded logits"
     assert torch.equal(amax.cpu(), want[1]), "row maximum"
-    assert_close(total, want[2], "row sum of the exponentials")
+    # a sum of exponentials: summation order and expf differ from the CPU's in the last bits
+    assert torch.allclose(total.cpu(), want[2], rtol=2e-5, atol=1e-6), "row sum of the exponentials"
     assert_close(y, want[4], "dropped probabilities")
     again = kernels.softmax_dropout(x, bias, seeds, 29, p=p)
     assert all(torch.equal(u_, v_) for u_, v_ in zip((logits, amax, total, keep, y), again)), "bit-reproducible"

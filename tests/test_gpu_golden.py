@@ -39,7 +39,7 @@ STOCHASTIC = {"dropout_rms_014afd4984e6": {"masks": (0, 3), "elementwise": {1: 0
               "dropout_ln_01fbd6c1b27f": {"masks": (0,), "elementwise": {}},
               "dropout_add_4b076ed1ff41": {"masks": (0,), "elementwise": {1: 0}},
               # logits, row maximum and row sum do not depend on the draw at all
-              "softmax_dropout_089fdab8f22b": {"masks": (3,), "elementwise": {4: 3}, "deterministic": (0, 1, 2)}}
+              "softmax_dropout_089fdab8f22b": {"masks": (3,), "elementwise": {4: 3}, "deterministic": (0, 1), "sums": (2,)}}
 
 
 def kernel_cases():
@@ -87,10 +87,12 @@ def test_kernels_reproduce_reference_outputs(name):
             assert g.shape == w.shape and g.dtype == w.dtype, f"{name} output {i}"
         for i in spec.get("deterministic", ()):
             assert_close(got[i], want[i], f"{name} output {i}")
+        for i in spec.get("sums", ()):   # a sum of exponentials: summation order and expf differ from the CPU's in the last bits
+            assert torch.allclose(got[i].cpu(), want[i], rtol=2e-5, atol=1e-6), f"{name} output {i}"
         for m in spec["masks"]:
             assert abs(got[m].float().mean().item() - want[m].float().mean().item()) < 0.02
         for out_i, mask_i in spec["elementwise"].items():
-            agree = got[mask_i].cpu() == want[mask_i]
+            agree = (got[mask_i].cpu() == want[mask_i]).reshape(want[out_i].shape)   # same elements, the output's shape
             assert agree.float().mean().item() > 0.7
             assert torch.equal(got[out_i].cpu()[agree], want[out_i][agree]), f"{name} output {out_i}"
         return
