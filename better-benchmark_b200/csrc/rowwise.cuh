@@ -413,4 +413,36 @@ __device__ __forceinline__ float greduce(float v, float* scratch) {
   }
 }
 
+// Two sums over the group at once: the shuffle chains of the two values interleave, so the pair
+// costs about one reduction's latency. `scratch` holds >= 64 floats.
+template <int G>
+__device__ __forceinline__ void greduce_sum2(float& a, float& b, float* scratch) {
+  if constexpr (G == 0) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      a += __shfl_xor_sync(0xffffffffu, a, o);
+      b += __shfl_xor_sync(0xffffffffu, b, o);
+    }
+    if (lane == 0) {
+      scratch[warp] = a;
+      scratch[32 + warp] = b;
+    }
+    __syncthreads();
+    a = 0.f;
+    b = 0.f;
+    for (int w = 0; w < nwarps; ++w) {
+      a += scratch[w];
+      b += scratch[32 + w];
+    }
+    __syncthreads();
+  } else {
+#pragma unroll
+    for (int o = G / 2; o > 0; o >>= 1) {
+      a += __shfl_xor_sync(0xffffffffu, a, o);
+      b += __shfl_xor_sync(0xffffffffu, b, o);
+    }
+  }
+}
+
 }  // namespace b200

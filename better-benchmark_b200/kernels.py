@@ -214,12 +214,15 @@ def _rows_2d(t: torch.Tensor, what: str):
     return rows, n, (s[0] if rows > 1 else n)
 
 
+_SUM_FORMS = {False: 0, True: 4, "both": 8}   # bits 2 and 3 of b200_norm_fwd_residual's mode word
+
+
 def norm_fwd(x: torch.Tensor, weight: torch.Tensor | None, bias: torch.Tensor | None, *,
              eps: float, rms: bool = False, out_dtype: torch.dtype | None = None,
              want_y: bool = True, want_mean: bool = False, want_rstd: bool = False,
              want_var: bool = False, correction: float = 0.0, keepdim: bool = True,
              prologue: str | None = None, residual: torch.Tensor | None = None, want_sum: bool = False,
-             round_sum: bool = False):
+             round_sum: bool | str = False):
     """LayerNorm (rms=False) or RMSNorm (rms=True) forward over the last dimension.
 
     ``prologue="gelu_erf"`` normalises ``gelu(x)`` (exact, erf form) rounded to x's dtype instead
@@ -227,7 +230,11 @@ def norm_fwd(x: torch.Tensor, weight: torch.Tensor | None, bias: torch.Tensor | 
     ``residual`` (x's shape, dtype and strides) normalises ``x + residual``; ``want_sum`` returns the
     sum, rounded to x's dtype, as a fifth value. The sum that is normalised stays in fp32 (Inductor's
     fused form, which the reference's fp64-anchored gate accepts) unless ``round_sum`` asks for the
-    eager graph's materialised 16-bit intermediate.
+    eager graph's materialised 16-bit intermediate (``True``) or for both (``"both"``, LayerNorm
+    only): each element then takes the fp32 form where that form's output exceeds 3 in magnitude and
+    the rounded form elsewhere, which is what the reference's own oracles for these regions return
+    (repros/canonical/var_mean_45f7dfd4a983/oracle.py:96-107) - small outputs equal the eager
+    module's, large ones carry no intermediate rounding.
 
     Returns (y, mean, rstd, var) with None for the outputs not requested. Statistics are fp32 with
     x's outer shape (plus a trailing 1 when ``keepdim``).
@@ -272,7 +279,7 @@ def norm_fwd(x: torch.Tensor, weight: torch.Tensor | None, bias: torch.Tensor | 
     check(lib.b200_norm_fwd_residual(_ptr(x), _ptr(residual), _ptr(total), _ptr(weight), _ptr(bias), _ptr(y),
                                      _ptr(mean), _ptr(rstd), _ptr(var), rows, n, x_stride, y_stride, _code(x),
                                      w_code, _DTYPE_CODE[out_dtype], float(eps), float(correction),
-                                     (1 if rms else 0) | _NORM_PROLOGUES[prologue] | (4 if round_sum else 0), _stream()),
+                                     (1 if rms else 0) | _NORM_PROLOGUES[prologue] | _SUM_FORMS[round_sum], _stream()),
           "b200_norm_fwd_residual")
     return (y, mean, rstd, var, total) if want_sum else (y, mean, rstd, var)
 

@@ -106,7 +106,11 @@ int32_t b200_norm_fwd(const void* x, const void* weight, const void* bias, void*
 /* b200_norm_fwd with a residual prologue: the rows that are normalised are x + residual
  * (var_mean_0ada225c0a04/repro.py:26-27). The sum stays in fp32, as in Inductor's fused kernel (the
  * form the reference's fp64-anchored gate accepts); adding 4 to rms rounds it to x's dtype first, as
- * the eager graph materialises it. residual: x's dtype, x's row stride; sum_out (may be NULL):
+ * the eager graph materialises it; adding 8 instead (plain LayerNorm only) normalises both forms,
+ * each with its own statistics, and gives every element the fp32 form where that form's rounded
+ * output exceeds 3 in magnitude and the rounded form elsewhere - what the reference's oracles for
+ * these regions return (var_mean_45f7dfd4a983/oracle.py:96-107). The statistics that are returned
+ * are those of the fp32 sum in every mode but 4. residual: x's dtype, x's row stride; sum_out (may be NULL):
  * receives the sum rounded to x's dtype, rows of n contiguous elements; y must have x's dtype.
  * residual = NULL is b200_norm_fwd. Replaces var_mean_0ada225c0a04/oracle.py, var_mean_f4578c128d74/oracle.py. */
 int32_t b200_norm_fwd_residual(const void* x, const void* residual, void* sum_out, const void* weight,

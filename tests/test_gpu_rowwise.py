@@ -327,6 +327,32 @@ def test_residual_prologue_layer_norm_matches_eager(rows, n, dtype):
     assert (mean3.double().cpu().view(-1) - mean64.view(-1)).abs().max().item() <= 1e-5 * max(1.0, mean64.abs().max().item())
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32], ids=["bf16", "f16", "f32"])
+@pytest.mark.parametrize("rows,n", [(300, 768), (64, 128), (96, 4096), (33, 32768), (5, 1001), (7, 10000)])
+def test_residual_layer_norm_both_forms_select_per_element(rows, n, dtype):
+    """round_sum="both": every element is the fp32-sum form where that form's output exceeds 3 in
+    magnitude and the rounded-sum form elsewhere (the rule of the reference's oracles for these
+    regions, repros/canonical/var_mean_45f7dfd4a983/oracle.py:96-107); the statistics and the sum
+    that are returned are those of the fp32 form. Resident and element-wise kernels."""
+    k = _kernels()
+    x = _randn((rows, n), dtype, seed=n + 7, scale=2.0).cuda()
+    r = _randn((rows, n), dtype, seed=n + 8, scale=1.0).cuda()
+    g = torch.Generator().manual_seed(2)
+    w = (2.0 * torch.randn(n, generator=g)).to(dtype).cuda()     # wide weights: many outputs beyond 3
+    b = torch.randn(n, generator=g).to(dtype).cuda()
+    kw = dict(eps=1e-12, residual=r, want_sum=True, want_mean=True, want_rstd=True)
+    y32, mean32, rstd32, _, total32 = k.norm_fwd(x, w, b, **kw)
+    y16 = k.norm_fwd(x, w, b, round_sum=True, **kw)[0]
+    y, mean, rstd, _, total = k.norm_fwd(x, w, b, round_sum="both", **kw)
+    assert b"residual add" in k.load().b200_last_kernel()
+    big = y32.float().abs() > 3.0
+    assert 0.02 < big.float().mean().item() < 0.98, "the case must exercise both branches"
+    assert torch.equal(y, torch.where(big, y32, y16))
+    assert torch.equal(mean, mean32) and torch.equal(rstd, rstd32) and torch.equal(total, total32)
+    if dtype == torch.float32:
+        assert torch.equal(y, y32) and torch.equal(y, y16), "fp32 tensors: one form only"
+
+
 def test_residual_prologue_rejections():
     from better_benchmark_b200 import kernels as kk
     k = _kernels()
@@ -337,3 +363,6 @@ def test_residual_prologue_rejections():
         k.norm_fwd(x, None, None, eps=1e-5, residual=torch.zeros(4, 64, device="cuda", dtype=torch.bfloat16))
     with pytest.raises(kk.UnsupportedLayout):
         k.norm_fwd(x, None, None, eps=1e-5, residual=x.clone(), out_dtype=torch.float32)        # y in another dtype
+    from better_benchmark_b200 import native
+    with pytest.raises(native.KernelArgumentError):
+        k.norm_fwd(x, None, None, eps=1e-5, residual=x.clone(), rms=True, round_sum="both")     # LayerNorm only
