@@ -696,6 +696,10 @@ static int launch_norm_fwd(const NormFwdParams& p, bool vector_ok, cudaStream_t 
     norm_fwd_resident_kernel<Tin, Tout, CC, GG><<<grid, g.threads, 0, st>>>(p);                      \
   } while (0)
     if (!g.block) {
+      if (p.res) {  // tuning knob: CTA size of the residual kernels (64, 128 or 256 threads)
+        static const int t_env = [] { const char* e = getenv("B200_NF_RES_THREADS"); return e ? atoi(e) : 0; }();
+        if (t_env == 64 || t_env == 128 || t_env == 256) g.threads = t_env;
+      }
       const int rows_per_cta = g.threads / g.g;
       const unsigned grid = (unsigned)((p.rows + rows_per_cta - 1) / rows_per_cta);
       if (g.g == 8) {
