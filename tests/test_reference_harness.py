@@ -74,6 +74,204 @@ def test_every_stub_registers_each_shape_point_under_the_reference_harness(tmp_p
     assert total >= 226
 
 
+_MIRROR_SCRIPT = r"""
+import contextlib, io, json, random, sys
+from pathlib import Path
+sys.path[:0] = [sys.argv[1], sys.argv[2] + "/scripts", sys.argv[2]]
+from better_benchmark_b200 import reference_arm as arm, harness as mirror
+oh, rh = arm._import_reference(Path(sys.argv[2]))
+import torch
+rnd = random.Random(5)
+g = torch.Generator().manual_seed(5)
+FLOATS = [torch.float32, torch.bfloat16, torch.float16]
+compare_cases = gate_cases = 0
+verdicts = {"compare": [0, 0], "gate": [0, 0]}
+bad = []
+
+def quiet(f, *a, **k):
+    with contextlib.redirect_stdout(io.StringIO()):
+        return f(*a, **k)
+
+for trial in range(300):
+    n_out = rnd.randint(1, 3)
+    eager, oracle = [], []
+    for _ in range(n_out):
+        shape = [rnd.randint(1, 9), rnd.randint(1, 33)]
+        kind = rnd.choice(["float", "float", "float", "int", "bool"])
+        if kind == "float":
+            dt = rnd.choice(FLOATS)
+            e = (torch.randn(shape, generator=g) * rnd.choice([0.01, 1.0, 30.0])).to(dt)
+            o = e.clone()
+            mode = rnd.choice(["same", "rel", "abs", "nan_same", "nan_diff", "dtype"])
+            if mode == "rel":
+                o = (e.float() * (1 + rnd.choice([1e-3, 5e-3, 2e-2, 1e-1]))).to(dt)
+            elif mode == "abs":
+                o = (e.float() + rnd.choice([1e-3, 5e-3, 2e-2, 1e-1])).to(dt)
+            elif mode == "nan_same":
+                e[0, 0] = float("nan"); o = e.clone()
+            elif mode == "nan_diff":
+                o = e.clone(); o[0, 0] = float("nan")
+            elif mode == "dtype":
+                o = e.float()
+        elif kind == "int":
+            e = torch.randint(-5, 5, shape, generator=g)
+            o = e.clone()
+            if rnd.random() < 0.3: o[0, 0] += 1
+        else:
+            e = torch.rand(shape, generator=g) > 0.5
+            o = e.clone()
+            if rnd.random() < 0.3: o[0, 0] = ~o[0, 0]
+        if rnd.random() < 0.05:
+            o = o[:, : max(1, o.shape[1] - 1)]          # shape mismatch
+        eager.append(e); oracle.append(o)
+    if rnd.random() < 0.05:
+        oracle = oracle[:-1] if len(oracle) > 1 else oracle + [oracle[0]]   # count mismatch
+    stochastic = {0} if rnd.random() < 0.15 else set()
+    a = quiet(oh._compare_oracle_outputs, eager, oracle, stochastic, atol=1e-2, rtol=1e-2)
+    b = quiet(mirror._compare_oracle_outputs, eager, oracle, stochastic, atol=1e-2, rtol=1e-2)
+    compare_cases += 1
+    verdicts["compare"][int(bool(a))] += 1
+    if bool(a) != bool(b):
+        bad.append(("compare", trial, bool(a), bool(b)))
+
+for trial in range(300):
+    n_out = rnd.randint(1, 3)
+    ref, comp, orc = [], [], []
+    for _ in range(n_out):
+        shape = [rnd.randint(1, 9), rnd.randint(1, 33)]
+        if rnd.random() < 0.15:
+            t = torch.randint(0, 9, shape, generator=g)
+            ref.append(t); comp.append(t.clone()); orc.append(t.clone()); continue
+        base = torch.randn(shape, generator=g, dtype=torch.float64) * rnd.choice([1e-3, 1.0, 100.0])
+        dt = rnd.choice(FLOATS)
+        ec, eo = rnd.choice([0.0, 1e-7, 1e-4, 1e-2]), rnd.choice([0.0, 1e-7, 2e-7, 1e-4, 2.9e-4, 3.1e-4, 1e-1])
+        c = (base * (1 + ec)).to(dt); o = (base * (1 + eo)).to(dt)
+        if rnd.random() < 0.1: o[0, 0] = float("nan")
+        if rnd.random() < 0.05: c[0, 0] = float("inf")
+        ref.append(base); comp.append(c); orc.append(o)
+    stochastic = {0} if rnd.random() < 0.15 else set()
+    a = oh._anchored_numerics_gate(orc, comp, ref, stochastic)
+    b = mirror._anchored_numerics_gate(orc, comp, ref, stochastic)
+    gate_cases += 1
+    verdicts["gate"][int(bool(a["pass"]))] += 1
+    same = a["pass"] == b["pass"] and a["worst_output_idx"] == b["worst_output_idx"] and len(a["per_output"]) == len(b["per_output"])
+    for x, y in zip(a["per_output"], b["per_output"]):
+        for key in ("skip", "pass"):
+            same = same and x.get(key) == y.get(key)
+        for key in ("err_oracle", "err_compiled", "threshold"):
+            if key in x or key in y:
+                u, v = x.get(key), y.get(key)
+                same = same and u is not None and v is not None and (u == v or (u != u and v != v) or abs(u - v) <= 1e-12 * max(abs(u), abs(v), 1e-300))
+    if not same:
+        bad.append(("gate", trial, a, b))
+print("RESULT " + json.dumps({"compare_cases": compare_cases, "gate_cases": gate_cases, "verdicts": verdicts,
+                              "mismatches": [str(m)[:600] for m in bad[:5]], "n_mismatches": len(bad)}))
+"""
+
+
+def test_mirror_comparison_and_gate_agree_with_the_reference_harness(tmp_path):
+    """The package's mirror of `_compare_oracle_outputs` (oracle_harness.py:865-923) and
+    `_anchored_numerics_gate` (:1479-1548) against the reference's own functions on 600 seeded
+    random cases: matching and perturbed floats of three dtypes, NaNs in the same and in different
+    places, dtype, shape and count mismatches, integer and boolean outputs, stochastic indices."""
+    import json
+
+    out = _run(_MIRROR_SCRIPT, str(tmp_path))
+    res = json.loads(next(l for l in out.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    assert res["compare_cases"] == 300 and res["gate_cases"] == 300
+    for kind in ("compare", "gate"):   # the cases must exercise both verdicts
+        assert min(res["verdicts"][kind]) >= 30, res["verdicts"]
+    assert res["n_mismatches"] == 0, res["mismatches"]
+
+
+_INPUTS_SCRIPT = r"""
+import json, sys
+from pathlib import Path
+sys.path[:0] = [sys.argv[1], sys.argv[2] + "/scripts", sys.argv[2]]
+from better_benchmark_b200 import reference_arm as arm, inputs as mirror, byte_model
+oh, rh = arm._import_reference(Path(sys.argv[2]))
+import byte_accounting
+import torch
+LIMIT = 48 << 20     # bytes of tensor inputs per point: generation runs on the CPU here
+dirs = sorted(p for p in (Path(sys.argv[2]) / "repros" / "canonical").iterdir() if (p / "shapes.json").is_file())
+points = compared = bytes_compared = 0
+bad = []
+
+def total_bytes(cfg):
+    n = 0
+    for spec in cfg["inputs"]:
+        if isinstance(spec, dict) and spec.get("kind", "tensor") == "tensor":
+            size = 1
+            for d, st in zip(spec["shape"], spec.get("stride") or mirror.contiguous_stride(spec["shape"])):
+                size += (d - 1) * st if d > 0 else 0
+            n += size * 4
+    return n
+
+def on_cpu(cfg):
+    for spec in cfg["inputs"]:
+        if isinstance(spec, dict) and spec.get("kind", "tensor") == "tensor":
+            spec["device"] = "cpu"
+    return cfg
+
+def same(a, b):
+    if isinstance(a, torch.Tensor) or isinstance(b, torch.Tensor):
+        return (isinstance(a, torch.Tensor) and isinstance(b, torch.Tensor) and a.dtype == b.dtype and a.shape == b.shape
+                and a.stride() == b.stride() and a.storage_offset() == b.storage_offset()
+                and torch.equal(torch.nan_to_num(a.float()), torch.nan_to_num(b.float())))
+    return type(a) == type(b) and a == b
+
+for d in dirs:
+    ref_cfgs = rh.load_shape_configs(str(d / "repro.py"))
+    my_cfgs = mirror.load_shape_configs(d / "repro.py")
+    if list(ref_cfgs) != list(my_cfgs):
+        bad.append((d.name, "labels differ")); continue
+    instance = None
+    for label in sorted(ref_cfgs, key=lambda k: total_bytes(ref_cfgs[k]))[:4]:   # the smallest points of the directory
+        points += 1
+        if total_bytes(ref_cfgs[label]) > LIMIT:
+            continue
+        oh._seed_input_generation(1)
+        a = rh.make_inputs_from_config(on_cpu(ref_cfgs[label]))
+        oh._seed_input_generation(1)
+        b = mirror.make_inputs_from_config(on_cpu(my_cfgs[label]))
+        compared += 1
+        if len(a) != len(b) or not all(same(x, y) for x, y in zip(a, b)):
+            bad.append((d.name, label, "inputs differ")); continue
+        # alias groups: inputs that share storage in one list must share it in the other
+        pa = [x.untyped_storage().data_ptr() if isinstance(x, torch.Tensor) else None for x in a]
+        pb = [x.untyped_storage().data_ptr() if isinstance(x, torch.Tensor) else None for x in b]
+        if [pa.index(v) for v in pa] != [pb.index(v) for v in pb]:
+            bad.append((d.name, label, "aliasing differs")); continue
+        if bytes_compared < 40:          # the byte model on the same inputs (an eager CPU run under dispatch)
+            try:
+                if instance is None:
+                    instance = oh.get_repro_instance(d)
+                want = int(byte_accounting.count_bytes_effective(instance, [x.clone() if isinstance(x, torch.Tensor) else x for x in a]))
+                got = int(byte_model.count_bytes_effective(instance, [x.clone() if isinstance(x, torch.Tensor) else x for x in b]))
+            except Exception as e:   # a graph that does not run on the CPU (device-specific ops): skipped
+                continue
+            bytes_compared += 1
+            if want != got:
+                bad.append((d.name, label, f"bytes {want} != {got}"))
+print("RESULT " + json.dumps({"dirs": len(dirs), "points": points, "compared": compared, "bytes_compared": bytes_compared,
+                              "n_bad": len(bad), "bad": [str(x) for x in bad[:8]]}))
+"""
+
+
+def test_mirror_shape_decoding_inputs_and_byte_model_agree_with_the_reference(tmp_path):
+    """`inputs.load_shape_configs` / `make_inputs_from_config` against `repro_harness.py:56-157`,
+    `:430-569` and `byte_model.count_bytes_effective` against `byte_accounting.py:54-66` on the staged
+    directories: same labels in the same order; with the same seed the same values, dtypes, strides,
+    storage offsets and alias groups (the four smallest points per directory, inputs up to 48 MB);
+    the same effective byte count on up to 40 of them."""
+    import json
+
+    out = _run(_INPUTS_SCRIPT, str(tmp_path), timeout=1500)
+    res = json.loads(next(l for l in out.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    assert res["dirs"] >= 19 and res["compared"] >= 60 and res["bytes_compared"] >= 20, res
+    assert res["n_bad"] == 0, res["bad"]
+
+
 _CHECK_SCRIPT = r"""
 import json, sys
 from pathlib import Path
