@@ -272,6 +272,108 @@ def test_mirror_shape_decoding_inputs_and_byte_model_agree_with_the_reference(tm
     assert res["n_bad"] == 0, res["bad"]
 
 
+_SWEEP_SCRIPT = r"""
+import json, random, sys
+from pathlib import Path
+sys.path[:0] = [sys.argv[1], sys.argv[2] + "/scripts", sys.argv[2]]
+from better_benchmark_b200 import reference_arm as arm, sweep as mirror
+oh, rh = arm._import_reference(Path(sys.argv[2]))
+import bench_parallel as bp
+rnd = random.Random(11)
+out_dir = Path(sys.argv[3])
+bad = []
+
+# task keys and their expansion over the staged directories (the mirror orders directories with the
+# most points first; the set of keys is what has to agree)
+dirs = sorted(p for p in (Path(sys.argv[2]) / "repros" / "canonical").iterdir() if (p / "repro.py").is_file())
+ref_tasks = bp._expand_oracle_shape_tasks(dirs)
+my_tasks = mirror.expand_shape_tasks(dirs)
+if sorted(ref_tasks) != sorted(my_tasks):
+    bad.append("task keys differ")
+if any(bp._oracle_dir_name(t) != mirror.oracle_dir_name(t) for t in ref_tasks):
+    bad.append("directory names of task keys differ")
+
+STATUSES = ["GOOD", "AT_FLOOR", "BAD_ORACLE"] + sorted(oh._INVALID_STATUSES)
+REF_POINT = ("oracle_us", "compile_us", "ratio", "status")
+
+def point():
+    status = rnd.choice(STATUSES + ["GOOD", "GOOD", "AT_FLOOR"])
+    us = rnd.choice([None, round(rnd.uniform(4, 900), 2), round(rnd.uniform(4, 900), 2)])
+    p = {"status": status, "oracle_us": us, "compile_us": rnd.choice([None, round(rnd.uniform(4, 900), 2)]),
+         "ratio": rnd.choice([None, round(rnd.uniform(0.3, 3), 3)])}
+    if rnd.random() < 0.7:
+        p["dispatch"] = {"fallback": rnd.random() < 0.2, "matched": "hardware+shape"}
+    if rnd.random() < 0.5:
+        p.update(region_bytes=rnd.randint(1, 1 << 30), oracle_gbps=rnd.uniform(1, 6000), sol_frac=rnd.random())
+    return p
+
+def subset_equal(ref, mine, where):
+    # everything the reference writes must be in the mirror's output with the same value; the mirror
+    # may add fields (its GB/s columns)
+    if isinstance(ref, dict):
+        if not isinstance(mine, dict):
+            bad.append(f"{where}: not a dict"); return
+        for k, v in ref.items():
+            if k not in mine:
+                bad.append(f"{where}: key {k!r} missing")
+            else:
+                subset_equal(v, mine[k], f"{where}.{k}")
+        if where.count(".") == 0 and set(mine) - set(ref):
+            bad.append(f"{where}: extra top-level keys {sorted(set(mine) - set(ref))}")
+    elif ref != mine:
+        bad.append(f"{where}: {ref!r} != {mine!r}")
+
+trials = 0
+for trial in range(60):
+    all_results, failures = {}, {}
+    for d in range(rnd.randint(1, 8)):
+        dname = f"/x/canonical/dir_{trial}_{d:02d}abcdef"
+        hashes = [f"{rnd.getrandbits(32):08x}" for _ in range(rnd.randint(0, 5))]
+        sharded = rnd.random() < 0.7
+        whole = {}
+        for h in hashes:
+            labels = [f"model{m}_{h}" for m in range(rnd.choice([1, 1, 2]))]   # two labels can share a hash
+            for label in labels:
+                if rnd.random() < 0.15:
+                    failures[mirror.make_task_key(dname, label)] = {"error": f"RuntimeError: boom {label}", "gpu": "0"}
+                    continue
+                if sharded:
+                    all_results[bp._make_shape_task_key(dname, label)] = {label: point()}
+                else:
+                    whole[label] = point()
+        if not sharded:
+            all_results[dname] = whole
+        if rnd.random() < 0.1:
+            all_results[mirror.make_task_key(dname, "__default__")] = {"default": point()}
+    a = bp._aggregate_oracle_timings(all_results)
+    b = mirror.aggregate_oracle_timings(all_results)
+    subset_equal(a, b, f"aggregate[{trial}]")
+    wa = bp._write_oracle_timings_output(out_dir / f"ref_{trial}.json", all_results, failures or None)
+    wb = mirror.write_oracle_timings(out_dir / f"mine_{trial}.json", all_results, failures or None)
+    subset_equal(wa, wb, f"write[{trial}]")
+    subset_equal(json.loads((out_dir / f"ref_{trial}.json").read_text()), json.loads((out_dir / f"mine_{trial}.json").read_text()),
+                 f"file[{trial}]")
+    trials += 1
+print("RESULT " + json.dumps({"tasks": len(ref_tasks), "trials": trials, "n_bad": len(bad), "bad": bad[:8]}))
+"""
+
+
+def test_mirror_sweep_tasks_and_timings_file_agree_with_the_reference(tmp_path):
+    """`sweep.expand_shape_tasks`, `aggregate_oracle_timings` and `write_oracle_timings` against
+    `scripts/bench_parallel.py:145-168`, `:1263-1384` and `:1407-1453` of the staged reference: the
+    same task keys for the staged directories, and on 60 seeded random result sets (sharded and whole
+    directories, shared shape hashes, invalid statuses, missing times, failed tasks) every field the
+    reference writes into the timings file with the same value; the mirror only adds fields."""
+    import json
+
+    if not (REF / "scripts" / "bench_parallel.py").is_file():
+        pytest.skip("the staged copy predates the sweep script: stage again")
+    out = _run(_SWEEP_SCRIPT, str(tmp_path))
+    res = json.loads(next(l for l in out.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    assert res["tasks"] >= 226 and res["trials"] == 60
+    assert res["n_bad"] == 0, res["bad"]
+
+
 _CHECK_SCRIPT = r"""
 import json, sys
 from pathlib import Path
