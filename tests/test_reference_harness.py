@@ -374,6 +374,78 @@ def test_mirror_sweep_tasks_and_timings_file_agree_with_the_reference(tmp_path):
     assert res["n_bad"] == 0, res["bad"]
 
 
+_LOCK_SCRIPT = r"""
+import json, os, subprocess, sys, time
+from pathlib import Path
+sys.path[:0] = [sys.argv[1], sys.argv[2] + "/scripts", sys.argv[2]]
+lock_dir = sys.argv[3]
+os.environ["COMPILE_UTILS_GPU_LOCK_DIR"] = lock_dir
+os.environ["CUDA_VISIBLE_DEVICES"] = "3"
+for k in ("INDUCTOR_GPU_BENCH_LOCK_DIR", "TORCHINDUCTOR_GPU_BENCH_LOCK_DIR"):
+    os.environ.pop(k, None)
+
+HOLD_REFERENCE = (
+    "import sys, time; sys.path[:0] = [%r + '/scripts', %r]\n"
+    "import oracle_harness as oh\n"
+    "with oh._gpu_exclusive_lock('holder'):\n"
+    "    print('HELD', flush=True); time.sleep(float(sys.argv[1]))\n"
+    "print('RELEASED', flush=True)\n" % (sys.argv[2], sys.argv[2]))
+HOLD_MIRROR = (
+    "import sys, time; sys.path[:0] = [%r]\n"
+    "from better_benchmark_b200 import gpu_lock\n"
+    "with gpu_lock.gpu_exclusive_lock('holder'):\n"
+    "    print('HELD', flush=True); time.sleep(float(sys.argv[1]))\n"
+    "print('RELEASED', flush=True)\n" % (sys.argv[1],))
+
+def holder(code, seconds):
+    p = subprocess.Popen([sys.executable, "-c", code, str(seconds)], stdout=subprocess.PIPE, text=True, env=os.environ.copy())
+    assert p.stdout.readline().strip() == "HELD"
+    return p
+
+out = {}
+# 1. the reference holds: the mirror must wait (time out while held, get through after the release)
+from better_benchmark_b200 import gpu_lock
+import oracle_harness as oh          # imported before any holder starts: the waits below time the locks only
+p = holder(HOLD_REFERENCE, 2.0)
+try:
+    with gpu_lock.gpu_exclusive_lock("waiter", timeout_s=0.4):
+        out["mirror_entered_while_reference_held"] = True
+except TimeoutError:
+    out["mirror_entered_while_reference_held"] = False
+meta = gpu_lock.read_lock_metadata(os.path.join(lock_dir, "gpu_3.lock"))
+out["mirror_reads_reference_metadata"] = {k: meta.get(k) for k in ("label", "mode", "gpu")}
+p.wait(timeout=20)
+t0 = time.time()
+with gpu_lock.gpu_exclusive_lock("waiter", timeout_s=5):
+    out["mirror_entered_after_release"] = True
+# 2. the mirror holds: the reference's lock (which has no timeout) must block until the release
+p = holder(HOLD_MIRROR, 1.5)
+t0 = time.time()
+with oh._gpu_exclusive_lock("waiter"):
+    out["reference_waited_s"] = round(time.time() - t0, 2)
+p.wait(timeout=20)
+out["files"] = sorted(os.listdir(lock_dir))
+print("RESULT " + json.dumps(out))
+"""
+
+
+def test_mirror_gpu_lock_and_the_reference_lock_exclude_each_other(tmp_path):
+    """A sweep of this backend and a sweep of the reference on one box must not time at once: the
+    mirror's lock (`gpu_lock.py`) and `oracle_harness._gpu_exclusive_lock` (:1614-1692) use the same
+    gate and lock files under the same directory rule and the same flock protocol. Checked with
+    holder processes on both sides."""
+    import json
+
+    out = _run(_LOCK_SCRIPT, str(tmp_path / "locks"), timeout=120)
+    res = json.loads(next(l for l in out.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    assert res["mirror_entered_while_reference_held"] is False
+    assert res["mirror_entered_after_release"] is True
+    assert res["mirror_reads_reference_metadata"]["label"] == "holder"
+    assert res["mirror_reads_reference_metadata"]["mode"] == "exclusive"
+    assert res["reference_waited_s"] >= 1.0, res          # it blocked for most of the holder's 1.5 s
+    assert res["files"] == ["gpu_3.gate", "gpu_3.lock"]
+
+
 _CHECK_SCRIPT = r"""
 import json, sys
 from pathlib import Path
