@@ -164,22 +164,60 @@ for trial in range(300):
                 same = same and u is not None and v is not None and (u == v or (u != u and v != v) or abs(u - v) <= 1e-12 * max(abs(u), abs(v), 1e-300))
     if not same:
         bad.append(("gate", trial, a, b))
-print("RESULT " + json.dumps({"compare_cases": compare_cases, "gate_cases": gate_cases, "verdicts": verdicts,
+# the reviewed opt-out: which annotations load, and which failing gates it may accept
+optout_cases = 0
+verdicts["optout"] = [0, 0]
+tmp = Path(sys.argv[3])
+METAS = [None, "not json", {}, {"numerics_optout": None}, {"numerics_optout": {"verified": True}},
+         {"numerics_optout": {"verified": True, "reason": "  "}}, {"numerics_optout": {"verified": "yes", "reason": "r"}},
+         {"numerics_optout": {"verified": True, "reason": "reviewed: rounding of the intermediate"}},
+         {"numerics_optout": {"verified": False, "reason": "r"}}, ["list"]]
+for i, meta in enumerate(METAS):
+    d = tmp / f"meta_{i}"
+    d.mkdir()
+    if meta is not None:
+        (d / "meta.json").write_text(meta if isinstance(meta, str) else json.dumps(meta))
+    with contextlib.redirect_stderr(io.StringIO()):
+        a, b = oh.load_numerics_optout(d), mirror.load_numerics_optout(d)
+    if a != b:
+        bad.append(("load_optout", i, a, b))
+opt = {"verified": True, "reason": "reviewed"}
+for trial in range(300):
+    entries = []
+    for idx in range(rnd.randint(0, 4)):
+        e = {"idx": idx, "pass": rnd.choice([True, False, False])}
+        if rnd.random() < 0.1:
+            e["skip"] = "non_float"; e.pop("pass")
+        else:
+            e["err_oracle"] = rnd.choice([None, float("nan"), float("inf"), 10 ** rnd.uniform(-9, 3)])
+            e["ref_absmax"] = rnd.choice([0.0, None, 10 ** rnd.uniform(-6, 4)])
+        entries.append(e)
+    result = rnd.choice([None, {"pass": False, "per_output": entries}, {"pass": False, "per_output": entries}])
+    use = rnd.choice([opt, opt, None, {}])
+    a, b = oh.numerics_optout_applies(result, use), mirror.numerics_optout_applies(result, use)
+    optout_cases += 1
+    verdicts["optout"][int(bool(a["accept"]))] += 1
+    wa, wb = a.get("worst_offender") or {}, b.get("worst_offender") or {}
+    if a["accept"] != b["accept"] or a.get("n_failing") != b.get("n_failing") or wa.get("idx") != wb.get("idx") \
+            or bool(wa.get("non_finite")) != bool(wb.get("non_finite")):
+        bad.append(("optout", trial, a, b))
+print("RESULT " + json.dumps({"compare_cases": compare_cases, "gate_cases": gate_cases, "optout_cases": optout_cases, "verdicts": verdicts,
                               "mismatches": [str(m)[:600] for m in bad[:5]], "n_mismatches": len(bad)}))
 """
 
 
 def test_mirror_comparison_and_gate_agree_with_the_reference_harness(tmp_path):
     """The package's mirror of `_compare_oracle_outputs` (oracle_harness.py:865-923) and
-    `_anchored_numerics_gate` (:1479-1548) against the reference's own functions on 600 seeded
+    `_anchored_numerics_gate` (:1479-1548), `load_numerics_optout` (:695-723) and
+    `numerics_optout_applies` (:726-806) against the reference's own functions on 900 seeded
     random cases: matching and perturbed floats of three dtypes, NaNs in the same and in different
     places, dtype, shape and count mismatches, integer and boolean outputs, stochastic indices."""
     import json
 
     out = _run(_MIRROR_SCRIPT, str(tmp_path))
     res = json.loads(next(l for l in out.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
-    assert res["compare_cases"] == 300 and res["gate_cases"] == 300
-    for kind in ("compare", "gate"):   # the cases must exercise both verdicts
+    assert res["compare_cases"] == 300 and res["gate_cases"] == 300 and res["optout_cases"] == 300
+    for kind in ("compare", "gate", "optout"):   # the cases must exercise both verdicts
         assert min(res["verdicts"][kind]) >= 30, res["verdicts"]
     assert res["n_mismatches"] == 0, res["mismatches"]
 
