@@ -484,6 +484,96 @@ def test_mirror_gpu_lock_and_the_reference_lock_exclude_each_other(tmp_path):
     assert res["files"] == ["gpu_3.gate", "gpu_3.lock"]
 
 
+_REGISTRY_SCRIPT = r"""
+import json, random, sys, types
+from pathlib import Path
+sys.path[:0] = [sys.argv[1], sys.argv[2] + "/scripts", sys.argv[2]]
+from better_benchmark_b200 import reference_arm as arm, harness as mirror
+oh, rh = arm._import_reference(Path(sys.argv[2]))
+import torch
+rnd = random.Random(23)
+SHAPES = [(8, 16), (4, 4, 4), (128,), (2, 3), (1, 1, 7, 7)]
+SIGS = [((8, 16),), ((8, 16), (128,)), ((4, 4, 4), (2, 3)), ((128,), (128,), (2, 3)), ((1, 1, 7, 7),)]
+STRINGS = {((8, 16),): "T([8, 16], bf16)", ((8, 16), (128,)): "T([8, 16], f32), T([128], f32), S([8, 16])",
+           ((4, 4, 4), (2, 3)): "T([4, 4, 4], f16), T([2, 3], i64)"}
+KEYS = ("matched", "fallback", "fn_name", "description", "tuned_hardware", "registered_shape", "configs",
+        "current_hardware", "actual_shapes", "dtype_mismatch")
+bad, outcomes = [], {"raise": 0}
+cases = 0
+
+def build(H, name, regs):
+    mod = types.ModuleType(name)
+    sys.modules[name] = mod
+    fns = []
+    for i, (hw, sig, cfg, as_string) in enumerate(regs):
+        src = f"def impl_{i}(inputs, **kw):\n    return ({i}, tuple(sorted(kw.items())))\n"
+        exec(compile(src, name, "exec"), mod.__dict__)
+        fn = mod.__dict__[f"impl_{i}"]
+        fn.__module__ = name
+        shapes = STRINGS[sig] if (as_string and sig in STRINGS) else sig
+        H.oracle_impl(hardware=hw, shapes=shapes, description=f"reg {i}", **cfg)(fn)
+        fns.append(fn)
+    return fns
+
+for trial in range(120):
+    regs = []
+    for _ in range(rnd.randint(1, 6)):
+        hw = rnd.choice([None, "B200", "B200", "H100"])
+        sig = rnd.choice([None, None] + SIGS)
+        cfg = rnd.choice([{}, {"BLOCK": rnd.choice([128, 256])}, {"num_warps": 4, "BLOCK": 64}])
+        regs.append((hw, sig, cfg, rnd.random() < 0.5))
+    fa = build(oh, f"_oracle_synth_ref_{trial}", regs)
+    fb = build(mirror, f"_oracle_synth_mine_{trial}", regs)
+    for kind in ("B200", "H100", "unknown"):
+        oh.get_gpu_kind._cached = kind
+        mirror.get_gpu_kind._cached = kind
+        for _ in range(4):
+            sig = rnd.choice(SIGS + [((3, 3),)])
+            dt = rnd.choice([torch.float32, torch.bfloat16, torch.float16])
+            inputs = [torch.empty(sh, dtype=dt, device="meta") for sh in sig]
+            if rnd.random() < 0.5:
+                inputs.insert(rnd.randint(0, len(inputs)), [8, -1])      # a lifted shape parameter
+            if rnd.random() < 0.3:
+                inputs.append(7)
+            res = []
+            for H, fns in ((oh, fa), (mirror, fb)):
+                try:
+                    fn, info = H.resolve_oracle(fns[0], inputs)
+                    res.append(("ok", fn(inputs), {k: info.get(k) for k in KEYS}))
+                except H.OracleDispatchError:
+                    res.append(("raise", None, None))
+            cases += 1
+            a, b = res
+            if a[0] == "raise":
+                outcomes["raise"] += 1
+            else:
+                outcomes[a[2]["matched"]] = outcomes.get(a[2]["matched"], 0) + 1
+            if a[0] != b[0] or a[1] != b[1]:
+                bad.append((trial, kind, str(a)[:200], str(b)[:200])); continue
+            if a[0] == "ok":
+                for k in KEYS:
+                    if a[2][k] != b[2][k]:
+                        bad.append((trial, kind, k, str(a[2][k])[:120], str(b[2][k])[:120]))
+print("RESULT " + json.dumps({"cases": cases, "outcomes": outcomes, "n_bad": len(bad), "bad": [str(x) for x in bad[:6]]}))
+"""
+
+
+def test_mirror_registration_and_dispatch_agree_with_the_reference(tmp_path):
+    """`oracle_impl` / `OracleRegistry.select` / `resolve_oracle` of the mirror against
+    oracle_harness.py:468-549, :251-340, :557-577 on 120 seeded random registries (hardware or none,
+    signature as tuples or as the repro's T()/S() string or none, bound launch arguments), resolved
+    on three GPU kinds with matching and foreign input signatures: the same entry is chosen (or the
+    same refusal raised), with the same dispatch record."""
+    import json
+
+    out = _run(_REGISTRY_SCRIPT, str(tmp_path))
+    res = json.loads(next(l for l in out.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    assert res["cases"] == 120 * 3 * 4
+    for tier in ("hardware+shape", "shape", "hardware", "any", "raise"):
+        assert res["outcomes"].get(tier, 0) >= 20, res["outcomes"]
+    assert res["n_bad"] == 0, res["bad"]
+
+
 _CHECK_SCRIPT = r"""
 import json, sys
 from pathlib import Path
