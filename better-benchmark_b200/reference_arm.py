@@ -48,7 +48,7 @@ STUB_ROOT = PACKAGE_DIR / "canonical"
 OWN_REPRO_ROOT = REPO_ROOT / "oracle" / "canonical"  # the five benchmark configurations' eager modules
 
 HARNESS_FILES = ("oracle_harness.py", "repro_harness.py", "byte_accounting.py", "input_codec.py",
-                 "scripts/gpu_lock.py", "scripts/bench_parallel.py")
+                 "scripts/gpu_lock.py", "scripts/bench_parallel.py", "scripts/model_graph_accounting.py")
 DIR_FILES = ("repro.py", "oracle.py", "shapes.json", "shapes.txt", "meta.json")
 
 # Directories without a stub here that are still worth timing: the nearest corpus points of the

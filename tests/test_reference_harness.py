@@ -574,6 +574,66 @@ def test_mirror_registration_and_dispatch_agree_with_the_reference(tmp_path):
     assert res["n_bad"] == 0, res["bad"]
 
 
+_ROLLUP_SCRIPT = r"""
+import contextlib, io, json, random, sys
+from pathlib import Path
+sys.path[:0] = [sys.argv[1], sys.argv[2] + "/scripts", sys.argv[2]]
+from better_benchmark_b200 import rollup
+import model_graph_accounting as mga
+rnd = random.Random(31)
+bad, modes = [], {}
+
+def occurrence(h):
+    return mga.PartitionOccurrence(graph_name="g", pattern_hash="p", shape_hash=h, n_ops=1, op_counts={}, origin_ops=[],
+                                   input_shapes=[], max_output_shape=None, has_reduction=False)
+
+def number():
+    return rnd.choice([None, "n/a", round(rnd.uniform(4, 900), 2), round(rnd.uniform(4, 900), 2)])
+
+for trial in range(400):
+    hashes = [f"{rnd.getrandbits(32):08x}" for _ in range(rnd.randint(0, 6))]
+    kind = rnd.random()
+    if kind < 0.1:
+        timing = None
+    elif kind < 0.25:
+        timing = {"oracle_us": number(), "compile_us": number()}                     # a file without per-shape data
+    else:
+        timing = {"oracle_us": number(), "compile_us": number(),
+                  "points_by_shape": {h: rnd.choice([{"oracle_us": number(), "compile_us": number(), "status": "GOOD"},
+                                                     "junk"]) for h in hashes if rnd.random() < 0.7}}
+        if rnd.random() < 0.1:
+            timing = {}
+    uses = [rnd.choice(hashes + ["ffffffff"]) for _ in range(rnd.randint(0, 12))] if hashes else ["ffffffff"] * rnd.randint(0, 3)
+    if hashes and rnd.random() < 0.25:                                                  # every use has a point of its own
+        timing = {"oracle_us": number(), "compile_us": number(),
+                  "points_by_shape": {h: {"oracle_us": round(rnd.uniform(4, 900), 2), "compile_us": number()} for h in hashes}}
+        uses = [rnd.choice(hashes) for _ in range(rnd.randint(1, 12))]
+    with contextlib.redirect_stderr(io.StringIO()):
+        a = mga._rollup_occurrence_timings(timing, [occurrence(h) for h in uses])
+    b = rollup.price_uses(timing, uses)
+    modes[a["mode"]] = modes.get(a["mode"], 0) + 1
+    if a != b:
+        bad.append((trial, a, b))
+print("RESULT " + json.dumps({"cases": 400, "modes": modes, "n_bad": len(bad), "bad": [str(x)[:500] for x in bad[:5]]}))
+"""
+
+
+def test_rollup_pricing_agrees_with_the_reference_accounting(tmp_path):
+    """`rollup.price_uses` against `_rollup_occurrence_timings`
+    (scripts/model_graph_accounting.py:413-535) on 400 seeded random directory records and use
+    lists: per-shape points, missing and non-numeric times, records without per-shape data, untimed
+    directories. Same totals, same matched / fallback / unpriced counts, same mode."""
+    import json
+
+    if not (REF / "scripts" / "model_graph_accounting.py").is_file():
+        pytest.skip("the staged copy predates the accounting script: stage again")
+    out = _run(_ROLLUP_SCRIPT, str(tmp_path))
+    res = json.loads(next(l for l in out.splitlines() if l.startswith("RESULT "))[len("RESULT "):])
+    for mode in ("untimed", "legacy", "per_shape", "partial", "fallback_only"):
+        assert res["modes"].get(mode, 0) >= 10, res["modes"]
+    assert res["n_bad"] == 0, res["bad"]
+
+
 _CHECK_SCRIPT = r"""
 import json, sys
 from pathlib import Path
