@@ -436,8 +436,8 @@ def main(argv=None) -> int:
     ap.add_argument("mode", choices=["stage", "check", "compare", "report", "tasks", "tree"])
     ap.add_argument("inputs", nargs="*", help="report: result files")
     ap.add_argument("--child", action="store_true", help="internal: run the tasks in this process")
-    ap.add_argument("--reference", default=os.environ.get("BETTER_BENCHMARK_CHECKOUT", ""),
-                    help="stage: the reference checkout (default: $BETTER_BENCHMARK_CHECKOUT)")
+    ap.add_argument("--reference", default=os.environ.get("REFERENCE_ROOT", ""),
+                    help="stage: the reference checkout (default: $REFERENCE_ROOT)")
     ap.add_argument("--ref", default=str(DEFAULT_REF), help="the staged copy")
     ap.add_argument("--out", default="reference_arm.jsonl")
     ap.add_argument("--workdir", default="/tmp/b200_reference_arm")
@@ -452,7 +452,7 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     if args.mode == "stage":
         if not args.reference:
-            ap.error("stage needs --reference <checkout of the reference> (or $BETTER_BENCHMARK_CHECKOUT)")
+            ap.error("stage needs --reference <checkout of the reference> (or $REFERENCE_ROOT)")
         print(json.dumps(stage(Path(args.reference), Path(args.ref)), indent=1))
         return 0
     if args.mode == "tree":
